@@ -1,0 +1,67 @@
+"""Batch sources for the training loop.
+
+``dummy_dataloader`` is the reference's random-token loader (``src/training/data/dummy.py:8-29``);
+``synthetic_loader`` yields the benchmark batches (seeded tokens, uniform random document lengths,
+``cu_seqlens`` packing). Every batch is a dict of *pinned host* tensors
+``{input_ids[T], labels[T], cu_seqlens[int32], row_len}`` for one DP rank.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterator, Optional, Tuple
+
+import torch
+
+from .packing import synthetic_packed_batch, pack_chunk_aligned
+
+
+def _pin(t: torch.Tensor) -> torch.Tensor:
+    if torch.cuda.is_available():
+        try:
+            return t.pin_memory()
+        except Exception:
+            return t
+    return t
+
+
+def dummy_dataloader(batch_size: int, seq_len: int, vocab_size: int, seed: int = 0) -> Iterator[Dict]:
+    g = torch.Generator().manual_seed(seed)
+    while True:
+        ids = torch.randint(0, vocab_size, (batch_size * seq_len,), generator=g)
+        labels = ids.clone()
+        cu = torch.arange(0, batch_size * seq_len + 1, seq_len, dtype=torch.int32)
+        labels[cu[:-1].long()] = -100
+        yield {"input_ids": _pin(ids), "labels": _pin(labels), "cu_seqlens": cu, "row_len": seq_len}
+
+
+def synthetic_loader(batch_size: int, seq_len: int, vocab_size: int, seed: int, doc_len_min: int,
+                     doc_len_max: int, align: int = 1, fixed: bool = False) -> Iterator[Dict]:
+    step = 0
+    cached = None
+    while True:
+        if fixed and cached is not None:
+            yield cached
+            continue
+        ids, labels, cu = synthetic_packed_batch(batch_size * seq_len, vocab_size, seed * 100003 + step,
+                                                 doc_len_min, doc_len_max, row_len=seq_len, align=align)
+        cached = {"input_ids": _pin(ids), "labels": _pin(labels), "cu_seqlens": cu, "row_len": seq_len}
+        yield cached
+        step += 1
+
+
+def build_data_iterator(args, cfg, mesh) -> Tuple[Iterator, Optional[object]]:
+    """Per-DP-rank batch iterator. TP ranks of one DP replica draw the same stream (same seed);
+    real-data runs broadcast from the owner rank through :class:`PrefetchBatcher`."""
+    gb = int(getattr(args, "batch_size", 1))
+    assert gb % mesh.dp == 0, f"batch_size {gb} must be divisible by dp {mesh.dp}"
+    lb = gb // mesh.dp
+    seq = int(getattr(args, "seq_len", 512))
+    seed = int(getattr(args, "seed", 0)) * 131 + mesh.dp_rank
+    if getattr(args, "use_dummy_data", False) and not getattr(args, "doc_len_max", 0):
+        return dummy_dataloader(lb, seq, cfg.vocab_size, seed), None
+    if getattr(args, "use_dummy_data", False) or getattr(args, "synthetic_data", False):
+        return synthetic_loader(lb, seq, cfg.vocab_size, seed, int(getattr(args, "doc_len_min", 64)),
+                                int(getattr(args, "doc_len_max", 256)),
+                                int(getattr(args, "doc_align", 1)),
+                                bool(getattr(args, "fixed_batch", False))), None
+    from .streaming import build_streaming_iterator
+    return build_streaming_iterator(args, cfg, mesh, lb, seq)

@@ -1,0 +1,582 @@
+"""Hybrid KDA / full-attention decoder with block attention residuals.
+
+One model class covers TP=1 and TP>1 (with Megatron sequence parallelism): between the
+tensor-parallel regions activations are ``[T/tp, D]`` token shards; inside them the projections
+see all ``T`` tokens and ``H/tp`` heads. The token axis is a packed stream of documents described
+by ``cu_seqlens`` (the batch dimension is folded into it).
+
+Parity notes against the reference (paths relative to its tree):
+  layer wiring        ``src/models/tp_model/layer.py:50-97``, ``kda.py:207-337``
+  block AttnRes       ``src/models/tp_model/model.py:575-727``, ``src/models/ops/attn_res.py:174-295``
+  state_dict keys     ``src/models/model.py:68-107`` (plain layout; written by the state-dict hooks below)
+Not in the reference: full-attention layers with RoPE, sequence parallelism, untied head,
+cu_seqlens-aware KDA under TP, backward collectives and replicated-gradient sync.
+"""
+from __future__ import annotations
+
+import math
+import zlib
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint as _ckpt
+
+from .. import ops
+from ..config import HippoConfig
+from ..parallel.collectives import gather_seq, reduce_scatter_seq, all_reduce_sum, all_gather_dim0, \
+    reduce_scatter_dim0
+from ..parallel.linear import column_linear_sp, row_linear_sp
+from ..parallel.mesh import get_mesh
+from ..ref.ops import positions_from_cu
+from .nvfp4_linear import NVFP4Linear
+
+
+def _pad_to(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+def _seeded(name: str, seed: int) -> torch.Generator:
+    g = torch.Generator(device="cpu")
+    g.manual_seed((zlib.crc32(name.encode()) + seed * 1000003) % (2 ** 31))
+    return g
+
+
+def _xavier(name: str, shape, seed: int) -> torch.Tensor:
+    """TP-invariant init: the full matrix is drawn from a per-name stream, shards are slices."""
+    fan_out, fan_in = shape
+    a = math.sqrt(6.0 / (fan_in + fan_out))
+    return (torch.rand(shape, generator=_seeded(name, seed)) * 2 - 1) * a
+
+
+def _shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[0] // world
+    return w[rank * n:(rank + 1) * n]
+
+
+def _shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[1] // world
+    return w[:, rank * n:(rank + 1) * n]
+
+
+def _mark(p: nn.Parameter, kind: str, replicated: bool = False, **kw) -> nn.Parameter:
+    p.opt_kind = kind
+    p.tp_replicated = replicated
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, device=None, dtype=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = _mark(nn.Parameter(torch.ones(dim, device=device, dtype=dtype)), "adamw", True)
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+# =============================================================================================== KDA
+class KDAAttention(nn.Module):
+    """Kimi delta attention block. Fused column-parallel input projection
+    ``[q | k | v | fg_first | b_proj | pad]`` (one all-gather -> GEMM), low-rank gate
+    projections, chunked KDA, gated per-head RMSNorm, row-parallel output projection."""
+
+    def __init__(self, cfg: HippoConfig, layer_idx: int, seed: int, device, dtype):
+        super().__init__()
+        m = get_mesh()
+        w, r = m.tp, m.tp_rank
+        self.cfg = cfg
+        D, H, K, Vd = cfg.hidden_size, cfg.num_heads, cfg.head_dim, cfg.head_v_dim
+        assert H % w == 0, "num_heads must be divisible by tp"
+        self.Hl = H // w
+        self.key_l, self.val_l = self.Hl * K, self.Hl * Vd
+        pre = f"layers.{layer_idx}.attn."
+        q = _shard_rows(_xavier(pre + "q", (cfg.key_dim, D), seed), r, w)
+        k = _shard_rows(_xavier(pre + "k", (cfg.key_dim, D), seed), r, w)
+        v = _shard_rows(_xavier(pre + "v", (cfg.value_dim, D), seed), r, w)
+        fg = _xavier(pre + "fg_first", (2 * Vd, D), seed)
+        b = _shard_rows(_xavier(pre + "b_proj", (H, D), seed), r, w)
+        self.sections = [self.key_l, self.key_l, self.val_l, 2 * Vd, self.Hl]
+        n_real = sum(self.sections)
+        n_pad = _pad_to(n_real, 64)
+        fused = torch.zeros(n_pad, D)
+        fused[:n_real] = torch.cat([q, k, v, fg, b], 0)
+        self.n_real = n_real
+        o_fg = 2 * self.key_l + self.val_l
+        self.in_proj_weight = _mark(
+            nn.Parameter(fused.to(device=device, dtype=dtype)), "muon",
+            muon_segments=[(0, 2 * self.key_l + self.val_l), (o_fg, o_fg + 2 * Vd), (o_fg + 2 * Vd, n_real)],
+            tp_replicated_rows=(o_fg, o_fg + 2 * Vd))
+        if cfg.use_short_conv:
+            def conv_w(nm, dim_full):
+                full = (torch.rand((dim_full, cfg.conv_size), generator=_seeded(pre + nm, seed)) * 2 - 1) \
+                    / math.sqrt(cfg.conv_size)
+                return _mark(nn.Parameter(_shard_rows(full, r, w).to(device=device, dtype=dtype)), "adamw")
+            self.q_conv1d_weight = conv_w("q_conv1d", cfg.key_dim)
+            self.k_conv1d_weight = conv_w("k_conv1d", cfg.key_dim)
+            self.v_conv1d_weight = conv_w("v_conv1d", cfg.value_dim)
+        self.f_proj1_weight = _mark(nn.Parameter(_shard_rows(
+            _xavier(pre + "f_proj1", (cfg.key_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon")
+        self.g_proj1_weight = _mark(nn.Parameter(_shard_rows(
+            _xavier(pre + "g_proj1", (cfg.value_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon")
+        self.g_proj1_bias = _mark(nn.Parameter(torch.zeros(self.val_l, device=device, dtype=dtype)), "adamw")
+        gen = _seeded(pre + "gate", seed)
+        if cfg.safe_gate:
+            A_full = torch.zeros(H)
+        else:
+            A_full = torch.log(torch.empty(H).uniform_(1, 16, generator=gen))
+        dt = torch.exp(torch.rand(cfg.key_dim, generator=gen) * (math.log(0.1) - math.log(0.001))
+                       + math.log(0.001)).clamp(min=1e-4)
+        dt_bias_full = dt + torch.log(-torch.expm1(-dt))
+        self.A_log = _mark(nn.Parameter(_shard_rows(A_full, r, w).to(device=device, dtype=torch.float32)), "adamw")
+        self.dt_bias = _mark(nn.Parameter(_shard_rows(dt_bias_full, r, w).to(device=device, dtype=torch.float32)),
+                             "adamw")
+        self.o_norm_weight = _mark(nn.Parameter(torch.ones(Vd, device=device, dtype=dtype)), "adamw", True)
+        self.o_proj_weight = _mark(nn.Parameter(_shard_cols(
+            _xavier(pre + "o_proj", (D, cfg.value_dim), seed), r, w).contiguous().to(device=device, dtype=dtype)),
+            "muon")
+        self._register_state_dict_hook(_kda_split_hook)
+        self._register_load_state_dict_pre_hook(_kda_fuse_hook, with_module=True)
+
+    def forward(self, h, cu_seqlens, initial_state):
+        cfg = self.cfg
+        K, Vd, Hl = cfg.head_dim, cfg.head_v_dim, self.Hl
+        proj = column_linear_sp(h, self.in_proj_weight)                       # [T, n_pad]
+        T = proj.shape[0]
+        q, k, v, fg, b, _ = torch.split(proj, self.sections + [proj.shape[1] - self.n_real], dim=1)
+        if cfg.use_short_conv:
+            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_seqlens)
+            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_seqlens)
+            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_seqlens)
+        else:
+            q, k, v = ops.silu(q), ops.silu(k), ops.silu(v)
+        g_raw = ops.linear(fg[:, :Vd].contiguous(), self.f_proj1_weight)
+        gate = ops.linear(fg[:, Vd:].contiguous(), self.g_proj1_weight, self.g_proj1_bias)
+        beta = torch.sigmoid(b.float())
+        if cfg.allow_neg_eigval:
+            beta = beta * 2.0
+        g = ops.kda_gate(g_raw.view(T, Hl, K), self.A_log, self.dt_bias, cfg.safe_gate, cfg.lower_bound)
+        o, final = ops.kda(q.reshape(T, Hl, K), k.reshape(T, Hl, K), v.reshape(T, Hl, Vd), g, beta,
+                           scale=K ** -0.5, initial_state=initial_state, cu_seqlens=cu_seqlens,
+                           use_qk_l2norm=True, mode=cfg.kda_mode)
+        o = ops.gated_rmsnorm(o, gate.view(T, Hl, Vd), self.o_norm_weight, cfg.rms_norm_eps)
+        out = row_linear_sp(o.reshape(T, Hl * Vd), self.o_proj_weight)       # [T/w, D]
+        return out, final
+
+
+def _kda_split_hook(module, state_dict, prefix, local_metadata):
+    """Emit the reference's separate keys instead of the fused storage."""
+    w = state_dict.pop(prefix + "in_proj_weight")
+    s = module.sections
+    o = 0
+    parts = []
+    for n in s:
+        parts.append(w[o:o + n]); o += n
+    state_dict[prefix + "qkv_proj.weight"] = torch.cat(parts[:3], 0)
+    state_dict[prefix + "fg_first.weight"] = parts[3]
+    state_dict[prefix + "b_proj.weight"] = parts[4]
+    for nm in ("f_proj1", "g_proj1", "o_proj", "o_norm", "q_conv1d", "k_conv1d", "v_conv1d"):
+        k = prefix + nm + "_weight"
+        if k in state_dict:
+            state_dict[prefix + nm + ".weight"] = state_dict.pop(k)
+    if prefix + "g_proj1_bias" in state_dict:
+        state_dict[prefix + "g_proj1.bias"] = state_dict.pop(prefix + "g_proj1_bias")
+
+
+def _kda_fuse_hook(module, state_dict, prefix, *args):
+    if prefix + "qkv_proj.weight" in state_dict:
+        qkv = state_dict.pop(prefix + "qkv_proj.weight")
+        fg = state_dict.pop(prefix + "fg_first.weight")
+        b = state_dict.pop(prefix + "b_proj.weight")
+        n_pad = module.in_proj_weight.shape[0]
+        fused = torch.zeros(n_pad, qkv.shape[1], dtype=qkv.dtype, device=qkv.device)
+        fused[:module.n_real] = torch.cat([qkv, fg, b], 0)
+        state_dict[prefix + "in_proj_weight"] = fused
+    for nm in ("f_proj1", "g_proj1", "o_proj", "o_norm", "q_conv1d", "k_conv1d", "v_conv1d"):
+        k = prefix + nm + ".weight"
+        if k in state_dict:
+            state_dict[prefix + nm + "_weight"] = state_dict.pop(k)
+    if prefix + "g_proj1.bias" in state_dict:
+        state_dict[prefix + "g_proj1_bias"] = state_dict.pop(prefix + "g_proj1.bias")
+
+
+# =============================================================================================== full attention
+class FullAttention(nn.Module):
+    """Causal softmax attention with RoPE, head-parallel over the gathered sequence."""
+
+    def __init__(self, cfg: HippoConfig, layer_idx: int, seed: int, device, dtype):
+        super().__init__()
+        m = get_mesh()
+        w, r = m.tp, m.tp_rank
+        self.cfg = cfg
+        D, H, dh = cfg.hidden_size, cfg.num_heads, cfg.head_dim
+        self.Hl = H // w
+        pre = f"layers.{layer_idx}.attn."
+        parts = [_shard_rows(_xavier(pre + n, (H * dh, D), seed), r, w) for n in ("q", "k", "v")]
+        self.qkv_proj_weight = _mark(nn.Parameter(torch.cat(parts, 0).to(device=device, dtype=dtype)), "muon")
+        self.o_proj_weight = _mark(nn.Parameter(_shard_cols(
+            _xavier(pre + "o_proj", (D, H * dh), seed), r, w).contiguous().to(device=device, dtype=dtype)), "muon")
+        self._register_state_dict_hook(_attn_names_out)
+        self._register_load_state_dict_pre_hook(_attn_names_in, with_module=True)
+
+    def forward(self, h, cu_seqlens, positions):
+        cfg = self.cfg
+        dh, Hl = cfg.head_dim, self.Hl
+        qkv = column_linear_sp(h, self.qkv_proj_weight)
+        T = qkv.shape[0]
+        q, k, v = (t.reshape(T, Hl, dh) for t in qkv.split(Hl * dh, dim=1))
+        q, k = ops.rope(q, k, positions, cfg.rope_theta)
+        o = ops.causal_attention(q, k, v, cu_seqlens, dh ** -0.5)
+        return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
+
+
+def _attn_names_out(module, sd, prefix, local_metadata):
+    for nm in ("qkv_proj", "o_proj"):
+        sd[prefix + nm + ".weight"] = sd.pop(prefix + nm + "_weight")
+
+
+def _attn_names_in(module, sd, prefix, *args):
+    for nm in ("qkv_proj", "o_proj"):
+        if prefix + nm + ".weight" in sd:
+            sd[prefix + nm + "_weight"] = sd.pop(prefix + nm + ".weight")
+
+
+# =============================================================================================== FFN
+class SwiGLU(nn.Module):
+    """down(silu(gate(x)) * up(x)); gate and up fused as one column-parallel ``[2I/w, D]`` weight
+    (first half gate, second half up), row-parallel down (``src/models/tp_model/swiglu.py:33-106``)."""
+
+    def __init__(self, cfg: HippoConfig, layer_idx: int, seed: int, device, dtype):
+        super().__init__()
+        m = get_mesh()
+        w, r = m.tp, m.tp_rank
+        D, I = cfg.hidden_size, cfg.intermediate_size
+        assert I % w == 0
+        pre = f"layers.{layer_idx}.ffn."
+        gate = _shard_rows(_xavier(pre + "gate", (I, D), seed), r, w)
+        up = _shard_rows(_xavier(pre + "up", (I, D), seed), r, w)
+        down = _shard_cols(_xavier(pre + "down", (D, I), seed), r, w).contiguous()
+        self.nvfp4 = cfg.ffn_nvfp4
+        if self.nvfp4:
+            nm = cfg.ffn_nvfp4_no_bf16_master
+            self.gate_up_proj = NVFP4Linear(D, 2 * I // w, nm, device, dtype, init_weight=torch.cat([gate, up], 0))
+            self.down_proj = NVFP4Linear(I // w, D, nm, device, dtype, init_weight=down)
+        else:
+            self.gate_up_proj = nn.Module()
+            self.gate_up_proj.weight = _mark(nn.Parameter(torch.cat([gate, up], 0).to(device=device, dtype=dtype)),
+                                             "muon")
+            self.down_proj = nn.Module()
+            self.down_proj.weight = _mark(nn.Parameter(down.to(device=device, dtype=dtype)), "muon")
+
+    def forward(self, h):
+        if self.nvfp4:
+            gu = self.gate_up_proj(gather_seq(h))
+            return reduce_scatter_seq(self.down_proj(ops.swiglu(gu)))
+        gu = column_linear_sp(h, self.gate_up_proj.weight)
+        return row_linear_sp(ops.swiglu(gu), self.down_proj.weight)
+
+
+# =============================================================================================== layer
+class HybridLayer(nn.Module):
+    def __init__(self, cfg: HippoConfig, layer_idx: int, kind: str, seed: int, device, dtype):
+        super().__init__()
+        self.kind = kind
+        self.attn_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)
+        self.attn = (KDAAttention if kind == "kda" else FullAttention)(cfg, layer_idx, seed, device, dtype)
+        self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)
+        self.ffn = SwiGLU(cfg, layer_idx, seed, device, dtype)
+
+    def forward(self, x, cu_seqlens, positions, initial_state):
+        h = self.attn_norm(x)
+        if self.kind == "kda":
+            o, final = self.attn(h, cu_seqlens, initial_state)
+        else:
+            o, final = self.attn(h, cu_seqlens, positions), None
+        x = x + o
+        x = x + self.ffn(self.ffn_norm(x))
+        return x, final
+
+
+# =============================================================================================== AttnRes
+class BlockAttnRes(nn.Module):
+    """Softmax mix over all earlier block outputs with a zero-initialised per-head pseudo-query.
+    Under sequence parallelism every rank mixes its own tokens over all heads, so the reference's
+    head all-gather (``src/models/ops/attn_res.py:115-118``) disappears."""
+
+    def __init__(self, cfg: HippoConfig, device, dtype):
+        super().__init__()
+        H = cfg.num_heads
+        self.query = _mark(nn.Parameter(torch.zeros(H, cfg.hidden_size // H, device=device, dtype=dtype)),
+                           "adamw", True)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)
+        self.eps = cfg.rms_norm_eps
+
+    def forward(self, blocks: List[torch.Tensor]) -> torch.Tensor:
+        return ops.attn_res(blocks, self.query, self.norm.weight, self.eps)
+
+
+# =============================================================================================== embed / head
+class _VocabParallelEmbed(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, v0):
+        m = get_mesh()
+        Vl = weight.shape[0]
+        local = ids - v0
+        mask = (local >= 0) & (local < Vl)
+        rows = weight[local.clamp(0, Vl - 1)] * mask.unsqueeze(-1).to(weight.dtype)
+        ctx.save_for_backward(local, mask)
+        ctx.Vl = Vl
+        return reduce_scatter_dim0(rows, m.tp_group, m.tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        m = get_mesh()
+        local, mask = ctx.saved_tensors
+        gg = all_gather_dim0(g.contiguous(), m.tp_group, m.tp)
+        dw = torch.zeros(ctx.Vl, gg.shape[1], dtype=torch.float32, device=gg.device)
+        sel = mask.nonzero(as_tuple=True)[0]
+        dw.index_add_(0, local[sel], gg[sel].float())
+        return None, dw.to(g.dtype), None
+
+
+class VocabParallelEmbedding(nn.Module):
+    """[V/w, D] shard; lookup of all T tokens, reduce-scattered to the [T/w, D] token shard
+    (``src/models/tp_model/embed.py:23-169`` all-reduces instead)."""
+
+    def __init__(self, cfg: HippoConfig, seed: int, device, dtype):
+        super().__init__()
+        m = get_mesh()
+        assert cfg.vocab_size % m.tp == 0, "vocab_size must be divisible by tp"
+        self.Vl = cfg.vocab_size // m.tp
+        self.v0 = m.tp_rank * self.Vl
+        full = torch.randn((cfg.vocab_size, cfg.hidden_size), generator=_seeded("embed_tokens", seed)) * 0.02
+        self.weight = _mark(nn.Parameter(full[self.v0:self.v0 + self.Vl].to(device=device, dtype=dtype)), "adamw")
+
+    def forward(self, ids):
+        return _VocabParallelEmbed.apply(ids, self.weight, self.v0)
+
+
+class _VocabParallelLCE(torch.autograd.Function):
+    """Fused linear + cross entropy over a vocab-sharded head. Loss, dx and dW are all produced in
+    forward, chunked over tokens so ``[T, V]`` logits never exist
+    (``fla/modules/fused_linear_cross_entropy.py:516-679``). x arrives as the SP token shard."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, targets, v0, num_chunks, n_valid_total):
+        m = get_mesh()
+        x = all_gather_dim0(x_shard, m.tp_group, m.tp)                  # [T, D]
+        T, D = x.shape
+        Vl = weight.shape[0]
+        local_t = targets - v0
+        own = (local_t >= 0) & (local_t < Vl) & (targets >= 0)
+        local_t = torch.where(own, local_t, torch.full_like(local_t, -1))
+        valid = targets >= 0
+        nv = float(n_valid_total)
+        dx = torch.empty_like(x)
+        dw = torch.zeros(Vl, D, dtype=torch.float32, device=x.device)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        cs = max(1, (T + num_chunks - 1) // num_chunks)
+        for s in range(0, T, cs):
+            e = min(T, s + cs)
+            xc = x[s:e]
+            z, mx, se, tz = ops.lce_chunk_stats(xc, weight, local_t[s:e])
+            if m.tp > 1:
+                gmx = mx.clone()
+                dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=m.tp_group)
+                se = se * (mx - gmx).exp()
+                pack = torch.stack([se, tz], 0)
+                dist.all_reduce(pack, group=m.tp_group)
+                se, tz, mx = pack[0], pack[1], gmx
+            lse = mx + se.log()
+            vc = valid[s:e]
+            loss_sum += torch.where(vc, lse - tz, torch.zeros_like(lse)).sum()
+            # dz = (softmax - onehot)/n_valid on valid rows
+            p = (z - lse.unsqueeze(-1)).exp()
+            lt = local_t[s:e]
+            rows = (lt >= 0).nonzero(as_tuple=True)[0]
+            p[rows, lt[rows]] -= 1.0
+            p = p * (vc.unsqueeze(-1).to(p.dtype) / nv)
+            pz = p.to(x.dtype)
+            dx[s:e] = ops.gemm_nn(pz, weight)
+            dw += ops.gemm_tn(pz, xc).float()
+        dx_shard = reduce_scatter_dim0(dx, m.tp_group, m.tp)
+        ctx.save_for_backward(dx_shard, dw.to(weight.dtype))
+        return loss_sum / nv
+
+    @staticmethod
+    def backward(ctx, do):
+        dx, dw = ctx.saved_tensors
+        return dx * do.to(dx.dtype), dw * do.to(dw.dtype), None, None, None, None
+
+
+class LMHeadLoss(nn.Module):
+    def __init__(self, cfg: HippoConfig, embed: VocabParallelEmbedding, seed: int, device, dtype):
+        super().__init__()
+        m = get_mesh()
+        self.cfg = cfg
+        self.Vl = cfg.vocab_size // m.tp
+        self.v0 = m.tp_rank * self.Vl
+        self.tied = cfg.tie_word_embeddings
+        if self.tied:
+            self._embed = [embed]          # not registered: the tied weight lives on the embedding
+        else:
+            full = torch.randn((cfg.vocab_size, cfg.hidden_size), generator=_seeded("lm_head", seed)) * 0.02
+            self.weight = _mark(nn.Parameter(full[self.v0:self.v0 + self.Vl].to(device=device, dtype=dtype)), "adamw")
+
+    def head_weight(self):
+        return self._embed[0].weight if self.tied else self.weight
+
+    def loss(self, x_shard, targets, n_valid_total):
+        return _VocabParallelLCE.apply(x_shard, self.head_weight(), targets, self.v0,
+                                       self.cfg.lce_num_chunks, n_valid_total)
+
+    def logits(self, x_shard):
+        """Inference: full-vocab logits for the gathered tokens (gathers vocab shards)."""
+        m = get_mesh()
+        x = gather_seq(x_shard)
+        z = ops.gemm_nt(x.contiguous(), self.head_weight())
+        if m.tp == 1:
+            return z
+        zs = all_gather_dim0(z.t().contiguous(), m.tp_group, m.tp)       # [V, T]
+        return zs.t()
+
+
+# =============================================================================================== model
+def shift_targets(labels: torch.Tensor, row_len: Optional[int] = None) -> torch.Tensor:
+    """targets[t] = labels[t+1]; the last token of every row (and of the stream) has no target."""
+    t = torch.full_like(labels, -100)
+    t[:-1] = labels[1:]
+    if row_len is not None and row_len > 0:
+        t[row_len - 1::row_len] = -100
+    return t
+
+
+class HippoModel(nn.Module):
+    """forward(input_ids[T], labels[T], cu_seqlens[N+1], kda_states) -> {loss | logits, kda_states}.
+
+    ``input_ids`` may also be ``[B, S]``; it is flattened and ``cu_seqlens`` defaults to row ends.
+    ``n_valid_total`` lets a caller weight a micro-batch loss by the step's total valid tokens
+    (sum over micro-batches then equals the full-step mean, ``loop/run.py:207-263``).
+    """
+
+    def __init__(self, cfg: HippoConfig, device=None, dtype=torch.float32, seed: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        self.mesh = get_mesh()
+        device = device if device is not None else torch.device("cpu")
+        self.embed_tokens = VocabParallelEmbedding(cfg, seed, device, dtype)
+        kinds = cfg.layer_types()
+        self.layers = nn.ModuleList([HybridLayer(cfg, i, kinds[i], seed, device, dtype)
+                                     for i in range(cfg.num_layers)])
+        self.attn_res = BlockAttnRes(cfg, device, dtype) if cfg.num_blocks > 1 else None
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)
+        self.lm_head = LMHeadLoss(cfg, self.embed_tokens, seed, device, dtype)
+        self.kda_layer_ids = [i for i, k in enumerate(kinds) if k == "kda"]
+
+    # ---- parameter views used by the optimizers / grad sync
+    def replicated_parameters(self):
+        return [p for p in self.parameters() if getattr(p, "tp_replicated", False)]
+
+    def partially_replicated_parameters(self):
+        return [p for p in self.parameters() if getattr(p, "tp_replicated_rows", None) is not None]
+
+    def sync_replicated_grads(self):
+        m = self.mesh
+        if m.tp == 1:
+            return
+        grads = [p.grad for p in self.replicated_parameters() if p.grad is not None]
+        grads += [p.grad[p.tp_replicated_rows[0]:p.tp_replicated_rows[1]]
+                  for p in self.partially_replicated_parameters() if p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        all_reduce_sum(flat, m.tp_group, m.tp)
+        off = 0
+        for g in grads:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g)); off += n
+
+    def num_parameters(self) -> int:
+        n = sum(p.numel() for p in self.parameters())
+        n += sum(mod.numel_logical() for mod in self.modules()
+                 if isinstance(mod, NVFP4Linear) and mod.no_master)
+        return n
+
+    def hidden(self, input_ids, cu_seqlens=None, kda_states=None):
+        cfg, m = self.cfg, self.mesh
+        if input_ids.dim() == 2:
+            B, S = input_ids.shape
+            if cu_seqlens is None:
+                cu_seqlens = torch.arange(0, (B + 1) * S, S, device=input_ids.device, dtype=torch.int32)
+            input_ids = input_ids.reshape(-1)
+        T = input_ids.shape[0]
+        if cu_seqlens is None:
+            cu_seqlens = torch.tensor([0, T], device=input_ids.device, dtype=torch.int32)
+        assert T % m.tp == 0, f"token count {T} must be divisible by tp {m.tp}"
+        positions = positions_from_cu(cu_seqlens, T, input_ids.device)
+        x = self.embed_tokens(input_ids)
+        blocks = [x]
+        finals: List[Optional[torch.Tensor]] = []
+        ki = 0
+        for b in range(cfg.num_blocks):
+            if b > 0:
+                x = self.attn_res(blocks)
+            for li in range(b * cfg.block_size, (b + 1) * cfg.block_size):
+                layer = self.layers[li]
+                init = None
+                if layer.kind == "kda":
+                    init = kda_states[ki] if kda_states is not None else None
+                    ki += 1
+                if cfg.gradient_checkpointing and self.training and li != cfg.num_layers - 1:
+                    x, fin = _ckpt(layer, x, cu_seqlens, positions, init, use_reentrant=False)
+                else:
+                    x, fin = layer(x, cu_seqlens, positions, init)
+                if layer.kind == "kda":
+                    finals.append(fin)
+            blocks.append(x)
+        return self.norm(x), finals
+
+    def forward(self, input_ids, labels=None, cu_seqlens=None, kda_states=None,
+                n_valid_total: Optional[float] = None) -> Dict[str, object]:
+        row_len = input_ids.shape[1] if input_ids.dim() == 2 else None
+        h, finals = self.hidden(input_ids, cu_seqlens, kda_states)
+        out: Dict[str, object] = {"kda_states": finals}
+        if labels is not None:
+            targets = shift_targets(labels.reshape(-1), row_len)
+            if n_valid_total is None:
+                n_valid_total = float((targets >= 0).sum().clamp(min=1))
+            out["loss"] = self.lm_head.loss(h, targets, n_valid_total)
+            out["n_valid"] = (targets >= 0).sum()
+        else:
+            out["logits"] = self.lm_head.logits(h)
+        return out
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
+                 top_k: int = 0, eos_token_id: Optional[int] = None) -> torch.Tensor:
+        """Greedy / top-k sampling with a full re-forward per token (``src/models/model.py:180-219``).
+        The prompt is padded to a multiple of tp so the sequence-parallel shard stays even."""
+        ids = input_ids.reshape(-1).clone()
+        w = self.mesh.tp
+        for _ in range(max_new_tokens):
+            T = ids.numel()
+            Tp = _pad_to(T, w)
+            padded = torch.cat([ids, ids.new_zeros(Tp - T)]) if Tp > T else ids
+            cu = torch.tensor([0, Tp], device=ids.device, dtype=torch.int32)
+            logits = self.forward(padded, cu_seqlens=cu)["logits"][T - 1].float()
+            if temperature <= 0:
+                nxt = logits.argmax()
+            else:
+                logits = logits / temperature
+                if top_k > 0:
+                    kth = logits.topk(top_k).values[-1]
+                    logits = logits.masked_fill(logits < kth, float("-inf"))
+                nxt = torch.multinomial(logits.softmax(-1), 1)[0]
+            ids = torch.cat([ids, nxt.reshape(1)])
+            if eos_token_id is not None and int(nxt) == eos_token_id:
+                break
+        return ids

@@ -1,0 +1,156 @@
+"""NVFP4 weight storage for the FFN linears.
+
+Three modes, as in the reference (``src/models/ops/nvfp4_linear.py:245-783``,
+``nvfp4_tp.py:341-935``):
+
+  bf16 master + STE   ``weight`` is a bf16 Parameter, re-quantised every forward
+  no master           only ``packed_weight`` u8 [N,K/2], ``scales`` e4m3 [N,K/16] and
+                      ``global_scale`` f32 [1] exist; the optimizer streams row chunks through
+                      ``material_chunk`` / ``commit_chunk`` / ``decay_and_apply_chunk``
+  (bf16 only = a plain bf16 weight; handled by the caller)
+
+Differences from the reference, on purpose: the GEMMs run on the FP4 tensor cores with
+activations quantised on the fly (the reference is W4A16 through Marlin), the element rounding
+is hardware RN-even, and ``global_scale`` is kept per module and recomputed on re-quantisation
+instead of being pinned to 1.0.
+"""
+from __future__ import annotations
+
+from typing import Iterator, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+class _NVFP4MatmulNoMaster(torch.autograd.Function):
+    """y = Q(x) dq(W)^T.  dX = dY dq(W);  dW = dY^T x is handed to ``module.grad_sink`` (no leaf)."""
+
+    @staticmethod
+    def forward(ctx, x, module, anchor):
+        ctx.module = module
+        ctx.save_for_backward(x)
+        return ops.nvfp4_linear(x, module.packed_weight, module.scales, module.global_scale,
+                                act_quant=module.act_quant)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        mod = ctx.module
+        dy = dy.contiguous()
+        w = ops.nvfp4_dequantize(mod.packed_weight, mod.scales, mod.global_scale, dy.dtype)
+        dx = ops.gemm_nn(dy, w)
+        dw = ops.gemm_tn(dy, x)
+        mod._accumulate_grad(dw)
+        return dx, None, None
+
+
+class _NVFP4MatmulSTE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, act_quant):
+        packed, scales, gs = ops.nvfp4_quantize(weight.detach())
+        ctx.save_for_backward(x, packed, scales, gs)
+        ctx.wdtype = weight.dtype
+        return ops.nvfp4_linear(x, packed, scales, gs, act_quant=act_quant)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, packed, scales, gs = ctx.saved_tensors
+        dy = dy.contiguous()
+        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)
+        return ops.gemm_nn(dy, w), ops.gemm_tn(dy, x).to(ctx.wdtype), None
+
+
+class NVFP4Linear(nn.Module):
+    """[out_features, in_features] linear stored (or trained through) NVFP4. No bias."""
+
+    CHUNK_ROWS = 4096
+
+    def __init__(self, in_features: int, out_features: int, no_master: bool, device=None,
+                 dtype=torch.bfloat16, act_quant: bool = True, init_weight: Optional[torch.Tensor] = None):
+        super().__init__()
+        assert in_features % 16 == 0
+        self.in_features, self.out_features = in_features, out_features
+        self.no_master = no_master
+        self.act_quant = act_quant
+        self.compute_dtype = dtype
+        if init_weight is None:
+            init_weight = torch.empty(out_features, in_features, device=device, dtype=torch.float32)
+            nn.init.xavier_uniform_(init_weight)
+        if no_master:
+            packed, scales, gs = ops.nvfp4_quantize(init_weight.to(device=device))
+            self.register_buffer("packed_weight", packed)
+            self.register_buffer("scales", scales)
+            self.register_buffer("global_scale", gs.float())
+            self.grad_w: Optional[torch.Tensor] = None      # accumulated dW (no autograd leaf exists)
+            self.grad_sink = None                            # optional callback(dw) e.g. host offload
+            # gives autograd something to hang the Function on when x does not require grad
+            self.register_buffer("_anchor", torch.zeros(1, device=device), persistent=False)
+        else:
+            self.weight = nn.Parameter(init_weight.to(device=device, dtype=dtype))
+            self.weight.opt_kind = "muon"
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.no_master:
+            return _NVFP4MatmulNoMaster.apply(x, self, self._anchor.requires_grad_(False))
+        return _NVFP4MatmulSTE.apply(x, self.weight, self.act_quant)
+
+    def _accumulate_grad(self, dw: torch.Tensor) -> None:
+        if self.grad_sink is not None:
+            self.grad_sink(self, dw)
+        elif self.grad_w is None:
+            self.grad_w = dw.clone()
+        else:
+            self.grad_w.add_(dw)
+
+    # ------------------------------------------------------------------ chunk API (optimizer side)
+    def chunk_ranges(self, rows: Optional[int] = None) -> Iterator[Tuple[int, int]]:
+        rows = rows or self.CHUNK_ROWS
+        for r0 in range(0, self.out_features, rows):
+            yield r0, min(r0 + rows, self.out_features)
+
+    def material_chunk(self, r0: int, r1: int, dtype=torch.float32) -> torch.Tensor:
+        return ops.nvfp4_dequantize(self.packed_weight[r0:r1], self.scales[r0:r1], self.global_scale, dtype)
+
+    def commit_chunk(self, r0: int, r1: int, w: torch.Tensor) -> None:
+        """Re-quantise rows [r0, r1) against the module's current global scale."""
+        packed, scales, _ = ops.nvfp4_quantize(w, self.global_scale)
+        self.packed_weight[r0:r1].copy_(packed)
+        self.scales[r0:r1].copy_(scales)
+
+    def apply_chunk_update(self, r0: int, r1: int, update: torch.Tensor, lr: float) -> None:
+        self.decay_and_apply_chunk(r0, r1, update, lr, 1.0)
+
+    def decay_and_apply_chunk(self, r0: int, r1: int, update: torch.Tensor, lr: float,
+                              wd_factor: float = 1.0) -> None:
+        """W[r0:r1] <- W*wd_factor - lr*update, then re-quantise those rows."""
+        w = self.material_chunk(r0, r1, torch.float32)
+        w.mul_(wd_factor).add_(update.float(), alpha=-lr)
+        self.commit_chunk(r0, r1, w)
+
+    def material_bf16_view(self) -> torch.Tensor:
+        return self.material_chunk(0, self.out_features, torch.bfloat16)
+
+    def commit_bf16_view(self, w: torch.Tensor) -> None:
+        """Full re-quantisation; also refreshes the tensor-level scale."""
+        packed, scales, gs = ops.nvfp4_quantize(w.float())
+        self.packed_weight.copy_(packed); self.scales.copy_(scales); self.global_scale.copy_(gs)
+
+    def refresh_global_scale(self, headroom: float = 1.0) -> None:
+        """Re-derive global_scale from the current contents (keeps e4m3 scales in range as W grows)."""
+        self.commit_bf16_view(self.material_chunk(0, self.out_features, torch.float32))
+
+    def numel_logical(self) -> int:
+        return self.in_features * self.out_features
+
+
+def nvfp4_modules(model: nn.Module) -> List[NVFP4Linear]:
+    return [m for m in model.modules() if isinstance(m, NVFP4Linear) and m.no_master]
+
+
+def repack_nvfp4_weights(model: nn.Module) -> int:
+    """Kept for API parity with ``nvfp4_linear.py:repack_nvfp4_weights``: the FP4 tensor-core
+    layout is the storage layout, so nothing has to be rebuilt after an optimizer step."""
+    return len(nvfp4_modules(model))

@@ -1,0 +1,206 @@
+"""Device dispatch: CUDA tensors -> sm_100a extension, CPU tensors -> torch oracle."""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..ref import kda as _rk
+from ..ref import ops as _ro
+
+
+def _cu():
+    from . import cuda_ops
+    return cuda_ops
+
+
+def cuda_ext_loaded() -> bool:
+    try:
+        from . import _ext
+        return _ext.is_loaded()
+    except Exception:
+        return False
+
+
+# ----------------------------------------------------------------------------- GEMMs
+def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a[M,K] @ b[N,K]^T -> [M,N]."""
+    if a.is_cuda:
+        return _cu().gemm_nt(a, b)
+    return a @ b.t()
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a[M,N] @ b[N,K] -> [M,K]."""
+    if a.is_cuda:
+        return _cu().gemm_nn(a, b)
+    return a @ b
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a[M,N]^T @ b[M,K] -> [N,K]."""
+    if a.is_cuda:
+        return _cu().gemm_tn(a, b)
+    return a.t() @ b
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        y = gemm_nt(x, w)
+        if bias is not None:
+            y = y + bias
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm_nn(dy, w) if ctx.needs_input_grad[0] else None
+        dw = gemm_tn(dy, x).to(w.dtype) if ctx.needs_input_grad[1] else None
+        db = dy.sum(0) if ctx.has_bias else None
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x W^T (+ b) on 2-D x."""
+    if x.is_cuda:
+        return _Linear.apply(x.contiguous(), w, bias)
+    return F.linear(x, w, bias)
+
+
+# ----------------------------------------------------------------------------- row ops
+def rmsnorm(x, weight, eps: float):
+    if x.is_cuda:
+        return _cu().rmsnorm(x, weight, eps)
+    return _ro.rmsnorm(x, weight, eps)
+
+
+def swiglu(gate_up):
+    if gate_up.is_cuda:
+        return _cu().swiglu(gate_up)
+    return _ro.swiglu(gate_up)
+
+
+def silu(x):
+    if x.is_cuda:
+        return _cu().silu(x)
+    return F.silu(x)
+
+
+def l2norm(x, eps: float = 1e-6):
+    return _rk.l2norm(x, eps)
+
+
+def gated_rmsnorm(o, gate, weight, eps: float):
+    if o.is_cuda:
+        return _cu().gated_rmsnorm(o, gate, weight, eps)
+    return _rk.gated_rmsnorm(o, gate, weight, eps)
+
+
+def short_conv_silu(x, weight, bias, cu_seqlens):
+    return _rk.short_conv_silu(x, weight, bias, cu_seqlens)
+
+
+# ----------------------------------------------------------------------------- KDA
+def kda_gate(x_g, A_log, dt_bias, safe_gate: bool = False, lower_bound: float = -5.0):
+    if x_g.is_cuda:
+        return _cu().kda_gate(x_g, A_log, dt_bias, safe_gate, lower_bound)
+    return _rk.kda_gate(x_g, A_log, dt_bias, safe_gate, lower_bound)
+
+
+def kda(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
+        use_qk_l2norm: bool = True, mode: str = "chunk") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Kimi delta attention over a packed token stream; see :mod:`hippolm_b200.ref.kda`."""
+    if q.is_cuda:
+        return _cu().kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+    if mode == "fused_recurrent":
+        return _rk.kda_recurrent(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+    return _rk.kda_chunked(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+
+
+# ----------------------------------------------------------------------------- attention
+def rope(q, k, positions, theta: float = 10000.0):
+    if q.is_cuda:
+        return _cu().rope(q, k, positions, theta)
+    cos, sin = _ro.rope_tables(positions, q.shape[-1], theta)
+    return _ro.apply_rope(q, cos, sin), _ro.apply_rope(k, cos, sin)
+
+
+def causal_attention(q, k, v, cu_seqlens, scale=None):
+    if q.is_cuda:
+        return _cu().causal_attention(q, k, v, cu_seqlens, scale)
+    return _ro.causal_attention(q, k, v, cu_seqlens, scale)
+
+
+def attn_res(sources: List[torch.Tensor], query, norm_weight, eps: float):
+    """sources: list of [T, D] tensors (oldest first)."""
+    if sources[0].is_cuda:
+        return _cu().attn_res(sources, query, norm_weight, eps)
+    return _ro.attn_res(torch.stack(sources, 0), query, norm_weight, eps)
+
+
+# ----------------------------------------------------------------------------- NVFP4
+def nvfp4_quantize(w, global_scale=None):
+    if w.is_cuda:
+        return _cu().nvfp4_quantize(w, global_scale)
+    return _ro.nvfp4_quantize(w, global_scale)
+
+
+def nvfp4_dequantize(packed, scales, global_scale, dtype=torch.float32):
+    if packed.is_cuda:
+        return _cu().nvfp4_dequantize(packed, scales, global_scale, dtype)
+    return _ro.nvfp4_dequantize(packed, scales, global_scale, dtype)
+
+
+def nvfp4_linear(x, packed, scales, global_scale, act_quant: bool = True):
+    """y = Q(x) @ dq(W)^T with block-scaled FP4 operands (fp32 accumulate)."""
+    if x.is_cuda:
+        return _cu().nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant)
+    w = _ro.nvfp4_dequantize(packed, scales, global_scale, torch.float32)
+    xf = x.float()
+    if act_quant:
+        xf = _ro.nvfp4_dequantize(*_ro.nvfp4_quantize(xf), dtype=torch.float32)
+    return (xf @ w.t()).to(x.dtype)
+
+
+# ----------------------------------------------------------------------------- optimizer math
+def newton_schulz5(G, steps: int = 5, eps: float = 1e-7):
+    if G.is_cuda:
+        return _cu().newton_schulz5(G, steps, eps)
+    return _ro.newton_schulz5(G, steps, eps)
+
+
+def adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale: float = 1.0):
+    """In-place standard AdamW (both bias corrections) on one tensor."""
+    if p.is_cuda:
+        return _cu().adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale)
+    gf = g.float() * grad_scale
+    mf = m.float().mul_(beta1).add_(gf, alpha=1 - beta1)
+    vf = v.float().mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
+    m.copy_(mf); v.copy_(vf)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    upd = (mf / bc1) / ((vf / bc2).sqrt() + eps)
+    pf = p.float().mul_(1 - lr * wd).add_(upd, alpha=-lr)
+    p.copy_(pf)
+
+
+# ----------------------------------------------------------------------------- LCE building block
+def lce_chunk_stats(x, w, targets_local):
+    """For one token chunk: logits = x @ w^T (fp32), returns (logits, rowmax, sumexp, target_logit).
+
+    targets_local: index into this rank's vocab shard, or -1 when the target lives elsewhere / ignored.
+    """
+    if x.is_cuda:
+        return _cu().lce_chunk_stats(x, w, targets_local)
+    z = x.float() @ w.float().t()
+    mx = z.max(-1).values
+    se = (z - mx.unsqueeze(-1)).exp().sum(-1)
+    tl = targets_local.clamp(min=0)
+    tz = z.gather(1, tl.unsqueeze(1)).squeeze(1)
+    tz = torch.where(targets_local >= 0, tz, torch.zeros_like(tz))
+    return z, mx, se, tz

@@ -1,0 +1,314 @@
+"""Muon (Newton-Schulz) for matrices, AdamW for everything else, global grad-norm clip.
+
+Device-resident by default (B200 has the HBM for it); ``offload=True`` keeps the optimizer state
+in pinned host memory and streams it through the GPU per parameter, which is the reference's only
+mode (``src/training/param_offload/muon.py:294-499``, ``adamw.py:233-432``).
+
+Formulas (``muon.py:247-287,392-473``):
+  M <- beta M + G;  U = G + beta M (nesterov);  W <- W (1 - lr wd) - lr NS5(U)
+AdamW here is the standard one (v from g^2, both bias corrections); ``reference_compat=True``
+reproduces the reference's variant (v from m^2, no first-moment correction, ``adamw.py:257-302``).
+Differences on purpose: NS runs on the whole (local) matrix, not on 4096-row slices
+(``ns_row_chunk`` restores slices); fused projections are orthogonalised per ``muon_segments``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..config import PrecisionConfig
+from ..models.nvfp4_linear import NVFP4Linear
+from ..parallel.mesh import get_mesh
+
+
+def _pinned_like(shape, dtype) -> torch.Tensor:
+    t = torch.zeros(shape, dtype=dtype)
+    if torch.cuda.is_available():
+        try:
+            t = t.pin_memory()
+        except Exception:
+            pass
+    return t
+
+
+class _Entry:
+    """One optimised tensor: a Parameter, or a no-master NVFP4 module (``param is None``)."""
+
+    def __init__(self, param: Optional[nn.Parameter], module: Optional[NVFP4Linear], name: str):
+        self.param, self.module, self.name = param, module, name
+        self.step = 0
+        self.exp_avg: Optional[torch.Tensor] = None
+        self.exp_avg_sq: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return tuple(self.param.shape) if self.param is not None else \
+            (self.module.out_features, self.module.in_features)
+
+    @property
+    def device(self):
+        return self.param.device if self.param is not None else self.module.packed_weight.device
+
+    def grad(self) -> Optional[torch.Tensor]:
+        return self.param.grad if self.param is not None else self.module.grad_w
+
+    def clear_grad(self):
+        if self.param is not None:
+            self.param.grad = None
+        else:
+            self.module.grad_w = None
+
+
+class Muon:
+    def __init__(self, lr: float = 0.02, momentum: float = 0.95, weight_decay: float = 0.0,
+                 nesterov: bool = True, ns_steps: int = 5, momentum_dtype=torch.bfloat16,
+                 offload: bool = False, ns_row_chunk: Optional[int] = None):
+        self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
+        self.nesterov, self.ns_steps = nesterov, ns_steps
+        self.momentum_dtype = momentum_dtype
+        self.offload = offload
+        self.ns_row_chunk = ns_row_chunk
+        self.entries: List[_Entry] = []
+
+    def set_lr(self, lr: float):
+        self.lr = lr
+
+    def add_param(self, p: nn.Parameter, name: str = ""):
+        assert p.ndim == 2, f"Muon takes 2-D weights, got {tuple(p.shape)} for {name}"
+        self._alloc(_Entry(p, None, name))
+
+    def register_nvfp4_module(self, mod: NVFP4Linear, name: str = ""):
+        self._alloc(_Entry(None, mod, name))
+
+    def _alloc(self, e: _Entry):
+        if self.offload:
+            e.exp_avg = _pinned_like(e.shape, self.momentum_dtype)
+        else:
+            e.exp_avg = torch.zeros(e.shape, dtype=self.momentum_dtype, device=e.device)
+        self.entries.append(e)
+
+    def _segments(self, e: _Entry) -> List[Tuple[int, int]]:
+        rows = e.shape[0]
+        segs = getattr(e.param, "muon_segments", None) if e.param is not None else None
+        segs = segs or [(0, rows)]
+        if self.ns_row_chunk:
+            out = []
+            for a, b in segs:
+                out += [(r, min(r + self.ns_row_chunk, b)) for r in range(a, b, self.ns_row_chunk)]
+            segs = out
+        return segs
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0):
+        for e in self.entries:
+            g = e.grad()
+            if g is None:
+                continue
+            dev = e.device
+            gf = g.to(torch.float32)
+            if grad_scale != 1.0:
+                gf = gf * grad_scale
+            m = e.exp_avg.to(dev, non_blocking=True).float() if self.offload else e.exp_avg.float()
+            m.mul_(self.momentum).add_(gf)
+            u = gf.add(m, alpha=self.momentum) if self.nesterov else m
+            if self.offload:
+                e.exp_avg.copy_(m.to(self.momentum_dtype), non_blocking=True)
+            else:
+                e.exp_avg.copy_(m)
+            wd_factor = 1.0 - self.lr * self.weight_decay
+            for (a, b) in self._segments(e):
+                if b <= a:
+                    continue
+                upd = ops.newton_schulz5(u[a:b], self.ns_steps)
+                if e.param is not None:
+                    pw = e.param.data[a:b]
+                    if wd_factor != 1.0:
+                        pw.mul_(wd_factor)
+                    pw.add_(upd.to(pw.dtype), alpha=-self.lr)
+                else:
+                    for r0, r1 in e.module.chunk_ranges():
+                        lo, hi = max(r0, a), min(r1, b)
+                        if lo < hi:
+                            e.module.decay_and_apply_chunk(lo, hi, upd[lo - a:hi - a], self.lr, wd_factor)
+            e.step += 1
+
+    def zero_grad(self):
+        for e in self.entries:
+            e.clear_grad()
+
+    def state_dict(self) -> Dict:
+        return {"lr": self.lr, "momentum": self.momentum, "weight_decay": self.weight_decay,
+                "nesterov": self.nesterov, "ns_steps": self.ns_steps,
+                "state": [{"shape": list(e.shape), "step": e.step,
+                           "kind": "nvfp4" if e.param is None else "param", "name": e.name,
+                           "grad": None, "exp_avg": e.exp_avg.detach().cpu().clone()} for e in self.entries]}
+
+    def load_state_dict(self, sd: Dict):
+        for k in ("lr", "momentum", "weight_decay", "nesterov", "ns_steps"):
+            if k in sd:
+                setattr(self, k, sd[k])
+        st = sd["state"]
+        if len(st) != len(self.entries):
+            raise ValueError(f"Muon state has {len(st)} entries, optimizer has {len(self.entries)}")
+        for e, s in zip(self.entries, st):
+            if tuple(s["shape"]) != e.shape:
+                raise ValueError(f"shape mismatch for {e.name}: {s['shape']} vs {e.shape}")
+            e.step = s["step"]
+            e.exp_avg.copy_(s["exp_avg"].to(e.exp_avg.dtype))
+
+
+class AdamW:
+    def __init__(self, lr: float = 0.004, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.01,
+                 m_dtype=torch.bfloat16, v_dtype=torch.bfloat16, offload: bool = False,
+                 reference_compat: bool = False):
+        self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
+        self.m_dtype, self.v_dtype, self.offload = m_dtype, v_dtype, offload
+        self.reference_compat = reference_compat
+        self.entries: List[_Entry] = []
+
+    def set_lr(self, lr: float):
+        self.lr = lr
+
+    def add_param(self, p: nn.Parameter, name: str = ""):
+        e = _Entry(p, None, name)
+        if self.offload:
+            e.exp_avg = _pinned_like(e.shape, self.m_dtype)
+            e.exp_avg_sq = _pinned_like(e.shape, self.v_dtype)
+        else:
+            e.exp_avg = torch.zeros(e.shape, dtype=self.m_dtype, device=p.device)
+            e.exp_avg_sq = torch.zeros(e.shape, dtype=self.v_dtype, device=p.device)
+        self.entries.append(e)
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0):
+        b1, b2 = self.betas
+        for e in self.entries:
+            g = e.grad()
+            if g is None:
+                continue
+            e.step += 1
+            p = e.param.data
+            if self.offload:
+                m = e.exp_avg.to(p.device, non_blocking=True)
+                v = e.exp_avg_sq.to(p.device, non_blocking=True)
+            else:
+                m, v = e.exp_avg, e.exp_avg_sq
+            if self.reference_compat:
+                gf = g.float() * grad_scale
+                mf = m.float().mul_(b1).add_(gf, alpha=1 - b1)
+                vf = v.float().mul_(b2).addcmul_(mf, mf, value=1 - b2)
+                m.copy_(mf); v.copy_(vf)
+                upd = mf / ((vf / (1 - b2 ** e.step)).sqrt() + self.eps)
+                p.copy_(p.float().mul_(1 - self.lr * self.weight_decay).add_(upd, alpha=-self.lr))
+            else:
+                ops.adamw_update(p, g, m, v, self.lr, b1, b2, self.eps, self.weight_decay, e.step, grad_scale)
+            if self.offload:
+                e.exp_avg.copy_(m, non_blocking=True)
+                e.exp_avg_sq.copy_(v, non_blocking=True)
+
+    def zero_grad(self):
+        for e in self.entries:
+            e.clear_grad()
+
+    def state_dict(self) -> Dict:
+        return {"lr": self.lr, "betas": list(self.betas), "eps": self.eps, "weight_decay": self.weight_decay,
+                "state": [{"shape": list(e.shape), "step": e.step, "kind": "param", "name": e.name, "grad": None,
+                           "exp_avg": e.exp_avg.detach().cpu().clone(),
+                           "exp_avg_sq": e.exp_avg_sq.detach().cpu().clone()} for e in self.entries]}
+
+    def load_state_dict(self, sd: Dict):
+        for k in ("lr", "eps", "weight_decay"):
+            if k in sd:
+                setattr(self, k, sd[k])
+        if "betas" in sd:
+            self.betas = tuple(sd["betas"])
+        st = sd["state"]
+        if len(st) != len(self.entries):
+            raise ValueError(f"AdamW state has {len(st)} entries, optimizer has {len(self.entries)}")
+        for e, s in zip(self.entries, st):
+            if tuple(s["shape"]) != e.shape:
+                raise ValueError(f"shape mismatch for {e.name}: {s['shape']} vs {e.shape}")
+            e.step = s["step"]
+            e.exp_avg.copy_(s["exp_avg"].to(e.exp_avg.dtype))
+            e.exp_avg_sq.copy_(s["exp_avg_sq"].to(e.exp_avg_sq.dtype))
+
+
+def build_param_groups(model: nn.Module, args=None, precision: Optional[PrecisionConfig] = None,
+                       offload: bool = False) -> Tuple[Muon, AdamW]:
+    """Route parameters (``src/training/param_offload/param_groups.py:27-153``): embeddings, head,
+    norms, biases, conv taps, gate scalars and the AttnRes query -> AdamW; every other 2-D weight
+    and every no-master NVFP4 module -> Muon (nesterov, 5 NS steps)."""
+    prec = precision or PrecisionConfig()
+    g = (lambda k, d: getattr(args, k, d) if args is not None else d)
+    muon = Muon(lr=g("muon_lr", 0.02), momentum=g("muon_momentum", 0.95),
+                weight_decay=g("muon_weight_decay", 0.0), nesterov=True, ns_steps=5,
+                momentum_dtype=prec.muon_momentum, offload=offload,
+                ns_row_chunk=g("muon_ns_row_chunk", None))
+    adamw = AdamW(lr=g("learning_rate", 0.004), betas=(g("adamw_beta1", 0.9), g("adamw_beta2", 0.95)),
+                  eps=g("adamw_eps", 1e-8), weight_decay=g("weight_decay", 0.01),
+                  m_dtype=prec.adamw_m, v_dtype=prec.adamw_v, offload=offload,
+                  reference_compat=bool(g("adamw_reference_compat", False)))
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        kind = getattr(p, "opt_kind", None)
+        if kind is None:
+            kind = "muon" if (p.ndim == 2 and "embed" not in name and "lm_head" not in name) else "adamw"
+        if kind == "muon" and p.ndim == 2:
+            muon.add_param(p, name)
+        else:
+            adamw.add_param(p, name)
+    for name, mod in model.named_modules():
+        if isinstance(mod, NVFP4Linear) and mod.no_master:
+            muon.register_nvfp4_module(mod, name)
+    return muon, adamw
+
+
+@torch.no_grad()
+def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None) -> torch.Tensor:
+    """||G||_2 over every gradient of the whole model (device-side; the reference reduces a host
+    fp64 scalar, ``src/training/loop/grad_norm.py:97-165``). TP-sharded tensors are summed over
+    the TP group; replicated ones are counted once."""
+    m = mesh or get_mesh()
+    dev = None
+    sharded = None
+    repl = None
+    for e in list(muon.entries) + list(adamw.entries):
+        g = e.grad()
+        if g is None:
+            continue
+        dev = g.device
+        gf = g.float()
+        rows = getattr(e.param, "tp_replicated_rows", None) if e.param is not None else None
+        is_repl = e.param is not None and getattr(e.param, "tp_replicated", False)
+        if is_repl:
+            s = gf.pow(2).sum(); repl = s if repl is None else repl + s
+        elif rows is not None:
+            a, b = rows
+            r = gf[a:b].pow(2).sum()
+            s = gf.pow(2).sum() - r
+            repl = r if repl is None else repl + r
+            sharded = s if sharded is None else sharded + s
+        else:
+            s = gf.pow(2).sum(); sharded = s if sharded is None else sharded + s
+    if dev is None:
+        return torch.zeros(())
+    z = torch.zeros((), device=dev)
+    sharded = z if sharded is None else sharded
+    repl = z if repl is None else repl
+    if m.tp > 1:
+        sharded = sharded.clone()
+        dist.all_reduce(sharded, group=m.tp_group)
+    return (sharded + repl).sqrt()
+
+
+def clip_coefficient(norm: float, max_norm: float) -> float:
+    """coef = max_norm/(norm+1e-6) applied only when norm > max_norm (``grad_norm.py:150-165``)."""
+    if max_norm is None or max_norm <= 0 or not math.isfinite(norm) or norm <= max_norm:
+        return 1.0
+    return max_norm / (norm + 1e-6)

@@ -1,0 +1,38 @@
+"""Fused compute + collective kernels over NVSwitch peer memory (entry points).
+
+``setup()`` allocates the symmetric workspace for the current TP group and switches the
+sequence-parallel linears from "NCCL then GEMM" to the single-kernel paths in
+``csrc/fused_comm.cu``. Until it is called (or on CPU) ``enabled()`` is False and the NCCL/gloo
+baseline runs.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+_STATE = {"ws": None}
+
+
+def enabled() -> bool:
+    return _STATE["ws"] is not None
+
+
+def setup(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16) -> bool:
+    from . import symm
+    ws = symm.create_workspace(mesh, max_tokens, max_width, dtype)
+    _STATE["ws"] = ws
+    return ws is not None
+
+
+def teardown() -> None:
+    _STATE["ws"] = None
+
+
+def allgather_gemm(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+    return _STATE["ws"].allgather_gemm(x, weight, transpose_w)
+
+
+def gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False) -> torch.Tensor:
+    return _STATE["ws"].gemm_reduce_scatter(x, weight, transpose_w)

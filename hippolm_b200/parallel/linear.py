@@ -1,0 +1,96 @@
+"""Sequence-parallel tensor-parallel linears.
+
+  column_linear_sp : x[T/w, K] --all-gather--> [T, K] @ W[N/w, K]^T -> [T, N/w]
+  row_linear_sp    : x[T, K/w] @ W[N, K/w]^T --reduce-scatter--> [T/w, N]
+
+Backward runs the conjugate collective (reduce-scatter / all-gather), which the reference's
+ColumnParallelLinear omits (``src/models/tp_model/_primitives.py:306-309``). On CUDA with a
+symmetric-memory workspace the collective is fused into the GEMM kernel
+(:mod:`hippolm_b200.parallel.fused`); otherwise NCCL/gloo + the plain GEMM op run back to back.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .collectives import all_gather_dim0, reduce_scatter_dim0
+from .mesh import get_mesh
+
+
+def _fused():
+    from . import fused
+    return fused if fused.enabled() else None
+
+
+class _ColumnLinearSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        m = get_mesh()
+        f = _fused()
+        if f is not None and x.is_cuda and m.tp > 1:
+            xg, y = f.allgather_gemm(x, weight)
+        else:
+            xg = all_gather_dim0(x, m.tp_group, m.tp)
+            y = ops.gemm_nt(xg, weight)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        m = get_mesh()
+        dy = dy.contiguous()
+        f = _fused()
+        dxg = None
+        if ctx.needs_input_grad[0]:
+            if f is not None and dy.is_cuda and m.tp > 1:
+                dx = f.gemm_reduce_scatter(dy, weight, transpose_w=True)
+            else:
+                dxg = ops.gemm_nn(dy, weight)                      # [T, K]
+                dx = reduce_scatter_dim0(dxg, m.tp_group, m.tp)
+        else:
+            dx = None
+        xg = all_gather_dim0(x, m.tp_group, m.tp)
+        dw = ops.gemm_tn(dy, xg)                                   # [N/w, K]
+        db = dy.sum(0) if ctx.has_bias else None
+        return dx, dw.to(weight.dtype), db
+
+
+class _RowLinearSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        m = get_mesh()
+        f = _fused()
+        if f is not None and x.is_cuda and m.tp > 1:
+            y = f.gemm_reduce_scatter(x, weight, transpose_w=False)
+        else:
+            y = reduce_scatter_dim0(ops.gemm_nt(x, weight), m.tp_group, m.tp)
+        ctx.save_for_backward(x, weight)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        m = get_mesh()
+        f = _fused()
+        dy = dy.contiguous()
+        if f is not None and dy.is_cuda and m.tp > 1:
+            dyg, dx = f.allgather_gemm(dy, weight, transpose_w=True)
+        else:
+            dyg = all_gather_dim0(dy, m.tp_group, m.tp)            # [T, N]
+            dx = ops.gemm_nn(dyg, weight)                          # [T, K/w]
+        dw = ops.gemm_tn(dyg, x)                                   # [N, K/w]
+        return dx, dw.to(weight.dtype)
+
+
+def column_linear_sp(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    return _ColumnLinearSP.apply(x, weight, bias)
+
+
+def row_linear_sp(x: torch.Tensor, weight: torch.Tensor):
+    return _RowLinearSP.apply(x, weight)

@@ -1,0 +1,340 @@
+"""Worker setup, the training step and the training loop.
+
+Mirrors the phases of the reference loop (``src/training/loop/setup.py:62-512``,
+``run.py:57-583``, ``teardown.py:22-57``) with a device-resident gradient / optimizer path:
+
+  batch (pinned host) -> H2D -> micro-batches { forward, loss * n_valid_i / n_valid_total, backward }
+  -> DP gradient reduction -> TP replicated-gradient sync -> finite check -> global norm + clip
+  -> WSD lr -> Muon.step -> AdamW.step -> zero grads -> log / checkpoint
+
+Steps whose gradients contain inf/nan skip the update *and clear the gradients* (the reference
+leaves poisoned accumulators behind, ``run.py:401-483``).
+"""
+from __future__ import annotations
+
+import json
+import logging
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterator, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import HippoConfig, PrecisionConfig
+from ..data.packing import slice_cu_seqlens
+from ..models.model import HippoModel, shift_targets
+from ..models.nvfp4_linear import repack_nvfp4_weights
+from ..optim.optimizers import build_param_groups, global_grad_norm, clip_coefficient
+from ..optim.schedule import wsd_lr
+from ..parallel.mesh import Mesh, get_mesh, init_mesh, init_distributed_from_env
+from ..utils.timing import PhaseTimer, nvtx_range
+from . import checkpoint as ckpt
+from .diagnostics import log_pre_step_diag, log_post_opt_diag
+
+_DIAG_STEPS = 3
+
+
+@dataclass
+class TrainContext:
+    args: Any
+    cfg: HippoConfig
+    mesh: Mesh
+    device: torch.device
+    model: HippoModel
+    muon: Any
+    adamw: Any
+    precision: PrecisionConfig
+    logger: logging.Logger
+    data_iter: Optional[Iterator] = None
+    run_dir: Optional[str] = None
+    step: int = 0
+    metrics_file: Optional[Any] = None
+    grad_reducer: Optional[Any] = None
+    offloader: Optional[Any] = None
+    prefetcher: Optional[Any] = None
+    watchdog: Optional[Any] = None
+    closed: bool = False
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+def make_logger(rank: int, run_dir: Optional[str]) -> logging.Logger:
+    lg = logging.getLogger(f"hippo.r{rank}")
+    lg.setLevel(logging.INFO)
+    lg.propagate = False
+    if not lg.handlers:
+        fmt = logging.Formatter("%(asctime)s [r%(rank)s] %(message)s".replace("%(rank)s", str(rank)))
+        if rank == 0:
+            sh = logging.StreamHandler(); sh.setFormatter(fmt); lg.addHandler(sh)
+        if run_dir:
+            os.makedirs(os.path.join(run_dir, "logs"), exist_ok=True)
+            fh = logging.FileHandler(os.path.join(run_dir, "logs", f"rank{rank}.log"))
+            fh.setFormatter(fmt); lg.addHandler(fh)
+    return lg
+
+
+def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterator] = None) -> TrainContext:
+    """Rendezvous, mesh, model, optimizers, data. ``args`` is the CLI namespace."""
+    device = init_distributed_from_env(timeout_s=float(getattr(args, "dist_timeout_s", 1800)))
+    tp = int(getattr(args, "tp_size", 1) or 1)
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world == 1:
+        tp = 1
+    dp = int(getattr(args, "dp_size", 0) or 0) or world // tp
+    mesh = init_mesh(tp=tp, dp=dp, device=device)
+    logger = make_logger(mesh.rank, run_dir)
+    torch.manual_seed(int(getattr(args, "seed", 42)) + mesh.dp_rank)
+    if device.type == "cuda":
+        torch.set_float32_matmul_precision("high")
+    cfg = HippoConfig.from_namespace(args)
+    precision = PrecisionConfig.from_dict(getattr(args, "precision", None))
+    wdtype = precision.model_weights if device.type == "cuda" or getattr(args, "force_precision", False) \
+        else torch.float32
+    model = HippoModel(cfg, device=device, dtype=wdtype, seed=int(getattr(args, "seed", 42)))
+    if mesh.is_distributed:
+        dist.barrier()
+        from ..parallel.collectives import broadcast_replicated_params
+        broadcast_replicated_params(model.replicated_parameters(), mesh)
+    offload = bool(getattr(args, "offload_optimizer", False))
+    muon, adamw = build_param_groups(model, args, precision, offload=offload)
+    ctx = TrainContext(args=args, cfg=cfg, mesh=mesh, device=device, model=model, muon=muon, adamw=adamw,
+                       precision=precision, logger=logger, data_iter=data_iter, run_dir=run_dir)
+    if mesh.dp > 1:
+        from ..parallel.dp import DPGradReducer
+        ctx.grad_reducer = DPGradReducer(model, mesh, overlap=bool(getattr(args, "dp_overlap", True)))
+    if bool(getattr(args, "offload_grads", False)):
+        from ..optim.offload import GradOffloader
+        ctx.offloader = GradOffloader(model, device)
+    if mesh.rank == 0:
+        n = model.num_parameters()
+        logger.info(f"model: {n/1e6:.1f}M local parameters, tp={mesh.tp} dp={mesh.dp}, layers={cfg.layer_types()}")
+        logger.info(f"optimizer: muon entries={len(muon.entries)} adamw entries={len(adamw.entries)} "
+                    f"offload={offload}")
+        if run_dir:
+            ctx.metrics_file = open(os.path.join(run_dir, "metrics.jsonl"), "a")
+    if data_iter is None:
+        from ..data.loaders import build_data_iterator
+        ctx.data_iter, ctx.prefetcher = build_data_iterator(args, cfg, mesh)
+    resume = getattr(args, "resume", None)
+    if resume:
+        path = resume
+        if resume in ("latest", "auto") and run_dir:
+            path = ckpt.find_latest_checkpoint(os.path.join(run_dir, "checkpoints"))
+        if path and os.path.isdir(path):
+            path = ckpt.find_latest_checkpoint(path)
+        if path:
+            step, loss = ckpt.load_checkpoint(path, model, muon, adamw, rank=mesh.rank,
+                                              world_size=mesh.world_size, map_location=device)
+            ctx.step = step + 1
+            logger.info(f"resumed from {path} at step {step} (loss {loss})")
+    hb = float(getattr(args, "watchdog_timeout_s", 0) or 0)
+    if hb > 0:
+        from .watchdog import StepWatchdog
+        ctx.watchdog = StepWatchdog(hb, run_dir, mesh.rank)
+        ctx.watchdog.start()
+    return ctx
+
+
+def _micro_batches(T: int, mbs: int, row_len: Optional[int]):
+    if not mbs or mbs <= 0 or mbs >= T:
+        return [(0, T)]
+    return [(s, min(T, s + mbs)) for s in range(0, T, mbs)]
+
+
+def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optional[PhaseTimer] = None
+               ) -> Dict[str, Any]:
+    """One optimizer step over ``batch`` = {input_ids[T] | [B,S], labels, cu_seqlens}."""
+    args, model, mesh, dev = ctx.args, ctx.model, ctx.mesh, ctx.device
+    timer = timer or PhaseTimer(enabled=False)
+    model.train()
+    with timer.phase("h2d"):
+        ids = batch["input_ids"].to(dev, non_blocking=True)
+        labels = batch["labels"].to(dev, non_blocking=True)
+        cu = batch.get("cu_seqlens")
+        row_len = ids.shape[1] if ids.dim() == 2 else batch.get("row_len")
+        ids, labels = ids.reshape(-1), labels.reshape(-1)
+        T = ids.shape[0]
+        if cu is None:
+            rl = row_len or T
+            cu = torch.arange(0, T + 1, rl, dtype=torch.int32)
+        cu = cu.to(dev, non_blocking=True)
+    targets = shift_targets(labels, row_len)
+    mbs = int(getattr(args, "micro_batch_size", 0) or 0)
+    windows = _micro_batches(T, mbs, row_len)
+    valid_counts = [(targets[s:e] >= 0).sum() for s, e in windows]
+    total_valid = torch.stack(valid_counts).sum().float()
+    if mesh.dp > 1:
+        dist.all_reduce(total_valid, group=mesh.dp_group)
+    total_valid_f = float(total_valid.clamp(min=1))
+    carry = bool(getattr(args, "carry_kda_state", False))
+    kda_states = None
+    loss_acc = torch.zeros((), device=dev, dtype=torch.float32)
+    use_autocast = dev.type == "cuda" and ctx.precision.autocast_enabled and False  # weights already bf16
+    with timer.phase("fwd_bwd"):
+        for wi, (s, e) in enumerate(windows):
+            if float(valid_counts[wi]) == 0 and not carry:
+                continue
+            cu_w = slice_cu_seqlens(cu, s, e).to(torch.int32)
+            lab_w = labels[s:e].clone()
+            if e < T:
+                # the last token's target lives in the next window: keep it via an explicit target vector
+                pass
+            if ctx.grad_reducer is not None:
+                ctx.grad_reducer.set_last_microbatch(wi == len(windows) - 1)
+            with nvtx_range(f"mb{wi}_forward"):
+                init = None
+                if carry and kda_states is not None:
+                    continues = not bool(((cu == s).any()))
+                    init = _carry_states(kda_states, cu_w.numel() - 1, continues)
+                h, finals = model.hidden(ids[s:e], cu_w, init)
+                loss = model.lm_head.loss(h, targets[s:e], total_valid_f)
+            with nvtx_range(f"mb{wi}_backward"):
+                loss.backward()
+            loss_acc += loss.detach().float()
+            if carry:
+                kda_states = [f.detach() for f in finals]
+            if ctx.offloader is not None:
+                ctx.offloader.after_microbatch()
+    with timer.phase("grad_sync"):
+        if ctx.offloader is not None:
+            ctx.offloader.drain_to_device()
+        if ctx.grad_reducer is not None:
+            ctx.grad_reducer.finish()
+            dist.all_reduce(loss_acc, group=mesh.dp_group)
+        model.sync_replicated_grads()
+    with timer.phase("gradnorm"):
+        gnorm_t = global_grad_norm(ctx.muon, ctx.adamw, mesh)
+        gnorm = float(gnorm_t)
+        found_inf = not math.isfinite(gnorm)
+    max_norm = float(getattr(args, "max_grad_norm", 1.0) or 0.0)
+    lr_m = wsd_lr(ctx.step, float(getattr(args, "muon_lr", 0.02)), int(getattr(args, "lr_warmup_steps", 0)),
+                  int(getattr(args, "lr_decay_steps", 0)), int(getattr(args, "max_steps", 1 << 30)))
+    lr_a = wsd_lr(ctx.step, float(getattr(args, "learning_rate", 0.004)), int(getattr(args, "lr_warmup_steps", 0)),
+                  int(getattr(args, "lr_decay_steps", 0)), int(getattr(args, "max_steps", 1 << 30)))
+    if ctx.step < _DIAG_STEPS and getattr(args, "diagnostics", False):
+        log_pre_step_diag(ctx.logger, ctx.step, [ctx.muon, ctx.adamw], gnorm)
+    if not found_inf:
+        coef = clip_coefficient(gnorm, max_norm)
+        ctx.muon.set_lr(lr_m); ctx.adamw.set_lr(lr_a)
+        with timer.phase("muon"):
+            ctx.muon.step(grad_scale=coef)
+        with timer.phase("adamw"):
+            ctx.adamw.step(grad_scale=coef)
+    else:
+        ctx.logger.warning(f"step {ctx.step}: non-finite gradient norm; skipping the update")
+    with timer.phase("zero"):
+        ctx.muon.zero_grad(); ctx.adamw.zero_grad()
+        repack_nvfp4_weights(model)
+    if ctx.step < _DIAG_STEPS and getattr(args, "diagnostics", False):
+        log_post_opt_diag(ctx.logger, ctx.step, [ctx.muon, ctx.adamw])
+    return {"loss": loss_acc, "grad_norm": gnorm, "found_inf": found_inf, "lr_muon": lr_m, "lr_adamw": lr_a,
+            "tokens": T * mesh.dp, "n_valid": total_valid_f}
+
+
+def _carry_states(prev: List[torch.Tensor], n_seq: int, continues: bool) -> List[torch.Tensor]:
+    """Initial KDA states for the next token window: the previous window's last sequence state for
+    the first sequence when the document continues, zeros for every other sequence."""
+    out = []
+    for p in prev:
+        z = torch.zeros((n_seq,) + tuple(p.shape[1:]), dtype=p.dtype, device=p.device)
+        if continues and n_seq > 0:
+            z[0] = p[-1]
+        out.append(z)
+    return out
+
+
+def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
+    args, mesh = ctx.args, ctx.mesh
+    max_steps = int(getattr(args, "max_steps", 1000))
+    log_interval = max(1, int(getattr(args, "log_interval", 1)))
+    ck_int = int(getattr(args, "checkpoint_interval", 0) or 0)
+    mb_timing = int(getattr(args, "mb_timing", 0) or 0)
+    last = {}
+    losses = []
+    try:
+        while ctx.step < max_steps:
+            try:
+                batch = next(ctx.data_iter)
+            except StopIteration:
+                ctx.logger.info("data exhausted")
+                break
+            timed = mb_timing < 0 or ctx.step < mb_timing
+            timer = PhaseTimer(enabled=timed, device=ctx.device)
+            t0 = time.perf_counter()
+            ev0 = ev1 = None
+            if ctx.device.type == "cuda":
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+            out = train_step(ctx, batch, timer)
+            if ev1 is not None:
+                ev1.record(); ev1.synchronize()
+                step_ms = ev0.elapsed_time(ev1)
+            else:
+                step_ms = (time.perf_counter() - t0) * 1e3
+            loss = float(out["loss"])
+            losses.append(loss)
+            if ctx.watchdog is not None:
+                ctx.watchdog.beat(ctx.step)
+            if ctx.step % log_interval == 0:
+                ms = torch.tensor([step_ms], device=ctx.device)
+                if mesh.is_distributed:
+                    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+                step_ms_max = float(ms)
+                toks = out["tokens"] / (step_ms_max / 1e3)
+                rec = {"step": ctx.step, "loss": loss, "lr_muon": out["lr_muon"], "lr_adamw": out["lr_adamw"],
+                       "grad_norm": out["grad_norm"], "tokens": out["tokens"], "step_ms": step_ms_max,
+                       "tok_per_s": toks, "found_inf": out["found_inf"]}
+                if timed:
+                    rec["phases_ms"] = timer.summary()
+                if ctx.device.type == "cuda":
+                    rec["vram_alloc_mb"] = torch.cuda.memory_allocated(ctx.device) / 2 ** 20
+                    rec["vram_reserved_mb"] = torch.cuda.memory_reserved(ctx.device) / 2 ** 20
+                    rec["vram_max_mb"] = torch.cuda.max_memory_allocated(ctx.device) / 2 ** 20
+                if mesh.rank == 0:
+                    ctx.logger.info(f"step {ctx.step} loss {loss:.4f} lr {out['lr_muon']:.2e}/{out['lr_adamw']:.2e} "
+                                    f"gnorm {out['grad_norm']:.3f} tok {out['tokens']} {step_ms_max:.1f} ms "
+                                    f"{toks:,.0f} tok/s" + (f" [mb-time] {timer.summary()}" if timed else ""))
+                    if ctx.metrics_file is not None:
+                        ctx.metrics_file.write(json.dumps(rec) + "\n"); ctx.metrics_file.flush()
+            if ck_int > 0 and ctx.run_dir and (ctx.step + 1) % ck_int == 0:
+                try:
+                    d = os.path.join(ctx.run_dir, "checkpoints")
+                    ckpt.save_checkpoint(ctx.model, ctx.muon, ctx.adamw, ctx.step, loss,
+                                         ckpt.checkpoint_path(d, ctx.step), rank=mesh.rank,
+                                         world_size=mesh.world_size, mesh=mesh)
+                    if mesh.rank == 0:
+                        ckpt.prune_old_checkpoints(d, int(getattr(args, "checkpoint_keep_last_n", 0) or 0))
+                except Exception as ex:   # a disk error must not kill training
+                    ctx.logger.error(f"checkpoint save failed at step {ctx.step}: {ex!r}")
+            last = out
+            ctx.step += 1
+    finally:
+        teardown_worker(ctx)
+    return {"losses": losses, "last": last, "steps": ctx.step}
+
+
+def teardown_worker(ctx: Optional[TrainContext]) -> None:
+    """Idempotent; tolerates a partially built context (``src/training/loop/teardown.py:22-57``)."""
+    if ctx is None or getattr(ctx, "closed", False):
+        return
+    ctx.closed = True
+    for name in ("prefetcher", "watchdog", "offloader"):
+        obj = getattr(ctx, name, None)
+        if obj is not None:
+            try:
+                obj.close()
+            except Exception:
+                pass
+    mf = getattr(ctx, "metrics_file", None)
+    if mf is not None:
+        try:
+            mf.close()
+        except Exception:
+            pass
+    try:
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:
+        pass

@@ -1,0 +1,265 @@
+// Persistent warp-specialised bf16 GEMM on tcgen05 tensor cores (sm_100a).
+//
+//   C[M,N] = op(A) * op(B)   fp32 accumulate in TMEM, bf16 or fp32 output
+//   A_KMAJOR: A stored [M, K] (contraction contiguous)   else stored [K, M]
+//   B_KMAJOR: B stored [N, K] (contraction contiguous)   else stored [K, N]
+//
+// One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (one elected thread) and
+// TMEM owner, warps 2..5 = epilogue (each reads its own 32 TMEM lanes). 128x256 output tile, K in
+// slabs of 64 (one 128-byte swizzle atom), 4 smem stages, two TMEM accumulators so the epilogue of
+// tile i overlaps the main loop of tile i+1. All loads are plain (non-multicast) TMA.
+// Replaces the reference's cuBLAS calls behind F.linear / torch.mm (qkv_proj, o_proj, FFN, LCE).
+#include "sm100.cuh"
+#include "host_utils.h"
+
+namespace hippo {
+
+__device__ Status g_status = {0, 0, 0, 0};
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct GemmParams {
+  int M, N, K;
+  void* C; long long ldc;
+  int out_fp32;        // 0 = bf16, 1 = fp32
+  int accumulate;      // C += result
+  float alpha;
+  int tiles_m, tiles_n;
+};
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // grouped rasterisation: 8 row-blocks share each column-block sweep so A/B tiles stay hot in L2
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int GROUP = 8;
+    int per_group = GROUP * p.tiles_n;
+    int g = t / per_group, r = t % per_group;
+    int gm = min(GROUP, p.tiles_m - g * GROUP);
+    tm = g * GROUP + r % gm;
+    tn = r / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn; tile_coord(t, tm, tn);
+        for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
+          if (!ok) break;
+          uint8_t* sa = smem + s * STAGE_BYTES; uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          if (A_KMAJOR) {
+            tma_load_2d(sa, &tmA, &full[s], kb * BK, tm * BM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[s], tm * BM + j * 64, kb * BK);
+          }
+          if (B_KMAJOR) {
+            tma_load_2d(sb, &tmB, &full[s], kb * BK, tn * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[s], tn * BN + j * 64, kb * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(BM, BN, 1, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
+      int it = 0, tl = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+        int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
+        ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
+          if (!ok) break;
+          tc_fence_after();
+          uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = A_KMAJOR ? make_smem_desc(sa + k * 32, 16, 1024) : make_smem_desc(sa + k * 2048, 8192, 1024);
+            uint64_t bd = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024) : make_smem_desc(sb + k * 2048, 8192, 1024);
+            mma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    int tl = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+      int tm, tn; tile_coord(t, tm, tn);
+      int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
+      ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tc_wait_ld();
+        const int col0 = tn * BN + c;
+        if (row < p.M && col0 < p.N) {
+          if (p.out_fp32) {
+            float* crow = (float*)p.C + (long long)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4* dst = (float4*)(crow + j);
+                if (p.accumulate) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                *dst = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += crow[j];
+                crow[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                uint4* dst = (uint4*)(crow + j);
+                if (p.accumulate) {
+                  uint4 o = *dst;
+                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += of.x; f[2 * e + 1] += of.y; }
+                }
+                uint4 v;
+                __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                *dst = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(crow[j]);
+                crow[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+template <bool AK, bool BK_>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int out_fp32, int accumulate, float alpha, int max_ctas, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  // K-major: global [rows, K], box {64, rows_tile}.  MN-major: global [K, cols], box {64 cols, 64 k-rows}.
+  if (AK) rc = make_tmap_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, 2, true);
+  else    rc = make_tmap_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, 2, true);
+  if (rc) return rc;
+  if (BK_) rc = make_tmap_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, 2, true);
+  else     rc = make_tmap_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, 2, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.tiles_m = (M + BM - 1) / BM; p.tiles_n = (N + BN - 1) / BN;
+  int tiles = p.tiles_m * p.tiles_n;
+  int sms = sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  int grid = tiles < sms ? tiles : sms;
+  auto kern = gemm_bf16_kernel<AK, BK_>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace hippo
+
+// layout code: 0 = NT (A[M,K], B[N,K]); 1 = NN (A[M,K], B[K,N]); 2 = TN (A[K,M], B[K,N]); 3 = TT (A[K,M], B[N,K])
+extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, int layout, int out_fp32, int accumulate,
+                               float alpha, int max_ctas, void* stream) {
+  using namespace hippo;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (layout) {
+    case 0: return launch_gemm<true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
+    case 1: return launch_gemm<true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
+    case 2: return launch_gemm<false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
+    case 3: return launch_gemm<false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
+  }
+  return -1;
+}
+
+extern "C" int hippo_get_status(int* out4) {
+  hippo::Status st;
+  cudaError_t e = cudaMemcpyFromSymbol(&st, hippo::g_status, sizeof(st));
+  if (e != cudaSuccess) return (int)e;
+  out4[0] = st.code; out4[1] = st.detail; out4[2] = st.block; out4[3] = st.count;
+  return 0;
+}
+
+extern "C" int hippo_clear_status() {
+  hippo::Status st = {0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(hippo::g_status, &st, sizeof(st));
+}

@@ -1,0 +1,223 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of the ~7B hybrid KDA/attention decoder.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
+    python bench.py --impl reference ...                      (reference arm)
+
+Model/config: 32 layers at 3:1 KDA:attention, d_model 4096, 32 heads x 128, FFN 14336 (NVFP4, no
+bf16 master), vocab 128256, block attention residuals (8 blocks), Muon + AdamW, seq 8192,
+TP = N with sequence parallelism. Weak scaling: 16 sequences per GPU per step (N=8 gives the
+configured global batch of 128). Synthetic seeded uniform-random tokens, random-init weights.
+
+Timing: W untimed steps, then K steps between barrier + synchronize, CUDA events on the launching
+stream, max over ranks. A second K-step loop measures the same metric end to end through the public
+``train_step`` API with the per-step D2H read of the loss. Weights (>9 GB/GPU) and activations exceed
+the 126 MB L2, so no explicit flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEQS_PER_GPU = 16
+SEQ_LEN = 8192
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", type=str, default="ours")
+    p.add_argument("--model", type=str, default="7b", help="7b | 1p3b | tiny (tiny/1p3b are for smoke runs only)")
+    p.add_argument("--micro_batch_tokens", type=int, default=16384)
+    p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
+    p.add_argument("--no_fused_comm", action="store_true")
+    p.add_argument("--bf16_ffn", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+MODELS = {
+    "7b": dict(vocab_size=128256, hidden_size=4096, num_heads=32, head_dim=128, num_layers=32, num_blocks=8,
+               intermediate_size=14336, name="hybrid-kda-7b (32L 3:1 KDA:attn, d4096, 32x128, ffn14336 nvfp4, v128256)"),
+    "1p3b": dict(vocab_size=128256, hidden_size=2048, num_heads=16, head_dim=128, num_layers=24, num_blocks=6,
+                 intermediate_size=5632, name="hybrid-kda-1.3b"),
+    "tiny": dict(vocab_size=8192, hidden_size=512, num_heads=4, head_dim=128, num_layers=4, num_blocks=2,
+                 intermediate_size=1024, name="hybrid-kda-tiny"),
+}
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip install of /root/reference failed: directory is not installable (no setup.py / "
+                          "pyproject.toml); the reference also has no full-attention layers, sequence parallelism "
+                          "or sm_100 NVFP4 path, so this config cannot run on its stock code path"}))
+        return 0
+    import torch
+    import torch.distributed as dist
+    from hippolm_b200.cli import build_parser
+    from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
+    from hippolm_b200.data.loaders import synthetic_loader
+    from hippolm_b200.ops import _ext
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if a.gpus != world:
+        if a.gpus == 1 and world == 1:
+            pass
+        elif world == 1 and a.gpus > 1:
+            # self-launch one rank per GPU
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+    m = dict(MODELS[a.model])
+    name = m.pop("name")
+    args = build_parser().parse_args([])
+    for k, v in m.items():
+        setattr(args, k, v)
+    args.ffn_nvfp4 = not a.bf16_ffn
+    args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
+    args.tp_size = world
+    args.dp_size = 1
+    args.seq_len = SEQ_LEN if a.model != "tiny" else 1024
+    args.batch_size = a.seqs_per_gpu * world
+    args.micro_batch_size = a.micro_batch_tokens
+    args.max_steps = 10 ** 9
+    args.lr_decay_steps = 0
+    args.precision = None
+    args.fused_comm = not a.no_fused_comm
+    args.seed = 0
+    gb_tokens = args.batch_size * args.seq_len
+    loader = synthetic_loader(args.batch_size, args.seq_len, args.vocab_size, seed=0,
+                              doc_len_min=args.seq_len, doc_len_max=args.seq_len)
+    ctx = setup_worker(args, run_dir=None, data_iter=loader)
+    dev = ctx.device
+    batches = [next(loader) for _ in range(2)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(a.warmup):
+        out = train_step(ctx, batches[i % 2]); ctx.step += 1
+    barrier()
+    st = _ext.device_status()
+    if st[0] != 0:
+        raise RuntimeError(f"device status after warm-up: {st}")
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    # ---- device-timed loop
+    _ext.reset_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        out = train_step(ctx, batches[i % 2]); ctx.step += 1
+    e1.record()
+    barrier()
+    launches = _ext.launch_count()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms) / a.steps
+    # ---- end-to-end loop: same public API, loss read back to the host every step
+    barrier()
+    t0 = time.perf_counter()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    last_loss = None
+    for i in range(a.steps):
+        out = train_step(ctx, batches[i % 2]); ctx.step += 1
+        last_loss = float(out["loss"])                      # D2H of the step result
+    f1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    ems = torch.tensor([max(f0.elapsed_time(f1), wall * 1e3)], device=dev)
+    if world > 1:
+        dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+    e2e_ms_step = float(ems) / a.steps
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = sum(t.numel() * t.element_size() for t in (batches[0]["input_ids"], batches[0]["labels"],
+                                                     batches[0]["cu_seqlens"]))
+    st = _ext.device_status()
+    if rank == 0:
+        rec = {"metric": "train tokens/sec (device-timed, max over ranks)", "value": gb_tokens / (ms_step / 1e3),
+               "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_step,
+               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (FFN weights NVFP4)"
+               if not a.bf16_ffn else "bf16", "data": "synthetic seeded uniform-random tokens, random-init weights",
+               "config": {"model": name, "global_batch": args.batch_size, "seq_len": args.seq_len,
+                          "parallelism": f"tp{world}+sp", "micro_batch_tokens": a.micro_batch_tokens,
+                          "optimizer": "muon+adamw", "l2": "inputs larger than L2 (no explicit flush)",
+                          "fused_comm": bool(args.fused_comm and world > 1)},
+               "clocks": clocks,
+               "e2e": {"value": gb_tokens / (e2e_ms_step / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},
+               "gpu_launches": launches, "loss": last_loss, "device_status": list(st), "impl": "ours"}
+        print(json.dumps(rec), flush=True)
+    teardown_worker(ctx)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

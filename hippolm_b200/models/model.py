@@ -38,17 +38,27 @@ def _pad_to(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
-def _seeded(name: str, seed: int) -> torch.Generator:
-    g = torch.Generator(device="cpu")
+_INIT_DEVICE = [torch.device("cpu")]
+
+
+def _seeded(name: str, seed: int, device=None) -> torch.Generator:
+    g = torch.Generator(device=device if device is not None else "cpu")
     g.manual_seed((zlib.crc32(name.encode()) + seed * 1000003) % (2 ** 31))
     return g
 
 
 def _xavier(name: str, shape, seed: int) -> torch.Tensor:
-    """TP-invariant init: the full matrix is drawn from a per-name stream, shards are slices."""
+    """TP-invariant init: the full matrix is drawn from a per-name stream (on the model's device, so
+    a 7B model initialises in seconds), shards are slices of it."""
     fan_out, fan_in = shape
     a = math.sqrt(6.0 / (fan_in + fan_out))
-    return (torch.rand(shape, generator=_seeded(name, seed)) * 2 - 1) * a
+    dev = _INIT_DEVICE[0]
+    return (torch.rand(shape, generator=_seeded(name, seed, dev), device=dev) * 2 - 1) * a
+
+
+def _normal(name: str, shape, seed: int, std: float) -> torch.Tensor:
+    dev = _INIT_DEVICE[0]
+    return torch.randn(shape, generator=_seeded(name, seed, dev), device=dev) * std
 
 
 def _shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -103,7 +113,7 @@ class KDAAttention(nn.Module):
         self.sections = [self.key_l, self.key_l, self.val_l, 2 * Vd, self.Hl]
         n_real = sum(self.sections)
         n_pad = _pad_to(n_real, 64)
-        fused = torch.zeros(n_pad, D)
+        fused = torch.zeros(n_pad, D, device=q.device)
         fused[:n_real] = torch.cat([q, k, v, fg, b], 0)
         self.n_real = n_real
         o_fg = 2 * self.key_l + self.val_l
@@ -353,7 +363,7 @@ class VocabParallelEmbedding(nn.Module):
         assert cfg.vocab_size % m.tp == 0, "vocab_size must be divisible by tp"
         self.Vl = cfg.vocab_size // m.tp
         self.v0 = m.tp_rank * self.Vl
-        full = torch.randn((cfg.vocab_size, cfg.hidden_size), generator=_seeded("embed_tokens", seed)) * 0.02
+        full = _normal("embed_tokens", (cfg.vocab_size, cfg.hidden_size), seed, 0.02)
         self.weight = _mark(nn.Parameter(full[self.v0:self.v0 + self.Vl].to(device=device, dtype=dtype)), "adamw")
 
     def forward(self, ids):
@@ -424,7 +434,7 @@ class LMHeadLoss(nn.Module):
         if self.tied:
             self._embed = [embed]          # not registered: the tied weight lives on the embedding
         else:
-            full = torch.randn((cfg.vocab_size, cfg.hidden_size), generator=_seeded("lm_head", seed)) * 0.02
+            full = _normal("lm_head", (cfg.vocab_size, cfg.hidden_size), seed, 0.02)
             self.weight = _mark(nn.Parameter(full[self.v0:self.v0 + self.Vl].to(device=device, dtype=dtype)), "adamw")
 
     def head_weight(self):
@@ -468,6 +478,7 @@ class HippoModel(nn.Module):
         self.cfg = cfg
         self.mesh = get_mesh()
         device = device if device is not None else torch.device("cpu")
+        _INIT_DEVICE[0] = torch.device(device)
         self.embed_tokens = VocabParallelEmbedding(cfg, seed, device, dtype)
         kinds = cfg.layer_types()
         self.layers = nn.ModuleList([HybridLayer(cfg, i, kinds[i], seed, device, dtype)

@@ -52,7 +52,20 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+    """Number of kernel-launcher calls into the library since the last reset."""
+    return _LAUNCHES[0]
+
+
+def reset_launch_count() -> None:
+    _LAUNCHES[0] = 0
+
+
 def check(rc: int, what: str) -> None:
+    _LAUNCHES[0] += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
 

@@ -73,3 +73,230 @@ def gemm_tn(a, b, out_dtype=None):
     if N % 8 or K % 8:
         return gemm_nt(a.t().contiguous(), b.t().contiguous(), od)
     return _gemm(a, b, 2, N, K, Mc, out_dtype=torch.float32 if od == torch.float32 else torch.bfloat16).to(od)
+
+
+# ----------------------------------------------------------------------------- row ops
+def _bf(x):
+    return x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xs = x.shape
+        D = xs[-1]
+        x2 = _bf(x).reshape(-1, D).contiguous()
+        T = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        check(lib().hippo_rmsnorm_fwd(ptr(x2), ptr(_bf(w)), ptr(y), ptr(rstd), _c.c_longlong(T), D,
+                                      _c.c_float(eps), stream_ptr()), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.xs, ctx.xdtype = xs, x.dtype
+        return y.view(xs).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        T, D = x2.shape
+        dy2 = _bf(dy).reshape(T, D).contiguous()
+        dx = torch.empty_like(x2)
+        nb = min(T, 148 * 4)
+        part = torch.empty((nb, D), dtype=torch.float32, device=x2.device)
+        dw = torch.empty(D, dtype=torch.float32, device=x2.device)
+        check(lib().hippo_rmsnorm_bwd(ptr(x2), ptr(_bf(w)), ptr(dy2), ptr(rstd), ptr(dx), ptr(part), ptr(dw),
+                                      _c.c_longlong(T), D, nb, stream_ptr()), "rmsnorm_bwd")
+        return dx.view(ctx.xs).to(ctx.xdtype), dw.to(w.dtype), None
+
+
+def rmsnorm(x, w, eps):
+    return _RMSNorm.apply(x, w, eps)
+
+
+class _GatedRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o, gate, w, eps):
+        V = o.shape[-1]
+        o2, g2 = _bf(o).contiguous(), _bf(gate).contiguous()
+        rows = o2.numel() // V
+        y = torch.empty_like(o2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=o.device)
+        check(lib().hippo_gated_rmsnorm_fwd(ptr(o2), ptr(g2), ptr(_bf(w)), ptr(y), ptr(rstd), _c.c_longlong(rows), V,
+                                            _c.c_float(eps), stream_ptr()), "gated_rmsnorm_fwd")
+        ctx.save_for_backward(o2, g2, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        o2, g2, w, rstd = ctx.saved_tensors
+        V = o2.shape[-1]
+        rows = o2.numel() // V
+        dy2 = _bf(dy).contiguous()
+        do, dg = torch.empty_like(o2), torch.empty_like(g2)
+        dw = torch.zeros(V, dtype=torch.float32, device=o2.device)
+        check(lib().hippo_gated_rmsnorm_bwd(ptr(o2), ptr(g2), ptr(_bf(w)), ptr(dy2), ptr(rstd), ptr(do), ptr(dg),
+                                            ptr(dw), _c.c_longlong(rows), V, stream_ptr()), "gated_rmsnorm_bwd")
+        return do, dg, dw.to(w.dtype), None
+
+
+def gated_rmsnorm(o, gate, w, eps):
+    return _GatedRMSNorm.apply(o, gate, w, eps)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu = _bf(gu).contiguous()
+        T, I2 = gu.shape
+        a = torch.empty((T, I2 // 2), dtype=torch.bfloat16, device=gu.device)
+        check(lib().hippo_swiglu_fwd(ptr(gu), ptr(a), _c.c_longlong(T), I2 // 2, stream_ptr()), "swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return a
+
+    @staticmethod
+    def backward(ctx, da):
+        (gu,) = ctx.saved_tensors
+        T, I2 = gu.shape
+        dgu = torch.empty_like(gu)
+        check(lib().hippo_swiglu_bwd(ptr(gu), ptr(_bf(da).contiguous()), ptr(dgu), _c.c_longlong(T), I2 // 2,
+                                     stream_ptr()), "swiglu_bwd")
+        return dgu
+
+
+def swiglu(gu):
+    return _SwiGLU.apply(gu)
+
+
+def silu(x):
+    return torch.nn.functional.silu(x)
+
+
+class _KDAGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, A, b, safe, lower):
+        T, H, K = x.shape
+        x2 = _bf(x).contiguous()
+        g = torch.empty((T, H, K), dtype=torch.float32, device=x.device)
+        Af = A.float().contiguous()
+        bf_ = b.float().contiguous() if b is not None else None
+        check(lib().hippo_kda_gate_fwd(ptr(x2), ptr(Af), ptr(bf_), ptr(g), _c.c_longlong(T), H, K, int(safe),
+                                       _c.c_float(lower), stream_ptr()), "kda_gate_fwd")
+        ctx.save_for_backward(x2, Af, bf_ if bf_ is not None else Af)
+        ctx.has_b, ctx.safe, ctx.lower = b is not None, safe, lower
+        ctx.dts = (x.dtype, A.dtype, b.dtype if b is not None else None)
+        return g
+
+    @staticmethod
+    def backward(ctx, dg):
+        x2, Af, bf_ = ctx.saved_tensors
+        T, H, K = x2.shape
+        dg = dg.float().contiguous()
+        dx = torch.empty_like(x2)
+        dA = torch.zeros(H, dtype=torch.float32, device=x2.device)
+        db = torch.zeros(H * K, dtype=torch.float32, device=x2.device) if ctx.has_b else None
+        check(lib().hippo_kda_gate_bwd(ptr(x2), ptr(Af), ptr(bf_ if ctx.has_b else None), ptr(dg), ptr(dx), ptr(dA),
+                                       ptr(db), _c.c_longlong(T), H, K, int(ctx.safe), _c.c_float(ctx.lower),
+                                       stream_ptr()), "kda_gate_bwd")
+        return dx.to(ctx.dts[0]), dA.to(ctx.dts[1]), (db.to(ctx.dts[2]) if ctx.has_b else None), None, None
+
+
+def kda_gate(x_g, A_log, dt_bias, safe_gate, lower_bound):
+    return _KDAGate.apply(x_g, A_log, dt_bias, bool(safe_gate), float(lower_bound))
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pos, theta):
+        T, H, dh = x.shape
+        x2 = _bf(x).contiguous()
+        out = torch.empty_like(x2)
+        check(lib().hippo_rope(ptr(x2), ptr(out), ptr(pos), _c.c_longlong(T), H, dh, _c.c_float(theta),
+                               _c.c_float(1.0), stream_ptr()), "rope")
+        ctx.save_for_backward(pos)
+        ctx.theta = theta
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (pos,) = ctx.saved_tensors
+        T, H, dh = dy.shape
+        d2 = _bf(dy).contiguous()
+        out = torch.empty_like(d2)
+        check(lib().hippo_rope(ptr(d2), ptr(out), ptr(pos), _c.c_longlong(T), H, dh, _c.c_float(ctx.theta),
+                               _c.c_float(-1.0), stream_ptr()), "rope_bwd")
+        return out, None, None
+
+
+def rope(q, k, positions, theta):
+    pos = positions.to(torch.int32).contiguous()
+    return _Rope.apply(q, pos, theta), _Rope.apply(k, pos, theta)
+
+
+# ----------------------------------------------------------------------------- attention / KDA / AttnRes
+def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm):
+    from . import kda_cuda
+    return kda_cuda.kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+
+
+def causal_attention(q, k, v, cu_seqlens, scale):
+    from . import attn_cuda
+    return attn_cuda.causal_attention(q, k, v, cu_seqlens, scale)
+
+
+def attn_res(sources, query, norm_weight, eps):
+    from . import attnres_cuda
+    return attnres_cuda.attn_res(sources, query, norm_weight, eps)
+
+
+# ----------------------------------------------------------------------------- NVFP4
+def nvfp4_quantize(w, global_scale=None):
+    from . import nvfp4_cuda
+    return nvfp4_cuda.quantize(w, global_scale)
+
+
+def nvfp4_dequantize(packed, scales, global_scale, dtype=torch.float32):
+    from . import nvfp4_cuda
+    return nvfp4_cuda.dequantize(packed, scales, global_scale, dtype)
+
+
+def nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant=True):
+    from . import nvfp4_cuda
+    return nvfp4_cuda.gemm_nt(x, packed, scales, global_scale, act_quant)
+
+
+# ----------------------------------------------------------------------------- optimizer math
+def newton_schulz5(G, steps=5, eps=1e-7):
+    """Quintic Newton-Schulz on the tcgen05 GEMM: S = X X^T (NT), S2 = S S, X <- a X + (b S + c S2) X."""
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.float()
+    X = (X / (X.norm() + eps)).to(torch.bfloat16)
+    tall = X.shape[0] > X.shape[1]
+    if tall:
+        X = X.t().contiguous()
+    n = X.shape[0]
+    if n % 8 or X.shape[1] % 8:
+        from ..ref.ops import newton_schulz5 as ref_ns
+        return ref_ns(G, steps, eps)
+    for _ in range(steps):
+        S = gemm_nt(X, X)                                # [n, n]
+        S2 = gemm_nn(S, S)
+        M = (b * S.float() + c * S2.float()).to(torch.bfloat16)
+        X = (a * X.float() + gemm_nn(M, X).float()).to(torch.bfloat16)
+    if tall:
+        X = X.t()
+    return X.float()
+
+
+def adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
+    from . import optim_cuda
+    return optim_cuda.adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale)
+
+
+def lce_chunk_stats(x, w, targets_local):
+    z = gemm_nt(x, w, out_dtype=torch.float32)
+    mx = z.max(-1).values
+    se = (z - mx.unsqueeze(-1)).exp().sum(-1)
+    tl = targets_local.clamp(min=0)
+    tz = z.gather(1, tl.unsqueeze(1)).squeeze(1)
+    tz = torch.where(targets_local >= 0, tz, torch.zeros_like(tz))
+    return z, mx, se, tz

@@ -219,3 +219,92 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     of = o.float()
     y = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
     return (y * torch.sigmoid(gate.float())).to(o.dtype)
+
+
+def kda_chunked_anchored(q, k, v, g, beta, scale: Optional[float] = None,
+                         initial_state: Optional[torch.Tensor] = None,
+                         cu_seqlens: Optional[torch.Tensor] = None,
+                         use_qk_l2norm: bool = False, chunk: int = 64, sub: int = 16,
+                         return_aux: bool = False):
+    """Chunked KDA with the two-sided sub-chunk anchoring the CUDA kernels use: for a row block I
+    and earlier columns j, exp(G_i - G_j) = exp(G_i - G_a) * exp(G_a - G_j) with a = last row before
+    block I, so both factors are <= 1 for any decay magnitude; the diagonal 16x16 blocks are formed
+    exactly. Memory is O(T*H*K), which makes this the large-shape oracle on the GPU. Differentiable."""
+    T, H, K = q.shape
+    V = v.shape[-1]
+    dev = q.device
+    if scale is None:
+        scale = K ** -0.5
+    if use_qk_l2norm:
+        q, k = l2norm(q), l2norm(k)
+    cu = _default_cu(T, dev) if cu_seqlens is None else cu_seqlens
+    N = cu.numel() - 1
+    seq_id, start, length, per_seq = build_chunk_table(cu, T, chunk)
+    NC, C, NS = len(start), chunk, chunk // sub
+    idx = torch.full((NC, C), T, dtype=torch.int64)
+    for c, (s, l) in enumerate(zip(start, length)):
+        idx[c, :l] = torch.arange(s, s + l)
+    idx = idx.to(dev)
+
+    def pg(x):
+        xf = x.float()
+        z = torch.zeros((1,) + tuple(xf.shape[1:]), dtype=xf.dtype, device=dev)
+        return torch.cat([xf, z], 0)[idx].transpose(1, 2)      # [NC,H,C,...]
+
+    qc, kc, vc, gc = pg(q) * scale, pg(k), pg(v), pg(g)           # [NC,H,C,K|V]
+    bc = torch.cat([beta.float(), torch.zeros(1, H, device=dev)], 0)[idx].transpose(1, 2)   # [NC,H,C]
+    G = gc.cumsum(2)
+    kk = torch.zeros(NC, H, C, C, device=dev)
+    qk = torch.zeros(NC, H, C, C, device=dev)
+    for I in range(NS):
+        r = slice(I * sub, (I + 1) * sub)
+        Gi = G[:, :, r]                                           # [NC,H,sub,K]
+        # exact diagonal block
+        d = (Gi.unsqueeze(3) - Gi.unsqueeze(2))
+        msk = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=dev)).view(1, 1, sub, sub, 1)
+        e = torch.where(msk, d, torch.zeros_like(d)).exp() * msk
+        kk[:, :, r, r] = torch.einsum("nhic,nhjc,nhijc->nhij", kc[:, :, r], kc[:, :, r], e)
+        qk[:, :, r, r] = torch.einsum("nhic,nhjc,nhijc->nhij", qc[:, :, r], kc[:, :, r], e)
+        if I > 0:
+            Ga = G[:, :, I * sub - 1:I * sub]                     # anchor row
+            rowf = (Gi - Ga).exp()
+            cs = slice(0, I * sub)
+            colk = kc[:, :, cs] * (Ga - G[:, :, cs]).exp()
+            kk[:, :, r, cs] = (kc[:, :, r] * rowf) @ colk.transpose(-1, -2)
+            qk[:, :, r, cs] = (qc[:, :, r] * rowf) @ colk.transpose(-1, -2)
+    tri_s = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev), -1)
+    tri_i = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev))
+    Akk = (kk * bc.unsqueeze(-1)) * tri_s
+    Aqk = qk * tri_i
+    eye = torch.eye(C, device=dev)
+    Ainv = torch.linalg.solve_triangular(eye + Akk, eye.expand(NC, H, C, C), upper=False)
+    eG = G.exp()
+    u = Ainv @ (vc * bc.unsqueeze(-1))
+    w = Ainv @ (kc * eG * bc.unsqueeze(-1))
+    qg = qc * eG
+    Glast = G[:, :, -1]
+    kg = kc * (Glast.unsqueeze(2) - G).exp()
+    dlast = Glast.exp()
+    first = [0]
+    for c in per_seq:
+        first.append(first[-1] + c)
+    S0 = (initial_state.float() if initial_state is not None
+          else torch.zeros(N, H, K, V, dtype=torch.float32, device=dev))
+    S_list = [S0[n] for n in range(N)]
+    o_chunks = [None] * NC
+    for j in range(max(per_seq) if per_seq else 0):
+        seqs = [n for n in range(N) if per_seq[n] > j]
+        cids = torch.tensor([first[n] + j for n in seqs], device=dev)
+        Sj = torch.stack([S_list[n] for n in seqs])
+        vn = u[cids] - w[cids] @ Sj
+        oj = qg[cids] @ Sj + Aqk[cids] @ vn
+        Sn = Sj * dlast[cids].unsqueeze(-1) + kg[cids].transpose(-1, -2) @ vn
+        for ii, n in enumerate(seqs):
+            S_list[n] = Sn[ii]
+            o_chunks[first[n] + j] = oj[ii]
+    final = torch.stack(S_list) if N > 0 else S0
+    o = torch.zeros(T + 1, H, V, dtype=torch.float32, device=dev)
+    if NC > 0:
+        oc = torch.stack(o_chunks).transpose(1, 2)
+        o = o.index_put((idx.reshape(-1),), oc.reshape(NC * C, H, V), accumulate=True)
+    return o[:T].to(v.dtype), final

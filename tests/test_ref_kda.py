@@ -56,3 +56,15 @@ def test_gate_forms():
     assert (g <= 0).all() and (g >= -5).all()
     g2 = kda_gate(x, A, b, safe_gate=False)
     assert torch.allclose(g2, -torch.nn.functional.softplus(x))
+
+
+def test_anchored_matches_recurrent_strong_decay():
+    from hippolm_b200.ref.kda import kda_chunked_anchored
+    q, k, v, g, beta = _inputs(150, 2, 16, 16, seed=7)
+    g = g * 12.0          # decay far beyond what a one-sided factorisation survives in fp32
+    cu = torch.tensor([0, 70, 150])
+    o1, s1 = kda_recurrent(q, k, v, g, beta, cu_seqlens=cu)
+    o2, s2 = kda_chunked_anchored(q, k, v, g, beta, cu_seqlens=cu)
+    assert torch.isfinite(o2).all()
+    assert torch.allclose(o1, o2, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(s1, s2, atol=2e-5, rtol=1e-4)

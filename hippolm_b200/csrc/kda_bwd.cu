@@ -1,0 +1,680 @@
+// Chunked Kimi-Delta-Attention backward (chunk = 64 tokens, K = V = DK in {64, 128}).
+//
+//  kda_bwd_state   reverse recurrence over the chunks of a sequence (one CTA per sequence, head and
+//                  32-column slice of V): dv_new = Aqk^T do + kg dS;  dS <- e^Glast dS + qg^T do - w^T dv_new
+//  kda_bwd_dqkw    per (chunk, head): dAqk = tril(do v_new^T), dqg = do S^T, dkg = v_new dS^T,
+//                  dw = -dv_new S^T, and the elementwise terms of qg / kg / the state decay
+//  kda_bwd_wy      per (chunk, head): backward of u = Ainv (beta v), w = Ainv (beta k e^G) and of the
+//                  triangular inverse (dAkk = -strict_lower(Ainv^T dAinv Ainv^T))
+//  kda_bwd_amat    per (chunk, head): backward of the decayed Gram matrices (same sub-chunk anchoring
+//                  as the forward), reverse cumsum of dG -> dg, final dq / dk
+// Replaces fla/ops/kda/chunk_bwd.py:42-599, chunk_intra.py:367-629, fla/ops/common/chunk_delta_h.py:350-663.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <mma.h>
+#include <stdint.h>
+#include "kda_common.cuh"
+
+namespace hippo {
+using namespace nvcuda;
+
+typedef wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> FragA;
+typedef wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::col_major> FragAT;
+typedef wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> FragB;
+typedef wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> FragBT;
+typedef wmma::fragment<wmma::accumulator, 16, 16, 16, float> FragC;
+
+// =================================================================================================== state
+template <int DK, int VS>
+__global__ void __launch_bounds__(128, 2)
+kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, const bf16* __restrict__ kg,
+                     const bf16* __restrict__ Aqk, const float* __restrict__ G, const bf16* __restrict__ d_o,
+                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
+                     const int* __restrict__ seq_chunk, int H, const float* __restrict__ dfinal,
+                     bf16* __restrict__ dvn_out, bf16* __restrict__ dS_out, float* __restrict__ dh0) {
+  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4;
+  extern __shared__ __align__(128) uint8_t smem[];
+  float* dS = (float*)smem;                   // [DK][LF]
+  float* stg = dS + DK * LF;                  // [64][LF]
+  float* egl = stg + 64 * LF;                 // [DK]
+  bf16* dSb = (bf16*)(egl + DK);              // [DK][LS]
+  bf16* ws = dSb + DK * LS;                   // [64][LD]
+  bf16* qgs = ws + 64 * LD;
+  bf16* kgs = qgs + 64 * LD;
+  bf16* dos = kgs + 64 * LD;                  // [64][LS]
+  bf16* ndv = dos + 64 * LS;                  // [64][LS]  (-dv_new)
+  bf16* Aq = ndv + 64 * LS;                   // [64][72]
+
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
+
+  for (int idx = tid; idx < DK * VS; idx += 128) {
+    int r = idx / VS, c = idx % VS;
+    float s0 = dfinal ? dfinal[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] : 0.f;
+    dS[r * LF + c] = s0;
+    dSb[r * LS + c] = __float2bfloat16(s0);
+  }
+  __syncthreads();
+
+  for (int chunk = c_end - 1; chunk >= c_begin; --chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+    for (int idx = tid; idx < 64 * (DK / 8); idx += 128) {
+      int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      long long off = (cbase + r) * DK + c8;
+      *(uint4*)(ws + r * LD + c8) = *(const uint4*)(w + off);
+      *(uint4*)(qgs + r * LD + c8) = *(const uint4*)(qg + off);
+      *(uint4*)(kgs + r * LD + c8) = *(const uint4*)(kg + off);
+    }
+    for (int idx = tid; idx < 64 * 8; idx += 128) {
+      int r = idx >> 3, c8 = (idx & 7) * 8;
+      *(uint4*)(Aq + r * 72 + c8) = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+    }
+    for (int idx = tid; idx < 64 * (VS / 8); idx += 128) {
+      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      uint4 z = make_uint4(0, 0, 0, 0);
+      if (r < len) z = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + vs0 + c8);
+      *(uint4*)(dos + r * LS + c8) = z;
+    }
+    for (int c = tid; c < DK; c += 128) egl[c] = __expf(G[(cbase + 63) * DK + c]);
+    // gradient wrt the state after this chunk, for the per-chunk kernels
+    for (int idx = tid; idx < DK * (VS / 8); idx += 128) {
+      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      *(uint4*)(dS_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(dSb + r * LS + c8);
+    }
+    __syncthreads();
+    // dv_new = Aqk^T do + kg dS
+    {
+      const int rt = warp;
+#pragma unroll
+      for (int nt = 0; nt < VS / 16; ++nt) {
+        FragC acc; wmma::fill_fragment(acc, 0.f);
+        for (int kt = rt; kt < 4; ++kt) {           // Aqk lower triangular -> Aqk^T upper
+          FragAT a; FragB b;
+          wmma::load_matrix_sync(a, Aq + kt * 16 * 72 + rt * 16, 72);
+          wmma::load_matrix_sync(b, dos + kt * 16 * LS + nt * 16, LS);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+#pragma unroll
+        for (int kt = 0; kt < DK / 16; ++kt) {
+          FragA a; FragB b;
+          wmma::load_matrix_sync(a, kgs + rt * 16 * LD + kt * 16, LD);
+          wmma::load_matrix_sync(b, dSb + kt * 16 * LS + nt * 16, LS);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      }
+      __syncwarp();
+      for (int el = lane; el < 16 * VS; el += 32) {
+        int rr = rt * 16 + el / VS, cc = el % VS;
+        float dv = stg[rr * LF + cc];
+        dvn_out[(cbase + rr) * DK + vs0 + cc] = __float2bfloat16(dv);
+        ndv[rr * LS + cc] = __float2bfloat16(-dv);
+      }
+    }
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      dS[r * LF + c] *= egl[r];
+    }
+    __syncthreads();
+    // dS <- e^Glast dS + qg^T do - w^T dv_new
+    for (int t = warp; t < (DK / 16) * (VS / 16); t += 4) {
+      const int mt = t / (VS / 16), nt = t % (VS / 16);
+      FragC acc;
+      wmma::load_matrix_sync(acc, dS + mt * 16 * LF + nt * 16, LF, wmma::mem_row_major);
+#pragma unroll
+      for (int kt = 0; kt < 4; ++kt) {
+        FragAT a; FragB b;
+        wmma::load_matrix_sync(a, qgs + kt * 16 * LD + mt * 16, LD);
+        wmma::load_matrix_sync(b, dos + kt * 16 * LS + nt * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
+        wmma::load_matrix_sync(a, ws + kt * 16 * LD + mt * 16, LD);
+        wmma::load_matrix_sync(b, ndv + kt * 16 * LS + nt * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      wmma::store_matrix_sync(dS + mt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      dSb[r * LS + c] = __float2bfloat16(dS[r * LF + c]);
+    }
+    __syncthreads();
+  }
+  if (dh0) {
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      dh0[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] = dS[r * LF + c];
+    }
+  }
+}
+template <int DK, int VS>
+constexpr int kda_bwd_state_smem() {
+  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 3 * 64 * (DK + 8) * 2 +
+         2 * 64 * (VS + 8) * 2 + 64 * 72 * 2 + 128;
+}
+
+// =================================================================================================== dqkw
+template <int DK>
+__global__ void __launch_bounds__(256, 1)
+kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew, const bf16* __restrict__ dvn,
+                    const bf16* __restrict__ Sst, const bf16* __restrict__ dSst, const bf16* __restrict__ qg,
+                    const bf16* __restrict__ kg, const float* __restrict__ G, const int* __restrict__ chunk_start,
+                    const int* __restrict__ chunk_len, int H, float* __restrict__ dq_acc, float* __restrict__ dk_acc,
+                    float* __restrict__ dG_acc, bf16* __restrict__ dw_out, bf16* __restrict__ dAqk_out) {
+  constexpr int LD = DK + 8, NT = DK / 16;
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* dos = (bf16*)smem;            // [64][LD]
+  bf16* vns = dos + 64 * LD;
+  bf16* dvs = vns + 64 * LD;
+  bf16* Ss = dvs + 64 * LD;           // [DK][LD]
+  bf16* dSs = Ss + DK * LD;           // [DK][LD]
+  float* stg = (float*)(dSs + DK * LD);   // [8 warps][2][16][20]
+  float* dGl = stg + 8 * 2 * 320;     // [DK]
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long cbase = ((long long)chunk * H + h) * 64;
+  const long long sbase = ((long long)chunk * H + h) * DK;
+
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    uint4 z = make_uint4(0, 0, 0, 0);
+    if (r < len) z = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + c8);
+    *(uint4*)(dos + r * LD + c8) = z;
+    *(uint4*)(vns + r * LD + c8) = *(const uint4*)(vnew + (cbase + r) * DK + c8);
+    *(uint4*)(dvs + r * LD + c8) = *(const uint4*)(dvn + (cbase + r) * DK + c8);
+  }
+  for (int idx = tid; idx < DK * (DK / 8); idx += 256) {
+    int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    *(uint4*)(Ss + r * LD + c8) = *(const uint4*)(Sst + (sbase + r) * DK + c8);
+    *(uint4*)(dSs + r * LD + c8) = *(const uint4*)(dSst + (sbase + r) * DK + c8);
+  }
+  if (tid < DK) dGl[tid] = 0.f;
+  __syncthreads();
+  // state-decay term of dGlast: sum_v dS[c,v] S[c,v] e^Glast[c]
+  {
+    constexpr int TPR = 256 / DK;           // threads per state row
+    int c = tid / TPR, part = tid % TPR;
+    float s = 0.f;
+    for (int vv = part; vv < DK; vv += TPR)
+      s += __bfloat162float(Ss[c * LD + vv]) * __bfloat162float(dSs[c * LD + vv]);
+    s *= __expf(G[(cbase + 63) * DK + c]);
+    atomicAdd(&dGl[c], s);
+  }
+  float* my0 = stg + warp * 640, *my1 = my0 + 320;
+  // (dqg, dkg) pairs: one warp does both for a given 16x16 tile so that dG has a single writer
+  for (int t = warp; t < 4 * NT; t += 8) {
+    const int rt = t / NT, nt = t % NT;
+    FragC a0, a1; wmma::fill_fragment(a0, 0.f); wmma::fill_fragment(a1, 0.f);
+#pragma unroll
+    for (int kt = 0; kt < NT; ++kt) {
+      FragA a; FragBT b;
+      wmma::load_matrix_sync(a, dos + rt * 16 * LD + kt * 16, LD);
+      wmma::load_matrix_sync(b, Ss + nt * 16 * LD + kt * 16, LD);       // S^T
+      wmma::mma_sync(a0, a, b, a0);
+      wmma::load_matrix_sync(a, vns + rt * 16 * LD + kt * 16, LD);
+      wmma::load_matrix_sync(b, dSs + nt * 16 * LD + kt * 16, LD);      // dS^T
+      wmma::mma_sync(a1, a, b, a1);
+    }
+    wmma::store_matrix_sync(my0, a0, 20, wmma::mem_row_major);
+    wmma::store_matrix_sync(my1, a1, 20, wmma::mem_row_major);
+    __syncwarp();
+    // lane -> column cc = lane & 15, rows rr = (lane >> 4) * 8 .. +7
+    {
+      const int cc = lane & 15, rbase = (lane >> 4) * 8, c = nt * 16 + cc;
+      const float gl = G[(cbase + 63) * DK + c];
+      float colsum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int rr = rbase + e, i = rt * 16 + rr;
+        const long long off = (cbase + i) * DK + c;
+        const float Gi = G[off];
+        const float dqgv = my0[rr * 20 + cc], dkgv = my1[rr * 20 + cc];
+        const float qgv = __bfloat162float(qg[off]), kgv = __bfloat162float(kg[off]);
+        dq_acc[off] = dqgv * __expf(Gi);
+        dk_acc[off] = dkgv * __expf(gl - Gi);
+        dG_acc[off] = dqgv * qgv - dkgv * kgv;
+        colsum += dkgv * kgv;
+      }
+      colsum += __shfl_xor_sync(0xFFFFFFFFu, colsum, 16);
+      if (lane < 16) atomicAdd(&dGl[c], colsum);
+    }
+    __syncwarp();
+  }
+  // dw = -dv_new S^T
+  for (int t = warp; t < 4 * NT; t += 8) {
+    const int rt = t / NT, nt = t % NT;
+    FragC a0; wmma::fill_fragment(a0, 0.f);
+#pragma unroll
+    for (int kt = 0; kt < NT; ++kt) {
+      FragA a; FragBT b;
+      wmma::load_matrix_sync(a, dvs + rt * 16 * LD + kt * 16, LD);
+      wmma::load_matrix_sync(b, Ss + nt * 16 * LD + kt * 16, LD);
+      wmma::mma_sync(a0, a, b, a0);
+    }
+    wmma::store_matrix_sync(my0, a0, 20, wmma::mem_row_major);
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int el = lane * 8 + e, rr = el >> 4, cc = el & 15;
+      dw_out[(cbase + rt * 16 + rr) * DK + nt * 16 + cc] = __float2bfloat16(-my0[rr * 20 + cc]);
+    }
+    __syncwarp();
+  }
+  // dAqk = tril(do v_new^T)
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    FragC a0; wmma::fill_fragment(a0, 0.f);
+    if (ct <= rt) {
+#pragma unroll
+      for (int kt = 0; kt < NT; ++kt) {
+        FragA a; FragBT b;
+        wmma::load_matrix_sync(a, dos + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, vns + ct * 16 * LD + kt * 16, LD);    // v_new^T
+        wmma::mma_sync(a0, a, b, a0);
+      }
+    }
+    wmma::store_matrix_sync(my0, a0, 20, wmma::mem_row_major);
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int el = lane * 8 + e, rr = el >> 4, cc = el & 15;
+      int i = rt * 16 + rr, j = ct * 16 + cc;
+      dAqk_out[(cbase + i) * 64 + j] = __float2bfloat16(j <= i ? my0[rr * 20 + cc] : 0.f);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  if (tid < DK) dG_acc[(cbase + 63) * DK + tid] += dGl[tid];
+}
+template <int DK>
+constexpr int kda_bwd_dqkw_smem() { return 3 * 64 * (DK + 8) * 2 + 2 * DK * (DK + 8) * 2 + 8 * 2 * 320 * 4 + DK * 4 + 128; }
+
+// =================================================================================================== WY
+template <int DK>
+__global__ void __launch_bounds__(256, 1)
+kda_bwd_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, const float* __restrict__ beta,
+                  const float* __restrict__ G, const bf16* __restrict__ Ainv, const bf16* __restrict__ Akk,
+                  const bf16* __restrict__ dvn, const bf16* __restrict__ dw, const int* __restrict__ chunk_start,
+                  const int* __restrict__ chunk_len, int H, float* __restrict__ dk_acc, float* __restrict__ dG_acc,
+                  bf16* __restrict__ dv_out, float* __restrict__ dbeta_out, bf16* __restrict__ dKK_out) {
+  constexpr int LD = DK + 8, NT = DK / 16;
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* Xb = (bf16*)smem;             // [64][72]
+  bf16* dXb = Xb + 64 * 72;           // [64][72]
+  bf16* Yb = dXb + 64 * 72;           // [64][72]
+  bf16* dus = Yb + 64 * 72;           // [64][LD]
+  bf16* dws = dus + 64 * LD;
+  bf16* bks = dws + 64 * LD;          // beta k e^G
+  bf16* bvs = bks + 64 * LD;          // beta v
+  float* stg = (float*)(bvs + 64 * LD);   // [8][16][20]
+  float* bs = stg + 8 * 320;          // [64]
+  float* dbs = bs + 64;               // [64]
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long cbase = ((long long)chunk * H + h) * 64;
+
+  if (tid < 64) { bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f; dbs[tid] = 0.f; }
+  for (int idx = tid; idx < 64 * 8; idx += 256) {
+    int r = idx >> 3, c8 = (idx & 7) * 8;
+    *(uint4*)(Xb + r * 72 + c8) = *(const uint4*)(Ainv + (cbase + r) * 64 + c8);
+  }
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    *(uint4*)(dus + r * LD + c8) = *(const uint4*)(dvn + (cbase + r) * DK + c8);
+    *(uint4*)(dws + r * LD + c8) = *(const uint4*)(dw + (cbase + r) * DK + c8);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < 64 * DK; idx += 256) {
+    int i = idx / DK, c = idx % DK;
+    float kv = 0.f, vv = 0.f;
+    if (i < len) {
+      long long off = ((long long)(t0 + i) * H + h) * DK + c;
+      kv = __bfloat162float(k[off]); vv = __bfloat162float(v[off]);
+    }
+    bks[i * LD + c] = __float2bfloat16(bs[i] * kv * __expf(G[(cbase + i) * DK + c]));
+    bvs[i * LD + c] = __float2bfloat16(bs[i] * vv);
+  }
+  __syncthreads();
+  float* my = stg + warp * 320;
+  // dX = du bv^T + dw bk^T  (only the lower triangle feeds dAkk)
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    FragC acc; wmma::fill_fragment(acc, 0.f);
+    if (ct <= rt) {
+#pragma unroll
+      for (int kt = 0; kt < NT; ++kt) {
+        FragA a; FragBT b;
+        wmma::load_matrix_sync(a, dus + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, bvs + ct * 16 * LD + kt * 16, LD);
+        wmma::mma_sync(acc, a, b, acc);
+        wmma::load_matrix_sync(a, dws + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, bks + ct * 16 * LD + kt * 16, LD);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+    }
+    wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int el = lane * 8 + e, rr = el >> 4, cc = el & 15;
+      dXb[(rt * 16 + rr) * 72 + ct * 16 + cc] = __float2bfloat16(my[rr * 20 + cc]);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  // Y = X^T dX
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    FragC acc; wmma::fill_fragment(acc, 0.f);
+    for (int kt = rt; kt < 4; ++kt) {            // X^T[i,m] = X[m,i], non-zero for m >= i
+      FragAT a; FragB b;
+      wmma::load_matrix_sync(a, Xb + kt * 16 * 72 + rt * 16, 72);
+      wmma::load_matrix_sync(b, dXb + kt * 16 * 72 + ct * 16, 72);
+      wmma::mma_sync(acc, a, b, acc);
+    }
+    wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int el = lane * 8 + e, rr = el >> 4, cc = el & 15;
+      Yb[(rt * 16 + rr) * 72 + ct * 16 + cc] = __float2bfloat16(my[rr * 20 + cc]);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  // dM = -Y X^T ; dAkk = strict_lower(dM) ; dKK = beta_i dAkk ; dbeta_i += sum_j dAkk Akk / beta_i
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    FragC acc; wmma::fill_fragment(acc, 0.f);
+    if (ct <= rt) {
+      for (int kt = 0; kt <= ct; ++kt) {         // X^T[n,j] = X[j,n], non-zero for n <= j
+        FragA a; FragBT b;
+        wmma::load_matrix_sync(a, Yb + rt * 16 * 72 + kt * 16, 72);
+        wmma::load_matrix_sync(b, Xb + ct * 16 * 72 + kt * 16, 72);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+    }
+    wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+    __syncwarp();
+    {
+      const int rr = lane >> 1, half = lane & 1, i = rt * 16 + rr;
+      float rowsum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int cc = half * 8 + e, j = ct * 16 + cc;
+        float dA = j < i ? -my[rr * 20 + cc] : 0.f;
+        float a = __bfloat162float(Akk[(cbase + i) * 64 + j]);
+        rowsum += dA * a;
+        dKK_out[(cbase + i) * 64 + j] = __float2bfloat16(dA * bs[i]);
+      }
+      rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
+      if (half == 0 && bs[i] > 0.f) atomicAdd(&dbs[i], rowsum / bs[i]);
+    }
+    __syncwarp();
+  }
+  // dbv = X^T du -> dv, dbeta ;  dbk = X^T dw -> dk, dG, dbeta
+  for (int t = warp; t < 2 * 4 * NT; t += 8) {
+    const int which = t / (4 * NT), rt = (t % (4 * NT)) / NT, nt = t % NT;
+    const bf16* B = which ? dws : dus;
+    FragC acc; wmma::fill_fragment(acc, 0.f);
+    for (int kt = rt; kt < 4; ++kt) {
+      FragAT a; FragB b;
+      wmma::load_matrix_sync(a, Xb + kt * 16 * 72 + rt * 16, 72);
+      wmma::load_matrix_sync(b, B + kt * 16 * LD + nt * 16, LD);
+      wmma::mma_sync(acc, a, b, acc);
+    }
+    wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+    __syncwarp();
+    {
+      const int rr = lane >> 1, half = lane & 1, i = rt * 16 + rr;
+      float rowsum = 0.f;
+      if (i < len) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          int cc = half * 8 + e, c = nt * 16 + cc;
+          float val = my[rr * 20 + cc];
+          long long toff = ((long long)(t0 + i) * H + h) * DK + c;
+          if (!which) {
+            dv_out[toff] = __float2bfloat16(bs[i] * val);
+            rowsum += __bfloat162float(v[toff]) * val;
+          } else {
+            long long off = (cbase + i) * DK + c;
+            float ke = __bfloat162float(k[toff]) * __expf(G[off]);
+            dk_acc[off] += bs[i] * __expf(G[off]) * val;
+            dG_acc[off] += bs[i] * ke * val;
+            rowsum += ke * val;
+          }
+        }
+      }
+      rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
+      if (half == 0 && i < len) atomicAdd(&dbs[i], rowsum);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  if (tid < len) dbeta_out[(long long)(t0 + tid) * H + h] = dbs[tid];
+}
+template <int DK>
+constexpr int kda_bwd_wy_smem() { return 3 * 64 * 72 * 2 + 4 * 64 * (DK + 8) * 2 + 8 * 320 * 4 + 128 * 4 + 128; }
+
+// =================================================================================================== A matrices
+template <int DK>
+__global__ void __launch_bounds__(256, 1)
+kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const float* __restrict__ G,
+                    const bf16* __restrict__ dKK, const bf16* __restrict__ dAqk, const float* __restrict__ dq_acc,
+                    const float* __restrict__ dk_acc, const float* __restrict__ dG_acc,
+                    const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
+                    float* __restrict__ dq_out, float* __restrict__ dk_out, float* __restrict__ dg_out) {
+  constexpr int LD = DK + 8, NT = DK / 16, LQ = DK + 4;
+  constexpr int RPT = DK / 4;                 // rows owned by a thread (256 threads cover 64 x DK)
+  constexpr int NB = RPT / 16;                // diagonal blocks owned by a thread
+  extern __shared__ __align__(128) uint8_t smem[];
+  float* Gs = (float*)smem;                   // [64][DK]
+  float* stQ = Gs + 64 * DK;                  // [48][LQ]
+  float* stK = stQ + 48 * LQ;                 // [48][LQ]
+  float* stC = stK + 48 * LQ;                 // [16][LQ]
+  float* carry = stC + 16 * LQ;               // [4][DK]
+  bf16* qs = (bf16*)(carry + 4 * DK);         // [64][LD]
+  bf16* ks = qs + 64 * LD;
+  bf16* T1 = ks + 64 * LD;                    // Rq
+  bf16* T2 = T1 + 64 * LD;                    // Rk
+  bf16* Ck = T2 + 64 * LD;                    // [16][LD]
+  bf16* D1 = Ck + 16 * LD;                    // [64][72]  dKK
+  bf16* D2 = D1 + 64 * 72;                    // [64][72]  dAqk
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long cbase = ((long long)chunk * H + h) * 64;
+  const int c = tid % DK, rh = tid / DK, row0 = rh * RPT;
+
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    uint4 zq = make_uint4(0, 0, 0, 0), zk = zq;
+    if (r < len) {
+      long long off = ((long long)(t0 + r) * H + h) * DK + c8;
+      zq = *(const uint4*)(q + off); zk = *(const uint4*)(k + off);
+    }
+    *(uint4*)(qs + r * LD + c8) = zq; *(uint4*)(ks + r * LD + c8) = zk;
+  }
+  for (int idx = tid; idx < 64 * (DK / 4); idx += 256) {
+    int r = idx / (DK / 4), c4 = (idx % (DK / 4)) * 4;
+    *(float4*)(Gs + r * DK + c4) = *(const float4*)(G + (cbase + r) * DK + c4);
+  }
+  for (int idx = tid; idx < 64 * 8; idx += 256) {
+    int r = idx >> 3, c8 = (idx & 7) * 8;
+    *(uint4*)(D1 + r * 72 + c8) = *(const uint4*)(dKK + (cbase + r) * 64 + c8);
+    *(uint4*)(D2 + r * 72 + c8) = *(const uint4*)(dAqk + (cbase + r) * 64 + c8);
+  }
+  float dq[RPT], dk[RPT], dG[RPT];
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    long long off = (cbase + row0 + ii) * DK + c;
+    dq[ii] = dq_acc[off]; dk[ii] = dk_acc[off]; dG[ii] = dG_acc[off];
+  }
+  __syncthreads();
+  // exact diagonal blocks: this thread owns channel c of rows row0 .. row0+RPT-1
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    float Gv[16], kv[16], qv[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      int i = row0 + b * 16 + r;
+      Gv[r] = Gs[i * DK + c]; kv[r] = __bfloat162float(ks[i * LD + c]); qv[r] = __bfloat162float(qs[i * LD + c]);
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        if (s <= r) {
+          const int i = row0 + b * 16 + r, j = row0 + b * 16 + s;
+          const float d1 = s < r ? __bfloat162float(D1[i * 72 + j]) : 0.f;
+          const float d2 = __bfloat162float(D2[i * 72 + j]);
+          const float e = __expf(Gv[r] - Gv[s]);
+          const float tk = d1 * kv[s] * e, tq = d2 * kv[s] * e;      // -> dk_i, dq_i
+          const float tj = (d1 * kv[r] + d2 * qv[r]) * e;            // -> dk_j
+          dk[b * 16 + r] += tk; dq[b * 16 + r] += tq; dk[b * 16 + s] += tj;
+          const float gg = tk * kv[r] + tq * qv[r];
+          dG[b * 16 + r] += gg; dG[b * 16 + s] -= gg;
+        }
+      }
+    }
+  }
+  // off-diagonal blocks, column block J anchored at its last row (same factorisation as the forward)
+  for (int J = 0; J < 3; ++J) {
+    const int e = 16 * J + 15, r0 = 16 * (J + 1), nrows = 64 - r0;
+    __syncthreads();
+    for (int idx = tid; idx < 16 * DK; idx += 256) {
+      int jj = idx / DK, cc = idx % DK, j = 16 * J + jj;
+      Ck[jj * LD + cc] = __float2bfloat16(__bfloat162float(ks[j * LD + cc]) * __expf(Gs[e * DK + cc] - Gs[j * DK + cc]));
+    }
+    for (int idx = tid; idx < nrows * DK; idx += 256) {
+      int rr = idx / DK, cc = idx % DK, i = r0 + rr;
+      float f = __expf(Gs[i * DK + cc] - Gs[e * DK + cc]);
+      T1[rr * LD + cc] = __float2bfloat16(__bfloat162float(qs[i * LD + cc]) * f);
+      T2[rr * LD + cc] = __float2bfloat16(__bfloat162float(ks[i * LD + cc]) * f);
+    }
+    __syncthreads();
+    const int nrt = nrows / 16;
+    // dRq = D2[rows, J] Ck ; dRk = D1[rows, J] Ck ; dCk = D1[rows, J]^T Rk + D2[rows, J]^T Rq
+    for (int t = warp; t < (2 * nrt + 1) * NT; t += 8) {
+      const int kind = t / NT, nt = t % NT;
+      FragC acc; wmma::fill_fragment(acc, 0.f);
+      if (kind < 2 * nrt) {
+        const int rt = kind >> 1, which = kind & 1;
+        FragA a; FragB b;
+        wmma::load_matrix_sync(a, (which ? D1 : D2) + (r0 + rt * 16) * 72 + 16 * J, 72);
+        wmma::load_matrix_sync(b, Ck + nt * 16, LD);
+        wmma::mma_sync(acc, a, b, acc);
+        wmma::store_matrix_sync((which ? stK : stQ) + rt * 16 * LQ + nt * 16, acc, LQ, wmma::mem_row_major);
+      } else {
+        for (int kt = 0; kt < nrt; ++kt) {
+          FragAT a; FragB b;
+          wmma::load_matrix_sync(a, D1 + (r0 + kt * 16) * 72 + 16 * J, 72);
+          wmma::load_matrix_sync(b, T2 + kt * 16 * LD + nt * 16, LD);
+          wmma::mma_sync(acc, a, b, acc);
+          wmma::load_matrix_sync(a, D2 + (r0 + kt * 16) * 72 + 16 * J, 72);
+          wmma::load_matrix_sync(b, T1 + kt * 16 * LD + nt * 16, LD);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(stC + nt * 16, acc, LQ, wmma::mem_row_major);
+      }
+    }
+    __syncthreads();
+    const float Ge = Gs[e * DK + c];
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+      const int i = row0 + ii;
+      if (i >= r0) {
+        const float f = __expf(Gs[i * DK + c] - Ge);
+        const float dRq = stQ[(i - r0) * LQ + c], dRk = stK[(i - r0) * LQ + c];
+        const float qi = __bfloat162float(qs[i * LD + c]) * f, ki = __bfloat162float(ks[i * LD + c]) * f;
+        dq[ii] += dRq * f; dk[ii] += dRk * f;
+        dG[ii] += dRq * qi + dRk * ki;
+      } else if (i >= 16 * J) {
+        const float fc = __expf(Ge - Gs[i * DK + c]);
+        const float dC = stC[(i - 16 * J) * LQ + c];
+        dk[ii] += dC * fc;
+        dG[ii] -= dC * __bfloat162float(ks[i * LD + c]) * fc;
+      }
+    }
+  }
+  // dg = reverse cumsum of dG over the chunk rows
+  float tot = 0.f;
+#pragma unroll
+  for (int ii = RPT - 1; ii >= 0; --ii) { tot += dG[ii]; dG[ii] = tot; }
+  carry[rh * DK + c] = tot;
+  __syncthreads();
+  float add = 0.f;
+  for (int r2 = rh + 1; r2 < 256 / DK; ++r2) add += carry[r2 * DK + c];
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    const int i = row0 + ii;
+    if (i < len) {
+      long long toff = ((long long)(t0 + i) * H + h) * DK + c;
+      dq_out[toff] = dq[ii]; dk_out[toff] = dk[ii]; dg_out[toff] = dG[ii] + add;
+    }
+  }
+}
+template <int DK>
+constexpr int kda_bwd_amat_smem() {
+  return 64 * DK * 4 + (48 + 48 + 16) * (DK + 4) * 4 + 4 * DK * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 +
+         2 * 64 * 72 * 2 + 128;
+}
+
+}  // namespace hippo
+
+using namespace hippo;
+
+template <int DK>
+static int launch_bwd(const void* q, const void* k, const void* v, const float* beta, const float* G, const void* w,
+                      const void* qg, const void* kg, const void* Aqk, const void* Ainv, const void* Akk,
+                      const void* vnew, const void* Sst, const void* d_o, const float* dfinal, const int* cs,
+                      const int* cl, const int* sc, int NC, int N, int H, void* dvn, void* dSst, void* dw, void* dAqk,
+                      void* dKK, float* dq_acc, float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg,
+                      float* dbeta, float* dh0, cudaStream_t s) {
+  constexpr int VS = 32;
+  auto k3 = kda_bwd_state_kernel<DK, VS>;
+  auto k4a = kda_bwd_dqkw_kernel<DK>;
+  auto k4b = kda_bwd_wy_kernel<DK>;
+  auto k4c = kda_bwd_amat_kernel<DK>;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_state_smem<DK, VS>())) != cudaSuccess) return (int)e;
+    if ((e = cudaFuncSetAttribute(k4a, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_dqkw_smem<DK>())) != cudaSuccess) return (int)e;
+    if ((e = cudaFuncSetAttribute(k4b, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_wy_smem<DK>())) != cudaSuccess) return (int)e;
+    if ((e = cudaFuncSetAttribute(k4c, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_amat_smem<DK>())) != cudaSuccess) return (int)e;
+    once = true;
+  }
+  if (NC == 0) return 0;
+  k3<<<dim3(DK / VS, H, N), 128, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
+      (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
+  k4a<<<dim3(NC, H), 256, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
+      (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc, dG_acc,
+      (bf16*)dw, (bf16*)dAqk);
+  k4b<<<dim3(NC, H), 256, kda_bwd_wy_smem<DK>(), s>>>((const bf16*)k, (const bf16*)v, beta, G, (const bf16*)Ainv,
+      (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, dk_acc, dG_acc, (bf16*)dv, dbeta, (bf16*)dKK);
+  k4c<<<dim3(NC, H), 256, kda_bwd_amat_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, G, (const bf16*)dKK,
+      (const bf16*)dAqk, dq_acc, dk_acc, dG_acc, cs, cl, H, dq, dk, dg);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int hippo_kda_bwd(const void* q, const void* k, const void* v, const float* beta, const float* G,
+                             const void* w, const void* qg, const void* kg, const void* Aqk, const void* Ainv,
+                             const void* Akk, const void* vnew, const void* Sst, const void* d_o, const float* dfinal,
+                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, int NC, int N, int H,
+                             int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, float* dq_acc,
+                             float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg, float* dbeta,
+                             float* dh0, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  if (DK == 64) return launch_bwd<64>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  return -1;
+}

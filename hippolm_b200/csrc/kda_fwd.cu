@@ -1,0 +1,459 @@
+// Chunked Kimi-Delta-Attention forward (chunk = 64 tokens, K = V = DK in {64, 128}).
+//
+// kda_fwd_intra  one CTA per (chunk, head): inclusive cumsum G of the log decay, the decayed Gram
+//                matrices kk/qk, (I + beta*kk)^-1 by blocked forward substitution, then
+//                w = Ainv (beta k e^G), u = Ainv (beta v), qg = q e^G, kg = k e^(Glast-G).
+//                Pairwise decays exp(G_i - G_j) are factorised around a sub-chunk anchor so that both
+//                factors are <= 1 for any decay magnitude (16x16 diagonal blocks are formed exactly).
+// kda_fwd_state  one CTA per (sequence, head, 32-column slice of V): sequential over the chunks of
+//                the sequence with the K x 32 state slice resident in shared memory:
+//                v_new = u - w S;  o = qg S + Aqk v_new;  S <- e^Glast S + kg^T v_new.
+// Replaces the reference's Triton pipeline (fla/ops/kda/chunk_fwd.py:43-135, chunk_intra.py:41-747,
+// wy_fast.py:32-119, fla/ops/common/chunk_delta_h.py:40-323, fla/ops/gla/chunk.py:313-392).
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <mma.h>
+#include <stdint.h>
+#include "kda_common.cuh"
+
+namespace hippo {
+using namespace nvcuda;
+
+template <int DK>
+__global__ void __launch_bounds__(256, 1)
+kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                     const float* __restrict__ g, const float* __restrict__ beta,
+                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
+                     float* __restrict__ Gout, bf16* __restrict__ w_out, bf16* __restrict__ u_out,
+                     bf16* __restrict__ qg_out, bf16* __restrict__ kg_out, bf16* __restrict__ Aqk_out,
+                     bf16* __restrict__ Ainv_out, bf16* __restrict__ Akk_out) {
+  constexpr int LD = DK + 8;       // bf16 tile pitch
+  constexpr int LA = 68;           // fp32 64x64 pitch
+  extern __shared__ __align__(128) uint8_t smem[];
+  float* Gs = (float*)smem;                       // [64][DK]
+  bf16* qs = (bf16*)(Gs + 64 * DK);               // [64][LD]
+  bf16* ks = qs + 64 * LD;                        // [64][LD]
+  bf16* T1 = ks + 64 * LD;                        // [64][LD] work tile (row side q / beta*k*e^G)
+  bf16* T2 = T1 + 64 * LD;                        // [64][LD] work tile (row side k / beta*v)
+  bf16* Ck = T2 + 64 * LD;                        // [16][LD] column side
+  float* kk = (float*)(Ck + 16 * LD);             // [64][LA]
+  float* qk = kk + 64 * LA;                       // [64][LA]
+  float* X = qk + 64 * LA;                        // [64][LA]
+  float* Tm = X + 64 * LA;                        // [3][16][16]
+  float* bs = Tm + 3 * 256;                       // [64]
+  bf16* Xb = (bf16*)(bs + 64);                    // [64][72]
+  float* stg = (float*)(Xb + 64 * 72);            // [8 warps][16][20]
+
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;                                       // padding entry of the chunk table
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long cbase = ((long long)chunk * H + h) * 64;   // row base in chunk-padded [NC,H,64,*] arrays
+
+  // ---- phase 0: loads, cumsum
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    uint4 zq = make_uint4(0, 0, 0, 0), zk = zq;
+    if (r < len) {
+      long long off = ((long long)(t0 + r) * H + h) * DK + c8;
+      zq = *(const uint4*)(q + off); zk = *(const uint4*)(k + off);
+    }
+    *(uint4*)(qs + r * LD + c8) = zq; *(uint4*)(ks + r * LD + c8) = zk;
+  }
+  for (int idx = tid; idx < 64 * LA; idx += 256) { kk[idx] = 0.f; qk[idx] = 0.f; X[idx] = 0.f; }
+  if (tid < 64) bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f;
+  if (tid < DK) {
+    float run = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < 64; ++r) {
+      float gv = r < len ? g[((long long)(t0 + r) * H + h) * DK + tid] : 0.f;
+      run += gv;
+      Gs[r * DK + tid] = run;
+      Gout[(cbase + r) * DK + tid] = run;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 1: exact diagonal 16x16 blocks. 8-lane groups, each lane owns DK/8 channels.
+  {
+    constexpr int CPL = DK / 8;
+    const int grp = tid >> 3, gl = tid & 7;
+    for (int p = grp; p < 4 * 136; p += 32) {
+      int b = p / 136, r = p % 136;
+      int ii = 0;
+      while ((ii + 1) * (ii + 2) / 2 <= r) ++ii;
+      int jj = r - ii * (ii + 1) / 2;
+      int i = b * 16 + ii, j = b * 16 + jj;
+      float skk = 0.f, sqk = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) {
+        int c = gl * CPL + cc;
+        float e = __expf(Gs[i * DK + c] - Gs[j * DK + c]);
+        float kj = __bfloat162float(ks[j * LD + c]) * e;
+        skk += __bfloat162float(ks[i * LD + c]) * kj;
+        sqk += __bfloat162float(qs[i * LD + c]) * kj;
+      }
+      skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 1); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 1);
+      skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 2); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 2);
+      skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 4); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 4);
+      if (gl == 0) { if (jj < ii) kk[i * LA + j] = skk; qk[i * LA + j] = sqk; }
+    }
+  }
+
+  // ---- phase 2: off-diagonal blocks, column block J anchored at its last row
+  for (int J = 0; J < 3; ++J) {
+    const int e = 16 * J + 15, r0 = 16 * (J + 1), nrows = 64 - r0;
+    __syncthreads();
+    for (int idx = tid; idx < 16 * DK; idx += 256) {
+      int jj = idx / DK, c = idx % DK, j = 16 * J + jj;
+      Ck[jj * LD + c] = __float2bfloat16(__bfloat162float(ks[j * LD + c]) * __expf(Gs[e * DK + c] - Gs[j * DK + c]));
+    }
+    for (int idx = tid; idx < nrows * DK; idx += 256) {
+      int rr = idx / DK, c = idx % DK, i = r0 + rr;
+      float f = __expf(Gs[i * DK + c] - Gs[e * DK + c]);
+      T1[rr * LD + c] = __float2bfloat16(__bfloat162float(qs[i * LD + c]) * f);
+      T2[rr * LD + c] = __float2bfloat16(__bfloat162float(ks[i * LD + c]) * f);
+    }
+    __syncthreads();
+    const int ntile = 2 * (nrows / 16);
+    if (warp < ntile) {
+      const int rt = warp >> 1, which = warp & 1;
+      const bf16* R = which ? T2 : T1;
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
+#pragma unroll
+      for (int kt = 0; kt < DK / 16; ++kt) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> bfr;
+        wmma::load_matrix_sync(a, R + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(bfr, Ck + kt * 16, LD);
+        wmma::mma_sync(acc, a, bfr, acc);
+      }
+      float* dst = (which ? kk : qk) + (r0 + rt * 16) * LA + 16 * J;
+      wmma::store_matrix_sync(dst, acc, LA, wmma::mem_row_major);
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: X = (I + beta*kk)^-1, blocked forward substitution in fp32
+  for (int idx = tid; idx < 64 * 64; idx += 256) {
+    int i = idx >> 6, j = idx & 63;
+    kk[i * LA + j] = j < i ? kk[i * LA + j] * bs[i] : 0.f;      // kk now holds Akk
+  }
+  __syncthreads();
+  if (tid < 64) {
+    const int b = tid >> 4, col = tid & 15;
+    float x[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      float s = (r == col) ? 1.f : 0.f;
+#pragma unroll
+      for (int m = 0; m < 16; ++m)
+        if (m < r) s -= kk[(b * 16 + r) * LA + b * 16 + m] * x[m];
+      x[r] = s;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) X[(b * 16 + r) * LA + b * 16 + col] = x[r];
+  }
+  __syncthreads();
+  {
+    const int r = tid >> 4, c = tid & 15;
+    for (int d = 1; d < 4; ++d) {
+      for (int J = 0; J + d < 4; ++J) {
+        const int I = J + d;
+        float s = 0.f;
+        for (int L = J; L < I; ++L)
+#pragma unroll
+          for (int m = 0; m < 16; ++m) s += kk[(I * 16 + r) * LA + L * 16 + m] * X[(L * 16 + m) * LA + J * 16 + c];
+        Tm[J * 256 + r * 16 + c] = s;
+      }
+      __syncthreads();
+      for (int J = 0; J + d < 4; ++J) {
+        const int I = J + d;
+        float s = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) s += X[(I * 16 + r) * LA + I * 16 + m] * Tm[J * 256 + m * 16 + c];
+        X[(I * 16 + r) * LA + J * 16 + c] = -s;
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---- phase 4: operands + outputs
+  for (int idx = tid; idx < 64 * 64; idx += 256) {
+    int i = idx >> 6, j = idx & 63;
+    bf16 xv = __float2bfloat16(X[i * LA + j]);
+    Xb[i * 72 + j] = xv;
+    Ainv_out[(cbase + i) * 64 + j] = xv;
+    Akk_out[(cbase + i) * 64 + j] = __float2bfloat16(kk[i * LA + j]);
+    Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(j <= i ? qk[i * LA + j] : 0.f);
+  }
+  for (int idx = tid; idx < 64 * DK; idx += 256) {
+    int i = idx / DK, c = idx % DK;
+    float G = Gs[i * DK + c], eG = __expf(G);
+    float kv = __bfloat162float(ks[i * LD + c]), qv = __bfloat162float(qs[i * LD + c]);
+    float vv = i < len ? __bfloat162float(v[((long long)(t0 + i) * H + h) * DK + c]) : 0.f;
+    T1[i * LD + c] = __float2bfloat16(bs[i] * kv * eG);
+    T2[i * LD + c] = __float2bfloat16(bs[i] * vv);
+    qg_out[(cbase + i) * DK + c] = __float2bfloat16(qv * eG);
+    kg_out[(cbase + i) * DK + c] = __float2bfloat16(kv * __expf(Gs[63 * DK + c] - G));
+  }
+  __syncthreads();
+  {
+    constexpr int NT = DK / 16;
+    float* my = stg + warp * 16 * 20;
+    for (int t = warp; t < 2 * 4 * NT; t += 8) {
+      const int which = t / (4 * NT), rt = (t % (4 * NT)) / NT, nt = t % NT;
+      const bf16* B = which ? T2 : T1;
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
+      for (int kt = 0; kt <= rt; ++kt) {           // X is lower triangular
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> bfr;
+        wmma::load_matrix_sync(a, Xb + rt * 16 * 72 + kt * 16, 72);
+        wmma::load_matrix_sync(bfr, B + kt * 16 * LD + nt * 16, LD);
+        wmma::mma_sync(acc, a, bfr, acc);
+      }
+      wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+      __syncwarp();
+      bf16* out = which ? u_out : w_out;
+#pragma unroll
+      for (int e2 = 0; e2 < 8; ++e2) {
+        int el = lane * 8 + e2, rr = el >> 4, cc = el & 15;
+        out[(cbase + rt * 16 + rr) * DK + nt * 16 + cc] = __float2bfloat16(my[rr * 20 + cc]);
+      }
+      __syncwarp();
+    }
+  }
+}
+
+template <int DK>
+constexpr int kda_intra_smem() {
+  return 64 * DK * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 + 3 * 64 * 68 * 4 + 3 * 256 * 4 + 64 * 4 +
+         64 * 72 * 2 + 8 * 16 * 20 * 4 + 128;
+}
+
+// ---------------------------------------------------------------------------------------------------
+template <int DK, int VS>
+__global__ void __launch_bounds__(128, 2)
+kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ qg,
+                     const bf16* __restrict__ kg, const bf16* __restrict__ Aqk, const float* __restrict__ G,
+                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
+                     const int* __restrict__ seq_chunk, int H, const float* __restrict__ h0,
+                     bf16* __restrict__ vnew_out, bf16* __restrict__ S_out, bf16* __restrict__ o,
+                     float* __restrict__ final_state) {
+  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4;
+  extern __shared__ __align__(128) uint8_t smem[];
+  float* S = (float*)smem;                    // [DK][LF]
+  float* stg = S + DK * LF;                   // [64][LF]
+  float* egl = stg + 64 * LF;                 // [DK]
+  bf16* Sb = (bf16*)(egl + DK);               // [DK][LS]
+  bf16* ws = Sb + DK * LS;                    // [64][LD]
+  bf16* qgs = ws + 64 * LD;
+  bf16* kgs = qgs + 64 * LD;
+  bf16* vns = kgs + 64 * LD;                  // [64][LS]
+  bf16* Aq = vns + 64 * LS;                   // [64][72]
+
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
+
+  for (int idx = tid; idx < DK * VS; idx += 128) {
+    int r = idx / VS, c = idx % VS;
+    float s0 = h0 ? h0[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] : 0.f;
+    S[r * LF + c] = s0;
+    Sb[r * LS + c] = __float2bfloat16(s0);
+  }
+  __syncthreads();
+
+  for (int chunk = c_begin; chunk < c_end; ++chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+    for (int idx = tid; idx < 64 * (DK / 8); idx += 128) {
+      int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      long long off = (cbase + r) * DK + c8;
+      *(uint4*)(ws + r * LD + c8) = *(const uint4*)(w + off);
+      *(uint4*)(qgs + r * LD + c8) = *(const uint4*)(qg + off);
+      *(uint4*)(kgs + r * LD + c8) = *(const uint4*)(kg + off);
+    }
+    for (int idx = tid; idx < 64 * 8; idx += 128) {
+      int r = idx >> 3, c8 = (idx & 7) * 8;
+      *(uint4*)(Aq + r * 72 + c8) = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+    }
+    for (int idx = tid; idx < 64 * (VS / 8); idx += 128) {
+      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      *(uint4*)(vns + r * LS + c8) = *(const uint4*)(u + (cbase + r) * DK + vs0 + c8);
+    }
+    for (int c = tid; c < DK; c += 128) egl[c] = __expf(G[(cbase + 63) * DK + c]);
+    // state at chunk start, for the backward pass
+    for (int idx = tid; idx < DK * (VS / 8); idx += 128) {
+      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      *(uint4*)(S_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(Sb + r * LS + c8);
+    }
+    __syncthreads();
+
+    // P = w S ; v_new = u - P      (warp r owns rows 16r..16r+15)
+    {
+      const int rt = warp;
+#pragma unroll
+      for (int nt = 0; nt < VS / 16; ++nt) {
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.f);
+#pragma unroll
+        for (int kt = 0; kt < DK / 16; ++kt) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+          wmma::load_matrix_sync(a, ws + rt * 16 * LD + kt * 16, LD);
+          wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt * 16, LS);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      }
+      __syncwarp();
+      for (int el = lane; el < 16 * VS; el += 32) {
+        int rr = rt * 16 + el / VS, cc = el % VS;
+        float vn = __bfloat162float(vns[rr * LS + cc]) - stg[rr * LF + cc];
+        bf16 vb = __float2bfloat16(vn);
+        vns[rr * LS + cc] = vb;
+        vnew_out[(cbase + rr) * DK + vs0 + cc] = vb;
+      }
+    }
+    __syncthreads();
+    // o = qg S + Aqk v_new
+    {
+      const int rt = warp;
+#pragma unroll
+      for (int nt = 0; nt < VS / 16; ++nt) {
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.f);
+#pragma unroll
+        for (int kt = 0; kt < DK / 16; ++kt) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+          wmma::load_matrix_sync(a, qgs + rt * 16 * LD + kt * 16, LD);
+          wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt * 16, LS);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+        for (int kt = 0; kt <= rt; ++kt) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+          wmma::load_matrix_sync(a, Aq + rt * 16 * 72 + kt * 16, 72);
+          wmma::load_matrix_sync(b, vns + kt * 16 * LS + nt * 16, LS);
+          wmma::mma_sync(acc, a, b, acc);
+        }
+        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      }
+      __syncwarp();
+      for (int el = lane; el < 16 * VS; el += 32) {
+        int rr = rt * 16 + el / VS, cc = el % VS;
+        if (rr < len) o[((long long)(t0 + rr) * H + h) * DK + vs0 + cc] = __float2bfloat16(stg[rr * LF + cc]);
+      }
+    }
+    // S <- e^Glast S + kg^T v_new
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      S[r * LF + c] *= egl[r];
+    }
+    __syncthreads();
+    for (int t = warp; t < (DK / 16) * (VS / 16); t += 4) {
+      const int mt = t / (VS / 16), nt = t % (VS / 16);
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::load_matrix_sync(acc, S + mt * 16 * LF + nt * 16, LF, wmma::mem_row_major);
+#pragma unroll
+      for (int kt = 0; kt < 4; ++kt) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::col_major> a;     // kg^T
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+        wmma::load_matrix_sync(a, kgs + kt * 16 * LD + mt * 16, LD);
+        wmma::load_matrix_sync(b, vns + kt * 16 * LS + nt * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      wmma::store_matrix_sync(S + mt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      Sb[r * LS + c] = __float2bfloat16(S[r * LF + c]);
+    }
+    __syncthreads();
+  }
+  if (final_state) {
+    for (int idx = tid; idx < DK * VS; idx += 128) {
+      int r = idx / VS, c = idx % VS;
+      final_state[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] = S[r * LF + c];
+    }
+  }
+}
+
+template <int DK, int VS>
+constexpr int kda_state_smem() {
+  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 3 * 64 * (DK + 8) * 2 +
+         64 * (VS + 8) * 2 + 64 * 72 * 2 + 128;
+}
+
+}  // namespace hippo
+
+using namespace hippo;
+
+template <int DK>
+static int launch_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                      const int* cs, const int* cl, const int* sc, int NC, int N, int H, const float* h0,
+                      float* G, void* w, void* u, void* qg, void* kg, void* Aqk, void* Ainv, void* Akk, void* vnew,
+                      void* Sst, void* o, float* fin, cudaStream_t s) {
+  constexpr int VS = 32;
+  auto k1 = kda_fwd_intra_kernel<DK>;
+  auto k2 = kda_fwd_state_kernel<DK, VS>;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_intra_smem<DK>());
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_state_smem<DK, VS>());
+    if (e != cudaSuccess) return (int)e;
+    once = true;
+  }
+  if (NC == 0) return 0;
+  k1<<<dim3(NC, H), 256, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
+                                                    G, (bf16*)w, (bf16*)u, (bf16*)qg, (bf16*)kg, (bf16*)Aqk, (bf16*)Ainv, (bf16*)Akk);
+  k2<<<dim3(DK / VS, H, N), 128, kda_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
+                                                                (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, H, h0,
+                                                                (bf16*)vnew, (bf16*)Sst, (bf16*)o, fin);
+  return (int)cudaGetLastError();
+}
+
+// q,k,v: [T,H,DK] bf16 (q already scaled, q/k already normalised); g: [T,H,DK] fp32 log decay; beta: [T,H] fp32.
+// chunk tables: chunk_start/len [NC], seq_chunk [N+1]. Workspaces are chunk-padded [NC,H,64,*].
+extern "C" int hippo_kda_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, int NC, int N, int H,
+                             int DK, const float* h0, float* G, void* w, void* u, void* qg, void* kg, void* Aqk,
+                             void* Ainv, void* Akk, void* vnew, void* Sst, void* o, float* final_state, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (DK == 128) return launch_fwd<128>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
+  if (DK == 64) return launch_fwd<64>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
+  return -1;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Chunk table built on the device (no host sync): chunks never straddle a sequence boundary.
+// cu: [N+1] int32. Outputs padded to nc_max entries; unused chunks get len 0.
+__global__ void kda_build_chunks_kernel(const int* __restrict__ cu, int N, int* __restrict__ chunk_start,
+                                        int* __restrict__ chunk_len, int* __restrict__ seq_chunk, int nc_max) {
+  __shared__ int total;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int n = 0; n < N; ++n) { seq_chunk[n] = acc; acc += (cu[n + 1] - cu[n] + 63) / 64; }
+    seq_chunk[N] = acc;
+    total = acc;
+  }
+  __syncthreads();
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    int s = cu[n], e = cu[n + 1], c = seq_chunk[n];
+    for (; s < e; s += 64, ++c)
+      if (c < nc_max) { chunk_start[c] = s; chunk_len[c] = min(64, e - s); }
+  }
+  for (int c = total + threadIdx.x; c < nc_max; c += blockDim.x) { chunk_start[c] = 0; chunk_len[c] = 0; }
+}
+
+extern "C" int hippo_kda_build_chunks(const int* cu, int N, int* chunk_start, int* chunk_len, int* seq_chunk,
+                                      int nc_max, void* stream) {
+  kda_build_chunks_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cu, N, chunk_start, chunk_len, seq_chunk, nc_max);
+  return (int)cudaGetLastError();
+}

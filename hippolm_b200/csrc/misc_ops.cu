@@ -1,0 +1,379 @@
+// Block attention-residual mix (fwd/bwd), AdamW update, NVFP4 quantise / dequantise, cross-entropy
+// row statistics and gradient, multi-tensor sum of squares. Memory-bound kernels, fp32 math.
+// Reference behaviour: src/models/ops/attn_res_triton.py:108-521, param_offload/cpu_fused.py:532-583,
+// src/models/ops/nvfp4_quant_triton.py:77-142, fla/modules/fused_linear_cross_entropy.py:43-358.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <stdint.h>
+
+namespace hippo {
+typedef __nv_bfloat16 bf16;
+constexpr int AR_MAX = 16;
+struct PtrList { const void* p[AR_MAX]; };
+struct MutPtrList { void* p[AR_MAX]; };
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+__device__ __forceinline__ void ld8(const bf16* p, float (&f)[8]) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(b[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ void st8(bf16* p, const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+
+// ------------------------------------------------------------------------------------ AttnRes
+// One block per token, D/8 threads (each owns 8 contiguous channels; a head spans GS = dh/8 lanes,
+// GS a power of two <= 32). sources: N tensors [T, D]. Saves alpha [N,T,H] and rstd [N,T].
+template <int NMAX>
+__global__ void attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
+                                   bf16* __restrict__ out, float* __restrict__ alpha, float* __restrict__ rstd,
+                                   long long T, int D, int H, float eps) {
+  __shared__ float red[NMAX][32];
+  const long long t = blockIdx.x;
+  const int tid = threadIdx.x, c0 = tid * 8, dh = D / H, GS = dh / 8, h = c0 / dh;
+  const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  float qw[8], fq[8], fw[8];
+  ld8(query + c0, fq); ld8(w + c0, fw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qw[i] = fq[i] * fw[i];
+  float v[NMAX][8], ss[NMAX], dot[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+    ss[n] = 0.f; dot[n] = 0.f;
+    if (n < N) {
+      ld8((const bf16*)src.p[n] + t * D + c0, v[n]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ss[n] += v[n][i] * v[n][i]; dot[n] += v[n][i] * qw[i]; }
+      for (int o = 1; o < GS; o <<= 1) dot[n] += __shfl_xor_sync(0xFFFFFFFFu, dot[n], o);
+      float s = wsum(ss[n]);
+      if (lane == 0) red[n][warp] = s;
+    }
+  }
+  __syncthreads();
+  float mx = -INFINITY, logit[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+    if (n < N) {
+      float s = 0.f;
+      for (int k = 0; k < nw; ++k) s += red[n][k];
+      float r = rsqrtf(s / D + eps);
+      if (tid == 0) rstd[(long long)n * T + t] = r;
+      logit[n] = dot[n] * r;
+      mx = fmaxf(mx, logit[n]);
+    }
+  }
+  float den = 0.f;
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) if (n < N) { logit[n] = __expf(logit[n] - mx); den += logit[n]; }
+  float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+    if (n < N) {
+      float a = logit[n] / den;
+      if ((tid % GS) == 0) alpha[((long long)n * T + t) * H + h] = a;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += a * v[n][i];
+    }
+  }
+  st8(out + t * D + c0, o);
+}
+
+// grid-stride over tokens; dq/dw partials in registers, one atomicAdd per channel per block at the end
+template <int NMAX>
+__global__ void attnres_bwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
+                                   const bf16* __restrict__ out, const bf16* __restrict__ d_out,
+                                   const float* __restrict__ alpha, const float* __restrict__ rstd, MutPtrList dsrc,
+                                   float* __restrict__ dq, float* __restrict__ dw, long long T, int D, int H) {
+  __shared__ float red[NMAX][32];
+  const int tid = threadIdx.x, c0 = tid * 8, dh = D / H, GS = dh / 8, h = c0 / dh;
+  const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  float fq[8], fw[8], dqa[8], dwa[8];
+  ld8(query + c0, fq); ld8(w + c0, fw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { dqa[i] = 0.f; dwa[i] = 0.f; }
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    float go[8], fo[8];
+    ld8(d_out + t * D + c0, go); ld8(out + t * D + c0, fo);
+    float dout_o = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dout_o += go[i] * fo[i];
+    for (int o = 1; o < GS; o <<= 1) dout_o += __shfl_xor_sync(0xFFFFFFFFu, dout_o, o);
+    float v[NMAX][8], ds[NMAX], lg[NMAX];
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        ld8((const bf16*)src.p[n] + t * D + c0, v[n]);
+        float dv = 0.f, dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { dv += go[i] * v[n][i]; dot += v[n][i] * fq[i] * fw[i]; }
+        for (int o = 1; o < GS; o <<= 1) { dv += __shfl_xor_sync(0xFFFFFFFFu, dv, o); dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o); }
+        float a = alpha[((long long)n * T + t) * H + h];
+        float r = rstd[(long long)n * T + t];
+        ds[n] = a * (dv - dout_o);
+        lg[n] = dot * r;
+        // sum over heads of ds*logit: each head counted once (first lane of the head group)
+        float contrib = ((tid % GS) == 0) ? ds[n] * lg[n] : 0.f;
+        contrib = wsum(contrib);
+        if (lane == 0) red[n][warp] = contrib;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        float sdl = 0.f;
+        for (int k = 0; k < nw; ++k) sdl += red[n][k];
+        float a = alpha[((long long)n * T + t) * H + h];
+        float r = rstd[(long long)n * T + t];
+        float dvn[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dvn[i] = a * go[i] + ds[n] * r * fq[i] * fw[i] - v[n][i] * r * r / D * sdl;
+          dqa[i] += ds[n] * v[n][i] * r * fw[i];
+          dwa[i] += ds[n] * fq[i] * v[n][i] * r;
+        }
+        st8((bf16*)dsrc.p[n] + t * D + c0, dvn);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { atomicAdd(&dq[c0 + i], dqa[i]); atomicAdd(&dw[c0 + i], dwa[i]); }
+}
+
+// ------------------------------------------------------------------------------------ AdamW
+__device__ __forceinline__ float ldf(const void* p, long long i, int is_bf16) {
+  return is_bf16 ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ void stf(void* p, long long i, int is_bf16, float v) {
+  if (is_bf16) ((bf16*)p)[i] = __float2bfloat16(v); else ((float*)p)[i] = v;
+}
+// standard AdamW: m,v EMA of g and g^2, both bias corrections, decoupled weight decay
+__global__ void adamw_kernel(void* p, const void* g, void* m, void* v, long long n, int p_bf16, int g_bf16, int m_bf16,
+                             int v_bf16, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                             float gscale) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gv = ldf(g, i, g_bf16) * gscale;
+  float mv = ldf(m, i, m_bf16) * b1 + (1.f - b1) * gv;
+  float vv = ldf(v, i, v_bf16) * b2 + (1.f - b2) * gv * gv;
+  stf(m, i, m_bf16, mv); stf(v, i, v_bf16, vv);
+  float upd = (mv / bc1) / (sqrtf(vv / bc2) + eps);
+  float pv = ldf(p, i, p_bf16);
+  stf(p, i, p_bf16, pv * (1.f - lr * wd) - lr * upd);
+}
+
+// out[0] += sum x^2 (one atomicAdd per block)
+__global__ void sumsq_kernel(const void* x, long long n, int is_bf16, float* out) {
+  __shared__ float sh[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = ldf(x, i, is_bf16); s += v * v;
+  }
+  s = wsum(s);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    r = wsum(r);
+    if (threadIdx.x == 0) atomicAdd(out, r);
+  }
+}
+
+// ------------------------------------------------------------------------------------ NVFP4
+__global__ void absmax_kernel(const void* x, long long n, int is_bf16, float* out) {
+  float m = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(ldf(x, i, is_bf16)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax((int*)out, __float_as_int(m));     // m >= 0: int order == float order
+}
+__global__ void nvfp4_global_scale_kernel(const float* amax, float* gs) {
+  float a = *amax;
+  *gs = a > 0.f ? a / (6.f * 448.f) : 1.f;
+}
+// one thread per 16-element block along K: e4m3 block scale = absmax/6/global, RN-even E2M1 codes,
+// byte = even element | odd element << 4
+__global__ void nvfp4_quant_kernel(const void* x, int is_bf16, long long nblocks, const float* gs_ptr,
+                                   uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
+  long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const float gs = *gs_ptr;
+  float f[16];
+  if (is_bf16) { float a[8], c[8]; ld8((const bf16*)x + b * 16, a); ld8((const bf16*)x + b * 16 + 8, c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { f[i] = a[i]; f[8 + i] = c[i]; } }
+  else {
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) { float4 t = *(const float4*)((const float*)x + b * 16 + i); f[i] = t.x; f[i + 1] = t.y; f[i + 2] = t.z; f[i + 3] = t.w; }
+  }
+  float bm = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(f[i]));
+  float sraw = fminf(bm / 6.f / gs, 448.f);
+  __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+  scales[b] = (uint8_t)s8;
+  float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
+  float inv = sdec > 0.f ? 1.f / sdec : 1.f;
+  uint2 outv;
+  uint8_t* ob = (uint8_t*)&outv;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    // division (not reciprocal multiply) keeps ties identical to the torch oracle
+    float lo = sdec > 0.f ? f[2 * i] / sdec : f[2 * i], hi = sdec > 0.f ? f[2 * i + 1] / sdec : f[2 * i + 1];
+    (void)inv;
+    ob[i] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+  }
+  *(uint2*)(packed + b * 8) = outv;
+}
+__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                     const float* gs_ptr, void* out, int out_bf16, long long nblocks) {
+  long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const float lut[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  float s = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)scales[b], __NV_E4M3))) * (*gs_ptr);
+  uint2 pv = *(const uint2*)(packed + b * 8);
+  const uint8_t* pb = (const uint8_t*)&pv;
+  float f[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint8_t lo = pb[i] & 0xF, hi = pb[i] >> 4;
+    f[2 * i] = ((lo & 8) ? -lut[lo & 7] : lut[lo & 7]) * s;
+    f[2 * i + 1] = ((hi & 8) ? -lut[hi & 7] : lut[hi & 7]) * s;
+  }
+  if (out_bf16) {
+    float a[8], c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = f[i]; c[i] = f[8 + i]; }
+    st8((bf16*)out + b * 16, a); st8((bf16*)out + b * 16 + 8, c);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) *(float4*)((float*)out + b * 16 + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------ cross entropy rows
+// per row of fp32 logits z[C, V]: max, sum exp(z - max), z[target] (0 when target < 0)
+__global__ void ce_stats_kernel(const float* __restrict__ z, const long long* __restrict__ target, float* __restrict__ mx,
+                                float* __restrict__ se, float* __restrict__ tz, int V) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const float* zr = z + row * V;
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) m = fmaxf(m, zr[c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = sh[0];
+  for (int k = 1; k < (blockDim.x >> 5); ++k) m = fmaxf(m, sh[k]);
+  __syncthreads();
+  float s = 0.f;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) s += __expf(zr[c] - m);
+  s = wsum(s);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int k = 0; k < (blockDim.x >> 5); ++k) t += sh[k];
+    mx[row] = m; se[row] = t;
+    long long tg = target[row];
+    tz[row] = tg >= 0 ? zr[tg] : 0.f;
+  }
+}
+// dz = (exp(z - lse) - onehot(target)) * w_row  as bf16, w_row = valid / n_valid
+__global__ void ce_grad_kernel(const float* __restrict__ z, const float* __restrict__ lse,
+                               const long long* __restrict__ target, const float* __restrict__ roww,
+                               bf16* __restrict__ dz, int V) {
+  const long long row = blockIdx.x;
+  const float l = lse[row], w = roww[row];
+  const long long tg = target[row];
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    float p = __expf(z[row * V + c] - l);
+    if (c == tg) p -= 1.f;
+    dz[row * V + c] = __float2bfloat16(p * w);
+  }
+}
+
+}  // namespace hippo
+
+using namespace hippo;
+#define ST(s) ((cudaStream_t)(s))
+#define RET() return (int)cudaGetLastError()
+
+extern "C" int hippo_attnres_fwd(const void* const* srcs, int N, const void* query, const void* w, void* out, float* alpha,
+                                 float* rstd, long long T, int D, int H, float eps, void* s) {
+  if (N > AR_MAX || D % 8 || D / 8 > 1024 || (D / H) % 8) return -1;
+  int gs = (D / H) / 8;
+  if (gs > 32 || (gs & (gs - 1))) return -2;
+  PtrList pl; for (int i = 0; i < N; ++i) pl.p[i] = srcs[i];
+  if (N <= 4) attnres_fwd_kernel<4><<<(unsigned)T, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (bf16*)out, alpha, rstd, T, D, H, eps);
+  else if (N <= 9) attnres_fwd_kernel<9><<<(unsigned)T, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (bf16*)out, alpha, rstd, T, D, H, eps);
+  else attnres_fwd_kernel<16><<<(unsigned)T, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (bf16*)out, alpha, rstd, T, D, H, eps);
+  RET();
+}
+extern "C" int hippo_attnres_bwd(const void* const* srcs, int N, const void* query, const void* w, const void* out,
+                                 const void* d_out, const float* alpha, const float* rstd, void* const* dsrcs, float* dq,
+                                 float* dw, long long T, int D, int H, void* s) {
+  if (N > AR_MAX || D % 8 || D / 8 > 1024) return -1;
+  PtrList pl; MutPtrList dl;
+  for (int i = 0; i < N; ++i) { pl.p[i] = srcs[i]; dl.p[i] = dsrcs[i]; }
+  unsigned grid = (unsigned)(T < 592 ? T : 592);
+  if (N <= 4) attnres_bwd_kernel<4><<<grid, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (const bf16*)out, (const bf16*)d_out, alpha, rstd, dl, dq, dw, T, D, H);
+  else if (N <= 9) attnres_bwd_kernel<9><<<grid, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (const bf16*)out, (const bf16*)d_out, alpha, rstd, dl, dq, dw, T, D, H);
+  else attnres_bwd_kernel<16><<<grid, D / 8, 0, ST(s)>>>(pl, N, (const bf16*)query, (const bf16*)w, (const bf16*)out, (const bf16*)d_out, alpha, rstd, dl, dq, dw, T, D, H);
+  RET();
+}
+extern "C" int hippo_adamw(void* p, const void* g, void* m, void* v, long long n, int p_bf16, int g_bf16, int m_bf16,
+                           int v_bf16, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                           float gscale, void* s) {
+  adamw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(s)>>>(p, g, m, v, n, p_bf16, g_bf16, m_bf16, v_bf16, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  RET();
+}
+extern "C" int hippo_sumsq(const void* x, long long n, int is_bf16, float* out, void* s) {
+  unsigned grid = (unsigned)((n + 256 * 8 - 1) / (256 * 8)); if (grid > 1184) grid = 1184; if (grid == 0) grid = 1;
+  sumsq_kernel<<<grid, 256, 0, ST(s)>>>(x, n, is_bf16, out);
+  RET();
+}
+// gs: device fp32[1]. compute_gs != 0: gs <- absmax(x)/(6*448) first (amax_scratch: device fp32[1])
+extern "C" int hippo_nvfp4_quantize(const void* x, int is_bf16, long long rows, long long K, float* gs, int compute_gs,
+                                    float* amax_scratch, void* packed, void* scales, void* s) {
+  if (K % 16) return -1;
+  long long n = rows * K, nb = n / 16;
+  if (compute_gs) {
+    cudaMemsetAsync(amax_scratch, 0, 4, ST(s));
+    unsigned grid = (unsigned)((n + 2047) / 2048); if (grid > 1184) grid = 1184;
+    absmax_kernel<<<grid, 256, 0, ST(s)>>>(x, n, is_bf16, amax_scratch);
+    nvfp4_global_scale_kernel<<<1, 1, 0, ST(s)>>>(amax_scratch, gs);
+  }
+  nvfp4_quant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>(x, is_bf16, nb, gs, (uint8_t*)packed, (uint8_t*)scales);
+  RET();
+}
+extern "C" int hippo_nvfp4_dequantize(const void* packed, const void* scales, const float* gs, void* out, int out_bf16,
+                                      long long rows, long long K, void* s) {
+  long long nb = rows * K / 16;
+  nvfp4_dequant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>((const uint8_t*)packed, (const uint8_t*)scales, gs, out, out_bf16, nb);
+  RET();
+}
+extern "C" int hippo_ce_stats(const float* z, const long long* target, float* mx, float* se, float* tz, long long C, int V, void* s) {
+  ce_stats_kernel<<<(unsigned)C, 512, 0, ST(s)>>>(z, target, mx, se, tz, V);
+  RET();
+}
+extern "C" int hippo_ce_grad(const float* z, const float* lse, const long long* target, const float* roww, void* dz,
+                             long long C, int V, void* s) {
+  ce_grad_kernel<<<(unsigned)C, 512, 0, ST(s)>>>(z, lse, target, roww, (bf16*)dz, V);
+  RET();
+}

@@ -157,22 +157,25 @@ class KDAAttention(nn.Module):
         K, Vd, Hl = cfg.head_dim, cfg.head_v_dim, self.Hl
         proj = column_linear_sp(h, self.in_proj_weight)                       # [T, n_pad]
         T = proj.shape[0]
-        q, k, v, fg, b, _ = torch.split(proj, self.sections + [proj.shape[1] - self.n_real], dim=1)
+        o_fg = 2 * self.key_l + self.val_l
+        fg = proj[:, o_fg:o_fg + 2 * Vd]
+        beta_mul = 2.0 if cfg.allow_neg_eigval else 1.0
         if cfg.use_short_conv:
-            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_seqlens)
-            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_seqlens)
-            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_seqlens)
+            q, k, v = proj[:, :self.key_l], proj[:, self.key_l:2 * self.key_l], proj[:, 2 * self.key_l:o_fg]
+            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_seqlens).reshape(T, Hl, K)
+            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_seqlens).reshape(T, Hl, K)
+            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_seqlens).reshape(T, Hl, Vd)
+            q = ops.l2norm(q) * (K ** -0.5)
+            k = ops.l2norm(k)
+            beta = torch.sigmoid(proj[:, o_fg + 2 * Vd:o_fg + 2 * Vd + Hl].float()) * beta_mul
         else:
-            q, k, v = ops.silu(q), ops.silu(k), ops.silu(v)
+            q, k, v, beta = ops.kda_prologue(proj, Hl, K, 0, self.key_l, 2 * self.key_l, o_fg + 2 * Vd,
+                                             K ** -0.5, beta_mul, True)
         g_raw = ops.linear(fg[:, :Vd].contiguous(), self.f_proj1_weight)
         gate = ops.linear(fg[:, Vd:].contiguous(), self.g_proj1_weight, self.g_proj1_bias)
-        beta = torch.sigmoid(b.float())
-        if cfg.allow_neg_eigval:
-            beta = beta * 2.0
         g = ops.kda_gate(g_raw.view(T, Hl, K), self.A_log, self.dt_bias, cfg.safe_gate, cfg.lower_bound)
-        o, final = ops.kda(q.reshape(T, Hl, K), k.reshape(T, Hl, K), v.reshape(T, Hl, Vd), g, beta,
-                           scale=K ** -0.5, initial_state=initial_state, cu_seqlens=cu_seqlens,
-                           use_qk_l2norm=True, mode=cfg.kda_mode)
+        o, final = ops.kda(q, k, v, g, beta, scale=1.0, initial_state=initial_state, cu_seqlens=cu_seqlens,
+                           use_qk_l2norm=False, mode=cfg.kda_mode)
         o = ops.gated_rmsnorm(o, gate.view(T, Hl, Vd), self.o_norm_weight, cfg.rms_norm_eps)
         out = row_linear_sp(o.reshape(T, Hl * Vd), self.o_proj_weight)       # [T/w, D]
         return out, final

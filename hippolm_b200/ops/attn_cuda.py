@@ -1,18 +1,62 @@
-"""CUDA path of causal varlen attention."""
+"""CUDA path of causal varlen attention (``csrc/attention.cu``)."""
 from __future__ import annotations
 
+import ctypes as _c
+
 import torch
-import torch.nn.functional as F
+
+from ._ext import lib, ptr, stream_ptr, check
+
+_CACHE = {"key": None}
+
+
+def tile_tables(cu_seqlens: torch.Tensor, T: int):
+    key = (cu_seqlens.data_ptr(), cu_seqlens._version, cu_seqlens.numel(), T)
+    if _CACHE["key"] == key and _CACHE.get("ref") is cu_seqlens:
+        return _CACHE["val"]
+    N = cu_seqlens.numel() - 1
+    cu = cu_seqlens.to(torch.int32).contiguous()
+    nt = (T + 63) // 64 + N
+    ts, tl, t0, te = (torch.empty(nt, dtype=torch.int32, device=cu.device) for _ in range(4))
+    check(lib().hippo_attn_build_tiles(ptr(cu), N, ptr(ts), ptr(tl), ptr(t0), ptr(te), nt, stream_ptr()),
+          "attn_build_tiles")
+    val = (ts, tl, t0, te, nt)
+    _CACHE.update(key=key, val=val, ref=cu_seqlens)
+    return val
+
+
+class _Attn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, scale):
+        T, H, DH = q.shape
+        assert DH in (64, 128), "CUDA attention supports head_dim 64 or 128"
+        q, k, v = (t.to(torch.bfloat16).contiguous() for t in (q, k, v))
+        ts, tl, t0, te, nt = tile_tables(cu_seqlens, T)
+        o = torch.empty_like(q)
+        lse = torch.empty((T, H), dtype=torch.float32, device=q.device)
+        check(lib().hippo_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(ts), ptr(tl), ptr(t0), nt, H, DH, _c.c_float(scale),
+                                   ptr(o), ptr(lse), stream_ptr()), "attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse, ts, tl, t0, te)
+        ctx.meta = (T, H, DH, nt, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, ts, tl, t0, te = ctx.saved_tensors
+        T, H, DH, nt, scale = ctx.meta
+        do = do.to(torch.bfloat16).contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty((T, H), dtype=torch.float32, device=q.device)
+        check(lib().hippo_attn_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(lse), ptr(delta), ptr(ts), ptr(tl),
+                                   ptr(t0), ptr(te), nt, H, DH, _c.c_longlong(T), _c.c_float(scale), ptr(dq), ptr(dk),
+                                   ptr(dv), stream_ptr()), "attn_bwd")
+        return dq, dk, dv, None, None
 
 
 def causal_attention(q, k, v, cu_seqlens, scale):
-    T, H, dh = q.shape
-    cu = [0, T] if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
-    outs = []
-    for s, e in zip(cu[:-1], cu[1:]):
-        if e <= s:
-            continue
-        o = F.scaled_dot_product_attention(q[s:e].transpose(0, 1).unsqueeze(0), k[s:e].transpose(0, 1).unsqueeze(0),
-                                           v[s:e].transpose(0, 1).unsqueeze(0), is_causal=True, scale=scale)
-        outs.append(o.squeeze(0).transpose(0, 1))
-    return torch.cat(outs, 0)
+    T, H, DH = q.shape
+    if scale is None:
+        scale = DH ** -0.5
+    if cu_seqlens is None:
+        cu_seqlens = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+    return _Attn.apply(q, k, v, cu_seqlens, float(scale))

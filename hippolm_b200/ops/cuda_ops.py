@@ -233,6 +233,43 @@ def rope(q, k, positions, theta):
 
 
 # ----------------------------------------------------------------------------- attention / KDA / AttnRes
+class _KDAPrologue(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu):
+        proj = _bf(proj).contiguous()
+        T, ld = proj.shape
+        dev = proj.device
+        q, k, v = (torch.empty((T, H, K), dtype=torch.bfloat16, device=dev) for _ in range(3))
+        beta, qr, kr = (torch.empty((T, H), dtype=torch.float32, device=dev) for _ in range(3))
+        check(lib().hippo_kda_prologue_fwd(ptr(proj), _c.c_longlong(ld), H, K, off_q, off_k, off_v, off_b, ptr(q),
+                                           ptr(k), ptr(v), ptr(beta), ptr(qr), ptr(kr), _c.c_longlong(T),
+                                           _c.c_float(scale), _c.c_float(beta_mul), int(apply_silu), stream_ptr()),
+              "kda_prologue_fwd")
+        ctx.save_for_backward(proj, qr, kr)
+        ctx.meta = (H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu)
+        return q, k, v, beta
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv, dbeta):
+        proj, qr, kr = ctx.saved_tensors
+        H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu = ctx.meta
+        T, ld = proj.shape
+        dproj = torch.zeros_like(proj)
+        dq = dq.float().contiguous() if dq is not None else torch.zeros((T, H, K), device=proj.device)
+        dk = dk.float().contiguous() if dk is not None else torch.zeros((T, H, K), device=proj.device)
+        dv = _bf(dv).contiguous() if dv is not None else torch.zeros((T, H, K), dtype=torch.bfloat16, device=proj.device)
+        dbeta = dbeta.float().contiguous() if dbeta is not None else torch.zeros((T, H), device=proj.device)
+        check(lib().hippo_kda_prologue_bwd(ptr(proj), _c.c_longlong(ld), H, K, off_q, off_k, off_v, off_b, ptr(dq),
+                                           ptr(dk), ptr(dv), ptr(dbeta), ptr(qr), ptr(kr), ptr(dproj),
+                                           _c.c_longlong(T), _c.c_float(scale), _c.c_float(beta_mul),
+                                           int(apply_silu), stream_ptr()), "kda_prologue_bwd")
+        return (dproj,) + (None,) * 9
+
+
+def kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu):
+    return _KDAPrologue.apply(proj, H, K, off_q, off_k, off_v, off_b, float(scale), float(beta_mul), bool(apply_silu))
+
+
 def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm):
     from . import kda_cuda
     return kda_cuda.kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)

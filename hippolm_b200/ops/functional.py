@@ -106,6 +106,21 @@ def short_conv_silu(x, weight, bias, cu_seqlens):
 
 
 # ----------------------------------------------------------------------------- KDA
+def kda_prologue(proj, H: int, K: int, off_q: int, off_k: int, off_v: int, off_b: int, scale: float,
+                 beta_mul: float = 1.0, apply_silu: bool = True):
+    """From the fused projection ``[T, n]`` (columns q | k | v | ... | b): q = l2norm(silu(q)) * scale,
+    k = l2norm(silu(k)), v = silu(v) as ``[T, H, K]`` and beta = sigmoid(b) * beta_mul as ``[T, H]`` fp32."""
+    if proj.is_cuda:
+        return _cu().kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu)
+    T = proj.shape[0]
+    act = F.silu if apply_silu else (lambda t: t)
+    q = _rk.l2norm(act(proj[:, off_q:off_q + H * K]).reshape(T, H, K)) * scale
+    k = _rk.l2norm(act(proj[:, off_k:off_k + H * K]).reshape(T, H, K))
+    v = act(proj[:, off_v:off_v + H * K]).reshape(T, H, K)
+    beta = torch.sigmoid(proj[:, off_b:off_b + H].float()) * beta_mul
+    return q, k, v, beta
+
+
 def kda_gate(x_g, A_log, dt_bias, safe_gate: bool = False, lower_bound: float = -5.0):
     if x_g.is_cuda:
         return _cu().kda_gate(x_g, A_log, dt_bias, safe_gate, lower_bound)

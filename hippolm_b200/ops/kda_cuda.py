@@ -69,5 +69,6 @@ def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm):
     if use_qk_l2norm:
         from ..ref.kda import l2norm
         q, k = l2norm(q.float()), l2norm(k.float())
-    q = q.float() * scale
+    if scale != 1.0:
+        q = q.float() * scale
     return _KDAFunction.apply(q, k, v, g, beta, initial_state, cu_seqlens)

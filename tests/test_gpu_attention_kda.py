@@ -1,0 +1,79 @@
+"""Flash attention and chunked KDA kernels vs fp32 torch oracles (forward + backward)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9)).item()
+
+
+@pytest.mark.parametrize("T,H,DH,cu", [(256, 2, 128, [0, 256]), (333, 2, 64, [0, 100, 333]),
+                                       (1000, 4, 128, [0, 64, 65, 700, 1000])])
+def test_causal_attention(T, H, DH, cu):
+    from hippolm_b200 import ops
+    from hippolm_b200.ref import ops as ro
+    g = torch.Generator(device="cuda").manual_seed(T)
+    q, k, v = (torch.randn(T, H, DH, device="cuda", generator=g).bfloat16() for _ in range(3))
+    do = torch.randn(T, H, DH, device="cuda", generator=g).bfloat16()
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    ins = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    o = ops.causal_attention(ins[0], ins[1], ins[2], cu_t)
+    o.backward(do)
+    ref_in = [t.float().requires_grad_(True) for t in (q, k, v)]
+    o2 = ro.causal_attention(ref_in[0], ref_in[1], ref_in[2], cu_t)
+    o2.backward(do.float())
+    assert _rel(o, o2) < 2e-2
+    for a, b in zip(ins, ref_in):
+        assert _rel(a.grad, b.grad) < 3e-2
+
+
+@pytest.mark.parametrize("T,H,D,cu,gs", [(128, 2, 128, [0, 128], 1.0), (200, 2, 64, [0, 70, 200], 1.0),
+                                         (700, 3, 128, [0, 100, 500, 700], 1.0), (512, 2, 128, [0, 512], 6.0)])
+def test_kda_forward_backward(T, H, D, cu, gs):
+    from hippolm_b200 import ops
+    from hippolm_b200.ops import _ext
+    from hippolm_b200.ref.kda import kda_chunked_anchored, l2norm
+    torch.manual_seed(T)
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda")) * gs
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    h0 = torch.randn(len(cu) - 1, H, D, D, device="cuda") * 0.1
+    do = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    df = torch.randn(len(cu) - 1, H, D, D, device="cuda") * 0.1
+    grads = []
+    outs = []
+    for impl in (0, 1):
+        ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta, h0)]
+        if impl == 0:
+            o, f = ops.kda(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, ins[5], cu_t, use_qk_l2norm=False)
+        else:
+            o, f = kda_chunked_anchored(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, ins[5], cu_t, False)
+        ((o.float() * do).sum() + (f * df).sum()).backward()
+        grads.append([t.grad for t in ins]); outs.append((o, f))
+    assert _rel(outs[0][0], outs[1][0]) < 2e-2 and _rel(outs[0][1], outs[1][1]) < 2e-2
+    for a, b in zip(*grads):
+        assert _rel(a, b) < 3e-2
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0
+
+
+def test_kda_matches_token_recurrence():
+    """Small case against the token-by-token oracle itself."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ref.kda import kda_recurrent, l2norm
+    torch.manual_seed(1)
+    T, H, D = 96, 1, 64
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda"))
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cu = torch.tensor([0, 40, 96], dtype=torch.int32, device="cuda")
+    o, f = ops.kda(q, k, v, g, beta, 1.0, None, cu, use_qk_l2norm=False)
+    o2, f2 = kda_recurrent(q.cpu(), k.cpu(), v.cpu(), g.cpu(), beta.cpu(), 1.0, None, cu.cpu().long())
+    assert _rel(o.cpu(), o2) < 2e-2 and _rel(f.cpu(), f2) < 2e-2

@@ -39,7 +39,8 @@ def parse():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="ours")
     p.add_argument("--model", type=str, default="7b", help="7b | 1p3b | tiny (tiny/1p3b are for smoke runs only)")
-    p.add_argument("--micro_batch_tokens", type=int, default=16384)
+    p.add_argument("--micro_batch_tokens", type=int, default=0,
+                   help="tokens per micro-batch; 0 = 8192 on one GPU (activations of 32 layers must fit), 16384 otherwise")
     p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
     p.add_argument("--no_fused_comm", action="store_true")
     p.add_argument("--bf16_ffn", action="store_true")
@@ -128,6 +129,8 @@ def main():
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}",
                    "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
             return subprocess.call(cmd)
+    if a.micro_batch_tokens <= 0:
+        a.micro_batch_tokens = 8192 if world == 1 else 16384
     m = dict(MODELS[a.model])
     name = m.pop("name")
     args = build_parser().parse_args([])

@@ -37,9 +37,10 @@ __device__ __forceinline__ void st8(bf16* p, const float (&f)[8]) {
 // One block per token, D/8 threads (each owns 8 contiguous channels; a head spans GS = dh/8 lanes,
 // GS a power of two <= 32). sources: N tensors [T, D]. Saves alpha [N,T,H] and rstd [N,T].
 template <int NMAX>
-__global__ void attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
-                                   bf16* __restrict__ out, float* __restrict__ alpha, float* __restrict__ rstd,
-                                   long long T, int D, int H, float eps) {
+__global__ void __launch_bounds__(512)
+attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
+                   bf16* __restrict__ out, float* __restrict__ alpha, float* __restrict__ rstd,
+                   long long T, int D, int H, float eps) {
   __shared__ float red[NMAX][32];
   const long long t = blockIdx.x;
   const int tid = threadIdx.x, c0 = tid * 8, dh = D / H, GS = dh / 8, h = c0 / dh;
@@ -48,21 +49,22 @@ __global__ void attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ 
   ld8(query + c0, fq); ld8(w + c0, fw);
 #pragma unroll
   for (int i = 0; i < 8; ++i) qw[i] = fq[i] * fw[i];
-  float v[NMAX][8], ss[NMAX], dot[NMAX];
+  float dot[NMAX];
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) {
-    ss[n] = 0.f; dot[n] = 0.f;
+    dot[n] = 0.f;
     if (n < N) {
-      ld8((const bf16*)src.p[n] + t * D + c0, v[n]);
+      float v[8], ss = 0.f;
+      ld8((const bf16*)src.p[n] + t * D + c0, v);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { ss[n] += v[n][i] * v[n][i]; dot[n] += v[n][i] * qw[i]; }
+      for (int i = 0; i < 8; ++i) { ss += v[i] * v[i]; dot[n] += v[i] * qw[i]; }
       for (int o = 1; o < GS; o <<= 1) dot[n] += __shfl_xor_sync(0xFFFFFFFFu, dot[n], o);
-      float s = wsum(ss[n]);
+      float s = wsum(ss);
       if (lane == 0) red[n][warp] = s;
     }
   }
   __syncthreads();
-  float mx = -INFINITY, logit[NMAX];
+  float mx = -INFINITY;
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) {
     if (n < N) {
@@ -70,21 +72,23 @@ __global__ void attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ 
       for (int k = 0; k < nw; ++k) s += red[n][k];
       float r = rsqrtf(s / D + eps);
       if (tid == 0) rstd[(long long)n * T + t] = r;
-      logit[n] = dot[n] * r;
-      mx = fmaxf(mx, logit[n]);
+      dot[n] *= r;                                     // logit
+      mx = fmaxf(mx, dot[n]);
     }
   }
   float den = 0.f;
 #pragma unroll
-  for (int n = 0; n < NMAX; ++n) if (n < N) { logit[n] = __expf(logit[n] - mx); den += logit[n]; }
+  for (int n = 0; n < NMAX; ++n) if (n < N) { dot[n] = __expf(dot[n] - mx); den += dot[n]; }
   float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) {
     if (n < N) {
-      float a = logit[n] / den;
+      float a = dot[n] / den;
       if ((tid % GS) == 0) alpha[((long long)n * T + t) * H + h] = a;
+      float v[8];
+      ld8((const bf16*)src.p[n] + t * D + c0, v);      // second read hits L1/L2
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] += a * v[n][i];
+      for (int i = 0; i < 8; ++i) o[i] += a * v[i];
     }
   }
   st8(out + t * D + c0, o);
@@ -92,10 +96,11 @@ __global__ void attnres_fwd_kernel(PtrList src, int N, const bf16* __restrict__ 
 
 // grid-stride over tokens; dq/dw partials in registers, one atomicAdd per channel per block at the end
 template <int NMAX>
-__global__ void attnres_bwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
-                                   const bf16* __restrict__ out, const bf16* __restrict__ d_out,
-                                   const float* __restrict__ alpha, const float* __restrict__ rstd, MutPtrList dsrc,
-                                   float* __restrict__ dq, float* __restrict__ dw, long long T, int D, int H) {
+__global__ void __launch_bounds__(512)
+attnres_bwd_kernel(PtrList src, int N, const bf16* __restrict__ query, const bf16* __restrict__ w,
+                   const bf16* __restrict__ out, const bf16* __restrict__ d_out,
+                   const float* __restrict__ alpha, const float* __restrict__ rstd, MutPtrList dsrc,
+                   float* __restrict__ dq, float* __restrict__ dw, long long T, int D, int H) {
   __shared__ float red[NMAX][32];
   const int tid = threadIdx.x, c0 = tid * 8, dh = D / H, GS = dh / 8, h = c0 / dh;
   const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
@@ -110,22 +115,23 @@ __global__ void attnres_bwd_kernel(PtrList src, int N, const bf16* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 8; ++i) dout_o += go[i] * fo[i];
     for (int o = 1; o < GS; o <<= 1) dout_o += __shfl_xor_sync(0xFFFFFFFFu, dout_o, o);
-    float v[NMAX][8], ds[NMAX], lg[NMAX];
+    float ds[NMAX];
     __syncthreads();
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) {
+      ds[n] = 0.f;
       if (n < N) {
-        ld8((const bf16*)src.p[n] + t * D + c0, v[n]);
+        float v[8];
+        ld8((const bf16*)src.p[n] + t * D + c0, v);
         float dv = 0.f, dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { dv += go[i] * v[n][i]; dot += v[n][i] * fq[i] * fw[i]; }
+        for (int i = 0; i < 8; ++i) { dv += go[i] * v[i]; dot += v[i] * fq[i] * fw[i]; }
         for (int o = 1; o < GS; o <<= 1) { dv += __shfl_xor_sync(0xFFFFFFFFu, dv, o); dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o); }
         float a = alpha[((long long)n * T + t) * H + h];
         float r = rstd[(long long)n * T + t];
         ds[n] = a * (dv - dout_o);
-        lg[n] = dot * r;
         // sum over heads of ds*logit: each head counted once (first lane of the head group)
-        float contrib = ((tid % GS) == 0) ? ds[n] * lg[n] : 0.f;
+        float contrib = ((tid % GS) == 0) ? ds[n] * dot * r : 0.f;
         contrib = wsum(contrib);
         if (lane == 0) red[n][warp] = contrib;
       }
@@ -138,12 +144,13 @@ __global__ void attnres_bwd_kernel(PtrList src, int N, const bf16* __restrict__ 
         for (int k = 0; k < nw; ++k) sdl += red[n][k];
         float a = alpha[((long long)n * T + t) * H + h];
         float r = rstd[(long long)n * T + t];
-        float dvn[8];
+        float v[8], dvn[8];
+        ld8((const bf16*)src.p[n] + t * D + c0, v);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          dvn[i] = a * go[i] + ds[n] * r * fq[i] * fw[i] - v[n][i] * r * r / D * sdl;
-          dqa[i] += ds[n] * v[n][i] * r * fw[i];
-          dwa[i] += ds[n] * fq[i] * v[n][i] * r;
+          dvn[i] = a * go[i] + ds[n] * r * fq[i] * fw[i] - v[i] * r * r / D * sdl;
+          dqa[i] += ds[n] * v[i] * r * fw[i];
+          dwa[i] += ds[n] * fq[i] * v[i] * r;
         }
         st8((bf16*)dsrc.p[n] + t * D + c0, dvn);
       }
@@ -316,7 +323,7 @@ using namespace hippo;
 
 extern "C" int hippo_attnres_fwd(const void* const* srcs, int N, const void* query, const void* w, void* out, float* alpha,
                                  float* rstd, long long T, int D, int H, float eps, void* s) {
-  if (N > AR_MAX || D % 8 || D / 8 > 1024 || (D / H) % 8) return -1;
+  if (N > AR_MAX || D % 8 || D / 8 > 512 || (D / H) % 8) return -1;
   int gs = (D / H) / 8;
   if (gs > 32 || (gs & (gs - 1))) return -2;
   PtrList pl; for (int i = 0; i < N; ++i) pl.p[i] = srcs[i];
@@ -328,7 +335,7 @@ extern "C" int hippo_attnres_fwd(const void* const* srcs, int N, const void* que
 extern "C" int hippo_attnres_bwd(const void* const* srcs, int N, const void* query, const void* w, const void* out,
                                  const void* d_out, const float* alpha, const float* rstd, void* const* dsrcs, float* dq,
                                  float* dw, long long T, int D, int H, void* s) {
-  if (N > AR_MAX || D % 8 || D / 8 > 1024) return -1;
+  if (N > AR_MAX || D % 8 || D / 8 > 512) return -1;
   PtrList pl; MutPtrList dl;
   for (int i = 0; i < N; ++i) { pl.p[i] = srcs[i]; dl.p[i] = dsrcs[i]; }
   unsigned grid = (unsigned)(T < 592 ? T : 592);

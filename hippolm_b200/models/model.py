@@ -120,7 +120,7 @@ class KDAAttention(nn.Module):
         self.in_proj_weight = _mark(
             nn.Parameter(fused.to(device=device, dtype=dtype)), "muon",
             muon_segments=[(0, 2 * self.key_l + self.val_l), (o_fg, o_fg + 2 * Vd), (o_fg + 2 * Vd, n_real)],
-            tp_replicated_rows=(o_fg, o_fg + 2 * Vd))
+            tp_replicated_rows=(o_fg, o_fg + 2 * Vd), tp_shard_dim=0)
         if cfg.use_short_conv:
             def conv_w(nm, dim_full):
                 full = (torch.rand((dim_full, cfg.conv_size), generator=_seeded(pre + nm, seed)) * 2 - 1) \
@@ -130,9 +130,9 @@ class KDAAttention(nn.Module):
             self.k_conv1d_weight = conv_w("k_conv1d", cfg.key_dim)
             self.v_conv1d_weight = conv_w("v_conv1d", cfg.value_dim)
         self.f_proj1_weight = _mark(nn.Parameter(_shard_rows(
-            _xavier(pre + "f_proj1", (cfg.key_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon")
+            _xavier(pre + "f_proj1", (cfg.key_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon", tp_shard_dim=0)
         self.g_proj1_weight = _mark(nn.Parameter(_shard_rows(
-            _xavier(pre + "g_proj1", (cfg.value_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon")
+            _xavier(pre + "g_proj1", (cfg.value_dim, Vd), seed), r, w).to(device=device, dtype=dtype)), "muon", tp_shard_dim=0)
         self.g_proj1_bias = _mark(nn.Parameter(torch.zeros(self.val_l, device=device, dtype=dtype)), "adamw")
         gen = _seeded(pre + "gate", seed)
         if cfg.safe_gate:
@@ -148,7 +148,7 @@ class KDAAttention(nn.Module):
         self.o_norm_weight = _mark(nn.Parameter(torch.ones(Vd, device=device, dtype=dtype)), "adamw", True)
         self.o_proj_weight = _mark(nn.Parameter(_shard_cols(
             _xavier(pre + "o_proj", (D, cfg.value_dim), seed), r, w).contiguous().to(device=device, dtype=dtype)),
-            "muon")
+            "muon", tp_shard_dim=1)
         self._register_state_dict_hook(_kda_split_hook)
         self._register_load_state_dict_pre_hook(_kda_fuse_hook, with_module=True)
 
@@ -230,9 +230,11 @@ class FullAttention(nn.Module):
         self.Hl = H // w
         pre = f"layers.{layer_idx}.attn."
         parts = [_shard_rows(_xavier(pre + n, (H * dh, D), seed), r, w) for n in ("q", "k", "v")]
-        self.qkv_proj_weight = _mark(nn.Parameter(torch.cat(parts, 0).to(device=device, dtype=dtype)), "muon")
+        self.qkv_proj_weight = _mark(nn.Parameter(torch.cat(parts, 0).to(device=device, dtype=dtype)), "muon",
+                                     tp_shard_dim=0)
         self.o_proj_weight = _mark(nn.Parameter(_shard_cols(
-            _xavier(pre + "o_proj", (D, H * dh), seed), r, w).contiguous().to(device=device, dtype=dtype)), "muon")
+            _xavier(pre + "o_proj", (D, H * dh), seed), r, w).contiguous().to(device=device, dtype=dtype)), "muon",
+            tp_shard_dim=1)
         self._register_state_dict_hook(_attn_names_out)
         self._register_load_state_dict_pre_hook(_attn_names_in, with_module=True)
 
@@ -278,12 +280,15 @@ class SwiGLU(nn.Module):
             nm = cfg.ffn_nvfp4_no_bf16_master
             self.gate_up_proj = NVFP4Linear(D, 2 * I // w, nm, device, dtype, init_weight=torch.cat([gate, up], 0))
             self.down_proj = NVFP4Linear(I // w, D, nm, device, dtype, init_weight=down)
+            self.gate_up_proj.tp_shard_dim, self.down_proj.tp_shard_dim = 0, 1
+            if not nm:
+                self.gate_up_proj.weight.tp_shard_dim, self.down_proj.weight.tp_shard_dim = 0, 1
         else:
             self.gate_up_proj = nn.Module()
             self.gate_up_proj.weight = _mark(nn.Parameter(torch.cat([gate, up], 0).to(device=device, dtype=dtype)),
-                                             "muon")
+                                             "muon", tp_shard_dim=0)
             self.down_proj = nn.Module()
-            self.down_proj.weight = _mark(nn.Parameter(down.to(device=device, dtype=dtype)), "muon")
+            self.down_proj.weight = _mark(nn.Parameter(down.to(device=device, dtype=dtype)), "muon", tp_shard_dim=1)
 
     def forward(self, h):
         if self.nvfp4:
@@ -408,12 +413,8 @@ class _VocabParallelLCE(torch.autograd.Function):
             vc = valid[s:e]
             loss_sum += torch.where(vc, lse - tz, torch.zeros_like(lse)).sum()
             # dz = (softmax - onehot)/n_valid on valid rows
-            p = (z - lse.unsqueeze(-1)).exp()
             lt = local_t[s:e]
-            rows = (lt >= 0).nonzero(as_tuple=True)[0]
-            p[rows, lt[rows]] -= 1.0
-            p = p * (vc.unsqueeze(-1).to(p.dtype) / nv)
-            pz = p.to(x.dtype)
+            pz = ops.lce_chunk_grad(z, lse, lt, vc.float() / nv).to(x.dtype)
             dx[s:e] = ops.gemm_nn(pz, weight)
             dw += ops.gemm_tn(pz, xc).float()
         dx_shard = reduce_scatter_dim0(dx, m.tp_group, m.tp)

@@ -331,9 +331,18 @@ def adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
 
 def lce_chunk_stats(x, w, targets_local):
     z = gemm_nt(x, w, out_dtype=torch.float32)
-    mx = z.max(-1).values
-    se = (z - mx.unsqueeze(-1)).exp().sum(-1)
-    tl = targets_local.clamp(min=0)
-    tz = z.gather(1, tl.unsqueeze(1)).squeeze(1)
-    tz = torch.where(targets_local >= 0, tz, torch.zeros_like(tz))
+    C, V = z.shape
+    mx, se, tz = (torch.empty(C, dtype=torch.float32, device=z.device) for _ in range(3))
+    tg = targets_local.to(torch.int64).contiguous()
+    check(lib().hippo_ce_stats(ptr(z), ptr(tg), ptr(mx), ptr(se), ptr(tz), _c.c_longlong(C), V, stream_ptr()), "ce_stats")
     return z, mx, se, tz
+
+
+def lce_chunk_grad(z, lse, targets_local, row_weight):
+    """dz = (softmax(z) - onehot) * row_weight as bf16 (z: fp32 logits of this vocab shard)."""
+    C, V = z.shape
+    dz = torch.empty((C, V), dtype=torch.bfloat16, device=z.device)
+    tg = targets_local.to(torch.int64).contiguous()
+    check(lib().hippo_ce_grad(ptr(z), ptr(lse.float().contiguous()), ptr(tg), ptr(row_weight.float().contiguous()),
+                              ptr(dz), _c.c_longlong(C), V, stream_ptr()), "ce_grad")
+    return dz

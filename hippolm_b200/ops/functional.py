@@ -219,3 +219,13 @@ def lce_chunk_stats(x, w, targets_local):
     tz = z.gather(1, tl.unsqueeze(1)).squeeze(1)
     tz = torch.where(targets_local >= 0, tz, torch.zeros_like(tz))
     return z, mx, se, tz
+
+
+def lce_chunk_grad(z, lse, targets_local, row_weight):
+    """(softmax(z) - onehot(target)) * row_weight, in the GEMM input dtype."""
+    if z.is_cuda:
+        return _cu().lce_chunk_grad(z, lse, targets_local, row_weight)
+    p = (z - lse.unsqueeze(-1)).exp()
+    rows = (targets_local >= 0).nonzero(as_tuple=True)[0]
+    p[rows, targets_local[rows]] -= 1.0
+    return p * row_weight.unsqueeze(-1)

@@ -1,23 +1,42 @@
-"""CUDA path of NVFP4 quantise / dequantise / block-scaled GEMM."""
+"""CUDA path of NVFP4 quantise / dequantise (``csrc/misc_ops.cu``) and the block-scaled GEMM."""
 from __future__ import annotations
+
+import ctypes as _c
 
 import torch
 
-from ..ref import ops as _ro
+from ._ext import lib, ptr, stream_ptr, check
 
 
-def quantize(w, global_scale=None):
-    return _ro.nvfp4_quantize(w, global_scale)
+def quantize(w: torch.Tensor, global_scale=None):
+    """[N, K] -> (packed u8 [N, K/2], e4m3 scales [N, K/16], fp32 global scale [1])."""
+    N, K = w.shape
+    assert K % 16 == 0
+    x = w if w.dtype in (torch.bfloat16, torch.float32) else w.float()
+    x = x.contiguous()
+    packed = torch.empty((N, K // 2), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((N, K // 16), dtype=torch.uint8, device=w.device)
+    compute = global_scale is None
+    gs = torch.empty(1, dtype=torch.float32, device=w.device) if compute else global_scale.float().reshape(1).contiguous()
+    scratch = torch.empty(1, dtype=torch.float32, device=w.device)
+    check(lib().hippo_nvfp4_quantize(ptr(x), int(x.dtype == torch.bfloat16), _c.c_longlong(N), _c.c_longlong(K), ptr(gs),
+                                     int(compute), ptr(scratch), ptr(packed), ptr(scales), stream_ptr()), "nvfp4_quantize")
+    return packed, scales.view(torch.float8_e4m3fn), gs
 
 
 def dequantize(packed, scales, global_scale, dtype=torch.float32):
-    return _ro.nvfp4_dequantize(packed, scales, global_scale, dtype)
+    N, K2 = packed.shape
+    K = K2 * 2
+    od = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    out = torch.empty((N, K), dtype=od, device=packed.device)
+    sc = scales.view(torch.uint8).contiguous()
+    check(lib().hippo_nvfp4_dequantize(ptr(packed.contiguous()), ptr(sc), ptr(global_scale.float().contiguous()), ptr(out),
+                                       int(od == torch.bfloat16), _c.c_longlong(N), _c.c_longlong(K), stream_ptr()),
+          "nvfp4_dequantize")
+    return out if od == dtype else out.to(dtype)
 
 
 def gemm_nt(x, packed, scales, global_scale, act_quant=True):
-    from . import cuda_ops
-    w = dequantize(packed, scales, global_scale, torch.bfloat16)
-    xq = x
-    if act_quant:
-        xq = dequantize(*quantize(x), dtype=torch.bfloat16)
-    return cuda_ops.gemm_nt(xq, w)
+    """y = Q(x) dq(W)^T."""
+    from . import fp4_gemm
+    return fp4_gemm.gemm_nt(x, packed, scales, global_scale, act_quant)

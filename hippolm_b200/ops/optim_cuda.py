@@ -1,13 +1,31 @@
-"""CUDA path of the optimizer update kernels."""
+"""CUDA path of the optimizer update kernels (``csrc/misc_ops.cu``)."""
 from __future__ import annotations
+
+import ctypes as _c
 
 import torch
 
+from ._ext import lib, ptr, stream_ptr, check
+
+
+def _isbf(t):
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
 
 def adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
-    gf = g.float() * grad_scale
-    mf = m.float().mul_(beta1).add_(gf, alpha=1 - beta1)
-    vf = v.float().mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
-    m.copy_(mf); v.copy_(vf)
-    upd = (mf / (1 - beta1 ** step)) / ((vf / (1 - beta2 ** step)).sqrt() + eps)
-    p.copy_(p.float().mul_(1 - lr * wd).add_(upd, alpha=-lr))
+    assert p.is_contiguous() and m.is_contiguous() and v.is_contiguous()
+    g = g.contiguous()
+    check(lib().hippo_adamw(ptr(p), ptr(g), ptr(m), ptr(v), _c.c_longlong(p.numel()), _isbf(p), _isbf(g), _isbf(m),
+                            _isbf(v), _c.c_float(lr), _c.c_float(beta1), _c.c_float(beta2), _c.c_float(eps),
+                            _c.c_float(wd), _c.c_float(1 - beta1 ** step), _c.c_float(1 - beta2 ** step),
+                            _c.c_float(grad_scale), stream_ptr()), "adamw")
+
+
+def sumsq_into(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[0] += sum(x^2) (fp32 accumulate)."""
+    x = x.contiguous()
+    check(lib().hippo_sumsq(ptr(x), _c.c_longlong(x.numel()), _isbf(x), ptr(out), stream_ptr()), "sumsq")

@@ -8,6 +8,9 @@ Formulas (``muon.py:247-287,392-473``):
   M <- beta M + G;  U = G + beta M (nesterov);  W <- W (1 - lr wd) - lr NS5(U)
 AdamW here is the standard one (v from g^2, both bias corrections); ``reference_compat=True``
 reproduces the reference's variant (v from m^2, no first-moment correction, ``adamw.py:257-302``).
+``ns_scope='shard'`` orthogonalises each TP rank's shard (what the reference does); ``'full'`` gathers a
+TP-sharded matrix to one owner rank per matrix, orthogonalises the whole matrix there and scatters the
+slices back (TP-invariant result).
 Differences on purpose: NS runs on the whole (local) matrix, not on 4096-row slices
 (``ns_row_chunk`` restores slices); fused projections are orthogonalised per ``muon_segments``.
 """
@@ -67,7 +70,8 @@ class _Entry:
 class Muon:
     def __init__(self, lr: float = 0.02, momentum: float = 0.95, weight_decay: float = 0.0,
                  nesterov: bool = True, ns_steps: int = 5, momentum_dtype=torch.bfloat16,
-                 offload: bool = False, ns_row_chunk: Optional[int] = None):
+                 offload: bool = False, ns_row_chunk: Optional[int] = None, ns_scope: str = "shard"):
+        self.ns_scope = ns_scope
         self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.nesterov, self.ns_steps = nesterov, ns_steps
         self.momentum_dtype = momentum_dtype
@@ -103,8 +107,33 @@ class Muon:
             segs = out
         return segs
 
+    def _shard_dim(self, e: _Entry, seg) -> Optional[int]:
+        """TP shard dimension of a segment (None = replicated / unsharded)."""
+        if e.param is not None:
+            rows = getattr(e.param, "tp_replicated_rows", None)
+            if getattr(e.param, "tp_replicated", False) or (rows is not None and seg[0] >= rows[0] and seg[1] <= rows[1]):
+                return None
+            return getattr(e.param, "tp_shard_dim", None)
+        return getattr(e.module, "tp_shard_dim", None)
+
+    def _apply(self, e: _Entry, a: int, b: int, upd: torch.Tensor, wd_factor: float):
+        if e.param is not None:
+            pw = e.param.data[a:b]
+            if wd_factor != 1.0:
+                pw.mul_(wd_factor)
+            pw.add_(upd.to(pw.dtype), alpha=-self.lr)
+        else:
+            for r0, r1 in e.module.chunk_ranges():
+                lo, hi = max(r0, a), min(r1, b)
+                if lo < hi:
+                    e.module.decay_and_apply_chunk(lo, hi, upd[lo - a:hi - a], self.lr, wd_factor)
+
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0):
+        mesh = get_mesh()
+        full_scope = self.ns_scope == "full" and mesh.tp > 1
+        wd_factor = 1.0 - self.lr * self.weight_decay
+        work = []                                   # (entry, a, b, u_segment)
         for e in self.entries:
             g = e.grad()
             if g is None:
@@ -120,22 +149,38 @@ class Muon:
                 e.exp_avg.copy_(m.to(self.momentum_dtype), non_blocking=True)
             else:
                 e.exp_avg.copy_(m)
-            wd_factor = 1.0 - self.lr * self.weight_decay
+            e.step += 1
             for (a, b) in self._segments(e):
                 if b <= a:
                     continue
-                upd = ops.newton_schulz5(u[a:b], self.ns_steps)
-                if e.param is not None:
-                    pw = e.param.data[a:b]
-                    if wd_factor != 1.0:
-                        pw.mul_(wd_factor)
-                    pw.add_(upd.to(pw.dtype), alpha=-self.lr)
+                if full_scope and self._shard_dim(e, (a, b)) is not None:
+                    work.append((e, a, b, u[a:b].contiguous()))
                 else:
-                    for r0, r1 in e.module.chunk_ranges():
-                        lo, hi = max(r0, a), min(r1, b)
-                        if lo < hi:
-                            e.module.decay_and_apply_chunk(lo, hi, upd[lo - a:hi - a], self.lr, wd_factor)
-            e.step += 1
+                    self._apply(e, a, b, ops.newton_schulz5(u[a:b], self.ns_steps), wd_factor)
+        if not work:
+            return
+        # full-matrix NS for TP-sharded matrices: matrix i is gathered to TP rank i % tp, orthogonalised there
+        # (every rank works on a different matrix of the round) and the slices are scattered back.
+        tp, r, grp = mesh.tp, mesh.tp_rank, mesh.tp_group
+        ranks = mesh.tp_ranks()
+        for r0 in range(0, len(work), tp):
+            rnd = work[r0:r0 + tp]
+            gathered = [None] * len(rnd)
+            for j, (e, a, b, u) in enumerate(rnd):
+                lst = [torch.empty_like(u) for _ in range(tp)] if r == j else None
+                dist.gather(u, lst, dst=ranks[j], group=grp)
+                gathered[j] = lst
+            outs = [None] * len(rnd)
+            for j, (e, a, b, u) in enumerate(rnd):
+                if r == j:
+                    dim = self._shard_dim(e, (a, b))
+                    full = torch.cat(gathered[j], dim=dim)
+                    o = ops.newton_schulz5(full, self.ns_steps)
+                    outs[j] = [t.contiguous() for t in o.chunk(tp, dim=dim)]
+            for j, (e, a, b, u) in enumerate(rnd):
+                mine = torch.empty_like(u)
+                dist.scatter(mine, outs[j] if r == j else None, src=ranks[j], group=grp)
+                self._apply(e, a, b, mine, wd_factor)
 
     def zero_grad(self):
         for e in self.entries:
@@ -248,7 +293,7 @@ def build_param_groups(model: nn.Module, args=None, precision: Optional[Precisio
     muon = Muon(lr=g("muon_lr", 0.02), momentum=g("muon_momentum", 0.95),
                 weight_decay=g("muon_weight_decay", 0.0), nesterov=True, ns_steps=5,
                 momentum_dtype=prec.muon_momentum, offload=offload,
-                ns_row_chunk=g("muon_ns_row_chunk", None))
+                ns_row_chunk=g("muon_ns_row_chunk", None), ns_scope=g("muon_ns_scope", "shard"))
     adamw = AdamW(lr=g("learning_rate", 0.004), betas=(g("adamw_beta1", 0.9), g("adamw_beta2", 0.95)),
                   eps=g("adamw_eps", 1e-8), weight_decay=g("weight_decay", 0.01),
                   m_dtype=prec.adamw_m, v_dtype=prec.adamw_v, offload=offload,
@@ -276,31 +321,33 @@ def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None) -> torch.Tensor:
     the TP group; replicated ones are counted once."""
     m = mesh or get_mesh()
     dev = None
-    sharded = None
-    repl = None
+    for e in list(muon.entries) + list(adamw.entries):
+        g = e.grad()
+        if g is not None:
+            dev = g.device
+            break
+    if dev is None:
+        return torch.zeros(())
+    acc = torch.zeros(2, dtype=torch.float32, device=dev)      # [sharded, replicated]
+    if dev.type == "cuda":
+        from ..ops.optim_cuda import sumsq_into
+    else:
+        def sumsq_into(x, out):
+            out += x.float().pow(2).sum()
     for e in list(muon.entries) + list(adamw.entries):
         g = e.grad()
         if g is None:
             continue
-        dev = g.device
-        gf = g.float()
         rows = getattr(e.param, "tp_replicated_rows", None) if e.param is not None else None
         is_repl = e.param is not None and getattr(e.param, "tp_replicated", False)
         if is_repl:
-            s = gf.pow(2).sum(); repl = s if repl is None else repl + s
+            sumsq_into(g, acc[1:2])
         elif rows is not None:
             a, b = rows
-            r = gf[a:b].pow(2).sum()
-            s = gf.pow(2).sum() - r
-            repl = r if repl is None else repl + r
-            sharded = s if sharded is None else sharded + s
+            sumsq_into(g[:a], acc[0:1]); sumsq_into(g[a:b], acc[1:2]); sumsq_into(g[b:], acc[0:1])
         else:
-            s = gf.pow(2).sum(); sharded = s if sharded is None else sharded + s
-    if dev is None:
-        return torch.zeros(())
-    z = torch.zeros((), device=dev)
-    sharded = z if sharded is None else sharded
-    repl = z if repl is None else repl
+            sumsq_into(g, acc[0:1])
+    sharded, repl = acc[0], acc[1]
     if m.tp > 1:
         sharded = sharded.clone()
         dist.all_reduce(sharded, group=m.tp_group)

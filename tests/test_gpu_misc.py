@@ -1,0 +1,84 @@
+"""AttnRes, NVFP4 quantiser, AdamW and cross-entropy kernels vs torch references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9)).item()
+
+
+@pytest.mark.parametrize("N,T,D,H", [(2, 100, 256, 4), (5, 300, 2048, 16), (9, 64, 4096, 32)])
+def test_attn_res(N, T, D, H):
+    from hippolm_b200 import ops
+    from hippolm_b200.ref import ops as ro
+    g = torch.Generator(device="cuda").manual_seed(N * T)
+    srcs = [torch.randn(T, D, device="cuda", generator=g).bfloat16().requires_grad_(True) for _ in range(N)]
+    q = (0.3 * torch.randn(H, D // H, device="cuda", generator=g)).bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16().requires_grad_(True)
+    dout = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    out = ops.attn_res(srcs, q, w, 1e-6)
+    out.backward(dout)
+    s2 = [s.detach().float().requires_grad_(True) for s in srcs]
+    q2, w2 = q.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    out2 = ro.attn_res(torch.stack(s2, 0), q2, w2, 1e-6)
+    out2.backward(dout.float())
+    assert _rel(out, out2) < 1e-2
+    for a, b in zip(srcs, s2):
+        assert _rel(a.grad, b.grad) < 3e-2
+    assert _rel(q.grad, q2.grad) < 3e-2 and _rel(w.grad, w2.grad) < 3e-2
+
+
+def test_nvfp4_quantize_byte_exact_and_roundtrip():
+    from hippolm_b200 import ops
+    from hippolm_b200.ref import ops as ro
+    torch.manual_seed(0)
+    w = torch.randn(256, 512, device="cuda") * 0.05
+    w[3, :16] = 0.0
+    p, s, gs = ops.nvfp4_quantize(w)
+    p2, s2, gs2 = ro.nvfp4_quantize(w.cpu())
+    assert torch.equal(gs.cpu(), gs2)
+    assert torch.equal(s.view(torch.uint8).cpu(), s2.view(torch.uint8))
+    assert torch.equal(p.cpu(), p2)
+    d = ops.nvfp4_dequantize(p, s, gs, torch.float32)
+    d2 = ro.nvfp4_dequantize(p2, s2, gs2)
+    assert torch.equal(d.cpu(), d2)
+    assert _rel(d, w) < 0.2
+    pb, sb, gb = ops.nvfp4_quantize(w.bfloat16(), gs)
+    assert pb.shape == p.shape
+
+
+def test_adamw_kernel():
+    from hippolm_b200 import ops
+    torch.manual_seed(0)
+    for dt in (torch.float32, torch.bfloat16):
+        p = torch.randn(1000, device="cuda").to(dt); g = torch.randn(1000, device="cuda").to(dt)
+        m = torch.zeros(1000, device="cuda").to(dt); v = torch.zeros(1000, device="cuda").to(dt)
+        pc, gc, mc, vc = (t.cpu().clone() for t in (p, g, m, v))
+        for step in (1, 2):
+            ops.adamw_update(p, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 0.5)
+            ops.adamw_update(pc, gc, mc, vc, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 0.5)
+        assert _rel(p.cpu(), pc) < (1e-5 if dt == torch.float32 else 2e-2)
+
+
+def test_lce_kernels():
+    from hippolm_b200 import ops
+    torch.manual_seed(0)
+    C, D, V = 300, 256, 1000
+    x = torch.randn(C, D, device="cuda").bfloat16()
+    w = (0.05 * torch.randn(V, D, device="cuda")).bfloat16()
+    tg = torch.randint(0, V, (C,), device="cuda"); tg[::7] = -1
+    z, mx, se, tz = ops.lce_chunk_stats(x, w, tg)
+    zr = x.float() @ w.float().t()
+    assert _rel(z, zr) < 1e-2
+    assert _rel(mx, zr.max(-1).values) < 1e-2
+    lse = mx + se.log()
+    assert _rel(lse, torch.logsumexp(zr, -1)) < 1e-2
+    roww = (tg >= 0).float() / 10.0
+    dz = ops.lce_chunk_grad(z, lse, tg, roww)
+    ref = torch.softmax(z, -1)
+    rows = (tg >= 0).nonzero(as_tuple=True)[0]
+    ref[rows, tg[rows]] -= 1
+    ref = ref * roww.unsqueeze(-1)
+    assert (dz.float() - ref).abs().max() < 1e-3

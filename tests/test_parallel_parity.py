@@ -1,0 +1,95 @@
+"""TP (+SP) and DP runs must reproduce the single-process loss and weights (CPU, gloo, spawned ranks)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _args(tp, dp, nvfp4=False):
+    from hippolm_b200.cli import build_parser
+    a = build_parser().parse_args([])
+    a.vocab_size, a.hidden_size, a.num_heads, a.head_dim = 256, 64, 4, 16
+    a.num_layers, a.num_blocks, a.intermediate_size = 4, 2, 128
+    a.batch_size, a.seq_len, a.max_steps, a.lr_decay_steps = 4, 64, 100, 0
+    a.tp_size, a.dp_size = tp, dp
+    a.ffn_nvfp4 = a.ffn_nvfp4_no_bf16_master = nvfp4
+    a.precision = {k: {"dtype": "fp32"} for k in ("model_weights", "gradients", "activations", "muon_momentum",
+                                                  "adamw_m", "adamw_v")}
+    a.seed = 3
+    a.muon_ns_scope = "full"
+    return a
+
+
+def _batch(dp_rank, dp):
+    from hippolm_b200.data.packing import synthetic_packed_batch
+    ids, labels, cu = synthetic_packed_batch(4 * 64, 256, 11, 16, 64, row_len=64)
+    if dp == 1:
+        return {"input_ids": ids, "labels": labels, "cu_seqlens": cu, "row_len": 64}
+    n = ids.numel() // dp
+    s, e = dp_rank * n, (dp_rank + 1) * n
+    from hippolm_b200.data.packing import slice_cu_seqlens
+    return {"input_ids": ids[s:e], "labels": labels[s:e], "cu_seqlens": slice_cu_seqlens(cu, s, e).int(), "row_len": 64}
+
+
+def _run(rank, world, port, tp, dp, nvfp4, out_path):
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    torch.set_num_threads(1)
+    from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
+    ctx = setup_worker(_args(tp, dp, nvfp4), run_dir=None, data_iter=iter(()))
+    losses = []
+    for _ in range(3):
+        out = train_step(ctx, _batch(ctx.mesh.dp_rank, dp)); ctx.step += 1
+        losses.append(float(out["loss"]))
+    sd = {k: v.detach().clone() for k, v in ctx.model.state_dict().items()}
+    torch.save({"losses": losses, "gnorm": out["grad_norm"], "sd": sd, "tp_rank": ctx.mesh.tp_rank}, out_path + f".{rank}")
+    teardown_worker(ctx)
+
+
+def _launch(tmp_path, tp, dp, nvfp4=False):
+    world = tp * dp
+    out = str(tmp_path / f"out_tp{tp}_dp{dp}")
+    if world == 1:
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+            os.environ.pop(k, None)
+        _run(0, 1, _free_port(), tp, dp, nvfp4, out)
+    else:
+        mp.spawn(_run, args=(world, _free_port(), tp, dp, nvfp4, out), nprocs=world, join=True)
+    return [torch.load(out + f".{r}", weights_only=False) for r in range(world)]
+
+
+@pytest.mark.parametrize("tp,dp", [(2, 1), (1, 2), (2, 2)])
+def test_parallel_matches_single(tmp_path, tp, dp):
+    ref = _launch(tmp_path, 1, 1)[0]
+    res = _launch(tmp_path, tp, dp)
+    for r in res:
+        for a, b in zip(r["losses"], ref["losses"]):
+            assert abs(a - b) < 2e-4, (r["losses"], ref["losses"])
+        assert abs(r["gnorm"] - ref["gnorm"]) < 5e-3 * max(1.0, ref["gnorm"])
+    # replicated parameters stay identical across TP ranks, sharded ones are slices of the reference
+    sd0 = res[0]["sd"]
+    full = ref["sd"]
+    assert torch.allclose(sd0["norm.weight"], full["norm.weight"], atol=1e-4)
+    assert torch.allclose(sd0["layers.0.attn.fg_first.weight"], full["layers.0.attn.fg_first.weight"], atol=1e-4)
+    if tp > 1:
+        other = res[1]["sd"]
+        assert torch.equal(sd0["norm.weight"], other["norm.weight"]) or \
+            torch.allclose(sd0["norm.weight"], other["norm.weight"], atol=1e-6)
+        w_full = full["layers.0.ffn.down_proj.weight"]
+        n = w_full.shape[1] // tp
+        assert torch.allclose(sd0["layers.0.ffn.down_proj.weight"], w_full[:, :n], atol=2e-4)
+        e_full = full["embed_tokens.weight"]
+        assert torch.allclose(other["embed_tokens.weight"], e_full[e_full.shape[0] // tp:], atol=2e-4)
+
+
+def test_nvfp4_tp2_runs_and_agrees_on_loss(tmp_path):
+    res = _launch(tmp_path, 2, 1, nvfp4=True)
+    assert abs(res[0]["losses"][0] - res[1]["losses"][0]) < 1e-5
+    assert all(l == l for l in res[0]["losses"])

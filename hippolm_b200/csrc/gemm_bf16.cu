@@ -21,6 +21,49 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 + 256;
 
+// Fused collective modes of the same kernel (COMM template parameter):
+//   COMM_AG  all-gather -> GEMM. The first `comm_ctas` CTAs push this rank's row shard of A into every
+//            peer's gathered buffer with plain P2P stores and bump the peer's arrival counter; GEMM CTAs
+//            walk the M tiles in arrival order and their TMA producer waits (bounded) on the counter of
+//            the source shard before the first load of that shard. Every TMA load reads local memory.
+//   COMM_RS  GEMM -> reduce-scatter. The epilogue stores each partial tile into the staging slot of the
+//            rank that owns those rows (P2P stores) and bumps that rank's counter; after its last tile
+//            every CTA joins the reduction of the local rows (wait for all sources, sum the slots).
+constexpr int COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2;
+constexpr int MAX_RANKS = 8;
+
+struct CommParams {
+  int world, rank;
+  int rows_per_shard;                 // AG: rows of A per source rank; RS: rows of C per owner rank
+  int comm_ctas;                      // AG: CTAs that copy instead of computing
+  uint32_t target;                    // counter value that means "complete for this call"
+  long long wait_cycles;              // bound of every spin
+  const void* x_local;                // AG: [rows_per_shard, K] bf16 (this rank's shard)
+  long long x_ld;                     // AG: row pitch of x_local in elements
+  void* buf_peer[MAX_RANKS];          // AG: gathered [world*rows_per_shard, K]; RS: staging [world][rows_per_shard, N]
+  uint32_t* flag_peer[MAX_RANKS];     // counters on every rank, indexed by source rank
+  void* out_local;                    // RS: [rows_per_shard, N] bf16
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded spin on a monotonic counter written by other GPUs
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, long long limit, int detail) {
+  if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+  long long t0 = clock64();
+  while ((int32_t)(ld_acquire_sys(p) - target) < 0) {
+    if (clock64() - t0 > limit) { report(kWaitPeerFlag, detail); return false; }
+    __nanosleep(64);
+  }
+  return true;
+}
+
 struct GemmParams {
   int M, N, K;
   void* C; long long ldc;
@@ -30,9 +73,10 @@ struct GemmParams {
   int tiles_m, tiles_n;
 };
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
+                 const __grid_constant__ CommParams cp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -56,23 +100,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int first_cta = (COMM == COMM_AG) ? cp.comm_ctas : 0;
+  const int n_gemm_ctas = gridDim.x - first_cta;
+  const int bid = (int)blockIdx.x - first_cta;
 
-  // grouped rasterisation: 8 row-blocks share each column-block sweep so A/B tiles stay hot in L2
+  // grouped rasterisation: 8 row-blocks share each column-block sweep so A/B tiles stay hot in L2.
+  // With a fused collective the row-blocks are walked shard by shard: AG in arrival order
+  // (own, rank-1, rank-2, ...), RS remote owners first (rank+1, ...), own rows last.
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int GROUP = 8;
+    int tiles_m = p.tiles_m, base_m = 0;
+    if (COMM != COMM_NONE) {
+      const int tms = cp.rows_per_shard / BM;            // row-blocks per shard
+      const int per_shard = tms * p.tiles_n;
+      const int si = t / per_shard;
+      t -= si * per_shard;
+      const int shard = (COMM == COMM_AG) ? (cp.rank - si + cp.world) % cp.world : (cp.rank + 1 + si) % cp.world;
+      base_m = shard * tms; tiles_m = tms;
+    }
     int per_group = GROUP * p.tiles_n;
     int g = t / per_group, r = t % per_group;
-    int gm = min(GROUP, p.tiles_m - g * GROUP);
-    tm = g * GROUP + r % gm;
+    int gm = min(GROUP, tiles_m - g * GROUP);
+    tm = base_m + g * GROUP + r % gm;
     tn = r / gm;
   };
+
+  if (COMM == COMM_AG && (int)blockIdx.x < cp.comm_ctas) {
+    // ---- copy role: push the local shard to every rank (own first), then bump that rank's counter
+    const long long row_bytes = (long long)p.K * 2;
+    const long long vec_per_row = row_bytes / 16;
+    const long long nvec = (long long)cp.rows_per_shard * vec_per_row;
+    for (int i = 0; i < cp.world; ++i) {
+      const int peer = (cp.rank + i) % cp.world;
+      uint4* dst = (uint4*)((uint8_t*)cp.buf_peer[peer] + (long long)cp.rank * cp.rows_per_shard * row_bytes);
+      for (long long v = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; v < nvec; v += (long long)cp.comm_ctas * GEMM_THREADS) {
+        const long long r = v / vec_per_row, c = v % vec_per_row;
+        dst[v] = *((const uint4*)((const uint8_t*)cp.x_local + r * cp.x_ld * 2) + c);
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) red_release_sys_add(cp.flag_peer[peer] + cp.rank, 1u);
+    }
+  } else
 
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      uint32_t seen = 0;
+      for (int t = bid; t < num_tiles && ok; t += n_gemm_ctas) {
         int tm, tn; tile_coord(t, tm, tn);
+        if (COMM == COMM_AG) {
+          const int shard = (tm * BM) / cp.rows_per_shard;
+          if (!((seen >> shard) & 1u)) {
+            ok = wait_counter(cp.flag_peer[cp.rank] + shard, cp.target, cp.wait_cycles, shard);
+            asm volatile("fence.proxy.async;" ::: "memory");     // remote generic-proxy writes -> TMA reads
+            seen |= 1u << shard;
+            if (!ok) break;
+          }
+        }
         for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
           int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
@@ -99,7 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_f16(BM, BN, 1, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
       int it = 0, tl = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+      for (int t = bid; t < num_tiles && ok; t += n_gemm_ctas, ++tl) {
         int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
         ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl);
         if (!ok) break;
@@ -126,7 +212,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     int tl = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+    for (int t = bid; t < num_tiles && ok; t += n_gemm_ctas, ++tl) {
       int tm, tn; tile_coord(t, tm, tn);
       int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
       ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl);
@@ -161,7 +247,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
-            __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+            __nv_bfloat16* crow;
+            if (COMM == COMM_RS) {
+              // partial tile goes to the staging slot [this rank] of the rank that owns these rows
+              const int owner = row / cp.rows_per_shard, lrow = row - owner * cp.rows_per_shard;
+              crow = (__nv_bfloat16*)cp.buf_peer[owner] + ((long long)cp.rank * cp.rows_per_shard + lrow) * p.N + col0;
+            } else {
+              crow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+            }
             if (col0 + 32 <= p.N) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -169,7 +262,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
                 uint4* dst = (uint4*)(crow + j);
-                if (p.accumulate) {
+                if (COMM != COMM_RS && p.accumulate) {
                   uint4 o = *dst;
                   const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
 #pragma unroll
@@ -184,12 +277,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
                 float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += __bfloat162float(crow[j]);
+                if (COMM != COMM_RS && p.accumulate) v += __bfloat162float(crow[j]);
                 crow[j] = __float2bfloat16(v);
               }
             }
           }
         }
+      }
+      if (COMM == COMM_RS) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(cp.flag_peer[(tm * BM) / cp.rows_per_shard] + cp.rank, 1u);
       }
       tc_fence_before();
       __syncwarp();
@@ -199,11 +297,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (COMM == COMM_RS) {
+    // ---- reduction of the rows this rank owns: wait for every source, then sum the staging slots
+    if ((int)threadIdx.x < cp.world)
+      wait_counter(cp.flag_peer[cp.rank] + threadIdx.x, cp.target, cp.wait_cycles, 100 + threadIdx.x);
+    __syncthreads();
+    const long long nvec = (long long)cp.rows_per_shard * p.N / 8;
+    const uint4* stage = (const uint4*)cp.buf_peer[cp.rank];
+    uint4* out = (uint4*)cp.out_local;
+    for (long long v = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; v < nvec; v += (long long)gridDim.x * GEMM_THREADS) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int sidx = 0; sidx < cp.world; ++sidx) {
+        uint4 x = __ldcg(stage + (long long)sidx * nvec + v);      // written by another GPU: bypass L1
+        const __nv_bfloat162* xb = (const __nv_bfloat162*)&x;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(xb[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+      }
+      uint4 o;
+      __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      out[v] = o;
+    }
+  }
 }
 
-template <bool AK, bool BK_>
+template <bool AK, bool BK_, int COMM>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                       long long ldc, int out_fp32, int accumulate, float alpha, int max_ctas, cudaStream_t stream) {
+                       long long ldc, int out_fp32, int accumulate, float alpha, int max_ctas, const CommParams& cp,
+                       cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc;
   // K-major: global [rows, K], box {64, rows_tile}.  MN-major: global [K, cols], box {64 cols, 64 k-rows}.
@@ -219,15 +341,18 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int tiles = p.tiles_m * p.tiles_n;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  int grid = tiles < sms ? tiles : sms;
-  auto kern = gemm_bf16_kernel<AK, BK_>;
+  int grid;
+  if (COMM == COMM_AG) grid = sms;                                    // copy CTAs + GEMM CTAs, all co-resident
+  else if (COMM == COMM_RS) grid = tiles < sms ? tiles : sms;
+  else grid = tiles < sms ? tiles : sms;
+  auto kern = gemm_bf16_kernel<AK, BK_, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, p, cp);
   return (int)cudaGetLastError();
 }
 
@@ -242,12 +367,57 @@ extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
   if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
   cudaStream_t s = (cudaStream_t)stream;
+  CommParams cp = {};
   switch (layout) {
-    case 0: return launch_gemm<true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
-    case 1: return launch_gemm<true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
-    case 2: return launch_gemm<false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
-    case 3: return launch_gemm<false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, s);
+    case 0: return launch_gemm<true, true, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
+    case 1: return launch_gemm<true, false, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
+    case 2: return launch_gemm<false, false, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
+    case 3: return launch_gemm<false, true, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
   }
+  return -1;
+}
+
+// All-gather -> GEMM.  x_local: [rows_per_shard, K] bf16 (pitch x_ld). xg_ptrs[r]: rank r's gathered buffer
+// [world*rows_per_shard, K] (peer-mapped symmetric memory, own entry = local). flag_ptrs[r]: rank r's counters
+// [world]. Computes C[world*rows_per_shard, N] = gathered(x) * op(B); layout 0: B stored [N, K]; 1: B stored [K, N].
+// `target` = number of calls made on these counters (this one included) * comm_ctas.
+extern "C" int hippo_allgather_gemm_bf16(const void* x_local, long long x_ld, void* const* xg_ptrs,
+                                         void* const* flag_ptrs, int world, int rank, int rows_per_shard,
+                                         const void* B, long long ldb, void* C, long long ldc, int N, int K, int layout,
+                                         int comm_ctas, unsigned target, long long wait_cycles, void* stream) {
+  using namespace hippo;
+  if (world < 1 || world > MAX_RANKS || rows_per_shard % BM || (K % 8) || (N % 8)) return -2;
+  CommParams cp = {};
+  cp.world = world; cp.rank = rank; cp.rows_per_shard = rows_per_shard; cp.comm_ctas = comm_ctas;
+  cp.target = target; cp.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
+  cp.x_local = x_local; cp.x_ld = x_ld;
+  for (int r = 0; r < world; ++r) { cp.buf_peer[r] = xg_ptrs[r]; cp.flag_peer[r] = (uint32_t*)flag_ptrs[r]; }
+  const int M = world * rows_per_shard;
+  const void* A = xg_ptrs[rank];
+  cudaStream_t s = (cudaStream_t)stream;
+  if (layout == 0) return launch_gemm<true, true, COMM_AG>(A, B, C, M, N, K, K, ldb, ldc, 0, 0, 1.f, 0, cp, s);
+  if (layout == 1) return launch_gemm<true, false, COMM_AG>(A, B, C, M, N, K, K, ldb, ldc, 0, 0, 1.f, 0, cp, s);
+  return -1;
+}
+
+// GEMM -> reduce-scatter.  A: [world*rows_per_shard, K] local bf16; partial C tiles are stored into the staging
+// slot [rank] of the owning rank (stage_ptrs[r]: [world][rows_per_shard, N] bf16 on rank r), then every rank sums its
+// own slots into out_local [rows_per_shard, N]. `target` = calls so far * (rows_per_shard/128) * ceil(N/256) * 4.
+extern "C" int hippo_gemm_reduce_scatter_bf16(const void* A, long long lda, const void* B, long long ldb,
+                                              void* const* stage_ptrs, void* const* flag_ptrs, int world, int rank,
+                                              int rows_per_shard, void* out_local, int N, int K, int layout,
+                                              unsigned target, long long wait_cycles, void* stream) {
+  using namespace hippo;
+  if (world < 1 || world > MAX_RANKS || rows_per_shard % BM || (K % 8) || (N % 8)) return -2;
+  CommParams cp = {};
+  cp.world = world; cp.rank = rank; cp.rows_per_shard = rows_per_shard; cp.target = target;
+  cp.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
+  for (int r = 0; r < world; ++r) { cp.buf_peer[r] = stage_ptrs[r]; cp.flag_peer[r] = (uint32_t*)flag_ptrs[r]; }
+  cp.out_local = out_local;
+  const int M = world * rows_per_shard;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (layout == 0) return launch_gemm<true, true, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
+  if (layout == 1) return launch_gemm<true, false, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
   return -1;
 }
 

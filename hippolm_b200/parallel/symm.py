@@ -1,0 +1,120 @@
+"""Symmetric (peer-mapped) memory workspace for the fused compute + collective kernels.
+
+The buffers are allocated with ``torch.distributed._symmetric_memory`` (cuMemCreate + handle exchange
+over the TP group); the kernels in ``csrc/gemm_bf16.cu`` only see raw peer pointers:
+
+  gathered[parity]   [T, Kmax] bf16 on every rank   target of the all-gather pushes (AG -> GEMM)
+  staging[parity]    [world][T/world, Nmax] bf16     per-source partial tiles (GEMM -> RS)
+  counters           uint32 [4][world]               monotonic arrival counters, one row per (op, parity)
+
+A rank can run at most one fused op ahead of its slowest peer (each op needs data from every peer), so
+two parities per op type are enough to keep a fast rank's pushes out of a buffer a slow rank still reads.
+Every wait inside the kernels is bounded; ``check_status`` raises if one ran out.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+from ..ops._ext import lib, ptr, stream_ptr, check
+
+_BM, _BN = 128, 256
+
+
+def _ptr_arr(ptrs) -> C.Array:
+    return (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+class FusedWorkspace:
+    def __init__(self, mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, comm_ctas: int = 16,
+                 wait_cycles: int = 0):
+        import torch.distributed._symmetric_memory as symm_mem
+        assert dtype == torch.bfloat16
+        self.mesh, self.world, self.rank = mesh, mesh.tp, mesh.tp_rank
+        self.max_tokens, self.max_width = max_tokens, max_width
+        self.comm_ctas, self.wait_cycles = comm_ctas, wait_cycles
+        dev = mesh.device
+        group = mesh.tp_group if mesh.tp_group is not None else dist.group.WORLD
+        nbytes = max_tokens * max_width * 2
+        self._bufs, self._hdls = [], []
+
+        def alloc(n):
+            t = symm_mem.empty(n, dtype=torch.uint8, device=dev)
+            h = symm_mem.rendezvous(t, group)
+            self._bufs.append(t); self._hdls.append(h)
+            return t, [int(p) for p in h.buffer_ptrs]
+
+        self.gathered = [alloc(nbytes) for _ in range(2)]
+        self.staging = [alloc(nbytes) for _ in range(2)]
+        self.flags_t, self.flag_ptrs = alloc(4 * 64 * 4)
+        self.flags_t.zero_()
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        self.calls = [0, 0, 0, 0]          # per counter row: AG parity 0/1, RS parity 0/1
+        self.ag_n = 0
+        self.rs_n = 0
+
+    def _row_ptrs(self, row: int) -> List[int]:
+        return [p + row * 64 * 4 for p in self.flag_ptrs]
+
+    # ------------------------------------------------------------------ all-gather -> GEMM
+    def allgather_gemm(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """x: [T/w, K] -> (gathered x [T, K] (a view of the workspace, valid until the next-but-one call),
+        y [T, N]) with y = gather(x) @ W^T (W: [N, K]) or gather(x) @ W (W: [K, N], transpose_w)."""
+        rows, K = x.shape
+        N = weight.shape[1] if transpose_w else weight.shape[0]
+        T = rows * self.world
+        assert rows % _BM == 0 and T * K <= self.max_tokens * self.max_width, "workspace too small / ragged shard"
+        x = x.contiguous()
+        weight = weight.contiguous()
+        par = self.ag_n & 1
+        self.ag_n += 1
+        row = par
+        self.calls[row] += 1
+        buf, ptrs = self.gathered[par]
+        y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        check(lib().hippo_allgather_gemm_bf16(ptr(x), C.c_longlong(x.stride(0)), _ptr_arr(ptrs), _ptr_arr(self._row_ptrs(row)),
+                                              self.world, self.rank, rows, ptr(weight), C.c_longlong(weight.stride(0)),
+                                              ptr(y), C.c_longlong(N), N, K, 1 if transpose_w else 0, self.comm_ctas,
+                                              C.c_uint(self.calls[row] * self.comm_ctas),
+                                              C.c_longlong(self.wait_cycles), stream_ptr()), "allgather_gemm")
+        xg = buf[:T * K * 2].view(torch.bfloat16).view(T, K)
+        return xg, y
+
+    # ------------------------------------------------------------------ GEMM -> reduce-scatter
+    def gemm_reduce_scatter(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False) -> torch.Tensor:
+        """x: [T, K_local] -> reduce_scatter(x @ W^T) [T/w, N] (W: [N, K_local]; transpose_w: W is [K_local, N])."""
+        T, K = x.shape
+        N = weight.shape[1] if transpose_w else weight.shape[0]
+        rows = T // self.world
+        assert rows % _BM == 0 and T * N <= self.max_tokens * self.max_width
+        x = x.contiguous(); weight = weight.contiguous()
+        par = self.rs_n & 1
+        self.rs_n += 1
+        row = 2 + par
+        self.calls[row] += 1
+        _, ptrs = self.staging[par]
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=x.device)
+        tiles = (rows // _BM) * ((N + _BN - 1) // _BN)
+        check(lib().hippo_gemm_reduce_scatter_bf16(ptr(x), C.c_longlong(x.stride(0)), ptr(weight),
+                                                   C.c_longlong(weight.stride(0)), _ptr_arr(ptrs),
+                                                   _ptr_arr(self._row_ptrs(row)), self.world, self.rank, rows, ptr(out),
+                                                   N, K, 1 if transpose_w else 0, C.c_uint(self.calls[row] * tiles * 4),
+                                                   C.c_longlong(self.wait_cycles), stream_ptr()), "gemm_reduce_scatter")
+        return out
+
+    def check_status(self) -> None:
+        st = _ext.device_status()
+        if st[0] != 0:
+            raise RuntimeError(f"a bounded device wait ran out: code={st[0]} detail={st[1]} block={st[2]} count={st[3]}")
+
+
+def create_workspace(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16) -> Optional[FusedWorkspace]:
+    if mesh.tp <= 1 or mesh.device.type != "cuda":
+        return None
+    return FusedWorkspace(mesh, max_tokens, max_width, dtype)

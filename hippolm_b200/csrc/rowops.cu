@@ -484,3 +484,43 @@ extern "C" int hippo_silu_fwd(const void* x, void* y, long long n, void* s) {
   silu_fwd_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, ST(s)>>>((const bf16*)x, (bf16*)y, n);
   RET();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate device memory (declared in no_alloc.h).
+// The per-block partial sums of dw, which hippo_rmsnorm_bwd takes as a caller-allocated buffer, live
+// here in a fixed array inside the library image. Each GPU that loads the library carries its own copy
+// of the array until the process exits.
+namespace hippo {
+constexpr int kNoAllocBlocks = 148;                    // one block per SM of a B200
+constexpr int kNoAllocMaxD = 8192;                     // widest row the entry point accepts
+static __device__ __align__(256) float g_noalloc_dw_part[kNoAllocBlocks * kNoAllocMaxD];   // 4.6 MiB
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};   // device address of the array, per device
+}  // namespace hippo
+
+extern "C" int hippo_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                         float* dw, long long T, int D, void* s) {
+  using namespace hippo;
+  if (T <= 0 || D <= 0 || D % 8 != 0 || D > kNoAllocMaxD) return -22;      // wider than the built-in scratch
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return -23;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // First call on this device: ask the runtime where this device's copy of the array lives. In host code
+    // the array's name is only a handle; a kernel must be given the address obtained here.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_dw_part);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part = g_noalloc_ptr[dev];
+  const int nblocks = (int)(T < kNoAllocBlocks ? T : kNoAllocBlocks);
+  const int maxv = (D + 2047) / 2048;
+  // every block writes all D entries of its own row of `part`, so nothing has to be cleared between calls
+  if (maxv <= 1) rmsnorm_bwd_kernel<1><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
+  else if (maxv == 2) rmsnorm_bwd_kernel<2><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
+  else rmsnorm_bwd_kernel<4><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
+  colsum_kernel<<<(D + 255) / 256, 256, 0, ST(s)>>>(part, dw, nblocks, D);
+  RET();
+}

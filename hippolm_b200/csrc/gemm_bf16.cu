@@ -70,6 +70,8 @@ struct GemmParams {
   int out_fp32;        // 0 = bf16, 1 = fp32
   int accumulate;      // C += result
   float alpha;
+  const void* Cin;     // optional bf16 [M, ldcin] addend: C = alpha*A*B + beta*Cin (bf16 output only)
+  long long ldcin; float beta;
   int tiles_m, tiles_n;
 };
 
@@ -268,6 +270,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                   for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += of.x; f[2 * e + 1] += of.y; }
                 }
+                if (COMM == COMM_NONE && p.Cin) {
+                  uint4 o = *(const uint4*)((const __nv_bfloat16*)p.Cin + (long long)row * p.ldcin + col0 + j);
+                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += p.beta * of.x; f[2 * e + 1] += p.beta * of.y; }
+                }
                 uint4 v;
                 __nv_bfloat162* vb = (__nv_bfloat162*)&v;
 #pragma unroll
@@ -278,6 +286,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
                 float v = __uint_as_float(r[j]) * p.alpha;
                 if (COMM != COMM_RS && p.accumulate) v += __bfloat162float(crow[j]);
+                if (COMM == COMM_NONE && p.Cin) v += p.beta * __bfloat162float(((const __nv_bfloat16*)p.Cin)[(long long)row * p.ldcin + col0 + j]);
                 crow[j] = __float2bfloat16(v);
               }
             }
@@ -322,6 +331,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// addend of the next plain launch (set by hippo_gemm_bf16_ex, cleared after use)
+static thread_local const void* g_cin = nullptr;
+static thread_local long long g_ldcin = 0;
+static thread_local float g_beta = 0.f;
+
 template <bool AK, bool BK_, int COMM>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int out_fp32, int accumulate, float alpha, int max_ctas, const CommParams& cp,
@@ -337,6 +351,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta;
   p.tiles_m = (M + BM - 1) / BM; p.tiles_n = (N + BN - 1) / BN;
   int tiles = p.tiles_m * p.tiles_n;
   int sms = sm_count();
@@ -419,6 +434,17 @@ extern "C" int hippo_gemm_reduce_scatter_bf16(const void* A, long long lda, cons
   if (layout == 0) return launch_gemm<true, true, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
   if (layout == 1) return launch_gemm<true, false, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
   return -1;
+}
+
+// C = alpha * op(A) op(B) + beta * Cin   (bf16 output; Cin may not alias C unless beta-only semantics are acceptable
+// per element, which they are: each output element is read once and written once by the same thread)
+extern "C" int hippo_gemm_bf16_ex(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K,
+                                  long long lda, long long ldb, long long ldc, long long ldcin, int layout, float alpha,
+                                  float beta, void* stream) {
+  hippo::g_cin = Cin; hippo::g_ldcin = ldcin; hippo::g_beta = beta;
+  int rc = hippo_gemm_bf16(A, B, C, M, N, K, lda, ldb, ldc, layout, 0, 0, alpha, 0, stream);
+  hippo::g_cin = nullptr; hippo::g_beta = 0.f;
+  return rc;
 }
 
 extern "C" int hippo_get_status(int* out4) {

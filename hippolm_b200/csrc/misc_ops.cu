@@ -384,3 +384,140 @@ extern "C" int hippo_ce_grad(const float* z, const float* lse, const long long* 
   ce_grad_kernel<<<(unsigned)C, 512, 0, ST(s)>>>(z, lse, target, roww, (bf16*)dz, V);
   RET();
 }
+
+// ------------------------------------------------------------------------------------ Muon elementwise
+namespace hippo {
+// m <- beta*m + g*gscale ; u <- g*gscale + beta*m (nesterov) or m ; ssq += sum u^2.  8 elements per thread.
+__global__ void muon_momentum_kernel(const void* g, int g_bf16, void* m, int m_bf16, bf16* __restrict__ u, long long n,
+                                     float beta, float gscale, int nesterov, float* ssq) {
+  __shared__ float sh[32];
+  float acc = 0.f;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+    float gv[8], mv[8], uv[8];
+    if (g_bf16) ld8((const bf16*)g + i, gv); else { float4 a = *(const float4*)((const float*)g + i), b = *(const float4*)((const float*)g + i + 4); gv[0]=a.x;gv[1]=a.y;gv[2]=a.z;gv[3]=a.w;gv[4]=b.x;gv[5]=b.y;gv[6]=b.z;gv[7]=b.w; }
+    if (m_bf16) ld8((const bf16*)m + i, mv); else { float4 a = *(const float4*)((const float*)m + i), b = *(const float4*)((const float*)m + i + 4); mv[0]=a.x;mv[1]=a.y;mv[2]=a.z;mv[3]=a.w;mv[4]=b.x;mv[5]=b.y;mv[6]=b.z;mv[7]=b.w; }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float gg = gv[e] * gscale;
+      mv[e] = beta * mv[e] + gg;
+      uv[e] = nesterov ? gg + beta * mv[e] : mv[e];
+      acc += uv[e] * uv[e];
+    }
+    if (m_bf16) st8((bf16*)m + i, mv); else { *(float4*)((float*)m + i) = make_float4(mv[0],mv[1],mv[2],mv[3]); *(float4*)((float*)m + i + 4) = make_float4(mv[4],mv[5],mv[6],mv[7]); }
+    st8(u + i, uv);
+  }
+  acc = wsum(acc);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    r = wsum(r);
+    if (threadIdx.x == 0) atomicAdd(ssq, r);
+  }
+}
+// sum of squares of rows [r0, r1) of a row-major bf16 matrix (segment norms)
+// x <- x / (sqrt(ssq) + eps)
+__global__ void scale_inv_norm_kernel(bf16* __restrict__ x, long long n, const float* ssq, float eps) {
+  const float s = 1.f / (sqrtf(*ssq) + eps);
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+    float v[8]; ld8(x + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= s;
+    st8(x + i, v);
+  }
+}
+// w <- w*wd - lr*o   (w bf16 or fp32, o bf16)
+__global__ void axpby_update_kernel(void* w, int w_bf16, const bf16* __restrict__ o, long long n, float wd, float lr) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+    float ov[8], wv[8]; ld8(o + i, ov);
+    if (w_bf16) ld8((const bf16*)w + i, wv); else { float4 a = *(const float4*)((const float*)w + i), b = *(const float4*)((const float*)w + i + 4); wv[0]=a.x;wv[1]=a.y;wv[2]=a.z;wv[3]=a.w;wv[4]=b.x;wv[5]=b.y;wv[6]=b.z;wv[7]=b.w; }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wv[e] = wv[e] * wd - lr * ov[e];
+    if (w_bf16) st8((bf16*)w + i, wv); else { *(float4*)((float*)w + i) = make_float4(wv[0],wv[1],wv[2],wv[3]); *(float4*)((float*)w + i + 4) = make_float4(wv[4],wv[5],wv[6],wv[7]); }
+  }
+}
+// NVFP4 weights without a master copy: dequantise a 16-element block, w <- w*wd - lr*o, re-quantise in place
+// (block scale recomputed, tensor-level scale kept)
+__global__ void nvfp4_apply_update_kernel(uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, const float* gs_ptr,
+                                          const bf16* __restrict__ o, long long nblocks, float wd, float lr) {
+  long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const float lut[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float gs = *gs_ptr;
+  float s = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)scales[b], __NV_E4M3))) * gs;
+  uint2 pv = *(const uint2*)(packed + b * 8);
+  const uint8_t* pb = (const uint8_t*)&pv;
+  float f[16], a[8], c[8];
+  ld8(o + b * 16, a); ld8(o + b * 16 + 8, c);
+  float bm = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint8_t lo = pb[i] & 0xF, hi = pb[i] >> 4;
+    f[2 * i] = ((lo & 8) ? -lut[lo & 7] : lut[lo & 7]) * s;
+    f[2 * i + 1] = ((hi & 8) ? -lut[hi & 7] : lut[hi & 7]) * s;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { f[i] = f[i] * wd - lr * (i < 8 ? a[i] : c[i - 8]); bm = fmaxf(bm, fabsf(f[i])); }
+  float sraw = fminf(bm / 6.f / gs, 448.f);
+  __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+  scales[b] = (uint8_t)s8;
+  float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
+  uint2 outv; uint8_t* ob = (uint8_t*)&outv;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float lo = sdec > 0.f ? f[2 * i] / sdec : f[2 * i], hi = sdec > 0.f ? f[2 * i + 1] / sdec : f[2 * i + 1];
+    ob[i] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+  }
+  *(uint2*)(packed + b * 8) = outv;
+}
+// vectorised AdamW for all-bf16 state (8 elements per thread)
+__global__ void adamw_bf16_kernel(bf16* __restrict__ p, const bf16* __restrict__ g, bf16* __restrict__ m, bf16* __restrict__ v,
+                                  long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                                  float gscale) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+    float pv[8], gv[8], mv[8], vv[8];
+    ld8(p + i, pv); ld8(g + i, gv); ld8(m + i, mv); ld8(v + i, vv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float gg = gv[e] * gscale;
+      mv[e] = mv[e] * b1 + (1.f - b1) * gg;
+      vv[e] = vv[e] * b2 + (1.f - b2) * gg * gg;
+      pv[e] = pv[e] * (1.f - lr * wd) - lr * (mv[e] / bc1) / (sqrtf(vv[e] / bc2) + eps);
+    }
+    st8(p + i, pv); st8(m + i, mv); st8(v + i, vv);
+  }
+}
+}  // namespace hippo
+
+static unsigned grid8(long long n) { long long b = (n / 8 + 255) / 256; if (b > 148 * 16) b = 148 * 16; if (b < 1) b = 1; return (unsigned)b; }
+
+extern "C" int hippo_muon_momentum(const void* g, int g_bf16, void* m, int m_bf16, void* u, long long n, float beta,
+                                   float gscale, int nesterov, float* ssq, void* s) {
+  if (n % 8) return -1;
+  cudaMemsetAsync(ssq, 0, 4, ST(s));
+  muon_momentum_kernel<<<grid8(n), 256, 0, ST(s)>>>(g, g_bf16, m, m_bf16, (bf16*)u, n, beta, gscale, nesterov, ssq);
+  RET();
+}
+extern "C" int hippo_scale_inv_norm(void* x, long long n, const float* ssq, float eps, void* s) {
+  if (n % 8) return -1;
+  scale_inv_norm_kernel<<<grid8(n), 256, 0, ST(s)>>>((bf16*)x, n, ssq, eps);
+  RET();
+}
+extern "C" int hippo_axpby_update(void* w, int w_bf16, const void* o, long long n, float wd, float lr, void* s) {
+  if (n % 8) return -1;
+  axpby_update_kernel<<<grid8(n), 256, 0, ST(s)>>>(w, w_bf16, (const bf16*)o, n, wd, lr);
+  RET();
+}
+extern "C" int hippo_nvfp4_apply_update(void* packed, void* scales, const float* gs, const void* o, long long rows,
+                                        long long K, float wd, float lr, void* s) {
+  if (K % 16) return -1;
+  long long nb = rows * K / 16;
+  nvfp4_apply_update_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>((uint8_t*)packed, (uint8_t*)scales, gs, (const bf16*)o, nb, wd, lr);
+  RET();
+}
+extern "C" int hippo_adamw_bf16(void* p, const void* g, void* m, void* v, long long n, float lr, float b1, float b2,
+                                float eps, float wd, float bc1, float bc2, float gscale, void* s) {
+  if (n % 8) return -1;
+  adamw_bf16_kernel<<<grid8(n), 256, 0, ST(s)>>>((bf16*)p, (const bf16*)g, (bf16*)m, (bf16*)v, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  RET();
+}

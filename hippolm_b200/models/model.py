@@ -416,7 +416,7 @@ class _VocabParallelLCE(torch.autograd.Function):
             lt = local_t[s:e]
             pz = ops.lce_chunk_grad(z, lse, lt, vc.float() / nv).to(x.dtype)
             dx[s:e] = ops.gemm_nn(pz, weight)
-            dw += ops.gemm_tn(pz, xc).float()
+            ops.gemm_tn_accumulate(pz, xc, dw)
         dx_shard = reduce_scatter_dim0(dx, m.tp_group, m.tp)
         ctx.save_for_backward(dx_shard, dw.to(weight.dtype))
         return loss_sum / nv

@@ -9,5 +9,5 @@ from .functional import (  # noqa: F401
     gemm_nt, gemm_nn, gemm_tn, linear, rmsnorm, swiglu, gated_rmsnorm, kda, kda_gate, kda_prologue,
     short_conv_silu, rope, causal_attention, attn_res, l2norm, silu,
     nvfp4_quantize, nvfp4_dequantize, nvfp4_linear, newton_schulz5, adamw_update,
-    lce_chunk_stats, lce_chunk_grad, cuda_ext_loaded,
+    lce_chunk_stats, lce_chunk_grad, gemm_tn_accumulate, cuda_ext_loaded,
 )

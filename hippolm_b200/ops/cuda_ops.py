@@ -346,3 +346,13 @@ def lce_chunk_grad(z, lse, targets_local, row_weight):
     check(lib().hippo_ce_grad(ptr(z), ptr(lse.float().contiguous()), ptr(tg), ptr(row_weight.float().contiguous()),
                               ptr(dz), _c.c_longlong(C), V, stream_ptr()), "ce_grad")
     return dz
+
+
+def gemm_tn_accumulate(a, b, out_fp32):
+    """out_fp32[N,K] += a[M,N]^T @ b[M,K] (fp32 accumulator tensor updated by the GEMM epilogue)."""
+    Mc, N = a.shape
+    K = b.shape[1]
+    if N % 8 or K % 8:
+        out_fp32 += (a.float().t() @ b.float())
+        return out_fp32
+    return _gemm(a.to(torch.bfloat16), b.to(torch.bfloat16), 2, N, K, Mc, out=out_fp32, accumulate=True)

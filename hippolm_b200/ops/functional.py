@@ -229,3 +229,11 @@ def lce_chunk_grad(z, lse, targets_local, row_weight):
     rows = (targets_local >= 0).nonzero(as_tuple=True)[0]
     p[rows, targets_local[rows]] -= 1.0
     return p * row_weight.unsqueeze(-1)
+
+
+def gemm_tn_accumulate(a, b, out_fp32):
+    """out_fp32 += a^T @ b."""
+    if a.is_cuda:
+        return _cu().gemm_tn_accumulate(a, b, out_fp32)
+    out_fp32 += a.float().t() @ b.float()
+    return out_fp32

@@ -1,0 +1,69 @@
+"""Device-side Muon: fused momentum/nesterov/norm kernel, Newton-Schulz on the tcgen05 GEMM with the
+polynomial folded into the GEMM epilogues (``C = alpha*A*B + beta*Cin``), fused parameter update
+(bf16 weights, or NVFP4 dequantise -> update -> re-quantise in one pass)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._ext import lib, ptr, stream_ptr, check
+
+_A, _B, _C = 3.4445, -4.7750, 2.0315
+
+
+def _gemm_ex(a, b, out, cin, M, N, K, layout, alpha, beta):
+    check(lib().hippo_gemm_bf16_ex(ptr(a), ptr(b), ptr(out), ptr(cin), M, N, K, C.c_longlong(a.stride(0)),
+                                   C.c_longlong(b.stride(0)), C.c_longlong(out.stride(0)),
+                                   C.c_longlong(cin.stride(0) if cin is not None else 0), layout, C.c_float(alpha),
+                                   C.c_float(beta), stream_ptr()), "gemm_bf16_ex")
+
+
+def supported(rows: int, cols: int) -> bool:
+    return rows % 8 == 0 and cols % 8 == 0 and (rows * cols) % 8 == 0
+
+
+def momentum_update(g: torch.Tensor, m: torch.Tensor, beta: float, gscale: float, nesterov: bool):
+    """m <- beta m + g*gscale (in place); returns (u bf16, sum(u^2) device scalar)."""
+    assert g.is_contiguous() and m.is_contiguous()
+    u = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
+    ssq = torch.empty(1, dtype=torch.float32, device=g.device)
+    check(lib().hippo_muon_momentum(ptr(g), int(g.dtype == torch.bfloat16), ptr(m), int(m.dtype == torch.bfloat16), ptr(u),
+                                    C.c_longlong(g.numel()), C.c_float(beta), C.c_float(gscale), int(nesterov), ptr(ssq),
+                                    stream_ptr()), "muon_momentum")
+    return u, ssq
+
+
+def newton_schulz_(u: torch.Tensor, ssq: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    """Orthogonalise u (bf16 [rows, cols], overwritten) given sum(u^2); returns the result (bf16)."""
+    rows, cols = u.shape
+    check(lib().hippo_scale_inv_norm(ptr(u), C.c_longlong(u.numel()), ptr(ssq), C.c_float(eps), stream_ptr()),
+          "scale_inv_norm")
+    n = min(rows, cols)
+    S = torch.empty((n, n), dtype=torch.bfloat16, device=u.device)
+    Mm = torch.empty((n, n), dtype=torch.bfloat16, device=u.device)
+    X, Xn = u, torch.empty_like(u)
+    for _ in range(steps):
+        if rows <= cols:
+            _gemm_ex(X, X, S, None, n, n, cols, 0, 1.0, 0.0)                 # S = X X^T
+            _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)                        # M = c S S + b S
+            _gemm_ex(Mm, X, Xn, X, rows, cols, n, 1, 1.0, _A)                # X' = M X + a X
+        else:
+            _gemm_ex(X, X, S, None, n, n, rows, 2, 1.0, 0.0)                 # S = X^T X
+            _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)
+            _gemm_ex(X, Mm, Xn, X, rows, cols, n, 1, 1.0, _A)                # X' = X M + a X
+        X, Xn = Xn, X
+    return X
+
+
+def apply_update(w: torch.Tensor, o: torch.Tensor, wd_factor: float, lr: float) -> None:
+    """w <- w*wd_factor - lr*o in place (w bf16/fp32 contiguous rows, o bf16)."""
+    check(lib().hippo_axpby_update(ptr(w), int(w.dtype == torch.bfloat16), ptr(o), C.c_longlong(w.numel()),
+                                   C.c_float(wd_factor), C.c_float(lr), stream_ptr()), "axpby_update")
+
+
+def nvfp4_apply_update(packed, scales, gs, o, wd_factor: float, lr: float) -> None:
+    rows, K2 = packed.shape
+    check(lib().hippo_nvfp4_apply_update(ptr(packed), ptr(scales.view(torch.uint8)), ptr(gs), ptr(o), C.c_longlong(rows),
+                                         C.c_longlong(K2 * 2), C.c_float(wd_factor), C.c_float(lr), stream_ptr()),
+          "nvfp4_apply_update")

@@ -19,6 +19,12 @@ def _isbf(t):
 def adamw_update(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
     assert p.is_contiguous() and m.is_contiguous() and v.is_contiguous()
     g = g.contiguous()
+    if all(t.dtype == torch.bfloat16 for t in (p, g, m, v)) and p.numel() % 8 == 0:
+        check(lib().hippo_adamw_bf16(ptr(p), ptr(g), ptr(m), ptr(v), _c.c_longlong(p.numel()), _c.c_float(lr),
+                                     _c.c_float(beta1), _c.c_float(beta2), _c.c_float(eps), _c.c_float(wd),
+                                     _c.c_float(1 - beta1 ** step), _c.c_float(1 - beta2 ** step),
+                                     _c.c_float(grad_scale), stream_ptr()), "adamw_bf16")
+        return
     check(lib().hippo_adamw(ptr(p), ptr(g), ptr(m), ptr(v), _c.c_longlong(p.numel()), _isbf(p), _isbf(g), _isbf(m),
                             _isbf(v), _c.c_float(lr), _c.c_float(beta1), _c.c_float(beta2), _c.c_float(eps),
                             _c.c_float(wd), _c.c_float(1 - beta1 ** step), _c.c_float(1 - beta2 ** step),

@@ -128,6 +128,31 @@ class Muon:
                 if lo < hi:
                     e.module.decay_and_apply_chunk(lo, hi, upd[lo - a:hi - a], self.lr, wd_factor)
 
+    def _step_cuda(self, e: _Entry, g: torch.Tensor, grad_scale: float, wd_factor: float, full_scope: bool) -> bool:
+        """Fully fused device path for one entry; returns False when a segment needs the generic path."""
+        from ..ops import muon_cuda as mc
+        segs = self._segments(e)
+        cols = e.shape[1]
+        if g.dtype not in (torch.bfloat16, torch.float32) or not g.is_contiguous():
+            return False
+        for (a, b) in segs:
+            if b > a and not mc.supported(b - a, cols):
+                return False
+            if full_scope and b > a and self._shard_dim(e, (a, b)) is not None:
+                return False
+        for (a, b) in segs:
+            if b <= a:
+                continue
+            u, ssq = mc.momentum_update(g[a:b], e.exp_avg[a:b], self.momentum, grad_scale, self.nesterov)
+            o = mc.newton_schulz_(u, ssq, self.ns_steps)
+            if e.param is not None:
+                mc.apply_update(e.param.data[a:b], o, wd_factor, self.lr)
+            else:
+                mod = e.module
+                mc.nvfp4_apply_update(mod.packed_weight[a:b], mod.scales[a:b], mod.global_scale, o, wd_factor, self.lr)
+        e.step += 1
+        return True
+
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0):
         mesh = get_mesh()
@@ -139,6 +164,8 @@ class Muon:
             if g is None:
                 continue
             dev = e.device
+            if dev.type == "cuda" and not self.offload and self._step_cuda(e, g, grad_scale, wd_factor, full_scope):
+                continue
             gf = g.to(torch.float32)
             if grad_scale != 1.0:
                 gf = gf * grad_scale

@@ -82,3 +82,38 @@ def test_lce_kernels():
     ref[rows, tg[rows]] -= 1
     ref = ref * roww.unsqueeze(-1)
     assert (dz.float() - ref).abs().max() < 1e-3
+
+
+def test_muon_fused_device_path_matches_reference():
+    import torch.nn as nn
+    from hippolm_b200.optim.optimizers import Muon
+    from hippolm_b200.ref.ops import newton_schulz5
+    torch.manual_seed(0)
+    for shape in ((256, 512), (768, 256)):
+        p = nn.Parameter(torch.randn(*shape, device="cuda").bfloat16())
+        g = (0.1 * torch.randn(*shape, device="cuda")).bfloat16()
+        p.grad = g.clone()
+        opt = Muon(lr=0.1, momentum=0.9, weight_decay=0.01, momentum_dtype=torch.bfloat16)
+        opt.add_param(p, "w")
+        w0 = p.detach().float().clone()
+        opt.step(grad_scale=0.5)
+        m = 0.5 * g.float()
+        u = 0.5 * g.float() + 0.9 * m
+        ref = w0 * (1 - 0.1 * 0.01) - 0.1 * newton_schulz5(u, 5)
+        assert _rel(opt.entries[0].exp_avg, m) < 1e-2
+        assert (p.detach().float() - ref).abs().max() < 0.03          # bf16 weights of magnitude ~4
+
+
+def test_nvfp4_fused_apply_update():
+    from hippolm_b200 import ops
+    from hippolm_b200.ops import muon_cuda as mc
+    torch.manual_seed(0)
+    w = torch.randn(128, 256, device="cuda") * 0.05
+    p, s, gs = ops.nvfp4_quantize(w)
+    o = torch.randn(128, 256, device="cuda").bfloat16()
+    w0 = ops.nvfp4_dequantize(p, s, gs)
+    mc.nvfp4_apply_update(p, s, gs, o, 0.99, 0.01)
+    w1 = ops.nvfp4_dequantize(p, s, gs)
+    target = w0 * 0.99 - 0.01 * o.float()
+    p2, s2, _ = ops.nvfp4_quantize(target, gs)
+    assert torch.equal(ops.nvfp4_dequantize(p2, s2, gs), w1)

@@ -145,6 +145,7 @@ def main():
     args.micro_batch_size = a.micro_batch_tokens
     args.max_steps = 10 ** 9
     args.lr_decay_steps = 0
+    args.lr_warmup_steps = 200          # WSD warm-up keeps the first steps stable on random-init weights
     args.precision = None
     args.fused_comm = not a.no_fused_comm
     args.seed = 0
@@ -212,7 +213,7 @@ def main():
                "config": {"model": name, "global_batch": args.batch_size, "seq_len": args.seq_len,
                           "parallelism": f"tp{world}+sp", "micro_batch_tokens": a.micro_batch_tokens,
                           "optimizer": "muon+adamw", "l2": "inputs larger than L2 (no explicit flush)",
-                          "fused_comm": bool(args.fused_comm and world > 1)},
+                          "fused_comm": bool(ctx.extras.get("fused_comm", False))},
                "clocks": clocks,
                "e2e": {"value": gb_tokens / (e2e_ms_step / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},

@@ -18,6 +18,13 @@ def enabled() -> bool:
     return _STATE["ws"] is not None
 
 
+def fits(rows_per_shard: int, tokens: int, width: int) -> bool:
+    """Shapes the fused kernels accept: 128-row shards, 8-element columns, inside the workspace."""
+    ws = _STATE["ws"]
+    return (ws is not None and rows_per_shard % 128 == 0 and width % 8 == 0
+            and tokens * width <= ws.max_tokens * ws.max_width)
+
+
 def setup(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16) -> bool:
     from . import symm
     ws = symm.create_workspace(mesh, max_tokens, max_width, dtype)

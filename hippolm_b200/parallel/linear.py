@@ -29,7 +29,8 @@ class _ColumnLinearSP(torch.autograd.Function):
     def forward(ctx, x, weight, bias):
         m = get_mesh()
         f = _fused()
-        if f is not None and x.is_cuda and m.tp > 1:
+        if f is not None and x.is_cuda and m.tp > 1 and f.fits(x.shape[0], x.shape[0] * m.tp, x.shape[1]) \
+                and weight.shape[0] % 8 == 0 and x.dtype == torch.bfloat16:
             xg, y = f.allgather_gemm(x, weight)
         else:
             xg = all_gather_dim0(x, m.tp_group, m.tp)
@@ -48,7 +49,8 @@ class _ColumnLinearSP(torch.autograd.Function):
         f = _fused()
         dxg = None
         if ctx.needs_input_grad[0]:
-            if f is not None and dy.is_cuda and m.tp > 1:
+            if f is not None and dy.is_cuda and m.tp > 1 and dy.dtype == torch.bfloat16 \
+                    and f.fits(dy.shape[0] // m.tp, dy.shape[0], weight.shape[1]) and dy.shape[1] % 8 == 0:
                 dx = f.gemm_reduce_scatter(dy, weight, transpose_w=True)
             else:
                 dxg = ops.gemm_nn(dy, weight)                      # [T, K]
@@ -66,7 +68,8 @@ class _RowLinearSP(torch.autograd.Function):
     def forward(ctx, x, weight):
         m = get_mesh()
         f = _fused()
-        if f is not None and x.is_cuda and m.tp > 1:
+        if f is not None and x.is_cuda and m.tp > 1 and x.dtype == torch.bfloat16 \
+                and f.fits(x.shape[0] // m.tp, x.shape[0], weight.shape[0]) and x.shape[1] % 8 == 0:
             y = f.gemm_reduce_scatter(x, weight, transpose_w=False)
         else:
             y = reduce_scatter_dim0(ops.gemm_nt(x, weight), m.tp_group, m.tp)
@@ -79,7 +82,8 @@ class _RowLinearSP(torch.autograd.Function):
         m = get_mesh()
         f = _fused()
         dy = dy.contiguous()
-        if f is not None and dy.is_cuda and m.tp > 1:
+        if f is not None and dy.is_cuda and m.tp > 1 and dy.dtype == torch.bfloat16 \
+                and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and weight.shape[1] % 8 == 0:
             dyg, dx = f.allgather_gemm(dy, weight, transpose_w=True)
         else:
             dyg = all_gather_dim0(dy, m.tp_group, m.tp)            # [T, N]

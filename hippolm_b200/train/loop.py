@@ -97,10 +97,20 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         dist.barrier()
         from ..parallel.collectives import broadcast_replicated_params
         broadcast_replicated_params(model.replicated_parameters(), mesh)
+    fused_on = False
+    if mesh.tp > 1 and device.type == "cuda" and bool(getattr(args, "fused_comm", True)):
+        # symmetric workspace for the fused all-gather->GEMM / GEMM->reduce-scatter kernels: the largest
+        # gathered / staged tensor is [micro-batch tokens, hidden]
+        from ..parallel import fused
+        mbt = int(getattr(args, "micro_batch_size", 0) or 0)
+        full = int(getattr(args, "batch_size", 1)) // max(1, dp) * int(getattr(args, "seq_len", 512))
+        tokens = min(mbt, full) if mbt > 0 else full
+        fused_on = (tokens // mesh.tp) % 128 == 0 and fused.setup(mesh, tokens, cfg.hidden_size)
     offload = bool(getattr(args, "offload_optimizer", False))
     muon, adamw = build_param_groups(model, args, precision, offload=offload)
     ctx = TrainContext(args=args, cfg=cfg, mesh=mesh, device=device, model=model, muon=muon, adamw=adamw,
                        precision=precision, logger=logger, data_iter=data_iter, run_dir=run_dir)
+    ctx.extras["fused_comm"] = fused_on
     if mesh.dp > 1:
         from ..parallel.dp import DPGradReducer
         ctx.grad_reducer = DPGradReducer(model, mesh, overlap=bool(getattr(args, "dp_overlap", True)))
@@ -111,7 +121,7 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         n = model.num_parameters()
         logger.info(f"model: {n/1e6:.1f}M local parameters, tp={mesh.tp} dp={mesh.dp}, layers={cfg.layer_types()}")
         logger.info(f"optimizer: muon entries={len(muon.entries)} adamw entries={len(adamw.entries)} "
-                    f"offload={offload}")
+                    f"offload={offload} fused_comm={fused_on}")
         if run_dir:
             ctx.metrics_file = open(os.path.join(run_dir, "metrics.jsonl"), "a")
     if data_iter is None:
@@ -320,6 +330,11 @@ def teardown_worker(ctx: Optional[TrainContext]) -> None:
     if ctx is None or getattr(ctx, "closed", False):
         return
     ctx.closed = True
+    try:
+        from ..parallel import fused as _fused
+        _fused.teardown()
+    except Exception:
+        pass
     for name in ("prefetcher", "watchdog", "offloader"):
         obj = getattr(ctx, name, None)
         if obj is not None:

@@ -1,0 +1,41 @@
+"""Tokenizer loading (``src/training/tokenizer.py:12-28``): a HuggingFace tokenizer directory, with
+``pad = eos`` when the tokenizer has no pad token. A byte-level fallback keeps the text pipeline usable
+(tests, offline boxes) when no tokenizer files are given."""
+from __future__ import annotations
+
+from typing import List, Optional
+
+
+class ByteTokenizer:
+    """UTF-8 bytes + 2 specials (256 = eos/pad, 257 = bos). vocab_size 258."""
+    vocab_size = 258
+    eos_token_id = 256
+    pad_token_id = 256
+    bos_token_id = 257
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
+        return list(text.encode("utf-8"))
+
+    def __call__(self, texts, add_special_tokens: bool = False, **kw):
+        if isinstance(texts, str):
+            return {"input_ids": self.encode(texts)}
+        return {"input_ids": [self.encode(t) for t in texts]}
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        return bytes(i for i in ids if 0 <= int(i) < 256).decode("utf-8", errors="replace")
+
+    def apply_chat_template(self, messages, tokenize: bool = False, add_generation_prompt: bool = True):
+        text = "".join(f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>\n" for m in messages)
+        if add_generation_prompt:
+            text += "<|im_start|>assistant\n"
+        return self.encode(text) if tokenize else text
+
+
+def load_tokenizer(path: Optional[str]):
+    if not path:
+        return ByteTokenizer()
+    from transformers import AutoTokenizer
+    tok = AutoTokenizer.from_pretrained(path, trust_remote_code=False)
+    if tok.pad_token_id is None:
+        tok.pad_token = tok.eos_token
+    return tok

@@ -1,0 +1,89 @@
+"""Streaming datasets, rotating parquet cache (injected list/download functions, no network), prefetch fan-out."""
+import queue
+
+import pyarrow as pa
+import pyarrow.parquet as pq
+import pytest
+import torch
+
+from hippolm_b200.data.prefetch import PrefetchBatcher, QueueIterator
+from hippolm_b200.data.streaming import (RotatingParquetIterable, StreamingDataset, MultiSourceStreamingDataset,
+                                         load_streaming_with_fallback, list_cached_parts)
+from hippolm_b200.data.tokenizer import ByteTokenizer, load_tokenizer
+
+
+def _make_download(log):
+    def download(part, dest):
+        log.append(part)
+        pq.write_table(pa.table({"content": [f"part{part} row{i}" for i in range(10)]}), str(dest))
+    return download
+
+
+def test_rotating_parquet_prefetch_and_eviction(tmp_path):
+    log = []
+    it = RotatingParquetIterable("org/ds", "cfg", lambda: [0, 1, 2], _make_download(log), cache_root=tmp_path)
+    rows = list(it)
+    assert len(rows) == 30 and rows[0]["content"] == "part0 row0" and rows[-1]["content"] == "part2 row9"
+    assert log == [0, 1, 2]
+    assert it.max_files_seen <= 2                       # never more than the current and the next part on disk
+    assert len(list_cached_parts("org/ds", "cfg", tmp_path)) == 1
+
+
+def test_rotating_parquet_download_error_surfaces(tmp_path):
+    def bad(part, dest):
+        if part == 1:
+            raise ConnectionError("boom")
+        pq.write_table(pa.table({"content": ["x"] * 4}), str(dest))
+    it = RotatingParquetIterable("d", None, lambda: [0, 1], bad, cache_root=tmp_path)
+    with pytest.raises(ConnectionError):
+        list(it)
+
+
+def test_streaming_dataset_pretrain_and_sft():
+    tok = ByteTokenizer()
+    ds = StreamingDataset([{"content": "ab"}, {"content": ""}, {"other": 1}, {"content": "xyz"}], tok)
+    docs = list(ds)
+    assert docs == [[97, 98, 256], [120, 121, 122, 256]]
+    sft = StreamingDataset([{"instruction": "hi", "output": "yo"}], tok, stage="sft")
+    text = tok.decode(list(sft)[0])
+    assert "<|im_start|>user\nhi<|im_end|>" in text and "assistant\nyo" in text
+    assert isinstance(load_tokenizer(None), ByteTokenizer)
+
+
+def test_multi_source_schedule():
+    a, b = ([f"a{i}"] for i in range(100)), ([f"b{i}"] for i in range(3))
+    ms = MultiSourceStreamingDataset({"a": a, "b": b}, [(4, {"a": 1, "b": 1}), (4, {"a": 3, "b": 1})])
+    out = [d[0] for d in ms]
+    assert out[:4] == ["a0", "b0", "a1", "b1"] and len(out) == 8 and out[4:7] == ["a2", "a3", "a4"]
+
+
+def test_fallback_only_on_network_errors():
+    def down():
+        raise ConnectionError("x")
+    assert load_streaming_with_fallback([("hf", down), ("ms", lambda: [1, 2])]) == [1, 2]
+    def bad():
+        raise ValueError("config")
+    with pytest.raises(ValueError):
+        load_streaming_with_fallback([("hf", bad), ("ms", lambda: [1])])
+    with pytest.raises(ConnectionError):
+        load_streaming_with_fallback([("hf", down)])
+
+
+def test_prefetch_fanout_sentinel_and_exception():
+    docs = [[1] * 40 for _ in range(12)]
+    qs = [queue.Queue(maxsize=8) for _ in range(2)]      # drained one after the other below
+    pb = PrefetchBatcher(iter(docs), qs, batch_size=2, seq_len=128, chunk_size=64, pack_buffer_size=2)
+    outs = [list(QueueIterator(q, timeout_s=10)) for q in qs]
+    pb.close()
+    assert len(outs[0]) == len(outs[1]) == 3
+    assert torch.equal(outs[0][0]["input_ids"], outs[1][0]["input_ids"]) and outs[0][0]["input_ids"].shape == (256,)
+    assert outs[0][0]["cu_seqlens"][-1] == 256
+
+    def broken():
+        yield [1, 2, 3]
+        raise RuntimeError("tokenizer died")
+    q = queue.Queue(maxsize=4)
+    pb = PrefetchBatcher(broken(), [q], 1, 64, 64, pack_buffer_size=8)
+    with pytest.raises(RuntimeError, match="tokenizer died"):
+        list(QueueIterator(q, timeout_s=10))
+    pb.close()

@@ -1,13 +1,46 @@
-"""Block-scaled NVFP4 GEMM entry point."""
+"""Block-scaled NVFP4 GEMM entry point (``csrc/gemm_fp4.cu``): y = Q(x) dq(W)^T on the FP4 tensor cores."""
 from __future__ import annotations
 
+import ctypes as C
+import os
+
 import torch
+
+from ._ext import lib, ptr, stream_ptr, check
+
+
+def tile_scales(scales: torch.Tensor, rows: int, K: int) -> torch.Tensor:
+    """logical e4m3 scales [rows, K/16] -> the 512-byte (128 rows x 4 k-groups) tiles the MMA reads."""
+    rp = (rows + 127) // 128 * 128
+    out = torch.empty(rp * (K // 16), dtype=torch.uint8, device=scales.device)
+    check(lib().hippo_nvfp4_tile_scales(ptr(scales.view(torch.uint8).contiguous()), ptr(out), C.c_longlong(rows),
+                                        C.c_longlong(K), stream_ptr()), "nvfp4_tile_scales")
+    return out
+
+
+def fp4_matmul(a_packed, a_scales, a_gs, b_packed, b_scales, b_gs) -> torch.Tensor:
+    """[M, K/2] x [N, K/2]^T with logical scales [*, K/16] and fp32 tensor scales -> bf16 [M, N]."""
+    M, K2 = a_packed.shape
+    N = b_packed.shape[0]
+    K = K2 * 2
+    sfa, sfb = tile_scales(a_scales, M, K), tile_scales(b_scales, N, K)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a_packed.device)
+    check(lib().hippo_gemm_nvfp4(ptr(a_packed), ptr(b_packed), ptr(sfa), ptr(sfb), ptr(a_gs), ptr(b_gs), ptr(out),
+                                 M, N, K, C.c_longlong(N), stream_ptr()), "gemm_nvfp4")
+    return out
+
+
+def supported(M: int, N: int, K: int) -> bool:
+    return K % 256 == 0 and N % 8 == 0 and os.environ.get("HIPPO_FP4_GEMM", "1") != "0"
 
 
 def gemm_nt(x, packed, scales, global_scale, act_quant=True):
     from . import cuda_ops, nvfp4_cuda
+    M, K = x.shape
+    N = packed.shape[0]
+    if act_quant and supported(M, N, K):
+        xp, xs, xg = nvfp4_cuda.quantize(x.contiguous())
+        return fp4_matmul(xp, xs, xg, packed, scales, global_scale.float().contiguous())
     w = nvfp4_cuda.dequantize(packed, scales, global_scale, torch.bfloat16)
-    xq = x
-    if act_quant:
-        xq = nvfp4_cuda.dequantize(*nvfp4_cuda.quantize(x), dtype=torch.bfloat16)
+    xq = nvfp4_cuda.dequantize(*nvfp4_cuda.quantize(x), dtype=torch.bfloat16) if act_quant else x
     return cuda_ops.gemm_nt(xq, w)

@@ -117,3 +117,22 @@ def test_nvfp4_fused_apply_update():
     target = w0 * 0.99 - 0.01 * o.float()
     p2, s2, _ = ops.nvfp4_quantize(target, gs)
     assert torch.equal(ops.nvfp4_dequantize(p2, s2, gs), w1)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (300, 264, 768), (1024, 512, 2048)])
+def test_nvfp4_tensor_core_gemm(M, N, K):
+    """Block-scaled FP4 MMA (kind::mxf4nvf4) vs the fp32 product of the dequantised operands."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ops import fp4_gemm, _ext
+    torch.manual_seed(M + K)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+    xp, xs, xg = ops.nvfp4_quantize(x)
+    wp, ws, wg = ops.nvfp4_quantize(w)
+    y = fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg)
+    ref = ops.nvfp4_dequantize(xp, xs, xg) @ ops.nvfp4_dequantize(wp, ws, wg).t()
+    assert _rel(y, ref) < 1e-2
+    y2 = ops.nvfp4_linear(x, wp, ws, wg, act_quant=True)
+    assert _rel(y2, ref) < 1e-2
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0

@@ -1,0 +1,35 @@
+#!/usr/bin/env python
+"""tcgen05 bf16 GEMM (NT / NN / TN) and block-scaled NVFP4 GEMM throughput against torch.matmul (cuBLAS) and
+the measured peak. Prints one JSON line per shape."""
+import json
+
+import torch
+
+from common import time_ms
+from hippolm_b200.ops import cuda_ops as co, nvfp4_cuda, fp4_gemm
+from hippolm_b200.utils.timing import load_measured_peaks
+
+SHAPES = [(8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336), (4096, 14336, 16384)]
+
+
+def main():
+    pk = load_measured_peaks()
+    for (M, N, K) in SHAPES:
+        a = torch.randn(M, K, device="cuda").bfloat16(); b = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+        bt, at = b.t().contiguous(), a.t().contiguous()
+        fl = 2.0 * M * N * K
+        rec = {"M": M, "N": N, "K": K}
+        for name, fn in (("nt", lambda: co.gemm_nt(a, b)), ("nn", lambda: co.gemm_nn(a, bt)),
+                         ("tn", lambda: co.gemm_tn(at, bt)), ("cublas", lambda: a @ b.t())):
+            ms = time_ms(fn, flush=False)
+            rec[name + "_tflops"] = round(fl / ms / 1e9, 1)
+        if K % 256 == 0:
+            xp, xs, xg = nvfp4_cuda.quantize(a); wp, ws, wg = nvfp4_cuda.quantize(b)
+            ms = time_ms(lambda: fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg), flush=False)
+            rec["nvfp4_tflops"] = round(fl / ms / 1e9, 1)
+        rec["bf16_frac_of_" + pk["source"] + "_peak"] = round(rec["nt_tflops"] / pk["bf16_tflops"], 3)
+        print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -157,7 +157,7 @@ constexpr int kda_bwd_state_smem() {
 
 // =================================================================================================== dqkw
 template <int DK>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew, const bf16* __restrict__ dvn,
                     const bf16* __restrict__ Sst, const bf16* __restrict__ dSst, const bf16* __restrict__ qg,
                     const bf16* __restrict__ kg, const float* __restrict__ G, const int* __restrict__ chunk_start,
@@ -170,8 +170,8 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
   bf16* dvs = vns + 64 * LD;
   bf16* Ss = dvs + 64 * LD;           // [DK][LD]
   bf16* dSs = Ss + DK * LD;           // [DK][LD]
-  float* stg = (float*)(dSs + DK * LD);   // [8 warps][2][16][20]
-  float* dGl = stg + 8 * 2 * 320;     // [DK]
+  float* stg = (float*)(dSs + DK * LD);   // [16 warps][2][16][20]
+  float* dGl = stg + 16 * 2 * 320;    // [DK]
   const int chunk = blockIdx.x, h = blockIdx.y;
   const int t0 = chunk_start[chunk], len = chunk_len[chunk];
   if (len == 0) return;
@@ -179,7 +179,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
   const long long cbase = ((long long)chunk * H + h) * 64;
   const long long sbase = ((long long)chunk * H + h) * DK;
 
-  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 512) {
     int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
     uint4 z = make_uint4(0, 0, 0, 0);
     if (r < len) z = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + c8);
@@ -187,7 +187,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
     *(uint4*)(vns + r * LD + c8) = *(const uint4*)(vnew + (cbase + r) * DK + c8);
     *(uint4*)(dvs + r * LD + c8) = *(const uint4*)(dvn + (cbase + r) * DK + c8);
   }
-  for (int idx = tid; idx < DK * (DK / 8); idx += 256) {
+  for (int idx = tid; idx < DK * (DK / 8); idx += 512) {
     int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
     *(uint4*)(Ss + r * LD + c8) = *(const uint4*)(Sst + (sbase + r) * DK + c8);
     *(uint4*)(dSs + r * LD + c8) = *(const uint4*)(dSst + (sbase + r) * DK + c8);
@@ -196,7 +196,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
   __syncthreads();
   // state-decay term of dGlast: sum_v dS[c,v] S[c,v] e^Glast[c]
   {
-    constexpr int TPR = 256 / DK;           // threads per state row
+    constexpr int TPR = 512 / DK;           // threads per state row
     int c = tid / TPR, part = tid % TPR;
     float s = 0.f;
     for (int vv = part; vv < DK; vv += TPR)
@@ -206,7 +206,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
   }
   float* my0 = stg + warp * 640, *my1 = my0 + 320;
   // (dqg, dkg) pairs: one warp does both for a given 16x16 tile so that dG has a single writer
-  for (int t = warp; t < 4 * NT; t += 8) {
+  for (int t = warp; t < 4 * NT; t += 16) {
     const int rt = t / NT, nt = t % NT;
     FragC a0, a1; wmma::fill_fragment(a0, 0.f); wmma::fill_fragment(a1, 0.f);
 #pragma unroll
@@ -245,7 +245,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
     __syncwarp();
   }
   // dw = -dv_new S^T
-  for (int t = warp; t < 4 * NT; t += 8) {
+  for (int t = warp; t < 4 * NT; t += 16) {
     const int rt = t / NT, nt = t % NT;
     FragC a0; wmma::fill_fragment(a0, 0.f);
 #pragma unroll
@@ -265,7 +265,7 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
     __syncwarp();
   }
   // dAqk = tril(do v_new^T)
-  for (int t = warp; t < 16; t += 8) {
+  for (int t = warp; t < 16; t += 16) {
     const int rt = t >> 2, ct = t & 3;
     FragC a0; wmma::fill_fragment(a0, 0.f);
     if (ct <= rt) {
@@ -291,15 +291,15 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
   if (tid < DK) dG_acc[(cbase + 63) * DK + tid] += dGl[tid];
 }
 template <int DK>
-constexpr int kda_bwd_dqkw_smem() { return 3 * 64 * (DK + 8) * 2 + 2 * DK * (DK + 8) * 2 + 8 * 2 * 320 * 4 + DK * 4 + 128; }
+constexpr int kda_bwd_dqkw_smem() { return 3 * 64 * (DK + 8) * 2 + 2 * DK * (DK + 8) * 2 + 16 * 2 * 320 * 4 + DK * 4 + 128; }
 
 // =================================================================================================== WY
 template <int DK>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 kda_bwd_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, const float* __restrict__ beta,
                   const float* __restrict__ G, const bf16* __restrict__ Ainv, const bf16* __restrict__ Akk,
                   const bf16* __restrict__ dvn, const bf16* __restrict__ dw, const int* __restrict__ chunk_start,
-                  const int* __restrict__ chunk_len, int H, float* __restrict__ dk_acc, float* __restrict__ dG_acc,
+                  const int* __restrict__ chunk_len, int H, bf16* __restrict__ dbk_out,
                   bf16* __restrict__ dv_out, float* __restrict__ dbeta_out, bf16* __restrict__ dKK_out) {
   constexpr int LD = DK + 8, NT = DK / 16;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -434,26 +434,33 @@ kda_bwd_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, const 
     {
       const int rr = lane >> 1, half = lane & 1, i = rt * 16 + rr;
       float rowsum = 0.f;
-      if (i < len) {
+      if (!which) {
+        // dv = beta * dbv ; dbeta += sum_c v * dbv  (v recovered from the beta*v tile)
+        const float inv_b = bs[i] > 0.f ? 1.f / bs[i] : 0.f;
+        float o8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          int cc = half * 8 + e, c = nt * 16 + cc;
-          float val = my[rr * 20 + cc];
-          long long toff = ((long long)(t0 + i) * H + h) * DK + c;
-          if (!which) {
-            dv_out[toff] = __float2bfloat16(bs[i] * val);
-            rowsum += __bfloat162float(v[toff]) * val;
-          } else {
-            long long off = (cbase + i) * DK + c;
-            float ke = __bfloat162float(k[toff]) * __expf(G[off]);
-            dk_acc[off] += bs[i] * __expf(G[off]) * val;
-            dG_acc[off] += bs[i] * ke * val;
-            rowsum += ke * val;
-          }
+          const int cc = half * 8 + e, c = nt * 16 + cc;
+          const float val = my[rr * 20 + cc];
+          o8[e] = bs[i] * val;
+          rowsum += __bfloat162float(bvs[i * LD + c]) * inv_b * val;
         }
+        if (i < len) {
+          uint4 pk; __nv_bfloat162* pb = (__nv_bfloat162*)&pk;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pb[e] = __floats2bfloat162_rn(o8[2 * e], o8[2 * e + 1]);
+          *(uint4*)(dv_out + ((long long)(t0 + i) * H + h) * DK + nt * 16 + half * 8) = pk;
+        }
+        rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
+        if (half == 0 && i < len) atomicAdd(&dbs[i], rowsum);
+      } else {
+        // dbk = X^T dw is consumed by the A-matrix kernel (dk, dG and the k part of dbeta)
+        uint4 pk; __nv_bfloat162* pb = (__nv_bfloat162*)&pk;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          pb[e] = __floats2bfloat162_rn(my[rr * 20 + half * 8 + 2 * e], my[rr * 20 + half * 8 + 2 * e + 1]);
+        *(uint4*)(dbk_out + (cbase + i) * DK + nt * 16 + half * 8) = pk;
       }
-      rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
-      if (half == 0 && i < len) atomicAdd(&dbs[i], rowsum);
     }
     __syncwarp();
   }
@@ -465,15 +472,18 @@ constexpr int kda_bwd_wy_smem() { return 3 * 64 * 72 * 2 + 4 * 64 * (DK + 8) * 2
 
 // =================================================================================================== A matrices
 template <int DK>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(4 * DK, 1)
 kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const float* __restrict__ G,
+                    const float* __restrict__ beta, const bf16* __restrict__ dbk,
                     const bf16* __restrict__ dKK, const bf16* __restrict__ dAqk, const float* __restrict__ dq_acc,
                     const float* __restrict__ dk_acc, const float* __restrict__ dG_acc,
                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
-                    float* __restrict__ dq_out, float* __restrict__ dk_out, float* __restrict__ dg_out) {
+                    float* __restrict__ dq_out, float* __restrict__ dk_out, float* __restrict__ dg_out,
+                    float* __restrict__ dbeta_out) {
   constexpr int LD = DK + 8, NT = DK / 16, LQ = DK + 4;
-  constexpr int RPT = DK / 4;                 // rows owned by a thread (256 threads cover 64 x DK)
-  constexpr int NB = RPT / 16;                // diagonal blocks owned by a thread
+  constexpr int NTHR = 4 * DK, NWARP = NTHR / 32;
+  constexpr int RPT = 16;                     // rows owned by a thread: one diagonal block
+  constexpr int NB = 1;
   extern __shared__ __align__(128) uint8_t smem[];
   float* Gs = (float*)smem;                   // [64][DK]
   float* stQ = Gs + 64 * DK;                  // [48][LQ]
@@ -487,6 +497,8 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   bf16* Ck = T2 + 64 * LD;                    // [16][LD]
   bf16* D1 = Ck + 16 * LD;                    // [64][72]  dKK
   bf16* D2 = D1 + 64 * 72;                    // [64][72]  dAqk
+  float* bs = (float*)(D2 + 64 * 72);         // [64] beta
+  float* dbs = bs + 64;                       // [64] k part of dbeta
   const int chunk = blockIdx.x, h = blockIdx.y;
   const int t0 = chunk_start[chunk], len = chunk_len[chunk];
   if (len == 0) return;
@@ -494,7 +506,7 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   const long long cbase = ((long long)chunk * H + h) * 64;
   const int c = tid % DK, rh = tid / DK, row0 = rh * RPT;
 
-  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+  for (int idx = tid; idx < 64 * (DK / 8); idx += NTHR) {
     int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
     uint4 zq = make_uint4(0, 0, 0, 0), zk = zq;
     if (r < len) {
@@ -503,15 +515,16 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     }
     *(uint4*)(qs + r * LD + c8) = zq; *(uint4*)(ks + r * LD + c8) = zk;
   }
-  for (int idx = tid; idx < 64 * (DK / 4); idx += 256) {
+  for (int idx = tid; idx < 64 * (DK / 4); idx += NTHR) {
     int r = idx / (DK / 4), c4 = (idx % (DK / 4)) * 4;
     *(float4*)(Gs + r * DK + c4) = *(const float4*)(G + (cbase + r) * DK + c4);
   }
-  for (int idx = tid; idx < 64 * 8; idx += 256) {
+  for (int idx = tid; idx < 64 * 8; idx += NTHR) {
     int r = idx >> 3, c8 = (idx & 7) * 8;
     *(uint4*)(D1 + r * 72 + c8) = *(const uint4*)(dKK + (cbase + r) * 64 + c8);
     *(uint4*)(D2 + r * 72 + c8) = *(const uint4*)(dAqk + (cbase + r) * 64 + c8);
   }
+  if (tid < 64) { bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f; dbs[tid] = 0.f; }
   float dq[RPT], dk[RPT], dG[RPT];
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) {
@@ -550,11 +563,11 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   for (int J = 0; J < 3; ++J) {
     const int e = 16 * J + 15, r0 = 16 * (J + 1), nrows = 64 - r0;
     __syncthreads();
-    for (int idx = tid; idx < 16 * DK; idx += 256) {
+    for (int idx = tid; idx < 16 * DK; idx += NTHR) {
       int jj = idx / DK, cc = idx % DK, j = 16 * J + jj;
       Ck[jj * LD + cc] = __float2bfloat16(__bfloat162float(ks[j * LD + cc]) * __expf(Gs[e * DK + cc] - Gs[j * DK + cc]));
     }
-    for (int idx = tid; idx < nrows * DK; idx += 256) {
+    for (int idx = tid; idx < nrows * DK; idx += NTHR) {
       int rr = idx / DK, cc = idx % DK, i = r0 + rr;
       float f = __expf(Gs[i * DK + cc] - Gs[e * DK + cc]);
       T1[rr * LD + cc] = __float2bfloat16(__bfloat162float(qs[i * LD + cc]) * f);
@@ -563,7 +576,7 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     __syncthreads();
     const int nrt = nrows / 16;
     // dRq = D2[rows, J] Ck ; dRk = D1[rows, J] Ck ; dCk = D1[rows, J]^T Rk + D2[rows, J]^T Rq
-    for (int t = warp; t < (2 * nrt + 1) * NT; t += 8) {
+    for (int t = warp; t < (2 * nrt + 1) * NT; t += NWARP) {
       const int kind = t / NT, nt = t % NT;
       FragC acc; wmma::fill_fragment(acc, 0.f);
       if (kind < 2 * nrt) {
@@ -605,6 +618,20 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
       }
     }
   }
+  // backward of w = Ainv (beta k e^G): dbk = Ainv^T dw arrives from the WY kernel
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    const int i = row0 + ii;
+    const float eG = __expf(Gs[i * DK + c]);
+    const float d = __bfloat162float(dbk[(cbase + i) * DK + c]);
+    const float ke = __bfloat162float(ks[i * LD + c]) * eG;
+    dk[ii] += bs[i] * eG * d;
+    dG[ii] += bs[i] * ke * d;
+    float part = ke * d;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+    if ((tid & 31) == 0) atomicAdd(&dbs[i], part);
+  }
   // dg = reverse cumsum of dG over the chunk rows
   float tot = 0.f;
 #pragma unroll
@@ -612,7 +639,7 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
   carry[rh * DK + c] = tot;
   __syncthreads();
   float add = 0.f;
-  for (int r2 = rh + 1; r2 < 256 / DK; ++r2) add += carry[r2 * DK + c];
+  for (int r2 = rh + 1; r2 < NTHR / DK; ++r2) add += carry[r2 * DK + c];
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) {
     const int i = row0 + ii;
@@ -621,11 +648,13 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
       dq_out[toff] = dq[ii]; dk_out[toff] = dk[ii]; dg_out[toff] = dG[ii] + add;
     }
   }
+  __syncthreads();
+  if (tid < len) dbeta_out[(long long)(t0 + tid) * H + h] += dbs[tid];
 }
 template <int DK>
 constexpr int kda_bwd_amat_smem() {
   return 64 * DK * 4 + (48 + 48 + 16) * (DK + 4) * 4 + 4 * DK * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 +
-         2 * 64 * 72 * 2 + 128;
+         2 * 64 * 72 * 2 + 128 * 4 + 128;
 }
 
 }  // namespace hippo
@@ -637,8 +666,8 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
                       const void* qg, const void* kg, const void* Aqk, const void* Ainv, const void* Akk,
                       const void* vnew, const void* Sst, const void* d_o, const float* dfinal, const int* cs,
                       const int* cl, const int* sc, int NC, int N, int H, void* dvn, void* dSst, void* dw, void* dAqk,
-                      void* dKK, float* dq_acc, float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg,
-                      float* dbeta, float* dh0, cudaStream_t s) {
+                      void* dKK, void* dbk, float* dq_acc, float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv,
+                      float* dg, float* dbeta, float* dh0, cudaStream_t s) {
   constexpr int VS = 32;
   auto k3 = kda_bwd_state_kernel<DK, VS>;
   auto k4a = kda_bwd_dqkw_kernel<DK>;
@@ -656,13 +685,13 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
   if (NC == 0) return 0;
   k3<<<dim3(DK / VS, H, N), 128, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
       (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
-  k4a<<<dim3(NC, H), 256, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
+  k4a<<<dim3(NC, H), 512, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
       (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc, dG_acc,
       (bf16*)dw, (bf16*)dAqk);
   k4b<<<dim3(NC, H), 256, kda_bwd_wy_smem<DK>(), s>>>((const bf16*)k, (const bf16*)v, beta, G, (const bf16*)Ainv,
-      (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, dk_acc, dG_acc, (bf16*)dv, dbeta, (bf16*)dKK);
-  k4c<<<dim3(NC, H), 256, kda_bwd_amat_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, G, (const bf16*)dKK,
-      (const bf16*)dAqk, dq_acc, dk_acc, dG_acc, cs, cl, H, dq, dk, dg);
+      (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, (bf16*)dbk, (bf16*)dv, dbeta, (bf16*)dKK);
+  k4c<<<dim3(NC, H), 4 * DK, kda_bwd_amat_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, G, beta, (const bf16*)dbk,
+      (const bf16*)dKK, (const bf16*)dAqk, dq_acc, dk_acc, dG_acc, cs, cl, H, dq, dk, dg, dbeta);
   return (int)cudaGetLastError();
 }
 
@@ -670,11 +699,11 @@ extern "C" int hippo_kda_bwd(const void* q, const void* k, const void* v, const 
                              const void* w, const void* qg, const void* kg, const void* Aqk, const void* Ainv,
                              const void* Akk, const void* vnew, const void* Sst, const void* d_o, const float* dfinal,
                              const int* chunk_start, const int* chunk_len, const int* seq_chunk, int NC, int N, int H,
-                             int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, float* dq_acc,
+                             int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, void* dbk, float* dq_acc,
                              float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg, float* dbeta,
                              float* dh0, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
-  if (DK == 64) return launch_bwd<64>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  if (DK == 64) return launch_bwd<64>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
   return -1;
 }

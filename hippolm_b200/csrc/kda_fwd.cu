@@ -20,7 +20,7 @@ namespace hippo {
 using namespace nvcuda;
 
 template <int DK>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                      const float* __restrict__ g, const float* __restrict__ beta,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
@@ -29,21 +29,24 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
                      bf16* __restrict__ Ainv_out, bf16* __restrict__ Akk_out) {
   constexpr int LD = DK + 8;       // bf16 tile pitch
   constexpr int LA = 68;           // fp32 64x64 pitch
+  constexpr int LG = DK + 4;       // fp32 G pitch (rows land on different banks)
   extern __shared__ __align__(128) uint8_t smem[];
-  float* Gs = (float*)smem;                       // [64][DK]
-  bf16* qs = (bf16*)(Gs + 64 * DK);               // [64][LD]
+  float* Gs = (float*)smem;                       // [64][LG]
+  bf16* qs = (bf16*)(Gs + 64 * LG);               // [64][LD]
   bf16* ks = qs + 64 * LD;                        // [64][LD]
   bf16* T1 = ks + 64 * LD;                        // [64][LD] work tile (row side q / beta*k*e^G)
   bf16* T2 = T1 + 64 * LD;                        // [64][LD] work tile (row side k / beta*v)
   bf16* Ck = T2 + 64 * LD;                        // [16][LD] column side
   float* kk = (float*)(Ck + 16 * LD);             // [64][LA]
-  float* qk = kk + 64 * LA;                       // [64][LA]
-  float* X = qk + 64 * LA;                        // [64][LA]
-  float* Tm = X + 64 * LA;                        // [3][16][16]
-  float* bs = Tm + 3 * 256;                       // [64]
+  float* bs = kk + 64 * LA;                       // [64]
   bf16* Xb = (bf16*)(bs + 64);                    // [64][72]
-  float* stg = (float*)(Xb + 64 * 72);            // [8 warps][16][20]
+  float* stg = (float*)(Xb + 64 * 72);            // [16 warps][16][20]
+  // the inverse (phase 3) reuses the work-tile region, which is idle between phases 2 and 4
+  float* X = (float*)T1;                          // [64][LA]
+  float* Tm = X + 64 * LA;                        // [3][16][16]
+  static_assert((2 * 64 + 16) * LD * 2 >= (64 * LA + 3 * 256) * 4, "inverse scratch must fit in the work tiles");
 
+  constexpr int NTHR = 512, NWARP = 16;
   const int chunk = blockIdx.x, h = blockIdx.y;
   const int t0 = chunk_start[chunk], len = chunk_len[chunk];
   if (len == 0) return;                                       // padding entry of the chunk table
@@ -51,7 +54,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   const long long cbase = ((long long)chunk * H + h) * 64;   // row base in chunk-padded [NC,H,64,*] arrays
 
   // ---- phase 0: loads, cumsum
-  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+  for (int idx = tid; idx < 64 * (DK / 8); idx += NTHR) {
     int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
     uint4 zq = make_uint4(0, 0, 0, 0), zk = zq;
     if (r < len) {
@@ -60,7 +63,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     }
     *(uint4*)(qs + r * LD + c8) = zq; *(uint4*)(ks + r * LD + c8) = zk;
   }
-  for (int idx = tid; idx < 64 * LA; idx += 256) { kk[idx] = 0.f; qk[idx] = 0.f; X[idx] = 0.f; }
+  for (int idx = tid; idx < 64 * LA; idx += NTHR) kk[idx] = 0.f;
   if (tid < 64) bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f;
   if (tid < DK) {
     float run = 0.f;
@@ -68,7 +71,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     for (int r = 0; r < 64; ++r) {
       float gv = r < len ? g[((long long)(t0 + r) * H + h) * DK + tid] : 0.f;
       run += gv;
-      Gs[r * DK + tid] = run;
+      Gs[r * LG + tid] = run;
       Gout[(cbase + r) * DK + tid] = run;
     }
   }
@@ -78,7 +81,9 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   {
     constexpr int CPL = DK / 8;
     const int grp = tid >> 3, gl = tid & 7;
-    for (int p = grp; p < 4 * 136; p += 32) {
+    for (int p0 = grp; p0 < 4 * 136 + 32; p0 += NTHR / 8) {     // uniform trip count: shuffles need every lane
+      const bool valid = p0 < 4 * 136;
+      const int p = valid ? p0 : 0;
       int b = p / 136, r = p % 136;
       int ii = 0;
       while ((ii + 1) * (ii + 2) / 2 <= r) ++ii;
@@ -87,8 +92,8 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       float skk = 0.f, sqk = 0.f;
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) {
-        int c = gl * CPL + cc;
-        float e = __expf(Gs[i * DK + c] - Gs[j * DK + c]);
+        int c = cc * 8 + gl;
+        float e = __expf(Gs[i * LG + c] - Gs[j * LG + c]);
         float kj = __bfloat162float(ks[j * LD + c]) * e;
         skk += __bfloat162float(ks[i * LD + c]) * kj;
         sqk += __bfloat162float(qs[i * LD + c]) * kj;
@@ -96,7 +101,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 1); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 1);
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 2); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 2);
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 4); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 4);
-      if (gl == 0) { if (jj < ii) kk[i * LA + j] = skk; qk[i * LA + j] = sqk; }
+      if (gl == 0 && valid) { if (jj < ii) kk[i * LA + j] = skk; Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(sqk); }
     }
   }
 
@@ -104,13 +109,13 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   for (int J = 0; J < 3; ++J) {
     const int e = 16 * J + 15, r0 = 16 * (J + 1), nrows = 64 - r0;
     __syncthreads();
-    for (int idx = tid; idx < 16 * DK; idx += 256) {
+    for (int idx = tid; idx < 16 * DK; idx += NTHR) {
       int jj = idx / DK, c = idx % DK, j = 16 * J + jj;
-      Ck[jj * LD + c] = __float2bfloat16(__bfloat162float(ks[j * LD + c]) * __expf(Gs[e * DK + c] - Gs[j * DK + c]));
+      Ck[jj * LD + c] = __float2bfloat16(__bfloat162float(ks[j * LD + c]) * __expf(Gs[e * LG + c] - Gs[j * LG + c]));
     }
-    for (int idx = tid; idx < nrows * DK; idx += 256) {
+    for (int idx = tid; idx < nrows * DK; idx += NTHR) {
       int rr = idx / DK, c = idx % DK, i = r0 + rr;
-      float f = __expf(Gs[i * DK + c] - Gs[e * DK + c]);
+      float f = __expf(Gs[i * LG + c] - Gs[e * LG + c]);
       T1[rr * LD + c] = __float2bfloat16(__bfloat162float(qs[i * LD + c]) * f);
       T2[rr * LD + c] = __float2bfloat16(__bfloat162float(ks[i * LD + c]) * f);
     }
@@ -129,16 +134,27 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
         wmma::load_matrix_sync(bfr, Ck + kt * 16, LD);
         wmma::mma_sync(acc, a, bfr, acc);
       }
-      float* dst = (which ? kk : qk) + (r0 + rt * 16) * LA + 16 * J;
-      wmma::store_matrix_sync(dst, acc, LA, wmma::mem_row_major);
+      if (which) {
+        wmma::store_matrix_sync(kk + (r0 + rt * 16) * LA + 16 * J, acc, LA, wmma::mem_row_major);
+      } else {
+        float* my = stg + warp * 16 * 20;
+        wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
+        __syncwarp();
+#pragma unroll
+        for (int e2 = 0; e2 < 8; ++e2) {
+          int el = lane * 8 + e2, rr = el >> 4, cc = el & 15;
+          Aqk_out[(cbase + r0 + rt * 16 + rr) * 64 + 16 * J + cc] = __float2bfloat16(my[rr * 20 + cc]);
+        }
+      }
     }
   }
   __syncthreads();
 
   // ---- phase 3: X = (I + beta*kk)^-1, blocked forward substitution in fp32
-  for (int idx = tid; idx < 64 * 64; idx += 256) {
+  for (int idx = tid; idx < 64 * 64; idx += NTHR) {
     int i = idx >> 6, j = idx & 63;
     kk[i * LA + j] = j < i ? kk[i * LA + j] * bs[i] : 0.f;      // kk now holds Akk
+    X[i * LA + j] = 0.f;
   }
   __syncthreads();
   if (tid < 64) {
@@ -157,9 +173,10 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   }
   __syncthreads();
   {
-    const int r = tid >> 4, c = tid & 15;
+    const int r = (tid >> 4) & 15, c = tid & 15;
+    const bool act = tid < 256;
     for (int d = 1; d < 4; ++d) {
-      for (int J = 0; J + d < 4; ++J) {
+      for (int J = 0; J + d < 4 && act; ++J) {
         const int I = J + d;
         float s = 0.f;
         for (int L = J; L < I; ++L)
@@ -168,7 +185,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
         Tm[J * 256 + r * 16 + c] = s;
       }
       __syncthreads();
-      for (int J = 0; J + d < 4; ++J) {
+      for (int J = 0; J + d < 4 && act; ++J) {
         const int I = J + d;
         float s = 0.f;
 #pragma unroll
@@ -180,29 +197,30 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   }
 
   // ---- phase 4: operands + outputs
-  for (int idx = tid; idx < 64 * 64; idx += 256) {
+  for (int idx = tid; idx < 64 * 64; idx += NTHR) {
     int i = idx >> 6, j = idx & 63;
     bf16 xv = __float2bfloat16(X[i * LA + j]);
     Xb[i * 72 + j] = xv;
     Ainv_out[(cbase + i) * 64 + j] = xv;
     Akk_out[(cbase + i) * 64 + j] = __float2bfloat16(kk[i * LA + j]);
-    Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(j <= i ? qk[i * LA + j] : 0.f);
+    if (j > i) Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(0.f);
   }
-  for (int idx = tid; idx < 64 * DK; idx += 256) {
+  __syncthreads();                                    // X (aliased on the work tiles) is consumed
+  for (int idx = tid; idx < 64 * DK; idx += NTHR) {
     int i = idx / DK, c = idx % DK;
-    float G = Gs[i * DK + c], eG = __expf(G);
+    float G = Gs[i * LG + c], eG = __expf(G);
     float kv = __bfloat162float(ks[i * LD + c]), qv = __bfloat162float(qs[i * LD + c]);
     float vv = i < len ? __bfloat162float(v[((long long)(t0 + i) * H + h) * DK + c]) : 0.f;
     T1[i * LD + c] = __float2bfloat16(bs[i] * kv * eG);
     T2[i * LD + c] = __float2bfloat16(bs[i] * vv);
     qg_out[(cbase + i) * DK + c] = __float2bfloat16(qv * eG);
-    kg_out[(cbase + i) * DK + c] = __float2bfloat16(kv * __expf(Gs[63 * DK + c] - G));
+    kg_out[(cbase + i) * DK + c] = __float2bfloat16(kv * __expf(Gs[63 * LG + c] - G));
   }
   __syncthreads();
   {
     constexpr int NT = DK / 16;
     float* my = stg + warp * 16 * 20;
-    for (int t = warp; t < 2 * 4 * NT; t += 8) {
+    for (int t = warp; t < 2 * 4 * NT; t += NWARP) {
       const int which = t / (4 * NT), rt = (t % (4 * NT)) / NT, nt = t % NT;
       const bf16* B = which ? T2 : T1;
       wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
@@ -229,8 +247,8 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
 
 template <int DK>
 constexpr int kda_intra_smem() {
-  return 64 * DK * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 + 3 * 64 * 68 * 4 + 3 * 256 * 4 + 64 * 4 +
-         64 * 72 * 2 + 8 * 16 * 20 * 4 + 128;
+  return 64 * (DK + 4) * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 + 64 * 68 * 4 + 64 * 4 +
+         64 * 72 * 2 + 16 * 16 * 20 * 4 + 128;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -411,7 +429,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const float* 
     once = true;
   }
   if (NC == 0) return 0;
-  k1<<<dim3(NC, H), 256, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
+  k1<<<dim3(NC, H), 512, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
                                                     G, (bf16*)w, (bf16*)u, (bf16*)qg, (bf16*)kg, (bf16*)Aqk, (bf16*)Ainv, (bf16*)Akk);
   k2<<<dim3(DK / VS, H, N), 128, kda_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
                                                                 (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, H, h0,

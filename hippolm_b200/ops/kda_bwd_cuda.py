@@ -15,7 +15,7 @@ def backward(ctx, do, dfin):
     dfin_c = dfin.float().contiguous() if dfin is not None else None
     bf = dict(dtype=torch.bfloat16, device=dev)
     f32 = dict(dtype=torch.float32, device=dev)
-    dvn, dw = torch.empty((NC, H, 64, DK), **bf), torch.empty((NC, H, 64, DK), **bf)
+    dvn, dw, dbk = (torch.empty((NC, H, 64, DK), **bf) for _ in range(3))
     dSst = torch.empty((NC, H, DK, DK), **bf)
     dAqk, dKK = torch.empty((NC, H, 64, 64), **bf), torch.empty((NC, H, 64, 64), **bf)
     dq_acc, dk_acc, dG_acc = (torch.empty((NC, H, 64, DK), **f32) for _ in range(3))
@@ -25,7 +25,7 @@ def backward(ctx, do, dfin):
     dh0 = torch.empty((N, H, DK, DK), **f32) if ctx.has_h0 else None
     check(lib().hippo_kda_bwd(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(G), ptr(w), ptr(qg), ptr(kg), ptr(Aqk), ptr(Ainv),
                               ptr(Akk), ptr(vnew), ptr(Sst), ptr(do), ptr(dfin_c), ptr(cs), ptr(cl), ptr(sc), NC, N, H,
-                              DK, ptr(dvn), ptr(dSst), ptr(dw), ptr(dAqk), ptr(dKK), ptr(dq_acc), ptr(dk_acc),
+                              DK, ptr(dvn), ptr(dSst), ptr(dw), ptr(dAqk), ptr(dKK), ptr(dbk), ptr(dq_acc), ptr(dk_acc),
                               ptr(dG_acc), ptr(dq), ptr(dk), ptr(dv), ptr(dg), ptr(dbeta), ptr(dh0), stream_ptr()),
           "kda_bwd")
     return dq, dk, dv, dg, dbeta, dh0, None

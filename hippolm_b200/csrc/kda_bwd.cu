@@ -25,14 +25,18 @@ typedef wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> FragBT
 typedef wmma::fragment<wmma::accumulator, 16, 16, 16, float> FragC;
 
 // =================================================================================================== state
+// 256 threads; the tiles of the next (earlier) chunk are fetched into registers during the math of the current one.
 template <int DK, int VS>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(256, 2)
 kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, const bf16* __restrict__ kg,
                      const bf16* __restrict__ Aqk, const float* __restrict__ G, const bf16* __restrict__ d_o,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
-                     const int* __restrict__ seq_chunk, int H, const float* __restrict__ dfinal,
-                     bf16* __restrict__ dvn_out, bf16* __restrict__ dS_out, float* __restrict__ dh0) {
-  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4;
+                     const int* __restrict__ seq_chunk, const int* __restrict__ seq_order, int H,
+                     const float* __restrict__ dfinal, bf16* __restrict__ dvn_out, bf16* __restrict__ dS_out,
+                     float* __restrict__ dh0) {
+  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4, NTHR = 256;
+  constexpr int NV_BIG = 64 * (DK / 8) / NTHR, NV_AQ = 64 * 8 / NTHR;
+  static_assert(64 * (VS / 8) <= NTHR && DK <= NTHR, "tile/thread mapping");
   extern __shared__ __align__(128) uint8_t smem[];
   float* dS = (float*)smem;                   // [DK][LF]
   float* stg = dS + DK * LF;                  // [64][LF]
@@ -45,82 +49,103 @@ kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, co
   bf16* ndv = dos + 64 * LS;                  // [64][LS]  (-dv_new)
   bf16* Aq = ndv + 64 * LS;                   // [64][72]
 
-  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = blockIdx.z;
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
 
-  for (int idx = tid; idx < DK * VS; idx += 128) {
+  for (int idx = tid; idx < DK * VS; idx += NTHR) {
     int r = idx / VS, c = idx % VS;
     float s0 = dfinal ? dfinal[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] : 0.f;
     dS[r * LF + c] = s0;
     dSb[r * LS + c] = __float2bfloat16(s0);
   }
+  uint4 rw[NV_BIG], rq[NV_BIG], rk[NV_BIG], ra[NV_AQ], rdo;
+  float rg = 0.f;
+  auto fetch = [&](int chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+#pragma unroll
+    for (int j = 0; j < NV_BIG; ++j) {
+      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      long long off = (cbase + r) * DK + c8;
+      rw[j] = *(const uint4*)(w + off); rq[j] = *(const uint4*)(qg + off); rk[j] = *(const uint4*)(kg + off);
+    }
+#pragma unroll
+    for (int j = 0; j < NV_AQ; ++j) {
+      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      ra[j] = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+    }
+    if (tid < 64 * (VS / 8)) {
+      int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
+      rdo = make_uint4(0, 0, 0, 0);
+      if (r < len) rdo = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + vs0 + c8);
+    }
+    if (tid < DK) rg = G[(cbase + 63) * DK + tid];
+  };
+  if (c_begin < c_end) fetch(c_end - 1);
   __syncthreads();
 
   for (int chunk = c_end - 1; chunk >= c_begin; --chunk) {
     const long long cbase = ((long long)chunk * H + h) * 64;
-    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
-    for (int idx = tid; idx < 64 * (DK / 8); idx += 128) {
-      int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
-      long long off = (cbase + r) * DK + c8;
-      *(uint4*)(ws + r * LD + c8) = *(const uint4*)(w + off);
-      *(uint4*)(qgs + r * LD + c8) = *(const uint4*)(qg + off);
-      *(uint4*)(kgs + r * LD + c8) = *(const uint4*)(kg + off);
+#pragma unroll
+    for (int j = 0; j < NV_BIG; ++j) {
+      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      *(uint4*)(ws + r * LD + c8) = rw[j]; *(uint4*)(qgs + r * LD + c8) = rq[j]; *(uint4*)(kgs + r * LD + c8) = rk[j];
     }
-    for (int idx = tid; idx < 64 * 8; idx += 128) {
-      int r = idx >> 3, c8 = (idx & 7) * 8;
-      *(uint4*)(Aq + r * 72 + c8) = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+#pragma unroll
+    for (int j = 0; j < NV_AQ; ++j) {
+      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      *(uint4*)(Aq + r * 72 + c8) = ra[j];
     }
-    for (int idx = tid; idx < 64 * (VS / 8); idx += 128) {
-      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
-      uint4 z = make_uint4(0, 0, 0, 0);
-      if (r < len) z = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + vs0 + c8);
-      *(uint4*)(dos + r * LS + c8) = z;
+    if (tid < 64 * (VS / 8)) {
+      int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
+      *(uint4*)(dos + r * LS + c8) = rdo;
     }
-    for (int c = tid; c < DK; c += 128) egl[c] = __expf(G[(cbase + 63) * DK + c]);
+    if (tid < DK) egl[tid] = __expf(rg);
     // gradient wrt the state after this chunk, for the per-chunk kernels
-    for (int idx = tid; idx < DK * (VS / 8); idx += 128) {
+    for (int idx = tid; idx < DK * (VS / 8); idx += NTHR) {
       int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
       *(uint4*)(dS_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(dSb + r * LS + c8);
     }
     __syncthreads();
+    if (chunk - 1 >= c_begin) fetch(chunk - 1);
     // dv_new = Aqk^T do + kg dS
+    const int rt = warp % 4, nt0 = warp / 4;
     {
-      const int rt = warp;
-#pragma unroll
-      for (int nt = 0; nt < VS / 16; ++nt) {
-        FragC acc; wmma::fill_fragment(acc, 0.f);
-        for (int kt = rt; kt < 4; ++kt) {           // Aqk lower triangular -> Aqk^T upper
-          FragAT a; FragB b;
-          wmma::load_matrix_sync(a, Aq + kt * 16 * 72 + rt * 16, 72);
-          wmma::load_matrix_sync(b, dos + kt * 16 * LS + nt * 16, LS);
-          wmma::mma_sync(acc, a, b, acc);
-        }
-#pragma unroll
-        for (int kt = 0; kt < DK / 16; ++kt) {
-          FragA a; FragB b;
-          wmma::load_matrix_sync(a, kgs + rt * 16 * LD + kt * 16, LD);
-          wmma::load_matrix_sync(b, dSb + kt * 16 * LS + nt * 16, LS);
-          wmma::mma_sync(acc, a, b, acc);
-        }
-        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      FragC acc; wmma::fill_fragment(acc, 0.f);
+      for (int kt = rt; kt < 4; ++kt) {           // Aqk lower triangular -> Aqk^T upper
+        FragAT a; FragB b;
+        wmma::load_matrix_sync(a, Aq + kt * 16 * 72 + rt * 16, 72);
+        wmma::load_matrix_sync(b, dos + kt * 16 * LS + nt0 * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
       }
+#pragma unroll
+      for (int kt = 0; kt < DK / 16; ++kt) {
+        FragA a; FragB b;
+        wmma::load_matrix_sync(a, kgs + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, dSb + kt * 16 * LS + nt0 * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      wmma::store_matrix_sync(stg + rt * 16 * LF + nt0 * 16, acc, LF, wmma::mem_row_major);
       __syncwarp();
-      for (int el = lane; el < 16 * VS; el += 32) {
-        int rr = rt * 16 + el / VS, cc = el % VS;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = rt * 16 + (el >> 4), cc = nt0 * 16 + (el & 15);
         float dv = stg[rr * LF + cc];
         dvn_out[(cbase + rr) * DK + vs0 + cc] = __float2bfloat16(dv);
         ndv[rr * LS + cc] = __float2bfloat16(-dv);
       }
     }
-    for (int idx = tid; idx < DK * VS; idx += 128) {
-      int r = idx / VS, c = idx % VS;
-      dS[r * LF + c] *= egl[r];
-    }
-    __syncthreads();
-    // dS <- e^Glast dS + qg^T do - w^T dv_new
-    for (int t = warp; t < (DK / 16) * (VS / 16); t += 4) {
+    __syncthreads();                              // ndv complete, dSb no longer read
+    // dS <- e^Glast dS + qg^T do - w^T dv_new   (each warp owns its tiles)
+    for (int t = warp; t < (DK / 16) * (VS / 16); t += 8) {
       const int mt = t / (VS / 16), nt = t % (VS / 16);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = mt * 16 + (el >> 4), cc = nt * 16 + (el & 15);
+        dS[rr * LF + cc] *= egl[rr];
+      }
+      __syncwarp();
       FragC acc;
       wmma::load_matrix_sync(acc, dS + mt * 16 * LF + nt * 16, LF, wmma::mem_row_major);
 #pragma unroll
@@ -134,16 +159,17 @@ kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, co
         wmma::mma_sync(acc, a, b, acc);
       }
       wmma::store_matrix_sync(dS + mt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
-    }
-    __syncthreads();
-    for (int idx = tid; idx < DK * VS; idx += 128) {
-      int r = idx / VS, c = idx % VS;
-      dSb[r * LS + c] = __float2bfloat16(dS[r * LF + c]);
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = mt * 16 + (el >> 4), cc = nt * 16 + (el & 15);
+        dSb[rr * LS + cc] = __float2bfloat16(dS[rr * LF + cc]);
+      }
     }
     __syncthreads();
   }
   if (dh0) {
-    for (int idx = tid; idx < DK * VS; idx += 128) {
+    for (int idx = tid; idx < DK * VS; idx += NTHR) {
       int r = idx / VS, c = idx % VS;
       dh0[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] = dS[r * LF + c];
     }
@@ -665,7 +691,7 @@ template <int DK>
 static int launch_bwd(const void* q, const void* k, const void* v, const float* beta, const float* G, const void* w,
                       const void* qg, const void* kg, const void* Aqk, const void* Ainv, const void* Akk,
                       const void* vnew, const void* Sst, const void* d_o, const float* dfinal, const int* cs,
-                      const int* cl, const int* sc, int NC, int N, int H, void* dvn, void* dSst, void* dw, void* dAqk,
+                      const int* cl, const int* sc, const int* so, int NC, int N, int H, void* dvn, void* dSst, void* dw, void* dAqk,
                       void* dKK, void* dbk, float* dq_acc, float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv,
                       float* dg, float* dbeta, float* dh0, cudaStream_t s) {
   constexpr int VS = 32;
@@ -683,8 +709,8 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
     once = true;
   }
   if (NC == 0) return 0;
-  k3<<<dim3(DK / VS, H, N), 128, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
-      (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
+  k3<<<dim3(DK / VS, H, N), 256, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
+      (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, so, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
   k4a<<<dim3(NC, H), 512, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
       (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc, dG_acc,
       (bf16*)dw, (bf16*)dAqk);
@@ -698,12 +724,12 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
 extern "C" int hippo_kda_bwd(const void* q, const void* k, const void* v, const float* beta, const float* G,
                              const void* w, const void* qg, const void* kg, const void* Aqk, const void* Ainv,
                              const void* Akk, const void* vnew, const void* Sst, const void* d_o, const float* dfinal,
-                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, int NC, int N, int H,
-                             int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, void* dbk, float* dq_acc,
+                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, const int* seq_order,
+                             int NC, int N, int H, int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, void* dbk, float* dq_acc,
                              float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg, float* dbeta,
                              float* dh0, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
-  if (DK == 64) return launch_bwd<64>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, seq_order, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
+  if (DK == 64) return launch_bwd<64>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, seq_order, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);
   return -1;
 }

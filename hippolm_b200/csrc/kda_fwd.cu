@@ -252,15 +252,20 @@ constexpr int kda_intra_smem() {
 }
 
 // ---------------------------------------------------------------------------------------------------
+// 256 threads. The tiles of chunk n+1 are fetched into registers while chunk n is computed, so the global
+// load latency is off the sequential critical path (the chain over chunks is what bounds this kernel).
 template <int DK, int VS>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(256, 2)
 kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ qg,
                      const bf16* __restrict__ kg, const bf16* __restrict__ Aqk, const float* __restrict__ G,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
-                     const int* __restrict__ seq_chunk, int H, const float* __restrict__ h0,
-                     bf16* __restrict__ vnew_out, bf16* __restrict__ S_out, bf16* __restrict__ o,
-                     float* __restrict__ final_state) {
-  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4;
+                     const int* __restrict__ seq_chunk, const int* __restrict__ seq_order, int H,
+                     const float* __restrict__ h0, bf16* __restrict__ vnew_out, bf16* __restrict__ S_out,
+                     bf16* __restrict__ o, float* __restrict__ final_state) {
+  constexpr int LD = DK + 8, LS = VS + 8, LF = VS + 4, NTHR = 256;
+  constexpr int NV_BIG = 64 * (DK / 8) / NTHR;          // uint4 per thread for one [64, DK] tile
+  constexpr int NV_AQ = 64 * 8 / NTHR;                   // Aqk tile
+  static_assert(64 * (VS / 8) <= NTHR && DK <= NTHR, "tile/thread mapping");
   extern __shared__ __align__(128) uint8_t smem[];
   float* S = (float*)smem;                    // [DK][LF]
   float* stg = S + DK * LF;                   // [64][LF]
@@ -272,64 +277,85 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
   bf16* vns = kgs + 64 * LD;                  // [64][LS]
   bf16* Aq = vns + 64 * LS;                   // [64][72]
 
-  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = blockIdx.z;
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
 
-  for (int idx = tid; idx < DK * VS; idx += 128) {
+  for (int idx = tid; idx < DK * VS; idx += NTHR) {
     int r = idx / VS, c = idx % VS;
     float s0 = h0 ? h0[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] : 0.f;
     S[r * LF + c] = s0;
     Sb[r * LS + c] = __float2bfloat16(s0);
   }
+  uint4 rw[NV_BIG], rq[NV_BIG], rk[NV_BIG], ra[NV_AQ], ru;
+  float rg = 0.f;
+  auto fetch = [&](int chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+#pragma unroll
+    for (int j = 0; j < NV_BIG; ++j) {
+      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      long long off = (cbase + r) * DK + c8;
+      rw[j] = *(const uint4*)(w + off); rq[j] = *(const uint4*)(qg + off); rk[j] = *(const uint4*)(kg + off);
+    }
+#pragma unroll
+    for (int j = 0; j < NV_AQ; ++j) {
+      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      ra[j] = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+    }
+    if (tid < 64 * (VS / 8)) {
+      int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
+      ru = *(const uint4*)(u + (cbase + r) * DK + vs0 + c8);
+    }
+    if (tid < DK) rg = G[(cbase + 63) * DK + tid];
+  };
+  if (c_begin < c_end) fetch(c_begin);
   __syncthreads();
 
   for (int chunk = c_begin; chunk < c_end; ++chunk) {
     const long long cbase = ((long long)chunk * H + h) * 64;
     const int t0 = chunk_start[chunk], len = chunk_len[chunk];
-    for (int idx = tid; idx < 64 * (DK / 8); idx += 128) {
-      int r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
-      long long off = (cbase + r) * DK + c8;
-      *(uint4*)(ws + r * LD + c8) = *(const uint4*)(w + off);
-      *(uint4*)(qgs + r * LD + c8) = *(const uint4*)(qg + off);
-      *(uint4*)(kgs + r * LD + c8) = *(const uint4*)(kg + off);
+    // registers -> shared tiles
+#pragma unroll
+    for (int j = 0; j < NV_BIG; ++j) {
+      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+      *(uint4*)(ws + r * LD + c8) = rw[j]; *(uint4*)(qgs + r * LD + c8) = rq[j]; *(uint4*)(kgs + r * LD + c8) = rk[j];
     }
-    for (int idx = tid; idx < 64 * 8; idx += 128) {
-      int r = idx >> 3, c8 = (idx & 7) * 8;
-      *(uint4*)(Aq + r * 72 + c8) = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+#pragma unroll
+    for (int j = 0; j < NV_AQ; ++j) {
+      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      *(uint4*)(Aq + r * 72 + c8) = ra[j];
     }
-    for (int idx = tid; idx < 64 * (VS / 8); idx += 128) {
-      int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
-      *(uint4*)(vns + r * LS + c8) = *(const uint4*)(u + (cbase + r) * DK + vs0 + c8);
+    if (tid < 64 * (VS / 8)) {
+      int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
+      *(uint4*)(vns + r * LS + c8) = ru;
     }
-    for (int c = tid; c < DK; c += 128) egl[c] = __expf(G[(cbase + 63) * DK + c]);
+    if (tid < DK) egl[tid] = __expf(rg);
     // state at chunk start, for the backward pass
-    for (int idx = tid; idx < DK * (VS / 8); idx += 128) {
+    for (int idx = tid; idx < DK * (VS / 8); idx += NTHR) {
       int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
       *(uint4*)(S_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(Sb + r * LS + c8);
     }
     __syncthreads();
+    if (chunk + 1 < c_end) fetch(chunk + 1);              // in flight during the math below
 
-    // P = w S ; v_new = u - P      (warp r owns rows 16r..16r+15)
+    // P = w S ; v_new = u - P      (8 warps: 4 row tiles x VS/16 column tiles)
+    const int rt = warp % 4, nt0 = warp / 4;              // VS/16 == 2 column tiles
     {
-      const int rt = warp;
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
 #pragma unroll
-      for (int nt = 0; nt < VS / 16; ++nt) {
-        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-        wmma::fill_fragment(acc, 0.f);
-#pragma unroll
-        for (int kt = 0; kt < DK / 16; ++kt) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-          wmma::load_matrix_sync(a, ws + rt * 16 * LD + kt * 16, LD);
-          wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt * 16, LS);
-          wmma::mma_sync(acc, a, b, acc);
-        }
-        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      for (int kt = 0; kt < DK / 16; ++kt) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+        wmma::load_matrix_sync(a, ws + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt0 * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
       }
+      wmma::store_matrix_sync(stg + rt * 16 * LF + nt0 * 16, acc, LF, wmma::mem_row_major);
       __syncwarp();
-      for (int el = lane; el < 16 * VS; el += 32) {
-        int rr = rt * 16 + el / VS, cc = el % VS;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = rt * 16 + (el >> 4), cc = nt0 * 16 + (el & 15);
         float vn = __bfloat162float(vns[rr * LS + cc]) - stg[rr * LF + cc];
         bf16 vb = __float2bfloat16(vn);
         vns[rr * LS + cc] = vb;
@@ -339,42 +365,41 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
     __syncthreads();
     // o = qg S + Aqk v_new
     {
-      const int rt = warp;
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
 #pragma unroll
-      for (int nt = 0; nt < VS / 16; ++nt) {
-        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-        wmma::fill_fragment(acc, 0.f);
-#pragma unroll
-        for (int kt = 0; kt < DK / 16; ++kt) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-          wmma::load_matrix_sync(a, qgs + rt * 16 * LD + kt * 16, LD);
-          wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt * 16, LS);
-          wmma::mma_sync(acc, a, b, acc);
-        }
-        for (int kt = 0; kt <= rt; ++kt) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-          wmma::load_matrix_sync(a, Aq + rt * 16 * 72 + kt * 16, 72);
-          wmma::load_matrix_sync(b, vns + kt * 16 * LS + nt * 16, LS);
-          wmma::mma_sync(acc, a, b, acc);
-        }
-        wmma::store_matrix_sync(stg + rt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
+      for (int kt = 0; kt < DK / 16; ++kt) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+        wmma::load_matrix_sync(a, qgs + rt * 16 * LD + kt * 16, LD);
+        wmma::load_matrix_sync(b, Sb + kt * 16 * LS + nt0 * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
       }
+      for (int kt = 0; kt <= rt; ++kt) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+        wmma::load_matrix_sync(a, Aq + rt * 16 * 72 + kt * 16, 72);
+        wmma::load_matrix_sync(b, vns + kt * 16 * LS + nt0 * 16, LS);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      wmma::store_matrix_sync(stg + rt * 16 * LF + nt0 * 16, acc, LF, wmma::mem_row_major);
       __syncwarp();
-      for (int el = lane; el < 16 * VS; el += 32) {
-        int rr = rt * 16 + el / VS, cc = el % VS;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = rt * 16 + (el >> 4), cc = nt0 * 16 + (el & 15);
         if (rr < len) o[((long long)(t0 + rr) * H + h) * DK + vs0 + cc] = __float2bfloat16(stg[rr * LF + cc]);
       }
     }
-    // S <- e^Glast S + kg^T v_new
-    for (int idx = tid; idx < DK * VS; idx += 128) {
-      int r = idx / VS, c = idx % VS;
-      S[r * LF + c] *= egl[r];
-    }
-    __syncthreads();
-    for (int t = warp; t < (DK / 16) * (VS / 16); t += 4) {
+    __syncthreads();                                       // every warp is done reading Sb
+    // S <- e^Glast S + kg^T v_new   (each warp owns its tiles: scale, accumulate, write S and the bf16 copy)
+    for (int t = warp; t < (DK / 16) * (VS / 16); t += 8) {
       const int mt = t / (VS / 16), nt = t % (VS / 16);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = mt * 16 + (el >> 4), cc = nt * 16 + (el & 15);
+        S[rr * LF + cc] *= egl[rr];
+      }
+      __syncwarp();
       wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
       wmma::load_matrix_sync(acc, S + mt * 16 * LF + nt * 16, LF, wmma::mem_row_major);
 #pragma unroll
@@ -386,16 +411,17 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
         wmma::mma_sync(acc, a, b, acc);
       }
       wmma::store_matrix_sync(S + mt * 16 * LF + nt * 16, acc, LF, wmma::mem_row_major);
-    }
-    __syncthreads();
-    for (int idx = tid; idx < DK * VS; idx += 128) {
-      int r = idx / VS, c = idx % VS;
-      Sb[r * LS + c] = __float2bfloat16(S[r * LF + c]);
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int el = lane * 8 + e, rr = mt * 16 + (el >> 4), cc = nt * 16 + (el & 15);
+        Sb[rr * LS + cc] = __float2bfloat16(S[rr * LF + cc]);
+      }
     }
     __syncthreads();
   }
   if (final_state) {
-    for (int idx = tid; idx < DK * VS; idx += 128) {
+    for (int idx = tid; idx < DK * VS; idx += NTHR) {
       int r = idx / VS, c = idx % VS;
       final_state[(((long long)seq * H + h) * DK + r) * DK + vs0 + c] = S[r * LF + c];
     }
@@ -414,7 +440,7 @@ using namespace hippo;
 
 template <int DK>
 static int launch_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta,
-                      const int* cs, const int* cl, const int* sc, int NC, int N, int H, const float* h0,
+                      const int* cs, const int* cl, const int* sc, const int* so, int NC, int N, int H, const float* h0,
                       float* G, void* w, void* u, void* qg, void* kg, void* Aqk, void* Ainv, void* Akk, void* vnew,
                       void* Sst, void* o, float* fin, cudaStream_t s) {
   constexpr int VS = 32;
@@ -431,8 +457,8 @@ static int launch_fwd(const void* q, const void* k, const void* v, const float* 
   if (NC == 0) return 0;
   k1<<<dim3(NC, H), 512, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
                                                     G, (bf16*)w, (bf16*)u, (bf16*)qg, (bf16*)kg, (bf16*)Aqk, (bf16*)Ainv, (bf16*)Akk);
-  k2<<<dim3(DK / VS, H, N), 128, kda_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
-                                                                (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, H, h0,
+  k2<<<dim3(DK / VS, H, N), 256, kda_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
+                                                                (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, so, H, h0,
                                                                 (bf16*)vnew, (bf16*)Sst, (bf16*)o, fin);
   return (int)cudaGetLastError();
 }
@@ -440,12 +466,12 @@ static int launch_fwd(const void* q, const void* k, const void* v, const float* 
 // q,k,v: [T,H,DK] bf16 (q already scaled, q/k already normalised); g: [T,H,DK] fp32 log decay; beta: [T,H] fp32.
 // chunk tables: chunk_start/len [NC], seq_chunk [N+1]. Workspaces are chunk-padded [NC,H,64,*].
 extern "C" int hippo_kda_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta,
-                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, int NC, int N, int H,
-                             int DK, const float* h0, float* G, void* w, void* u, void* qg, void* kg, void* Aqk,
+                             const int* chunk_start, const int* chunk_len, const int* seq_chunk, const int* seq_order,
+                             int NC, int N, int H, int DK, const float* h0, float* G, void* w, void* u, void* qg, void* kg, void* Aqk,
                              void* Ainv, void* Akk, void* vnew, void* Sst, void* o, float* final_state, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  if (DK == 128) return launch_fwd<128>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
-  if (DK == 64) return launch_fwd<64>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
+  if (DK == 128) return launch_fwd<128>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, seq_order, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
+  if (DK == 64) return launch_fwd<64>(q, k, v, g, beta, chunk_start, chunk_len, seq_chunk, seq_order, NC, N, H, h0, G, w, u, qg, kg, Aqk, Ainv, Akk, vnew, Sst, o, final_state, s);
   return -1;
 }
 
@@ -453,7 +479,8 @@ extern "C" int hippo_kda_fwd(const void* q, const void* k, const void* v, const 
 // Chunk table built on the device (no host sync): chunks never straddle a sequence boundary.
 // cu: [N+1] int32. Outputs padded to nc_max entries; unused chunks get len 0.
 __global__ void kda_build_chunks_kernel(const int* __restrict__ cu, int N, int* __restrict__ chunk_start,
-                                        int* __restrict__ chunk_len, int* __restrict__ seq_chunk, int nc_max) {
+                                        int* __restrict__ chunk_len, int* __restrict__ seq_chunk,
+                                        int* __restrict__ seq_order, int nc_max) {
   __shared__ int total;
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -468,10 +495,20 @@ __global__ void kda_build_chunks_kernel(const int* __restrict__ cu, int N, int* 
       if (c < nc_max) { chunk_start[c] = s; chunk_len[c] = min(64, e - s); }
   }
   for (int c = total + threadIdx.x; c < nc_max; c += blockDim.x) { chunk_start[c] = 0; chunk_len[c] = 0; }
+  // launch order of the sequential state kernels: longest sequence first, so the longest chain starts at time 0
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    const int len_n = cu[n + 1] - cu[n];
+    int rank = 0;
+    for (int m = 0; m < N; ++m) {
+      const int len_m = cu[m + 1] - cu[m];
+      rank += (len_m > len_n) || (len_m == len_n && m < n);
+    }
+    seq_order[rank] = n;
+  }
 }
 
 extern "C" int hippo_kda_build_chunks(const int* cu, int N, int* chunk_start, int* chunk_len, int* seq_chunk,
-                                      int nc_max, void* stream) {
-  kda_build_chunks_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cu, N, chunk_start, chunk_len, seq_chunk, nc_max);
+                                      int* seq_order, int nc_max, void* stream) {
+  kda_build_chunks_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cu, N, chunk_start, chunk_len, seq_chunk, seq_order, nc_max);
   return (int)cudaGetLastError();
 }

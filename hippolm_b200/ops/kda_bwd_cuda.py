@@ -8,7 +8,7 @@ from ._ext import lib, ptr, stream_ptr, check
 
 
 def backward(ctx, do, dfin):
-    q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc = ctx.saved_tensors
+    q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc, so = ctx.saved_tensors
     T, H, DK, NC, N = ctx.dims
     dev = q.device
     do = do.to(torch.bfloat16).contiguous()
@@ -24,7 +24,7 @@ def backward(ctx, do, dfin):
     dbeta = torch.empty((T, H), **f32)
     dh0 = torch.empty((N, H, DK, DK), **f32) if ctx.has_h0 else None
     check(lib().hippo_kda_bwd(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(G), ptr(w), ptr(qg), ptr(kg), ptr(Aqk), ptr(Ainv),
-                              ptr(Akk), ptr(vnew), ptr(Sst), ptr(do), ptr(dfin_c), ptr(cs), ptr(cl), ptr(sc), NC, N, H,
+                              ptr(Akk), ptr(vnew), ptr(Sst), ptr(do), ptr(dfin_c), ptr(cs), ptr(cl), ptr(sc), ptr(so), NC, N, H,
                               DK, ptr(dvn), ptr(dSst), ptr(dw), ptr(dAqk), ptr(dKK), ptr(dbk), ptr(dq_acc), ptr(dk_acc),
                               ptr(dG_acc), ptr(dq), ptr(dk), ptr(dv), ptr(dg), ptr(dbeta), ptr(dh0), stream_ptr()),
           "kda_bwd")

@@ -23,8 +23,10 @@ def chunk_tables(cu_seqlens: torch.Tensor, T: int):
     cs = torch.empty(nc_max, dtype=torch.int32, device=cu.device)
     cl = torch.empty(nc_max, dtype=torch.int32, device=cu.device)
     sc = torch.empty(N + 1, dtype=torch.int32, device=cu.device)
-    check(lib().hippo_kda_build_chunks(ptr(cu), N, ptr(cs), ptr(cl), ptr(sc), nc_max, stream_ptr()), "kda_build_chunks")
-    val = (cs, cl, sc, nc_max, N)
+    so = torch.empty(N, dtype=torch.int32, device=cu.device)
+    check(lib().hippo_kda_build_chunks(ptr(cu), N, ptr(cs), ptr(cl), ptr(sc), ptr(so), nc_max, stream_ptr()),
+          "kda_build_chunks")
+    val = (cs, cl, sc, so, nc_max, N)
     _TABLE_CACHE.update(key=key, val=val, ref=cu_seqlens)
     return val
 
@@ -37,7 +39,7 @@ class _KDAFunction(torch.autograd.Function):
         dev = q.device
         q, k, v = (t.to(torch.bfloat16).contiguous() for t in (q, k, v))
         g, beta = g.float().contiguous(), beta.float().contiguous()
-        cs, cl, sc, NC, N = chunk_tables(cu_seqlens, T)
+        cs, cl, sc, so, NC, N = chunk_tables(cu_seqlens, T)
         bf = dict(dtype=torch.bfloat16, device=dev)
         G = torch.empty((NC, H, 64, DK), dtype=torch.float32, device=dev)
         w, u, qg, kg, vnew = (torch.empty((NC, H, 64, DK), **bf) for _ in range(5))
@@ -46,10 +48,10 @@ class _KDAFunction(torch.autograd.Function):
         o = torch.empty((T, H, DK), **bf)
         fin = torch.empty((N, H, DK, DK), dtype=torch.float32, device=dev)
         h0c = h0.float().contiguous() if h0 is not None else None
-        check(lib().hippo_kda_fwd(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(cs), ptr(cl), ptr(sc), NC, N, H, DK,
+        check(lib().hippo_kda_fwd(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(cs), ptr(cl), ptr(sc), ptr(so), NC, N, H, DK,
                                   ptr(h0c), ptr(G), ptr(w), ptr(u), ptr(qg), ptr(kg), ptr(Aqk), ptr(Ainv), ptr(Akk), ptr(vnew),
                                   ptr(Sst), ptr(o), ptr(fin), stream_ptr()), "kda_fwd")
-        ctx.save_for_backward(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc)
+        ctx.save_for_backward(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc, so)
         ctx.dims = (T, H, DK, NC, N)
         ctx.has_h0 = h0 is not None
         return o, fin

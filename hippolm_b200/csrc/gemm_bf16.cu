@@ -20,6 +20,7 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GEMM_SMEM_RS = 3 * STAGE_BYTES + 4 * 32 * 512 + 1024 + 256;
 
 // Fused collective modes of the same kernel (COMM template parameter):
 //   COMM_AG  all-gather -> GEMM. The first `comm_ctas` CTAs push this rank's row shard of A into every
@@ -78,10 +79,13 @@ struct GemmParams {
 template <bool A_KMAJOR, bool B_KMAJOR, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
-                 const __grid_constant__ CommParams cp) {
+                 const __grid_constant__ CommParams cp, const __grid_constant__ CUtensorMap tmOwn) {
+  // GEMM->RS trades one pipeline stage for a 64 KB epilogue staging area (coalesced 512-byte remote stores)
+  constexpr int NST = (COMM == COMM_RS) ? 3 : STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + 3 * STAGE_BYTES;                 // only used by COMM_RS: 4 warps x [32][512 B]
+  uint64_t* full = (uint64_t*)(smem + ((COMM == COMM_RS) ? 3 * STAGE_BYTES + 4 * 32 * 512 : STAGES * STAGE_BYTES));
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -96,6 +100,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+    if (COMM == COMM_AG) prefetch_tmap(&tmOwn);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -128,20 +133,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   };
 
   if (COMM == COMM_AG && (int)blockIdx.x < cp.comm_ctas) {
-    // ---- copy role: push the local shard to every rank (own first), then bump that rank's counter
+    // ---- copy role: the shard travels in 128-row blocks; each block goes to every rank (own first, then rank+1,
+    // ...) and bumps that rank's counter for (this source, this block), so consumers can start on the first
+    // blocks of a remote shard while the rest is still in flight.
     const long long row_bytes = (long long)p.K * 2;
     const long long vec_per_row = row_bytes / 16;
-    const long long nvec = (long long)cp.rows_per_shard * vec_per_row;
-    for (int i = 0; i < cp.world; ++i) {
-      const int peer = (cp.rank + i) % cp.world;
-      uint4* dst = (uint4*)((uint8_t*)cp.buf_peer[peer] + (long long)cp.rank * cp.rows_per_shard * row_bytes);
-      for (long long v = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; v < nvec; v += (long long)cp.comm_ctas * GEMM_THREADS) {
-        const long long r = v / vec_per_row, c = v % vec_per_row;
-        dst[v] = *((const uint4*)((const uint8_t*)cp.x_local + r * cp.x_ld * 2) + c);
+    const int bps = cp.rows_per_shard / BM;                  // blocks per shard
+    const long long nvec = (long long)BM * vec_per_row;      // vectors per block
+    // remote pushes only: own tiles read x_local in place (tmOwn); a caller that needs the complete gathered
+    // buffer afterwards copies its own rows in with a plain device copy
+    for (int pass = 0; pass < 1; ++pass) {
+      for (int rb = blockIdx.x; rb < bps; rb += cp.comm_ctas) {
+        const uint8_t* src = (const uint8_t*)cp.x_local + (long long)rb * BM * cp.x_ld * 2;
+        for (int i = (pass == 0 ? 1 : 0); i < (pass == 0 ? cp.world : 1); ++i) {
+          const int peer = (cp.rank + i) % cp.world;
+          uint4* dst = (uint4*)((uint8_t*)cp.buf_peer[peer] + ((long long)cp.rank * cp.rows_per_shard + (long long)rb * BM) * row_bytes);
+          // 8 independent 16-byte loads in flight per thread before the stores (memory-level parallelism)
+          for (long long v0 = threadIdx.x; v0 < nvec; v0 += (long long)GEMM_THREADS * 8) {
+            uint4 tmp[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const long long v = v0 + (long long)j * GEMM_THREADS;
+              if (v < nvec) { const long long r = v / vec_per_row, c = v % vec_per_row; tmp[j] = __ldg((const uint4*)(src + r * cp.x_ld * 2) + c); }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const long long v = v0 + (long long)j * GEMM_THREADS;
+              if (v < nvec) dst[v] = tmp[j];
+            }
+          }
+          if (pass == 0) {
+            __threadfence_system();
+            __syncthreads();
+            if (threadIdx.x == 0) red_release_sys_add(cp.flag_peer[peer] + cp.rank * bps + rb, 1u);
+          }
+        }
       }
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0) red_release_sys_add(cp.flag_peer[peer] + cp.rank, 1u);
     }
   } else
 
@@ -149,25 +176,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      uint32_t seen = 0;
+      int last_tm = -1;
       for (int t = bid; t < num_tiles && ok; t += n_gemm_ctas) {
         int tm, tn; tile_coord(t, tm, tn);
-        if (COMM == COMM_AG) {
-          const int shard = (tm * BM) / cp.rows_per_shard;
-          if (!((seen >> shard) & 1u)) {
-            ok = wait_counter(cp.flag_peer[cp.rank] + shard, cp.target, cp.wait_cycles, shard);
+        const int own_lo = cp.rank * (cp.rows_per_shard / BM), own_hi = own_lo + cp.rows_per_shard / BM;
+        const bool own_tile = (COMM == COMM_AG) && tm >= own_lo && tm < own_hi;
+        if (COMM == COMM_AG && !own_tile) {
+          if (tm != last_tm) {                               // one acquire per new row block (tm is block-indexed)
+            ok = wait_counter(cp.flag_peer[cp.rank] + tm, cp.target, cp.wait_cycles, tm);
             asm volatile("fence.proxy.async;" ::: "memory");     // remote generic-proxy writes -> TMA reads
-            seen |= 1u << shard;
+            last_tm = tm;
             if (!ok) break;
           }
         }
         for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
-          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          int s = it % NST; uint32_t ph = (it / NST) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
           if (!ok) break;
           uint8_t* sa = smem + s * STAGE_BYTES; uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full[s], STAGE_BYTES);
-          if (A_KMAJOR) {
+          if (COMM == COMM_AG && own_tile) {
+            tma_load_2d(sa, &tmOwn, &full[s], kb * BK, (tm - own_lo) * BM);
+          } else if (A_KMAJOR) {
             tma_load_2d(sa, &tmA, &full[s], kb * BK, tm * BM);
           } else {
 #pragma unroll
@@ -194,7 +224,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          int s = it % NST; uint32_t ph = (it / NST) & 1;
           ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
           if (!ok) break;
           tc_fence_after();
@@ -223,6 +253,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      if (COMM == COMM_RS) {
+        // partial tile -> staging slot [this rank] of the rank that owns these rows. The warp first lays its
+        // 32 x 256 slab out in shared memory, then every store instruction writes one contiguous 512-byte row.
+        uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 512);          // [32 rows][32 x 16 B]
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * p.alpha, __uint_as_float(r[j + 2 * e + 1]) * p.alpha);
+            const int piece = (c + j) / 8;                                   // 16-byte piece within the row
+            slab[lane * 32 + (piece ^ (lane & 31))] = v;                     // xor swizzle: conflict-free both ways
+          }
+        }
+        __syncwarp();
+        const int row_base = tm * BM + q * 32;
+        const int owner = row_base / cp.rows_per_shard;
+        const int ncols = min(BN, p.N - tn * BN);                            // multiple of 8
+        __nv_bfloat16* dst0 = (__nv_bfloat16*)cp.buf_peer[owner] +
+                              ((long long)cp.rank * cp.rows_per_shard + (row_base - owner * cp.rows_per_shard)) * p.N + tn * BN;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; ++rr) {
+          if (row_base + rr < p.M && lane * 8 < ncols)
+            *(uint4*)(dst0 + (long long)rr * p.N + lane * 8) = slab[rr * 32 + (lane ^ (rr & 31))];
+        }
+        __syncwarp();
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -314,19 +377,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const long long nvec = (long long)cp.rows_per_shard * p.N / 8;
     const uint4* stage = (const uint4*)cp.buf_peer[cp.rank];
     uint4* out = (uint4*)cp.out_local;
-    for (long long v = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; v < nvec; v += (long long)gridDim.x * GEMM_THREADS) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long stride = (long long)gridDim.x * GEMM_THREADS;
+    for (long long v0 = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; v0 < nvec; v0 += stride * 4) {
+      float acc[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
       for (int sidx = 0; sidx < cp.world; ++sidx) {
-        uint4 x = __ldcg(stage + (long long)sidx * nvec + v);      // written by another GPU: bypass L1
-        const __nv_bfloat162* xb = (const __nv_bfloat162*)&x;
+        uint4 x[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(xb[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+        for (int j = 0; j < 4; ++j) {                        // 4 independent loads in flight per source
+          const long long v = v0 + j * stride;
+          x[j] = v < nvec ? __ldcg(stage + (long long)sidx * nvec + v) : make_uint4(0, 0, 0, 0);   // written by another GPU: bypass L1
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162* xb = (const __nv_bfloat162*)&x[j];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(xb[e]); acc[j][2 * e] += f.x; acc[j][2 * e + 1] += f.y; }
+        }
       }
-      uint4 o;
-      __nv_bfloat162* ob = (__nv_bfloat162*)&o;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-      out[v] = o;
+      for (int j = 0; j < 4; ++j) {
+        const long long v = v0 + j * stride;
+        if (v < nvec) {
+          uint4 o;
+          __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[j][2 * e], acc[j][2 * e + 1]);
+          out[v] = o;
+        }
+      }
     }
   }
 }
@@ -360,14 +442,20 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (COMM == COMM_AG) grid = sms;                                    // copy CTAs + GEMM CTAs, all co-resident
   else if (COMM == COMM_RS) grid = tiles < sms ? tiles : sms;
   else grid = tiles < sms ? tiles : sms;
+  CUtensorMap tmOwn = tmA;
+  if (COMM == COMM_AG) {
+    rc = make_tmap_2d(&tmOwn, cp.x_local, (uint64_t)K, (uint64_t)cp.rows_per_shard, (uint64_t)cp.x_ld * 2, BK, BM, 2, true);
+    if (rc) return rc;
+  }
   auto kern = gemm_bf16_kernel<AK, BK_, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         COMM == COMM_RS ? GEMM_SMEM_RS : GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, p, cp);
+  kern<<<grid, GEMM_THREADS, COMM == COMM_RS ? GEMM_SMEM_RS : GEMM_SMEM, stream>>>(tmA, tmB, p, cp, tmOwn);
   return (int)cudaGetLastError();
 }
 
@@ -395,7 +483,7 @@ extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int
 // All-gather -> GEMM.  x_local: [rows_per_shard, K] bf16 (pitch x_ld). xg_ptrs[r]: rank r's gathered buffer
 // [world*rows_per_shard, K] (peer-mapped symmetric memory, own entry = local). flag_ptrs[r]: rank r's counters
 // [world]. Computes C[world*rows_per_shard, N] = gathered(x) * op(B); layout 0: B stored [N, K]; 1: B stored [K, N].
-// `target` = number of calls made on these counters (this one included) * comm_ctas.
+// flag_ptrs[r]: rank r's counters [world * rows_per_shard/128]; `target` = number of calls made on them (this one included).
 extern "C" int hippo_allgather_gemm_bf16(const void* x_local, long long x_ld, void* const* xg_ptrs,
                                          void* const* flag_ptrs, int world, int rank, int rows_per_shard,
                                          const void* B, long long ldb, void* C, long long ldc, int N, int K, int layout,

@@ -36,9 +36,9 @@ def teardown() -> None:
     _STATE["ws"] = None
 
 
-def allgather_gemm(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False
+def allgather_gemm(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False, need_gathered: bool = True
                    ) -> Tuple[torch.Tensor, torch.Tensor]:
-    return _STATE["ws"].allgather_gemm(x, weight, transpose_w)
+    return _STATE["ws"].allgather_gemm(x, weight, transpose_w, need_gathered)
 
 
 def gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False) -> torch.Tensor:

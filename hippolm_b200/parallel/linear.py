@@ -31,7 +31,7 @@ class _ColumnLinearSP(torch.autograd.Function):
         f = _fused()
         if f is not None and x.is_cuda and m.tp > 1 and f.fits(x.shape[0], x.shape[0] * m.tp, x.shape[1]) \
                 and weight.shape[0] % 8 == 0 and x.dtype == torch.bfloat16:
-            xg, y = f.allgather_gemm(x, weight)
+            xg, y = f.allgather_gemm(x, weight, need_gathered=False)
         else:
             xg = all_gather_dim0(x, m.tp_group, m.tp)
             y = ops.gemm_nt(xg, weight)

@@ -5,7 +5,8 @@ over the TP group); the kernels in ``csrc/gemm_bf16.cu`` only see raw peer point
 
   gathered[parity]   [T, Kmax] bf16 on every rank   target of the all-gather pushes (AG -> GEMM)
   staging[parity]    [world][T/world, Nmax] bf16     per-source partial tiles (GEMM -> RS)
-  counters           uint32 [4][world]               monotonic arrival counters, one row per (op, parity)
+  counters           uint32 [4][1024]                monotonic arrival counters, one row per (op, parity); AG: one per
+                                                     (source rank, 128-row block), RS: one per source rank
 
 A rank can run at most one fused op ahead of its slowest peer (each op needs data from every peer), so
 two parities per op type are enough to keep a fast rank's pushes out of a buffer a slow rank still reads.
@@ -30,6 +31,8 @@ def _ptr_arr(ptrs) -> C.Array:
 
 
 class FusedWorkspace:
+    FLAG_ROW = 1024          # counters per (op, parity) row: world * row blocks per shard <= 1024
+
     def __init__(self, mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, comm_ctas: int = 16,
                  wait_cycles: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
@@ -50,7 +53,7 @@ class FusedWorkspace:
 
         self.gathered = [alloc(nbytes) for _ in range(2)]
         self.staging = [alloc(nbytes) for _ in range(2)]
-        self.flags_t, self.flag_ptrs = alloc(4 * 64 * 4)
+        self.flags_t, self.flag_ptrs = alloc(4 * self.FLAG_ROW * 4)
         self.flags_t.zero_()
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
@@ -59,17 +62,18 @@ class FusedWorkspace:
         self.rs_n = 0
 
     def _row_ptrs(self, row: int) -> List[int]:
-        return [p + row * 64 * 4 for p in self.flag_ptrs]
+        return [p + row * self.FLAG_ROW * 4 for p in self.flag_ptrs]
 
     # ------------------------------------------------------------------ all-gather -> GEMM
-    def allgather_gemm(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False
-                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    def allgather_gemm(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False,
+                       need_gathered: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
         """x: [T/w, K] -> (gathered x [T, K] (a view of the workspace, valid until the next-but-one call),
         y [T, N]) with y = gather(x) @ W^T (W: [N, K]) or gather(x) @ W (W: [K, N], transpose_w)."""
         rows, K = x.shape
         N = weight.shape[1] if transpose_w else weight.shape[0]
         T = rows * self.world
         assert rows % _BM == 0 and T * K <= self.max_tokens * self.max_width, "workspace too small / ragged shard"
+        assert T // _BM <= self.FLAG_ROW
         x = x.contiguous()
         weight = weight.contiguous()
         par = self.ag_n & 1
@@ -81,9 +85,12 @@ class FusedWorkspace:
         check(lib().hippo_allgather_gemm_bf16(ptr(x), C.c_longlong(x.stride(0)), _ptr_arr(ptrs), _ptr_arr(self._row_ptrs(row)),
                                               self.world, self.rank, rows, ptr(weight), C.c_longlong(weight.stride(0)),
                                               ptr(y), C.c_longlong(N), N, K, 1 if transpose_w else 0, self.comm_ctas,
-                                              C.c_uint(self.calls[row] * self.comm_ctas),
+                                              C.c_uint(self.calls[row]),
                                               C.c_longlong(self.wait_cycles), stream_ptr()), "allgather_gemm")
         xg = buf[:T * K * 2].view(torch.bfloat16).view(T, K)
+        if need_gathered:
+            # the kernel reads the own shard in place; complete the gathered view for later users (dW GEMM)
+            xg[self.rank * rows:(self.rank + 1) * rows].copy_(x)
         return xg, y
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter

@@ -32,11 +32,11 @@ def test_bounded_wait_reports_and_returns():
     xs = (C.c_void_p * 2)(xg0.data_ptr(), xg1.data_ptr())
     fs = (C.c_void_p * 2)(f0.data_ptr(), f1.data_ptr())
     rc = lib().hippo_allgather_gemm_bf16(ptr(x), C.c_longlong(K), xs, fs, 2, 0, rows, ptr(w), C.c_longlong(K), ptr(y),
-                                         C.c_longlong(N), N, K, 0, 4, C.c_uint(4), C.c_longlong(2_000_000), stream_ptr())
+                                         C.c_longlong(N), N, K, 0, 4, C.c_uint(1), C.c_longlong(2_000_000), stream_ptr())
     assert rc == 0
     torch.cuda.synchronize()                     # returns: the wait on shard 1 ran out after ~1 ms
     st = _ext.device_status()
-    assert st[0] == 5 and st[1] == 1, st         # kWaitPeerFlag on source shard 1
+    assert st[0] == 5 and st[1] == 1, st         # kWaitPeerFlag on row block 1 (first block of the absent source)
     ref = x.float() @ w.float().t()
     assert (y[:rows].float() - ref).abs().max() < 0.05 * ref.abs().max()     # own shard was still computed
     _ext.clear_device_status()

@@ -25,9 +25,10 @@ typedef wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> FragBT
 typedef wmma::fragment<wmma::accumulator, 16, 16, 16, float> FragC;
 
 // =================================================================================================== state
-// 256 threads; the tiles of the next (earlier) chunk are fetched into registers during the math of the current one.
+// 256 threads, one CTA per SM; the tiles of the next (earlier) chunk stream into the second shared-memory buffer
+// with cp.async during the math of the current one.
 template <int DK, int VS>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 1)
 kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, const bf16* __restrict__ kg,
                      const bf16* __restrict__ Aqk, const float* __restrict__ G, const bf16* __restrict__ d_o,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
@@ -42,12 +43,9 @@ kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, co
   float* stg = dS + DK * LF;                  // [64][LF]
   float* egl = stg + 64 * LF;                 // [DK]
   bf16* dSb = (bf16*)(egl + DK);              // [DK][LS]
-  bf16* ws = dSb + DK * LS;                   // [64][LD]
-  bf16* qgs = ws + 64 * LD;
-  bf16* kgs = qgs + 64 * LD;
-  bf16* dos = kgs + 64 * LD;                  // [64][LS]
-  bf16* ndv = dos + 64 * LS;                  // [64][LS]  (-dv_new)
-  bf16* Aq = ndv + 64 * LS;                   // [64][72]
+  bf16* ndv = dSb + DK * LS;                  // [64][LS]  (-dv_new)
+  bf16* tiles = ndv + 64 * LS;                // 2 x { w, qg, kg: [64][LD] ; Aqk: [64][72] ; do: [64][LS] ; Glast: DK floats }
+  constexpr int TILE_ELEMS = 3 * 64 * LD + 64 * 72 + 64 * LS + 2 * DK;
 
   const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -59,56 +57,49 @@ kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, co
     dS[r * LF + c] = s0;
     dSb[r * LS + c] = __float2bfloat16(s0);
   }
-  uint4 rw[NV_BIG], rq[NV_BIG], rk[NV_BIG], ra[NV_AQ], rdo;
-  float rg = 0.f;
-  auto fetch = [&](int chunk) {
+  auto fetch = [&](int chunk, int buf) {
     const long long cbase = ((long long)chunk * H + h) * 64;
     const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+    bf16* tb = tiles + buf * TILE_ELEMS;
+    bf16* ws_ = tb; bf16* qgs_ = ws_ + 64 * LD; bf16* kgs_ = qgs_ + 64 * LD; bf16* Aq_ = kgs_ + 64 * LD;
+    bf16* dos_ = Aq_ + 64 * 72; float* gl_ = (float*)(dos_ + 64 * LS);
 #pragma unroll
     for (int j = 0; j < NV_BIG; ++j) {
       int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
       long long off = (cbase + r) * DK + c8;
-      rw[j] = *(const uint4*)(w + off); rq[j] = *(const uint4*)(qg + off); rk[j] = *(const uint4*)(kg + off);
+      cp_async16(ws_ + r * LD + c8, w + off); cp_async16(qgs_ + r * LD + c8, qg + off); cp_async16(kgs_ + r * LD + c8, kg + off);
     }
 #pragma unroll
     for (int j = 0; j < NV_AQ; ++j) {
       int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
-      ra[j] = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+      cp_async16(Aq_ + r * 72 + c8, Aqk + (cbase + r) * 64 + c8);
     }
     if (tid < 64 * (VS / 8)) {
       int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
-      rdo = make_uint4(0, 0, 0, 0);
-      if (r < len) rdo = *(const uint4*)(d_o + ((long long)(t0 + r) * H + h) * DK + vs0 + c8);
+      const bool ok = r < len;                               // rows past the chunk end read as zeros
+      cp_async16(dos_ + r * LS + c8, d_o + ((long long)(t0 + (ok ? r : 0)) * H + h) * DK + vs0 + c8, ok ? 16 : 0);
     }
-    if (tid < DK) rg = G[(cbase + 63) * DK + tid];
+    if (tid < DK / 4) cp_async16(gl_ + tid * 4, G + (cbase + 63) * DK + tid * 4);
+    cp_async_commit();
   };
-  if (c_begin < c_end) fetch(c_end - 1);
+  if (c_begin < c_end) fetch(c_end - 1, 0);
   __syncthreads();
 
   for (int chunk = c_end - 1; chunk >= c_begin; --chunk) {
     const long long cbase = ((long long)chunk * H + h) * 64;
-#pragma unroll
-    for (int j = 0; j < NV_BIG; ++j) {
-      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
-      *(uint4*)(ws + r * LD + c8) = rw[j]; *(uint4*)(qgs + r * LD + c8) = rq[j]; *(uint4*)(kgs + r * LD + c8) = rk[j];
-    }
-#pragma unroll
-    for (int j = 0; j < NV_AQ; ++j) {
-      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
-      *(uint4*)(Aq + r * 72 + c8) = ra[j];
-    }
-    if (tid < 64 * (VS / 8)) {
-      int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
-      *(uint4*)(dos + r * LS + c8) = rdo;
-    }
-    if (tid < DK) egl[tid] = __expf(rg);
+    const int buf = (c_end - 1 - chunk) & 1;
+    bf16* ws = tiles + buf * TILE_ELEMS; bf16* qgs = ws + 64 * LD; bf16* kgs = qgs + 64 * LD; bf16* Aq = kgs + 64 * LD;
+    bf16* dos = Aq + 64 * 72; const float* gl = (const float*)(dos + 64 * LS);
+    cp_async_wait_all();
+    __syncthreads();                                        // this chunk's tiles have landed; the other buffer is free
+    if (chunk - 1 >= c_begin) fetch(chunk - 1, buf ^ 1);
+    if (tid < DK) egl[tid] = __expf(gl[tid]);
     // gradient wrt the state after this chunk, for the per-chunk kernels
     for (int idx = tid; idx < DK * (VS / 8); idx += NTHR) {
       int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
       *(uint4*)(dS_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(dSb + r * LS + c8);
     }
     __syncthreads();
-    if (chunk - 1 >= c_begin) fetch(chunk - 1);
     // dv_new = Aqk^T do + kg dS
     const int rt = warp % 4, nt0 = warp / 4;
     {
@@ -177,8 +168,8 @@ kda_bwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, co
 }
 template <int DK, int VS>
 constexpr int kda_bwd_state_smem() {
-  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 3 * 64 * (DK + 8) * 2 +
-         2 * 64 * (VS + 8) * 2 + 64 * 72 * 2 + 128;
+  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 64 * (VS + 8) * 2 +
+         2 * (3 * 64 * (DK + 8) + 64 * 72 + 64 * (VS + 8) + 2 * DK) * 2 + 128;
 }
 
 // =================================================================================================== dqkw

@@ -252,10 +252,11 @@ constexpr int kda_intra_smem() {
 }
 
 // ---------------------------------------------------------------------------------------------------
-// 256 threads. The tiles of chunk n+1 are fetched into registers while chunk n is computed, so the global
-// load latency is off the sequential critical path (the chain over chunks is what bounds this kernel).
+// 256 threads, one CTA per SM. The tiles of chunk n+1 stream into the second shared-memory buffer with cp.async
+// while chunk n is computed, so the global load latency is off the sequential critical path (the chain over
+// chunks is what bounds this kernel).
 template <int DK, int VS>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 1)
 kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ qg,
                      const bf16* __restrict__ kg, const bf16* __restrict__ Aqk, const float* __restrict__ G,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
@@ -271,11 +272,9 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
   float* stg = S + DK * LF;                   // [64][LF]
   float* egl = stg + 64 * LF;                 // [DK]
   bf16* Sb = (bf16*)(egl + DK);               // [DK][LS]
-  bf16* ws = Sb + DK * LS;                    // [64][LD]
-  bf16* qgs = ws + 64 * LD;
-  bf16* kgs = qgs + 64 * LD;
-  bf16* vns = kgs + 64 * LD;                  // [64][LS]
-  bf16* Aq = vns + 64 * LS;                   // [64][72]
+  bf16* vns = Sb + DK * LS;                   // [64][LS]
+  bf16* tiles = vns + 64 * LS;                // 2 x { w, qg, kg: [64][LD] ; Aqk: [64][72] ; u: [64][LS] ; Glast: DK floats }
+  constexpr int TILE_ELEMS = 3 * 64 * LD + 64 * 72 + 64 * LS + 2 * DK;
 
   const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -287,56 +286,52 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
     S[r * LF + c] = s0;
     Sb[r * LS + c] = __float2bfloat16(s0);
   }
-  uint4 rw[NV_BIG], rq[NV_BIG], rk[NV_BIG], ra[NV_AQ], ru;
-  float rg = 0.f;
-  auto fetch = [&](int chunk) {
+  auto fetch = [&](int chunk, int buf) {
     const long long cbase = ((long long)chunk * H + h) * 64;
+    bf16* tb = tiles + buf * TILE_ELEMS;
+    bf16* ws_ = tb; bf16* qgs_ = ws_ + 64 * LD; bf16* kgs_ = qgs_ + 64 * LD; bf16* Aq_ = kgs_ + 64 * LD;
+    bf16* us_ = Aq_ + 64 * 72; float* gl_ = (float*)(us_ + 64 * LS);
 #pragma unroll
     for (int j = 0; j < NV_BIG; ++j) {
       int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
       long long off = (cbase + r) * DK + c8;
-      rw[j] = *(const uint4*)(w + off); rq[j] = *(const uint4*)(qg + off); rk[j] = *(const uint4*)(kg + off);
+      cp_async16(ws_ + r * LD + c8, w + off); cp_async16(qgs_ + r * LD + c8, qg + off); cp_async16(kgs_ + r * LD + c8, kg + off);
     }
 #pragma unroll
     for (int j = 0; j < NV_AQ; ++j) {
       int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
-      ra[j] = *(const uint4*)(Aqk + (cbase + r) * 64 + c8);
+      cp_async16(Aq_ + r * 72 + c8, Aqk + (cbase + r) * 64 + c8);
     }
     if (tid < 64 * (VS / 8)) {
       int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
-      ru = *(const uint4*)(u + (cbase + r) * DK + vs0 + c8);
+      cp_async16(us_ + r * LS + c8, u + (cbase + r) * DK + vs0 + c8);
     }
-    if (tid < DK) rg = G[(cbase + 63) * DK + tid];
+    if (tid < DK / 4) cp_async16(gl_ + tid * 4, G + (cbase + 63) * DK + tid * 4);
+    cp_async_commit();
   };
-  if (c_begin < c_end) fetch(c_begin);
+  if (c_begin < c_end) fetch(c_begin, 0);
   __syncthreads();
 
   for (int chunk = c_begin; chunk < c_end; ++chunk) {
     const long long cbase = ((long long)chunk * H + h) * 64;
     const int t0 = chunk_start[chunk], len = chunk_len[chunk];
-    // registers -> shared tiles
-#pragma unroll
-    for (int j = 0; j < NV_BIG; ++j) {
-      int idx = tid + j * NTHR, r = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
-      *(uint4*)(ws + r * LD + c8) = rw[j]; *(uint4*)(qgs + r * LD + c8) = rq[j]; *(uint4*)(kgs + r * LD + c8) = rk[j];
-    }
-#pragma unroll
-    for (int j = 0; j < NV_AQ; ++j) {
-      int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
-      *(uint4*)(Aq + r * 72 + c8) = ra[j];
-    }
+    const int buf = (chunk - c_begin) & 1;
+    bf16* ws = tiles + buf * TILE_ELEMS; bf16* qgs = ws + 64 * LD; bf16* kgs = qgs + 64 * LD; bf16* Aq = kgs + 64 * LD;
+    bf16* us = Aq + 64 * 72; const float* gl = (const float*)(us + 64 * LS);
+    cp_async_wait_all();
+    __syncthreads();                                        // this chunk's tiles have landed; the other buffer is free
+    if (chunk + 1 < c_end) fetch(chunk + 1, buf ^ 1);       // in flight during the math below
     if (tid < 64 * (VS / 8)) {
       int r = tid / (VS / 8), c8 = (tid % (VS / 8)) * 8;
-      *(uint4*)(vns + r * LS + c8) = ru;
+      *(uint4*)(vns + r * LS + c8) = *(const uint4*)(us + r * LS + c8);
     }
-    if (tid < DK) egl[tid] = __expf(rg);
+    if (tid < DK) egl[tid] = __expf(gl[tid]);
     // state at chunk start, for the backward pass
     for (int idx = tid; idx < DK * (VS / 8); idx += NTHR) {
       int r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
       *(uint4*)(S_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(Sb + r * LS + c8);
     }
     __syncthreads();
-    if (chunk + 1 < c_end) fetch(chunk + 1);              // in flight during the math below
 
     // P = w S ; v_new = u - P      (8 warps: 4 row tiles x VS/16 column tiles)
     const int rt = warp % 4, nt0 = warp / 4;              // VS/16 == 2 column tiles
@@ -430,8 +425,8 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
 
 template <int DK, int VS>
 constexpr int kda_state_smem() {
-  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 3 * 64 * (DK + 8) * 2 +
-         64 * (VS + 8) * 2 + 64 * 72 * 2 + 128;
+  return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 64 * (VS + 8) * 2 +
+         2 * (3 * 64 * (DK + 8) + 64 * 72 + 64 * (VS + 8) + 2 * DK) * 2 + 128;
 }
 
 }  // namespace hippo

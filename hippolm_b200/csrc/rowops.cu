@@ -524,3 +524,73 @@ extern "C" int hippo_rmsnorm_bwd_noalloc(const void* x, const void* w, const voi
   colsum_kernel<<<(D + 255) / 256, 256, 0, ST(s)>>>(part, dw, nblocks, D);
   RET();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Depthwise causal short convolution (width W <= 8) + SiLU over a packed token stream, with the taps
+// reset at document starts (pos_in_doc[t] = position of token t inside its document).
+//   y[t, d] = silu( sum_w weight[d, w] * x[t - (W-1) + w, d]  (taps with t - (W-1) + w before the doc start are 0) )
+// Replaces fla/modules/conv/triton/kernels.py:36-153 (causal_conv1d fwd/bwd) for the use_short_conv option.
+namespace hippo {
+__global__ void short_conv_fwd_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                                      const int* __restrict__ pos, bf16* __restrict__ y, long long T, int D, int W) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * D) return;
+  long long t = idx / D; int d = (int)(idx % D);
+  int p = pos[t];
+  float acc = 0.f;
+  for (int wi = 0; wi < W; ++wi) {
+    int shift = W - 1 - wi;
+    if (p >= shift) acc += __bfloat162float(w[d * W + wi]) * __bfloat162float(x[(t - shift) * ldx + d]);
+  }
+  y[idx] = __float2bfloat16(acc * sigmoidf_(acc));
+}
+// dx[t, d] = sum_w weight[d, w] * dpre[t + (W-1) - w, d] for targets inside the same document;
+// dw[d, w] += sum_t dpre[t, d] * x[t - (W-1) + w, d].  dpre = dy * silu'(pre), pre recomputed.
+__global__ void short_conv_bwd_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                                      const int* __restrict__ pos, const bf16* __restrict__ dy, bf16* __restrict__ dx,
+                                      long long lddx, float* __restrict__ dw, long long T, int D, int W) {
+  // one thread per channel d, grid-stride over token ranges (blockIdx.y); dpre of the last W-1 tokens is recomputed
+  int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float wv[8], dwacc[8];
+  for (int i = 0; i < W; ++i) { wv[i] = __bfloat162float(w[d * W + i]); dwacc[i] = 0.f; }
+  const long long per = (T + gridDim.y - 1) / gridDim.y;
+  const long long t_lo = (long long)blockIdx.y * per, t_hi = t_lo + per < T ? t_lo + per : T;
+  auto dpre_at = [&](long long t) -> float {
+    int p = pos[t];
+    float pre = 0.f;
+    for (int wi = 0; wi < W; ++wi) { int sh = W - 1 - wi; if (p >= sh) pre += wv[wi] * __bfloat162float(x[(t - sh) * ldx + d]); }
+    float s = sigmoidf_(pre);
+    return __bfloat162float(dy[t * D + d]) * s * (1.f + pre * (1.f - s));
+  };
+  for (long long t = t_lo; t < t_hi; ++t) {
+    // gradient wrt x[t]: contributions of outputs t .. t+W-1 that lie in the same document
+    float g = 0.f;
+    for (int sh = 0; sh < W; ++sh) {
+      long long to = t + sh;
+      if (to < T && pos[to] >= sh) g += wv[W - 1 - sh] * dpre_at(to);
+    }
+    dx[t * lddx + d] = __float2bfloat16(g);
+    // weight gradient from output t
+    float dp = dpre_at(t);
+    int p = pos[t];
+    for (int wi = 0; wi < W; ++wi) { int sh = W - 1 - wi; if (p >= sh) dwacc[wi] += dp * __bfloat162float(x[(t - sh) * ldx + d]); }
+  }
+  for (int i = 0; i < W; ++i) atomicAdd(&dw[d * W + i], dwacc[i]);
+}
+}  // namespace hippo
+
+extern "C" int hippo_short_conv_fwd(const void* x, long long ldx, const void* w, const int* pos, void* y, long long T,
+                                    int D, int W, void* s) {
+  if (W > 8) return -1;
+  long long n = T * D;
+  hippo::short_conv_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (bf16*)y, T, D, W);
+  RET();
+}
+extern "C" int hippo_short_conv_bwd(const void* x, long long ldx, const void* w, const int* pos, const void* dy, void* dx,
+                                    long long lddx, float* dw, long long T, int D, int W, void* s) {
+  if (W > 8) return -1;
+  dim3 grid((D + 127) / 128, (unsigned)(T < 64 ? 1 : (T / 64 > 512 ? 512 : T / 64)));
+  hippo::short_conv_bwd_kernel<<<grid, 128, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (const bf16*)dy, (bf16*)dx, lddx, dw, T, D, W);
+  RET();
+}

@@ -232,6 +232,42 @@ def rope(q, k, positions, theta):
     return _Rope.apply(q, pos, theta), _Rope.apply(k, pos, theta)
 
 
+class _ShortConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, pos):
+        T, D = x.shape
+        W = weight.shape[1]
+        xb = _bf(x)
+        if xb.stride(1) != 1:
+            xb = xb.contiguous()
+        wb = _bf(weight).contiguous()
+        y = torch.empty((T, D), dtype=torch.bfloat16, device=x.device)
+        check(lib().hippo_short_conv_fwd(ptr(xb), _c.c_longlong(xb.stride(0)), ptr(wb), ptr(pos), ptr(y), _c.c_longlong(T),
+                                         D, W, stream_ptr()), "short_conv_fwd")
+        ctx.save_for_backward(xb, wb, pos)
+        ctx.wdtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, wb, pos = ctx.saved_tensors
+        T, D = dy.shape
+        W = wb.shape[1]
+        dy = _bf(dy).contiguous()
+        dx = torch.empty((T, D), dtype=torch.bfloat16, device=dy.device)
+        dw = torch.zeros((D, W), dtype=torch.float32, device=dy.device)
+        check(lib().hippo_short_conv_bwd(ptr(xb), _c.c_longlong(xb.stride(0)), ptr(wb), ptr(pos), ptr(dy), ptr(dx),
+                                         _c.c_longlong(D), ptr(dw), _c.c_longlong(T), D, W, stream_ptr()), "short_conv_bwd")
+        return dx, dw.to(ctx.wdtype), None
+
+
+def short_conv_silu(x, weight, bias, cu_seqlens):
+    assert bias is None, "conv_bias is not supported on the CUDA path"
+    from ..ref.ops import positions_from_cu
+    pos = positions_from_cu(cu_seqlens, x.shape[0], x.device).to(torch.int32).contiguous()
+    return _ShortConv.apply(x, weight, pos)
+
+
 # ----------------------------------------------------------------------------- attention / KDA / AttnRes
 class _KDAPrologue(torch.autograd.Function):
     @staticmethod

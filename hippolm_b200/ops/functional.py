@@ -102,6 +102,8 @@ def gated_rmsnorm(o, gate, weight, eps: float):
 
 
 def short_conv_silu(x, weight, bias, cu_seqlens):
+    if x.is_cuda and bias is None and weight.shape[1] <= 8:
+        return _cu().short_conv_silu(x, weight, bias, cu_seqlens)
     return _rk.short_conv_silu(x, weight, bias, cu_seqlens)
 
 

@@ -77,3 +77,18 @@ def test_rope():
     qf = q.detach().float().requires_grad_(True)
     ro.apply_rope(qf, cos, sin).backward(dq.float())
     _close(q.grad, qf.grad, 1e-2)
+
+
+def test_short_conv_silu_varlen():
+    from hippolm_b200 import ops
+    from hippolm_b200.ref import kda as rk
+    T, D, W = 300, 256, 4
+    proj = torch.randn(T, 3 * D, device="cuda").bfloat16()
+    x = proj[:, D:2 * D].detach().requires_grad_(True)          # strided view, as in the model
+    w = (0.5 * torch.randn(D, W, device="cuda")).bfloat16().requires_grad_(True)
+    cu = torch.tensor([0, 1, 50, 51, 52, 300], dtype=torch.int32, device="cuda")
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    y = ops.short_conv_silu(x, w, None, cu); y.backward(dy)
+    x2, w2 = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    y2 = rk.short_conv_silu(x2, w2, None, cu); y2.backward(dy.float())
+    _close(y, y2, 1e-2); _close(x.grad, x2.grad, 2e-2); _close(w.grad, w2.grad, 2e-2)

@@ -136,12 +136,18 @@ class Muon:
         if g.dtype not in (torch.bfloat16, torch.float32) or not g.is_contiguous():
             return False
         for (a, b) in segs:
-            if b > a and not mc.supported(b - a, cols):
-                return False
             if full_scope and b > a and self._shard_dim(e, (a, b)) is not None:
                 return False
         for (a, b) in segs:
             if b <= a:
+                continue
+            if not mc.supported(b - a, cols):
+                # tiny / ragged segment (e.g. H/tp beta rows): generic path on this slice only
+                gf = g[a:b].float() * grad_scale
+                m = e.exp_avg[a:b].float().mul_(self.momentum).add_(gf)
+                e.exp_avg[a:b].copy_(m)
+                u = gf.add(m, alpha=self.momentum) if self.nesterov else m
+                self._apply(e, a, b, ops.newton_schulz5(u, self.ns_steps), wd_factor)
                 continue
             u, ssq = mc.momentum_update(g[a:b], e.exp_avg[a:b], self.momentum, grad_scale, self.nesterov)
             o = mc.newton_schulz_(u, ssq, self.ns_steps)

@@ -1,6 +1,7 @@
 #!/usr/bin/env python
 """tcgen05 bf16 GEMM (NT / NN / TN) and block-scaled NVFP4 GEMM throughput against torch.matmul (cuBLAS) and
 the measured peak. Prints one JSON line per shape."""
+import argparse
 import json
 
 import torch
@@ -13,14 +14,36 @@ SHAPES = [(8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384,
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", type=str, default="", help="M,N,K: run only this shape")
+    ap.add_argument("--profile", type=str, default="", help="nt|nn|tn|nvfp4: launch only this kernel a few times (for ncu)")
+    cli = ap.parse_args()
+    shapes = [tuple(int(v) for v in cli.shape.split(","))] if cli.shape else SHAPES
+    if cli.profile:
+        M, N, K = shapes[0]
+        a = torch.randn(M, K, device="cuda").bfloat16(); b = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+        bt, at = b.t().contiguous(), a.t().contiguous()
+        if cli.profile == "nvfp4":
+            xp, xs, xg = nvfp4_cuda.quantize(a); wp, ws, wg = nvfp4_cuda.quantize(b)
+            fn = lambda: fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg)
+        else:
+            fn = {"nt": lambda: co.gemm_nt(a, b), "nn": lambda: co.gemm_nn(a, bt), "tn": lambda: co.gemm_tn(at, bt)}[cli.profile]
+        for _ in range(4):
+            fn()
+        torch.cuda.synchronize()
+        return
     pk = load_measured_peaks()
-    for (M, N, K) in SHAPES:
+    for (M, N, K) in shapes:
         a = torch.randn(M, K, device="cuda").bfloat16(); b = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
         bt, at = b.t().contiguous(), a.t().contiguous()
         fl = 2.0 * M * N * K
         rec = {"M": M, "N": N, "K": K}
         for name, fn in (("nt", lambda: co.gemm_nt(a, b)), ("nn", lambda: co.gemm_nn(a, bt)),
-                         ("tn", lambda: co.gemm_tn(at, bt)), ("cublas", lambda: a @ b.t())):
+                         ("tn", lambda: co.gemm_tn(at, bt)),
+                         ("nt_1sm", lambda: co._gemm(a, b, 0, M, N, K, kernel="1sm")),
+                         ("nn_1sm", lambda: co._gemm(a, bt, 1, M, N, K, kernel="1sm")),
+                         ("tn_1sm", lambda: co._gemm(at, bt, 2, M, N, K, kernel="1sm")),
+                         ("cublas", lambda: a @ b.t())):
             ms = time_ms(fn, flush=False)
             rec[name + "_tflops"] = round(fl / ms / 1e9, 1)
         if K % 256 == 0:

@@ -11,6 +11,7 @@
 // Replaces the reference's cuBLAS calls behind F.linear / torch.mm (qkv_proj, o_proj, FFN, LCE).
 #include "sm100.cuh"
 #include "host_utils.h"
+#include "gemm_params.h"
 
 namespace hippo {
 
@@ -64,17 +65,6 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
   }
   return true;
 }
-
-struct GemmParams {
-  int M, N, K;
-  void* C; long long ldc;
-  int out_fp32;        // 0 = bf16, 1 = fp32
-  int accumulate;      // C += result
-  float alpha;
-  const void* Cin;     // optional bf16 [M, ldcin] addend: C = alpha*A*B + beta*Cin (bf16 output only)
-  long long ldcin; float beta;
-  int tiles_m, tiles_n;
-};
 
 template <bool A_KMAJOR, bool B_KMAJOR, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -462,14 +452,21 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
 }  // namespace hippo
 
 // layout code: 0 = NT (A[M,K], B[N,K]); 1 = NN (A[M,K], B[K,N]); 2 = TN (A[K,M], B[K,N]); 3 = TT (A[K,M], B[N,K])
-extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                               long long ldb, long long ldc, int layout, int out_fp32, int accumulate,
-                               float alpha, int max_ctas, void* stream) {
+static int gemm_bf16_dispatch(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                              long long ldb, long long ldc, int layout, int out_fp32, int accumulate,
+                              float alpha, int max_ctas, void* stream, bool allow_pair) {
   using namespace hippo;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
   if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
   cudaStream_t s = (cudaStream_t)stream;
+  if (allow_pair && M > 128 && layout >= 0 && layout <= 3 && gemm_2sm_enabled()) {
+    // CTA-pair kernel (256x256 tiles over two SMs): half the shared-memory operand traffic per SM
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+    p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta; p.tiles_m = p.tiles_n = 0;
+    return launch_gemm_2sm(A, B, layout, lda, ldb, p, max_ctas, s);
+  }
   CommParams cp = {};
   switch (layout) {
     case 0: return launch_gemm<true, true, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
@@ -478,6 +475,19 @@ extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int
     case 3: return launch_gemm<false, true, COMM_NONE>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32, accumulate, alpha, max_ctas, cp, s);
   }
   return -1;
+}
+
+extern "C" int hippo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, int layout, int out_fp32, int accumulate,
+                               float alpha, int max_ctas, void* stream) {
+  return gemm_bf16_dispatch(A, B, C, M, N, K, lda, ldb, ldc, layout, out_fp32, accumulate, alpha, max_ctas, stream, true);
+}
+
+// The one-CTA kernel regardless of size (tests and benches compare the two kernels).
+extern "C" int hippo_gemm_bf16_1sm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int layout, int out_fp32, int accumulate,
+                                   float alpha, int max_ctas, void* stream) {
+  return gemm_bf16_dispatch(A, B, C, M, N, K, lda, ldb, ldc, layout, out_fp32, accumulate, alpha, max_ctas, stream, false);
 }
 
 // All-gather -> GEMM.  x_local: [rows_per_shard, K] bf16 (pitch x_ld). xg_ptrs[r]: rank r's gathered buffer

@@ -1,0 +1,322 @@
+// CTA-pair bf16 GEMM on tcgen05 tensor cores (sm_100a): two CTAs on neighbouring SMs share one 256x256 tile.
+//
+// A 128x256 one-CTA tile reads 12 KB of operands from shared memory per 128x256x16 MMA, which caps the
+// tensor pipe at the shared-memory bandwidth (~0.8 of peak). With `cta_group::2` each CTA of the pair stages
+// its own 128 rows of A and only HALF of the B tile (128 of the 256 columns); the MMA issued by the leader
+// CTA (cluster rank 0) runs on both SMs, every SM reading 8 KB per step, and the accumulator of the pair is
+// split by rows: rows 0..127 in the leader's TMEM, rows 128..255 in the peer's.
+//
+// Per CTA (192 threads): warp 0 = TMA producer (own A rows, own B half; the completion bytes of both CTAs land
+// on the LEADER's full barrier), warp 1 = MMA issuer (leader only) and TMEM owner, warps 2..5 = epilogue of the
+// CTA's own 128 rows. The leader's MMA thread releases shared-memory stages and publishes accumulators by
+// committing to the barrier of each CTA in turn (two plain commits, no cluster-multicast qualifier anywhere);
+// the peer's epilogue warps hand the accumulator back with a remote mbarrier arrive. 6 stages of 32 KB, two
+// 256-column accumulators. All loads are plain TMA loads of local memory. Every wait is bounded.
+// Replaces the reference's cuBLAS calls behind F.linear / torch.mm (qkv_proj, o_proj, FFN, LCE, Newton-Schulz).
+#include "sm100.cuh"
+#include "host_utils.h"
+#include "gemm_params.h"
+#include <stdlib.h>
+
+namespace hippo {
+namespace sm2 {
+
+constexpr int BM = 128;            // rows per CTA; the pair covers 256
+constexpr int BN = 256;            // columns of the pair tile
+constexpr int BNH = BN / 2;        // columns of B staged by each CTA
+constexpr int BK = 64, UMMA_K = 16, STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) inside CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// plain tiled load into this CTA's shared memory; the completion bytes go to a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // used in the leader only
+  uint64_t* empty = full + STAGES;                             // one per CTA
+  uint64_t* tfull = empty + STAGES;                            // one per CTA
+  uint64_t* tempty = tfull + 2;                                // used in the leader only (8 arrivals)
+  uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int num_tiles = p.tiles_m * p.tiles_n;                 // pair tiles (256 x 256)
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                     // both CTAs' barriers are initialised before any remote arrive
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;  // whole TMEM of the SM: the same address in both CTAs
+
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int GROUP = 8;                  // 8 pair-tiles (2048 rows) share each column sweep
+    int per_group = GROUP * p.tiles_n;
+    int g = t / per_group, r = t % per_group;
+    int gm = min(GROUP, p.tiles_m - g * GROUP);
+    tm = g * GROUP + r % gm;
+    tn = r / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = cid; t < num_tiles && ok; t += n_clusters) {
+        int tm, tn; tile_coord(t, tm, tn);
+        const int row0 = (tm * 2 + (int)rank) * BM;            // this CTA's rows of A / C
+        const int col0 = tn * BN + (int)rank * BNH;            // this CTA's half of the B tile
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          uint8_t* sa = smem + s * STAGE_BYTES; uint8_t* sb = sa + A_BYTES;
+          if (A_KMAJOR) {
+            tma_load_2d_pair(sa, &tmA, bar, kb * BK, row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tmA, bar, row0 + j * 64, kb * BK);
+          }
+          if (B_KMAJOR) {
+            tma_load_2d_pair(sb, &tmB, bar, kb * BK, col0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tmB, bar, col0 + j * 64, kb * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, 1, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
+      int it = 0, tl = 0;
+      bool ok = true;
+      for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
+        int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
+        ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
+          if (!ok) break;
+          tc_fence_after();
+          uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t ad = A_KMAJOR ? make_smem_desc(sa + k * 32, 16, 1024) : make_smem_desc(sa + k * 2048, 8192, 1024);
+            uint64_t bd = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024) : make_smem_desc(sb + k * 2048, 8192, 1024);
+            mma_f16_ss_pair(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&empty[s]);
+          tc_commit_pair(e);                                    // stage free in this CTA ...
+          tc_commit_pair(map_to_cta(e, 1));                     // ... and in the peer
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&tfull[acc]);
+          tc_commit_pair(f);
+          tc_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    int tl = 0;
+    bool ok = true;
+    for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
+      int tm, tn; tile_coord(t, tm, tn);
+      int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
+      ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = (tm * 2 + (int)rank) * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tc_wait_ld();
+        const int col0 = tn * BN + c;
+        if (row < p.M && col0 < p.N) {
+          if (p.out_fp32) {
+            float* crow = (float*)p.C + (long long)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4* dst = (float4*)(crow + j);
+                if (p.accumulate) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                *dst = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += crow[j];
+                crow[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                uint4* dst = (uint4*)(crow + j);
+                if (p.accumulate) {
+                  uint4 o = *dst;
+                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += of.x; f[2 * e + 1] += of.y; }
+                }
+                if (p.Cin) {
+                  uint4 o = *(const uint4*)((const __nv_bfloat16*)p.Cin + (long long)row * p.ldcin + col0 + j);
+                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += p.beta * of.x; f[2 * e + 1] += p.beta * of.y; }
+                }
+                uint4 v;
+                __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                *dst = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(crow[j]);
+                if (p.Cin) v += p.beta * __bfloat162float(((const __nv_bfloat16*)p.Cin)[(long long)row * p.ldcin + col0 + j]);
+                crow[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));   // hand the accumulator back to the leader
+    }
+  }
+  // Neither CTA may leave (or free its TMEM) while the other can still read its shared memory or signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+template <bool AK, bool BK_>
+static int launch(const void* A, const void* B, long long lda, long long ldb, GemmParams p, int max_ctas,
+                  cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (AK) rc = make_tmap_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda * 2, BK, BM, 2, true);
+  else    rc = make_tmap_2d(&tmA, A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda * 2, 64, BK, 2, true);
+  if (rc) return rc;
+  if (BK_) rc = make_tmap_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb * 2, BK, BNH, 2, true);
+  else     rc = make_tmap_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb * 2, 64, BK, 2, true);
+  if (rc) return rc;
+  p.tiles_m = (p.M + 2 * BM - 1) / (2 * BM); p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  int sms = sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  int clusters = sms / 2;
+  if (clusters < 1) clusters = 1;
+  if (tiles < clusters) clusters = tiles;
+  auto kern = gemm_bf16_2sm_kernel<AK, BK_>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  kern<<<2 * clusters, THREADS, SMEM, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace sm2
+
+bool gemm_2sm_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("HIPPO_GEMM_2SM"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
+
+int launch_gemm_2sm(const void* A, const void* B, int layout, long long lda, long long ldb, const GemmParams& p,
+                    int max_ctas, cudaStream_t stream) {
+  switch (layout) {
+    case 0: return sm2::launch<true, true>(A, B, lda, ldb, p, max_ctas, stream);
+    case 1: return sm2::launch<true, false>(A, B, lda, ldb, p, max_ctas, stream);
+    case 2: return sm2::launch<false, false>(A, B, lda, ldb, p, max_ctas, stream);
+    case 3: return sm2::launch<false, true>(A, B, lda, ldb, p, max_ctas, stream);
+  }
+  return -1;
+}
+
+}  // namespace hippo
+
+// Explicit entry point of the CTA-pair kernel (tests and benches compare it with the one-CTA kernel).
+// layout code: 0 = NT (A[M,K], B[N,K]); 1 = NN (A[M,K], B[K,N]); 2 = TN (A[K,M], B[K,N]); 3 = TT (A[K,M], B[N,K])
+extern "C" int hippo_gemm_bf16_2sm(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K,
+                                   long long lda, long long ldb, long long ldc, long long ldcin, int layout,
+                                   int out_fp32, int accumulate, float alpha, float beta, void* stream) {
+  using namespace hippo;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0;
+  return launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
+}

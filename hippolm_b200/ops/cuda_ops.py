@@ -15,7 +15,8 @@ _c = ctypes
 # ----------------------------------------------------------------------------- GEMM
 def _gemm(a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int, K: int,
           out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, accumulate: bool = False,
-          alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+          alpha: float = 1.0, max_ctas: int = 0, kernel: str = "auto") -> torch.Tensor:
+    """kernel: "auto" (CTA-pair kernel for M > 128, else one-CTA), "1sm" or "2sm" (explicit, for tests / benches)."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "bf16 GEMM operands required"
     if a.stride(-1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
         a = a.contiguous()
@@ -23,7 +24,15 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int, K: int,
         b = b.contiguous()
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    rc = lib().hippo_gemm_bf16(ptr(a), ptr(b), ptr(out), M, N, K, _c.c_longlong(a.stride(0)),
+    if kernel == "2sm":
+        rc = lib().hippo_gemm_bf16_2sm(ptr(a), ptr(b), ptr(out), None, M, N, K, _c.c_longlong(a.stride(0)),
+                                       _c.c_longlong(b.stride(0)), _c.c_longlong(out.stride(0)), _c.c_longlong(0),
+                                       layout, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                                       _c.c_float(alpha), _c.c_float(0.0), stream_ptr())
+        check(rc, "hippo_gemm_bf16_2sm")
+        return out
+    fn = lib().hippo_gemm_bf16_1sm if kernel == "1sm" else lib().hippo_gemm_bf16
+    rc = fn(ptr(a), ptr(b), ptr(out), M, N, K, _c.c_longlong(a.stride(0)),
                                _c.c_longlong(b.stride(0)), _c.c_longlong(out.stride(0)), layout,
                                1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
                                _c.c_float(alpha), max_ctas, stream_ptr())

@@ -39,3 +39,29 @@ def test_gemm_fp32_out_and_accumulate():
     co._gemm(a, b, 0, 512, 256, 384, out=out, accumulate=True, alpha=0.5)
     ref = 1.0 + 0.5 * (a.float() @ b.float().t())
     assert (out - ref).abs().max() < 1e-2
+
+
+@pytest.mark.parametrize("kernel", ["1sm", "2sm"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (384, 520, 200), (1000, 264, 136), (2048, 1024, 1024), (4096, 1800, 512)])
+def test_gemm_one_cta_and_cta_pair_kernels(kernel, M, N, K):
+    """Both kernels, named explicitly, against the fp32 product: NT, NN and TN operand layouts, ragged M / N / K."""
+    from hippolm_b200.ops import cuda_ops as co
+    from hippolm_b200.ops import _ext
+    _ext.clear_device_status()
+    g = torch.Generator(device="cuda").manual_seed(3 * M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    bt, at = b.t().contiguous(), a.t().contiguous()
+    ref = _ref(a, bt)
+    tol = 2e-2 * (K ** 0.5)
+    y = co._gemm(a, b, 0, M, N, K, kernel=kernel)
+    assert (y.float() - ref).abs().max() < tol
+    y = co._gemm(a, bt, 1, M, N, K, kernel=kernel)
+    assert (y.float() - ref).abs().max() < tol
+    y = co._gemm(at, bt, 2, M, N, K, kernel=kernel)
+    assert (y.float() - ref).abs().max() < tol
+    out = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    co._gemm(a, b, 0, M, N, K, out=out, accumulate=True, alpha=0.5, kernel=kernel)
+    assert (out - (1.0 + 0.5 * ref)).abs().max() < tol
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0

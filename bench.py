@@ -130,7 +130,9 @@ def main():
                    "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
             return subprocess.call(cmd)
     if a.micro_batch_tokens <= 0:
-        a.micro_batch_tokens = 8192 if world == 1 else 16384
+        # one 8192-token sequence per GPU and micro-batch: activations per rank stay constant under TP + sequence
+        # parallelism, and the per-head KDA state recurrences get `world` sequences to run side by side
+        a.micro_batch_tokens = 8192 * world
     m = dict(MODELS[a.model])
     name = m.pop("name")
     args = build_parser().parse_args([])
@@ -217,7 +219,8 @@ def main():
                "clocks": clocks,
                "e2e": {"value": gb_tokens / (e2e_ms_step / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},
-               "gpu_launches": launches, "loss": last_loss, "device_status": list(st), "impl": "ours"}
+               "gpu_launches": launches, "loss": last_loss,
+               "max_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "device_status": list(st), "impl": "ours"}
         print(json.dumps(rec), flush=True)
     teardown_worker(ctx)
     return 0

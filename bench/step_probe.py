@@ -25,12 +25,19 @@ def main():
     ap.add_argument("--seq_len", type=int, default=8192)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--bf16_ffn", action="store_true")
+    ap.add_argument("--heads", type=int, default=32, help="e.g. 4 = the local heads of one TP=8 rank")
+    ap.add_argument("--ffn", type=int, default=14336, help="e.g. 1792 = the local FFN width of one TP=8 rank")
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--micro", type=int, default=0, help="micro-batch tokens (default: one sequence)")
+    ap.add_argument("--kineto", action="store_true", help="after the timed steps, trace one more step with torch.profiler "
+                    "and print GPU-busy time vs wall time and the top kernels (diagnosis only, not a benchmark number)")
     a = ap.parse_args()
     args = build_parser().parse_args([])
-    args.vocab_size, args.hidden_size, args.num_heads, args.head_dim = 128256, 4096, 32, 128
-    args.num_layers, args.num_blocks, args.intermediate_size = a.layers, max(1, a.layers // 4), 14336
+    args.vocab_size, args.hidden_size, args.num_heads, args.head_dim = a.vocab, 4096, a.heads, 128
+    args.num_layers, args.num_blocks, args.intermediate_size = a.layers, max(1, a.layers // 4), a.ffn
+    args.attn_res_heads = 32
     args.ffn_nvfp4 = args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
-    args.batch_size, args.seq_len, args.micro_batch_size, args.max_steps = a.seqs, a.seq_len, a.seq_len, 10 ** 9
+    args.batch_size, args.seq_len, args.micro_batch_size, args.max_steps = a.seqs, a.seq_len, a.micro or a.seq_len, 10 ** 9
     t0 = time.time()
     loader = synthetic_loader(args.batch_size, args.seq_len, args.vocab_size, 0, a.seq_len, a.seq_len)
     ctx = setup_worker(args, run_dir=None, data_iter=loader)
@@ -47,6 +54,23 @@ def main():
         print(i, "step s", round(time.time() - t0, 3), "loss", round(float(out["loss"]), 4), tm.summary(),
               "launches", _ext.launch_count(), "status", _ext.device_status(), flush=True)
     print("max mem GB", round(torch.cuda.max_memory_allocated() / 2 ** 30, 2))
+    if a.kineto:
+        from torch.profiler import profile, ProfilerActivity
+        torch.cuda.synchronize()
+        t0 = time.time()
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            train_step(ctx, batch)
+            torch.cuda.synchronize()
+        wall = time.time() - t0
+        ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+        busy = sum(e.device_time for e in ev) / 1e3
+        print(f"traced step: wall {wall * 1e3:.1f} ms, sum of GPU kernel time {busy:.1f} ms, kernels {len(ev)}")
+        agg = {}
+        for e in ev:
+            k = e.name.split("<")[0].split("(")[0][:60]
+            c = agg.setdefault(k, [0, 0.0]); c[0] += 1; c[1] += e.device_time / 1e3
+        for k, (c, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:25]:
+            print(f"  {ms:9.2f} ms {c:6d}  {k}")
 
 
 if __name__ == "__main__":

@@ -41,6 +41,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--safe_gate", type=_bool, default=False); a("--lower_bound", type=float, default=-5.0)
     a("--conv_size", type=int, default=4); a("--conv_bias", type=_bool, default=False)
     a("--num_layers", type=int, default=4); a("--num_blocks", type=int, default=1)
+    a("--attn_res_heads", type=int, default=0)
     a("--full_attn_interval", type=int, default=4); a("--rope_theta", type=float, default=10000.0)
     a("--intermediate_size", type=int, default=1024); a("--rms_norm_eps", type=float, default=1e-6)
     a("--ffn_nvfp4", type=_bool, default=False); a("--ffn_nvfp4_marlin", type=_bool, default=False)

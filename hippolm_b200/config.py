@@ -49,6 +49,7 @@ class HippoConfig:
     # depth
     num_layers: int = 4
     num_blocks: int = 1
+    attn_res_heads: int = 0                 # heads of the block-attn-res pseudo-query; 0 = num_heads
     full_attn_interval: int = 4             # layer i is full attention when (i+1) % interval == 0; 0 = all KDA
     rope_theta: float = 10000.0
     # ffn

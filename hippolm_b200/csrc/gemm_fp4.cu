@@ -13,6 +13,9 @@
 // src/models/ops/cuda/marlin_build/sources/marlin/marlin_template.h).
 #include "sm100.cuh"
 #include "host_utils.h"
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
 
 namespace hippo {
 
@@ -22,27 +25,65 @@ constexpr int F_A_BYTES = F_BM * F_BKB, F_B_BYTES = F_BN * F_BKB, F_SF_BYTES = 4
 constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES + 2 * F_SF_BYTES;
 constexpr int F_THREADS = 192;
 constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + 1024 + 256;
+constexpr int F_RS_SLAB_BYTES = 4 * 32 * 256;               // epilogue staging of the reduce-scatter variant
+constexpr int F_SMEM_RS = F_SMEM + F_RS_SLAB_BYTES;
 constexpr int F_TMEM_SF0 = 256;                             // accumulators use columns [0, 256)
 
 struct Fp4Params {
   int M, N, K;                   // K in elements (multiple of 256)
   const uint8_t* sfa;            // tiled scales of A: [ceil(M/128)][K/64][512]
   const uint8_t* sfb;            // tiled scales of B: [ceil(N/128)][K/64][512]
-  const float* gsa; const float* gsb;
+  const float* gsa; const float* gsb;   // F_COMM_AG: gsa points at one tensor scale per source rank
   __nv_bfloat16* C; long long ldc;
   int tiles_m, tiles_n;
+  // F_COMM_AG: A (packed bytes, scale tiles, per-source tensor scales) is this rank's gathered FP4 buffer, filled
+  // shard by shard by every rank's nvfp4_quant_push_kernel; `flags[src * (rows_per_shard/128) + row block]`
+  // reaches `target` once all K slabs of that row block have landed.
+  int world, rank, rows_per_shard;
+  const uint32_t* flags; uint32_t target; long long wait_cycles;
+  // F_COMM_RS: partial tiles go to the staging slot [rank] of the rank that owns the rows, then every rank sums its slots
+  void* stage_peer[8]; uint32_t* rs_flag_peer[8]; uint32_t rs_target; void* out_local;
 };
+
+constexpr int F_COMM_NONE = 0, F_COMM_AG = 1, F_COMM_RS = 2;
+
+__device__ __forceinline__ uint32_t f_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float f_ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void f_red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded spin on a monotonic counter written by other GPUs
+__device__ __forceinline__ bool f_wait_counter(const uint32_t* p, uint32_t target, long long limit, int detail) {
+  if ((int32_t)(f_ld_acquire_sys(p) - target) >= 0) return true;
+  long long t0 = clock64();
+  while ((int32_t)(f_ld_acquire_sys(p) - target) < 0) {
+    if (clock64() - t0 > limit) { report(kWaitPeerFlag, detail); return false; }
+    __nanosleep(64);
+  }
+  return true;
+}
 
 __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+template <int COMM>
 __global__ void __launch_bounds__(F_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp4Params p) {
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ Fp4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + F_STAGES * F_STAGE_BYTES);
+  uint8_t* epi_stage = smem + F_STAGES * F_STAGE_BYTES;      // F_COMM_RS only: 4 warps x [32 rows][256 B]
+  uint64_t* full = (uint64_t*)(smem + F_STAGES * F_STAGE_BYTES + (COMM == F_COMM_RS ? F_RS_SLAB_BYTES : 0));
   uint64_t* empty = full + F_STAGES;
   uint64_t* tfull = empty + F_STAGES;
   uint64_t* tempty = tfull + 2;
@@ -64,20 +105,41 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // grouped rasterisation; with a fused collective the row blocks are walked shard by shard: all-gather in arrival
+  // order (own, rank-1, rank-2, ...), reduce-scatter remote owners first (rank+1, ...), own rows last
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int GROUP = 8;
+    int tiles_m = p.tiles_m, base_m = 0;
+    if (COMM != F_COMM_NONE) {
+      const int tms = p.rows_per_shard / F_BM;
+      const int per_shard = tms * p.tiles_n;
+      const int si = t / per_shard;
+      t -= si * per_shard;
+      const int shard = (COMM == F_COMM_AG) ? (p.rank - si + p.world) % p.world : (p.rank + 1 + si) % p.world;
+      base_m = shard * tms; tiles_m = tms;
+    }
     int per_group = GROUP * p.tiles_n;
     int g = t / per_group, r = t % per_group;
-    int gm = min(GROUP, p.tiles_m - g * GROUP);
-    tm = g * GROUP + r % gm;
+    int gm = min(GROUP, tiles_m - g * GROUP);
+    tm = base_m + g * GROUP + r % gm;
     tn = r / gm;
   };
 
   if (warp == 0) {
     if (lane == 0) {
       int it = 0; bool ok = true;
+      int last_tm = -1;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn; tile_coord(t, tm, tn);
+        if (COMM == F_COMM_AG && tm != last_tm) {
+          const int bps = p.rows_per_shard / F_BM;
+          if (tm / bps != p.rank) {                          // own rows were written by the previous local kernel
+            ok = f_wait_counter(p.flags + tm, p.target, p.wait_cycles, tm);
+            asm volatile("fence.proxy.async;" ::: "memory");  // remote generic-proxy writes -> TMA / bulk reads
+            if (!ok) break;
+          }
+          last_tm = tm;
+        }
         for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
           int s = it % F_STAGES; uint32_t ph = (it / F_STAGES) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
@@ -130,7 +192,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     const int q = warp & 3;
     int tl = 0; bool ok = true;
-    const float alpha = (*p.gsa) * (*p.gsb);
+    float alpha = (COMM == F_COMM_AG) ? 0.f : (*p.gsa) * (*p.gsb);
+    const float gsb = *p.gsb;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
       int tm, tn; tile_coord(t, tm, tn);
       int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
@@ -138,8 +201,47 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+      // the tensor scale of the source shard was pushed before the row block's counter was released
+      if (COMM == F_COMM_AG) alpha = f_ld_relaxed_sys_f32(p.gsa + (tm * F_BM) / p.rows_per_shard) * gsb;
       const int row = tm * F_BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * F_BN + ((uint32_t)(q * 32) << 16);
+      if (COMM == F_COMM_RS) {
+        // The warp lays its 32 x 128 slab out in shared memory (xor-swizzled 16-byte pieces), then each store
+        // instruction writes two contiguous 256-byte rows into the owner's staging slot [this rank].
+        uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 256);
+#pragma unroll 1
+        for (int c = 0; c < F_BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * alpha, __uint_as_float(r[j + 2 * e + 1]) * alpha);
+            const int piece = (c + j) / 8;
+            slab[lane * 16 + (piece ^ (lane & 15))] = v;
+          }
+        }
+        __syncwarp();
+        const int row_base = tm * F_BM + q * 32;
+        const int owner = row_base / p.rows_per_shard;
+        const int ncols = min(F_BN, p.N - tn * F_BN);
+        __nv_bfloat16* dst0 = (__nv_bfloat16*)p.stage_peer[owner] +
+                              ((long long)p.rank * p.rows_per_shard + (row_base - owner * p.rows_per_shard)) * p.N + tn * F_BN;
+        const int pc = lane & 15;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; rr += 2) {
+          const int r2 = rr + (lane >> 4);
+          if (row_base + r2 < p.M && pc * 8 < ncols)
+            *(uint4*)(dst0 + (long long)r2 * p.N + pc * 8) = slab[r2 * 16 + (pc ^ (r2 & 15))];
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) f_red_release_sys_add(p.rs_flag_peer[owner] + p.rank, 1u);
+      } else
 #pragma unroll 1
       for (int c = 0; c < F_BN; c += 32) {
         uint32_t r[32];
@@ -173,6 +275,119 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (COMM == F_COMM_RS) {
+    // reduction of the rows this rank owns: wait (bounded) for every source, then sum the staging slots
+    if ((int)threadIdx.x < p.world)
+      f_wait_counter(p.rs_flag_peer[p.rank] + threadIdx.x, p.rs_target, p.wait_cycles, 100 + threadIdx.x);
+    __syncthreads();
+    const long long nvec = (long long)p.rows_per_shard * p.N / 8;
+    const uint4* stage = (const uint4*)p.stage_peer[p.rank];
+    uint4* out = (uint4*)p.out_local;
+    const long long stride = (long long)gridDim.x * F_THREADS;
+    for (long long v0 = (long long)blockIdx.x * F_THREADS + threadIdx.x; v0 < nvec; v0 += stride * 4) {
+      float acc[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+      for (int sidx = 0; sidx < p.world; ++sidx) {
+        uint4 x[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long v = v0 + j * stride;
+          x[j] = v < nvec ? __ldcg(stage + (long long)sidx * nvec + v) : make_uint4(0, 0, 0, 0);   // written by another GPU: bypass L1
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162* xb = (const __nv_bfloat162*)&x[j];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(xb[e]); acc[j][2 * e] += f.x; acc[j][2 * e + 1] += f.y; }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long v = v0 + j * stride;
+        if (v < nvec) {
+          uint4 o;
+          __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[j][2 * e], acc[j][2 * e + 1]);
+          out[v] = o;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Quantise this rank's activation shard x[rows, K] (bf16) to NVFP4 and push the result straight into every rank's
+// gathered buffer (own rank included): packed bytes at row offset rank*rows, scale bytes already in the 512-byte
+// MMA tile layout, and the shard's tensor scale at slot [rank]. One CTA per (128-row block, 512-column slab): the
+// slab is quantised into shared memory first so that every remote store is a full 16-byte vector, then the CTA
+// releases the (source rank, row block) arrival counter on each destination. The all-gather therefore moves
+// 0.5625 bytes per element instead of 2, and the consumer GEMM (F_COMM_AG) starts on whatever has arrived.
+// Buffer layout on every rank: [T, K/2] packed | [T/128][K/64][512] scale tiles | 8 x fp32 tensor scales.
+struct QuantPushParams {
+  const __nv_bfloat16* x; long long ldx; int rows, K;
+  const float* gs;                 // this shard's tensor scale (device fp32[1])
+  int world, rank;
+  uint8_t* buf_peer[8];
+  uint32_t* flag_peer[8];
+};
+
+__global__ void __launch_bounds__(256)
+nvfp4_quant_push_kernel(const __grid_constant__ QuantPushParams q) {
+  __shared__ __align__(16) uint8_t s_packed[128 * 256];
+  __shared__ __align__(16) uint8_t s_sf[8 * 512];
+  const int tid = threadIdx.x;
+  const int k0 = blockIdx.x * 512, rb = blockIdx.y, row0 = rb * 128;
+  const float gs = *q.gs;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int blk = tid + i * 256, r = blk >> 5, kb = blk & 31;
+    const __nv_bfloat16* src = q.x + (long long)(row0 + r) * q.ldx + k0 + kb * 16;
+    uint4 raw[2] = {__ldg((const uint4*)src), __ldg((const uint4*)src + 1)};
+    const __nv_bfloat162* h2 = (const __nv_bfloat162*)raw;
+    float f[16];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { float2 t = __bfloat1622float2(h2[e]); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
+    float bm = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) bm = fmaxf(bm, fabsf(f[e]));
+    const float sraw = fminf(bm / 6.f / gs, 448.f);
+    const __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+    const float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
+    uint2 outv;
+    uint8_t* ob = (uint8_t*)&outv;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      // division (not reciprocal multiply) keeps ties identical to the stand-alone quantise kernel
+      const float lo = sdec > 0.f ? f[2 * e] / sdec : f[2 * e], hi = sdec > 0.f ? f[2 * e + 1] / sdec : f[2 * e + 1];
+      ob[e] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+    }
+    *(uint2*)(s_packed + r * 256 + kb * 8) = outv;
+    s_sf[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = (uint8_t)s8;
+  }
+  __syncthreads();
+  const long long T = (long long)q.world * q.rows;
+  const long long sf_off = T * (q.K / 2), gs_off = sf_off + T * (q.K / 16);
+  const int bps = q.rows / 128;
+  for (int d = 0; d < q.world; ++d) {
+    const int peer = (q.rank + d) % q.world;
+    uint8_t* base = q.buf_peer[peer];
+    uint8_t* pk = base + ((long long)q.rank * q.rows + row0) * (q.K / 2) + k0 / 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int v = tid + j * 256, r = v >> 4, c = v & 15;
+      *(uint4*)(pk + (long long)r * (q.K / 2) + c * 16) = *(const uint4*)(s_packed + r * 256 + c * 16);
+    }
+    uint8_t* sf = base + sf_off + (((long long)q.rank * q.rows + row0) / 128 * (q.K / 64) + k0 / 64) * 512;
+    *(uint4*)(sf + tid * 16) = *(const uint4*)(s_sf + tid * 16);
+    if (tid == 0) ((float*)(base + gs_off))[q.rank] = gs;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) f_red_release_sys_add(q.flag_peer[peer] + q.rank * bps + rb, 1u);
+  }
 }
 
 // logical e4m3 scales [rows, K/16] -> 512-byte tiles [ceil(rows/128)][K/64][(m%32)*16 + ((m%128)/32)*4 + kg]
@@ -218,10 +433,92 @@ extern "C" int hippo_gemm_nvfp4(const void* A, const void* B, const void* sfa, c
   int grid = tiles < sms ? tiles : sms;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<F_COMM_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  gemm_nvfp4_kernel<<<grid, F_THREADS, F_SMEM, (cudaStream_t)stream>>>(tmA, tmB, p);
+  gemm_nvfp4_kernel<F_COMM_NONE><<<grid, F_THREADS, F_SMEM, (cudaStream_t)stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+// Quantise + push (see nvfp4_quant_push_kernel). x: [rows, K] bf16 with pitch ldx; rows % 128 == 0, K % 512 == 0.
+// buf_ptrs[r] / flag_ptrs[r]: rank r's gathered FP4 buffer and its arrival counters [world * rows/128].
+extern "C" int hippo_nvfp4_quant_push(const void* x, long long ldx, int rows, int K, const float* gs,
+                                      void* const* buf_ptrs, void* const* flag_ptrs, int world, int rank, void* stream) {
+  if (rows <= 0 || rows % 128 || K % 512 || world < 1 || world > 8 || ((uintptr_t)x & 15) || (ldx % 8)) return -2;
+  QuantPushParams q;
+  q.x = (const __nv_bfloat16*)x; q.ldx = ldx; q.rows = rows; q.K = K; q.gs = gs; q.world = world; q.rank = rank;
+  for (int r = 0; r < world; ++r) { q.buf_peer[r] = (uint8_t*)buf_ptrs[r]; q.flag_peer[r] = (uint32_t*)flag_ptrs[r]; }
+  nvfp4_quant_push_kernel<<<dim3(K / 512, rows / 128), 256, 0, (cudaStream_t)stream>>>(q);
+  return (int)cudaGetLastError();
+}
+
+// All-gather -> FP4 GEMM, consumer side: C[world*rows_per_shard, N] = gathered(A) * B^T. `gathered` is this rank's
+// gathered FP4 buffer (layout in nvfp4_quant_push_kernel), `flags` its arrival counters, `target` the counter value
+// that means "this call's slabs have all landed" (calls so far * K/512).
+extern "C" int hippo_allgather_gemm_nvfp4(const void* gathered, const void* flags, int world, int rank,
+                                          int rows_per_shard, const void* B, const void* sfb, const float* gsb, void* C,
+                                          long long ldc, int N, int K, unsigned target, long long wait_cycles,
+                                          void* stream) {
+  if (world < 1 || world > 8 || rows_per_shard % F_BM || K % 512 || (N % 8) || (ldc % 8)) return -2;
+  const int M = world * rows_per_shard;
+  const uint8_t* base = (const uint8_t*)gathered;
+  const long long sf_off = (long long)M * (K / 2), gs_off = sf_off + (long long)M * (K / 16);
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, base, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, F_BKB, F_BM, 1, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, F_BKB, F_BN, 1, true);
+  if (rc) return rc;
+  Fp4Params p = {};
+  p.M = M; p.N = N; p.K = K; p.sfa = base + sf_off; p.sfb = (const uint8_t*)sfb;
+  p.gsa = (const float*)(base + gs_off); p.gsb = gsb; p.C = (__nv_bfloat16*)C; p.ldc = ldc;
+  p.tiles_m = M / F_BM; p.tiles_n = (N + F_BN - 1) / F_BN;
+  p.world = world; p.rank = rank; p.rows_per_shard = rows_per_shard;
+  p.flags = (const uint32_t*)flags; p.target = target; p.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
+  int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+  int grid = tiles < sms ? tiles : sms;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<F_COMM_AG>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  gemm_nvfp4_kernel<F_COMM_AG><<<grid, F_THREADS, F_SMEM, (cudaStream_t)stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+// FP4 GEMM -> reduce-scatter. A: [world*rows_per_shard, K/2] local packed activations (+ tiled scales, tensor scale);
+// partial C tiles go to the staging slot [rank] of the owning rank (stage_ptrs[r]: [world][rows_per_shard, N] bf16 on
+// rank r); every rank then sums its slots into out_local [rows_per_shard, N].
+// `target` = calls so far * (rows_per_shard/128) * ceil(N/128) * 4.
+extern "C" int hippo_gemm_reduce_scatter_nvfp4(const void* A, const void* sfa, const float* gsa, const void* B,
+                                               const void* sfb, const float* gsb, void* const* stage_ptrs,
+                                               void* const* flag_ptrs, int world, int rank, int rows_per_shard,
+                                               void* out_local, int N, int K, unsigned target, long long wait_cycles,
+                                               void* stream) {
+  if (world < 1 || world > 8 || rows_per_shard % F_BM || K % 256 || (N % 8)) return -2;
+  const int M = world * rows_per_shard;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, F_BKB, F_BM, 1, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, F_BKB, F_BN, 1, true);
+  if (rc) return rc;
+  Fp4Params p = {};
+  p.M = M; p.N = N; p.K = K; p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.gsa = gsa; p.gsb = gsb;
+  p.C = nullptr; p.ldc = N;
+  p.tiles_m = M / F_BM; p.tiles_n = (N + F_BN - 1) / F_BN;
+  p.world = world; p.rank = rank; p.rows_per_shard = rows_per_shard;
+  p.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
+  for (int r = 0; r < world; ++r) { p.stage_peer[r] = stage_ptrs[r]; p.rs_flag_peer[r] = (uint32_t*)flag_ptrs[r]; }
+  p.rs_target = target; p.out_local = out_local;
+  int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+  int grid = tiles < sms ? tiles : sms;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<F_COMM_RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_RS);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  gemm_nvfp4_kernel<F_COMM_RS><<<grid, F_THREADS, F_SMEM_RS, (cudaStream_t)stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
 }

@@ -369,6 +369,14 @@ extern "C" int hippo_nvfp4_quantize(const void* x, int is_bf16, long long rows, 
   nvfp4_quant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>(x, is_bf16, nb, gs, (uint8_t*)packed, (uint8_t*)scales);
   RET();
 }
+// gs <- absmax(x)/(6*448) (1 when x is all zero). scratch, gs: device fp32[1]
+extern "C" int hippo_nvfp4_tensor_scale(const void* x, long long n, int is_bf16, float* scratch, float* gs, void* s) {
+  cudaMemsetAsync(scratch, 0, 4, ST(s));
+  unsigned grid = (unsigned)((n + 2047) / 2048); if (grid > 1184) grid = 1184; if (grid == 0) grid = 1;
+  absmax_kernel<<<grid, 256, 0, ST(s)>>>(x, n, is_bf16, scratch);
+  nvfp4_global_scale_kernel<<<1, 1, 0, ST(s)>>>(scratch, gs);
+  RET();
+}
 extern "C" int hippo_nvfp4_dequantize(const void* packed, const void* scales, const float* gs, void* out, int out_bf16,
                                       long long rows, long long K, void* s) {
   long long nb = rows * K / 16;

@@ -28,7 +28,7 @@ from .. import ops
 from ..config import HippoConfig
 from ..parallel.collectives import gather_seq, reduce_scatter_seq, all_reduce_sum, all_gather_dim0, \
     reduce_scatter_dim0
-from ..parallel.linear import column_linear_sp, row_linear_sp
+from ..parallel.linear import column_linear_sp, row_linear_sp, nvfp4_column_linear_sp, nvfp4_row_linear_sp
 from ..parallel.mesh import get_mesh
 from ..ref.ops import positions_from_cu
 from .nvfp4_linear import NVFP4Linear
@@ -292,8 +292,8 @@ class SwiGLU(nn.Module):
 
     def forward(self, h):
         if self.nvfp4:
-            gu = self.gate_up_proj(gather_seq(h))
-            return reduce_scatter_seq(self.down_proj(ops.swiglu(gu)))
+            gu = nvfp4_column_linear_sp(h, self.gate_up_proj)
+            return nvfp4_row_linear_sp(ops.swiglu(gu), self.down_proj)
         gu = column_linear_sp(h, self.gate_up_proj.weight)
         return row_linear_sp(ops.swiglu(gu), self.down_proj.weight)
 
@@ -327,7 +327,7 @@ class BlockAttnRes(nn.Module):
 
     def __init__(self, cfg: HippoConfig, device, dtype):
         super().__init__()
-        H = cfg.num_heads
+        H = cfg.attn_res_heads or cfg.num_heads
         self.query = _mark(nn.Parameter(torch.zeros(H, cfg.hidden_size // H, device=device, dtype=dtype)),
                            "adamw", True)
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)

@@ -92,6 +92,111 @@ class _RowLinearSP(torch.autograd.Function):
         return dx, dw.to(weight.dtype)
 
 
+def _nvfp4_operands(module, weight):
+    """(packed, scales, global_scale) of an NVFP4Linear: its buffers (no master) or the freshly quantised master."""
+    if module.no_master:
+        return module.packed_weight, module.scales, module.global_scale
+    return ops.nvfp4_quantize(weight.detach())
+
+
+class _NVFP4ColumnSP(torch.autograd.Function):
+    """x[T/w, K] --all-gather--> Q(x) dq(W[N/w, K])^T on the FP4 tensor cores. Backward runs in bf16 on the
+    dequantised weight (as the reference's NVFP4 backward, ``src/models/ops/nvfp4_tp.py:61-335``):
+    dX = reduce-scatter(dY dq(W)) fused into the GEMM, dW = dY^T gather(x). ``weight`` is the bf16 master
+    (STE mode) or a dummy anchor (no-master mode, where dW goes to ``module._accumulate_grad``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, module):
+        m = get_mesh()
+        packed, scales, gs = _nvfp4_operands(module, weight)
+        f = _fused()
+        y = None
+        if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
+            y = f.nvfp4_allgather_gemm(x, packed, scales, gs)          # None when the shape is not covered
+        if y is None:
+            xg = all_gather_dim0(x, m.tp_group, m.tp) if m.tp > 1 else x
+            y = ops.nvfp4_linear(xg, packed, scales, gs, act_quant=module.act_quant)
+        ctx.module = module
+        ctx.save_for_backward(x, packed, scales, gs)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, packed, scales, gs = ctx.saved_tensors
+        mod, m = ctx.module, get_mesh()
+        dy = dy.contiguous()
+        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)               # [N/w, K]
+        f = _fused()
+        if m.tp == 1:
+            dx, xg = ops.gemm_nn(dy, w), x
+        else:
+            if f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
+                    and f.fits(dy.shape[0] // m.tp, dy.shape[0], w.shape[1]) and dy.shape[1] % 8 == 0:
+                dx = f.gemm_reduce_scatter(dy, w, transpose_w=True)
+            else:
+                dx = reduce_scatter_dim0(ops.gemm_nn(dy, w), m.tp_group, m.tp)
+            xg = all_gather_dim0(x, m.tp_group, m.tp)
+        dw = ops.gemm_tn(dy, xg)
+        if mod.no_master:
+            mod._accumulate_grad(dw)
+            return dx, None, None
+        return dx, dw.to(mod.weight.dtype), None
+
+
+class _NVFP4RowSP(torch.autograd.Function):
+    """x[T, K/w] -> reduce-scatter(Q(x) dq(W[N, K/w])^T) [T/w, N]; backward in bf16: dY is all-gathered inside
+    the dX GEMM, dW = gather(dY)^T x."""
+
+    @staticmethod
+    def forward(ctx, x, weight, module):
+        m = get_mesh()
+        packed, scales, gs = _nvfp4_operands(module, weight)
+        f = _fused()
+        y = None
+        if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
+            y = f.nvfp4_gemm_reduce_scatter(x, packed, scales, gs)
+        if y is None:
+            y = ops.nvfp4_linear(x, packed, scales, gs, act_quant=module.act_quant)
+            if m.tp > 1:
+                y = reduce_scatter_dim0(y, m.tp_group, m.tp)
+        ctx.module = module
+        ctx.save_for_backward(x, packed, scales, gs)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, packed, scales, gs = ctx.saved_tensors
+        mod, m = ctx.module, get_mesh()
+        dy = dy.contiguous()
+        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)               # [N, K/w]
+        f = _fused()
+        if m.tp == 1:
+            dyg, dx = dy, ops.gemm_nn(dy, w)
+        elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
+                and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and w.shape[1] % 8 == 0:
+            dyg, dx = f.allgather_gemm(dy, w, transpose_w=True)
+        else:
+            dyg = all_gather_dim0(dy, m.tp_group, m.tp)
+            dx = ops.gemm_nn(dyg, w)
+        dw = ops.gemm_tn(dyg, x)
+        if mod.no_master:
+            mod._accumulate_grad(dw)
+            return dx, None, None
+        return dx, dw.to(mod.weight.dtype), None
+
+
+def _nvfp4_weight_arg(module):
+    return module._anchor.requires_grad_(False) if module.no_master else module.weight
+
+
+def nvfp4_column_linear_sp(x: torch.Tensor, module):
+    return _NVFP4ColumnSP.apply(x, _nvfp4_weight_arg(module), module)
+
+
+def nvfp4_row_linear_sp(x: torch.Tensor, module):
+    return _NVFP4RowSP.apply(x, _nvfp4_weight_arg(module), module)
+
+
 def column_linear_sp(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
     return _ColumnLinearSP.apply(x, weight, bias)
 

@@ -5,7 +5,8 @@ over the TP group); the kernels in ``csrc/gemm_bf16.cu`` only see raw peer point
 
   gathered[parity]   [T, Kmax] bf16 on every rank   target of the all-gather pushes (AG -> GEMM)
   staging[parity]    [world][T/world, Nmax] bf16     per-source partial tiles (GEMM -> RS)
-  counters           uint32 [4][1024]                monotonic arrival counters, one row per (op, parity); AG: one per
+  gathered_fp4[par]  NVFP4 bytes + scale tiles      target of the quantise-and-push kernel (FP4 AG -> GEMM)
+  counters           uint32 [6][1024]                monotonic arrival counters, one row per (op, parity); AG: one per
                                                      (source rank, 128-row block), RS: one per source rank
 
 A rank can run at most one fused op ahead of its slowest peer (each op needs data from every peer), so
@@ -32,6 +33,7 @@ def _ptr_arr(ptrs) -> C.Array:
 
 class FusedWorkspace:
     FLAG_ROW = 1024          # counters per (op, parity) row: world * row blocks per shard <= 1024
+    N_ROWS = 6
 
     def __init__(self, mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, comm_ctas: int = 16,
                  wait_cycles: int = 0):
@@ -53,16 +55,38 @@ class FusedWorkspace:
 
         self.gathered = [alloc(nbytes) for _ in range(2)]
         self.staging = [alloc(nbytes) for _ in range(2)]
-        self.flags_t, self.flag_ptrs = alloc(4 * self.FLAG_ROW * 4)
+        # NVFP4 gathered activations: [T, K/2] packed | [T/128][K/64][512] scale tiles | 8 tensor scales
+        self.gathered_fp4 = [alloc(max_tokens * max_width * 9 // 16 + 256) for _ in range(2)]
+        self.flags_t, self.flag_ptrs = alloc(self.N_ROWS * self.FLAG_ROW * 4)
         self.flags_t.zero_()
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
-        self.calls = [0, 0, 0, 0]          # per counter row: AG parity 0/1, RS parity 0/1
+        self._group = group
+        # per counter row (bf16 AG parity 0/1, RS parity 0/1, FP4 AG parity 0/1): the value every counter of the row
+        # reaches once all calls made so far have completed, and the row-block count those calls used
+        self.targets = [0] * self.N_ROWS
+        self.row_blocks = [0] * self.N_ROWS
         self.ag_n = 0
         self.rs_n = 0
+        self.fp4_n = 0
 
     def _row_ptrs(self, row: int) -> List[int]:
         return [p + row * self.FLAG_ROW * 4 for p in self.flag_ptrs]
+
+    def _use_row(self, row: int, blocks: int, increment: int) -> int:
+        """Book one call on a counter row and return its target. Every counter of a row must see the same
+        increments, so a call that indexes the row differently (another row-block count) first drains the
+        group and restarts the row from zero; all ranks take this branch at the same call."""
+        if self.row_blocks[row] not in (0, blocks):
+            torch.cuda.synchronize(self.mesh.device)
+            dist.barrier(group=self._group)
+            self.flags_t.view(torch.int32).view(self.N_ROWS, self.FLAG_ROW)[row].zero_()
+            torch.cuda.synchronize(self.mesh.device)
+            dist.barrier(group=self._group)
+            self.targets[row] = 0
+        self.row_blocks[row] = blocks
+        self.targets[row] = (self.targets[row] + increment) & 0xFFFFFFFF     # the kernels compare modulo 2^32
+        return self.targets[row]
 
     # ------------------------------------------------------------------ all-gather -> GEMM
     def allgather_gemm(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False,
@@ -79,13 +103,13 @@ class FusedWorkspace:
         par = self.ag_n & 1
         self.ag_n += 1
         row = par
-        self.calls[row] += 1
+        target = self._use_row(row, rows // _BM, 1)
         buf, ptrs = self.gathered[par]
         y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
         check(lib().hippo_allgather_gemm_bf16(ptr(x), C.c_longlong(x.stride(0)), _ptr_arr(ptrs), _ptr_arr(self._row_ptrs(row)),
                                               self.world, self.rank, rows, ptr(weight), C.c_longlong(weight.stride(0)),
                                               ptr(y), C.c_longlong(N), N, K, 1 if transpose_w else 0, self.comm_ctas,
-                                              C.c_uint(self.calls[row]),
+                                              C.c_uint(target),
                                               C.c_longlong(self.wait_cycles), stream_ptr()), "allgather_gemm")
         xg = buf[:T * K * 2].view(torch.bfloat16).view(T, K)
         if need_gathered:
@@ -104,15 +128,76 @@ class FusedWorkspace:
         par = self.rs_n & 1
         self.rs_n += 1
         row = 2 + par
-        self.calls[row] += 1
         _, ptrs = self.staging[par]
         out = torch.empty((rows, N), dtype=torch.bfloat16, device=x.device)
         tiles = (rows // _BM) * ((N + _BN - 1) // _BN)
+        target = self._use_row(row, 1, tiles * 4)
         check(lib().hippo_gemm_reduce_scatter_bf16(ptr(x), C.c_longlong(x.stride(0)), ptr(weight),
                                                    C.c_longlong(weight.stride(0)), _ptr_arr(ptrs),
                                                    _ptr_arr(self._row_ptrs(row)), self.world, self.rank, rows, ptr(out),
-                                                   N, K, 1 if transpose_w else 0, C.c_uint(self.calls[row] * tiles * 4),
+                                                   N, K, 1 if transpose_w else 0, C.c_uint(target),
                                                    C.c_longlong(self.wait_cycles), stream_ptr()), "gemm_reduce_scatter")
+        return out
+
+    # ------------------------------------------------------------------ NVFP4: quantise + push -> FP4 GEMM
+    def nvfp4_allgather_gemm(self, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
+                             global_scale: torch.Tensor) -> Optional[torch.Tensor]:
+        """x: [T/w, K] bf16 -> Q(gather(x)) dq(W)^T [T, N]. Each rank quantises its shard with its own tensor scale and
+        pushes 0.5625 bytes per element to every peer; the GEMM applies the source rank's scale per row block."""
+        from ..ops import fp4_gemm
+        rows, K = x.shape
+        N = packed.shape[0]
+        T = rows * self.world
+        if rows % _BM or K % 512 or N % 8 or x.dtype != torch.bfloat16 or T * K > self.max_tokens * self.max_width \
+                or T // _BM > self.FLAG_ROW:
+            return None
+        x = x.contiguous()
+        par = self.fp4_n & 1
+        self.fp4_n += 1
+        row = 4 + par
+        target = self._use_row(row, rows // _BM, K // 512)
+        buf, ptrs = self.gathered_fp4[par]
+        gs = torch.empty(1, dtype=torch.float32, device=x.device)
+        scratch = torch.empty(1, dtype=torch.float32, device=x.device)
+        check(lib().hippo_nvfp4_tensor_scale(ptr(x), C.c_longlong(x.numel()), 1, ptr(scratch), ptr(gs), stream_ptr()),
+              "nvfp4_tensor_scale")
+        check(lib().hippo_nvfp4_quant_push(ptr(x), C.c_longlong(x.stride(0)), rows, K, ptr(gs), _ptr_arr(ptrs),
+                                           _ptr_arr(self._row_ptrs(row)), self.world, self.rank, stream_ptr()),
+              "nvfp4_quant_push")
+        sfb = fp4_gemm.tile_scales(scales, N, K)
+        y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        gsw = global_scale.float().contiguous()
+        check(lib().hippo_allgather_gemm_nvfp4(ptr(buf), C.c_void_p(self._row_ptrs(row)[self.rank]), self.world, self.rank,
+                                               rows, ptr(packed), ptr(sfb), ptr(gsw), ptr(y), C.c_longlong(N), N, K,
+                                               C.c_uint(target), C.c_longlong(self.wait_cycles), stream_ptr()),
+              "allgather_gemm_nvfp4")
+        return y
+
+    def nvfp4_gemm_reduce_scatter(self, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
+                                  global_scale: torch.Tensor) -> Optional[torch.Tensor]:
+        """x: [T, K_local] bf16 -> reduce_scatter(Q(x) dq(W)^T) [T/w, N]; partial tiles leave from the GEMM epilogue."""
+        from ..ops import fp4_gemm, nvfp4_cuda
+        T, K = x.shape
+        N = packed.shape[0]
+        rows = T // self.world
+        if rows % _BM or T % self.world or K % 256 or N % 8 or x.dtype != torch.bfloat16 \
+                or T * N > self.max_tokens * self.max_width:
+            return None
+        xp, xs, xg = nvfp4_cuda.quantize(x.contiguous())
+        sfa, sfb = fp4_gemm.tile_scales(xs, T, K), fp4_gemm.tile_scales(scales, N, K)
+        par = self.rs_n & 1
+        self.rs_n += 1
+        row = 2 + par
+        _, ptrs = self.staging[par]
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=x.device)
+        tiles = (rows // _BM) * ((N + 127) // 128)
+        target = self._use_row(row, 1, tiles * 4)
+        gsw = global_scale.float().contiguous()
+        check(lib().hippo_gemm_reduce_scatter_nvfp4(ptr(xp), ptr(sfa), ptr(xg), ptr(packed), ptr(sfb), ptr(gsw),
+                                                    _ptr_arr(ptrs), _ptr_arr(self._row_ptrs(row)), self.world, self.rank,
+                                                    rows, ptr(out), N, K, C.c_uint(target),
+                                                    C.c_longlong(self.wait_cycles), stream_ptr()),
+              "gemm_reduce_scatter_nvfp4")
         return out
 
     def check_status(self) -> None:

@@ -44,6 +44,45 @@ def test_bounded_wait_reports_and_returns():
     assert float(z.sum()) == 8.0
 
 
+def test_nvfp4_fused_kernels_single_rank():
+    """The quantise-and-push kernel, the gathered-input FP4 GEMM and the FP4 GEMM -> reduce-scatter kernel with a
+    world of one rank (every push lands in local buffers): layouts and epilogues against the plain FP4 GEMM."""
+    from hippolm_b200.ops import _ext, nvfp4_cuda, fp4_gemm
+    from hippolm_b200.ops._ext import lib, ptr, stream_ptr, check
+    _ext.clear_device_status()
+    rows, K, N = 384, 1024, 520
+    x = torch.randn(rows, K, device="cuda").bfloat16()
+    W = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+    wp, wsc, wgs = nvfp4_cuda.quantize(W)
+    ref = fp4_gemm.gemm_nt(x, wp, wsc, wgs)
+    buf = torch.zeros(rows * K * 9 // 16 + 256, device="cuda", dtype=torch.uint8)
+    flags = torch.zeros(64, device="cuda", dtype=torch.int32)
+    gs = torch.empty(1, device="cuda"); scratch = torch.empty(1, device="cuda")
+    check(lib().hippo_nvfp4_tensor_scale(ptr(x), C.c_longlong(x.numel()), 1, ptr(scratch), ptr(gs), stream_ptr()), "scale")
+    bufs = (C.c_void_p * 1)(buf.data_ptr()); fl = (C.c_void_p * 1)(flags.data_ptr())
+    check(lib().hippo_nvfp4_quant_push(ptr(x), C.c_longlong(K), rows, K, ptr(gs), bufs, fl, 1, 0, stream_ptr()), "push")
+    xp, xs, xg = nvfp4_cuda.quantize(x)
+    assert torch.equal(buf[:rows * K // 2].view(rows, K // 2), xp)
+    assert torch.equal(buf[rows * K // 2: rows * K // 2 + rows * K // 16], fp4_gemm.tile_scales(xs, rows, K))
+    assert int(flags[0]) == K // 512 and int(flags[rows // 128 - 1]) == K // 512
+    sfb = fp4_gemm.tile_scales(wsc, N, K)
+    y = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    check(lib().hippo_allgather_gemm_nvfp4(ptr(buf), ptr(flags), 1, 0, rows, ptr(wp), ptr(sfb), ptr(wgs), ptr(y),
+                                           C.c_longlong(N), N, K, C.c_uint(K // 512), C.c_longlong(0), stream_ptr()), "ag")
+    assert torch.equal(y, ref)
+    stage = torch.zeros(rows, N, device="cuda", dtype=torch.bfloat16)
+    rflags = torch.zeros(8, device="cuda", dtype=torch.int32)
+    out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    sfa = fp4_gemm.tile_scales(xs, rows, K)
+    st = (C.c_void_p * 1)(stage.data_ptr()); rf = (C.c_void_p * 1)(rflags.data_ptr())
+    tiles = (rows // 128) * ((N + 127) // 128)
+    check(lib().hippo_gemm_reduce_scatter_nvfp4(ptr(xp), ptr(sfa), ptr(xg), ptr(wp), ptr(sfb), ptr(wgs), st, rf, 1, 0, rows,
+                                                ptr(out), N, K, C.c_uint(tiles * 4), C.c_longlong(0), stream_ptr()), "rs")
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    assert _ext.device_status()[0] == 0
+
+
 _CHILD = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["HIPPO_ROOT"])
@@ -75,6 +114,24 @@ for it in range(3):
     assert rel(out, ref) < 2e-2, rel(out, ref)
     out2 = ws.gemm_reduce_scatter(a, W2.t().contiguous(), transpose_w=True)
     assert rel(out2, ref) < 2e-2
+    # NVFP4: quantise-and-push -> FP4 GEMM, FP4 GEMM -> reduce-scatter, against the unfused FP4 GEMM
+    from hippolm_b200.ops import nvfp4_cuda, fp4_gemm
+    rows, K, N = 512, 1024, 768
+    x = torch.randn(rows, K, device=dev).bfloat16(); W = (0.05 * torch.randn(N, K, device=dev)).bfloat16()
+    dist.broadcast(W, 0)
+    wp, wsc, wgs = nvfp4_cuda.quantize(W)
+    y = ws.nvfp4_allgather_gemm(x, wp, wsc, wgs)
+    assert y is not None
+    xg_ref = all_gather_dim0(x, mesh.tp_group, w_)
+    ref = torch.cat([fp4_gemm.gemm_nt(xg_ref[i * rows:(i + 1) * rows].contiguous(), wp, wsc, wgs) for i in range(w_)], 0)
+    assert rel(y, ref) < 1e-3, ("fp4 ag", rel(y, ref))
+    T, Kl, N2 = 1024, 512, 1024
+    a = torch.randn(T, Kl, device=dev).bfloat16(); W2 = (0.05 * torch.randn(N2, Kl, device=dev)).bfloat16()
+    w2p, w2s, w2g = nvfp4_cuda.quantize(W2)
+    out = ws.nvfp4_gemm_reduce_scatter(a, w2p, w2s, w2g)
+    assert out is not None
+    ref = reduce_scatter_dim0(fp4_gemm.gemm_nt(a, w2p, w2s, w2g).float(), mesh.tp_group, w_)
+    assert rel(out, ref) < 2e-2, ("fp4 rs", rel(out, ref))
 torch.cuda.synchronize()
 ws.check_status()
 dist.barrier()

@@ -441,6 +441,41 @@ extern "C" int hippo_gemm_nvfp4(const void* A, const void* B, const void* sfa, c
   return (int)cudaGetLastError();
 }
 
+// Gathered FP4 buffer (layout above) -> bf16 [T, K]: the activations exactly as the FP4 GEMM consumed them,
+// for the weight-gradient product of the backward pass. One thread per 16-element block.
+__global__ void nvfp4_dequant_gathered_kernel(const uint8_t* __restrict__ buf, long long T, int K, int rows_per_shard,
+                                              __nv_bfloat16* __restrict__ out) {
+  const long long nb = T * (K / 16);
+  const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  const long long m = b / (K / 16);
+  const int kg = (int)(b % (K / 16));
+  const long long sf_off = T * (K / 2), gs_off = sf_off + T * (K / 16);
+  const float gs = ((const float*)(buf + gs_off))[m / rows_per_shard];
+  const uint8_t s8 = buf[sf_off + ((m / 128) * (K / 64) + kg / 4) * 512 + (m % 32) * 16 + ((m % 128) / 32) * 4 + (kg % 4)];
+  const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)s8, __NV_E4M3))) * gs;
+  const float lut[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const uint2 pv = *(const uint2*)(buf + b * 8);
+  const uint8_t* pb = (const uint8_t*)&pv;
+  uint4 o[2];
+  __nv_bfloat162* ob = (__nv_bfloat162*)o;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint8_t lo = pb[i] & 0xF, hi = pb[i] >> 4;
+    ob[i] = __floats2bfloat162_rn(((lo & 8) ? -lut[lo & 7] : lut[lo & 7]) * sc, ((hi & 8) ? -lut[hi & 7] : lut[hi & 7]) * sc);
+  }
+  uint4* dst = (uint4*)(out + b * 16);
+  dst[0] = o[0]; dst[1] = o[1];
+}
+
+extern "C" int hippo_nvfp4_dequant_gathered(const void* buf, long long T, int K, int rows_per_shard, void* out, void* stream) {
+  if (T <= 0 || K % 64 || rows_per_shard <= 0 || (T % 128)) return -2;
+  const long long nb = T * (K / 16);
+  nvfp4_dequant_gathered_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)buf, T, K, rows_per_shard, (__nv_bfloat16*)out);
+  return (int)cudaGetLastError();
+}
+
 // Quantise + push (see nvfp4_quant_push_kernel). x: [rows, K] bf16 with pitch ldx; rows % 128 == 0, K % 512 == 0.
 // buf_ptrs[r] / flag_ptrs[r]: rank r's gathered FP4 buffer and its arrival counters [world * rows/128].
 extern "C" int hippo_nvfp4_quant_push(const void* x, long long ldx, int rows, int K, const float* gs,

@@ -41,8 +41,7 @@ class _NVFP4MatmulNoMaster(torch.autograd.Function):
         dy = dy.contiguous()
         w = ops.nvfp4_dequantize(mod.packed_weight, mod.scales, mod.global_scale, dy.dtype)
         dx = ops.gemm_nn(dy, w)
-        dw = ops.gemm_tn(dy, x)
-        mod._accumulate_grad(dw)
+        mod.accumulate_grad_product(dy, x)
         return dx, None, None
 
 
@@ -96,6 +95,15 @@ class NVFP4Linear(nn.Module):
         if self.no_master:
             return _NVFP4MatmulNoMaster.apply(x, self, self._anchor.requires_grad_(False))
         return _NVFP4MatmulSTE.apply(x, self.weight, self.act_quant)
+
+    def accumulate_grad_product(self, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """grad_w += dy^T x. Once the accumulator exists the GEMM epilogue adds into it directly (no dW temporary,
+        no separate add pass); the first micro-batch and the host-offload sink take the materialised product."""
+        if self.grad_sink is None and self.grad_w is not None and dy.is_cuda and self.grad_w.dtype == torch.bfloat16 \
+                and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0:
+            ops.gemm_tn_accumulate(dy, x, self.grad_w)
+        else:
+            self._accumulate_grad(ops.gemm_tn(dy, x))
 
     def _accumulate_grad(self, dw: torch.Tensor) -> None:
         if self.grad_sink is not None:

@@ -45,20 +45,25 @@ def gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool
     return _STATE["ws"].gemm_reduce_scatter(x, weight, transpose_w)
 
 
-def nvfp4_allgather_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor
-                         ) -> Optional[torch.Tensor]:
-    """x[T/w, K] bf16 -> Q(gather(x)) dq(W)^T [T, N] with the FP4 shard exchange inside the GEMM kernel.
-    None when the workspace / kernel does not cover the shape (the caller then runs NCCL + the plain FP4 GEMM)."""
+def nvfp4_allgather_gemm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor,
+                         keep_gathered: bool = False):
+    """x[T/w, K] bf16 -> (Q(gather(x)) dq(W)^T [T, N], kept gathered FP4 bytes or None) with the FP4 shard exchange
+    inside the quantise and GEMM kernels. (None, None) when the workspace / kernel does not cover the shape (the
+    caller then runs NCCL + the plain FP4 GEMM)."""
     ws = _STATE["ws"]
-    if ws is None or not hasattr(ws, "nvfp4_allgather_gemm"):
-        return None
-    return ws.nvfp4_allgather_gemm(x, packed, scales, global_scale)
+    if ws is None:
+        return None, None
+    return ws.nvfp4_allgather_gemm(x, packed, scales, global_scale, keep_gathered)
+
+
+def nvfp4_dequant_gathered(saved: torch.Tensor, T: int, K: int) -> torch.Tensor:
+    return _STATE["ws"].nvfp4_dequant_gathered(saved, T, K)
 
 
 def nvfp4_gemm_reduce_scatter(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor
                               ) -> Optional[torch.Tensor]:
     """x[T, K/w] bf16 -> reduce_scatter(Q(x) dq(W)^T) [T/w, N] with the partial tiles pushed from the epilogue."""
     ws = _STATE["ws"]
-    if ws is None or not hasattr(ws, "nvfp4_gemm_reduce_scatter"):
+    if ws is None:
         return None
     return ws.nvfp4_gemm_reduce_scatter(x, packed, scales, global_scale)

@@ -10,6 +10,7 @@ symmetric-memory workspace the collective is fused into the GEMM kernel
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -17,6 +18,11 @@ import torch
 from .. import ops
 from .collectives import all_gather_dim0, reduce_scatter_dim0
 from .mesh import get_mesh
+
+
+# Keep the gathered input of a column-parallel linear for its weight-gradient GEMM instead of gathering it a second
+# time in the backward pass (memory for NVLink traffic). HIPPO_KEEP_GATHERED=0 restores the re-gather.
+KEEP_GATHERED = os.environ.get("HIPPO_KEEP_GATHERED", "1") != "0"
 
 
 def _fused():
@@ -32,12 +38,19 @@ class _ColumnLinearSP(torch.autograd.Function):
         if f is not None and x.is_cuda and m.tp > 1 and f.fits(x.shape[0], x.shape[0] * m.tp, x.shape[1]) \
                 and weight.shape[0] % 8 == 0 and x.dtype == torch.bfloat16:
             xg, y = f.allgather_gemm(x, weight, need_gathered=False)
+            if KEEP_GATHERED:
+                # a private copy of the gathered activations for the dW GEMM of the backward pass (the workspace
+                # view is recycled two calls later); costs T*K*2 bytes per layer, saves one all-gather per layer
+                rows = x.shape[0]
+                xg = xg.clone()
+                xg[m.tp_rank * rows:(m.tp_rank + 1) * rows].copy_(x)
         else:
             xg = all_gather_dim0(x, m.tp_group, m.tp)
             y = ops.gemm_nt(xg, weight)
         if bias is not None:
             y = y + bias
-        ctx.save_for_backward(x, weight)
+        ctx.kept = bool(KEEP_GATHERED and m.tp > 1)
+        ctx.save_for_backward(xg if ctx.kept else x, weight)
         ctx.has_bias = bias is not None
         return y
 
@@ -57,7 +70,7 @@ class _ColumnLinearSP(torch.autograd.Function):
                 dx = reduce_scatter_dim0(dxg, m.tp_group, m.tp)
         else:
             dx = None
-        xg = all_gather_dim0(x, m.tp_group, m.tp)
+        xg = x if ctx.kept else all_gather_dim0(x, m.tp_group, m.tp)
         dw = ops.gemm_tn(dy, xg)                                   # [N/w, K]
         db = dy.sum(0) if ctx.has_bias else None
         return dx, dw.to(weight.dtype), db
@@ -110,14 +123,20 @@ class _NVFP4ColumnSP(torch.autograd.Function):
         m = get_mesh()
         packed, scales, gs = _nvfp4_operands(module, weight)
         f = _fused()
-        y = None
+        y, kept = None, None
         if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
-            y = f.nvfp4_allgather_gemm(x, packed, scales, gs)          # None when the shape is not covered
+            y, kept = f.nvfp4_allgather_gemm(x, packed, scales, gs, keep_gathered=KEEP_GATHERED)   # None: not covered
         if y is None:
             xg = all_gather_dim0(x, m.tp_group, m.tp) if m.tp > 1 else x
             y = ops.nvfp4_linear(xg, packed, scales, gs, act_quant=module.act_quant)
+            if KEEP_GATHERED and m.tp > 1:
+                kept = xg
         ctx.module = module
-        ctx.save_for_backward(x, packed, scales, gs)
+        # kept: the gathered input, either bf16 [T, K] or the FP4 bytes the GEMM consumed (uint8, dequantised in backward:
+        # dW = dY^T Q(x) is the exact weight gradient of the quantised forward)
+        ctx.kept_kind = 0 if kept is None else (2 if kept.dtype == torch.uint8 else 1)
+        ctx.T, ctx.K = x.shape[0] * m.tp, x.shape[1]
+        ctx.save_for_backward(x if kept is None else kept, packed, scales, gs)
         return y
 
     @staticmethod
@@ -135,12 +154,17 @@ class _NVFP4ColumnSP(torch.autograd.Function):
                 dx = f.gemm_reduce_scatter(dy, w, transpose_w=True)
             else:
                 dx = reduce_scatter_dim0(ops.gemm_nn(dy, w), m.tp_group, m.tp)
-            xg = all_gather_dim0(x, m.tp_group, m.tp)
-        dw = ops.gemm_tn(dy, xg)
+            if ctx.kept_kind == 2:
+                xg = f.nvfp4_dequant_gathered(x, ctx.T, ctx.K) if f is not None else None
+                assert xg is not None, "the fused workspace was torn down between forward and backward"
+            elif ctx.kept_kind == 1:
+                xg = x
+            else:
+                xg = all_gather_dim0(x, m.tp_group, m.tp)
         if mod.no_master:
-            mod._accumulate_grad(dw)
+            mod.accumulate_grad_product(dy, xg)
             return dx, None, None
-        return dx, dw.to(mod.weight.dtype), None
+        return dx, ops.gemm_tn(dy, xg).to(mod.weight.dtype), None
 
 
 class _NVFP4RowSP(torch.autograd.Function):
@@ -178,11 +202,10 @@ class _NVFP4RowSP(torch.autograd.Function):
         else:
             dyg = all_gather_dim0(dy, m.tp_group, m.tp)
             dx = ops.gemm_nn(dyg, w)
-        dw = ops.gemm_tn(dyg, x)
         if mod.no_master:
-            mod._accumulate_grad(dw)
+            mod.accumulate_grad_product(dyg, x)
             return dx, None, None
-        return dx, dw.to(mod.weight.dtype), None
+        return dx, ops.gemm_tn(dyg, x).to(mod.weight.dtype), None
 
 
 def _nvfp4_weight_arg(module):

@@ -141,7 +141,7 @@ class FusedWorkspace:
 
     # ------------------------------------------------------------------ NVFP4: quantise + push -> FP4 GEMM
     def nvfp4_allgather_gemm(self, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
-                             global_scale: torch.Tensor) -> Optional[torch.Tensor]:
+                             global_scale: torch.Tensor, keep_gathered: bool = False):
         """x: [T/w, K] bf16 -> Q(gather(x)) dq(W)^T [T, N]. Each rank quantises its shard with its own tensor scale and
         pushes 0.5625 bytes per element to every peer; the GEMM applies the source rank's scale per row block."""
         from ..ops import fp4_gemm
@@ -150,7 +150,7 @@ class FusedWorkspace:
         T = rows * self.world
         if rows % _BM or K % 512 or N % 8 or x.dtype != torch.bfloat16 or T * K > self.max_tokens * self.max_width \
                 or T // _BM > self.FLAG_ROW:
-            return None
+            return None, None
         x = x.contiguous()
         par = self.fp4_n & 1
         self.fp4_n += 1
@@ -171,7 +171,18 @@ class FusedWorkspace:
                                                rows, ptr(packed), ptr(sfb), ptr(gsw), ptr(y), C.c_longlong(N), N, K,
                                                C.c_uint(target), C.c_longlong(self.wait_cycles), stream_ptr()),
               "allgather_gemm_nvfp4")
-        return y
+        if keep_gathered:
+            # the gathered FP4 activations (packed + scale tiles + per-source tensor scales) for the backward dW
+            nbytes = T * K // 2 + T * K // 16 + 32
+            return y, buf[:nbytes].clone()
+        return y, None
+
+    def nvfp4_dequant_gathered(self, saved: torch.Tensor, T: int, K: int) -> torch.Tensor:
+        """bf16 [T, K] view of a gathered FP4 buffer kept by ``nvfp4_allgather_gemm``."""
+        out = torch.empty((T, K), dtype=torch.bfloat16, device=saved.device)
+        check(lib().hippo_nvfp4_dequant_gathered(ptr(saved), C.c_longlong(T), K, T // self.world, ptr(out), stream_ptr()),
+              "nvfp4_dequant_gathered")
+        return out
 
     def nvfp4_gemm_reduce_scatter(self, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
                                   global_scale: torch.Tensor) -> Optional[torch.Tensor]:

@@ -120,9 +120,13 @@ for it in range(3):
     x = torch.randn(rows, K, device=dev).bfloat16(); W = (0.05 * torch.randn(N, K, device=dev)).bfloat16()
     dist.broadcast(W, 0)
     wp, wsc, wgs = nvfp4_cuda.quantize(W)
-    y = ws.nvfp4_allgather_gemm(x, wp, wsc, wgs)
+    y, kept = ws.nvfp4_allgather_gemm(x, wp, wsc, wgs, keep_gathered=True)
     assert y is not None
     xg_ref = all_gather_dim0(x, mesh.tp_group, w_)
+    xq = ws.nvfp4_dequant_gathered(kept, rows * w_, K)
+    xq_ref = torch.cat([nvfp4_cuda.dequantize(*nvfp4_cuda.quantize(xg_ref[i * rows:(i + 1) * rows].contiguous()),
+                                              dtype=torch.bfloat16) for i in range(w_)], 0)
+    assert torch.equal(xq, xq_ref), "kept FP4 activations differ"
     ref = torch.cat([fp4_gemm.gemm_nt(xg_ref[i * rows:(i + 1) * rows].contiguous(), wp, wsc, wgs) for i in range(w_)], 0)
     assert rel(y, ref) < 1e-3, ("fp4 ag", rel(y, ref))
     T, Kl, N2 = 1024, 512, 1024

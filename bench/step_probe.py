@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--ffn", type=int, default=14336, help="e.g. 1792 = the local FFN width of one TP=8 rank")
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--micro", type=int, default=0, help="micro-batch tokens (default: one sequence)")
+    ap.add_argument("--gemm_log", action="store_true", help="time every bf16 GEMM call of one extra step with CUDA events "
+                    "and print time and TFLOP/s per (layout, M, N, K) (diagnosis only)")
     ap.add_argument("--kineto", action="store_true", help="after the timed steps, trace one more step with torch.profiler "
                     "and print GPU-busy time vs wall time and the top kernels (diagnosis only, not a benchmark number)")
     a = ap.parse_args()
@@ -54,6 +56,29 @@ def main():
         print(i, "step s", round(time.time() - t0, 3), "loss", round(float(out["loss"]), 4), tm.summary(),
               "launches", _ext.launch_count(), "status", _ext.device_status(), flush=True)
     print("max mem GB", round(torch.cuda.max_memory_allocated() / 2 ** 30, 2))
+    if a.gemm_log:
+        from hippolm_b200.ops import cuda_ops
+        orig, recs = cuda_ops._gemm, []
+
+        def timed(a_, b_, layout, M, N, K, *args_, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = orig(a_, b_, layout, M, N, K, *args_, **kw)
+            e1.record()
+            recs.append(((layout, M, N, K), e0, e1))
+            return out
+        cuda_ops._gemm = timed
+        train_step(ctx, batch)
+        torch.cuda.synchronize()
+        cuda_ops._gemm = orig
+        agg = {}
+        for key, e0, e1 in recs:
+            c = agg.setdefault(key, [0, 0.0]); c[0] += 1; c[1] += e0.elapsed_time(e1)
+        tot = sum(v[1] for v in agg.values())
+        print(f"bf16 GEMM calls {len(recs)}, total {tot:.1f} ms")
+        for (layout, M, N, K), (c, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:40]:
+            tf = 2.0 * M * N * K * c / ms / 1e9
+            print(f"  {ms:8.2f} ms {c:5d} x  {'NT NN TN TT'.split()[layout]} M={M:6d} N={N:6d} K={K:6d}  {tf:7.1f} TFLOP/s")
     if a.kineto:
         from torch.profiler import profile, ProfilerActivity
         torch.cuda.synchronize()

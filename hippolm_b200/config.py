@@ -65,7 +65,7 @@ class HippoConfig:
     ffn_nvfp4_no_bf16_master: bool = False
     # memory policy
     gradient_checkpointing: bool = False
-    lce_num_chunks: int = 8
+    lce_num_chunks: int = 0                 # token chunks of the fused linear+CE head; 0 = sized automatically
     # derived
     block_size: int = field(init=False, default=0)
 

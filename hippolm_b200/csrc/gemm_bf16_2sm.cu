@@ -184,65 +184,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
-        tmem_ld_32x32(taddr + c, r);
-        tc_wait_ld();
+        EpiPrefetch pre;
         const int col0 = tn * BN + c;
-        if (row < p.M && col0 < p.N) {
-          if (p.out_fp32) {
-            float* crow = (float*)p.C + (long long)row * p.ldc + col0;
-            if (col0 + 32 <= p.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
-                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                float4* dst = (float4*)(crow + j);
-                if (p.accumulate) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                *dst = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += crow[j];
-                crow[j] = v;
-              }
-            }
-          } else {
-            __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
-            if (col0 + 32 <= p.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
-                uint4* dst = (uint4*)(crow + j);
-                if (p.accumulate) {
-                  uint4 o = *dst;
-                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += of.x; f[2 * e + 1] += of.y; }
-                }
-                if (p.Cin) {
-                  uint4 o = *(const uint4*)((const __nv_bfloat16*)p.Cin + (long long)row * p.ldcin + col0 + j);
-                  const __nv_bfloat162* ob = (const __nv_bfloat162*)&o;
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) { float2 of = __bfloat1622float2(ob[e]); f[2 * e] += p.beta * of.x; f[2 * e + 1] += p.beta * of.y; }
-                }
-                uint4 v;
-                __nv_bfloat162* vb = (__nv_bfloat162*)&v;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-                *dst = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += __bfloat162float(crow[j]);
-                if (p.Cin) v += p.beta * __bfloat162float(((const __nv_bfloat16*)p.Cin)[(long long)row * p.ldcin + col0 + j]);
-                crow[j] = __float2bfloat16(v);
-              }
-            }
-          }
-        }
+        tmem_ld_32x32(taddr + c, r);
+        epi_prefetch(p, row, col0, pre);          // addends travel while the TMEM load completes
+        tc_wait_ld();
+        epi_store(p, r, row, col0, pre);
       }
       tc_fence_before();
       __syncwarp();

@@ -397,7 +397,13 @@ class _VocabParallelLCE(torch.autograd.Function):
         dx = torch.empty_like(x)
         dw = torch.zeros(Vl, D, dtype=torch.float32, device=x.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
-        cs = max(1, (T + num_chunks - 1) // num_chunks)
+        if num_chunks > 0:
+            cs = max(1, (T + num_chunks - 1) // num_chunks)
+        else:
+            # automatic: the largest chunk whose fp32 logits tile [cs, V/w] stays near 2 GiB. Bigger chunks mean
+            # fewer read-modify-write passes over the fp32 dW accumulator and deeper (K = cs) dW GEMMs.
+            cs = max(1024, ((1 << 31) // (4 * Vl)) // 128 * 128)
+            cs = min(cs, T)
         for s in range(0, T, cs):
             e = min(T, s + cs)
             xc = x[s:e]

@@ -7,7 +7,27 @@ import torch
 
 from ._ext import lib, ptr, stream_ptr, check
 
+import os
+
 _CACHE = {"key": None}
+_CACHE128 = {"key": None}
+_USE_TC = os.environ.get("HIPPO_ATTN_TC", "1") != "0"
+
+
+def tile_tables_128(cu_seqlens: torch.Tensor, T: int):
+    """128-row query tiles (start, length, document start) for the tcgen05 forward kernel."""
+    key = (cu_seqlens.data_ptr(), cu_seqlens._version, cu_seqlens.numel(), T)
+    if _CACHE128["key"] == key and _CACHE128.get("ref") is cu_seqlens:
+        return _CACHE128["val"]
+    N = cu_seqlens.numel() - 1
+    cu = cu_seqlens.to(torch.int32).contiguous()
+    nt = (T + 127) // 128 + N
+    ts, tl, t0 = (torch.empty(nt, dtype=torch.int32, device=cu.device) for _ in range(3))
+    check(lib().hippo_attn_build_tiles_rows(ptr(cu), N, 128, ptr(ts), ptr(tl), ptr(t0), nt, stream_ptr()),
+          "attn_build_tiles_rows")
+    val = (ts, tl, t0, nt)
+    _CACHE128.update(key=key, val=val, ref=cu_seqlens)
+    return val
 
 
 def tile_tables(cu_seqlens: torch.Tensor, T: int):
@@ -34,8 +54,14 @@ class _Attn(torch.autograd.Function):
         ts, tl, t0, te, nt = tile_tables(cu_seqlens, T)
         o = torch.empty_like(q)
         lse = torch.empty((T, H), dtype=torch.float32, device=q.device)
-        check(lib().hippo_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(ts), ptr(tl), ptr(t0), nt, H, DH, _c.c_float(scale),
-                                   ptr(o), ptr(lse), stream_ptr()), "attn_fwd")
+        if DH == 128 and _USE_TC:
+            # tcgen05 forward: S and P V in TMEM, 128 x 128 tiles fed by TMA
+            ts8, tl8, t08, nt8 = tile_tables_128(cu_seqlens, T)
+            check(lib().hippo_attn_fwd_tc(ptr(q), ptr(k), ptr(v), ptr(ts8), ptr(tl8), ptr(t08), nt8, H, _c.c_longlong(T),
+                                          _c.c_float(scale), ptr(o), ptr(lse), stream_ptr()), "attn_fwd_tc")
+        else:
+            check(lib().hippo_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(ts), ptr(tl), ptr(t0), nt, H, DH, _c.c_float(scale),
+                                       ptr(o), ptr(lse), stream_ptr()), "attn_fwd")
         ctx.save_for_backward(q, k, v, o, lse, ts, tl, t0, te)
         ctx.meta = (T, H, DH, nt, scale)
         return o

@@ -9,6 +9,10 @@
 namespace hippo {
 
 inline PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  // The encode call is a driver-API call and needs a current context on the calling thread; a thread that has not
+  // made a runtime call yet (an autograd worker entering one of our launchers first) has none bound.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   if (!fn) {
     void* p = nullptr;

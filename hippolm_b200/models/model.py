@@ -397,6 +397,7 @@ class _VocabParallelLCE(torch.autograd.Function):
         dx = torch.empty_like(x)
         dw = torch.zeros(Vl, D, dtype=torch.float32, device=x.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        loss_sum_raw = torch.zeros(1, dtype=torch.float32, device=x.device)     # filled by the fused CE kernels
         if num_chunks > 0:
             cs = max(1, (T + num_chunks - 1) // num_chunks)
         else:
@@ -404,9 +405,25 @@ class _VocabParallelLCE(torch.autograd.Function):
             # fewer read-modify-write passes over the fp32 dW accumulator and deeper (K = cs) dW GEMMs.
             cs = max(1024, ((1 << 31) // (4 * Vl)) // 128 * 128)
             cs = min(cs, T)
+        ws = None
+        if m.tp > 1 and x.is_cuda:
+            from ..parallel import fused as _fused
+            from ..ops import cuda_ops as _cuda_ops
+            ws = _fused.workspace()
+            if ws is not None and min(cs, T) > ws.lce_rows:
+                ws = None
         for s in range(0, T, cs):
             e = min(T, s + cs)
             xc = x[s:e]
+            if ws is not None:
+                # cross-rank max / sum-exp merge inside the kernels: statistics go to every rank by peer stores,
+                # the gradient kernel waits for all sources; no collective call per chunk
+                z = _cuda_ops.gemm_nt(xc, weight, out_dtype=torch.float32)
+                handle = ws.lce_stats_push(z, local_t[s:e])
+                pz = ws.lce_grad_merge(handle, z, valid[s:e].float() / nv, loss_sum_raw)
+                dx[s:e] = ops.gemm_nn(pz, weight)
+                ops.gemm_tn_accumulate(pz, xc, dw)
+                continue
             z, mx, se, tz = ops.lce_chunk_stats(xc, weight, local_t[s:e])
             if m.tp > 1:
                 gmx = mx.clone()
@@ -425,7 +442,7 @@ class _VocabParallelLCE(torch.autograd.Function):
             ops.gemm_tn_accumulate(pz, xc, dw)
         dx_shard = reduce_scatter_dim0(dx, m.tp_group, m.tp)
         ctx.save_for_backward(dx_shard, dw.to(weight.dtype))
-        return loss_sum / nv
+        return (loss_sum + loss_sum_raw[0]) / nv
 
     @staticmethod
     def backward(ctx, do):

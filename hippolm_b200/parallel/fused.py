@@ -67,3 +67,8 @@ def nvfp4_gemm_reduce_scatter(x: torch.Tensor, packed: torch.Tensor, scales: tor
     if ws is None:
         return None
     return ws.nvfp4_gemm_reduce_scatter(x, packed, scales, global_scale)
+
+
+def workspace():
+    """The active symmetric workspace (None until setup())."""
+    return _STATE["ws"]

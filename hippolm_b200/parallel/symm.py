@@ -6,7 +6,8 @@ over the TP group); the kernels in ``csrc/gemm_bf16.cu`` only see raw peer point
   gathered[parity]   [T, Kmax] bf16 on every rank   target of the all-gather pushes (AG -> GEMM)
   staging[parity]    [world][T/world, Nmax] bf16     per-source partial tiles (GEMM -> RS)
   gathered_fp4[par]  NVFP4 bytes + scale tiles      target of the quantise-and-push kernel (FP4 AG -> GEMM)
-  counters           uint32 [6][1024]                monotonic arrival counters, one row per (op, parity); AG: one per
+  lce_stats[par]     float4 [world][T]              per-source (max, sum exp, target logit) rows of the LCE head
+  counters           uint32 [8][1024]                monotonic arrival counters, one row per (op, parity); AG: one per
                                                      (source rank, 128-row block), RS: one per source rank
 
 A rank can run at most one fused op ahead of its slowest peer (each op needs data from every peer), so
@@ -33,7 +34,7 @@ def _ptr_arr(ptrs) -> C.Array:
 
 class FusedWorkspace:
     FLAG_ROW = 1024          # counters per (op, parity) row: world * row blocks per shard <= 1024
-    N_ROWS = 6
+    N_ROWS = 8
 
     def __init__(self, mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, comm_ctas: int = 16,
                  wait_cycles: int = 0):
@@ -57,6 +58,9 @@ class FusedWorkspace:
         self.staging = [alloc(nbytes) for _ in range(2)]
         # NVFP4 gathered activations: [T, K/2] packed | [T/128][K/64][512] scale tiles | 8 tensor scales
         self.gathered_fp4 = [alloc(max_tokens * max_width * 9 // 16 + 256) for _ in range(2)]
+        self.lce_rows = max_tokens
+        self.lce_stats = [alloc(self.world * max_tokens * 16) for _ in range(2)]
+        self.lce_n = 0
         self.flags_t, self.flag_ptrs = alloc(self.N_ROWS * self.FLAG_ROW * 4)
         self.flags_t.zero_()
         torch.cuda.synchronize(dev)
@@ -210,6 +214,33 @@ class FusedWorkspace:
                                                     C.c_longlong(self.wait_cycles), stream_ptr()),
               "gemm_reduce_scatter_nvfp4")
         return out
+
+    # ------------------------------------------------------------------ vocab-parallel CE: in-kernel cross-rank softmax
+    def lce_stats_push(self, z: torch.Tensor, targets_local: torch.Tensor):
+        """Row statistics of this rank's logits shard z[C, V/w] pushed to every rank. Returns the handle for lce_grad_merge."""
+        Cr, V = z.shape
+        assert Cr <= self.lce_rows and z.dtype == torch.float32 and z.is_contiguous()
+        par = self.lce_n & 1
+        self.lce_n += 1
+        row = 6 + par
+        target = self._use_row(row, 1, Cr)
+        _, ptrs = self.lce_stats[par]
+        tg = targets_local.to(torch.int64).contiguous()
+        check(lib().hippo_ce_stats_push(ptr(z), ptr(tg), C.c_longlong(Cr), V, _ptr_arr(ptrs), _ptr_arr(self._row_ptrs(row)),
+                                        self.world, self.rank, self.lce_rows, stream_ptr()), "ce_stats_push")
+        return (par, row, target, tg)
+
+    def lce_grad_merge(self, handle, z: torch.Tensor, row_weight: torch.Tensor, loss_sum: torch.Tensor) -> torch.Tensor:
+        """dz[C, V/w] (bf16) from the merged statistics of all ranks; adds sum(lse - z_target) of weighted rows to loss_sum."""
+        par, row, target, tg = handle
+        Cr, V = z.shape
+        _, ptrs = self.lce_stats[par]
+        dz = torch.empty((Cr, V), dtype=torch.bfloat16, device=z.device)
+        rw = row_weight.float().contiguous()
+        check(lib().hippo_ce_grad_merge(ptr(z), ptr(tg), ptr(rw), ptr(dz), C.c_longlong(Cr), V, ptr(loss_sum), _ptr_arr(ptrs),
+                                        _ptr_arr(self._row_ptrs(row)), self.world, self.rank, self.lce_rows,
+                                        C.c_uint(target), C.c_longlong(self.wait_cycles), stream_ptr()), "ce_grad_merge")
+        return dz
 
     def check_status(self) -> None:
         st = _ext.device_status()

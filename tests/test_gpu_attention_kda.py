@@ -10,7 +10,8 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("T,H,DH,cu", [(256, 2, 128, [0, 256]), (333, 2, 64, [0, 100, 333]),
-                                       (1000, 4, 128, [0, 64, 65, 700, 1000])])
+                                       (1000, 4, 128, [0, 64, 65, 700, 1000]),
+                                       (2048, 2, 128, [0, 300, 1500, 2048])])
 def test_causal_attention(T, H, DH, cu):
     from hippolm_b200 import ops
     from hippolm_b200.ref import ops as ro
@@ -27,6 +28,13 @@ def test_causal_attention(T, H, DH, cu):
     assert _rel(o, o2) < 2e-2
     for a, b in zip(ins, ref_in):
         assert _rel(a.grad, b.grad) < 3e-2
+
+
+def test_causal_attention_mma_sync_path(monkeypatch):
+    """head_dim 128 through the mma.sync kernels (the path head_dim 64 always takes)."""
+    from hippolm_b200.ops import attn_cuda
+    monkeypatch.setattr(attn_cuda, "_USE_TC", False)
+    test_causal_attention(1000, 4, 128, [0, 64, 65, 700, 1000])
 
 
 @pytest.mark.parametrize("T,H,D,cu,gs", [(128, 2, 128, [0, 128], 1.0), (200, 2, 64, [0, 70, 200], 1.0),

@@ -136,6 +136,30 @@ for it in range(3):
     assert out is not None
     ref = reduce_scatter_dim0(fp4_gemm.gemm_nt(a, w2p, w2s, w2g).float(), mesh.tp_group, w_)
     assert rel(out, ref) < 2e-2, ("fp4 rs", rel(out, ref))
+    # vocab-parallel cross entropy: statistics pushed to every rank, merged inside the gradient kernel
+    Cr, Vl = 256, 1000
+    z = 3 * torch.randn(Cr, Vl, device=dev)
+    tgt = torch.randint(0, Vl * w_, (Cr,), device=dev); dist.broadcast(tgt, 0)
+    tgt[::7] = -100
+    local = tgt - r_ * Vl
+    own = (local >= 0) & (local < Vl) & (tgt >= 0)
+    local_t = torch.where(own, local, torch.full_like(local, -1))
+    valid = tgt >= 0
+    roww = valid.float() / valid.sum()
+    loss_raw = torch.zeros(1, device=dev)
+    hd = ws.lce_stats_push(z, local_t)
+    dz = ws.lce_grad_merge(hd, z, roww, loss_raw)
+    zs = [torch.empty_like(z) for _ in range(w_)]
+    dist.all_gather(zs, z, group=mesh.tp_group)
+    zfull = torch.cat(zs, 1)
+    lse = torch.logsumexp(zfull, 1)
+    tz = zfull.gather(1, tgt.clamp(min=0)[:, None])[:, 0]
+    ref_loss = ((lse - tz) * valid).sum()
+    assert abs(loss_raw.item() - ref_loss.item()) < 2e-3 * abs(ref_loss.item()), (loss_raw.item(), ref_loss.item())
+    pr = (zfull - lse[:, None]).exp()
+    pr[valid, tgt[valid]] -= 1
+    refdz = (pr * roww[:, None])[:, r_ * Vl:(r_ + 1) * Vl]
+    assert (dz.float() - refdz).abs().max() < 2e-2 * roww.max(), "fused CE gradient"
 torch.cuda.synchronize()
 ws.check_status()
 dist.barrier()

@@ -14,6 +14,7 @@
 #include <mma.h>
 #include <stdint.h>
 #include "kda_common.cuh"
+#include <stdlib.h>
 
 namespace hippo {
 using namespace nvcuda;
@@ -170,6 +171,163 @@ template <int DK, int VS>
 constexpr int kda_bwd_state_smem() {
   return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 64 * (VS + 8) * 2 +
          2 * (3 * 64 * (DK + 8) + 64 * 72 + 64 * (VS + 8) + 2 * DK) * 2 + 128;
+}
+
+// Register-resident variant for DK = 128 (mma.sync m16n8k16 + ldmatrix): warp w keeps rows 16w..16w+15 of the fp32
+// state gradient in registers across the whole (reverse) chain; only its bf16 image lives in shared memory as the B
+// operand of the next chunk. Two barriers per chunk, tiles double-buffered with cp.async.
+template <int VS>
+__global__ void __launch_bounds__(256, 1)
+kda_bwd_state_mma_kernel(const bf16* __restrict__ w, const bf16* __restrict__ qg, const bf16* __restrict__ kg,
+                         const bf16* __restrict__ Aqk, const float* __restrict__ G, const bf16* __restrict__ d_o,
+                         const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
+                         const int* __restrict__ seq_chunk, const int* __restrict__ seq_order, int H,
+                         const float* __restrict__ dfinal, bf16* __restrict__ dvn_out, bf16* __restrict__ dS_out,
+                         float* __restrict__ dh0) {
+  constexpr int DK = 128, LD = DK + 8, LS = VS + 8, LQ = 72, NTHR = 256;
+  static_assert(VS == 32, "warp tiling below assumes a 32-column value slice");
+  constexpr int TILE_ELEMS = 3 * 64 * LD + 64 * LQ + 64 * LS + 2 * DK;
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* tiles = (bf16*)smem;                                 // 2 x { w, qg, kg: [64][LD]; Aqk: [64][LQ]; do: [64][LS]; Glast }
+  bf16* dSb = tiles + 2 * TILE_ELEMS;                        // [DK][LS]
+  bf16* ndv = dSb + DK * LS;                                 // [64][LS]   (-dv_new)
+  float* egl = (float*)(ndv + 64 * LS);                      // [DK]
+
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
+  if (c_begin >= c_end) return;
+  const int mt = warp & 3, nh = warp >> 2;
+  const int srow = warp * 16 + g;
+
+  float dS[4][4];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int c = vs0 + nt * 8 + 2 * t4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = srow + (e >> 1) * 8;
+      dS[nt][e] = dfinal ? dfinal[(((long long)seq * H + h) * DK + r) * DK + c + (e & 1)] : 0.f;
+    }
+    *(unsigned*)(dSb + srow * LS + nt * 8 + 2 * t4) = kda_pack2(dS[nt][0], dS[nt][1]);
+    *(unsigned*)(dSb + (srow + 8) * LS + nt * 8 + 2 * t4) = kda_pack2(dS[nt][2], dS[nt][3]);
+  }
+  auto fetch = [&](int chunk, int buf) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+    bf16* ws_ = tiles + buf * TILE_ELEMS; bf16* qgs_ = ws_ + 64 * LD; bf16* kgs_ = qgs_ + 64 * LD; bf16* Aq_ = kgs_ + 64 * LD;
+    bf16* dos_ = Aq_ + 64 * LQ; float* gl_ = (float*)(dos_ + 64 * LS);
+#pragma unroll
+    for (int j = 0; j < 64 * (DK / 8) / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx >> 4, c8 = (idx & 15) * 8;
+      const long long off = (cbase + r) * DK + c8;
+      cp_async16(ws_ + r * LD + c8, w + off); cp_async16(qgs_ + r * LD + c8, qg + off); cp_async16(kgs_ + r * LD + c8, kg + off);
+    }
+#pragma unroll
+    for (int j = 0; j < 64 * 8 / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      cp_async16(Aq_ + r * LQ + c8, Aqk + (cbase + r) * 64 + c8);
+    }
+    {
+      const int r = tid >> 2, c8 = (tid & 3) * 8;
+      const bool ok = r < len;                               // rows past the chunk end read as zeros
+      cp_async16(dos_ + r * LS + c8, d_o + ((long long)(t0 + (ok ? r : 0)) * H + h) * DK + vs0 + c8, ok ? 16 : 0);
+    }
+    if (tid < DK / 4) cp_async16(gl_ + tid * 4, G + (cbase + 63) * DK + tid * 4);
+    cp_async_commit();
+  };
+  fetch(c_end - 1, 0);
+  cp_async_wait_all();
+  __syncthreads();
+
+  for (int chunk = c_end - 1; chunk >= c_begin; --chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int buf = (c_end - 1 - chunk) & 1;
+    const bf16* ws = tiles + buf * TILE_ELEMS; const bf16* qgs = ws + 64 * LD; const bf16* kgs = qgs + 64 * LD;
+    const bf16* Aq = kgs + 64 * LD; const bf16* dos = Aq + 64 * LQ; const float* gl = (const float*)(dos + 64 * LS);
+    if (chunk - 1 >= c_begin) fetch(chunk - 1, buf ^ 1);     // the other buffer was released at the last barrier
+    if (tid < DK) egl[tid] = __expf(gl[tid]);
+    // gradient wrt the state after this chunk, for the per-chunk kernels
+#pragma unroll
+    for (int j = 0; j < DK * (VS / 8) / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      *(uint4*)(dS_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(dSb + r * LS + c8);
+    }
+    // ---- dv_new = Aqk^T do + kg dS   (rows mt*16.., columns nh*16..)
+    {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int kt = mt; kt < 4; ++kt) {                      // Aqk lower triangular -> Aqk^T upper
+        unsigned af[4], b[4];
+        kda_frag_a_t(af, Aq, LQ, mt * 16, kt * 16, lane);
+        kda_frag_b2(b, dos, LS, kt * 16, nh * 16, lane);
+        kda_mma16816(acc[0], af, b[0], b[1]);
+        kda_mma16816(acc[1], af, b[2], b[3]);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        unsigned af[4], b[4];
+        kda_frag_a(af, kgs, LD, mt * 16, kk * 16, lane);
+        kda_frag_b2(b, dSb, LS, kk * 16, nh * 16, lane);
+        kda_mma16816(acc[0], af, b[0], b[1]);
+        kda_mma16816(acc[1], af, b[2], b[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int c = nh * 16 + nt * 8 + 2 * t4;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = mt * 16 + g + hh * 8;
+          *(unsigned*)(dvn_out + (cbase + r) * DK + vs0 + c) = kda_pack2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+          *(unsigned*)(ndv + r * LS + c) = kda_pack2(-acc[nt][2 * hh], -acc[nt][2 * hh + 1]);
+        }
+      }
+    }
+    __syncthreads();                                          // ndv complete; every warp is past its reads of dSb
+    // ---- dS <- e^Glast dS + qg^T do - w^T dv_new   (this warp's 16 rows, all VS columns)
+    {
+      const float e0 = egl[srow], e1 = egl[srow + 8];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { dS[nt][0] *= e0; dS[nt][1] *= e0; dS[nt][2] *= e1; dS[nt][3] *= e1; }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        unsigned af[4], b0[4], b1[4];
+        kda_frag_a_t(af, qgs, LD, warp * 16, kk * 16, lane);
+        kda_frag_b2(b0, dos, LS, kk * 16, 0, lane);
+        kda_frag_b2(b1, dos, LS, kk * 16, 16, lane);
+        kda_mma16816(dS[0], af, b0[0], b0[1]);
+        kda_mma16816(dS[1], af, b0[2], b0[3]);
+        kda_mma16816(dS[2], af, b1[0], b1[1]);
+        kda_mma16816(dS[3], af, b1[2], b1[3]);
+        kda_frag_a_t(af, ws, LD, warp * 16, kk * 16, lane);
+        kda_frag_b2(b0, ndv, LS, kk * 16, 0, lane);
+        kda_frag_b2(b1, ndv, LS, kk * 16, 16, lane);
+        kda_mma16816(dS[0], af, b0[0], b0[1]);
+        kda_mma16816(dS[1], af, b0[2], b0[3]);
+        kda_mma16816(dS[2], af, b1[0], b1[1]);
+        kda_mma16816(dS[3], af, b1[2], b1[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        *(unsigned*)(dSb + srow * LS + nt * 8 + 2 * t4) = kda_pack2(dS[nt][0], dS[nt][1]);
+        *(unsigned*)(dSb + (srow + 8) * LS + nt * 8 + 2 * t4) = kda_pack2(dS[nt][2], dS[nt][3]);
+      }
+    }
+    cp_async_wait_all();                                      // the next (earlier) chunk's tiles have landed
+    __syncthreads();
+  }
+  if (dh0) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int c = vs0 + nt * 8 + 2 * t4;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *(float2*)(dh0 + (((long long)seq * H + h) * DK + srow + hh * 8) * DK + c) = make_float2(dS[nt][2 * hh], dS[nt][2 * hh + 1]);
+    }
+  }
+}
+template <int VS>
+constexpr int kda_bwd_state_mma_smem() {
+  return (2 * (3 * 64 * 136 + 64 * 72 + 64 * (VS + 8) + 2 * 128) + 128 * (VS + 8) + 64 * (VS + 8)) * 2 + 128 * 4 + 128;
 }
 
 // =================================================================================================== dqkw
@@ -678,6 +836,13 @@ constexpr int kda_bwd_amat_smem() {
 
 using namespace hippo;
 
+// HIPPO_KDA_STATE_MMA=0 selects the WMMA state kernel for head_dim 128 as well (it always serves head_dim 64)
+static bool kda_bwd_state_mma_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("HIPPO_KDA_STATE_MMA"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
+
 template <int DK>
 static int launch_bwd(const void* q, const void* k, const void* v, const float* beta, const float* G, const void* w,
                       const void* qg, const void* kg, const void* Aqk, const void* Ainv, const void* Akk,
@@ -700,6 +865,17 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
     once = true;
   }
   if (NC == 0) return 0;
+  if (DK == 128 && kda_bwd_state_mma_enabled()) {
+    auto k3m = kda_bwd_state_mma_kernel<VS>;
+    static bool once3 = false;
+    if (!once3) {
+      cudaError_t e = cudaFuncSetAttribute(k3m, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_state_mma_smem<VS>());
+      if (e != cudaSuccess) return (int)e;
+      once3 = true;
+    }
+    k3m<<<dim3(DK / VS, H, N), 256, kda_bwd_state_mma_smem<VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
+        (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, so, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
+  } else
   k3<<<dim3(DK / VS, H, N), 256, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
       (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, so, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
   k4a<<<dim3(NC, H), 512, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,

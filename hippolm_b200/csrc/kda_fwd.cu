@@ -15,6 +15,7 @@
 #include <mma.h>
 #include <stdint.h>
 #include "kda_common.cuh"
+#include <stdlib.h>
 
 namespace hippo {
 using namespace nvcuda;
@@ -423,6 +424,201 @@ kda_fwd_state_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, con
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Register-resident variant of the state recurrence for DK = 128 (mma.sync m16n8k16 + ldmatrix).
+// The chain over chunks is what bounds this kernel, so everything is arranged around its critical path
+//     S(t) -> P = w S -> v_new = u - P -> S(t+1) = e^Glast S + kg^T v_new
+// * the fp32 state never leaves registers: warp w owns rows 16w..16w+15 of the [128 x VS] slice (16 values per thread);
+//   only its bf16 image goes to shared memory as the B operand of the next chunk;
+// * the output product o = qg S + Aqk v_new is not on the chain, so it runs AFTER the state update, reusing the
+//   B fragments of S it kept from the P product; the next chunk's P product of faster warps overlaps it;
+// * two barriers per chunk; tiles arrive by cp.async in two double-buffered sets with different lifetimes
+//   ({w, u, kg, Glast} until the state update, {qg, Aqk} until the deferred output product).
+template <int VS>
+__global__ void __launch_bounds__(256, 1)
+kda_fwd_state_mma_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ qg,
+                         const bf16* __restrict__ kg, const bf16* __restrict__ Aqk, const float* __restrict__ G,
+                         const int* __restrict__ chunk_start, const int* __restrict__ chunk_len,
+                         const int* __restrict__ seq_chunk, const int* __restrict__ seq_order, int H,
+                         const float* __restrict__ h0, bf16* __restrict__ vnew_out, bf16* __restrict__ S_out,
+                         bf16* __restrict__ o, float* __restrict__ final_state) {
+  constexpr int DK = 128, LD = DK + 8, LS = VS + 8, LQ = 72, NTHR = 256;
+  static_assert(VS == 32, "warp tiling below assumes a 32-column value slice");
+  constexpr int SETA = 2 * 64 * LD + 64 * LS + 2 * DK;       // bf16 elements: w, kg, u, Glast (DK floats)
+  constexpr int SETB = 64 * LD + 64 * LQ;                    // qg, Aqk
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* setA = (bf16*)smem;                                  // 2 x SETA
+  bf16* setB = setA + 2 * SETA;                              // 2 x SETB
+  bf16* Sb = setB + 2 * SETB;                                // [DK][LS] bf16 image of the state
+  bf16* vns = Sb + DK * LS;                                  // 2 x [64][LS]
+  float* egl = (float*)(vns + 2 * 64 * LS);                  // [DK]
+
+  const int vs0 = blockIdx.x * VS, h = blockIdx.y, seq = seq_order[blockIdx.z];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int c_begin = seq_chunk[seq], c_end = seq_chunk[seq + 1];
+  if (c_begin >= c_end) return;
+  const int mt = warp & 3, nh = warp >> 2;                   // P / o products: 16-row tile mt, 16-column half nh
+  const int srow = warp * 16 + g;                            // state rows of this thread: srow, srow + 8
+
+  float S[4][4];                                             // [n-tile][c0..c3]
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int c = vs0 + nt * 8 + 2 * t4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = srow + (e >> 1) * 8;
+      S[nt][e] = h0 ? h0[(((long long)seq * H + h) * DK + r) * DK + c + (e & 1)] : 0.f;
+    }
+    *(unsigned*)(Sb + srow * LS + nt * 8 + 2 * t4) = kda_pack2(S[nt][0], S[nt][1]);
+    *(unsigned*)(Sb + (srow + 8) * LS + nt * 8 + 2 * t4) = kda_pack2(S[nt][2], S[nt][3]);
+  }
+  auto fetchA = [&](int chunk, int buf) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    bf16* ws_ = setA + buf * SETA; bf16* kgs_ = ws_ + 64 * LD; bf16* us_ = kgs_ + 64 * LD; float* gl_ = (float*)(us_ + 64 * LS);
+#pragma unroll
+    for (int j = 0; j < 64 * (DK / 8) / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx >> 4, c8 = (idx & 15) * 8;
+      const long long off = (cbase + r) * DK + c8;
+      cp_async16(ws_ + r * LD + c8, w + off); cp_async16(kgs_ + r * LD + c8, kg + off);
+    }
+    { const int r = tid >> 2, c8 = (tid & 3) * 8; cp_async16(us_ + r * LS + c8, u + (cbase + r) * DK + vs0 + c8); }
+    if (tid < DK / 4) cp_async16(gl_ + tid * 4, G + (cbase + 63) * DK + tid * 4);
+  };
+  auto fetchB = [&](int chunk, int buf) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    bf16* qgs_ = setB + buf * SETB; bf16* Aq_ = qgs_ + 64 * LD;
+#pragma unroll
+    for (int j = 0; j < 64 * (DK / 8) / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx >> 4, c8 = (idx & 15) * 8;
+      cp_async16(qgs_ + r * LD + c8, qg + (cbase + r) * DK + c8);
+    }
+#pragma unroll
+    for (int j = 0; j < 64 * 8 / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx >> 3, c8 = (idx & 7) * 8;
+      cp_async16(Aq_ + r * LQ + c8, Aqk + (cbase + r) * 64 + c8);
+    }
+  };
+  fetchA(c_begin, 0); cp_async_commit();
+  fetchB(c_begin, 0); cp_async_commit();
+  cp_async_wait_all();
+  __syncthreads();
+
+  for (int chunk = c_begin; chunk < c_end; ++chunk) {
+    const long long cbase = ((long long)chunk * H + h) * 64;
+    const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+    const int a = (chunk - c_begin) & 1;
+    const bf16* ws = setA + a * SETA; const bf16* kgs = ws + 64 * LD; const bf16* us = kgs + 64 * LD;
+    const float* gl = (const float*)(us + 64 * LS);
+    const bf16* qgs = setB + a * SETB; const bf16* Aq = qgs + 64 * LD;
+    bf16* vn = vns + a * 64 * LS;
+
+    if (chunk + 1 < c_end) fetchA(chunk + 1, a ^ 1);          // set A of the previous chunk was released at its last barrier
+    cp_async_commit();
+    if (tid < DK) egl[tid] = __expf(gl[tid]);
+    // state at chunk start, for the backward pass
+#pragma unroll
+    for (int j = 0; j < DK * (VS / 8) / NTHR; ++j) {
+      const int idx = tid + j * NTHR, r = idx / (VS / 8), c8 = (idx % (VS / 8)) * 8;
+      *(uint4*)(S_out + (((long long)chunk * H + h) * DK + r) * DK + vs0 + c8) = *(const uint4*)(Sb + r * LS + c8);
+    }
+
+    // ---- P = w S (rows mt*16.., columns nh*16..), v_new = u - P. The B fragments of S are kept for the output product.
+    unsigned bS[8][4];
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      unsigned af[4];
+      kda_frag_a(af, ws, LD, mt * 16, kk * 16, lane);
+      kda_frag_b2(bS[kk], Sb, LS, kk * 16, nh * 16, lane);
+      kda_mma16816(acc[0], af, bS[kk][0], bS[kk][1]);
+      kda_mma16816(acc[1], af, bS[kk][2], bS[kk][3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int c = nh * 16 + nt * 8 + 2 * t4;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int r = mt * 16 + g + hh * 8;
+        const float2 uv = __bfloat1622float2(*(const __nv_bfloat162*)(us + r * LS + c));
+        const unsigned pk = kda_pack2(uv.x - acc[nt][2 * hh], uv.y - acc[nt][2 * hh + 1]);
+        *(unsigned*)(vn + r * LS + c) = pk;
+        *(unsigned*)(vnew_out + (cbase + r) * DK + vs0 + c) = pk;
+      }
+    }
+    __syncthreads();                                          // v_new complete; every warp is past its reads of Sb
+    if (chunk + 1 < c_end) fetchB(chunk + 1, a ^ 1);          // set B of the previous chunk: its output product is done
+    cp_async_commit();
+
+    // ---- S <- e^Glast S + kg^T v_new   (this warp's 16 state rows, all VS columns)
+    {
+      const float e0 = egl[srow], e1 = egl[srow + 8];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { S[nt][0] *= e0; S[nt][1] *= e0; S[nt][2] *= e1; S[nt][3] *= e1; }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        unsigned af[4], b0[4], b1[4];
+        kda_frag_a_t(af, kgs, LD, warp * 16, kk * 16, lane);
+        kda_frag_b2(b0, vn, LS, kk * 16, 0, lane);
+        kda_frag_b2(b1, vn, LS, kk * 16, 16, lane);
+        kda_mma16816(S[0], af, b0[0], b0[1]);
+        kda_mma16816(S[1], af, b0[2], b0[3]);
+        kda_mma16816(S[2], af, b1[0], b1[1]);
+        kda_mma16816(S[3], af, b1[2], b1[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        *(unsigned*)(Sb + srow * LS + nt * 8 + 2 * t4) = kda_pack2(S[nt][0], S[nt][1]);
+        *(unsigned*)(Sb + (srow + 8) * LS + nt * 8 + 2 * t4) = kda_pack2(S[nt][2], S[nt][3]);
+      }
+    }
+    cp_async_wait_group<1>();                                 // next chunk's set A (and this chunk's set B) have landed
+    __syncthreads();
+
+    // ---- o = qg S(chunk start) + Aqk v_new   (off the chain: uses the kept fragments of S)
+    {
+      float oc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        unsigned af[4];
+        kda_frag_a(af, qgs, LD, mt * 16, kk * 16, lane);
+        kda_mma16816(oc[0], af, bS[kk][0], bS[kk][1]);
+        kda_mma16816(oc[1], af, bS[kk][2], bS[kk][3]);
+      }
+      for (int kk = 0; kk <= mt; ++kk) {                      // Aqk is lower triangular in 16-row blocks
+        unsigned af[4], bv[4];
+        kda_frag_a(af, Aq, LQ, mt * 16, kk * 16, lane);
+        kda_frag_b2(bv, vn, LS, kk * 16, nh * 16, lane);
+        kda_mma16816(oc[0], af, bv[0], bv[1]);
+        kda_mma16816(oc[1], af, bv[2], bv[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int c = nh * 16 + nt * 8 + 2 * t4;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = mt * 16 + g + hh * 8;
+          if (r < len)
+            *(unsigned*)(o + ((long long)(t0 + r) * H + h) * DK + vs0 + c) = kda_pack2(oc[nt][2 * hh], oc[nt][2 * hh + 1]);
+        }
+      }
+    }
+  }
+  if (final_state) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int c = vs0 + nt * 8 + 2 * t4;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *(float2*)(final_state + (((long long)seq * H + h) * DK + srow + hh * 8) * DK + c) = make_float2(S[nt][2 * hh], S[nt][2 * hh + 1]);
+    }
+  }
+}
+
+template <int VS>
+constexpr int kda_state_mma_smem() {
+  return (2 * (2 * 64 * 136 + 64 * (VS + 8) + 2 * 128) + 2 * (64 * 136 + 64 * 72) + 128 * (VS + 8) + 2 * 64 * (VS + 8)) * 2 + 128 * 4 + 128;
+}
+
 template <int DK, int VS>
 constexpr int kda_state_smem() {
   return DK * (VS + 4) * 4 + 64 * (VS + 4) * 4 + DK * 4 + DK * (VS + 8) * 2 + 64 * (VS + 8) * 2 +
@@ -432,6 +628,13 @@ constexpr int kda_state_smem() {
 }  // namespace hippo
 
 using namespace hippo;
+
+// HIPPO_KDA_STATE_MMA=0 selects the WMMA state kernels for head_dim 128 as well (they always serve head_dim 64)
+static bool kda_state_mma_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("HIPPO_KDA_STATE_MMA"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
 
 template <int DK>
 static int launch_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta,
@@ -452,6 +655,19 @@ static int launch_fwd(const void* q, const void* k, const void* v, const float* 
   if (NC == 0) return 0;
   k1<<<dim3(NC, H), 512, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
                                                     G, (bf16*)w, (bf16*)u, (bf16*)qg, (bf16*)kg, (bf16*)Aqk, (bf16*)Ainv, (bf16*)Akk);
+  if (DK == 128 && kda_state_mma_enabled()) {
+    auto k3 = kda_fwd_state_mma_kernel<VS>;
+    static bool once3 = false;
+    if (!once3) {
+      cudaError_t e = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_state_mma_smem<VS>());
+      if (e != cudaSuccess) return (int)e;
+      once3 = true;
+    }
+    k3<<<dim3(DK / VS, H, N), 256, kda_state_mma_smem<VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
+                                                                  (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, so, H, h0,
+                                                                  (bf16*)vnew, (bf16*)Sst, (bf16*)o, fin);
+    return (int)cudaGetLastError();
+  }
   k2<<<dim3(DK / VS, H, N), 256, kda_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)u, (const bf16*)qg,
                                                                 (const bf16*)kg, (const bf16*)Aqk, G, cs, cl, sc, so, H, h0,
                                                                 (bf16*)vnew, (bf16*)Sst, (bf16*)o, fin);

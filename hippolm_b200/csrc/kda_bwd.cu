@@ -468,6 +468,134 @@ kda_bwd_dqkw_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew,
 template <int DK>
 constexpr int kda_bwd_dqkw_smem() { return 3 * 64 * (DK + 8) * 2 + 2 * DK * (DK + 8) * 2 + 16 * 2 * 320 * 4 + DK * 4 + 128; }
 
+// mma.sync variant for DK = 128: the four products of a chunk share one K loop (A fragments of do / v_new / dv_new,
+// B fragments of S^T and dS^T loaded once per step) and the epilogue works on the accumulator fragments directly.
+// 16 warps: warp (rt, ng) owns rows rt*16.. and columns ng*32.. of dqg / dkg / dw, and tile (rt, ct = ng) of dAqk.
+__global__ void __launch_bounds__(512, 1)
+kda_bwd_dqkw_mma_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ vnew, const bf16* __restrict__ dvn,
+                        const bf16* __restrict__ Sst, const bf16* __restrict__ dSst, const bf16* __restrict__ qg,
+                        const bf16* __restrict__ kg, const float* __restrict__ G, const int* __restrict__ chunk_start,
+                        const int* __restrict__ chunk_len, int H, float* __restrict__ dq_acc, float* __restrict__ dk_acc,
+                        float* __restrict__ dG_acc, bf16* __restrict__ dw_out, bf16* __restrict__ dAqk_out) {
+  constexpr int DK = 128, LD = DK + 8;
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* dos = (bf16*)smem;            // [64][LD]
+  bf16* vns = dos + 64 * LD;
+  bf16* dvs = vns + 64 * LD;
+  bf16* Ss = dvs + 64 * LD;           // [DK][LD]   S[c][v]
+  bf16* dSs = Ss + DK * LD;           // [DK][LD]
+  float* dGl = (float*)(dSs + DK * LD);   // [DK]
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const long long cbase = ((long long)chunk * H + h) * 64;
+  const long long sbase = ((long long)chunk * H + h) * DK;
+
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 512) {
+    const int r = idx >> 4, c8 = (idx & 15) * 8;
+    cp_async16(dos + r * LD + c8, d_o + ((long long)(t0 + (r < len ? r : 0)) * H + h) * DK + c8, r < len ? 16 : 0);
+    cp_async16(vns + r * LD + c8, vnew + (cbase + r) * DK + c8);
+    cp_async16(dvs + r * LD + c8, dvn + (cbase + r) * DK + c8);
+  }
+  for (int idx = tid; idx < DK * (DK / 8); idx += 512) {
+    const int r = idx >> 4, c8 = (idx & 15) * 8;
+    cp_async16(Ss + r * LD + c8, Sst + (sbase + r) * DK + c8);
+    cp_async16(dSs + r * LD + c8, dSst + (sbase + r) * DK + c8);
+  }
+  cp_async_commit();
+  if (tid < DK) dGl[tid] = 0.f;
+  cp_async_wait_all();
+  __syncthreads();
+  // state-decay term of dGlast: sum_v dS[c,v] S[c,v] e^Glast[c]   (4 threads per state row)
+  {
+    const int c = tid >> 2, part = tid & 3;
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 a = *(const uint4*)(Ss + c * LD + part * 32 + j * 8), b = *(const uint4*)(dSs + c * LD + part * 32 + j * 8);
+      const __nv_bfloat162* ab = (const __nv_bfloat162*)&a; const __nv_bfloat162* bb = (const __nv_bfloat162*)&b;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 x = __bfloat1622float2(ab[e]), y = __bfloat1622float2(bb[e]); s += x.x * y.x + x.y * y.y; }
+    }
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    if (part == 0) atomicAdd(&dGl[c], s * __expf(G[(cbase + 63) * DK + c]));
+  }
+  const int rt = warp & 3, ng = warp >> 2;
+  float aq[4][4], ak[4][4], aw[4][4], aa[2][4];
+#pragma unroll
+  for (int n = 0; n < 4; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { aq[n][e] = 0.f; ak[n][e] = 0.f; aw[n][e] = 0.f; }
+#pragma unroll
+  for (int n = 0; n < 2; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) aa[n][e] = 0.f;
+  const bool do_a = ng <= rt;                        // lower-triangular 16x16 tiles of dAqk
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    unsigned fo[4], fv[4], fd[4], b0[4], b1[4];
+    kda_frag_a(fo, dos, LD, rt * 16, kk * 16, lane);
+    kda_frag_a(fv, vns, LD, rt * 16, kk * 16, lane);
+    kda_frag_a(fd, dvs, LD, rt * 16, kk * 16, lane);
+    kda_frag_bt2(b0, Ss, LD, ng * 32, kk * 16, lane);        // S^T: n = state row c, k = v
+    kda_frag_bt2(b1, Ss, LD, ng * 32 + 16, kk * 16, lane);
+    kda_mma16816(aq[0], fo, b0[0], b0[1]); kda_mma16816(aq[1], fo, b0[2], b0[3]);
+    kda_mma16816(aq[2], fo, b1[0], b1[1]); kda_mma16816(aq[3], fo, b1[2], b1[3]);
+    kda_mma16816(aw[0], fd, b0[0], b0[1]); kda_mma16816(aw[1], fd, b0[2], b0[3]);
+    kda_mma16816(aw[2], fd, b1[0], b1[1]); kda_mma16816(aw[3], fd, b1[2], b1[3]);
+    kda_frag_bt2(b0, dSs, LD, ng * 32, kk * 16, lane);
+    kda_frag_bt2(b1, dSs, LD, ng * 32 + 16, kk * 16, lane);
+    kda_mma16816(ak[0], fv, b0[0], b0[1]); kda_mma16816(ak[1], fv, b0[2], b0[3]);
+    kda_mma16816(ak[2], fv, b1[0], b1[1]); kda_mma16816(ak[3], fv, b1[2], b1[3]);
+    if (do_a) {
+      kda_frag_bt2(b0, vns, LD, ng * 16, kk * 16, lane);     // v_new^T: n = chunk row j, k = v
+      kda_mma16816(aa[0], fo, b0[0], b0[1]); kda_mma16816(aa[1], fo, b0[2], b0[3]);
+    }
+  }
+  // ---- epilogue on the fragments: thread holds rows i0, i0+8 and column pairs c, c+1 of each n-tile
+  const int i0 = rt * 16 + g;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int c = ng * 32 + n * 8 + 2 * t4;
+    const float2 gl = *(const float2*)(G + (cbase + 63) * DK + c);
+    float cs0 = 0.f, cs1 = 0.f;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const long long off = (cbase + i0 + hh * 8) * DK + c;
+      const float2 Gi = *(const float2*)(G + off);
+      const float2 qv = __bfloat1622float2(*(const __nv_bfloat162*)(qg + off));
+      const float2 kv = __bfloat1622float2(*(const __nv_bfloat162*)(kg + off));
+      const float dq0 = aq[n][2 * hh], dq1 = aq[n][2 * hh + 1], dk0 = ak[n][2 * hh], dk1 = ak[n][2 * hh + 1];
+      *(float2*)(dq_acc + off) = make_float2(dq0 * __expf(Gi.x), dq1 * __expf(Gi.y));
+      *(float2*)(dk_acc + off) = make_float2(dk0 * __expf(gl.x - Gi.x), dk1 * __expf(gl.y - Gi.y));
+      *(float2*)(dG_acc + off) = make_float2(dq0 * qv.x - dk0 * kv.x, dq1 * qv.y - dk1 * kv.y);
+      cs0 += dk0 * kv.x; cs1 += dk1 * kv.y;
+      *(unsigned*)(dw_out + off) = kda_pack2(-aw[n][2 * hh], -aw[n][2 * hh + 1]);
+    }
+    // column sums over the 16 rows of this tile: lanes with the same t4
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) { cs0 += __shfl_xor_sync(0xFFFFFFFFu, cs0, o); cs1 += __shfl_xor_sync(0xFFFFFFFFu, cs1, o); }
+    if (g == 0) { atomicAdd(&dGl[c], cs0); atomicAdd(&dGl[c + 1], cs1); }
+  }
+  // dAqk = tril(do v_new^T): warp (rt, ct = ng) writes its 16x16 tile, zeros above the diagonal
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int j = ng * 16 + n * 8 + 2 * t4;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int i = i0 + hh * 8;
+      const float v0 = (do_a && j <= i) ? aa[n][2 * hh] : 0.f, v1 = (do_a && j + 1 <= i) ? aa[n][2 * hh + 1] : 0.f;
+      *(unsigned*)(dAqk_out + (cbase + i) * 64 + j) = kda_pack2(v0, v1);
+    }
+  }
+  __syncthreads();
+  // the element (63, c) of dG_acc was written above by the warp owning row 63; its writer is inside this CTA
+  if (tid < DK) dG_acc[(cbase + 63) * DK + tid] += dGl[tid];
+}
+constexpr int kda_bwd_dqkw_mma_smem() { return 3 * 64 * 136 * 2 + 2 * 128 * 136 * 2 + 128 * 4 + 128; }
+
 // =================================================================================================== WY
 template <int DK>
 __global__ void __launch_bounds__(256, 2)
@@ -878,6 +1006,17 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
   } else
   k3<<<dim3(DK / VS, H, N), 256, kda_bwd_state_smem<DK, VS>(), s>>>((const bf16*)w, (const bf16*)qg, (const bf16*)kg,
       (const bf16*)Aqk, G, (const bf16*)d_o, cs, cl, sc, so, H, dfinal, (bf16*)dvn, (bf16*)dSst, dh0);
+  if (DK == 128 && kda_bwd_state_mma_enabled()) {
+    static bool once4 = false;
+    if (!once4) {
+      cudaError_t e = cudaFuncSetAttribute(kda_bwd_dqkw_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_dqkw_mma_smem());
+      if (e != cudaSuccess) return (int)e;
+      once4 = true;
+    }
+    kda_bwd_dqkw_mma_kernel<<<dim3(NC, H), 512, kda_bwd_dqkw_mma_smem(), s>>>((const bf16*)d_o, (const bf16*)vnew,
+        (const bf16*)dvn, (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc,
+        dG_acc, (bf16*)dw, (bf16*)dAqk);
+  } else
   k4a<<<dim3(NC, H), 512, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
       (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc, dG_acc,
       (bf16*)dw, (bf16*)dAqk);

@@ -44,6 +44,11 @@ __device__ __forceinline__ void kda_frag_a_t(unsigned (&r)[4], const bf16* tile,
 __device__ __forceinline__ void kda_frag_b2(unsigned (&r)[4], const bf16* tile, int ld, int k0, int n0, int lane) {
   kda_ldsm_x4_t(r, tile + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + n0 + (lane >> 4) * 8);
 }
+// B fragments of two adjacent n-tiles from a row-major [n][ld] tile (k contiguous, i.e. B^T is stored):
+// r[0], r[1] -> n-tile at n0, r[2], r[3] -> n-tile at n0 + 8
+__device__ __forceinline__ void kda_frag_bt2(unsigned (&r)[4], const bf16* tile, int ld, int n0, int k0, int lane) {
+  kda_ldsm_x4(r, tile + (n0 + (lane & 7) + (lane >> 4) * 8) * ld + k0 + ((lane >> 3) & 1) * 8);
+}
 __device__ __forceinline__ unsigned kda_pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);

@@ -108,7 +108,7 @@ def main():
     a = parse()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "pip install of /root/reference failed: directory is not installable (no setup.py / "
+                          "pip install of the reference tree failed: directory is not installable (no setup.py / "
                           "pyproject.toml); the reference also has no full-attention layers, sequence parallelism "
                           "or sm_100 NVFP4 path, so this config cannot run on its stock code path"}))
         return 0

@@ -2,7 +2,7 @@
 
 ``setup()`` allocates the symmetric workspace for the current TP group and switches the
 sequence-parallel linears from "NCCL then GEMM" to the single-kernel paths in
-``csrc/fused_comm.cu``. Until it is called (or on CPU) ``enabled()`` is False and the NCCL/gloo
+``csrc/gemm_bf16.cu`` / ``csrc/gemm_fp4.cu`` / ``csrc/lce_fused.cu``. Until it is called (or on CPU) ``enabled()`` is False and the NCCL/gloo
 baseline runs.
 """
 from __future__ import annotations

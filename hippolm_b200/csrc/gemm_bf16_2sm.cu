@@ -110,6 +110,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       bool ok = true;
       for (int t = cid; t < num_tiles && ok; t += n_clusters) {
         int tm, tn; tile_coord(t, tm, tn);
+        if (p.sym_lower && tn > tm) continue;                  // symmetric output: tiles above the diagonal are mirrored later
         const int row0 = (tm * 2 + (int)rank) * BM;            // this CTA's rows of A / C
         const int col0 = tn * BN + (int)rank * BNH;            // this CTA's half of the B tile
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -139,9 +140,11 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, 1, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
       int it = 0, tl = 0;
       bool ok = true;
-      for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
-        int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
-        ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl);
+      for (int t = cid; t < num_tiles && ok; t += n_clusters) {
+        if (p.sym_lower) { int tm, tn; tile_coord(t, tm, tn); if (tn > tm) continue; }
+        const int tl_now = tl++;
+        int acc = tl_now & 1; uint32_t aph = (tl_now >> 1) & 1;
+        ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl_now);
         if (!ok) break;
         tc_fence_after();
         uint32_t d_tmem = tmem_base + acc * BN;
@@ -172,10 +175,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     int tl = 0;
     bool ok = true;
-    for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
+    for (int t = cid; t < num_tiles && ok; t += n_clusters) {
       int tm, tn; tile_coord(t, tm, tn);
-      int acc = tl & 1; uint32_t aph = (tl >> 1) & 1;
-      ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl);
+      if (p.sym_lower && tn > tm) continue;
+      const int tl_now = tl++;
+      int acc = tl_now & 1; uint32_t aph = (tl_now >> 1) & 1;
+      ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl_now);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -234,6 +239,23 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
 
 }  // namespace sm2
 
+// C[i][j] = C[j][i] for j > i (bf16, n x n, pitch ldc): fills the tiles a symmetric-output GEMM skipped.
+__global__ void symmetrize_lower_kernel(__nv_bfloat16* __restrict__ C, int n, long long ldc) {
+  __shared__ __nv_bfloat16 tile[32][34];
+  const int bi = blockIdx.y, bj = blockIdx.x;             // source block (rows bi*32.., cols bj*32..) with bj <= bi
+  if (bj > bi) return;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    const int i = bi * 32 + r, j = bj * 32 + tx;
+    tile[r][tx] = (i < n && j < n) ? C[(long long)i * ldc + j] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int i = bj * 32 + r, j = bi * 32 + tx;          // destination element (i, j) = source (j, i)
+    if (i < n && j < n && j > i) C[(long long)i * ldc + j] = tile[tx][r];
+  }
+}
+
 bool gemm_2sm_enabled() {
   static int v = -1;
   if (v < 0) { const char* e = getenv("HIPPO_GEMM_2SM"); v = (e && e[0] == '0') ? 0 : 1; }
@@ -264,6 +286,24 @@ extern "C" int hippo_gemm_bf16_2sm(const void* A, const void* B, void* C, const 
   if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
-  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0;
+  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0;
   return launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
+}
+
+// Symmetric product (C = C^T by construction, e.g. X X^T or S S + S with S symmetric), bf16 n x n output: only the
+// tiles on or below the diagonal are computed, then mirrored. Same arguments as hippo_gemm_bf16_2sm otherwise.
+extern "C" int hippo_gemm_bf16_sym(const void* A, const void* B, void* C, const void* Cin, int n, int K, long long lda,
+                                   long long ldb, long long ldc, long long ldcin, int layout, float alpha, float beta,
+                                   void* stream) {
+  using namespace hippo;
+  if (n <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (ldc % 8) || ((uintptr_t)C & 15)) return -2;
+  GemmParams p;
+  p.M = n; p.N = n; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = 0; p.accumulate = 0; p.alpha = alpha;
+  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 1;
+  int rc = launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
+  if (rc) return rc;
+  const unsigned nb = (unsigned)((n + 31) / 32);
+  symmetrize_lower_kernel<<<dim3(nb, nb), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)C, n, ldc);
+  return (int)cudaGetLastError();
 }

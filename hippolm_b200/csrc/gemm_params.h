@@ -15,6 +15,7 @@ struct GemmParams {
   const void* Cin;     // optional bf16 [M, ldcin] addend: C = alpha*A*B + beta*Cin (bf16 output only)
   long long ldcin; float beta;
   int tiles_m, tiles_n;
+  int sym_lower;       // CTA-pair kernel: skip the 256x256 tiles above the diagonal (square symmetric output)
 };
 
 #ifdef __CUDACC__

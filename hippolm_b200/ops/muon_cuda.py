@@ -19,6 +19,18 @@ def _gemm_ex(a, b, out, cin, M, N, K, layout, alpha, beta):
                                    C.c_float(beta), stream_ptr()), "gemm_bf16_ex")
 
 
+def _gemm_sym(a, b, out, cin, n, K, layout, alpha, beta):
+    """Square symmetric product (X X^T, X^T X, c S S + b S): only the tiles on or below the diagonal are computed by the
+    CTA-pair kernel and then mirrored, which halves the cost of these steps."""
+    check(lib().hippo_gemm_bf16_sym(ptr(a), ptr(b), ptr(out), ptr(cin), n, K, C.c_longlong(a.stride(0)),
+                                    C.c_longlong(b.stride(0)), C.c_longlong(out.stride(0)),
+                                    C.c_longlong(cin.stride(0) if cin is not None else 0), layout, C.c_float(alpha),
+                                    C.c_float(beta), stream_ptr()), "gemm_bf16_sym")
+
+
+_SYM_MIN = 512          # below this the mirror pass costs more than the skipped tiles
+
+
 def supported(rows: int, cols: int) -> bool:
     return rows % 8 == 0 and cols % 8 == 0 and (rows * cols) % 8 == 0
 
@@ -44,13 +56,22 @@ def newton_schulz_(u: torch.Tensor, ssq: torch.Tensor, steps: int = 5, eps: floa
     Mm = torch.empty((n, n), dtype=torch.bfloat16, device=u.device)
     X, Xn = u, torch.empty_like(u)
     for _ in range(steps):
+        sym = n >= _SYM_MIN
         if rows <= cols:
-            _gemm_ex(X, X, S, None, n, n, cols, 0, 1.0, 0.0)                 # S = X X^T
-            _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)                        # M = c S S + b S
+            if sym:
+                _gemm_sym(X, X, S, None, n, cols, 0, 1.0, 0.0)               # S = X X^T  (lower tiles + mirror)
+                _gemm_sym(S, S, Mm, S, n, n, 1, _C, _B)                      # M = c S S + b S
+            else:
+                _gemm_ex(X, X, S, None, n, n, cols, 0, 1.0, 0.0)
+                _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)
             _gemm_ex(Mm, X, Xn, X, rows, cols, n, 1, 1.0, _A)                # X' = M X + a X
         else:
-            _gemm_ex(X, X, S, None, n, n, rows, 2, 1.0, 0.0)                 # S = X^T X
-            _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)
+            if sym:
+                _gemm_sym(X, X, S, None, n, rows, 2, 1.0, 0.0)               # S = X^T X
+                _gemm_sym(S, S, Mm, S, n, n, 1, _C, _B)
+            else:
+                _gemm_ex(X, X, S, None, n, n, rows, 2, 1.0, 0.0)
+                _gemm_ex(S, S, Mm, S, n, n, n, 1, _C, _B)
             _gemm_ex(X, Mm, Xn, X, rows, cols, n, 1, 1.0, _A)                # X' = X M + a X
         X, Xn = Xn, X
     return X

@@ -65,3 +65,26 @@ def test_gemm_one_cta_and_cta_pair_kernels(kernel, M, N, K):
     assert (out - (1.0 + 0.5 * ref)).abs().max() < tol
     torch.cuda.synchronize()
     assert _ext.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("n,K", [(512, 256), (1000, 328), (2048, 1024)])
+def test_symmetric_output_gemm(n, K):
+    """X X^T and c S S + b S through the lower-tiles-then-mirror path against the fp32 products."""
+    from hippolm_b200.ops import muon_cuda as mc, _ext
+    _ext.clear_device_status()
+    g = torch.Generator(device="cuda").manual_seed(n + K)
+    x = torch.randn(n, K, device="cuda", generator=g).bfloat16()
+    S = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+    mc._gemm_sym(x, x, S, None, n, K, 0, 1.0, 0.0)
+    ref = x.float() @ x.float().t()
+    assert (S.float() - ref).abs().max() < 2e-2 * (K ** 0.5) * 4
+    assert torch.equal(S, S.t())
+    M = torch.empty_like(S)
+    Ss = (S.float() / n).bfloat16()
+    Ss = torch.tril(Ss) + torch.tril(Ss, -1).t()
+    mc._gemm_sym(Ss, Ss, M, Ss, n, n, 1, 0.5, 2.0)
+    ref2 = 0.5 * (Ss.float() @ Ss.float()) + 2.0 * Ss.float()
+    assert (M.float() - ref2).abs().max() < 3e-2 * max(1.0, float(ref2.abs().max()))
+    assert torch.equal(M, M.t())
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0

@@ -89,7 +89,7 @@ def test_muon_fused_device_path_matches_reference():
     from hippolm_b200.optim.optimizers import Muon
     from hippolm_b200.ref.ops import newton_schulz5
     torch.manual_seed(0)
-    for shape in ((256, 512), (768, 256)):
+    for shape in ((256, 512), (768, 256), (1024, 1536), (1536, 640)):     # the last two take the symmetric-tile GEMMs
         p = nn.Parameter(torch.randn(*shape, device="cuda").bfloat16())
         g = (0.1 * torch.randn(*shape, device="cuda")).bfloat16()
         p.grad = g.clone()

@@ -77,7 +77,7 @@ def test_symmetric_output_gemm(n, K):
     S = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
     mc._gemm_sym(x, x, S, None, n, K, 0, 1.0, 0.0)
     ref = x.float() @ x.float().t()
-    assert (S.float() - ref).abs().max() < 2e-2 * (K ** 0.5) * 4
+    assert bool(((S.float() - ref).abs() <= 8e-3 * ref.abs() + 2e-2 * (K ** 0.5)).all())     # bf16 output rounding
     assert torch.equal(S, S.t())
     M = torch.empty_like(S)
     Ss = (S.float() / n).bfloat16()

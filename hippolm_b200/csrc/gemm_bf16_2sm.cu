@@ -78,7 +78,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int num_tiles = p.tiles_m * p.tiles_n;                 // pair tiles (256 x 256)
+  // pair tiles (256 x 256); a symmetric-output launch enumerates only the tiles on or below the diagonal
+  const int num_tiles = p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
   const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
 
@@ -96,6 +97,13 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const uint32_t tmem_base = *tmem_slot;  // whole TMEM of the SM: the same address in both CTAs
 
   auto tile_coord = [&](int t, int& tm, int& tn) {
+    if (p.sym_lower) {                    // row-major walk of the lower triangle: t = tm (tm + 1) / 2 + tn
+      tm = (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f);
+      while ((tm + 1) * (tm + 2) / 2 <= t) ++tm;
+      while (tm * (tm + 1) / 2 > t) --tm;
+      tn = t - tm * (tm + 1) / 2;
+      return;
+    }
     const int GROUP = 8;                  // 8 pair-tiles (2048 rows) share each column sweep
     int per_group = GROUP * p.tiles_n;
     int g = t / per_group, r = t % per_group;
@@ -110,7 +118,6 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       bool ok = true;
       for (int t = cid; t < num_tiles && ok; t += n_clusters) {
         int tm, tn; tile_coord(t, tm, tn);
-        if (p.sym_lower && tn > tm) continue;                  // symmetric output: tiles above the diagonal are mirrored later
         const int row0 = (tm * 2 + (int)rank) * BM;            // this CTA's rows of A / C
         const int col0 = tn * BN + (int)rank * BNH;            // this CTA's half of the B tile
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -141,7 +148,6 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int it = 0, tl = 0;
       bool ok = true;
       for (int t = cid; t < num_tiles && ok; t += n_clusters) {
-        if (p.sym_lower) { int tm, tn; tile_coord(t, tm, tn); if (tn > tm) continue; }
         const int tl_now = tl++;
         int acc = tl_now & 1; uint32_t aph = (tl_now >> 1) & 1;
         ok = mbar_wait(&tempty[acc], aph ^ 1, kWaitTmemEmpty, tl_now);
@@ -177,7 +183,6 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     bool ok = true;
     for (int t = cid; t < num_tiles && ok; t += n_clusters) {
       int tm, tn; tile_coord(t, tm, tn);
-      if (p.sym_lower && tn > tm) continue;
       const int tl_now = tl++;
       int acc = tl_now & 1; uint32_t aph = (tl_now >> 1) & 1;
       ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl_now);
@@ -225,7 +230,8 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   int clusters = sms / 2;
   if (clusters < 1) clusters = 1;
-  if (tiles < clusters) clusters = tiles;
+  const int work = p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : tiles;
+  if (work < clusters) clusters = work;
   auto kern = gemm_bf16_2sm_kernel<AK, BK_>;
   static bool attr_set = false;
   if (!attr_set) {

@@ -40,7 +40,7 @@ def parse():
     p.add_argument("--impl", type=str, default="ours")
     p.add_argument("--model", type=str, default="7b", help="7b | 1p3b | tiny (tiny/1p3b are for smoke runs only)")
     p.add_argument("--micro_batch_tokens", type=int, default=0,
-                   help="tokens per micro-batch; 0 = 8192 on one GPU (activations of 32 layers must fit), 16384 otherwise")
+                   help="tokens per micro-batch; 0 = 8192 x number of GPUs (activations per rank stay constant under TP + SP)")
     p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
     p.add_argument("--no_fused_comm", action="store_true")
     p.add_argument("--bf16_ffn", action="store_true")

@@ -773,6 +773,184 @@ kda_bwd_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, const 
 template <int DK>
 constexpr int kda_bwd_wy_smem() { return 3 * 64 * 72 * 2 + 4 * 64 * (DK + 8) * 2 + 8 * 320 * 4 + 128 * 4 + 128; }
 
+// mma.sync variant for DK = 128: every product works on accumulator fragments (no staging tile), the epilogues run on
+// the fragments directly. 8 warps, two CTAs per SM.
+__global__ void __launch_bounds__(256, 2)
+kda_bwd_wy_mma_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, const float* __restrict__ beta,
+                      const float* __restrict__ G, const bf16* __restrict__ Ainv, const bf16* __restrict__ Akk,
+                      const bf16* __restrict__ dvn, const bf16* __restrict__ dw, const int* __restrict__ chunk_start,
+                      const int* __restrict__ chunk_len, int H, bf16* __restrict__ dbk_out,
+                      bf16* __restrict__ dv_out, float* __restrict__ dbeta_out, bf16* __restrict__ dKK_out) {
+  constexpr int DK = 128, LD = DK + 8, LX = 72;
+  extern __shared__ __align__(128) uint8_t smem[];
+  bf16* Xb = (bf16*)smem;             // [64][LX]  X = (I + Akk)^-1
+  bf16* dXb = Xb + 64 * LX;           // [64][LX]
+  bf16* Yb = dXb + 64 * LX;           // [64][LX]
+  bf16* dus = Yb + 64 * LX;           // [64][LD]  dv_new
+  bf16* dws = dus + 64 * LD;          // [64][LD]  dw
+  bf16* bks = dws + 64 * LD;          // beta k e^G
+  bf16* bvs = bks + 64 * LD;          // beta v
+  float* bs = (float*)(bvs + 64 * LD);    // [64]
+  float* dbs = bs + 64;               // [64]
+  const int chunk = blockIdx.x, h = blockIdx.y;
+  const int t0 = chunk_start[chunk], len = chunk_len[chunk];
+  if (len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const long long cbase = ((long long)chunk * H + h) * 64;
+
+  if (tid < 64) { bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f; dbs[tid] = 0.f; }
+  for (int idx = tid; idx < 64 * 8; idx += 256) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    cp_async16(Xb + r * LX + c8, Ainv + (cbase + r) * 64 + c8);
+  }
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    const int r = idx >> 4, c8 = (idx & 15) * 8;
+    cp_async16(dus + r * LD + c8, dvn + (cbase + r) * DK + c8);
+    cp_async16(dws + r * LD + c8, dw + (cbase + r) * DK + c8);
+  }
+  cp_async_commit();
+  __syncthreads();                                 // bs visible
+  for (int idx = tid; idx < 64 * (DK / 8); idx += 256) {
+    const int i = idx >> 4, c8 = (idx & 15) * 8;
+    uint4 kq = make_uint4(0, 0, 0, 0), vq = kq;
+    if (i < len) {
+      const long long off = ((long long)(t0 + i) * H + h) * DK + c8;
+      kq = *(const uint4*)(k + off); vq = *(const uint4*)(v + off);
+    }
+    const float4 g0 = *(const float4*)(G + (cbase + i) * DK + c8), g1 = *(const float4*)(G + (cbase + i) * DK + c8 + 4);
+    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const __nv_bfloat162* kb = (const __nv_bfloat162*)&kq; const __nv_bfloat162* vb = (const __nv_bfloat162*)&vq;
+    uint4 ok, ov;
+    unsigned* okw = (unsigned*)&ok; unsigned* ovw = (unsigned*)&ov;
+    const float b = bs[i];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 kf = __bfloat1622float2(kb[e]), vf = __bfloat1622float2(vb[e]);
+      okw[e] = kda_pack2(b * kf.x * __expf(gv[2 * e]), b * kf.y * __expf(gv[2 * e + 1]));
+      ovw[e] = kda_pack2(b * vf.x, b * vf.y);
+    }
+    *(uint4*)(bks + i * LD + c8) = ok;
+    *(uint4*)(bvs + i * LD + c8) = ov;
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  // ---- dX = du bv^T + dw bk^T  (only the lower triangle feeds dAkk); 16x16 tiles (rt, ct)
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    if (ct <= rt) {
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        unsigned a[4], b[4];
+        kda_frag_a(a, dus, LD, rt * 16, kk * 16, lane);
+        kda_frag_bt2(b, bvs, LD, ct * 16, kk * 16, lane);
+        kda_mma16816(acc[0], a, b[0], b[1]); kda_mma16816(acc[1], a, b[2], b[3]);
+        kda_frag_a(a, dws, LD, rt * 16, kk * 16, lane);
+        kda_frag_bt2(b, bks, LD, ct * 16, kk * 16, lane);
+        kda_mma16816(acc[0], a, b[0], b[1]); kda_mma16816(acc[1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *(unsigned*)(dXb + (rt * 16 + g + hh * 8) * LX + ct * 16 + n * 8 + 2 * t4) = kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
+  }
+  __syncthreads();
+  // ---- Y = X^T dX
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    for (int kt = rt; kt < 4; ++kt) {              // X^T[i,m] = X[m,i], non-zero for m >= i
+      unsigned a[4], b[4];
+      kda_frag_a_t(a, Xb, LX, rt * 16, kt * 16, lane);
+      kda_frag_b2(b, dXb, LX, kt * 16, ct * 16, lane);
+      kda_mma16816(acc[0], a, b[0], b[1]); kda_mma16816(acc[1], a, b[2], b[3]);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *(unsigned*)(Yb + (rt * 16 + g + hh * 8) * LX + ct * 16 + n * 8 + 2 * t4) = kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
+  }
+  __syncthreads();
+  // ---- dM = -Y X^T ; dAkk = strict_lower(dM) ; dKK = beta_i dAkk ; dbeta_i += sum_j dAkk Akk / beta_i
+  for (int t = warp; t < 16; t += 8) {
+    const int rt = t >> 2, ct = t & 3;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    if (ct <= rt) {
+      for (int kt = 0; kt <= ct; ++kt) {           // X^T[n,j] = X[j,n], non-zero for n <= j
+        unsigned a[4], b[4];
+        kda_frag_a(a, Yb, LX, rt * 16, kt * 16, lane);
+        kda_frag_bt2(b, Xb, LX, ct * 16, kt * 16, lane);
+        kda_mma16816(acc[0], a, b[0], b[1]); kda_mma16816(acc[1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int i = rt * 16 + g + hh * 8;
+      const float bi = bs[i];
+      float rowsum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int j = ct * 16 + n * 8 + 2 * t4;
+        const float d0 = j < i ? -acc[n][2 * hh] : 0.f, d1 = j + 1 < i ? -acc[n][2 * hh + 1] : 0.f;
+        const float2 av = __bfloat1622float2(*(const __nv_bfloat162*)(Akk + (cbase + i) * 64 + j));
+        rowsum += d0 * av.x + d1 * av.y;
+        *(unsigned*)(dKK_out + (cbase + i) * 64 + j) = kda_pack2(d0 * bi, d1 * bi);
+      }
+      rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
+      rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 2);
+      if (t4 == 0 && bi > 0.f) atomicAdd(&dbs[i], rowsum / bi);
+    }
+  }
+  // ---- dbv = X^T du -> dv, dbeta ;  dbk = X^T dw -> consumed by the A-matrix kernel
+  {
+    const int which = warp >> 2, rt = warp & 3;
+    const bf16* B = which ? dws : dus;
+    float acc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) { acc[n][0] = 0.f; acc[n][1] = 0.f; acc[n][2] = 0.f; acc[n][3] = 0.f; }
+    for (int kt = rt; kt < 4; ++kt) {
+      unsigned a[4];
+      kda_frag_a_t(a, Xb, LX, rt * 16, kt * 16, lane);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        unsigned b[4];
+        kda_frag_b2(b, B, LD, kt * 16, np * 16, lane);
+        kda_mma16816(acc[2 * np], a, b[0], b[1]); kda_mma16816(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int i = rt * 16 + g + hh * 8;
+      if (!which) {
+        // dv = beta * dbv ; dbeta += sum_c v * dbv  (v recovered from the beta*v tile)
+        const float bi = bs[i], inv_b = bi > 0.f ? 1.f / bi : 0.f;
+        float rowsum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          const int c = n * 8 + 2 * t4;
+          const float v0 = acc[n][2 * hh], v1 = acc[n][2 * hh + 1];
+          const float2 bv = __bfloat1622float2(*(const __nv_bfloat162*)(bvs + i * LD + c));
+          rowsum += (bv.x * v0 + bv.y * v1) * inv_b;
+          if (i < len) *(unsigned*)(dv_out + ((long long)(t0 + i) * H + h) * DK + c) = kda_pack2(bi * v0, bi * v1);
+        }
+        rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 1);
+        rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, 2);
+        if (t4 == 0 && i < len) atomicAdd(&dbs[i], rowsum);
+      } else {
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+          *(unsigned*)(dbk_out + (cbase + i) * DK + n * 8 + 2 * t4) = kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < len) dbeta_out[(long long)(t0 + tid) * H + h] = dbs[tid];
+}
+constexpr int kda_bwd_wy_mma_smem() { return 3 * 64 * 72 * 2 + 4 * 64 * 136 * 2 + 128 * 4 + 128; }
+
 // =================================================================================================== A matrices
 template <int DK>
 __global__ void __launch_bounds__(4 * DK, 1)
@@ -1020,6 +1198,16 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
   k4a<<<dim3(NC, H), 512, kda_bwd_dqkw_smem<DK>(), s>>>((const bf16*)d_o, (const bf16*)vnew, (const bf16*)dvn,
       (const bf16*)Sst, (const bf16*)dSst, (const bf16*)qg, (const bf16*)kg, G, cs, cl, H, dq_acc, dk_acc, dG_acc,
       (bf16*)dw, (bf16*)dAqk);
+  if (DK == 128 && kda_bwd_state_mma_enabled()) {
+    static bool once5 = false;
+    if (!once5) {
+      cudaError_t e = cudaFuncSetAttribute(kda_bwd_wy_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_bwd_wy_mma_smem());
+      if (e != cudaSuccess) return (int)e;
+      once5 = true;
+    }
+    kda_bwd_wy_mma_kernel<<<dim3(NC, H), 256, kda_bwd_wy_mma_smem(), s>>>((const bf16*)k, (const bf16*)v, beta, G,
+        (const bf16*)Ainv, (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, (bf16*)dbk, (bf16*)dv, dbeta, (bf16*)dKK);
+  } else
   k4b<<<dim3(NC, H), 256, kda_bwd_wy_smem<DK>(), s>>>((const bf16*)k, (const bf16*)v, beta, G, (const bf16*)Ainv,
       (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, (bf16*)dbk, (bf16*)dv, dbeta, (bf16*)dKK);
   k4c<<<dim3(NC, H), 4 * DK, kda_bwd_amat_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, G, beta, (const bf16*)dbk,

@@ -70,8 +70,14 @@ class _Entry:
 class Muon:
     def __init__(self, lr: float = 0.02, momentum: float = 0.95, weight_decay: float = 0.0,
                  nesterov: bool = True, ns_steps: int = 5, momentum_dtype=torch.bfloat16,
-                 offload: bool = False, ns_row_chunk: Optional[int] = None, ns_scope: str = "shard"):
+                 offload: bool = False, ns_row_chunk: Optional[int] = None, ns_scope: str = "shard",
+                 dp_shard: bool = False):
         self.ns_scope = ns_scope
+        # Under data parallelism every matrix has one owner among the DP replicas (greedy by size): only the owner runs
+        # momentum + Newton-Schulz + the update, then broadcasts the new weights to its DP peers. Cuts the Muon work per
+        # rank by the DP degree; the reference has neither data parallelism nor this split.
+        self.dp_shard = dp_shard
+        self._owners: Optional[List[int]] = None
         self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.nesterov, self.ns_steps = nesterov, ns_steps
         self.momentum_dtype = momentum_dtype
@@ -159,13 +165,57 @@ class Muon:
         e.step += 1
         return True
 
+    def _dp_owners(self, dp: int) -> List[int]:
+        """Owner (DP rank) of every entry: largest matrices first, each to the least loaded replica."""
+        if self._owners is None or len(self._owners) != len(self.entries):
+            load = [0] * dp
+            owners = [0] * len(self.entries)
+            for idx in sorted(range(len(self.entries)), key=lambda i: -self.entries[i].shape[0] * self.entries[i].shape[1]):
+                o = min(range(dp), key=lambda r: load[r])
+                owners[idx] = o
+                load[o] += self.entries[idx].shape[0] * self.entries[idx].shape[1]
+            self._owners = owners
+        return self._owners
+
+    def _broadcast_from_owners(self, mesh, owners: List[int]) -> None:
+        ranks = mesh.dp_ranks()
+        for idx, e in enumerate(self.entries):
+            src = ranks[owners[idx]]
+            if e.param is not None:
+                dist.broadcast(e.param.data, src=src, group=mesh.dp_group)
+            else:
+                mod = e.module
+                for t in (mod.packed_weight, mod.scales, mod.global_scale):
+                    # byte view: not every backend carries float8
+                    dist.broadcast(t.view(torch.uint8) if t.dtype not in (torch.float32, torch.uint8) else t,
+                                   src=src, group=mesh.dp_group)
+
+    @torch.no_grad()
+    def sync_dp_state(self) -> None:
+        """Momentum of every matrix from its owner to the DP peers (before a checkpoint: only owners keep it current)."""
+        mesh = get_mesh()
+        if not (self.dp_shard and mesh.dp > 1) or self._owners is None:
+            return
+        ranks = mesh.dp_ranks()
+        for idx, e in enumerate(self.entries):
+            if e.exp_avg.is_cuda or dist.get_backend(mesh.dp_group) == "gloo":
+                dist.broadcast(e.exp_avg, src=ranks[self._owners[idx]], group=mesh.dp_group)
+            else:                                   # pinned host state under an NCCL group: stage through the device
+                t = e.exp_avg.to(mesh.device)
+                dist.broadcast(t, src=ranks[self._owners[idx]], group=mesh.dp_group)
+                e.exp_avg.copy_(t)
+
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0):
         mesh = get_mesh()
         full_scope = self.ns_scope == "full" and mesh.tp > 1
         wd_factor = 1.0 - self.lr * self.weight_decay
+        owners = self._dp_owners(mesh.dp) if (self.dp_shard and mesh.dp > 1 and not full_scope) else None
         work = []                                   # (entry, a, b, u_segment)
-        for e in self.entries:
+        for idx, e in enumerate(self.entries):
+            if owners is not None and owners[idx] != mesh.dp_rank:
+                e.step += 1                         # the owner updates this matrix; the new weights arrive below
+                continue
             g = e.grad()
             if g is None:
                 continue
@@ -190,6 +240,8 @@ class Muon:
                     work.append((e, a, b, u[a:b].contiguous()))
                 else:
                     self._apply(e, a, b, ops.newton_schulz5(u[a:b], self.ns_steps), wd_factor)
+        if owners is not None:
+            self._broadcast_from_owners(mesh, owners)
         if not work:
             return
         # full-matrix NS for TP-sharded matrices: matrix i is gathered to TP rank i % tp, orthogonalised there
@@ -326,7 +378,8 @@ def build_param_groups(model: nn.Module, args=None, precision: Optional[Precisio
     muon = Muon(lr=g("muon_lr", 0.02), momentum=g("muon_momentum", 0.95),
                 weight_decay=g("muon_weight_decay", 0.0), nesterov=True, ns_steps=5,
                 momentum_dtype=prec.muon_momentum, offload=offload,
-                ns_row_chunk=g("muon_ns_row_chunk", None), ns_scope=g("muon_ns_scope", "shard"))
+                ns_row_chunk=g("muon_ns_row_chunk", None), ns_scope=g("muon_ns_scope", "shard"),
+                dp_shard=bool(g("muon_dp_shard", True)))
     adamw = AdamW(lr=g("learning_rate", 0.004), betas=(g("adamw_beta1", 0.9), g("adamw_beta2", 0.95)),
                   eps=g("adamw_eps", 1e-8), weight_decay=g("weight_decay", 0.01),
                   m_dtype=prec.adamw_m, v_dtype=prec.adamw_v, offload=offload,

@@ -113,7 +113,11 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
     ctx.extras["fused_comm"] = fused_on
     if mesh.dp > 1:
         from ..parallel.dp import DPGradReducer
-        ctx.grad_reducer = DPGradReducer(model, mesh, overlap=bool(getattr(args, "dp_overlap", True)))
+        # With the fused TP kernels active the DP all-reduces run after backward instead of beside it: an NCCL kernel
+        # that shares the GPU with a persistent kernel spinning on its TP peers can keep part of that kernel's grid
+        # from becoming resident, and the peers would wait for tiles that are never computed.
+        overlap = bool(getattr(args, "dp_overlap", True)) and not fused_on
+        ctx.grad_reducer = DPGradReducer(model, mesh, overlap=overlap)
     if bool(getattr(args, "offload_grads", False)):
         from ..optim.offload import GradOffloader
         ctx.offloader = GradOffloader(model, device)
@@ -309,6 +313,7 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                     if ctx.metrics_file is not None:
                         ctx.metrics_file.write(json.dumps(rec) + "\n"); ctx.metrics_file.flush()
             if ck_int > 0 and ctx.run_dir and (ctx.step + 1) % ck_int == 0:
+                ctx.muon.sync_dp_state()              # collective: outside the try so that every rank takes part
                 try:
                     d = os.path.join(ctx.run_dir, "checkpoints")
                     ckpt.save_checkpoint(ctx.model, ctx.muon, ctx.adamw, ctx.step, loss,

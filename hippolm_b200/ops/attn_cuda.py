@@ -1,13 +1,13 @@
-"""CUDA path of causal varlen attention (``csrc/attention.cu``)."""
+"""CUDA path of causal varlen attention: tcgen05 kernels for head_dim 128 (``csrc/attention_tc.cu``), mma.sync kernels
+for head_dim 64 (``csrc/attention.cu``). The reference has no softmax-attention layer."""
 from __future__ import annotations
 
 import ctypes as _c
+import os
 
 import torch
 
 from ._ext import lib, ptr, stream_ptr, check
-
-import os
 
 _CACHE = {"key": None}
 _CACHE128 = {"key": None}

@@ -78,6 +78,10 @@ def test_parallel_matches_single(tmp_path, tp, dp):
     full = ref["sd"]
     assert torch.allclose(sd0["norm.weight"], full["norm.weight"], atol=1e-4)
     assert torch.allclose(sd0["layers.0.attn.fg_first.weight"], full["layers.0.attn.fg_first.weight"], atol=1e-4)
+    if dp > 1 and tp == 1:
+        # Muon work is split by ownership across the DP replicas; the broadcast leaves every replica with the same weights
+        for k in sd0:
+            assert torch.equal(sd0[k], res[1]["sd"][k]), k
     if tp > 1:
         other = res[1]["sd"]
         assert torch.equal(sd0["norm.weight"], other["norm.weight"]) or \

@@ -41,7 +41,6 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   float* kk = (float*)(Ck + 16 * LD);             // [64][LA]
   float* bs = kk + 64 * LA;                       // [64]
   bf16* Xb = (bf16*)(bs + 64);                    // [64][72]
-  float* stg = (float*)(Xb + 64 * 72);            // [16 warps][16][20]
   // the inverse (phase 3) reuses the work-tile region, which is idle between phases 2 and 4
   float* X = (float*)T1;                          // [64][LA]
   float* Tm = X + 64 * LA;                        // [3][16][16]
@@ -91,13 +90,20 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       int jj = r - ii * (ii + 1) / 2;
       int i = b * 16 + ii, j = b * 16 + jj;
       float skk = 0.f, sqk = 0.f;
+      // lane gl owns channels 32 m + 4 gl .. + 3: one float4 / uint2 per operand and group, conflict-free across the 8 lanes
 #pragma unroll
-      for (int cc = 0; cc < CPL; ++cc) {
-        int c = cc * 8 + gl;
-        float e = __expf(Gs[i * LG + c] - Gs[j * LG + c]);
-        float kj = __bfloat162float(ks[j * LD + c]) * e;
-        skk += __bfloat162float(ks[i * LD + c]) * kj;
-        sqk += __bfloat162float(qs[i * LD + c]) * kj;
+      for (int m = 0; m < CPL / 4; ++m) {
+        const int c = m * 32 + gl * 4;
+        const float4 gi = *(const float4*)(Gs + i * LG + c), gj = *(const float4*)(Gs + j * LG + c);
+        const uint2 kiw = *(const uint2*)(ks + i * LD + c), kjw = *(const uint2*)(ks + j * LD + c), qiw = *(const uint2*)(qs + i * LD + c);
+        const float2 ki0 = __bfloat1622float2(*(const __nv_bfloat162*)&kiw.x), ki1 = __bfloat1622float2(*(const __nv_bfloat162*)&kiw.y);
+        const float2 kj0 = __bfloat1622float2(*(const __nv_bfloat162*)&kjw.x), kj1 = __bfloat1622float2(*(const __nv_bfloat162*)&kjw.y);
+        const float2 qi0 = __bfloat1622float2(*(const __nv_bfloat162*)&qiw.x), qi1 = __bfloat1622float2(*(const __nv_bfloat162*)&qiw.y);
+        float t;
+        t = kj0.x * __expf(gi.x - gj.x); skk += ki0.x * t; sqk += qi0.x * t;
+        t = kj0.y * __expf(gi.y - gj.y); skk += ki0.y * t; sqk += qi0.y * t;
+        t = kj1.x * __expf(gi.z - gj.z); skk += ki1.x * t; sqk += qi1.x * t;
+        t = kj1.y * __expf(gi.w - gj.w); skk += ki1.y * t; sqk += qi1.y * t;
       }
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 1); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 1);
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 2); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 2);
@@ -125,28 +131,24 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     if (warp < ntile) {
       const int rt = warp >> 1, which = warp & 1;
       const bf16* R = which ? T2 : T1;
-      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-      wmma::fill_fragment(acc, 0.f);
+      const int g = lane >> 2, t4 = lane & 3;
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int kt = 0; kt < DK / 16; ++kt) {
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> bfr;
-        wmma::load_matrix_sync(a, R + rt * 16 * LD + kt * 16, LD);
-        wmma::load_matrix_sync(bfr, Ck + kt * 16, LD);
-        wmma::mma_sync(acc, a, bfr, acc);
+        unsigned a[4], b[4];
+        kda_frag_a(a, R, LD, rt * 16, kt * 16, lane);
+        kda_frag_bt2(b, Ck, LD, 0, kt * 16, lane);                  // Ck^T: n = column-block row, k = channel
+        kda_mma16816(acc[0], a, b[0], b[1]);
+        kda_mma16816(acc[1], a, b[2], b[3]);
       }
-      if (which) {
-        wmma::store_matrix_sync(kk + (r0 + rt * 16) * LA + 16 * J, acc, LA, wmma::mem_row_major);
-      } else {
-        float* my = stg + warp * 16 * 20;
-        wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
-        __syncwarp();
 #pragma unroll
-        for (int e2 = 0; e2 < 8; ++e2) {
-          int el = lane * 8 + e2, rr = el >> 4, cc = el & 15;
-          Aqk_out[(cbase + r0 + rt * 16 + rr) * 64 + 16 * J + cc] = __float2bfloat16(my[rr * 20 + cc]);
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int i = r0 + rt * 16 + g + hh * 8, j = 16 * J + n * 8 + 2 * t4;
+          if (which) *(float2*)(kk + i * LA + j) = make_float2(acc[n][2 * hh], acc[n][2 * hh + 1]);
+          else *(unsigned*)(Aqk_out + (cbase + i) * 64 + j) = kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
         }
-      }
     }
   }
   __syncthreads();
@@ -207,49 +209,68 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     if (j > i) Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(0.f);
   }
   __syncthreads();                                    // X (aliased on the work tiles) is consumed
-  for (int idx = tid; idx < 64 * DK; idx += NTHR) {
-    int i = idx / DK, c = idx % DK;
-    float G = Gs[i * LG + c], eG = __expf(G);
-    float kv = __bfloat162float(ks[i * LD + c]), qv = __bfloat162float(qs[i * LD + c]);
-    float vv = i < len ? __bfloat162float(v[((long long)(t0 + i) * H + h) * DK + c]) : 0.f;
-    T1[i * LD + c] = __float2bfloat16(bs[i] * kv * eG);
-    T2[i * LD + c] = __float2bfloat16(bs[i] * vv);
-    qg_out[(cbase + i) * DK + c] = __float2bfloat16(qv * eG);
-    kg_out[(cbase + i) * DK + c] = __float2bfloat16(kv * __expf(Gs[63 * LG + c] - G));
+  for (int idx = tid; idx < 64 * (DK / 8); idx += NTHR) {
+    const int i = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
+    uint4 vq = make_uint4(0, 0, 0, 0);
+    if (i < len) vq = *(const uint4*)(v + ((long long)(t0 + i) * H + h) * DK + c8);
+    const uint4 kq = *(const uint4*)(ks + i * LD + c8), qq = *(const uint4*)(qs + i * LD + c8);
+    const __nv_bfloat162* kb = (const __nv_bfloat162*)&kq; const __nv_bfloat162* qb = (const __nv_bfloat162*)&qq;
+    const __nv_bfloat162* vb = (const __nv_bfloat162*)&vq;
+    uint4 o1, o2, oq, ok;
+    unsigned* w1 = (unsigned*)&o1; unsigned* w2 = (unsigned*)&o2; unsigned* wq = (unsigned*)&oq; unsigned* wk = (unsigned*)&ok;
+    const float b = bs[i];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = c8 + 2 * e;
+      const float G0 = Gs[i * LG + c], G1 = Gs[i * LG + c + 1];
+      const float e0 = __expf(G0), e1 = __expf(G1);
+      const float2 kf = __bfloat1622float2(kb[e]), qf = __bfloat1622float2(qb[e]), vf = __bfloat1622float2(vb[e]);
+      w1[e] = kda_pack2(b * kf.x * e0, b * kf.y * e1);
+      w2[e] = kda_pack2(b * vf.x, b * vf.y);
+      wq[e] = kda_pack2(qf.x * e0, qf.y * e1);
+      wk[e] = kda_pack2(kf.x * __expf(Gs[63 * LG + c] - G0), kf.y * __expf(Gs[63 * LG + c + 1] - G1));
+    }
+    *(uint4*)(T1 + i * LD + c8) = o1;
+    *(uint4*)(T2 + i * LD + c8) = o2;
+    *(uint4*)(qg_out + (cbase + i) * DK + c8) = oq;
+    *(uint4*)(kg_out + (cbase + i) * DK + c8) = ok;
   }
   __syncthreads();
   {
-    constexpr int NT = DK / 16;
-    float* my = stg + warp * 16 * 20;
-    for (int t = warp; t < 2 * 4 * NT; t += NWARP) {
-      const int which = t / (4 * NT), rt = (t % (4 * NT)) / NT, nt = t % NT;
-      const bf16* B = which ? T2 : T1;
-      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-      wmma::fill_fragment(acc, 0.f);
-      for (int kt = 0; kt <= rt; ++kt) {           // X is lower triangular
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> bfr;
-        wmma::load_matrix_sync(a, Xb + rt * 16 * 72 + kt * 16, 72);
-        wmma::load_matrix_sync(bfr, B + kt * 16 * LD + nt * 16, LD);
-        wmma::mma_sync(acc, a, bfr, acc);
-      }
-      wmma::store_matrix_sync(my, acc, 20, wmma::mem_row_major);
-      __syncwarp();
-      bf16* out = which ? u_out : w_out;
+    // w = X (beta k e^G), u = X (beta v): warp (which, rt, column half) owns a 16-row x (DK/2)-column slab
+    static_assert(NWARP == 16, "slab assignment below assumes 16 warps");
+    const int which = warp >> 3, rt = (warp >> 1) & 3, ch = warp & 1;
+    const bf16* B = which ? T2 : T1;
+    bf16* out = which ? u_out : w_out;
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr int NP = DK / 32;                       // pairs of n-tiles in half of the columns
+    float acc[2 * NP][4];
 #pragma unroll
-      for (int e2 = 0; e2 < 8; ++e2) {
-        int el = lane * 8 + e2, rr = el >> 4, cc = el & 15;
-        out[(cbase + rt * 16 + rr) * DK + nt * 16 + cc] = __float2bfloat16(my[rr * 20 + cc]);
+    for (int n = 0; n < 2 * NP; ++n) { acc[n][0] = 0.f; acc[n][1] = 0.f; acc[n][2] = 0.f; acc[n][3] = 0.f; }
+    for (int kt = 0; kt <= rt; ++kt) {                // X is lower triangular
+      unsigned a[4];
+      kda_frag_a(a, Xb, 72, rt * 16, kt * 16, lane);
+#pragma unroll
+      for (int np = 0; np < NP; ++np) {
+        unsigned b[4];
+        kda_frag_b2(b, B, LD, kt * 16, ch * (DK / 2) + np * 16, lane);
+        kda_mma16816(acc[2 * np], a, b[0], b[1]);
+        kda_mma16816(acc[2 * np + 1], a, b[2], b[3]);
       }
-      __syncwarp();
     }
+#pragma unroll
+    for (int n = 0; n < 2 * NP; ++n)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *(unsigned*)(out + (cbase + rt * 16 + g + hh * 8) * DK + ch * (DK / 2) + n * 8 + 2 * t4) =
+            kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
   }
 }
 
 template <int DK>
 constexpr int kda_intra_smem() {
   return 64 * (DK + 4) * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 + 64 * 68 * 4 + 64 * 4 +
-         64 * 72 * 2 + 16 * 16 * 20 * 4 + 128;
+         64 * 72 * 2 + 128;
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -65,6 +65,36 @@ def main():
             print(json.dumps({"op": "gemm->reduce_scatter " + name, "world": w, "T": T, "N": N, "K": K, "nccl_rs_ms": round(t_rs, 3),
                               "gemm_ms": round(t_mm, 3), "unfused_ms": round(t_rs + t_mm, 3), "fused_ms": round(t_f, 3),
                               "roofline_ms": round(roof, 3), "fused_frac_of_roofline": round(roof / t_f, 3)}), flush=True)
+    # NVFP4 FFN: quantise-and-push -> FP4 GEMM (0.5625 bytes per element on the wire) and FP4 GEMM -> reduce-scatter.
+    # FP4 tensor-core peak is taken as 4x the measured bf16 peak (no measured FP4 figure exists).
+    from hippolm_b200.ops import nvfp4_cuda, fp4_gemm
+    fp4_peak = 4.0 * pk["bf16_tflops"] * 1e12
+    N, K = 2 * 14336 // w, D
+    x = torch.randn(T // w, K, device=dev).bfloat16(); W = (0.02 * torch.randn(N, K, device=dev)).bfloat16()
+    wp, wsc, wgs = nvfp4_cuda.quantize(W)
+    xg = all_gather_dim0(x, g, w)
+    t_ag = timed(lambda: all_gather_dim0(x, g, w), g)
+    t_mm = timed(lambda: fp4_gemm.gemm_nt(xg, wp, wsc, wgs), g)
+    t_f = timed(lambda: ws.nvfp4_allgather_gemm(x, wp, wsc, wgs), g)
+    roof = max(2.0 * T * N * K / fp4_peak, (w - 1) * x.numel() * 0.5625 / (pk["nvlink_gbs"] * 1e9)) * 1e3
+    if mesh.rank == 0:
+        print(json.dumps({"op": "nvfp4 quantise+push->gemm ffn gate_up", "world": w, "T": T, "N": N, "K": K,
+                          "nccl_ag_bf16_ms": round(t_ag, 3), "quant+fp4_gemm_ms": round(t_mm, 3),
+                          "unfused_ms": round(t_ag + t_mm, 3), "fused_ms": round(t_f, 3), "roofline_ms": round(roof, 3),
+                          "fused_frac_of_roofline": round(roof / t_f, 3)}), flush=True)
+    N, K = D, 14336 // w // 256 * 256
+    a = torch.randn(T, K, device=dev).bfloat16(); W = (0.02 * torch.randn(N, K, device=dev)).bfloat16()
+    wp, wsc, wgs = nvfp4_cuda.quantize(W)
+    y = fp4_gemm.gemm_nt(a, wp, wsc, wgs)
+    t_rs = timed(lambda: reduce_scatter_dim0(y, g, w), g)
+    t_mm = timed(lambda: fp4_gemm.gemm_nt(a, wp, wsc, wgs), g)
+    t_f = timed(lambda: ws.nvfp4_gemm_reduce_scatter(a, wp, wsc, wgs), g)
+    roof = max(2.0 * T * N * K / fp4_peak, (w - 1) / w * T * N * 2 / (pk["nvlink_gbs"] * 1e9)) * 1e3
+    if mesh.rank == 0:
+        print(json.dumps({"op": "nvfp4 gemm->reduce_scatter ffn down", "world": w, "T": T, "N": N, "K": K,
+                          "nccl_rs_ms": round(t_rs, 3), "quant+fp4_gemm_ms": round(t_mm, 3), "unfused_ms": round(t_rs + t_mm, 3),
+                          "fused_ms": round(t_f, 3), "roofline_ms": round(roof, 3),
+                          "fused_frac_of_roofline": round(roof / t_f, 3)}), flush=True)
     torch.cuda.synchronize()
     ws.check_status()
     dist.barrier()

@@ -177,6 +177,11 @@ class Muon:
             self._owners = owners
         return self._owners
 
+    def dp_owner_map(self, dp: int) -> Dict[int, int]:
+        """id(parameter) / id(NVFP4 module) -> owning DP rank, for a gradient reducer that reduces to the owner only."""
+        owners = self._dp_owners(dp)
+        return {id(e.param if e.param is not None else e.module): owners[i] for i, e in enumerate(self.entries)}
+
     def _broadcast_from_owners(self, mesh, owners: List[int]) -> None:
         ranks = mesh.dp_ranks()
         for idx, e in enumerate(self.entries):
@@ -401,11 +406,15 @@ def build_param_groups(model: nn.Module, args=None, precision: Optional[Precisio
 
 
 @torch.no_grad()
-def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None) -> torch.Tensor:
+def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None, owner_reduced: bool = False) -> torch.Tensor:
     """||G||_2 over every gradient of the whole model (device-side; the reference reduces a host
     fp64 scalar, ``src/training/loop/grad_norm.py:97-165``). TP-sharded tensors are summed over
-    the TP group; replicated ones are counted once."""
+    the TP group; replicated ones are counted once. ``owner_reduced``: the Muon gradients were reduced to
+    their owning DP replica only, so every matrix is counted by its owner, the all-reduced rest by DP rank 0,
+    and the partial sums are added over the DP group."""
     m = mesh or get_mesh()
+    owner_reduced = bool(owner_reduced and m.dp > 1 and muon.dp_shard)
+    m_owners = muon._dp_owners(m.dp) if owner_reduced else None
     dev = None
     for e in list(muon.entries) + list(adamw.entries):
         g = e.grad()
@@ -420,9 +429,12 @@ def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None) -> torch.Tensor:
     else:
         def sumsq_into(x, out):
             out += x.float().pow(2).sum()
-    for e in list(muon.entries) + list(adamw.entries):
+    n_muon = len(muon.entries)
+    for idx, e in enumerate(list(muon.entries) + list(adamw.entries)):
         g = e.grad()
         if g is None:
+            continue
+        if owner_reduced and (m_owners[idx] if idx < n_muon else 0) != m.dp_rank:
             continue
         rows = getattr(e.param, "tp_replicated_rows", None) if e.param is not None else None
         is_repl = e.param is not None and getattr(e.param, "tp_replicated", False)
@@ -433,6 +445,8 @@ def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None) -> torch.Tensor:
             sumsq_into(g[:a], acc[0:1]); sumsq_into(g[a:b], acc[1:2]); sumsq_into(g[b:], acc[0:1])
         else:
             sumsq_into(g, acc[0:1])
+    if owner_reduced:
+        dist.all_reduce(acc, group=m.dp_group)
     sharded, repl = acc[0], acc[1]
     if m.tp > 1:
         sharded = sharded.clone()

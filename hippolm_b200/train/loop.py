@@ -117,7 +117,12 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         # that shares the GPU with a persistent kernel spinning on its TP peers can keep part of that kernel's grid
         # from becoming resident, and the peers would wait for tiles that are never computed.
         overlap = bool(getattr(args, "dp_overlap", True)) and not fused_on
-        ctx.grad_reducer = DPGradReducer(model, mesh, overlap=overlap)
+        # optional: reduce the Muon gradients to their owning replica only (needs the ownership split of the Muon work)
+        owners = None
+        if bool(getattr(args, "dp_reduce_to_owner", False)) and muon.dp_shard and (muon.ns_scope != "full" or mesh.tp == 1):
+            owners = muon.dp_owner_map(mesh.dp)
+        ctx.extras["owner_reduced"] = owners is not None
+        ctx.grad_reducer = DPGradReducer(model, mesh, overlap=overlap, owners=owners)
     if bool(getattr(args, "offload_grads", False)):
         from ..optim.offload import GradOffloader
         ctx.offloader = GradOffloader(model, device)
@@ -219,7 +224,7 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
             dist.all_reduce(loss_acc, group=mesh.dp_group)
         model.sync_replicated_grads()
     with timer.phase("gradnorm"):
-        gnorm_t = global_grad_norm(ctx.muon, ctx.adamw, mesh)
+        gnorm_t = global_grad_norm(ctx.muon, ctx.adamw, mesh, owner_reduced=bool(ctx.extras.get("owner_reduced", False)))
         gnorm = float(gnorm_t)
         found_inf = not math.isfinite(gnorm)
     max_norm = float(getattr(args, "max_grad_norm", 1.0) or 0.0)

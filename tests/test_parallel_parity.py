@@ -12,7 +12,7 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _args(tp, dp, nvfp4=False):
+def _args(tp, dp, nvfp4=False, to_owner=False):
     from hippolm_b200.cli import build_parser
     a = build_parser().parse_args([])
     a.vocab_size, a.hidden_size, a.num_heads, a.head_dim = 256, 64, 4, 16
@@ -24,6 +24,7 @@ def _args(tp, dp, nvfp4=False):
                                                   "adamw_m", "adamw_v")}
     a.seed = 3
     a.muon_ns_scope = "full"
+    a.dp_reduce_to_owner = to_owner
     return a
 
 
@@ -38,12 +39,12 @@ def _batch(dp_rank, dp):
     return {"input_ids": ids[s:e], "labels": labels[s:e], "cu_seqlens": slice_cu_seqlens(cu, s, e).int(), "row_len": 64}
 
 
-def _run(rank, world, port, tp, dp, nvfp4, out_path):
+def _run(rank, world, port, tp, dp, nvfp4, out_path, to_owner=False):
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
     torch.set_num_threads(1)
     from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
-    ctx = setup_worker(_args(tp, dp, nvfp4), run_dir=None, data_iter=iter(()))
+    ctx = setup_worker(_args(tp, dp, nvfp4, to_owner), run_dir=None, data_iter=iter(()))
     losses = []
     for _ in range(3):
         out = train_step(ctx, _batch(ctx.mesh.dp_rank, dp)); ctx.step += 1
@@ -53,15 +54,15 @@ def _run(rank, world, port, tp, dp, nvfp4, out_path):
     teardown_worker(ctx)
 
 
-def _launch(tmp_path, tp, dp, nvfp4=False):
+def _launch(tmp_path, tp, dp, nvfp4=False, to_owner=False):
     world = tp * dp
-    out = str(tmp_path / f"out_tp{tp}_dp{dp}")
+    out = str(tmp_path / f"out_tp{tp}_dp{dp}_{int(to_owner)}")
     if world == 1:
         for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
             os.environ.pop(k, None)
         _run(0, 1, _free_port(), tp, dp, nvfp4, out)
     else:
-        mp.spawn(_run, args=(world, _free_port(), tp, dp, nvfp4, out), nprocs=world, join=True)
+        mp.spawn(_run, args=(world, _free_port(), tp, dp, nvfp4, out, to_owner), nprocs=world, join=True)
     return [torch.load(out + f".{r}", weights_only=False) for r in range(world)]
 
 
@@ -97,3 +98,15 @@ def test_nvfp4_tp2_runs_and_agrees_on_loss(tmp_path):
     res = _launch(tmp_path, 2, 1, nvfp4=True)
     assert abs(res[0]["losses"][0] - res[1]["losses"][0]) < 1e-5
     assert all(l == l for l in res[0]["losses"])
+
+
+def test_dp_reduce_to_owner_matches_single(tmp_path):
+    """Muon gradients reduced to their owning replica only: same losses, same global gradient norm, same weights."""
+    ref = _launch(tmp_path, 1, 1)[0]
+    res = _launch(tmp_path, 1, 2, to_owner=True)
+    for r in res:
+        for a, b in zip(r["losses"], ref["losses"]):
+            assert abs(a - b) < 2e-4, (r["losses"], ref["losses"])
+        assert abs(r["gnorm"] - ref["gnorm"]) < 5e-3 * max(1.0, ref["gnorm"])
+    for k in res[0]["sd"]:
+        assert torch.equal(res[0]["sd"][k], res[1]["sd"][k]), k

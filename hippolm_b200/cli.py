@@ -65,7 +65,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--checkpoint_keep_last_n", type=int, default=3); a("--output_dir", type=str, default="output")
     a("--resume", type=str, default=None); a("--diagnostics", type=_bool, default=False)
     a("--mb_timing", type=int, default=0); a("--empty_cache_between_mb", type=_bool, default=False)
-    a("--watchdog_timeout_s", type=float, default=0.0)
+    a("--peer_timeout_s", type=float, default=0.0); a("--dist_timeout_s", type=float, default=1800.0); a("--watchdog_timeout_s", type=float, default=0.0)
     # data
     a("--stage", type=str, default="pretrain"); a("--use_modelscope", type=_bool, default=False)
     a("--pretrain_dataset_hf", type=str, default=None); a("--pretrain_dataset_ms", type=str, default=None)

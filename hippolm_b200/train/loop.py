@@ -53,6 +53,7 @@ class TrainContext:
     step: int = 0
     metrics_file: Optional[Any] = None
     grad_reducer: Optional[Any] = None
+    liveness: Optional[Any] = None
     offloader: Optional[Any] = None
     prefetcher: Optional[Any] = None
     watchdog: Optional[Any] = None
@@ -111,6 +112,12 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
     ctx = TrainContext(args=args, cfg=cfg, mesh=mesh, device=device, model=model, muon=muon, adamw=adamw,
                        precision=precision, logger=logger, data_iter=data_iter, run_dir=run_dir)
     ctx.extras["fused_comm"] = fused_on
+    peer_timeout = float(getattr(args, "peer_timeout_s", 0) or 0)
+    if peer_timeout > 0 and mesh.is_distributed:
+        from .liveness import PeerLiveness, default_store
+        store = default_store()
+        if store is not None:
+            ctx.liveness = PeerLiveness(store, mesh.rank, mesh.world_size, peer_timeout)
     if mesh.dp > 1:
         from ..parallel.dp import DPGradReducer
         # With the fused TP kernels active the DP all-reduces run after backward instead of beside it: an NCCL kernel
@@ -286,7 +293,16 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
             if ctx.device.type == "cuda":
                 ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 ev0.record()
-            out = train_step(ctx, batch, timer)
+            if ctx.liveness is not None:
+                # a peer that left (or went silent) is found here, on the host, before this step's first launch
+                ctx.liveness.beat(ctx.step)
+                ctx.liveness.check()
+                try:
+                    out = train_step(ctx, batch, timer)
+                except Exception as ex:           # e.g. a collective that ran into the process-group timeout
+                    raise ctx.liveness.diagnose(ex)
+            else:
+                out = train_step(ctx, batch, timer)
             if ev1 is not None:
                 ev1.record(); ev1.synchronize()
                 step_ms = ev0.elapsed_time(ev1)
@@ -330,7 +346,13 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                     ctx.logger.error(f"checkpoint save failed at step {ctx.step}: {ex!r}")
             last = out
             ctx.step += 1
+    except BaseException as ex:
+        if ctx.liveness is not None:
+            ctx.liveness.mark_exit(repr(ex))
+        raise
     finally:
+        if ctx.liveness is not None:
+            ctx.liveness.mark_exit("finished")
         teardown_worker(ctx)
     return {"losses": losses, "last": last, "steps": ctx.step}
 

@@ -1,5 +1,5 @@
-"""VRAM tooling (``tools/vram_profile/*.py``): memory-history snapshots, a polling thread on
-``torch.cuda.mem_get_info`` and a saved-tensor size probe."""
+"""VRAM tooling (``tools/vram_profile/*.py``): memory-history snapshots and their analysis by allocation site, a
+polling thread on ``torch.cuda.mem_get_info``, a saved-tensor size probe and its per-module attribution."""
 from __future__ import annotations
 
 import contextlib
@@ -79,3 +79,83 @@ def vram_line(device) -> str:
         return "vram n/a"
     return (f"vram alloc {torch.cuda.memory_allocated(device) / 2**20:.0f} MiB reserved "
             f"{torch.cuda.memory_reserved(device) / 2**20:.0f} MiB max {torch.cuda.max_memory_allocated(device) / 2**20:.0f} MiB")
+
+
+def analyze_snapshot(snapshot, top: int = 20, package_hint: str = "hippolm_b200") -> List[Dict]:
+    """Live allocations of an allocator snapshot grouped by the code that made them
+    (``tools/vram_profile/analyze_snapshot.py`` in the reference).
+
+    ``snapshot``: the dict from ``torch.cuda.memory._snapshot()`` or the path of a pickle written by
+    ``torch.cuda.memory._dump_snapshot``. Every active block is attributed to the innermost frame of its stack that
+    lies inside ``package_hint`` (else the innermost Python frame). Returns the ``top`` groups, largest first:
+    ``{"where": "file:line name", "bytes": .., "blocks": ..}``."""
+    if isinstance(snapshot, (str, bytes)):
+        import pickle
+        with open(snapshot, "rb") as f:
+            snapshot = pickle.load(f)
+    groups: Dict[str, List[int]] = {}
+    for seg in snapshot.get("segments", []):
+        for blk in seg.get("blocks", []):
+            if blk.get("state") != "active_allocated":
+                continue
+            frames = blk.get("frames") or []
+            pick = None
+            for fr in frames:
+                fn = fr.get("filename", "")
+                if package_hint in fn:
+                    pick = fr
+                    break
+            if pick is None:
+                pick = next((fr for fr in frames if fr.get("filename", "").endswith(".py")), None)
+            where = f"{pick['filename']}:{pick.get('line', 0)} {pick.get('name', '')}" if pick else "<no stack>"
+            g = groups.setdefault(where, [0, 0])
+            g[0] += int(blk.get("size", 0)); g[1] += 1
+    out = [{"where": k, "bytes": v[0], "blocks": v[1]} for k, v in groups.items()]
+    out.sort(key=lambda r: -r["bytes"])
+    return out[:top]
+
+
+def saved_bytes_by_module(model: torch.nn.Module, run, depth: int = 2) -> List[Dict]:
+    """Bytes autograd keeps for backward, attributed to the sub-module whose forward saved them (module paths cut at
+    ``depth`` components). ``run()`` performs one forward pass of ``model``. Tells which layer type sets the activation
+    memory of a micro-batch (``tools/vram_profile/saved_tensor_probe.py`` in the reference)."""
+    stack: List[str] = []
+    totals: Dict[str, List[int]] = {}
+    seen = set()
+    handles = []
+
+    def pre(name):
+        def hook(mod, args):
+            stack.append(name)
+        return hook
+
+    def post(name):
+        def hook(mod, args, out):
+            if stack and stack[-1] == name:
+                stack.pop()
+        return hook
+
+    for name, mod in model.named_modules():
+        if not name:
+            continue
+        short = ".".join(name.split(".")[:depth])
+        handles.append(mod.register_forward_pre_hook(pre(short)))
+        handles.append(mod.register_forward_hook(post(short)))
+
+    def pack(t):
+        key = (t.data_ptr(), t.numel())
+        if key not in seen:
+            seen.add(key)
+            g = totals.setdefault(stack[-1] if stack else "<top>", [0, 0])
+            g[0] += t.numel() * t.element_size(); g[1] += 1
+        return t
+
+    try:
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+            run()
+    finally:
+        for h in handles:
+            h.remove()
+    out = [{"module": k, "bytes": v[0], "tensors": v[1]} for k, v in totals.items()]
+    out.sort(key=lambda r: -r["bytes"])
+    return out

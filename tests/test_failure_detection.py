@@ -36,7 +36,7 @@ def _worker(rank, world, port, mode, out_path):
                 if mode == "raise":
                     raise RuntimeError("injected failure on rank 1")
                 if mode == "silent":
-                    time.sleep(3.0)               # stays alive but stops beating and never joins the collective
+                    time.sleep(20.0)              # stays alive but stops beating and never joins the collective
                     break
             if mode == "silent" and rank == 0 and step == 2:
                 time.sleep(2.0)                   # let the peer's heartbeat age past the liveness timeout
@@ -66,14 +66,13 @@ def test_survivor_learns_that_a_peer_left(tmp_path, mode):
     out = str(tmp_path / mode)
     ctx = mp.spawn(_worker, args=(2, _free_port(), mode, out), nprocs=2, join=False)
     deadline = time.time() + 60
-    while not all(os.path.exists(out + f".{r}") for r in range(2)) and time.time() < deadline:
+    while not os.path.exists(out + ".0") and time.time() < deadline:      # only the survivor's verdict matters
         time.sleep(0.2)
-    res = [torch.load(out + f".{r}") for r in range(2)]
+    r0 = torch.load(out + ".0")
     for p in ctx.processes:
-        p.join(timeout=10)
+        p.join(timeout=2)
         if p.is_alive():
             p.terminate()
-    r0 = res[0]
     assert r0["error"] == "PeerLost" and r0["lost_rank"] == 1, r0
     assert r0["steps"] == 2 and r0["seconds"] < 30, r0
     if mode == "raise":

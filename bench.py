@@ -19,14 +19,11 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, ROOT)
 
 SEQS_PER_GPU = 16
 SEQ_LEN = 8192
@@ -44,54 +41,13 @@ def parse():
     p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
     p.add_argument("--no_fused_comm", action="store_true")
     p.add_argument("--bf16_ffn", action="store_true")
+    p.add_argument("--no_kda", dest="kda", action="store_false",
+                   help="skip the standalone chunked-KDA timing that rank 0 adds to the JSON line (outside the timed region)")
+    p.add_argument("--kda_only", action="store_true", help="print only the standalone chunked-KDA timing")
+    p.add_argument("--ref_ffn", type=str, default="nvfp4", help="reference arm FFN storage: nvfp4 (dequantise + cuBLAS) | bf16")
+    p.add_argument("--ref_budget_s", type=float, default=1500.0,
+                   help="reference arm: wall-clock budget; fewer than --steps steps are timed if they would not fit")
     return p.parse_args()
-
-
-class ClockSampler:
-    """nvidia-smi clock / throttle-reason sampler running during the timed region."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int = 0):
-        self.idx = gpu_index
-        self.rows = []
-        self.proc = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
-        except Exception:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
-                for n, v in zip(names, r[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            except Exception:
-                continue
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
 
 
 MODELS = {
@@ -104,13 +60,67 @@ MODELS = {
 }
 
 
+def kda_times(B=4, T=8192, H=16, D=128, docs=8, iters=10):
+    """Standalone chunked-KDA forward and forward+backward time through the public autograd op (B=4, T=8192, H=16,
+    K=V=128, 8 documents, bf16), CUDA events, warm-up, L2 flushed between iterations."""
+    import statistics
+    import torch
+    import torch.nn.functional as F
+    from hippolm_b200.ops.kda_cuda import _KDAFunction
+    torch.manual_seed(0)
+    dev, TT = "cuda", B * T
+    q = F.normalize(torch.randn(TT, H, D, device=dev), dim=-1).bfloat16().requires_grad_(True)
+    k = F.normalize(torch.randn(TT, H, D, device=dev), dim=-1).bfloat16().requires_grad_(True)
+    v = torch.randn(TT, H, D, device=dev).bfloat16().requires_grad_(True)
+    g = (-F.softplus(torch.randn(TT, H, D, device=dev))).requires_grad_(True)
+    beta = torch.sigmoid(torch.randn(TT, H, device=dev)).requires_grad_(True)
+    h0 = torch.zeros(docs, H, D, D, device=dev)
+    cuts = torch.sort(torch.randperm(TT - 1)[:docs - 1] + 1).values
+    cu = torch.cat([torch.zeros(1, dtype=torch.long), cuts, torch.tensor([TT])]).to(torch.int32).to(dev)
+    do = torch.randn(TT, H, D, device=dev).bfloat16()
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
+
+    def fwd():
+        with torch.no_grad():
+            _KDAFunction.apply(q, k, v, g, beta, h0, cu)
+
+    def fwd_bwd():
+        for t in (q, k, v, g, beta):
+            t.grad = None
+        o = _KDAFunction.apply(q, k, v, g, beta, h0, cu)
+        o = o[0] if isinstance(o, (tuple, list)) else o
+        o.backward(do)
+
+    def time_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    return {"kda_fwd_ms": round(time_ms(fwd), 3), "kda_fwd_bwd_ms": round(time_ms(fwd_bwd), 3),
+            "kda_config": {"B": B, "T": T, "H": H, "K": D, "V": D, "docs": docs, "dtype": "bf16",
+                           "l2": "flushed between iterations", "impl": "hippolm_b200 chunked KDA (CUDA)"}}
+
+
 def main():
     a = parse()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip install of the reference tree failed: directory is not installable (no setup.py / "
-                          "pyproject.toml); the reference also has no full-attention layers, sequence parallelism "
-                          "or sm_100 NVFP4 path, so this config cannot run on its stock code path"}))
+        # the reference arm imports nothing of this repository's package: only baseline/reference_arm.py and the
+        # unmodified reference tree under baseline/_ref
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+        return reference_arm.run_kda_only() if a.kda_only else reference_arm.run_train(a)
+    sys.path.insert(0, ROOT)
+    sys.path.insert(1, os.path.join(ROOT, "bench"))
+    from clocks import ClockSampler
+    if a.kda_only:
+        print(json.dumps(dict(kda_times(), impl="ours")), flush=True)
         return 0
     import torch
     import torch.distributed as dist
@@ -207,6 +217,16 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in (batches[0]["input_ids"], batches[0]["labels"],
                                                      batches[0]["cu_seqlens"]))
     st = _ext.device_status()
+    kda = {}
+    if a.kda:
+        # second half of the headline metric: standalone chunked-KDA forward+backward (rank 0 only, outside the timed
+        # regions; the other ranks wait at the barrier)
+        if rank == 0:
+            try:
+                kda = kda_times()
+            except Exception as ex:                                   # noqa: BLE001
+                kda = {"kda_unavailable": f"{type(ex).__name__}: {str(ex)[:200]}"}
+        barrier()
     if rank == 0:
         rec = {"metric": "train tokens/sec (device-timed, max over ranks)", "value": gb_tokens / (ms_step / 1e3),
                "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_step,
@@ -221,6 +241,7 @@ def main():
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},
                "gpu_launches": launches, "loss": last_loss,
                "max_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "device_status": list(st), "impl": "ours"}
+        rec.update(kda)
         print(json.dumps(rec), flush=True)
     teardown_worker(ctx)
     return 0

@@ -1,5 +1,6 @@
-"""bench.py contract pieces that need no GPU: the reference arm answers with one JSON line and exit code 0, and the
-Muon ownership split across data-parallel replicas is balanced and deterministic."""
+"""bench.py contract pieces that need no GPU: without a CUDA device the reference arm still answers with one JSON line
+and exit code 0 and imports nothing of this package, and the Muon ownership split across data-parallel replicas is
+balanced and deterministic."""
 import json
 import os
 import subprocess
@@ -11,12 +12,25 @@ import torch.nn as nn
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_reference_arm_reports_unavailable():
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "1",
-                        "--warmup", "1"], capture_output=True, text=True, timeout=120)
+def test_reference_arm_answers_without_a_gpu():
+    import pytest
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "src")):
+        pytest.skip("the reference tree has not been copied to baseline/_ref")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--model", "tiny", "--gpus", "1", "--steps", "1",
+                        "--warmup", "1"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     rec = json.loads(r.stdout.strip().splitlines()[-1])
-    assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and rec["unavailable"]
+    assert rec["impl"] == "reference"
+    if not torch.cuda.is_available():
+        # the tree imports, but its worker needs a CUDA device: the arm says so instead of failing
+        assert "CUDA" in rec["unavailable"]
+    else:
+        assert rec.get("value", 0) > 0 or rec.get("unavailable")
+
+
+def test_reference_arm_source_does_not_import_the_package():
+    src = open(os.path.join(ROOT, "baseline", "reference_arm.py")).read()
+    assert "import hippolm_b200" not in src and "from hippolm_b200" not in src
 
 
 def test_muon_dp_owner_assignment_is_balanced():

@@ -23,9 +23,13 @@ def _pin(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def dummy_dataloader(batch_size: int, seq_len: int, vocab_size: int, seed: int = 0) -> Iterator[Dict]:
-    g = torch.Generator().manual_seed(seed)
+def dummy_dataloader(batch_size: int, seq_len: int, vocab_size: int, seed: int = 0, start_step: int = 0
+                     ) -> Iterator[Dict]:
+    """Batch ``i`` depends on ``(seed, i)`` only, so a resumed run continues the stream at ``start_step``."""
+    step = start_step
     while True:
+        g = torch.Generator().manual_seed(seed * 1000003 + step)
+        step += 1
         ids = torch.randint(0, vocab_size, (batch_size * seq_len,), generator=g)
         labels = ids.clone()
         cu = torch.arange(0, batch_size * seq_len + 1, seq_len, dtype=torch.int32)
@@ -34,8 +38,8 @@ def dummy_dataloader(batch_size: int, seq_len: int, vocab_size: int, seed: int =
 
 
 def synthetic_loader(batch_size: int, seq_len: int, vocab_size: int, seed: int, doc_len_min: int,
-                     doc_len_max: int, align: int = 1, fixed: bool = False) -> Iterator[Dict]:
-    step = 0
+                     doc_len_max: int, align: int = 1, fixed: bool = False, start_step: int = 0) -> Iterator[Dict]:
+    step = start_step
     cached = None
     while True:
         if fixed and cached is not None:
@@ -48,20 +52,27 @@ def synthetic_loader(batch_size: int, seq_len: int, vocab_size: int, seed: int, 
         step += 1
 
 
-def build_data_iterator(args, cfg, mesh) -> Tuple[Iterator, Optional[object]]:
+def build_data_iterator(args, cfg, mesh, start_step: int = 0) -> Tuple[Iterator, Optional[object]]:
     """Per-DP-rank batch iterator. TP ranks of one DP replica draw the same stream (same seed);
-    real-data runs broadcast from the owner rank through :class:`PrefetchBatcher`."""
+    real-data runs broadcast from the owner rank through :class:`PrefetchBatcher`. ``start_step`` batches have
+    already been consumed by the run being resumed: synthetic streams jump there, real-data streams are fast-forwarded."""
     gb = int(getattr(args, "batch_size", 1))
     assert gb % mesh.dp == 0, f"batch_size {gb} must be divisible by dp {mesh.dp}"
     lb = gb // mesh.dp
     seq = int(getattr(args, "seq_len", 512))
     seed = int(getattr(args, "seed", 0)) * 131 + mesh.dp_rank
     if getattr(args, "use_dummy_data", False) and not getattr(args, "doc_len_max", 0):
-        return dummy_dataloader(lb, seq, cfg.vocab_size, seed), None
+        return dummy_dataloader(lb, seq, cfg.vocab_size, seed, start_step), None
     if getattr(args, "use_dummy_data", False) or getattr(args, "synthetic_data", False):
         return synthetic_loader(lb, seq, cfg.vocab_size, seed, int(getattr(args, "doc_len_min", 64)),
                                 int(getattr(args, "doc_len_max", 256)),
                                 int(getattr(args, "doc_align", 1)),
-                                bool(getattr(args, "fixed_batch", False))), None
+                                bool(getattr(args, "fixed_batch", False)), start_step), None
     from .streaming import build_streaming_iterator
-    return build_streaming_iterator(args, cfg, mesh, lb, seq)
+    it, pre = build_streaming_iterator(args, cfg, mesh, lb, seq)
+    for _ in range(start_step):
+        try:
+            next(it)
+        except StopIteration:
+            break
+    return it, pre

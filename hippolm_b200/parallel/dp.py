@@ -31,6 +31,7 @@ class DPGradReducer:
         self._buckets = {}                # owner (None = all-reduce) -> [tensors]
         self._elems = {}
         self._hooked = False
+        self._seen = set()                # ids of the gradients a hook has bucketed in this step
         if overlap and mesh.dp > 1:
             for p in model.parameters():
                 if p.requires_grad:
@@ -43,6 +44,7 @@ class DPGradReducer:
     def _hook(self, p):
         if not self._last or p.grad is None:
             return
+        self._seen.add(id(p))
         self._add(p.grad, self.owners.get(id(p)))
 
     def _add(self, g: torch.Tensor, owner=None):
@@ -69,10 +71,12 @@ class DPGradReducer:
     def finish(self):
         if self.mesh.dp == 1:
             return
-        if not self._hooked:
-            for p in self.model.parameters():
-                if p.grad is not None:
-                    self._add(p.grad, self.owners.get(id(p)))
+        # everything a hook has not bucketed in this step (no hooks at all, or a gradient that was installed after
+        # backward, e.g. uploaded from the host accumulators); every replica walks the parameters in the same order
+        for p in self.model.parameters():
+            if p.grad is not None and id(p) not in self._seen:
+                self._add(p.grad, self.owners.get(id(p)))
+        self._seen = set()
         for mod in self.model.modules():
             if isinstance(mod, NVFP4Linear) and mod.no_master and mod.grad_w is not None:
                 self._add(mod.grad_w, self.owners.get(id(mod)))

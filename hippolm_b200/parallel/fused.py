@@ -25,9 +25,9 @@ def fits(rows_per_shard: int, tokens: int, width: int) -> bool:
             and tokens * width <= ws.max_tokens * ws.max_width)
 
 
-def setup(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16) -> bool:
+def setup(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, wait_cycles: int = 0) -> bool:
     from . import symm
-    ws = symm.create_workspace(mesh, max_tokens, max_width, dtype)
+    ws = symm.create_workspace(mesh, max_tokens, max_width, dtype, wait_cycles=wait_cycles)
     _STATE["ws"] = ws
     return ws is not None
 

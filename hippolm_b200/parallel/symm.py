@@ -248,7 +248,8 @@ class FusedWorkspace:
             raise RuntimeError(f"a bounded device wait ran out: code={st[0]} detail={st[1]} block={st[2]} count={st[3]}")
 
 
-def create_workspace(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16) -> Optional[FusedWorkspace]:
+def create_workspace(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, wait_cycles: int = 0
+                     ) -> Optional[FusedWorkspace]:
     if mesh.tp <= 1 or mesh.device.type != "cuda":
         return None
-    return FusedWorkspace(mesh, max_tokens, max_width, dtype)
+    return FusedWorkspace(mesh, max_tokens, max_width, dtype, wait_cycles=wait_cycles)

@@ -106,7 +106,10 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         mbt = int(getattr(args, "micro_batch_size", 0) or 0)
         full = int(getattr(args, "batch_size", 1)) // max(1, dp) * int(getattr(args, "seq_len", 512))
         tokens = min(mbt, full) if mbt > 0 else full
-        fused_on = (tokens // mesh.tp) % 128 == 0 and fused.setup(mesh, tokens, cfg.hidden_size)
+        # bound of every device-side wait on a peer, in milliseconds of SM clock (0 = the kernels' default, ~2 s)
+        wait_ms = float(getattr(args, "fused_wait_ms", 0) or 0)
+        fused_on = (tokens // mesh.tp) % 128 == 0 and fused.setup(mesh, tokens, cfg.hidden_size,
+                                                                  wait_cycles=int(wait_ms * 1.9e6))
     offload = bool(getattr(args, "offload_optimizer", False))
     muon, adamw = build_param_groups(model, args, precision, offload=offload)
     ctx = TrainContext(args=args, cfg=cfg, mesh=mesh, device=device, model=model, muon=muon, adamw=adamw,
@@ -123,7 +126,10 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         # With the fused TP kernels active the DP all-reduces run after backward instead of beside it: an NCCL kernel
         # that shares the GPU with a persistent kernel spinning on its TP peers can keep part of that kernel's grid
         # from becoming resident, and the peers would wait for tiles that are never computed.
-        overlap = bool(getattr(args, "dp_overlap", True)) and not fused_on
+        # With gradient offload the hooks of the offloader free ``p.grad`` as soon as it is final, so there is nothing
+        # to reduce during backward: the reduction then runs on the gradients uploaded by ``drain_to_device``.
+        overlap = (bool(getattr(args, "dp_overlap", True)) and not fused_on
+                   and not bool(getattr(args, "offload_grads", False)))
         # optional: reduce the Muon gradients to their owning replica only (needs the ownership split of the Muon work)
         owners = None
         if bool(getattr(args, "dp_reduce_to_owner", False)) and muon.dp_shard and (muon.ns_scope != "full" or mesh.tp == 1):
@@ -140,10 +146,8 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
                     f"offload={offload} fused_comm={fused_on}")
         if run_dir:
             ctx.metrics_file = open(os.path.join(run_dir, "metrics.jsonl"), "a")
-    if data_iter is None:
-        from ..data.loaders import build_data_iterator
-        ctx.data_iter, ctx.prefetcher = build_data_iterator(args, cfg, mesh)
     resume = getattr(args, "resume", None)
+    data_step = 0
     if resume:
         path = resume
         if resume in ("latest", "auto") and run_dir:
@@ -151,10 +155,16 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         if path and os.path.isdir(path):
             path = ckpt.find_latest_checkpoint(path)
         if path:
-            step, loss = ckpt.load_checkpoint(path, model, muon, adamw, rank=mesh.rank,
-                                              world_size=mesh.world_size, map_location=device)
+            info: Dict[str, Any] = {}
+            step, loss = ckpt.load_checkpoint(path, model, muon, adamw, rank=mesh.rank, world_size=mesh.world_size,
+                                              map_location=device, mesh=mesh, info=info)
             ctx.step = step + 1
-            logger.info(f"resumed from {path} at step {step} (loss {loss})")
+            data_step = int(info.get("data_step", step + 1))
+            logger.info(f"resumed from {path} at step {step} (loss {loss}); data position {data_step}")
+    if data_iter is None:
+        from ..data.loaders import build_data_iterator
+        # the loader continues after the batches the checkpointed run had consumed instead of replaying them
+        ctx.data_iter, ctx.prefetcher = build_data_iterator(args, cfg, mesh, start_step=data_step)
     hb = float(getattr(args, "watchdog_timeout_s", 0) or 0)
     if hb > 0:
         from .watchdog import StepWatchdog
@@ -189,26 +199,25 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
     targets = shift_targets(labels, row_len)
     mbs = int(getattr(args, "micro_batch_size", 0) or 0)
     windows = _micro_batches(T, mbs, row_len)
-    valid_counts = [(targets[s:e] >= 0).sum() for s, e in windows]
-    total_valid = torch.stack(valid_counts).sum().float()
+    # valid-target count per window, summed over the data-parallel replicas, read back once per step: every replica
+    # then runs (or skips) the same windows and issues the same gradient collectives
+    counts_t = torch.stack([(targets[s:e] >= 0).sum() for s, e in windows]).float()
+    counts_g = counts_t.clone()
     if mesh.dp > 1:
-        dist.all_reduce(total_valid, group=mesh.dp_group)
-    total_valid_f = float(total_valid.clamp(min=1))
+        dist.all_reduce(counts_g, group=mesh.dp_group)
+    counts = counts_g.tolist()
+    total_valid_f = max(float(sum(counts)), 1.0)
     carry = bool(getattr(args, "carry_kda_state", False))
+    run = [wi for wi in range(len(windows)) if counts[wi] > 0 or carry]
+    last_run = run[-1] if run else -1
     kda_states = None
     loss_acc = torch.zeros((), device=dev, dtype=torch.float32)
-    use_autocast = dev.type == "cuda" and ctx.precision.autocast_enabled and False  # weights already bf16
     with timer.phase("fwd_bwd"):
-        for wi, (s, e) in enumerate(windows):
-            if float(valid_counts[wi]) == 0 and not carry:
-                continue
+        for wi in run:
+            s, e = windows[wi]
             cu_w = slice_cu_seqlens(cu, s, e).to(torch.int32)
-            lab_w = labels[s:e].clone()
-            if e < T:
-                # the last token's target lives in the next window: keep it via an explicit target vector
-                pass
             if ctx.grad_reducer is not None:
-                ctx.grad_reducer.set_last_microbatch(wi == len(windows) - 1)
+                ctx.grad_reducer.set_last_microbatch(wi == last_run)
             with nvtx_range(f"mb{wi}_forward"):
                 init = None
                 if carry and kda_states is not None:
@@ -223,6 +232,12 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
                 kda_states = [f.detach() for f in finals]
             if ctx.offloader is not None:
                 ctx.offloader.after_microbatch()
+            if bool(getattr(args, "empty_cache_between_mb", False)) and dev.type == "cuda":
+                torch.cuda.empty_cache()          # trades step time for a lower reserved-memory peak
+    if not run:
+        # no window of any replica holds a valid target: nothing was computed, nothing to apply
+        return {"loss": loss_acc, "grad_norm": 0.0, "found_inf": False, "lr_muon": 0.0, "lr_adamw": 0.0,
+                "tokens": T * mesh.dp, "n_valid": 0.0}
     with timer.phase("grad_sync"):
         if ctx.offloader is not None:
             ctx.offloader.drain_to_device()
@@ -234,6 +249,10 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
         gnorm_t = global_grad_norm(ctx.muon, ctx.adamw, mesh, owner_reduced=bool(ctx.extras.get("owner_reduced", False)))
         gnorm = float(gnorm_t)
         found_inf = not math.isfinite(gnorm)
+    if ctx.extras.get("fused_comm", False):
+        # the host is in step with the device here (the norm was just read back): a bounded wait on a peer that ran out
+        # during this step left unfinished tiles behind, so the gradients must not be applied
+        _check_fused_status(ctx)
     max_norm = float(getattr(args, "max_grad_norm", 1.0) or 0.0)
     lr_m = wsd_lr(ctx.step, float(getattr(args, "muon_lr", 0.02)), int(getattr(args, "lr_warmup_steps", 0)),
                   int(getattr(args, "lr_decay_steps", 0)), int(getattr(args, "max_steps", 1 << 30)))
@@ -257,6 +276,23 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
         log_post_opt_diag(ctx.logger, ctx.step, [ctx.muon, ctx.adamw])
     return {"loss": loss_acc, "grad_norm": gnorm, "found_inf": found_inf, "lr_muon": lr_m, "lr_adamw": lr_a,
             "tokens": T * mesh.dp, "n_valid": total_valid_f}
+
+
+class FusedCommTimeout(RuntimeError):
+    """A device-side wait on a tensor-parallel peer ran out inside a fused compute + collective kernel."""
+
+
+def _check_fused_status(ctx: TrainContext) -> None:
+    from ..ops import _ext
+    st = _ext.device_status()
+    if st[0] == 0:
+        return
+    _ext.clear_device_status()
+    ctx.muon.zero_grad(); ctx.adamw.zero_grad()
+    msg = (f"step {ctx.step}: a fused collective gave up waiting for a peer (code={st[0]} detail={st[1]} block={st[2]} "
+           f"count={st[3]}); the update was not applied and the gradients were cleared")
+    ctx.logger.error(msg)
+    raise FusedCommTimeout(msg)
 
 
 def _carry_states(prev: List[torch.Tensor], n_seq: int, continues: bool) -> List[torch.Tensor]:

@@ -45,7 +45,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--full_attn_interval", type=int, default=4); a("--rope_theta", type=float, default=10000.0)
     a("--intermediate_size", type=int, default=1024); a("--rms_norm_eps", type=float, default=1e-6)
     a("--ffn_nvfp4", type=_bool, default=False); a("--ffn_nvfp4_marlin", type=_bool, default=False)
-    a("--ffn_nvfp4_no_bf16_master", type=_bool, default=False)
+    a("--ffn_nvfp4_no_bf16_master", type=_bool, default=False); a("--nvfp4_stochastic_rounding", type=_bool, default=True)
     a("--gradient_checkpointing", type=_bool, default=False); a("--lce_num_chunks", type=int, default=0)
     # training
     a("--batch_size", type=int, default=1); a("--seq_len", type=int, default=512)
@@ -59,7 +59,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--gradient_accumulation_steps", type=int, default=1)
     a("--lr_warmup_steps", type=int, default=0); a("--lr_decay_steps", type=int, default=0)
     a("--max_grad_norm", type=float, default=1.0); a("--seed", type=int, default=42)
-    a("--carry_kda_state", type=_bool, default=False)
+    a("--carry_kda_state", type=_bool, default=False); a("--trainable_regex", type=str, default=None)
     # logging / checkpoints
     a("--log_interval", type=int, default=1); a("--checkpoint_interval", type=int, default=0)
     a("--checkpoint_keep_last_n", type=int, default=3); a("--output_dir", type=str, default="output")

@@ -86,6 +86,12 @@ class HippoConfig:
             raise ValueError("ffn_nvfp4_no_bf16_master requires ffn_nvfp4")
         if self.hidden_size % self.num_heads != 0:
             raise ValueError("hidden_size must be divisible by num_heads (AttnRes heads)")
+        # accepted names whose only supported value is the reference's production setting: refuse the other value
+        # instead of silently ignoring it
+        if self.use_bias:
+            raise ValueError("use_bias=true is not supported: the projections carry no bias term")
+        if self.conv_bias:
+            raise ValueError("conv_bias=true is not supported: the short-convolution kernels carry no bias term")
 
     # ---- derived sizes
     @property

@@ -707,6 +707,34 @@ extern "C" int hippo_kda_fwd(const void* q, const void* k, const void* v, const 
   return -1;
 }
 
+// Only the per-chunk kernel (gate cumsum, WY / A matrices): recomputes G, w, u, qg, kg, Aqk, Ainv, Akk from the inputs.
+// Used by the backward pass when the forward was asked not to keep these tensors (activation-memory option).
+template <int DK>
+static int launch_fwd_intra(const void* q, const void* k, const void* v, const float* g, const float* beta, const int* cs,
+                            const int* cl, int NC, int H, float* G, void* w, void* u, void* qg, void* kg, void* Aqk,
+                            void* Ainv, void* Akk, cudaStream_t s) {
+  auto k1 = kda_fwd_intra_kernel<DK>;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, kda_intra_smem<DK>());
+    if (e != cudaSuccess) return (int)e;
+    once = true;
+  }
+  if (NC == 0) return 0;
+  k1<<<dim3(NC, H), 512, kda_intra_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, g, beta, cs, cl, H,
+                                                    G, (bf16*)w, (bf16*)u, (bf16*)qg, (bf16*)kg, (bf16*)Aqk, (bf16*)Ainv, (bf16*)Akk);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int hippo_kda_fwd_intra(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                   const int* chunk_start, const int* chunk_len, int NC, int H, int DK, float* G, void* w,
+                                   void* u, void* qg, void* kg, void* Aqk, void* Ainv, void* Akk, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (DK == 128) return launch_fwd_intra<128>(q, k, v, g, beta, chunk_start, chunk_len, NC, H, G, w, u, qg, kg, Aqk, Ainv, Akk, s);
+  if (DK == 64) return launch_fwd_intra<64>(q, k, v, g, beta, chunk_start, chunk_len, NC, H, G, w, u, qg, kg, Aqk, Ainv, Akk, s);
+  return -1;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // Chunk table built on the device (no host sync): chunks never straddle a sequence boundary.
 // cu: [N+1] int32. Outputs padded to nc_max entries; unused chunks get len 0.

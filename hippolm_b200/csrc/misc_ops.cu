@@ -444,37 +444,102 @@ __global__ void axpby_update_kernel(void* w, int w_bf16, const bf16* __restrict_
     if (w_bf16) st8((bf16*)w + i, wv); else { *(float4*)((float*)w + i) = make_float4(wv[0],wv[1],wv[2],wv[3]); *(float4*)((float*)w + i + 4) = make_float4(wv[4],wv[5],wv[6],wv[7]); }
   }
 }
-// NVFP4 weights without a master copy: dequantise a 16-element block, w <- w*wd - lr*o, re-quantise in place
-// (block scale recomputed, tensor-level scale kept)
-__global__ void nvfp4_apply_update_kernel(uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, const float* gs_ptr,
-                                          const bf16* __restrict__ o, long long nblocks, float wd, float lr) {
-  long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= nblocks) return;
+// NVFP4 weights without a master copy. One optimizer update of a tensor is three launches:
+//   1. nvfp4_update_absmax_kernel   absmax of the UPDATED values w*wd - lr*o (nothing is written)
+//   2. nvfp4_global_scale_kernel    tensor scale of the updated tensor, gs_new = absmax / (6 * 448)
+//   3. nvfp4_apply_update_kernel    dequantise each 16-element block with the old tensor scale, update, re-quantise
+//                                   against gs_new with a block scale rounded UP to e4m3 (no element exceeds 6 block
+//                                   scales, so nothing saturates however far the weights have grown) and E2M1 codes
+//                                   chosen by STOCHASTIC rounding.
+// Round-to-nearest would drop every update smaller than half a code step (most Muon steps are), so a no-master weight
+// would stop learning; with stochastic rounding the expected stored value equals the exact updated value.
+// Random numbers: Philox4x32-10 keyed by (seed, 0) with the block index as counter: reproducible for a given seed,
+// independent of the launch geometry.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += 0x9E3779B9u; k.y += 0xBB67AE85u;
+  }
+  return c;
+}
+__device__ __forceinline__ void nvfp4_updated_block(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                                    float gs, const bf16* __restrict__ o, long long b, float wd, float lr,
+                                                    float (&f)[16], float& bm) {
   const float lut[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float gs = *gs_ptr;
   float s = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)scales[b], __NV_E4M3))) * gs;
   uint2 pv = *(const uint2*)(packed + b * 8);
   const uint8_t* pb = (const uint8_t*)&pv;
-  float f[16], a[8], c[8];
+  float a[8], c[8];
   ld8(o + b * 16, a); ld8(o + b * 16 + 8, c);
-  float bm = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     uint8_t lo = pb[i] & 0xF, hi = pb[i] >> 4;
     f[2 * i] = ((lo & 8) ? -lut[lo & 7] : lut[lo & 7]) * s;
     f[2 * i + 1] = ((hi & 8) ? -lut[hi & 7] : lut[hi & 7]) * s;
   }
+  bm = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) { f[i] = f[i] * wd - lr * (i < 8 ? a[i] : c[i - 8]); bm = fmaxf(bm, fabsf(f[i])); }
-  float sraw = fminf(bm / 6.f / gs, 448.f);
-  __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
-  scales[b] = (uint8_t)s8;
-  float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
-  uint2 outv; uint8_t* ob = (uint8_t*)&outv;
+}
+__global__ void nvfp4_update_absmax_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                           const float* gs_ptr, const bf16* __restrict__ o, long long nblocks, float wd,
+                                           float lr, float* amax) {
+  const float gs = *gs_ptr;
+  float m = 0.f;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (long long)gridDim.x * blockDim.x) {
+    float f[16], bm;
+    nvfp4_updated_block(packed, scales, gs, o, b, wd, lr, f, bm);
+    m = fmaxf(m, bm);
+  }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float lo = sdec > 0.f ? f[2 * i] / sdec : f[2 * i], hi = sdec > 0.f ? f[2 * i + 1] / sdec : f[2 * i + 1];
-    ob[i] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  if ((threadIdx.x & 31) == 0) atomicMax((int*)amax, __float_as_int(m));
+}
+// E2M1 code (magnitude index 0..7) of |x| <= 6 by stochastic rounding with u uniform in [0, 1)
+__device__ __forceinline__ uint8_t e2m1_sr(float x, float u) {
+  const float ax = fminf(fabsf(x), 6.f);
+  // grid 0, .5, 1, 1.5, 2, 3, 4, 6: step .5 below 2, 1 below 4, 2 above
+  float lo, step; int idx;
+  if (ax < 2.f) { idx = (int)(ax * 2.f); lo = idx * .5f; step = .5f; }
+  else if (ax < 4.f) { idx = 4 + (int)(ax - 2.f); lo = 2.f + (float)(idx - 4); step = 1.f; }
+  else { idx = ax < 6.f ? 6 : 7; lo = idx == 6 ? 4.f : 6.f; step = 2.f; }
+  if (idx < 7 && u < (ax - lo) / step) ++idx;
+  return (uint8_t)(idx | (x < 0.f ? 8 : 0));
+}
+__global__ void nvfp4_apply_update_kernel(uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, const float* gs_old_ptr,
+                                          const float* gs_new_ptr, const bf16* __restrict__ o, long long nblocks,
+                                          long long block0, float wd, float lr, uint32_t seed, int stochastic) {
+  long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const float gs_new = *gs_new_ptr;
+  float f[16], bm;
+  nvfp4_updated_block(packed, scales, *gs_old_ptr, o, b, wd, lr, f, bm);
+  // block scale rounded up to the next e4m3 value: absmax / scale <= 6, nothing clips
+  const float sraw = fminf(bm / 6.f / gs_new, 448.f);
+  __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+  if (__half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) < sraw && s8 < 0x7E) ++s8;
+  scales[b] = (uint8_t)s8;
+  const float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs_new;
+  const float inv = sdec > 0.f ? 1.f / sdec : 0.f;
+  uint2 outv; uint8_t* ob = (uint8_t*)&outv;
+  if (stochastic) {
+    const unsigned long long gb = (unsigned long long)(block0 + b);
+    uint32_t r[8];
+    uint4 r0 = philox4x32_10(make_uint4((uint32_t)gb, (uint32_t)(gb >> 32), 0u, 0u), make_uint2(seed, 0x5EEDu));
+    uint4 r1 = philox4x32_10(make_uint4((uint32_t)gb, (uint32_t)(gb >> 32), 1u, 0u), make_uint2(seed, 0x5EEDu));
+    r[0] = r0.x; r[1] = r0.y; r[2] = r0.z; r[3] = r0.w; r[4] = r1.x; r[5] = r1.y; r[6] = r1.z; r[7] = r1.w;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float u0 = (float)(r[i] & 0xFFFFu) * (1.f / 65536.f), u1 = (float)(r[i] >> 16) * (1.f / 65536.f);
+      ob[i] = (uint8_t)(e2m1_sr(f[2 * i] * inv, u0) | (e2m1_sr(f[2 * i + 1] * inv, u1) << 4));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      ob[i] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_E2M1, cudaRoundNearest);
   }
   *(uint2*)(packed + b * 8) = outv;
 }
@@ -516,11 +581,30 @@ extern "C" int hippo_axpby_update(void* w, int w_bf16, const void* o, long long 
   axpby_update_kernel<<<grid8(n), 256, 0, ST(s)>>>(w, w_bf16, (const bf16*)o, n, wd, lr);
   RET();
 }
-extern "C" int hippo_nvfp4_apply_update(void* packed, void* scales, const float* gs, const void* o, long long rows,
-                                        long long K, float wd, float lr, void* s) {
+// Pass 1 of a no-master NVFP4 update: amax <- max(amax, absmax(w*wd - lr*o)) over rows of one segment (amax: device
+// fp32[1], zeroed by the caller before the first segment of a tensor).
+extern "C" int hippo_nvfp4_update_absmax(const void* packed, const void* scales, const float* gs, const void* o,
+                                         long long rows, long long K, float wd, float lr, float* amax, void* s) {
   if (K % 16) return -1;
   long long nb = rows * K / 16;
-  nvfp4_apply_update_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>((uint8_t*)packed, (uint8_t*)scales, gs, (const bf16*)o, nb, wd, lr);
+  unsigned grid = (unsigned)((nb + 255) / 256); if (grid > 2368) grid = 2368; if (grid == 0) grid = 1;
+  nvfp4_update_absmax_kernel<<<grid, 256, 0, ST(s)>>>((const uint8_t*)packed, (const uint8_t*)scales, gs, (const bf16*)o, nb, wd, lr, amax);
+  RET();
+}
+// gs_new <- amax / (6 * 448) (1 for an all-zero tensor)
+extern "C" int hippo_nvfp4_scale_from_absmax(const float* amax, float* gs_new, void* s) {
+  nvfp4_global_scale_kernel<<<1, 1, 0, ST(s)>>>(amax, gs_new);
+  RET();
+}
+// Pass 2: rows of one segment re-quantised against gs_new (gs_old == gs_new keeps the tensor scale). block0 = index of the
+// segment's first 16-element block inside the tensor (the random stream is a function of (seed, global block index)).
+extern "C" int hippo_nvfp4_apply_update(void* packed, void* scales, const float* gs_old, const float* gs_new, const void* o,
+                                        long long rows, long long K, long long block0, float wd, float lr, unsigned seed,
+                                        int stochastic, void* s) {
+  if (K % 16) return -1;
+  long long nb = rows * K / 16;
+  nvfp4_apply_update_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, ST(s)>>>((uint8_t*)packed, (uint8_t*)scales, gs_old, gs_new,
+                                                                            (const bf16*)o, nb, block0, wd, lr, seed, stochastic);
   RET();
 }
 extern "C" int hippo_adamw_bf16(void* p, const void* g, void* m, void* v, long long n, float lr, float b1, float b2,

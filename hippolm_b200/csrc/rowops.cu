@@ -3,6 +3,7 @@
 // vector accesses. Each forward has its backward here. They replace the reference's Triton kernels
 // (fla/modules/layernorm.py:194-458, fused_norm_gate.py:35-330, l2norm.py:25-112, gate.py:143-417).
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -495,32 +496,38 @@ constexpr int kNoAllocBlocks = 148;                    // one block per SM of a 
 constexpr int kNoAllocMaxD = 8192;                     // widest row the entry point accepts
 static __device__ __align__(256) float g_noalloc_dw_part[kNoAllocBlocks * kNoAllocMaxD];   // 4.6 MiB
 constexpr int kNoAllocMaxDevices = 64;
-static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};   // device address of the array, per device
+// device address of the array, per device; host threads may race to fill an entry, but they all store the same value,
+// and the atomic keeps the store and the later loads well-defined
+static std::atomic<float*> g_noalloc_ptr[kNoAllocMaxDevices];
 }  // namespace hippo
 
 extern "C" int hippo_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
                                          float* dw, long long T, int D, void* s) {
   using namespace hippo;
   if (T <= 0 || D <= 0 || D % 8 != 0 || D > kNoAllocMaxD) return -22;      // wider than the built-in scratch
+  if (T > 0x7fffffffLL) return -24;                                        // the kernels index rows with 32-bit ints
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kNoAllocMaxDevices) return -23;
-  if (g_noalloc_ptr[dev] == nullptr) {
+  float* part = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (part == nullptr) {
     // First call on this device: ask the runtime where this device's copy of the array lives. In host code
     // the array's name is only a handle; a kernel must be given the address obtained here.
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, g_noalloc_dw_part);
     if (e != cudaSuccess) return (int)e;
-    g_noalloc_ptr[dev] = p;
+    g_noalloc_ptr[dev].store(p, std::memory_order_release);
+    part = p;
   }
-  float* part = g_noalloc_ptr[dev];
   const int nblocks = (int)(T < kNoAllocBlocks ? T : kNoAllocBlocks);
   const int maxv = (D + 2047) / 2048;
   // every block writes all D entries of its own row of `part`, so nothing has to be cleared between calls
   if (maxv <= 1) rmsnorm_bwd_kernel<1><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
   else if (maxv == 2) rmsnorm_bwd_kernel<2><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
   else rmsnorm_bwd_kernel<4><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, part, (int)T, D);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;                                     // do not sum partials that were never written
   colsum_kernel<<<(D + 255) / 256, 256, 0, ST(s)>>>(part, dw, nblocks, D);
   RET();
 }

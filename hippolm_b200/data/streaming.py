@@ -283,24 +283,31 @@ def build_streaming_iterator(args, cfg, mesh, local_batch: int, seq_len: int):
     from .tokenizer import load_tokenizer
     tok = load_tokenizer(getattr(args, "tokenizer_path", None))
     data_files = getattr(args, "data_files", None)
-    if not data_files:
-        raise ValueError("no dataset configured: set use_dummy_data / synthetic_data, or data_files (parquet or jsonl)")
-    files = data_files if isinstance(data_files, (list, tuple)) else [data_files]
+    if data_files:
+        files = data_files if isinstance(data_files, (list, tuple)) else [data_files]
+        if getattr(args, "shuffle", False):
+            import random
+            files = list(files)
+            random.Random(int(getattr(args, "seed", 0))).shuffle(files)
 
-    def rows():
-        import json
-        for i, f in enumerate(files):
-            if i % mesh.dp != mesh.dp_rank and len(files) >= mesh.dp:
-                continue
-            if str(f).endswith(".parquet"):
-                yield from iter_parquet_rows(f)
-            else:
-                with open(f) as fh:
-                    for line in fh:
-                        if line.strip():
-                            yield json.loads(line)
-    ds = StreamingDataset(rows(), tok, getattr(args, "text_field", "content"), getattr(args, "stage", "pretrain"),
-                          max_len=seq_len)
+        def rows():
+            import json
+            for i, f in enumerate(files):
+                if i % mesh.dp != mesh.dp_rank and len(files) >= mesh.dp:
+                    continue
+                if str(f).endswith(".parquet"):
+                    yield from iter_parquet_rows(f)
+                else:
+                    with open(f) as fh:
+                        for line in fh:
+                            if line.strip():
+                                yield json.loads(line)
+        ds = StreamingDataset(rows(), tok, getattr(args, "text_field", "content"), getattr(args, "stage", "pretrain"),
+                              max_len=seq_len)
+    else:
+        # hub datasets named by --pretrain_* / --sft_* (ModelScope first with --use_modelscope, hub as the fallback)
+        from .sources import build_hub_dataset
+        ds = build_hub_dataset(args, tok, seq_len)
     q = queue.Queue(maxsize=2)
     pb = PrefetchBatcher(ds, [q], local_batch, seq_len, cfg.pack_chunk_size, int(getattr(args, "pack_buffer_size", 2048)),
                          pad_id=getattr(tok, "pad_token_id", 0) or 0, eos_id=getattr(tok, "eos_token_id", None))

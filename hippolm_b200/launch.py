@@ -3,7 +3,11 @@
 ``select_gpus`` picks the largest contiguous run of 8/4/2/1 GPUs with enough free memory, reading
 free memory through an injectable query (NVML -> torch fallback) so it is testable without a GPU.
 ``launch`` runs one worker per GPU with ``torch.multiprocessing.spawn`` (or inline when world == 1);
-under ``torchrun`` (RANK set) the worker simply runs in this process.
+under ``torchrun`` (RANK set) the worker simply runs in this process. Before spawning on a CUDA machine it
+picks the GPUs with ``select_gpus(args.min_gpu_memory_mb, want=world)`` and exposes exactly that run to the
+workers through ``CUDA_VISIBLE_DEVICES``. ``--tp_sim`` runs the same ranks as CPU processes over gloo
+(the reference's TP simulation puts N ranks on one GPU, ``src/training/launch/tp_sim.py:26``; here the
+simulated ranks need no GPU at all).
 """
 from __future__ import annotations
 
@@ -54,10 +58,42 @@ def _spawn_entry(rank: int, world: int, port: int, fn, args):
     fn(args)
 
 
+def pick_devices(args, world: int, query: Optional[Callable[[], Sequence[int]]] = None,
+                 have_cuda: Optional[bool] = None) -> Optional[List[int]]:
+    """GPU indices for ``world`` workers, None when the run uses no GPU (CPU box or ``--tp_sim``).
+    Raises when fewer than ``world`` contiguous GPUs have ``min_gpu_memory_mb`` free."""
+    if bool(getattr(args, "tp_sim", False)):
+        return None
+    if have_cuda is None:
+        import torch
+        have_cuda = torch.cuda.is_available()
+    if not have_cuda:
+        return None
+    need = int(getattr(args, "min_gpu_memory_mb", 0) or 0)
+    gpus = select_gpus(need, want=world, query=query)
+    if len(gpus) != world:
+        raise RuntimeError(f"no contiguous run of {world} GPU(s) with {need} MiB free "
+                           f"(lower --min_gpu_memory_mb or the number of ranks)")
+    return gpus
+
+
 def launch(fn, args, world: int) -> None:
-    if "RANK" in os.environ or world <= 1:
+    if "RANK" in os.environ:
+        fn(args)                         # under torchrun: the launcher already chose the devices
+        return
+    if bool(getattr(args, "tp_sim", False)):
+        os.environ["HIPPO_TP_SIM"] = "1"  # ranks become CPU processes over gloo (see parallel/mesh.py)
+    gpus = pick_devices(args, max(1, world))
+    if world <= 1:
+        if gpus is not None:
+            os.environ["LOCAL_RANK"] = str(gpus[0])     # the inline worker binds to the selected GPU
         fn(args)
         return
+    if gpus is not None:
+        # the spawned workers see exactly the selected run, as local devices 0..world-1
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = [int(x) for x in vis.split(",")] if vis else None
+        os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(str(phys[g] if phys else g) for g in gpus)
     import torch.multiprocessing as mp
     port = 29500 + os.getpid() % 1000
     mp.spawn(_spawn_entry, args=(world, port, fn, args), nprocs=world, join=True)

@@ -175,7 +175,7 @@ class KDAAttention(nn.Module):
         gate = ops.linear(fg[:, Vd:].contiguous(), self.g_proj1_weight, self.g_proj1_bias)
         g = ops.kda_gate(g_raw.view(T, Hl, K), self.A_log, self.dt_bias, cfg.safe_gate, cfg.lower_bound)
         o, final = ops.kda(q, k, v, g, beta, scale=1.0, initial_state=initial_state, cu_seqlens=cu_seqlens,
-                           use_qk_l2norm=False, mode=cfg.kda_mode)
+                           use_qk_l2norm=False, mode=cfg.kda_mode, skip_saved=cfg.kda_skip_aqk_akk_saved)
         o = ops.gated_rmsnorm(o, gate.view(T, Hl, Vd), self.o_norm_weight, cfg.rms_norm_eps)
         out = row_linear_sp(o.reshape(T, Hl * Vd), self.o_proj_weight)       # [T/w, D]
         return out, final

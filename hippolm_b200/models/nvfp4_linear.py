@@ -74,6 +74,7 @@ class NVFP4Linear(nn.Module):
         self.no_master = no_master
         self.act_quant = act_quant
         self.compute_dtype = dtype
+        self.stochastic_rounding = True          # optimizer updates of the no-master weight round without bias
         if init_weight is None:
             init_weight = torch.empty(out_features, in_features, device=device, dtype=torch.float32)
             nn.init.xavier_uniform_(init_weight)
@@ -93,7 +94,8 @@ class NVFP4Linear(nn.Module):
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.no_master:
-            return _NVFP4MatmulNoMaster.apply(x, self, self._anchor.requires_grad_(False))
+            return _NVFP4MatmulNoMaster.apply(x, self, self._anchor.requires_grad_(torch.is_grad_enabled()
+                                                                                   and not x.requires_grad))
         return _NVFP4MatmulSTE.apply(x, self.weight, self.act_quant)
 
     def accumulate_grad_product(self, dy: torch.Tensor, x: torch.Tensor) -> None:
@@ -122,9 +124,27 @@ class NVFP4Linear(nn.Module):
     def material_chunk(self, r0: int, r1: int, dtype=torch.float32) -> torch.Tensor:
         return ops.nvfp4_dequantize(self.packed_weight[r0:r1], self.scales[r0:r1], self.global_scale, dtype)
 
-    def commit_chunk(self, r0: int, r1: int, w: torch.Tensor) -> None:
-        """Re-quantise rows [r0, r1) against the module's current global scale."""
-        packed, scales, _ = ops.nvfp4_quantize(w, self.global_scale)
+    def commit_chunk(self, r0: int, r1: int, w: torch.Tensor, stochastic: bool = False) -> None:
+        """Re-quantise rows [r0, r1) against the module's tensor scale. If the rows have outgrown that scale (a block
+        scale would exceed the e4m3 maximum of 448 and clip), the whole tensor is first re-expressed against a larger
+        tensor scale. ``stochastic``: unbiased rounding for optimizer updates of a weight that has no master copy
+        (round-to-nearest silently drops every update below half a code step)."""
+        need = w.detach().abs().max().float() / (6.0 * 448.0)
+        if bool(need > self.global_scale.reshape(()).float()):
+            full = self.material_chunk(0, self.out_features, torch.float32)
+            full[r0:r1] = w.float()
+            self.global_scale.copy_(torch.maximum(need, full.abs().max() / (6.0 * 448.0)).reshape(1))
+            packed, scales, _ = ops.nvfp4_quantize(full, self.global_scale)
+            self.packed_weight.copy_(packed); self.scales.copy_(scales)
+            if not stochastic:
+                return
+        if stochastic:
+            from ..ref.ops import nvfp4_quantize_stochastic
+            self._sr_calls = getattr(self, "_sr_calls", 0) + 1
+            gen = torch.Generator(device=w.device).manual_seed(0x5EED + 7919 * self._sr_calls + r0)
+            packed, scales, _ = nvfp4_quantize_stochastic(w, self.global_scale, gen)
+        else:
+            packed, scales, _ = ops.nvfp4_quantize(w, self.global_scale)
         self.packed_weight[r0:r1].copy_(packed)
         self.scales[r0:r1].copy_(scales)
 
@@ -136,7 +156,7 @@ class NVFP4Linear(nn.Module):
         """W[r0:r1] <- W*wd_factor - lr*update, then re-quantise those rows."""
         w = self.material_chunk(r0, r1, torch.float32)
         w.mul_(wd_factor).add_(update.float(), alpha=-lr)
-        self.commit_chunk(r0, r1, w)
+        self.commit_chunk(r0, r1, w, stochastic=self.stochastic_rounding)
 
     def material_bf16_view(self) -> torch.Tensor:
         return self.material_chunk(0, self.out_features, torch.bfloat16)

@@ -315,9 +315,9 @@ def kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_
     return _KDAPrologue.apply(proj, H, K, off_q, off_k, off_v, off_b, float(scale), float(beta_mul), bool(apply_silu))
 
 
-def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm):
+def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm, skip_saved=False, mode="chunk"):
     from . import kda_cuda
-    return kda_cuda.kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+    return kda_cuda.kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm, skip_saved, mode)
 
 
 def causal_attention(q, k, v, cu_seqlens, scale):

@@ -130,10 +130,12 @@ def kda_gate(x_g, A_log, dt_bias, safe_gate: bool = False, lower_bound: float = 
 
 
 def kda(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
-        use_qk_l2norm: bool = True, mode: str = "chunk") -> Tuple[torch.Tensor, torch.Tensor]:
-    """Kimi delta attention over a packed token stream; see :mod:`hippolm_b200.ref.kda`."""
+        use_qk_l2norm: bool = True, mode: str = "chunk", skip_saved: bool = False
+        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Kimi delta attention over a packed token stream; see :mod:`hippolm_b200.ref.kda`. ``skip_saved`` (CUDA): keep
+    fewer activations for backward and recompute the per-chunk matrices there."""
     if q.is_cuda:
-        return _cu().kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
+        return _cu().kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm, skip_saved, mode)
     if mode == "fused_recurrent":
         return _rk.kda_recurrent(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)
     return _rk.kda_chunked(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm)

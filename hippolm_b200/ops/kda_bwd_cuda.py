@@ -8,8 +8,13 @@ from ._ext import lib, ptr, stream_ptr, check
 
 
 def backward(ctx, do, dfin):
-    q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc, so = ctx.saved_tensors
     T, H, DK, NC, N = ctx.dims
+    if getattr(ctx, "skip_saved", False):
+        from .kda_cuda import recompute_intra
+        q, k, v, beta, g, vnew, Sst, cs, cl, sc, so = ctx.saved_tensors
+        G, w, qg, kg, Aqk, Ainv, Akk = recompute_intra(q, k, v, g, beta, cs, cl, NC, H, DK)
+    else:
+        q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, cs, cl, sc, so = ctx.saved_tensors
     dev = q.device
     do = do.to(torch.bfloat16).contiguous()
     dfin_c = dfin.float().contiguous() if dfin is not None else None
@@ -28,4 +33,4 @@ def backward(ctx, do, dfin):
                               DK, ptr(dvn), ptr(dSst), ptr(dw), ptr(dAqk), ptr(dKK), ptr(dbk), ptr(dq_acc), ptr(dk_acc),
                               ptr(dG_acc), ptr(dq), ptr(dk), ptr(dv), ptr(dg), ptr(dbeta), ptr(dh0), stream_ptr()),
           "kda_bwd")
-    return dq, dk, dv, dg, dbeta, dh0, None
+    return dq, dk, dv, dg, dbeta, dh0, None, None

@@ -83,8 +83,27 @@ def apply_update(w: torch.Tensor, o: torch.Tensor, wd_factor: float, lr: float) 
                                    C.c_float(wd_factor), C.c_float(lr), stream_ptr()), "axpby_update")
 
 
-def nvfp4_apply_update(packed, scales, gs, o, wd_factor: float, lr: float) -> None:
-    rows, K2 = packed.shape
-    check(lib().hippo_nvfp4_apply_update(ptr(packed), ptr(scales.view(torch.uint8)), ptr(gs), ptr(o), C.c_longlong(rows),
-                                         C.c_longlong(K2 * 2), C.c_float(wd_factor), C.c_float(lr), stream_ptr()),
-          "nvfp4_apply_update")
+def nvfp4_apply_update(mod, segments, wd_factor: float, lr: float, seed: int, stochastic: bool = True) -> None:
+    """In-place update of a no-master NVFP4 weight: ``segments`` = [(row0, row1, o bf16 [row1-row0, K])] covering the
+    rows that change. Three passes on the device and no host sync: absmax of the updated values over all segments,
+    tensor scale from it, re-quantisation (block scales rounded up, stochastic E2M1 rounding) against the new scale."""
+    packed, scales, gs = mod.packed_weight, mod.scales.view(torch.uint8), mod.global_scale
+    K = packed.shape[1] * 2
+    whole = sum(b - a for a, b, _ in segments) == packed.shape[0]
+    tmp = torch.zeros(2, dtype=torch.float32, device=packed.device)          # [absmax, new tensor scale]
+    amax, gs_new = tmp[0:1], tmp[1:2]
+    if whole:
+        for a, b, o in segments:
+            check(lib().hippo_nvfp4_update_absmax(ptr(packed[a:b]), ptr(scales[a:b]), ptr(gs), ptr(o), C.c_longlong(b - a),
+                                                  C.c_longlong(K), C.c_float(wd_factor), C.c_float(lr), ptr(amax),
+                                                  stream_ptr()), "nvfp4_update_absmax")
+        check(lib().hippo_nvfp4_scale_from_absmax(ptr(amax), ptr(gs_new), stream_ptr()), "nvfp4_scale_from_absmax")
+    else:
+        gs_new = gs                # a partial update cannot move the tensor scale of the rows it does not touch
+    for a, b, o in segments:
+        check(lib().hippo_nvfp4_apply_update(ptr(packed[a:b]), ptr(scales[a:b]), ptr(gs), ptr(gs_new), ptr(o),
+                                             C.c_longlong(b - a), C.c_longlong(K), C.c_longlong(a * (K // 16)),
+                                             C.c_float(wd_factor), C.c_float(lr), C.c_uint(seed & 0xFFFFFFFF),
+                                             1 if stochastic else 0, stream_ptr()), "nvfp4_apply_update")
+    if whole:
+        gs.copy_(gs_new)

@@ -16,6 +16,7 @@ Differences on purpose: NS runs on the whole (local) matrix, not on 4096-row sli
 """
 from __future__ import annotations
 
+import re
 import math
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -71,8 +72,11 @@ class Muon:
     def __init__(self, lr: float = 0.02, momentum: float = 0.95, weight_decay: float = 0.0,
                  nesterov: bool = True, ns_steps: int = 5, momentum_dtype=torch.bfloat16,
                  offload: bool = False, ns_row_chunk: Optional[int] = None, ns_scope: str = "shard",
-                 dp_shard: bool = False):
+                 dp_shard: bool = False, stochastic_rounding: bool = True, sr_seed: int = 0):
         self.ns_scope = ns_scope
+        # no-master NVFP4 weights are re-quantised with stochastic rounding (expected value = exact update), keyed by
+        # (sr_seed, entry, step) so a run is reproducible
+        self.stochastic_rounding, self.sr_seed = stochastic_rounding, int(sr_seed)
         # Under data parallelism every matrix has one owner among the DP replicas (greedy by size): only the owner runs
         # momentum + Newton-Schulz + the update, then broadcasts the new weights to its DP peers. Cuts the Muon work per
         # rank by the DP degree; the reference has neither data parallelism nor this split.
@@ -96,6 +100,7 @@ class Muon:
         self._alloc(_Entry(None, mod, name))
 
     def _alloc(self, e: _Entry):
+        e.idx = len(self.entries)
         if self.offload:
             e.exp_avg = _pinned_like(e.shape, self.momentum_dtype)
         else:
@@ -144,6 +149,7 @@ class Muon:
         for (a, b) in segs:
             if full_scope and b > a and self._shard_dim(e, (a, b)) is not None:
                 return False
+        fp4_segments = []
         for (a, b) in segs:
             if b <= a:
                 continue
@@ -160,8 +166,12 @@ class Muon:
             if e.param is not None:
                 mc.apply_update(e.param.data[a:b], o, wd_factor, self.lr)
             else:
-                mod = e.module
-                mc.nvfp4_apply_update(mod.packed_weight[a:b], mod.scales[a:b], mod.global_scale, o, wd_factor, self.lr)
+                fp4_segments.append((a, b, o))
+        if fp4_segments:
+            # all segments of a no-master NVFP4 tensor share one tensor scale: update them together
+            mc.nvfp4_apply_update(e.module, fp4_segments, wd_factor, self.lr,
+                                  seed=(self.sr_seed * 1000003 + e.step * 7919 + getattr(e, "idx", 0)) & 0x7FFFFFFF,
+                                  stochastic=self.stochastic_rounding)
         e.step += 1
         return True
 
@@ -384,7 +394,8 @@ def build_param_groups(model: nn.Module, args=None, precision: Optional[Precisio
                 weight_decay=g("muon_weight_decay", 0.0), nesterov=True, ns_steps=5,
                 momentum_dtype=prec.muon_momentum, offload=offload,
                 ns_row_chunk=g("muon_ns_row_chunk", None), ns_scope=g("muon_ns_scope", "shard"),
-                dp_shard=bool(g("muon_dp_shard", True)))
+                dp_shard=bool(g("muon_dp_shard", True)),
+                stochastic_rounding=bool(g("nvfp4_stochastic_rounding", True)), sr_seed=int(g("seed", 0) or 0))
     adamw = AdamW(lr=g("learning_rate", 0.004), betas=(g("adamw_beta1", 0.9), g("adamw_beta2", 0.95)),
                   eps=g("adamw_eps", 1e-8), weight_decay=g("weight_decay", 0.01),
                   m_dtype=prec.adamw_m, v_dtype=prec.adamw_v, offload=offload,
@@ -399,8 +410,11 @@ def build_param_groups(model: nn.Module, args=None, precision: Optional[Precisio
             muon.add_param(p, name)
         else:
             adamw.add_param(p, name)
+    rx = g("trainable_regex", None)
     for name, mod in model.named_modules():
         if isinstance(mod, NVFP4Linear) and mod.no_master:
+            if rx and not re.search(rx, name):
+                continue                     # frozen: the module keeps its weights, its dW products are dropped
             muon.register_nvfp4_module(mod, name)
     return muon, adamw
 

@@ -208,16 +208,20 @@ class _NVFP4RowSP(torch.autograd.Function):
         return dx, ops.gemm_tn(dyg, x).to(mod.weight.dtype), None
 
 
-def _nvfp4_weight_arg(module):
-    return module._anchor.requires_grad_(False) if module.no_master else module.weight
+def _nvfp4_weight_arg(module, x):
+    if not module.no_master:
+        return module.weight
+    # a no-master module has no autograd leaf: when nothing upstream requires a gradient (everything else frozen) the
+    # anchor does, so that backward still reaches this layer and its dW product is formed
+    return module._anchor.requires_grad_(torch.is_grad_enabled() and not x.requires_grad)
 
 
 def nvfp4_column_linear_sp(x: torch.Tensor, module):
-    return _NVFP4ColumnSP.apply(x, _nvfp4_weight_arg(module), module)
+    return _NVFP4ColumnSP.apply(x, _nvfp4_weight_arg(module, x), module)
 
 
 def nvfp4_row_linear_sp(x: torch.Tensor, module):
-    return _NVFP4RowSP.apply(x, _nvfp4_weight_arg(module), module)
+    return _NVFP4RowSP.apply(x, _nvfp4_weight_arg(module, x), module)
 
 
 def column_linear_sp(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):

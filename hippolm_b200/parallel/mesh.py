@@ -85,7 +85,8 @@ def init_distributed_from_env(backend: Optional[str] = None, timeout_s: float = 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
-    use_cuda = torch.cuda.is_available()
+    # HIPPO_TP_SIM=1 (``--tp_sim``): simulated ranks are CPU processes over gloo even on a GPU machine
+    use_cuda = torch.cuda.is_available() and os.environ.get("HIPPO_TP_SIM", "0") != "1"
     device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)

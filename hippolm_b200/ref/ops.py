@@ -137,6 +137,36 @@ def nvfp4_quantize(w: torch.Tensor, global_scale: Optional[torch.Tensor] = None
     return packed.contiguous(), sc.contiguous(), gs
 
 
+def nvfp4_quantize_stochastic(w: torch.Tensor, global_scale: torch.Tensor, generator: Optional[torch.Generator] = None
+                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """NVFP4 quantisation for weights that have no master copy: block scales rounded UP to e4m3 (no element exceeds six
+    block scales) and E2M1 codes by stochastic rounding, so that E[dequantise(quantise(w))] = w for |w| inside the
+    range of ``global_scale``. Same layout as :func:`nvfp4_quantize`."""
+    N, K = w.shape
+    assert K % 16 == 0
+    gs = global_scale.float().reshape(1)
+    blk = w.float().view(N, K // 16, 16)
+    want = (blk.abs().amax(-1) / 6.0 / gs).clamp(max=448.0)
+    sc = want.to(torch.float8_e4m3fn)
+    low = sc.float() < want
+    bumped = (sc.view(torch.uint8) + low.to(torch.uint8)).clamp(max=0x7E).view(torch.float8_e4m3fn)
+    sc = torch.where(low, bumped.float(), sc.float()).to(torch.float8_e4m3fn)
+    scf = sc.float() * gs
+    denom = torch.where(scf > 0, scf, torch.ones_like(scf)).unsqueeze(-1)
+    xs = (blk / denom).clamp(-6.0, 6.0)
+    ax = xs.abs()
+    levels = torch.tensor(E2M1_LEVELS, dtype=torch.float32, device=w.device)
+    idx = (torch.bucketize(ax, levels, right=True) - 1).clamp(0, 7)          # largest level <= |x|
+    lo = levels[idx]
+    hi = levels[(idx + 1).clamp(max=7)]
+    p = torch.where(hi > lo, (ax - lo) / (hi - lo).clamp(min=1e-9), torch.zeros_like(ax))
+    u = torch.rand(ax.shape, generator=generator, device=w.device)
+    idx = (idx + (u < p).long()).clamp(max=7)
+    code = (idx | ((xs < 0).long() << 3)).view(N, K).to(torch.uint8)
+    packed = code[:, 0::2] | (code[:, 1::2] << 4)
+    return packed.contiguous(), sc.contiguous(), gs
+
+
 def nvfp4_dequantize(packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor,
                      dtype=torch.float32) -> torch.Tensor:
     N, K2 = packed.shape

@@ -110,6 +110,12 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         wait_ms = float(getattr(args, "fused_wait_ms", 0) or 0)
         fused_on = (tokens // mesh.tp) % 128 == 0 and fused.setup(mesh, tokens, cfg.hidden_size,
                                                                   wait_cycles=int(wait_ms * 1.9e6))
+    rx = getattr(args, "trainable_regex", None)
+    if rx:
+        # train only the parameters whose name matches (e.g. "ffn" for the feed-forward weights alone)
+        import re
+        for name, p in model.named_parameters():
+            p.requires_grad_(bool(re.search(rx, name)))
     offload = bool(getattr(args, "offload_optimizer", False))
     muon, adamw = build_param_groups(model, args, precision, offload=offload)
     ctx = TrainContext(args=args, cfg=cfg, mesh=mesh, device=device, model=model, muon=muon, adamw=adamw,
@@ -165,6 +171,7 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         from ..data.loaders import build_data_iterator
         # the loader continues after the batches the checkpointed run had consumed instead of replaying them
         ctx.data_iter, ctx.prefetcher = build_data_iterator(args, cfg, mesh, start_step=data_step)
+        ctx.extras["own_data_iter"] = True
     hb = float(getattr(args, "watchdog_timeout_s", 0) or 0)
     if hb > 0:
         from .watchdog import StepWatchdog
@@ -198,6 +205,11 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
         cu = cu.to(dev, non_blocking=True)
     targets = shift_targets(labels, row_len)
     mbs = int(getattr(args, "micro_batch_size", 0) or 0)
+    gas = int(getattr(args, "gradient_accumulation_steps", 1) or 1)
+    if mbs <= 0 and gas > 1:
+        # the step's tokens are cut into ``gas`` windows; in the reference the number of chunks per step replaced this
+        # knob (``src/training/loop/run.py:92-115``), here it stays as the way to ask for N windows without naming a size
+        mbs = -(-T // gas)
     windows = _micro_batches(T, mbs, row_len)
     # valid-target count per window, summed over the data-parallel replicas, read back once per step: every replica
     # then runs (or skips) the same windows and issues the same gradient collectives
@@ -320,8 +332,18 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
             try:
                 batch = next(ctx.data_iter)
             except StopIteration:
-                ctx.logger.info("data exhausted")
-                break
+                # end of an epoch: a finite dataset is re-opened until --epochs passes have been made
+                epoch = ctx.extras.get("epoch", 0) + 1
+                if epoch >= int(getattr(args, "epochs", 1) or 1) or not ctx.extras.get("own_data_iter", False):
+                    ctx.logger.info("data exhausted")
+                    break
+                ctx.extras["epoch"] = epoch
+                ctx.logger.info(f"epoch {epoch + 1}/{args.epochs}")
+                if ctx.prefetcher is not None:
+                    ctx.prefetcher.close()
+                from ..data.loaders import build_data_iterator
+                ctx.data_iter, ctx.prefetcher = build_data_iterator(args, ctx.cfg, mesh)
+                continue
             timed = mb_timing < 0 or ctx.step < mb_timing
             timer = PhaseTimer(enabled=timed, device=ctx.device)
             t0 = time.perf_counter()

@@ -103,3 +103,44 @@ def test_hippo_config_validation():
         HippoConfig(ffn_nvfp4=False, ffn_nvfp4_no_bf16_master=True)
     c = HippoConfig(head_dim=100, pack_chunk_size=0)
     assert c.pack_chunk_size == 128 and c.block_size == 4
+
+
+def test_launch_selects_gpus_and_tp_sim_skips_them():
+    """``launch`` goes through ``select_gpus`` (``--min_gpu_memory_mb``); ``--tp_sim`` asks for no GPU."""
+    import types
+    import pytest
+    from hippolm_b200.launch import pick_devices
+    a = types.SimpleNamespace(min_gpu_memory_mb=10240, tp_sim=False)
+    free = [50000, 1000, 50000, 50000, 100, 50000, 50000, 50000]
+    assert pick_devices(a, 2, query=lambda: free, have_cuda=True) == [2, 3]
+    assert pick_devices(a, 1, query=lambda: free, have_cuda=True) == [0]
+    with pytest.raises(RuntimeError):
+        pick_devices(a, 4, query=lambda: free, have_cuda=True)
+    assert pick_devices(a, 2, query=lambda: free, have_cuda=False) is None
+    a.tp_sim = True
+    assert pick_devices(a, 2, query=lambda: free, have_cuda=True) is None
+
+
+def test_every_flag_is_read_somewhere_and_unsupported_values_are_refused():
+    """No parsed-but-ignored flag: each parser destination is read by the package (or the entry scripts), and the
+    two switches that only exist for configuration compatibility refuse the unsupported value."""
+    import glob
+    import re
+    import pytest
+    from hippolm_b200.cli import build_parser
+    from hippolm_b200.config import HippoConfig
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = ""
+    for f in glob.glob(os.path.join(root, "hippolm_b200", "**", "*.py"), recursive=True) + \
+            glob.glob(os.path.join(root, "scripts", "*.py")):
+        if not f.endswith(os.path.join("hippolm_b200", "cli.py")):
+            src += open(f).read()
+    by_pattern = {"pretrain_en_multi_config", "pretrain_zh_multi_config", "pretrain_en_qa_config", "pretrain_zh_qa_config"}
+    assert 'f"pretrain_{label}_config"' in src            # the four subset names are read through this pattern
+    unused = [a.dest for a in build_parser()._actions
+              if a.dest != "help" and a.dest not in by_pattern and not re.search(r"\b" + a.dest + r"\b", src)]
+    assert unused == [], unused
+    with pytest.raises(ValueError):
+        HippoConfig(use_bias=True)
+    with pytest.raises(ValueError):
+        HippoConfig(conv_bias=True)

@@ -85,3 +85,63 @@ def test_kda_matches_token_recurrence():
     o, f = ops.kda(q, k, v, g, beta, 1.0, None, cu, use_qk_l2norm=False)
     o2, f2 = kda_recurrent(q.cpu(), k.cpu(), v.cpu(), g.cpu(), beta.cpu(), 1.0, None, cu.cpu().long())
     assert _rel(o.cpu(), o2) < 2e-2 and _rel(f.cpu(), f2) < 2e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_kda_recurrent_kernel_matches_oracle_and_chunk_kernels(D):
+    """``kda_mode: fused_recurrent`` without gradients runs the token-recurrent kernel: same function as the token oracle
+    and as the chunk kernels, including initial state, several sequences and the final state."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ops import _ext
+    from hippolm_b200.ref.kda import kda_recurrent, l2norm
+    torch.manual_seed(D)
+    T, H = 300, 3
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda"))
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cu = torch.tensor([0, 1, 130, 300], dtype=torch.int32, device="cuda")
+    h0 = torch.randn(3, H, D, D, device="cuda") * 0.1
+    n0 = _ext.launch_count()
+    with torch.no_grad():
+        o, f = ops.kda(q, k, v, g, beta, 1.0, h0, cu, use_qk_l2norm=False, mode="fused_recurrent")
+        assert _ext.launch_count() == n0 + 1                    # one kernel, not the chunk pipeline
+        oc, fc = ops.kda(q, k, v, g, beta, 1.0, h0, cu, use_qk_l2norm=False, mode="chunk")
+    o2, f2 = kda_recurrent(q.cpu(), k.cpu(), v.cpu(), g.cpu(), beta.cpu(), 1.0, h0.cpu(), cu.cpu().long())
+    assert _rel(o.cpu(), o2) < 1e-2 and _rel(f.cpu(), f2) < 1e-3
+    assert _rel(o, oc) < 2e-2 and _rel(f, fc) < 2e-2
+    # with gradients required the same mode falls back to the differentiable chunk kernels
+    qg = q.clone().requires_grad_(True)
+    o3, _ = ops.kda(qg, k, v, g, beta, 1.0, h0, cu, use_qk_l2norm=False, mode="fused_recurrent")
+    o3.float().sum().backward()
+    assert qg.grad is not None and torch.isfinite(qg.grad).all()
+
+
+def test_kda_skip_saved_recomputes_identical_gradients():
+    """``kda_skip_aqk_akk_saved``: fewer saved activations, bit-identical outputs and gradients."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ref.kda import l2norm
+    torch.manual_seed(5)
+    T, H, D = 700, 3, 128
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda"))
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cu = torch.tensor([0, 100, 500, 700], dtype=torch.int32, device="cuda")
+    h0 = torch.randn(3, H, D, D, device="cuda") * 0.1
+    do = torch.randn(T, H, D, device="cuda")
+    res = []
+    for skip in (False, True):
+        ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta, h0)]
+        saved = []
+        with torch.autograd.graph.saved_tensors_hooks(lambda t: (saved.append(t.numel() * t.element_size()), t)[1],
+                                                      lambda t: t):
+            o, f = ops.kda(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, ins[5], cu, use_qk_l2norm=False, skip_saved=skip)
+        ((o.float() * do).sum() + f.sum()).backward()
+        res.append((o, f, [t.grad for t in ins], sum(saved)))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    for a, b in zip(res[0][2], res[1][2]):
+        assert torch.equal(a, b)
+    assert res[1][3] < 0.6 * res[0][3], (res[0][3], res[1][3])

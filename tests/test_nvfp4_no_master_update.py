@@ -1,0 +1,131 @@
+"""No-master NVFP4 weights must keep learning: updates far below one code step survive in expectation (stochastic
+rounding), and a weight that outgrows the tensor scale it was first quantised with is not clipped. CPU tests cover the
+torch restatement and the module's chunk API; the GPU tests cover the fused device kernels of the Muon path."""
+import pytest
+import torch
+
+from hippolm_b200.models.nvfp4_linear import NVFP4Linear
+from hippolm_b200.ref import ops as ro
+
+
+def test_stochastic_quantiser_is_unbiased_and_never_clips():
+    torch.manual_seed(0)
+    w = torch.randn(64, 256) * 0.05
+    _, _, gs = ro.nvfp4_quantize(w)
+    g = torch.Generator().manual_seed(1)
+    acc = torch.zeros_like(w)
+    n = 400
+    for _ in range(n):
+        p, s, _ = ro.nvfp4_quantize_stochastic(w, gs, g)
+        acc += ro.nvfp4_dequantize(p, s, gs)
+    mean = acc / n
+    # per-element standard error of the mean is ~ step / sqrt(12 n) with step <= absmax / 3
+    assert (mean - w).abs().max() < 0.25 * w.abs().max() / 3
+    assert abs(float((mean - w).mean())) < 2e-5
+    # round-to-nearest of the same tensor has a visible bias per element but none of the noise
+    p, s, _ = ro.nvfp4_quantize_stochastic(w, gs, g)
+    dq = ro.nvfp4_dequantize(p, s, gs)
+    assert float(dq.abs().max()) >= float(w.abs().max()) * 0.999          # block scale rounded up: the maximum survives
+
+
+def test_tiny_updates_accumulate_through_the_chunk_api():
+    torch.manual_seed(0)
+    lin = NVFP4Linear(256, 64, no_master=True)
+    w0 = lin.material_chunk(0, 64).clone()
+    ulp = float(w0.abs().max()) / 6 * 0.5                                 # smallest code step of the largest block
+    step = ulp / 8
+    upd = torch.ones(64, 256)
+    for _ in range(200):
+        lin.decay_and_apply_chunk(0, 64, upd, lr=step)                    # w <- w - step
+    moved = float((lin.material_chunk(0, 64) - w0).mean())
+    assert abs(moved - (-200 * step)) < 0.1 * 200 * step, (moved, -200 * step)
+    lin2 = NVFP4Linear(256, 64, no_master=True, init_weight=w0)
+    lin2.stochastic_rounding = False
+    w20 = lin2.material_chunk(0, 64).clone()
+    for _ in range(200):
+        lin2.decay_and_apply_chunk(0, 64, upd, lr=step)
+    stuck = float((lin2.material_chunk(0, 64) - w20).mean())
+    assert abs(stuck) < 0.5 * 200 * step                                  # round-to-nearest loses most of the movement
+
+
+def test_weight_growing_past_the_initial_scale_is_not_clipped():
+    torch.manual_seed(1)
+    lin = NVFP4Linear(64, 32, no_master=True)
+    w = lin.material_chunk(0, 32).clone()
+    big = w * 4.0
+    lin.stochastic_rounding = False
+    lin.commit_chunk(0, 16, big[:16])                                     # half the rows grow 4x
+    out = lin.material_chunk(0, 32)
+    assert float(out[:16].abs().max()) > 3.9 * float(w[:16].abs().max())
+    assert (out[:16] - big[:16]).abs().max() < 0.3 * big[:16].abs().max() / 6 * 2
+    assert (out[16:] - w[16:]).abs().max() < 0.3 * w.abs().max()          # untouched rows survive the rescale
+
+
+@pytest.mark.gpu
+def test_fused_update_kernel_tiny_steps_move_the_mean():
+    from hippolm_b200.ops import muon_cuda as mc
+    torch.manual_seed(0)
+    lin = NVFP4Linear(1024, 256, no_master=True, device="cuda")
+    w0 = lin.material_chunk(0, 256).clone()
+    step = float(w0.abs().max()) / 6 * 0.5 / 8
+    o = torch.ones(256, 1024, device="cuda", dtype=torch.bfloat16)
+    for i in range(200):
+        mc.nvfp4_apply_update(lin, [(0, 128, o[:128]), (128, 256, o[128:])], 1.0, step, seed=i)
+    moved = float((lin.material_chunk(0, 256) - w0).mean())
+    assert abs(moved + 200 * step) < 0.1 * 200 * step, (moved, -200 * step)
+    # same seed, same result (counter-based random numbers)
+    a, b = (NVFP4Linear(1024, 256, no_master=True, device="cuda", init_weight=w0) for _ in range(2))
+    for m in (a, b):
+        mc.nvfp4_apply_update(m, [(0, 256, o)], 1.0, step, seed=7)
+    assert torch.equal(a.packed_weight, b.packed_weight) and torch.equal(a.scales.view(torch.uint8), b.scales.view(torch.uint8))
+    # round-to-nearest loses the movement
+    c = NVFP4Linear(1024, 256, no_master=True, device="cuda", init_weight=w0)
+    c0 = c.material_chunk(0, 256).clone()
+    for i in range(200):
+        mc.nvfp4_apply_update(c, [(0, 256, o)], 1.0, step, seed=i, stochastic=False)
+    assert abs(float((c.material_chunk(0, 256) - c0).mean())) < 0.5 * 200 * step
+
+
+@pytest.mark.gpu
+def test_fused_update_kernel_follows_a_growing_weight():
+    from hippolm_b200.ops import muon_cuda as mc
+    torch.manual_seed(2)
+    lin = NVFP4Linear(512, 128, no_master=True, device="cuda")
+    w0 = lin.material_chunk(0, 128).clone()
+    gs0 = float(lin.global_scale)
+    # w <- w - lr * o with o = -3 w / lr: the weight becomes 4 w, beyond the range of the first tensor scale
+    o = (-3.0 * w0).bfloat16()
+    mc.nvfp4_apply_update(lin, [(0, 128, o)], 1.0, 1.0, seed=1, stochastic=False)
+    out = lin.material_chunk(0, 128)
+    assert float(lin.global_scale) > 3.5 * gs0
+    assert float(out.abs().max()) > 3.9 * float(w0.abs().max())
+    rel = float((out - 4 * w0).norm() / (4 * w0).norm())
+    assert rel < 0.15, rel
+    # and shrinking back by the same factor restores the resolution
+    o = (0.75 * out).bfloat16()
+    mc.nvfp4_apply_update(lin, [(0, 128, o)], 1.0, 1.0, seed=2, stochastic=False)
+    assert float(lin.global_scale) < 1.2 * gs0
+
+
+def test_loss_decreases_with_only_the_nvfp4_ffn_trainable():
+    """``configs/test/nvfp4.yml`` with every parameter frozen except the no-master FP4 feed-forward weights: the loss on
+    a fixed batch must still go down, i.e. the FP4 weights really move under Muon's small steps."""
+    import os
+    from hippolm_b200.cli import parse_args
+    from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
+    from hippolm_b200.data.loaders import synthetic_loader
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    a = parse_args(["--config", os.path.join(root, "configs/test/nvfp4.yml"), "--trainable_regex", r"ffn\.",
+                    "--max_steps", "1000", "--muon_lr", "0.02"])
+    loader = synthetic_loader(a.batch_size, a.seq_len, a.vocab_size, 0, 16, 64, fixed=True)
+    ctx = setup_worker(a, run_dir=None, data_iter=loader)
+    assert len(ctx.adamw.entries) == 0 and len(ctx.muon.entries) > 0
+    assert all(e.param is None for e in ctx.muon.entries)            # only no-master FP4 modules are optimised
+    batch = next(loader)
+    losses = []
+    for _ in range(30):
+        losses.append(float(train_step(ctx, batch)["loss"])); ctx.step += 1
+    teardown_worker(ctx)
+    assert losses[-1] < losses[0] - 0.05, losses

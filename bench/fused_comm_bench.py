@@ -38,7 +38,10 @@ def main():
     dev = init_distributed_from_env()
     w = dist.get_world_size()
     mesh = init_mesh(tp=w, device=dev)
-    T, D = 16384, 4096
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per call; 0 = 8192 per rank (the training micro-batch)")
+    T, D = ap.parse_args().tokens or 8192 * w, 4096
     assert fused.setup(mesh, T, D)
     ws = fused._STATE["ws"]
     pk = load_measured_peaks()

@@ -29,6 +29,9 @@ def main():
     ap.add_argument("--ffn", type=int, default=14336, help="e.g. 1792 = the local FFN width of one TP=8 rank")
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--micro", type=int, default=0, help="micro-batch tokens (default: one sequence)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree; > 1 runs under torch.distributed.run with "
+                    "that many ranks (full model dimensions, rank 0 prints)")
+    ap.add_argument("--no_fused_comm", action="store_true")
     ap.add_argument("--gemm_log", action="store_true", help="time every bf16 GEMM call of one extra step with CUDA events "
                     "and print time and TFLOP/s per (layout, M, N, K) (diagnosis only)")
     ap.add_argument("--kineto", action="store_true", help="after the timed steps, trace one more step with torch.profiler "
@@ -40,6 +43,10 @@ def main():
     args.attn_res_heads = 32
     args.ffn_nvfp4 = args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
     args.batch_size, args.seq_len, args.micro_batch_size, args.max_steps = a.seqs, a.seq_len, a.micro or a.seq_len, 10 ** 9
+    args.tp_size, args.dp_size, args.fused_comm = a.tp, 1, not a.no_fused_comm
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    if not rank0:
+        sys.stdout = open(os.devnull, "w")
     t0 = time.time()
     loader = synthetic_loader(args.batch_size, args.seq_len, args.vocab_size, 0, a.seq_len, a.seq_len)
     ctx = setup_worker(args, run_dir=None, data_iter=loader)

@@ -45,7 +45,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--full_attn_interval", type=int, default=4); a("--rope_theta", type=float, default=10000.0)
     a("--intermediate_size", type=int, default=1024); a("--rms_norm_eps", type=float, default=1e-6)
     a("--ffn_nvfp4", type=_bool, default=False); a("--ffn_nvfp4_marlin", type=_bool, default=False)
-    a("--ffn_nvfp4_no_bf16_master", type=_bool, default=False); a("--nvfp4_stochastic_rounding", type=_bool, default=True)
+    a("--ffn_nvfp4_no_bf16_master", type=_bool, default=False); a("--nvfp4_stochastic_rounding", type=_bool, default=True); a("--ffn_nvfp4_backward", type=str, default="bf16")
     a("--gradient_checkpointing", type=_bool, default=False); a("--lce_num_chunks", type=int, default=0)
     # training
     a("--batch_size", type=int, default=1); a("--seq_len", type=int, default=512)

@@ -199,6 +199,30 @@ __global__ void sumsq_kernel(const void* x, long long n, int is_bf16, float* out
   }
 }
 
+// Sum of squares of MANY tensors in one launch (the global gradient norm): one table entry per tensor segment,
+// out[slot] += sum x^2. Blocks walk (entry, 2048-element piece) pairs; one atomicAdd per piece.
+struct SumsqEntry { const void* ptr; long long n; int is_bf16; int slot; long long piece0; };
+__global__ void sumsq_multi_kernel(const SumsqEntry* __restrict__ tab, int n_entries, long long n_pieces, float* out) {
+  __shared__ float sh[32];
+  for (long long pc = blockIdx.x; pc < n_pieces; pc += gridDim.x) {
+    int lo = 0, hi = n_entries - 1;                       // last entry whose first piece is <= pc
+    while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (tab[mid].piece0 <= pc) lo = mid; else hi = mid - 1; }
+    const SumsqEntry e = tab[lo];
+    const long long i0 = (pc - e.piece0) * 2048;
+    float s = 0.f;
+    for (long long i = i0 + threadIdx.x; i < e.n && i < i0 + 2048; i += blockDim.x) { float v = ldf(e.ptr, i, e.is_bf16); s += v * v; }
+    s = wsum(s);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+      r = wsum(r);
+      if (threadIdx.x == 0) atomicAdd(out + e.slot, r);
+    }
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------------------------ NVFP4
 __global__ void absmax_kernel(const void* x, long long n, int is_bf16, float* out) {
   float m = 0.f;
@@ -353,6 +377,13 @@ extern "C" int hippo_adamw(void* p, const void* g, void* m, void* v, long long n
 extern "C" int hippo_sumsq(const void* x, long long n, int is_bf16, float* out, void* s) {
   unsigned grid = (unsigned)((n + 256 * 8 - 1) / (256 * 8)); if (grid > 1184) grid = 1184; if (grid == 0) grid = 1;
   sumsq_kernel<<<grid, 256, 0, ST(s)>>>(x, n, is_bf16, out);
+  RET();
+}
+// table: device array of n_entries SumsqEntry {ptr, n, is_bf16, slot, first piece index} (pieces of 2048 elements)
+extern "C" int hippo_sumsq_multi(const void* table, int n_entries, long long n_pieces, float* out, void* s) {
+  if (n_entries <= 0 || n_pieces <= 0) return 0;
+  unsigned grid = (unsigned)(n_pieces < 2368 ? n_pieces : 2368);
+  sumsq_multi_kernel<<<grid, 256, 0, ST(s)>>>((const SumsqEntry*)table, n_entries, n_pieces, out);
   RET();
 }
 // gs: device fp32[1]. compute_gs != 0: gs <- absmax(x)/(6*448) first (amax_scratch: device fp32[1])

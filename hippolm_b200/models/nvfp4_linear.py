@@ -75,6 +75,11 @@ class NVFP4Linear(nn.Module):
         self.act_quant = act_quant
         self.compute_dtype = dtype
         self.stochastic_rounding = True          # optimizer updates of the no-master weight round without bias
+        # backward on the FP4 tensor cores: dX = Q(dY) Q(W^T)^T needs W quantised along its OTHER axis (16-element blocks
+        # along out_features); that second encoding is derived from the stored one and cached until the weight changes
+        self.fp4_backward = False
+        self._w_version = 0
+        self._wt_cache = None                     # (version, packed_t [K, N/2], scales_t [K, N/16], gs_t [1])
         if init_weight is None:
             init_weight = torch.empty(out_features, in_features, device=device, dtype=torch.float32)
             nn.init.xavier_uniform_(init_weight)
@@ -115,6 +120,28 @@ class NVFP4Linear(nn.Module):
         else:
             self.grad_w.add_(dw)
 
+    def weight_changed(self) -> None:
+        """Every writer of the stored weight calls this (optimizer kernels, chunk commits, checkpoint loads)."""
+        self._w_version += 1
+
+    def transposed_operands(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """NVFP4 encoding of W^T ([in_features, out_features], blocks along out_features) for the dX product."""
+        c = self._wt_cache
+        ver = (self._w_version, 0 if self.no_master else self.weight._version)
+        if c is not None and c[0] == ver:
+            return c[1], c[2], c[3]
+        if self.no_master:
+            w = ops.nvfp4_dequantize(self.packed_weight, self.scales, self.global_scale, torch.bfloat16)
+        else:
+            w = self.weight.detach()
+        packed, scales, gs = ops.nvfp4_quantize(w.t().contiguous())
+        self._wt_cache = (ver, packed, scales, gs)
+        return packed, scales, gs
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self.weight_changed()
+
     # ------------------------------------------------------------------ chunk API (optimizer side)
     def chunk_ranges(self, rows: Optional[int] = None) -> Iterator[Tuple[int, int]]:
         rows = rows or self.CHUNK_ROWS
@@ -136,6 +163,7 @@ class NVFP4Linear(nn.Module):
             self.global_scale.copy_(torch.maximum(need, full.abs().max() / (6.0 * 448.0)).reshape(1))
             packed, scales, _ = ops.nvfp4_quantize(full, self.global_scale)
             self.packed_weight.copy_(packed); self.scales.copy_(scales)
+            self.weight_changed()
             if not stochastic:
                 return
         if stochastic:
@@ -147,6 +175,7 @@ class NVFP4Linear(nn.Module):
             packed, scales, _ = ops.nvfp4_quantize(w, self.global_scale)
         self.packed_weight[r0:r1].copy_(packed)
         self.scales[r0:r1].copy_(scales)
+        self.weight_changed()
 
     def apply_chunk_update(self, r0: int, r1: int, update: torch.Tensor, lr: float) -> None:
         self.decay_and_apply_chunk(r0, r1, update, lr, 1.0)
@@ -165,6 +194,7 @@ class NVFP4Linear(nn.Module):
         """Full re-quantisation; also refreshes the tensor-level scale."""
         packed, scales, gs = ops.nvfp4_quantize(w.float())
         self.packed_weight.copy_(packed); self.scales.copy_(scales); self.global_scale.copy_(gs)
+        self.weight_changed()
 
     def refresh_global_scale(self, headroom: float = 1.0) -> None:
         """Re-derive global_scale from the current contents (keeps e4m3 scales in range as W grows)."""

@@ -107,3 +107,4 @@ def nvfp4_apply_update(mod, segments, wd_factor: float, lr: float, seed: int, st
                                              1 if stochastic else 0, stream_ptr()), "nvfp4_apply_update")
     if whole:
         gs.copy_(gs_new)
+    mod.weight_changed()

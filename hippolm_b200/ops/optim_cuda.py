@@ -35,3 +35,22 @@ def sumsq_into(x: torch.Tensor, out: torch.Tensor) -> None:
     """out[0] += sum(x^2) (fp32 accumulate)."""
     x = x.contiguous()
     check(lib().hippo_sumsq(ptr(x), _c.c_longlong(x.numel()), _isbf(x), ptr(out), stream_ptr()), "sumsq")
+
+
+def sumsq_multi(items, out: torch.Tensor) -> None:
+    """items: [(tensor, slot)]; out[slot] += sum(tensor^2) for all of them in ONE launch (table of pointers uploaded
+    from a small pinned buffer). Tensors must be contiguous bf16 / fp32."""
+    import struct
+    items = [(t, sl) for t, sl in items if t.numel() > 0]
+    if not items:
+        return
+    rec, piece = [], 0
+    for t, slot in items:
+        assert t.is_contiguous()
+        rec.append(struct.pack("<QqiiQ", t.data_ptr(), t.numel(), _isbf(t), slot, piece))
+        piece += (t.numel() + 2047) // 2048
+    raw = b"".join(rec)
+    host = torch.frombuffer(bytearray(raw), dtype=torch.uint8).pin_memory()
+    tab = host.to(out.device, non_blocking=True)
+    check(lib().hippo_sumsq_multi(ptr(tab), len(items), _c.c_longlong(piece), ptr(out), stream_ptr()), "sumsq_multi")
+    tab.record_stream(torch.cuda.current_stream())

@@ -154,12 +154,21 @@ class Muon:
             if b <= a:
                 continue
             if not mc.supported(b - a, cols):
-                # tiny / ragged segment (e.g. H/tp beta rows): generic path on this slice only
+                # tiny / ragged segment (e.g. the H/tp rows of the beta projection): elementwise momentum on the slice,
+                # then Newton-Schulz on the tcgen05 path after padding with zero rows (zero rows stay zero through every
+                # iteration and do not touch the others, so the real rows get exactly their own result)
                 gf = g[a:b].float() * grad_scale
                 m = e.exp_avg[a:b].float().mul_(self.momentum).add_(gf)
                 e.exp_avg[a:b].copy_(m)
                 u = gf.add(m, alpha=self.momentum) if self.nesterov else m
-                self._apply(e, a, b, ops.newton_schulz5(u, self.ns_steps), wd_factor)
+                if cols % 8 == 0 and e.param is not None:
+                    rp = (b - a + 7) // 8 * 8
+                    up = torch.zeros((rp, cols), dtype=torch.bfloat16, device=u.device)
+                    up[:b - a] = u
+                    ssq = up.float().pow(2).sum().reshape(1)
+                    self._apply(e, a, b, mc.newton_schulz_(up, ssq, self.ns_steps)[:b - a], wd_factor)
+                else:
+                    self._apply(e, a, b, ops.newton_schulz5(u, self.ns_steps), wd_factor)
                 continue
             u, ssq = mc.momentum_update(g[a:b], e.exp_avg[a:b], self.momentum, grad_scale, self.nesterov)
             o = mc.newton_schulz_(u, ssq, self.ns_steps)
@@ -438,11 +447,7 @@ def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None, owner_reduced: bool = 
     if dev is None:
         return torch.zeros(())
     acc = torch.zeros(2, dtype=torch.float32, device=dev)      # [sharded, replicated]
-    if dev.type == "cuda":
-        from ..ops.optim_cuda import sumsq_into
-    else:
-        def sumsq_into(x, out):
-            out += x.float().pow(2).sum()
+    items = []                                                 # (gradient segment, slot)
     n_muon = len(muon.entries)
     for idx, e in enumerate(list(muon.entries) + list(adamw.entries)):
         g = e.grad()
@@ -453,12 +458,18 @@ def global_grad_norm(muon: Muon, adamw: AdamW, mesh=None, owner_reduced: bool = 
         rows = getattr(e.param, "tp_replicated_rows", None) if e.param is not None else None
         is_repl = e.param is not None and getattr(e.param, "tp_replicated", False)
         if is_repl:
-            sumsq_into(g, acc[1:2])
+            items.append((g, 1))
         elif rows is not None:
             a, b = rows
-            sumsq_into(g[:a], acc[0:1]); sumsq_into(g[a:b], acc[1:2]); sumsq_into(g[b:], acc[0:1])
+            items += [(g[:a], 0), (g[a:b], 1), (g[b:], 0)]
         else:
-            sumsq_into(g, acc[0:1])
+            items.append((g, 0))
+    if dev.type == "cuda" and all(t.is_contiguous() and t.dtype in (torch.bfloat16, torch.float32) for t, _ in items):
+        from ..ops.optim_cuda import sumsq_multi
+        sumsq_multi(items, acc)                                # one launch for the whole model
+    else:
+        for t, slot in items:
+            acc[slot] += t.float().pow(2).sum()
     if owner_reduced:
         dist.all_reduce(acc, group=m.dp_group)
     sharded, repl = acc[0], acc[1]

@@ -105,6 +105,13 @@ class _RowLinearSP(torch.autograd.Function):
         return dx, dw.to(weight.dtype)
 
 
+def _fp4_backward(module, dy: torch.Tensor, contraction: int, out: int) -> bool:
+    """dX of an NVFP4 linear on the FP4 tensor cores? Needs the option, a CUDA bf16 gradient and shapes the block-scaled
+    GEMM covers (contraction a multiple of 256, output a multiple of 8)."""
+    return (bool(getattr(module, "fp4_backward", False)) and dy.is_cuda and dy.dtype == torch.bfloat16
+            and contraction % 256 == 0 and out % 8 == 0)
+
+
 def _nvfp4_operands(module, weight):
     """(packed, scales, global_scale) of an NVFP4Linear: its buffers (no master) or the freshly quantised master."""
     if module.no_master:
@@ -144,12 +151,24 @@ class _NVFP4ColumnSP(torch.autograd.Function):
         x, packed, scales, gs = ctx.saved_tensors
         mod, m = ctx.module, get_mesh()
         dy = dy.contiguous()
-        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)               # [N/w, K]
         f = _fused()
+        dx = None
+        if _fp4_backward(mod, dy, contraction=dy.shape[1], out=ctx.K):
+            # dX = Q(dY) Q(W^T)^T on the FP4 tensor cores (W^T re-encoded along N once per optimizer step)
+            pt, st, gt = mod.transposed_operands()
+            if m.tp == 1:
+                dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True)
+            elif f is not None:
+                dx = f.nvfp4_gemm_reduce_scatter(dy, pt, st, gt)              # None: shape not covered
+        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype) if dx is None else None   # [N/w, K]
         if m.tp == 1:
-            dx, xg = ops.gemm_nn(dy, w), x
+            if dx is None:
+                dx = ops.gemm_nn(dy, w)
+            xg = x
         else:
-            if f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
+            if dx is not None:
+                pass
+            elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
                     and f.fits(dy.shape[0] // m.tp, dy.shape[0], w.shape[1]) and dy.shape[1] % 8 == 0:
                 dx = f.gemm_reduce_scatter(dy, w, transpose_w=True)
             else:
@@ -192,16 +211,32 @@ class _NVFP4RowSP(torch.autograd.Function):
         x, packed, scales, gs = ctx.saved_tensors
         mod, m = ctx.module, get_mesh()
         dy = dy.contiguous()
-        w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)               # [N, K/w]
         f = _fused()
-        if m.tp == 1:
-            dyg, dx = dy, ops.gemm_nn(dy, w)
-        elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
-                and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and w.shape[1] % 8 == 0:
-            dyg, dx = f.allgather_gemm(dy, w, transpose_w=True)
-        else:
-            dyg = all_gather_dim0(dy, m.tp_group, m.tp)
-            dx = ops.gemm_nn(dyg, w)
+        if m.tp == 1 and _fp4_backward(mod, dy, contraction=dy.shape[1], out=x.shape[1]):
+            pt, st, gt = mod.transposed_operands()
+            dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True)             # Q(dY) Q(W^T)^T
+            if mod.no_master:
+                mod.accumulate_grad_product(dy, x)
+                return dx, None, None
+            return dx, ops.gemm_tn(dy, x).to(mod.weight.dtype), None
+        dx = dyg = None
+        if m.tp > 1 and f is not None and _fp4_backward(mod, dy, contraction=dy.shape[1], out=x.shape[1]):
+            # the gradient shard is quantised and pushed as FP4 (0.5625 bytes per element on the wire), the dX GEMM runs
+            # on the FP4 tensor cores, and the gathered Q(dY) is dequantised once for the dW product
+            pt, st, gt = mod.transposed_operands()
+            dx, kept = f.nvfp4_allgather_gemm(dy, pt, st, gt, keep_gathered=True)
+            if dx is not None:
+                dyg = f.nvfp4_dequant_gathered(kept, dy.shape[0] * m.tp, dy.shape[1])
+        if dx is None:
+            w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype)           # [N, K/w]
+            if m.tp == 1:
+                dyg, dx = dy, ops.gemm_nn(dy, w)
+            elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
+                    and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and w.shape[1] % 8 == 0:
+                dyg, dx = f.allgather_gemm(dy, w, transpose_w=True)
+            else:
+                dyg = all_gather_dim0(dy, m.tp_group, m.tp)
+                dx = ops.gemm_nn(dyg, w)
         if mod.no_master:
             mod.accumulate_grad_product(dyg, x)
             return dx, None, None

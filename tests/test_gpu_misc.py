@@ -105,18 +105,40 @@ def test_muon_fused_device_path_matches_reference():
 
 
 def test_nvfp4_fused_apply_update():
-    from hippolm_b200 import ops
+    """Fused dequantise -> update -> re-quantise of a no-master weight (round-to-nearest mode): the stored result is
+    the updated tensor up to one FP4 rounding, with the tensor scale following the new absmax."""
+    from hippolm_b200.models.nvfp4_linear import NVFP4Linear
     from hippolm_b200.ops import muon_cuda as mc
     torch.manual_seed(0)
     w = torch.randn(128, 256, device="cuda") * 0.05
-    p, s, gs = ops.nvfp4_quantize(w)
+    lin = NVFP4Linear(256, 128, no_master=True, device="cuda", init_weight=w)
     o = torch.randn(128, 256, device="cuda").bfloat16()
-    w0 = ops.nvfp4_dequantize(p, s, gs)
-    mc.nvfp4_apply_update(p, s, gs, o, 0.99, 0.01)
-    w1 = ops.nvfp4_dequantize(p, s, gs)
+    w0 = lin.material_chunk(0, 128)
+    mc.nvfp4_apply_update(lin, [(0, 64, o[:64]), (64, 128, o[64:])], 0.99, 0.01, seed=3, stochastic=False)
+    w1 = lin.material_chunk(0, 128)
     target = w0 * 0.99 - 0.01 * o.float()
-    p2, s2, _ = ops.nvfp4_quantize(target, gs)
-    assert torch.equal(ops.nvfp4_dequantize(p2, s2, gs), w1)
+    assert float((w1 - target).norm() / target.norm()) < 0.12
+    assert abs(float(lin.global_scale) - float(target.abs().max()) / (6 * 448)) < 1e-3 * float(lin.global_scale)
+    assert float(w1.abs().max()) >= 0.99 * float(target.abs().max())
+
+
+def test_muon_ragged_segment_stays_on_the_device_kernels():
+    """A segment whose row count is not a multiple of 8 (the H/tp rows of the beta projection) is padded with zero rows
+    and orthogonalised by the tcgen05 Newton-Schulz path; the result equals the fp32 oracle on the real rows."""
+    import torch.nn as nn
+    from hippolm_b200.optim.optimizers import Muon
+    from hippolm_b200.ref.ops import newton_schulz5
+    torch.manual_seed(1)
+    p = nn.Parameter(torch.randn(4, 512, device="cuda").bfloat16())
+    g = (0.1 * torch.randn(4, 512, device="cuda")).bfloat16()
+    p.grad = g.clone()
+    opt = Muon(lr=0.1, momentum=0.9, weight_decay=0.0, momentum_dtype=torch.bfloat16)
+    opt.add_param(p, "b_proj")
+    w0 = p.detach().float().clone()
+    opt.step(grad_scale=1.0)
+    u = g.float() + 0.9 * g.float()
+    ref = w0 - 0.1 * newton_schulz5(u, 5)
+    assert (p.detach().float() - ref).abs().max() < 0.03
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 256), (300, 264, 768), (1024, 512, 2048)])
@@ -136,3 +158,19 @@ def test_nvfp4_tensor_core_gemm(M, N, K):
     assert _rel(y2, ref) < 1e-2
     torch.cuda.synchronize()
     assert _ext.device_status()[0] == 0
+
+
+def test_sumsq_multi_one_launch():
+    """The global gradient norm sums every tensor in one launch: mixed dtypes, ragged sizes, two output slots."""
+    from hippolm_b200.ops import optim_cuda, _ext
+    torch.manual_seed(0)
+    ts = [torch.randn(n, device="cuda").to(dt) for n, dt in ((5, torch.float32), (2048, torch.bfloat16),
+                                                             (2049, torch.bfloat16), (100003, torch.float32),
+                                                             (4096 * 33, torch.bfloat16))]
+    items = [(t, i % 2) for i, t in enumerate(ts)]
+    out = torch.zeros(2, device="cuda")
+    n0 = _ext.launch_count()
+    optim_cuda.sumsq_multi(items, out)
+    assert _ext.launch_count() == n0 + 1
+    ref = [sum(float(t.float().pow(2).sum()) for t, s in items if s == k) for k in (0, 1)]
+    assert abs(float(out[0]) - ref[0]) < 1e-3 * ref[0] and abs(float(out[1]) - ref[1]) < 1e-3 * ref[1]

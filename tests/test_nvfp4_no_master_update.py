@@ -129,3 +129,43 @@ def test_loss_decreases_with_only_the_nvfp4_ffn_trainable():
         losses.append(float(train_step(ctx, batch)["loss"])); ctx.step += 1
     teardown_worker(ctx)
     assert losses[-1] < losses[0] - 0.05, losses
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("no_master", [True, False])
+def test_fp4_backward_dx_matches_dequantised_oracle(no_master):
+    """``ffn_nvfp4_backward: fp4``: dX = Q(dY) Q(W^T)^T on the FP4 tensor cores against dY dq(W) in fp32 (cosine >= 0.99),
+    dW unchanged, and the cached transposed encoding follows the weight through an optimizer update."""
+    from hippolm_b200.parallel.linear import nvfp4_column_linear_sp, nvfp4_row_linear_sp
+    from hippolm_b200.ops import muon_cuda as mc
+    from hippolm_b200 import ops
+    torch.manual_seed(0)
+    T, K, N = 512, 1024, 768
+    for fn in (nvfp4_column_linear_sp, nvfp4_row_linear_sp):
+        lin = NVFP4Linear(K, N, no_master=no_master, device="cuda", dtype=torch.bfloat16)
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        dy = torch.randn(T, N, device="cuda").bfloat16()
+        grads = {}
+        for mode in (False, True):
+            lin.fp4_backward = mode
+            lin.grad_w = None if no_master else None
+            if not no_master:
+                lin.weight.grad = None
+            xi = x.clone().requires_grad_(True)
+            fn(xi, lin).backward(dy)
+            grads[mode] = (xi.grad.float(), (lin.grad_w if no_master else lin.weight.grad).float().clone())
+        if no_master:
+            wdq = ops.nvfp4_dequantize(lin.packed_weight, lin.scales, lin.global_scale, torch.float32)
+        else:
+            wdq = ops.nvfp4_dequantize(*ops.nvfp4_quantize(lin.weight.detach()), dtype=torch.float32)
+        ref = dy.float() @ wdq
+        cos = lambda a, b: float((a * b).sum() / (a.norm() * b.norm()))
+        assert cos(grads[False][0], ref) > 0.999
+        assert cos(grads[True][0], ref) > 0.99, cos(grads[True][0], ref)
+        assert abs(float(grads[True][0].norm() / ref.norm()) - 1.0) < 0.05
+        assert torch.equal(grads[True][1], grads[False][1])                     # dW is not touched by the option
+    if no_master:
+        p0 = lin.transposed_operands()[0].clone()
+        o = torch.randn(N, K, device="cuda").bfloat16()
+        mc.nvfp4_apply_update(lin, [(0, N, o)], 1.0, 0.05, seed=1)
+        assert not torch.equal(lin.transposed_operands()[0], p0)                # cache invalidated by the update

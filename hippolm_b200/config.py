@@ -63,7 +63,8 @@ class HippoConfig:
     ffn_nvfp4: bool = False
     ffn_nvfp4_marlin: bool = False          # accepted for config compatibility; FP4 tensor cores are always used
     # backward of the NVFP4 FFN: "bf16" = dX and dW as bf16 GEMMs on the dequantised weight (the reference's choice,
-    # ``src/models/ops/nvfp4_marlin.py:1036-1077``); "fp4" = dX = Q(dY) Q(W^T)^T on the FP4 tensor cores
+    # ``src/models/ops/nvfp4_marlin.py:1036-1077``); "fp4_dx" = dX = Q(dY) Q(W^T)^T on the FP4 tensor cores, dW in bf16;
+    # "fp4" = dX as above and dW = Q(dY^T) Q(x^T)^T with both operands re-quantised along the token axis
     ffn_nvfp4_backward: str = "bf16"
     ffn_nvfp4_no_bf16_master: bool = False
     # memory policy
@@ -85,8 +86,8 @@ class HippoConfig:
         if self.pack_chunk_size <= 0:
             self.pack_chunk_size = self.head_dim
         self.pack_chunk_size = ((self.pack_chunk_size + 63) // 64) * 64
-        if self.ffn_nvfp4_backward not in ("bf16", "fp4"):
-            raise ValueError(f"ffn_nvfp4_backward must be bf16|fp4, got {self.ffn_nvfp4_backward!r}")
+        if self.ffn_nvfp4_backward not in ("bf16", "fp4_dx", "fp4"):
+            raise ValueError(f"ffn_nvfp4_backward must be bf16|fp4_dx|fp4, got {self.ffn_nvfp4_backward!r}")
         if self.ffn_nvfp4_no_bf16_master and not self.ffn_nvfp4:
             raise ValueError("ffn_nvfp4_no_bf16_master requires ffn_nvfp4")
         if self.hidden_size % self.num_heads != 0:

@@ -123,42 +123,71 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   };
 
   if (COMM == COMM_AG && (int)blockIdx.x < cp.comm_ctas) {
-    // ---- copy role: the shard travels in 128-row blocks; each block goes to every rank (own first, then rank+1,
-    // ...) and bumps that rank's counter for (this source, this block), so consumers can start on the first
-    // blocks of a remote shard while the rest is still in flight.
-    const long long row_bytes = (long long)p.K * 2;
-    const long long vec_per_row = row_bytes / 16;
-    const int bps = cp.rows_per_shard / BM;                  // blocks per shard
-    const long long nvec = (long long)BM * vec_per_row;      // vectors per block
-    // remote pushes only: own tiles read x_local in place (tmOwn); a caller that needs the complete gathered
-    // buffer afterwards copies its own rows in with a plain device copy
-    for (int pass = 0; pass < 1; ++pass) {
-      for (int rb = blockIdx.x; rb < bps; rb += cp.comm_ctas) {
-        const uint8_t* src = (const uint8_t*)cp.x_local + (long long)rb * BM * cp.x_ld * 2;
-        for (int i = (pass == 0 ? 1 : 0); i < (pass == 0 ? cp.world : 1); ++i) {
-          const int peer = (cp.rank + i) % cp.world;
-          uint4* dst = (uint4*)((uint8_t*)cp.buf_peer[peer] + ((long long)cp.rank * cp.rows_per_shard + (long long)rb * BM) * row_bytes);
-          // 8 independent 16-byte loads in flight per thread before the stores (memory-level parallelism)
-          for (long long v0 = threadIdx.x; v0 < nvec; v0 += (long long)GEMM_THREADS * 8) {
-            uint4 tmp[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const long long v = v0 + (long long)j * GEMM_THREADS;
-              if (v < nvec) { const long long r = v / vec_per_row, c = v % vec_per_row; tmp[j] = __ldg((const uint4*)(src + r * cp.x_ld * 2) + c); }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const long long v = v0 + (long long)j * GEMM_THREADS;
-              if (v < nvec) dst[v] = tmp[j];
-            }
-          }
-          if (pass == 0) {
-            __threadfence_system();
-            __syncthreads();
-            if (threadIdx.x == 0) red_release_sys_add(cp.flag_peer[peer] + cp.rank * bps + rb, 1u);
-          }
+    // ---- copy role, driven by ONE thread with bulk async copies (TMA): a chunk of the local shard is read into shared
+    // memory once and stored from there into the gathered buffer of every peer (7 stores per local read at 8 ranks),
+    // through a ring of 4 buffers with the loads two chunks ahead of the stores. The shard travels in 128-row blocks;
+    // once every store of a block has completed, the block's arrival counter is released on each peer, so consumers
+    // start on the first blocks of a remote shard while the rest is still in flight. Own tiles read x_local in place
+    // (tmOwn); a caller that needs the complete gathered buffer afterwards copies its own rows in with a device copy.
+    if (threadIdx.x == 0) {
+      const long long row_bytes = (long long)p.K * 2;
+      const int bps = cp.rows_per_shard / BM;                           // 128-row blocks per shard
+      int rpc = (int)(STAGE_BYTES / row_bytes);                         // rows per chunk (one ring buffer)
+      if (rpc > BM) rpc = BM;
+      const int cpb = (BM + rpc - 1) / rpc;                             // chunks per block
+      const int my_blocks = (bps - (int)blockIdx.x + cp.comm_ctas - 1) / cp.comm_ctas;
+      const int total = my_blocks > 0 ? my_blocks * cpb : 0;
+      const bool contiguous = cp.x_ld == (long long)p.K;
+      auto chunk_rows = [&](int c, int& rb, int& r0) {                  // chunk -> (row block, first row in block) -> rows
+        rb = (int)blockIdx.x + (c / cpb) * cp.comm_ctas;
+        r0 = (c % cpb) * rpc;
+        return min(rpc, BM - r0);
+      };
+      auto load = [&](int c) {
+        int rb, r0; const int nr = chunk_rows(c, rb, r0);
+        uint8_t* buf = smem + (c & 3) * STAGE_BYTES;
+        const uint8_t* src = (const uint8_t*)cp.x_local + ((long long)rb * BM + r0) * cp.x_ld * 2;
+        mbar_expect_tx(&full[c & 3], (uint32_t)(nr * row_bytes));
+        if (contiguous) {
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(buf)), "l"(src), "r"((uint32_t)(nr * row_bytes)), "r"(smem_u32(&full[c & 3])) : "memory");
+        } else {
+          for (int r = 0; r < nr; ++r)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(buf + r * row_bytes)), "l"(src + (long long)r * cp.x_ld * 2), "r"((uint32_t)row_bytes),
+                           "r"(smem_u32(&full[c & 3])) : "memory");
         }
+      };
+      auto release_block = [&](int rb) {
+        for (int i = 1; i < cp.world; ++i) {
+          const int peer = (cp.rank + i) % cp.world;
+          red_release_sys_add(cp.flag_peer[peer] + cp.rank * bps + rb, 1u);
+        }
+      };
+      bool ok = row_bytes <= STAGE_BYTES && (row_bytes % 16) == 0;
+      if (!ok) report(kBadArgument, (int)p.K);
+      if (ok && total > 0) { load(0); if (total > 1) load(1); }
+      int released = 0;                                                 // chunks whose blocks have been released so far
+      for (int c = 0; ok && c < total; ++c) {
+        // stores of chunks <= c - 2 are complete (wait at the end of the previous iteration): their buffers are free
+        if (c + 2 < total) load(c + 2);
+        ok = mbar_wait(&full[c & 3], (c >> 2) & 1, kWaitTmaFull, c);
+        if (!ok) break;
+        int rb, r0; const int nr = chunk_rows(c, rb, r0);
+        const uint8_t* buf = smem + (c & 3) * STAGE_BYTES;
+        const long long off = ((long long)cp.rank * cp.rows_per_shard + (long long)rb * BM + r0) * row_bytes;
+        for (int i = 1; i < cp.world; ++i) {
+          const int peer = (cp.rank + i) % cp.world;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"((uint8_t*)cp.buf_peer[peer] + off), "r"(smem_u32(buf)), "r"((uint32_t)(nr * row_bytes)) : "memory");
+        }
+        tma_store_commit();
+        tma_store_wait<1>();                                            // everything but the newest group has completed
+        // chunks 0 .. c-1 are complete: release every block that ends inside them
+        while (released + cpb <= c) { release_block((int)blockIdx.x + (released / cpb) * cp.comm_ctas); released += cpb; }
       }
+      tma_store_wait<0>();
+      if (ok) while (released < total) { release_block((int)blockIdx.x + (released / cpb) * cp.comm_ctas); released += cpb; }
     }
   } else
 

@@ -35,6 +35,7 @@ struct Fp4Params {
   const uint8_t* sfb;            // tiled scales of B: [ceil(N/128)][K/64][512]
   const float* gsa; const float* gsb;   // F_COMM_AG: gsa points at one tensor scale per source rank
   __nv_bfloat16* C; long long ldc;
+  int accumulate;                // plain mode: C += result (the weight-gradient product adds into the accumulator)
   int tiles_m, tiles_n;
   // F_COMM_AG: A (packed bytes, scale tiles, per-source tensor scales) is this rank's gathered FP4 buffer, filled
   // shard by shard by every rank's nvfp4_quant_push_kernel; `flags[src * (rows_per_shard/128) + row block]`
@@ -251,19 +252,32 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (row < p.M && col0 < p.N) {
           __nv_bfloat16* crow = p.C + (long long)row * p.ldc + col0;
           if (col0 + 32 <= p.N) {
+            uint4 old[4];
+            if (p.accumulate) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) old[j] = *(const uint4*)(crow + 8 * j);   // four loads in flight
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 v;
               __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+              const __nv_bfloat162* ob = (const __nv_bfloat162*)&old[j / 8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * alpha, __uint_as_float(r[j + 2 * e + 1]) * alpha);
+              for (int e = 0; e < 4; ++e) {
+                float lo = __uint_as_float(r[j + 2 * e]) * alpha, hi = __uint_as_float(r[j + 2 * e + 1]) * alpha;
+                if (p.accumulate) { const float2 o2 = __bfloat1622float2(ob[e]); lo += o2.x; hi += o2.y; }
+                vb[e] = __floats2bfloat162_rn(lo, hi);
+              }
               *(uint4*)(crow + j) = v;
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) crow[j] = __float2bfloat16(__uint_as_float(r[j]) * alpha);
+              if (col0 + j < p.N) {
+                float v = __uint_as_float(r[j]) * alpha;
+                if (p.accumulate) v += __bfloat162float(crow[j]);
+                crow[j] = __float2bfloat16(v);
+              }
           }
         }
       }
@@ -390,6 +404,60 @@ nvfp4_quant_push_kernel(const __grid_constant__ QuantPushParams q) {
   }
 }
 
+// Transposed NVFP4 quantisation for the weight-gradient product dW = dY^T x, whose contraction runs over TOKENS:
+// x[T, C] (bf16, row pitch ldx) -> packed [C, T/2] (16-element blocks along T), block scales written straight into the
+// 512-byte MMA tile layout [ceil(C/128)][T/64][512] (no separate re-tiling pass). One CTA transposes a 256-token x
+// 64-channel tile through shared memory: coalesced 128-byte row reads, then thread (channel, 64-token group) quantises
+// four 16-token blocks and writes 32 contiguous packed bytes and 4 contiguous scale bytes.
+__global__ void __launch_bounds__(256)
+nvfp4_quant_transposed_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, long long T, int C, const float* gs_ptr,
+                              uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiled) {
+  __shared__ __nv_bfloat16 tile[256][66];
+  const long long t0 = (long long)blockIdx.x * 256;
+  const int c0 = blockIdx.y * 64;
+  const int tid = threadIdx.x;
+  // 256 rows x 64 channels = 2048 16-byte vectors; rows beyond T or channels beyond C read as zero
+  for (int v = tid; v < 2048; v += 256) {
+    const int r = v >> 3, cv = (v & 7) * 8;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (t0 + r < T && c0 + cv < C) val = __ldg((const uint4*)(x + (t0 + r) * ldx + c0 + cv));
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&val;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) *(__nv_bfloat162*)&tile[r][cv + 2 * e] = h[e];
+  }
+  __syncthreads();
+  const int c = tid & 63, q = tid >> 6;                      // channel, group of four 16-token blocks
+  if (c0 + c >= C) return;
+  const float gs = *gs_ptr;
+  const long long kg0 = t0 / 16 + q * 4;                     // first k-group (16-token block) of this thread
+  uint4 outv[2];
+  uint8_t* ob = (uint8_t*)outv;
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    float f[16], bm = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) { f[e] = __bfloat162float(tile[q * 64 + b * 16 + e][c]); bm = fmaxf(bm, fabsf(f[e])); }
+    const float sraw = fminf(bm / 6.f / gs, 448.f);
+    const __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+    const float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float lo = sdec > 0.f ? f[2 * e] / sdec : f[2 * e], hi = sdec > 0.f ? f[2 * e + 1] / sdec : f[2 * e + 1];
+      ob[b * 8 + e] = (uint8_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+    }
+    sfw |= (uint32_t)s8 << (8 * b);
+  }
+  const long long tq = t0 + q * 64;
+  if (tq < T) {                                              // T is a multiple of 64 (checked by the launcher)
+    const int m = c0 + c;
+    uint4* dst = (uint4*)(packed + (long long)m * (T / 2) + tq / 2);
+    dst[0] = outv[0]; dst[1] = outv[1];
+    const long long tile_idx = (long long)(m / 128) * (T / 64) + kg0 / 4;
+    *(uint32_t*)(sf_tiled + tile_idx * 512 + (m % 32) * 16 + ((m % 128) / 32) * 4) = sfw;
+  }
+}
+
 // logical e4m3 scales [rows, K/16] -> 512-byte tiles [ceil(rows/128)][K/64][(m%32)*16 + ((m%128)/32)*4 + kg]
 __global__ void nvfp4_tile_scales_kernel(const uint8_t* __restrict__ sf, uint8_t* __restrict__ out, long long rows,
                                          int kgroups /* K/16 */, long long rows_padded) {
@@ -405,6 +473,8 @@ __global__ void nvfp4_tile_scales_kernel(const uint8_t* __restrict__ sf, uint8_t
 }  // namespace hippo
 
 using namespace hippo;
+
+static thread_local int g_fp4_accumulate = 0;   // set by hippo_gemm_nvfp4_accumulate for the next plain launch
 
 extern "C" int hippo_nvfp4_tile_scales(const void* sf, void* out, long long rows, long long K, void* stream) {
   if (K % 64) return -1;
@@ -427,7 +497,7 @@ extern "C" int hippo_gemm_nvfp4(const void* A, const void* B, const void* sfa, c
   if (rc) return rc;
   Fp4Params p;
   p.M = M; p.N = N; p.K = K; p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.gsa = gsa; p.gsb = gsb;
-  p.C = (__nv_bfloat16*)C; p.ldc = ldc;
+  p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.accumulate = g_fp4_accumulate; g_fp4_accumulate = 0;
   p.tiles_m = (M + F_BM - 1) / F_BM; p.tiles_n = (N + F_BN - 1) / F_BN;
   int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
   int grid = tiles < sms ? tiles : sms;
@@ -438,6 +508,25 @@ extern "C" int hippo_gemm_nvfp4(const void* A, const void* B, const void* sfa, c
     attr_set = true;
   }
   gemm_nvfp4_kernel<F_COMM_NONE><<<grid, F_THREADS, F_SMEM, (cudaStream_t)stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+// Same product, added into C (bf16): C += (A sfa)(B sfb)^T gsa gsb.
+extern "C" int hippo_gemm_nvfp4_accumulate(const void* A, const void* B, const void* sfa, const void* sfb, const float* gsa,
+                                           const float* gsb, void* C, int M, int N, int K, long long ldc, void* stream) {
+  g_fp4_accumulate = 1;
+  return hippo_gemm_nvfp4(A, B, sfa, sfb, gsa, gsb, C, M, N, K, ldc, stream);
+}
+
+// x[T, C] bf16 -> NVFP4 of x^T: packed [C, T/2], scales in MMA tile layout [ceil(C/128)][T/64][512] (zero-filled by the
+// caller when C is not a multiple of 128), against the tensor scale *gs. T must be a multiple of 64, C of 8.
+extern "C" int hippo_nvfp4_quantize_transposed(const void* x, long long ldx, long long T, int C, const float* gs,
+                                               void* packed, void* sf_tiled, void* stream) {
+  if (T <= 0 || C <= 0) return 0;
+  if ((T % 64) || (C % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)packed & 15)) return -2;
+  dim3 grid((unsigned)((T + 255) / 256), (unsigned)((C + 63) / 64));
+  nvfp4_quant_transposed_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, T, C, gs,
+                                                                       (uint8_t*)packed, (uint8_t*)sf_tiled);
   return (int)cudaGetLastError();
 }
 

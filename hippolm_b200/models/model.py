@@ -281,7 +281,8 @@ class SwiGLU(nn.Module):
             self.gate_up_proj = NVFP4Linear(D, 2 * I // w, nm, device, dtype, init_weight=torch.cat([gate, up], 0))
             self.down_proj = NVFP4Linear(I // w, D, nm, device, dtype, init_weight=down)
             self.gate_up_proj.tp_shard_dim, self.down_proj.tp_shard_dim = 0, 1
-            self.gate_up_proj.fp4_backward = self.down_proj.fp4_backward = cfg.ffn_nvfp4_backward == "fp4"
+            self.gate_up_proj.fp4_backward = self.down_proj.fp4_backward = cfg.ffn_nvfp4_backward in ("fp4", "fp4_dx")
+            self.gate_up_proj.fp4_backward_dw = self.down_proj.fp4_backward_dw = cfg.ffn_nvfp4_backward == "fp4"
             if not nm:
                 self.gate_up_proj.weight.tp_shard_dim, self.down_proj.weight.tp_shard_dim = 0, 1
         else:

@@ -78,6 +78,7 @@ class NVFP4Linear(nn.Module):
         # backward on the FP4 tensor cores: dX = Q(dY) Q(W^T)^T needs W quantised along its OTHER axis (16-element blocks
         # along out_features); that second encoding is derived from the stored one and cached until the weight changes
         self.fp4_backward = False
+        self.fp4_backward_dw = False              # with fp4_backward: also dW = Q(dY^T) Q(x^T)^T on the FP4 tensor cores
         self._w_version = 0
         self._wt_cache = None                     # (version, packed_t [K, N/2], scales_t [K, N/16], gs_t [1])
         if init_weight is None:
@@ -106,7 +107,18 @@ class NVFP4Linear(nn.Module):
     def accumulate_grad_product(self, dy: torch.Tensor, x: torch.Tensor) -> None:
         """grad_w += dy^T x. Once the accumulator exists the GEMM epilogue adds into it directly (no dW temporary,
         no separate add pass); the first micro-batch and the host-offload sink take the materialised product."""
-        if self.grad_sink is None and self.grad_w is not None and dy.is_cuda and self.grad_w.dtype == torch.bfloat16 \
+        if self.fp4_backward and self.fp4_backward_dw and self.grad_sink is None and dy.is_cuda \
+                and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and dy.shape[0] % 256 == 0 \
+                and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0 and dy.stride(1) == 1 and x.stride(1) == 1:
+            # dW += Q(dY^T) Q(x^T)^T on the FP4 tensor cores: both operands re-quantised with their blocks along the tokens
+            from ..ops import nvfp4_cuda, fp4_gemm
+            ap, asf, ags = nvfp4_cuda.quantize_transposed(dy)
+            bp, bsf, bgs = nvfp4_cuda.quantize_transposed(x)
+            if self.grad_w is None:
+                self.grad_w = fp4_gemm.fp4_matmul_tiled(ap, asf, ags, bp, bsf, bgs)
+            else:
+                fp4_gemm.fp4_matmul_tiled(ap, asf, ags, bp, bsf, bgs, out=self.grad_w, accumulate=True)
+        elif self.grad_sink is None and self.grad_w is not None and dy.is_cuda and self.grad_w.dtype == torch.bfloat16 \
                 and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0:
             ops.gemm_tn_accumulate(dy, x, self.grad_w)
         else:

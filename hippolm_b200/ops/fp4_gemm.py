@@ -30,6 +30,21 @@ def fp4_matmul(a_packed, a_scales, a_gs, b_packed, b_scales, b_gs) -> torch.Tens
     return out
 
 
+def fp4_matmul_tiled(a_packed, sfa_tiled, a_gs, b_packed, sfb_tiled, b_gs, out=None, accumulate: bool = False) -> torch.Tensor:
+    """Same product with block scales that are already in the MMA tile layout; ``accumulate`` adds into ``out`` (bf16)."""
+    M, K2 = a_packed.shape
+    N = b_packed.shape[0]
+    K = K2 * 2
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a_packed.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1
+    fn = lib().hippo_gemm_nvfp4_accumulate if accumulate else lib().hippo_gemm_nvfp4
+    check(fn(ptr(a_packed), ptr(b_packed), ptr(sfa_tiled), ptr(sfb_tiled), ptr(a_gs), ptr(b_gs), ptr(out), M, N, K,
+             C.c_longlong(out.stride(0)), stream_ptr()), "gemm_nvfp4")
+    return out
+
+
 def supported(M: int, N: int, K: int) -> bool:
     return K % 256 == 0 and N % 8 == 0 and os.environ.get("HIPPO_FP4_GEMM", "1") != "0"
 

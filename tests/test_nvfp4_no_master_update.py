@@ -169,3 +169,31 @@ def test_fp4_backward_dx_matches_dequantised_oracle(no_master):
         o = torch.randn(N, K, device="cuda").bfloat16()
         mc.nvfp4_apply_update(lin, [(0, N, o)], 1.0, 0.05, seed=1)
         assert not torch.equal(lin.transposed_operands()[0], p0)                # cache invalidated by the update
+
+
+@pytest.mark.gpu
+def test_fp4_backward_dw_matches_fp32_oracle_and_accumulates():
+    """``ffn_nvfp4_backward: fp4``: dW = Q(dY^T) Q(x^T)^T with the blocks along the token axis, against dY^T x in fp32
+    (cosine >= 0.99), accumulated over micro-batches by the GEMM epilogue; and the transposed quantiser itself against
+    the row quantiser applied to the transposed tensor (bit-identical codes and scales)."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ops import nvfp4_cuda, fp4_gemm
+    torch.manual_seed(0)
+    T, K, N = 1024, 512, 384
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    p_t, sf_t, gs_t = nvfp4_cuda.quantize_transposed(x)
+    p_r, s_r, gs_r = nvfp4_cuda.quantize(x.t().contiguous())
+    assert torch.equal(gs_t, gs_r) and torch.equal(p_t, p_r)
+    assert torch.equal(sf_t, fp4_gemm.tile_scales(s_r, K, T))
+    lin = NVFP4Linear(K, N, no_master=True, device="cuda", dtype=torch.bfloat16)
+    lin.fp4_backward = lin.fp4_backward_dw = True
+    ref = torch.zeros(N, K, device="cuda")
+    for i in range(3):
+        xi = torch.randn(T, K, device="cuda").bfloat16()
+        dy = (torch.randn(T, N, device="cuda") * (1 + i)).bfloat16()
+        lin.accumulate_grad_product(dy, xi)
+        ref += dy.float().t() @ xi.float()
+    g = lin.grad_w.float()
+    cos = float((g * ref).sum() / (g.norm() * ref.norm()))
+    assert cos > 0.99, cos
+    assert abs(float(g.norm() / ref.norm()) - 1.0) < 0.05

@@ -14,6 +14,7 @@ cu_seqlens-aware KDA under TP, backward collectives and replicated-gradient sync
 """
 from __future__ import annotations
 
+import os
 import math
 import zlib
 from typing import Dict, List, Optional, Tuple
@@ -363,8 +364,35 @@ class _VocabParallelEmbed(torch.autograd.Function):
         return None, dw.to(g.dtype), None
 
 
+class _PeerEmbed(torch.autograd.Function):
+    """CUDA path: rows of this rank's token shard gathered from the owning ranks' weight mirrors by one kernel
+    (``csrc/embed.cu``); the weight gradient pulls the output-gradient rows it needs from the peers' gradient mirrors."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, module):
+        from ..ops import embed_cuda
+        m = get_mesh()
+        T = ids.numel()
+        n = T // m.tp
+        mine = ids[m.tp_rank * n:(m.tp_rank + 1) * n]
+        ctx.module, ctx.T = module, T
+        ctx.save_for_backward(ids)
+        return embed_cuda.gather(mine, module.weight_ptrs(), module.Vl, weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops import embed_cuda
+        (ids,) = ctx.saved_tensors
+        mod, m = ctx.module, get_mesh()
+        g = g.to(torch.bfloat16).contiguous()
+        dw = embed_cuda.grad(ids, mod.grad_ptrs(g), ctx.T // m.tp, mod.v0, mod.Vl, g.shape[1])
+        return None, dw.to(mod.weight.dtype), None
+
+
 class VocabParallelEmbedding(nn.Module):
-    """[V/w, D] shard; lookup of all T tokens, reduce-scattered to the [T/w, D] token shard
+    """[V/w, D] shard. CUDA: one gather kernel reads the rows of the rank's own [T/w] token shard from the rank that owns
+    each vocabulary row (peer loads from a symmetric mirror of the weight shards, refreshed after every optimizer step);
+    CPU / no peer access: lookup of all T tokens, masked, reduce-scattered to the [T/w, D] token shard
     (``src/models/tp_model/embed.py:23-169`` all-reduces instead)."""
 
     def __init__(self, cfg: HippoConfig, seed: int, device, dtype):
@@ -375,8 +403,51 @@ class VocabParallelEmbedding(nn.Module):
         self.v0 = m.tp_rank * self.Vl
         full = _normal("embed_tokens", (cfg.vocab_size, cfg.hidden_size), seed, 0.02)
         self.weight = _mark(nn.Parameter(full[self.v0:self.v0 + self.Vl].to(device=device, dtype=dtype)), "adamw")
+        self._mirror = None          # SymmetricMirror of the weight shard (TP > 1 on CUDA)
+        self._gmirror = None         # SymmetricMirror (two parities) of the output-gradient shard
+        self._dirty = True           # weight changed since the mirror was published
+        self._gpar = 0
+
+    def weights_changed(self) -> None:
+        """Called after every optimizer step / checkpoint load: the peer-readable mirror is re-published on next use."""
+        self._dirty = True
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self._dirty = True
+
+    def _peer_path(self, ids) -> bool:
+        m = get_mesh()
+        return (ids.is_cuda and self.weight.dtype == torch.bfloat16 and self.weight.shape[1] % 8 == 0
+                and ids.numel() % m.tp == 0 and os.environ.get("HIPPO_PEER_EMBED", "1") != "0")
+
+    def weight_ptrs(self) -> List[int]:
+        m = get_mesh()
+        if m.tp == 1:
+            return [self.weight.data_ptr()]
+        if self._mirror is None:
+            from ..parallel.symm import SymmetricMirror
+            self._mirror = SymmetricMirror(m, self.weight.numel() * 2)
+        if self._dirty:
+            self._mirror.publish(self.weight.detach())
+            self._dirty = False
+        return self._mirror.ptrs()
+
+    def grad_ptrs(self, g: torch.Tensor) -> List[int]:
+        m = get_mesh()
+        if m.tp == 1:
+            return [g.data_ptr()]
+        nbytes = g.numel() * 2
+        if self._gmirror is None or self._gmirror.nbytes < nbytes:
+            from ..parallel.symm import SymmetricMirror
+            self._gmirror = SymmetricMirror(m, nbytes, parities=2)
+        self._gpar ^= 1
+        self._gmirror.publish(g, self._gpar)
+        return self._gmirror.ptrs(self._gpar)
 
     def forward(self, ids):
+        if self._peer_path(ids):
+            return _PeerEmbed.apply(ids, self.weight, self)
         return _VocabParallelEmbed.apply(ids, self.weight, self.v0)
 
 
@@ -518,6 +589,10 @@ class HippoModel(nn.Module):
         self.kda_layer_ids = [i for i, k in enumerate(kinds) if k == "kda"]
 
     # ---- parameter views used by the optimizers / grad sync
+    def after_optimizer_step(self) -> None:
+        """Hook for whoever writes the parameters in place (optimizer kernels, weight surgery): derived copies are stale."""
+        self.embed_tokens.weights_changed()
+
     def replicated_parameters(self):
         return [p for p in self.parameters() if getattr(p, "tp_replicated", False)]
 

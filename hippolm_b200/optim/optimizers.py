@@ -139,19 +139,26 @@ class Muon:
                 if lo < hi:
                     e.module.decay_and_apply_chunk(lo, hi, upd[lo - a:hi - a], self.lr, wd_factor)
 
-    def _step_cuda(self, e: _Entry, g: torch.Tensor, grad_scale: float, wd_factor: float, full_scope: bool) -> bool:
-        """Fully fused device path for one entry; returns False when a segment needs the generic path."""
+    def _step_cuda(self, e: _Entry, g: torch.Tensor, grad_scale: float, wd_factor: float, full_scope: bool,
+                   work: Optional[list] = None) -> bool:
+        """Fully fused device path for one entry; returns False when the entry needs the generic path. Segments that are
+        tensor-parallel shards of a larger matrix are, under ``ns_scope = full``, only given their momentum update here and
+        queued on ``work`` (entry, row0, row1, u) for the gather -> full-matrix Newton-Schulz -> scatter rounds."""
         from ..ops import muon_cuda as mc
         segs = self._segments(e)
         cols = e.shape[1]
         if g.dtype not in (torch.bfloat16, torch.float32) or not g.is_contiguous():
             return False
         for (a, b) in segs:
-            if full_scope and b > a and self._shard_dim(e, (a, b)) is not None:
+            if full_scope and b > a and self._shard_dim(e, (a, b)) is not None and (work is None or not mc.supported(b - a, cols)):
                 return False
         fp4_segments = []
         for (a, b) in segs:
             if b <= a:
+                continue
+            if full_scope and self._shard_dim(e, (a, b)) is not None:
+                u, _ = mc.momentum_update(g[a:b], e.exp_avg[a:b], self.momentum, grad_scale, self.nesterov)
+                work.append((e, a, b, u))
                 continue
             if not mc.supported(b - a, cols):
                 # tiny / ragged segment (e.g. the H/tp rows of the beta projection): elementwise momentum on the slice,
@@ -244,7 +251,7 @@ class Muon:
             if g is None:
                 continue
             dev = e.device
-            if dev.type == "cuda" and not self.offload and self._step_cuda(e, g, grad_scale, wd_factor, full_scope):
+            if dev.type == "cuda" and not self.offload and self._step_cuda(e, g, grad_scale, wd_factor, full_scope, work):
                 continue
             gf = g.to(torch.float32)
             if grad_scale != 1.0:
@@ -272,6 +279,7 @@ class Muon:
         # (every rank works on a different matrix of the round) and the slices are scattered back.
         tp, r, grp = mesh.tp, mesh.tp_rank, mesh.tp_group
         ranks = mesh.tp_ranks()
+        fp4_pending: Dict[int, list] = {}           # id(module) -> [module, [(a, b, o)]]: all segments share one tensor scale
         for r0 in range(0, len(work), tp):
             rnd = work[r0:r0 + tp]
             gathered = [None] * len(rnd)
@@ -284,12 +292,34 @@ class Muon:
                 if r == j:
                     dim = self._shard_dim(e, (a, b))
                     full = torch.cat(gathered[j], dim=dim)
-                    o = ops.newton_schulz5(full, self.ns_steps)
+                    o = self._ns_full(full)
                     outs[j] = [t.contiguous() for t in o.chunk(tp, dim=dim)]
             for j, (e, a, b, u) in enumerate(rnd):
                 mine = torch.empty_like(u)
                 dist.scatter(mine, outs[j] if r == j else None, src=ranks[j], group=grp)
-                self._apply(e, a, b, mine, wd_factor)
+                if mine.is_cuda and mine.dtype == torch.bfloat16 and not self.offload:
+                    from ..ops import muon_cuda as mc
+                    if e.param is not None:
+                        mc.apply_update(e.param.data[a:b], mine, wd_factor, self.lr)
+                    else:
+                        fp4_pending.setdefault(id(e.module), [e, []])[1].append((a, b, mine))
+                else:
+                    self._apply(e, a, b, mine, wd_factor)
+        for e, segs in fp4_pending.values():
+            from ..ops import muon_cuda as mc
+            mc.nvfp4_apply_update(e.module, sorted(segs, key=lambda t: t[0]), wd_factor, self.lr,
+                                  seed=(self.sr_seed * 1000003 + e.step * 7919 + getattr(e, "idx", 0)) & 0x7FFFFFFF,
+                                  stochastic=self.stochastic_rounding)
+
+    def _ns_full(self, full: torch.Tensor) -> torch.Tensor:
+        """Newton-Schulz of a gathered full matrix: the tcgen05 path for bf16 CUDA matrices, the fp32 oracle otherwise."""
+        if full.is_cuda and full.dtype == torch.bfloat16:
+            from ..ops import muon_cuda as mc
+            if mc.supported(full.shape[0], full.shape[1]):
+                full = full.contiguous()
+                ssq = full.float().pow(2).sum().reshape(1)
+                return mc.newton_schulz_(full, ssq, self.ns_steps)
+        return ops.newton_schulz5(full, self.ns_steps)
 
     def zero_grad(self):
         for e in self.entries:

@@ -248,6 +248,40 @@ class FusedWorkspace:
             raise RuntimeError(f"a bounded device wait ran out: code={st[0]} detail={st[1]} block={st[2]} count={st[3]}")
 
 
+class SymmetricMirror:
+    """A peer-readable copy of a per-rank tensor (the embedding shard, an output-gradient shard): ``parities`` buffers
+    of ``nbytes`` in symmetric memory. ``publish(src, parity)`` copies ``src`` in and runs a barrier over the TP group on
+    the current stream, after which every rank may read every rank's buffer of that parity through ``ptrs(parity)``.
+    With two parities a rank can publish the next tensor while slower peers still read the previous one."""
+
+    def __init__(self, mesh, nbytes: int, parities: int = 1):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.mesh = mesh
+        self.group = mesh.tp_group if mesh.tp_group is not None else dist.group.WORLD
+        self.nbytes = int(nbytes)
+        self._bufs, self._ptrs = [], []
+        for _ in range(parities):
+            t = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=mesh.device)
+            h = symm_mem.rendezvous(t, self.group)
+            self._bufs.append((t, h))
+            self._ptrs.append([int(p) for p in h.buffer_ptrs])
+        self._token = torch.zeros(1, device=mesh.device)
+
+    def ptrs(self, parity: int = 0) -> List[int]:
+        return self._ptrs[parity]
+
+    def local(self, parity: int = 0) -> torch.Tensor:
+        return self._bufs[parity][0]
+
+    def publish(self, src: torch.Tensor, parity: int = 0) -> None:
+        raw = src.contiguous().view(torch.uint8).reshape(-1)
+        assert raw.numel() <= self.nbytes
+        self._bufs[parity][0][:raw.numel()].copy_(raw)
+        # stream-ordered barrier: the collective completes on a rank only after every rank has reached it, i.e. after
+        # every rank's copy above
+        dist.all_reduce(self._token, group=self.group)
+
+
 def create_workspace(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, wait_cycles: int = 0
                      ) -> Optional[FusedWorkspace]:
     if mesh.tp <= 1 or mesh.device.type != "cuda":

@@ -284,6 +284,7 @@ def train_step(ctx: TrainContext, batch: Dict[str, torch.Tensor], timer: Optiona
     with timer.phase("zero"):
         ctx.muon.zero_grad(); ctx.adamw.zero_grad()
         repack_nvfp4_weights(model)
+        model.after_optimizer_step()
     if ctx.step < _DIAG_STEPS and getattr(args, "diagnostics", False):
         log_post_opt_diag(ctx.logger, ctx.step, [ctx.muon, ctx.adamw])
     return {"loss": loss_acc, "grad_norm": gnorm, "found_inf": found_inf, "lr_muon": lr_m, "lr_adamw": lr_a,

@@ -174,3 +174,28 @@ def test_sumsq_multi_one_launch():
     assert _ext.launch_count() == n0 + 1
     ref = [sum(float(t.float().pow(2).sum()) for t, s in items if s == k) for k in (0, 1)]
     assert abs(float(out[0]) - ref[0]) < 1e-3 * ref[0] and abs(float(out[1]) - ref[1]) < 1e-3 * ref[1]
+
+
+def test_embed_gather_and_grad_kernels():
+    """Embedding kernels against torch indexing: several vocabulary shards (here all in local memory, one pointer per
+    shard as the peer path passes them), ids outside the vocabulary, repeated ids in the gradient."""
+    from hippolm_b200.ops import embed_cuda
+    torch.manual_seed(0)
+    world, Vl, D, T = 4, 50, 256, 64
+    shards = [torch.randn(Vl, D, device="cuda").bfloat16() for _ in range(world)]
+    full = torch.cat(shards, 0)
+    ids = torch.randint(0, world * Vl, (T,), device="cuda")
+    ids[3] = ids[5] = ids[9]                                             # repeated id
+    out = embed_cuda.gather(ids[16:32], [s.data_ptr() for s in shards], Vl, D)    # "rank 1" of 4: tokens 16..31
+    assert torch.equal(out, full[ids[16:32]])
+    bad = ids[:8].clone(); bad[2] = -1; bad[4] = world * Vl
+    outb = embed_cuda.gather(bad, [s.data_ptr() for s in shards], Vl, D)
+    assert float(outb[2].abs().max()) == 0 and float(outb[4].abs().max()) == 0 and torch.equal(outb[0], full[bad[0]])
+    g = [torch.randn(T // world, D, device="cuda").bfloat16() for _ in range(world)]    # per-rank token shards
+    gfull = torch.cat(g, 0).float()
+    for r in range(world):
+        dw = embed_cuda.grad(ids, [t.data_ptr() for t in g], T // world, r * Vl, Vl, D)
+        ref = torch.zeros(Vl, D, device="cuda")
+        sel = ((ids >= r * Vl) & (ids < (r + 1) * Vl)).nonzero(as_tuple=True)[0]
+        ref.index_add_(0, ids[sel] - r * Vl, gfull[sel])
+        assert (dw - ref).abs().max() < 1e-4

@@ -392,7 +392,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
-  p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta; p.sym_lower = 0;
+  p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta; p.sym_lower = 0; p.ksplit = 0;
   p.tiles_m = (M + BM - 1) / BM; p.tiles_n = (N + BN - 1) / BN;
   int tiles = p.tiles_m * p.tiles_n;
   int sms = sm_count();
@@ -433,7 +433,7 @@ static int gemm_bf16_dispatch(const void* A, const void* B, void* C, int M, int 
     // CTA-pair kernel (256x256 tiles over two SMs): half the shared-memory operand traffic per SM
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
-    p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0;
+    p.Cin = g_cin; p.ldcin = g_ldcin; p.beta = g_beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0; p.ksplit = 0;
     return launch_gemm_2sm(A, B, layout, lda, ldb, p, max_ctas, s);
   }
   CommParams cp = {};

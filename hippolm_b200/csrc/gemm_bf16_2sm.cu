@@ -79,8 +79,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   // pair tiles (256 x 256); a symmetric-output launch enumerates only the tiles on or below the diagonal
-  const int num_tiles = p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : p.tiles_m * p.tiles_n;
-  const int kblocks = (p.K + BK - 1) / BK;
+  const int out_tiles = p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : p.tiles_m * p.tiles_n;
+  const int kblocks_all = (p.K + BK - 1) / BK;
+  // split-K: work item t = slice * out_tiles + tile; every slice covers kb_per k-blocks (the last one what is left)
+  const int ksplit = p.ksplit > 1 ? p.ksplit : 1;
+  const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
+  const int num_tiles = out_tiles * ksplit;
   const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -117,10 +121,11 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int it = 0;
       bool ok = true;
       for (int t = cid; t < num_tiles && ok; t += n_clusters) {
-        int tm, tn; tile_coord(t, tm, tn);
+        int tm, tn; tile_coord(t % out_tiles, tm, tn);
         const int row0 = (tm * 2 + (int)rank) * BM;            // this CTA's rows of A / C
         const int col0 = tn * BN + (int)rank * BNH;            // this CTA's half of the B tile
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int kb0 = (t / out_tiles) * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
           if (!ok) break;
@@ -154,7 +159,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!ok) break;
         tc_fence_after();
         uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int kb0 = (t / out_tiles) * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
           if (!ok) break;
@@ -164,7 +170,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t ad = A_KMAJOR ? make_smem_desc(sa + k * 32, 16, 1024) : make_smem_desc(sa + k * 2048, 8192, 1024);
             uint64_t bd = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024) : make_smem_desc(sb + k * 2048, 8192, 1024);
-            mma_f16_ss_pair(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+            mma_f16_ss_pair(d_tmem, ad, bd, idesc, ((kb - kb0) | k) ? 1u : 0u);
           }
           const uint32_t e = smem_u32(&empty[s]);
           tc_commit_pair(e);                                    // stage free in this CTA ...
@@ -182,7 +188,9 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     int tl = 0;
     bool ok = true;
     for (int t = cid; t < num_tiles && ok; t += n_clusters) {
-      int tm, tn; tile_coord(t, tm, tn);
+      int tm, tn; tile_coord(t % out_tiles, tm, tn);
+      GemmParams pe = p;                                          // split-K: this slice's partial-product plane
+      if (ksplit > 1) pe.C = (float*)p.C + (long long)(t / out_tiles) * p.M * p.ldc;
       const int tl_now = tl++;
       int acc = tl_now & 1; uint32_t aph = (tl_now >> 1) & 1;
       ok = mbar_wait(&tfull[acc], aph, kWaitTmemFull, tl_now);
@@ -197,9 +205,9 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         EpiPrefetch pre;
         const int col0 = tn * BN + c;
         tmem_ld_32x32(taddr + c, r);
-        epi_prefetch(p, row, col0, pre);          // addends travel while the TMEM load completes
+        epi_prefetch(pe, row, col0, pre);         // addends travel while the TMEM load completes
         tc_wait_ld();
-        epi_store(p, r, row, col0, pre);
+        epi_store(pe, r, row, col0, pre);
       }
       tc_fence_before();
       __syncwarp();
@@ -230,7 +238,7 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   int clusters = sms / 2;
   if (clusters < 1) clusters = 1;
-  const int work = p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : tiles;
+  const int work = (p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : tiles) * (p.ksplit > 1 ? p.ksplit : 1);
   if (work < clusters) clusters = work;
   auto kern = gemm_bf16_2sm_kernel<AK, BK_>;
   static bool attr_set = false;
@@ -292,8 +300,61 @@ extern "C" int hippo_gemm_bf16_2sm(const void* A, const void* B, void* C, const 
   if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15)) return -3;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
-  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0;
+  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0; p.ksplit = 0;
   return launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
+}
+
+// out (+)= alpha * sum over the ksplit partial planes of the fp32 workspace [ksplit][M][N]
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, long long plane, void* out, int out_fp32,
+                                     long long ldo, int N, int accumulate, float alpha, long long n) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float4 a = *(const float4*)(ws + i);
+    for (int s = 1; s < ksplit; ++s) {
+      const float4 b = *(const float4*)(ws + s * plane + i);
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    a.x *= alpha; a.y *= alpha; a.z *= alpha; a.w *= alpha;
+    const long long r = i / N; const int c = (int)(i % N);          // N % 4 == 0: the four elements share a row
+    if (out_fp32) {
+      float4* o = (float4*)((float*)out + r * ldo + c);
+      if (accumulate) { const float4 v = *o; a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+      *o = a;
+    } else {
+      __nv_bfloat162* o = (__nv_bfloat162*)((__nv_bfloat16*)out + r * ldo + c);
+      if (accumulate) {
+        const float2 v0 = __bfloat1622float2(o[0]), v1 = __bfloat1622float2(o[1]);
+        a.x += v0.x; a.y += v0.y; a.z += v1.x; a.w += v1.y;
+      }
+      o[0] = __floats2bfloat162_rn(a.x, a.y); o[1] = __floats2bfloat162_rn(a.z, a.w);
+    }
+  }
+}
+
+// Split-K product for outputs with too few 256x256 tiles to fill the GPU (weight gradients of narrow projections with
+// a contraction over tens of thousands of tokens): work item = (tile, K slice); partial products go to `workspace`
+// (fp32, ksplit * M * N elements, provided by the caller), then one reduction pass writes C (+= when accumulate).
+// Deterministic: the slices are summed in a fixed order.
+extern "C" int hippo_gemm_bf16_splitk(const void* A, const void* B, void* C, float* workspace, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int layout, int out_fp32,
+                                      int accumulate, float alpha, int ksplit, void* stream) {
+  using namespace hippo;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (N % 4) || ksplit < 2) return -2;
+  if ((out_fp32 ? (ldc % 4) : (ldc % 8)) || ((uintptr_t)C & 15) || ((uintptr_t)workspace & 15)) return -3;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = workspace; p.ldc = N; p.out_fp32 = 1; p.accumulate = 0; p.alpha = 1.f;
+  // every slice must own at least one k-block (an empty slice would publish an accumulator nobody wrote)
+  const int kblocks = (K + sm2::BK - 1) / sm2::BK;
+  if (ksplit > kblocks) ksplit = kblocks;
+  const int kb_per = (kblocks + ksplit - 1) / ksplit;
+  ksplit = (kblocks + kb_per - 1) / kb_per;
+  p.Cin = nullptr; p.ldcin = 0; p.beta = 0.f; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0; p.ksplit = ksplit;
+  int rc = launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
+  if (rc) return rc;
+  const long long n = (long long)M * N;
+  unsigned grid = (unsigned)((n / 4 + 255) / 256); if (grid > 1184) grid = 1184; if (grid == 0) grid = 1;
+  splitk_reduce_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(workspace, ksplit, n, C, out_fp32, ldc, N, accumulate, alpha, n);
+  return (int)cudaGetLastError();
 }
 
 // Symmetric product (C = C^T by construction, e.g. X X^T or S S + S with S symmetric), bf16 n x n output: only the
@@ -306,7 +367,7 @@ extern "C" int hippo_gemm_bf16_sym(const void* A, const void* B, void* C, const 
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (ldc % 8) || ((uintptr_t)C & 15)) return -2;
   GemmParams p;
   p.M = n; p.N = n; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = 0; p.accumulate = 0; p.alpha = alpha;
-  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 1;
+  p.Cin = Cin; p.ldcin = ldcin; p.beta = beta; p.tiles_m = p.tiles_n = 0; p.sym_lower = 1; p.ksplit = 0;
   int rc = launch_gemm_2sm(A, B, layout, lda, ldb, p, 0, (cudaStream_t)stream);
   if (rc) return rc;
   const unsigned nb = (unsigned)((n + 31) / 32);

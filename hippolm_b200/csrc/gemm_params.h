@@ -16,6 +16,8 @@ struct GemmParams {
   long long ldcin; float beta;
   int tiles_m, tiles_n;
   int sym_lower;       // CTA-pair kernel: skip the 256x256 tiles above the diagonal (square symmetric output)
+  int ksplit;          // CTA-pair kernel: > 1 = the contraction is cut into ksplit slices, work item = (tile, slice), slice s
+                       // writes its fp32 partial product to C + s * M * ldc (C is then a [ksplit * M, ldc] fp32 workspace)
 };
 
 #ifdef __CUDACC__

@@ -1,6 +1,7 @@
 """CUDA execution path: autograd Functions over the sm_100a kernels in ``hippolm_b200/csrc``."""
 from __future__ import annotations
 
+import os
 import ctypes
 from typing import List, Optional, Tuple
 
@@ -31,6 +32,16 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int, K: int,
                                        _c.c_float(alpha), _c.c_float(0.0), stream_ptr())
         check(rc, "hippo_gemm_bf16_2sm")
         return out
+    ks = _splitk_factor(M, N, K) if kernel == "auto" else 1
+    if ks > 1:
+        # too few 256x256 output tiles for 74 CTA pairs (weight gradients of narrow projections): cut the contraction
+        ws = torch.empty(ks * M * N, dtype=torch.float32, device=a.device)
+        rc = lib().hippo_gemm_bf16_splitk(ptr(a), ptr(b), ptr(out), ptr(ws), M, N, K, _c.c_longlong(a.stride(0)),
+                                          _c.c_longlong(b.stride(0)), _c.c_longlong(out.stride(0)), layout,
+                                          1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                                          _c.c_float(alpha), ks, stream_ptr())
+        check(rc, "hippo_gemm_bf16_splitk")
+        return out
     fn = lib().hippo_gemm_bf16_1sm if kernel == "1sm" else lib().hippo_gemm_bf16
     rc = fn(ptr(a), ptr(b), ptr(out), M, N, K, _c.c_longlong(a.stride(0)),
                                _c.c_longlong(b.stride(0)), _c.c_longlong(out.stride(0)), layout,
@@ -38,6 +49,27 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int, K: int,
                                _c.c_float(alpha), max_ctas, stream_ptr())
     check(rc, "hippo_gemm_bf16")
     return out
+
+
+_SPLITK = os.environ.get("HIPPO_GEMM_SPLITK", "1") != "0"
+
+
+def _splitk_factor(M: int, N: int, K: int, clusters: int = 74) -> int:
+    """Number of K slices for the CTA-pair kernel: the factor that minimises (waves of 256x256 work items) / slices plus
+    the cost of the reduction pass. 1 = plain launch. Only long contractions with few output tiles qualify."""
+    if not _SPLITK or M <= 128 or N % 4 or K < 4096:
+        return 1
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if tiles >= 2 * clusters:
+        return 1
+    best, best_cost = 1, float(-(-tiles // clusters))
+    for s in (2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64):
+        if K < 2048 * s or tiles * s > 8 * clusters or s * M * N * 4 > (1 << 28):
+            break
+        cost = (-(-tiles * s // clusters)) / s + 0.03 + (s + 1) * 467.0 / K
+        if cost < 0.9 * best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def _pad_cols(x: torch.Tensor, mult: int = 8) -> torch.Tensor:

@@ -88,3 +88,37 @@ def test_symmetric_output_gemm(n, K):
     assert torch.equal(M, M.t())
     torch.cuda.synchronize()
     assert _ext.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("M,N,K,layout", [(512, 128, 16384, 2), (1024, 512, 8200, 2), (300, 264, 9000, 0), (1536, 1024, 12288, 1)])
+def test_gemm_split_k(M, N, K, layout):
+    """Few output tiles and a long contraction: the dispatcher cuts K into slices (work item = tile x slice, fp32
+    partial planes, one reduction pass). Same result as the fp32 product, bf16 and fp32 outputs, accumulate included,
+    and bit-identical between two runs (the slices are summed in a fixed order)."""
+    from hippolm_b200.ops import cuda_ops as co
+    from hippolm_b200.ops import _ext
+    assert co._splitk_factor(M, N, K) > 1
+    _ext.clear_device_status()
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    ref = a.float() @ b.float().t()
+    if layout == 0:
+        A, B = a, b
+    elif layout == 1:
+        A, B = a, b.t().contiguous()
+    else:
+        A, B = a.t().contiguous(), b.t().contiguous()
+    tol = 2e-2 * (K ** 0.5)
+    y = co._gemm(A, B, layout, M, N, K)
+    assert (y.float() - ref).abs().max() < tol
+    y2 = co._gemm(A, B, layout, M, N, K)
+    assert torch.equal(y, y2)
+    acc = torch.full((M, N), 3.0, device="cuda", dtype=torch.float32)
+    co._gemm(A, B, layout, M, N, K, out=acc, accumulate=True, alpha=0.5)
+    assert (acc - (3.0 + 0.5 * ref)).abs().max() < 1e-2 * (K ** 0.5) * 0.5 + 1e-2
+    accb = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    co._gemm(A, B, layout, M, N, K, out=accb, accumulate=True)
+    assert (accb.float() - (1.0 + ref)).abs().max() < tol
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0

@@ -161,7 +161,9 @@ def test_fp4_backward_dx_matches_dequantised_oracle(no_master):
         ref = dy.float() @ wdq
         cos = lambda a, b: float((a * b).sum() / (a.norm() * b.norm()))
         assert cos(grads[False][0], ref) > 0.999
-        assert cos(grads[True][0], ref) > 0.99, cos(grads[True][0], ref)
+        # no-master: W^T is a re-encoding of the stored FP4 weight. With a master the forward and the transposed
+        # encoding are two independent roundings of the same bf16 weight, so the distance to dq(Q(W)) is one rounding more
+        assert cos(grads[True][0], ref) > (0.99 if no_master else 0.985), cos(grads[True][0], ref)
         assert abs(float(grads[True][0].norm() / ref.norm()) - 1.0) < 0.05
         assert torch.equal(grads[True][1], grads[False][1])                     # dW is not touched by the option
     if no_master:

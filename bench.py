@@ -241,6 +241,13 @@ def main():
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},
                "gpu_launches": launches, "loss": last_loss,
                "max_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "device_status": list(st), "impl": "ours"}
+        try:
+            from hippolm_b200.parallel import fused as _fused
+            # per (op, shape): did the one-kernel compute+collective path win the timing against NCCL + plain GEMM?
+            rec["config"]["fused_comm_choices"] = {"/".join(str(x) for x in k): ("fused" if v else "nccl+gemm")
+                                                   for k, v in _fused.choices().items()}
+        except Exception:                                              # noqa: BLE001
+            pass
         rec.update(kda)
         print(json.dumps(rec), flush=True)
     teardown_worker(ctx)

@@ -16,6 +16,7 @@
 #include "sm100.cuh"
 #include "host_utils.h"
 #include "gemm_params.h"
+#include "gemm_comm.cuh"
 #include <stdlib.h>
 
 namespace hippo {
@@ -64,9 +65,14 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc,
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+// COMM == COMM_AG: all-gather -> GEMM in this kernel. The first cp.comm_ctas CTAs (whole clusters) run the bulk-copy
+// role of gemm_comm.cuh instead of computing; the GEMM clusters walk the 256-row pair tiles shard by shard in arrival
+// order, every CTA's TMA producer acquiring (bounded) the arrival counter of ITS 128-row block before the block's first
+// load; tiles of the own shard read x_local in place through tmOwn. All loads are plain TMA loads of local memory.
+template <bool A_KMAJOR, bool B_KMAJOR, int COMM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
+                     const __grid_constant__ CommParams cp, const __grid_constant__ CUtensorMap tmOwn) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // used in the leader only
@@ -85,13 +91,15 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int ksplit = p.ksplit > 1 ? p.ksplit : 1;
   const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
   const int num_tiles = out_tiles * ksplit;
-  const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
+  const int comm_clusters = (COMM == COMM_AG) ? cp.comm_ctas >> 1 : 0;
+  const int cid = ((int)blockIdx.x >> 1) - comm_clusters, n_clusters = ((int)gridDim.x >> 1) - comm_clusters;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+    if (COMM == COMM_AG) prefetch_tmap(&tmOwn);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -109,22 +117,46 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       return;
     }
     const int GROUP = 8;                  // 8 pair-tiles (2048 rows) share each column sweep
+    int tiles_m = p.tiles_m, base_m = 0;
+    if (COMM == COMM_AG) {                // shard by shard in arrival order: own, rank-1, rank-2, ...
+      const int tms = cp.rows_per_shard / (2 * BM);
+      const int per_shard = tms * p.tiles_n;
+      const int si = t / per_shard;
+      t -= si * per_shard;
+      base_m = ((cp.rank - si + cp.world) % cp.world) * tms; tiles_m = tms;
+    }
     int per_group = GROUP * p.tiles_n;
     int g = t / per_group, r = t % per_group;
-    int gm = min(GROUP, p.tiles_m - g * GROUP);
-    tm = g * GROUP + r % gm;
+    int gm = min(GROUP, tiles_m - g * GROUP);
+    tm = base_m + g * GROUP + r % gm;
     tn = r / gm;
   };
 
+  if (COMM == COMM_AG && (int)blockIdx.x < cp.comm_ctas) {
+    if (threadIdx.x == 0) ag_copy_role<STAGE_BYTES, BM>(smem, full, cp, p.K, (int)blockIdx.x);
+  } else
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      int last_rb = -1;
       for (int t = cid; t < num_tiles && ok; t += n_clusters) {
         int tm, tn; tile_coord(t % out_tiles, tm, tn);
         const int row0 = (tm * 2 + (int)rank) * BM;            // this CTA's rows of A / C
         const int col0 = tn * BN + (int)rank * BNH;            // this CTA's half of the B tile
         const int kb0 = (t / out_tiles) * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+        bool own_tile = false;
+        if (COMM == COMM_AG) {
+          const int rb = tm * 2 + (int)rank;                   // this CTA's 128-row block of the gathered A
+          const int own_lo = cp.rank * (cp.rows_per_shard / BM);
+          own_tile = rb >= own_lo && rb < own_lo + cp.rows_per_shard / BM;
+          if (!own_tile && rb != last_rb) {                    // one acquire per new row block
+            ok = wait_counter(cp.flag_peer[cp.rank] + rb, cp.target, cp.wait_cycles, rb);
+            asm volatile("fence.proxy.async;" ::: "memory");   // remote async-proxy writes -> TMA reads
+            last_rb = rb;
+            if (!ok) break;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
@@ -132,7 +164,9 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
           uint8_t* sa = smem + s * STAGE_BYTES; uint8_t* sb = sa + A_BYTES;
-          if (A_KMAJOR) {
+          if (COMM == COMM_AG && own_tile) {
+            tma_load_2d_pair(sa, &tmOwn, bar, kb * BK, row0 - cp.rank * cp.rows_per_shard);
+          } else if (A_KMAJOR) {
             tma_load_2d_pair(sa, &tmA, bar, kb * BK, row0);
           } else {
 #pragma unroll
@@ -221,9 +255,9 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-template <bool AK, bool BK_>
+template <bool AK, bool BK_, int COMM>
 static int launch(const void* A, const void* B, long long lda, long long ldb, GemmParams p, int max_ctas,
-                  cudaStream_t stream) {
+                  const CommParams& cp, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc;
   if (AK) rc = make_tmap_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda * 2, BK, BM, 2, true);
@@ -232,6 +266,11 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   if (BK_) rc = make_tmap_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb * 2, BK, BNH, 2, true);
   else     rc = make_tmap_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb * 2, 64, BK, 2, true);
   if (rc) return rc;
+  CUtensorMap tmOwn = tmA;
+  if (COMM == COMM_AG) {
+    rc = make_tmap_2d(&tmOwn, cp.x_local, (uint64_t)p.K, (uint64_t)cp.rows_per_shard, (uint64_t)cp.x_ld * 2, BK, BM, 2, true);
+    if (rc) return rc;
+  }
   p.tiles_m = (p.M + 2 * BM - 1) / (2 * BM); p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   int sms = sm_count();
@@ -239,15 +278,15 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   int clusters = sms / 2;
   if (clusters < 1) clusters = 1;
   const int work = (p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : tiles) * (p.ksplit > 1 ? p.ksplit : 1);
-  if (work < clusters) clusters = work;
-  auto kern = gemm_bf16_2sm_kernel<AK, BK_>;
+  if (COMM == COMM_NONE && work < clusters) clusters = work;   // AG: copy clusters + GEMM clusters, all co-resident
+  auto kern = gemm_bf16_2sm_kernel<AK, BK_, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  kern<<<2 * clusters, THREADS, SMEM, stream>>>(tmA, tmB, p);
+  kern<<<2 * clusters, THREADS, SMEM, stream>>>(tmA, tmB, p, cp, tmOwn);
   return (int)cudaGetLastError();
 }
 
@@ -278,12 +317,22 @@ bool gemm_2sm_enabled() {
 
 int launch_gemm_2sm(const void* A, const void* B, int layout, long long lda, long long ldb, const GemmParams& p,
                     int max_ctas, cudaStream_t stream) {
+  CommParams cp = {};
   switch (layout) {
-    case 0: return sm2::launch<true, true>(A, B, lda, ldb, p, max_ctas, stream);
-    case 1: return sm2::launch<true, false>(A, B, lda, ldb, p, max_ctas, stream);
-    case 2: return sm2::launch<false, false>(A, B, lda, ldb, p, max_ctas, stream);
-    case 3: return sm2::launch<false, true>(A, B, lda, ldb, p, max_ctas, stream);
+    case 0: return sm2::launch<true, true, COMM_NONE>(A, B, lda, ldb, p, max_ctas, cp, stream);
+    case 1: return sm2::launch<true, false, COMM_NONE>(A, B, lda, ldb, p, max_ctas, cp, stream);
+    case 2: return sm2::launch<false, false, COMM_NONE>(A, B, lda, ldb, p, max_ctas, cp, stream);
+    case 3: return sm2::launch<false, true, COMM_NONE>(A, B, lda, ldb, p, max_ctas, cp, stream);
   }
+  return -1;
+}
+
+// All-gather -> GEMM on the CTA-pair kernel (layout 0: B stored [N, K]; 1: B stored [K, N]); cp as for the one-CTA kernel,
+// with comm_ctas even and rows_per_shard a multiple of 256.
+int launch_allgather_gemm_2sm(const void* A, const void* B, int layout, long long lda, long long ldb, const GemmParams& p,
+                              const CommParams& cp, cudaStream_t stream) {
+  if (layout == 0) return sm2::launch<true, true, COMM_AG>(A, B, lda, ldb, p, 0, cp, stream);
+  if (layout == 1) return sm2::launch<true, false, COMM_AG>(A, B, lda, ldb, p, 0, cp, stream);
   return -1;
 }
 

@@ -7,7 +7,8 @@ baseline runs.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+import os
+from typing import Callable, Dict, Optional, Tuple
 
 import torch
 
@@ -34,6 +35,7 @@ def setup(mesh, max_tokens: int, max_width: int, dtype=torch.bfloat16, wait_cycl
 
 def teardown() -> None:
     _STATE["ws"] = None
+    _CHOICE.clear()
 
 
 def allgather_gemm(x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False, need_gathered: bool = True
@@ -67,6 +69,66 @@ def nvfp4_gemm_reduce_scatter(x: torch.Tensor, packed: torch.Tensor, scales: tor
     if ws is None:
         return None
     return ws.nvfp4_gemm_reduce_scatter(x, packed, scales, global_scale)
+
+
+# ---------------------------------------------------------------------------------------------- fused or not, measured
+# A fused kernel hides the transfer behind the GEMM but computes on the one-CTA GEMM (or carries copy CTAs); NCCL followed
+# by the CTA-pair GEMM exposes the transfer but computes faster. Which one wins depends on the op, its shape and the
+# number of ranks (at 2 ranks the transfer is small, at 8 it is as long as the GEMM), so every (op, shape) is timed once,
+# at its first use, on the device, as the max over the ranks, and the faster variant is used from then on.
+_CHOICE: Dict[tuple, bool] = {}
+_AUTOTUNE = os.environ.get("HIPPO_FUSED_AUTOTUNE", "1") != "0"
+
+
+def tuned(key: tuple, fused_fn: Callable[[], object], unfused_fn: Callable[[], object]):
+    """Result of ``fused_fn()`` or ``unfused_fn()``, whichever was faster when ``key`` was first seen. Both compute the
+    same values; every rank of the TP group must call this with the same key at the same point (the timing is collective).
+    A ``fused_fn`` that returns None (shape not covered) settles the choice on the unfused path."""
+    ws = _STATE["ws"]
+    if ws is None:
+        return unfused_fn()
+    use = _CHOICE.get(key)
+    if use is None and not _AUTOTUNE:
+        use = True
+    if use is not None:
+        if use:
+            out = fused_fn()
+            if not _is_none(out):
+                return out
+        return unfused_fn()
+    import torch.distributed as dist
+    group = ws._group
+    res, times = {}, {}
+    for name, fn in (("unfused", unfused_fn), ("fused", fused_fn)):
+        out = fn()                                            # warm-up (and the coverage check of the fused path)
+        if _is_none(out):
+            times[name] = float("inf")
+            continue
+        ts = []
+        for _ in range(2):
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); out = fn(); e1.record(); e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        t = torch.tensor([min(ts)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        times[name], res[name] = float(t), out
+    use = times["fused"] <= times["unfused"]
+    _CHOICE[key] = use
+    if ws.rank == 0:
+        import logging
+        logging.getLogger("hippo.r0").info(f"fused-comm choice {key}: fused {times['fused']:.3f} ms, "
+                                           f"unfused {times['unfused']:.3f} ms -> {'fused' if use else 'unfused'}")
+    return res["fused" if use else "unfused"]
+
+
+def _is_none(out) -> bool:
+    return out is None or (isinstance(out, tuple) and out[0] is None)
+
+
+def choices() -> Dict[tuple, bool]:
+    return dict(_CHOICE)
 
 
 def workspace():

@@ -35,18 +35,24 @@ class _ColumnLinearSP(torch.autograd.Function):
     def forward(ctx, x, weight, bias):
         m = get_mesh()
         f = _fused()
+        def unfused():
+            g = all_gather_dim0(x, m.tp_group, m.tp)
+            return g, ops.gemm_nt(g, weight), False
+
+        def fused_path():
+            g, yy = f.allgather_gemm(x, weight, need_gathered=False)
+            return g, yy, True
         if f is not None and x.is_cuda and m.tp > 1 and f.fits(x.shape[0], x.shape[0] * m.tp, x.shape[1]) \
                 and weight.shape[0] % 8 == 0 and x.dtype == torch.bfloat16:
-            xg, y = f.allgather_gemm(x, weight, need_gathered=False)
-            if KEEP_GATHERED:
+            xg, y, was_fused = f.tuned(("ag", x.shape[0], x.shape[1], weight.shape[0], 0), fused_path, unfused)
+            if was_fused and KEEP_GATHERED:
                 # a private copy of the gathered activations for the dW GEMM of the backward pass (the workspace
                 # view is recycled two calls later); costs T*K*2 bytes per layer, saves one all-gather per layer
                 rows = x.shape[0]
                 xg = xg.clone()
                 xg[m.tp_rank * rows:(m.tp_rank + 1) * rows].copy_(x)
         else:
-            xg = all_gather_dim0(x, m.tp_group, m.tp)
-            y = ops.gemm_nt(xg, weight)
+            xg, y, _ = unfused()
         if bias is not None:
             y = y + bias
         ctx.kept = bool(KEEP_GATHERED and m.tp > 1)
@@ -62,12 +68,14 @@ class _ColumnLinearSP(torch.autograd.Function):
         f = _fused()
         dxg = None
         if ctx.needs_input_grad[0]:
+            def unfused():
+                return reduce_scatter_dim0(ops.gemm_nn(dy, weight), m.tp_group, m.tp)
             if f is not None and dy.is_cuda and m.tp > 1 and dy.dtype == torch.bfloat16 \
                     and f.fits(dy.shape[0] // m.tp, dy.shape[0], weight.shape[1]) and dy.shape[1] % 8 == 0:
-                dx = f.gemm_reduce_scatter(dy, weight, transpose_w=True)
+                dx = f.tuned(("rs", dy.shape[0], dy.shape[1], weight.shape[1], 1),
+                             lambda: f.gemm_reduce_scatter(dy, weight, transpose_w=True), unfused)
             else:
-                dxg = ops.gemm_nn(dy, weight)                      # [T, K]
-                dx = reduce_scatter_dim0(dxg, m.tp_group, m.tp)
+                dx = unfused()
         else:
             dx = None
         xg = x if ctx.kept else all_gather_dim0(x, m.tp_group, m.tp)
@@ -81,11 +89,14 @@ class _RowLinearSP(torch.autograd.Function):
     def forward(ctx, x, weight):
         m = get_mesh()
         f = _fused()
+        def unfused():
+            return reduce_scatter_dim0(ops.gemm_nt(x, weight), m.tp_group, m.tp)
         if f is not None and x.is_cuda and m.tp > 1 and x.dtype == torch.bfloat16 \
                 and f.fits(x.shape[0] // m.tp, x.shape[0], weight.shape[0]) and x.shape[1] % 8 == 0:
-            y = f.gemm_reduce_scatter(x, weight, transpose_w=False)
+            y = f.tuned(("rs", x.shape[0], x.shape[1], weight.shape[0], 0),
+                        lambda: f.gemm_reduce_scatter(x, weight, transpose_w=False), unfused)
         else:
-            y = reduce_scatter_dim0(ops.gemm_nt(x, weight), m.tp_group, m.tp)
+            y = unfused()
         ctx.save_for_backward(x, weight)
         return y
 
@@ -95,12 +106,15 @@ class _RowLinearSP(torch.autograd.Function):
         m = get_mesh()
         f = _fused()
         dy = dy.contiguous()
+        def unfused():
+            g = all_gather_dim0(dy, m.tp_group, m.tp)              # [T, N]
+            return g, ops.gemm_nn(g, weight)                       # [T, K/w]
         if f is not None and dy.is_cuda and m.tp > 1 and dy.dtype == torch.bfloat16 \
                 and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and weight.shape[1] % 8 == 0:
-            dyg, dx = f.allgather_gemm(dy, weight, transpose_w=True)
+            dyg, dx = f.tuned(("ag", dy.shape[0], dy.shape[1], weight.shape[1], 1),
+                              lambda: f.allgather_gemm(dy, weight, transpose_w=True), unfused)
         else:
-            dyg = all_gather_dim0(dy, m.tp_group, m.tp)            # [T, N]
-            dx = ops.gemm_nn(dyg, weight)                          # [T, K/w]
+            dyg, dx = unfused()
         dw = ops.gemm_tn(dyg, x)                                   # [N, K/w]
         return dx, dw.to(weight.dtype)
 
@@ -130,14 +144,16 @@ class _NVFP4ColumnSP(torch.autograd.Function):
         m = get_mesh()
         packed, scales, gs = _nvfp4_operands(module, weight)
         f = _fused()
-        y, kept = None, None
-        if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
-            y, kept = f.nvfp4_allgather_gemm(x, packed, scales, gs, keep_gathered=KEEP_GATHERED)   # None: not covered
-        if y is None:
+
+        def unfused():
             xg = all_gather_dim0(x, m.tp_group, m.tp) if m.tp > 1 else x
-            y = ops.nvfp4_linear(xg, packed, scales, gs, act_quant=module.act_quant)
-            if KEEP_GATHERED and m.tp > 1:
-                kept = xg
+            return ops.nvfp4_linear(xg, packed, scales, gs, act_quant=module.act_quant), \
+                (xg if KEEP_GATHERED and m.tp > 1 else None)
+        if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
+            y, kept = f.tuned(("fp4_ag", x.shape[0], x.shape[1], packed.shape[0]),
+                              lambda: f.nvfp4_allgather_gemm(x, packed, scales, gs, keep_gathered=KEEP_GATHERED), unfused)
+        else:
+            y, kept = unfused()
         ctx.module = module
         # kept: the gathered input, either bf16 [T, K] or the FP4 bytes the GEMM consumed (uint8, dequantised in backward:
         # dW = dY^T Q(x) is the exact weight gradient of the quantised forward)
@@ -159,7 +175,9 @@ class _NVFP4ColumnSP(torch.autograd.Function):
             if m.tp == 1:
                 dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True)
             elif f is not None:
-                dx = f.nvfp4_gemm_reduce_scatter(dy, pt, st, gt)              # None: shape not covered
+                dx = f.tuned(("fp4_rs", dy.shape[0], dy.shape[1], pt.shape[0]),
+                             lambda: f.nvfp4_gemm_reduce_scatter(dy, pt, st, gt),     # None: shape not covered
+                             lambda: reduce_scatter_dim0(ops.nvfp4_linear(dy, pt, st, gt, act_quant=True), m.tp_group, m.tp))
         w = ops.nvfp4_dequantize(packed, scales, gs, dy.dtype) if dx is None else None   # [N/w, K]
         if m.tp == 1:
             if dx is None:
@@ -170,7 +188,9 @@ class _NVFP4ColumnSP(torch.autograd.Function):
                 pass
             elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
                     and f.fits(dy.shape[0] // m.tp, dy.shape[0], w.shape[1]) and dy.shape[1] % 8 == 0:
-                dx = f.gemm_reduce_scatter(dy, w, transpose_w=True)
+                dx = f.tuned(("rs", dy.shape[0], dy.shape[1], w.shape[1], 1),
+                             lambda: f.gemm_reduce_scatter(dy, w, transpose_w=True),
+                             lambda: reduce_scatter_dim0(ops.gemm_nn(dy, w), m.tp_group, m.tp))
             else:
                 dx = reduce_scatter_dim0(ops.gemm_nn(dy, w), m.tp_group, m.tp)
             if ctx.kept_kind == 2:
@@ -195,13 +215,14 @@ class _NVFP4RowSP(torch.autograd.Function):
         m = get_mesh()
         packed, scales, gs = _nvfp4_operands(module, weight)
         f = _fused()
-        y = None
+        def unfused():
+            yy = ops.nvfp4_linear(x, packed, scales, gs, act_quant=module.act_quant)
+            return reduce_scatter_dim0(yy, m.tp_group, m.tp) if m.tp > 1 else yy
         if f is not None and x.is_cuda and m.tp > 1 and module.act_quant:
-            y = f.nvfp4_gemm_reduce_scatter(x, packed, scales, gs)
-        if y is None:
-            y = ops.nvfp4_linear(x, packed, scales, gs, act_quant=module.act_quant)
-            if m.tp > 1:
-                y = reduce_scatter_dim0(y, m.tp_group, m.tp)
+            y = f.tuned(("fp4_rs", x.shape[0], x.shape[1], packed.shape[0]),
+                        lambda: f.nvfp4_gemm_reduce_scatter(x, packed, scales, gs), unfused)
+        else:
+            y = unfused()
         ctx.module = module
         ctx.save_for_backward(x, packed, scales, gs)
         return y
@@ -233,7 +254,11 @@ class _NVFP4RowSP(torch.autograd.Function):
                 dyg, dx = dy, ops.gemm_nn(dy, w)
             elif f is not None and dy.is_cuda and dy.dtype == torch.bfloat16 \
                     and f.fits(dy.shape[0], dy.shape[0] * m.tp, dy.shape[1]) and w.shape[1] % 8 == 0:
-                dyg, dx = f.allgather_gemm(dy, w, transpose_w=True)
+                def unfused():
+                    g = all_gather_dim0(dy, m.tp_group, m.tp)
+                    return g, ops.gemm_nn(g, w)
+                dyg, dx = f.tuned(("ag", dy.shape[0], dy.shape[1], w.shape[1], 1),
+                                  lambda: f.allgather_gemm(dy, w, transpose_w=True), unfused)
             else:
                 dyg = all_gather_dim0(dy, m.tp_group, m.tp)
                 dx = ops.gemm_nn(dyg, w)

@@ -107,6 +107,11 @@ for it in range(3):
     Wt = W.t().contiguous()
     _, y2 = ws.allgather_gemm(x, Wt, transpose_w=True)
     assert rel(y2, xg_ref.float() @ W.float().t()) < 2e-2
+    # 512-row shards take the CTA-pair kernel (256-row pair tiles); 384-row shards take the one-CTA kernel
+    x3 = torch.randn(384, K, device=dev).bfloat16()
+    xg3, y3 = ws.allgather_gemm(x3, W)
+    xg3_ref = all_gather_dim0(x3, mesh.tp_group, w_)
+    assert torch.equal(xg3, xg3_ref) and rel(y3, xg3_ref.float() @ W.float().t()) < 2e-2
     T, Kl, N2 = 1024, 512, 1024
     a = torch.randn(T, Kl, device=dev).bfloat16(); W2 = (0.05 * torch.randn(N2, Kl, device=dev)).bfloat16()
     out = ws.gemm_reduce_scatter(a, W2)

@@ -199,3 +199,34 @@ def test_fp4_backward_dw_matches_fp32_oracle_and_accumulates():
     cos = float((g * ref).sum() / (g.norm() * ref.norm()))
     assert cos > 0.99, cos
     assert abs(float(g.norm() / ref.norm()) - 1.0) < 0.05
+
+
+@pytest.mark.gpu
+def test_fp4_backward_loss_curve_tracks_bf16_backward():
+    """50 steps on a fixed batch at small width (no-master NVFP4 FFN, everything trainable): the loss with the FFN
+    backward on the FP4 tensor cores (dX and dW) follows the bf16-backward run."""
+    import os
+    from hippolm_b200.cli import build_parser
+    from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
+    from hippolm_b200.data.loaders import synthetic_loader
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    curves = {}
+    for mode in ("bf16", "fp4"):
+        a = build_parser().parse_args([])
+        a.vocab_size, a.hidden_size, a.num_heads, a.head_dim = 2048, 512, 4, 128
+        a.num_layers, a.num_blocks, a.intermediate_size = 4, 2, 1024
+        a.ffn_nvfp4 = a.ffn_nvfp4_no_bf16_master = True
+        a.ffn_nvfp4_backward = mode
+        a.batch_size, a.seq_len, a.max_steps, a.seed = 4, 512, 1000, 1
+        loader = synthetic_loader(a.batch_size, a.seq_len, a.vocab_size, 0, 128, 512, fixed=True)
+        ctx = setup_worker(a, run_dir=None, data_iter=loader)
+        batch = next(loader)
+        losses = []
+        for _ in range(50):
+            losses.append(float(train_step(ctx, batch)["loss"])); ctx.step += 1
+        teardown_worker(ctx)
+        curves[mode] = losses
+    b, f = curves["bf16"], curves["fp4"]
+    assert b[-1] < b[0] - 1.0 and f[-1] < f[0] - 1.0, (b[0], b[-1], f[0], f[-1])
+    assert abs(f[-1] - b[-1]) < 0.15 * max(b[0] - b[-1], 1e-6), (b[-1], f[-1])

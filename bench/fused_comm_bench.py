@@ -41,9 +41,13 @@ def main():
     import argparse
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=0, help="tokens per call; 0 = 8192 per rank (the training micro-batch)")
-    T, D = ap.parse_args().tokens or 8192 * w, 4096
+    ap.add_argument("--comm_ctas", type=int, default=0, help="copy CTAs of the all-gather kernels (0 = the default, 16)")
+    a = ap.parse_args()
+    T, D = a.tokens or 8192 * w, 4096
     assert fused.setup(mesh, T, D)
     ws = fused._STATE["ws"]
+    if a.comm_ctas > 0:
+        ws.comm_ctas = a.comm_ctas
     pk = load_measured_peaks()
     g = mesh.tp_group
     for (name, N, K) in [("attn in_proj", 6400 // w // 64 * 64, D), ("ffn gate_up", 2 * 14336 // w, D)]:

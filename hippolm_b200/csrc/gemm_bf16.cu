@@ -410,6 +410,14 @@ extern "C" int hippo_gemm_reduce_scatter_bf16(const void* A, long long lda, cons
   cp.out_local = out_local;
   const int M = world * rows_per_shard;
   cudaStream_t s = (cudaStream_t)stream;
+  static int pair = -1;
+  if (pair < 0) { const char* e = getenv("HIPPO_FUSED_PAIR"); pair = (e && e[0] == '0') ? 0 : 1; }
+  if (pair && gemm_2sm_enabled() && rows_per_shard % 256 == 0 && (layout == 0 || layout == 1)) {
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = N; p.out_fp32 = 0; p.accumulate = 0; p.alpha = 1.f;
+    p.Cin = nullptr; p.ldcin = 0; p.beta = 0.f; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0; p.ksplit = 0;
+    return launch_gemm_reduce_scatter_2sm(A, B, layout, lda, ldb, p, cp, s);
+  }
   if (layout == 0) return launch_gemm<true, true, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
   if (layout == 1) return launch_gemm<true, false, COMM_RS>(A, B, nullptr, M, N, K, lda, ldb, N, 0, 0, 1.f, 0, cp, s);
   return -1;

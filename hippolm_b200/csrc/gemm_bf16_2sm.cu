@@ -65,6 +65,11 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc,
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// COMM == COMM_RS: GEMM -> reduce-scatter in this kernel. Pair tiles are walked remote owners first (rank+1, ...), own
+// rows last; the epilogue of every CTA lays its warps' 32 x 256 slabs out in shared memory (the space of pipeline stages
+// 4 and 5; the main loop runs on 4 stages) and writes 512-byte rows into the staging slot [this rank] of the rank that
+// owns the rows, then releases that rank's per-source counter; after its last tile every CTA joins the reduction of the
+// local rows (bounded wait for all sources, sum of the slots).
 // COMM == COMM_AG: all-gather -> GEMM in this kernel. The first cp.comm_ctas CTAs (whole clusters) run the bulk-copy
 // role of gemm_comm.cuh instead of computing; the GEMM clusters walk the 256-row pair tiles shard by shard in arrival
 // order, every CTA's TMA producer acquiring (bounded) the arrival counter of ITS 128-row block before the block's first
@@ -91,6 +96,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int ksplit = p.ksplit > 1 ? p.ksplit : 1;
   const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
   const int num_tiles = out_tiles * ksplit;
+  constexpr int NST = (COMM == COMM_RS) ? 4 : STAGES;              // RS: stages 4 and 5 are the epilogue staging area
+  uint8_t* epi_stage = smem + 4 * STAGE_BYTES;                      // COMM_RS only: 4 warps x [32][512 B]
   const int comm_clusters = (COMM == COMM_AG) ? cp.comm_ctas >> 1 : 0;
   const int cid = ((int)blockIdx.x >> 1) - comm_clusters, n_clusters = ((int)gridDim.x >> 1) - comm_clusters;
 
@@ -118,12 +125,13 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
     const int GROUP = 8;                  // 8 pair-tiles (2048 rows) share each column sweep
     int tiles_m = p.tiles_m, base_m = 0;
-    if (COMM == COMM_AG) {                // shard by shard in arrival order: own, rank-1, rank-2, ...
+    if (COMM != COMM_NONE) {              // shard by shard: AG in arrival order (own, rank-1, ...), RS remote owners first
       const int tms = cp.rows_per_shard / (2 * BM);
       const int per_shard = tms * p.tiles_n;
       const int si = t / per_shard;
       t -= si * per_shard;
-      base_m = ((cp.rank - si + cp.world) % cp.world) * tms; tiles_m = tms;
+      const int shard = (COMM == COMM_AG) ? (cp.rank - si + cp.world) % cp.world : (cp.rank + 1 + si) % cp.world;
+      base_m = shard * tms; tiles_m = tms;
     }
     int per_group = GROUP * p.tiles_n;
     int g = t / per_group, r = t % per_group;
@@ -158,7 +166,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          int s = it % NST; uint32_t ph = (it / NST) & 1;
           ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
           if (!ok) break;
           if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
@@ -195,7 +203,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t d_tmem = tmem_base + acc * BN;
         const int kb0 = (t / out_tiles) * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          int s = it % NST; uint32_t ph = (it / NST) & 1;
           ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
           if (!ok) break;
           tc_fence_after();
@@ -233,6 +241,44 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tc_fence_after();
       const int row = (tm * 2 + (int)rank) * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      if (COMM == COMM_RS) {
+        uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 512);          // [32 rows][32 x 16 B]
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * p.alpha, __uint_as_float(r[j + 2 * e + 1]) * p.alpha);
+            const int piece = (c + j) / 8;                                   // 16-byte piece within the row
+            slab[lane * 32 + (piece ^ (lane & 31))] = v;                     // xor swizzle: conflict-free both ways
+          }
+        }
+        // the accumulator is in shared memory now: hand it back to the leader before the (slow) remote stores
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+        const int row_base = (tm * 2 + (int)rank) * BM + q * 32;
+        const int owner = row_base / cp.rows_per_shard;
+        const int ncols = min(BN, p.N - tn * BN);                            // multiple of 8
+        __nv_bfloat16* dst0 = (__nv_bfloat16*)cp.buf_peer[owner] +
+                              ((long long)cp.rank * cp.rows_per_shard + (row_base - owner * cp.rows_per_shard)) * p.N + tn * BN;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; ++rr) {
+          if (row_base + rr < p.M && lane * 8 < ncols)
+            *(uint4*)(dst0 + (long long)rr * p.N + lane * 8) = slab[rr * 32 + (lane ^ (rr & 31))];
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(cp.flag_peer[owner] + cp.rank, 1u);
+        __syncwarp();                                                        // the slab is free for the next tile
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -253,6 +299,48 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   __syncthreads();
   cluster_sync_all();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (COMM == COMM_RS) {
+    // ---- reduction of the rows this rank owns: wait for every source, then sum the staging slots
+    if ((int)threadIdx.x < cp.world)
+      wait_counter(cp.flag_peer[cp.rank] + threadIdx.x, cp.target, cp.wait_cycles, 100 + threadIdx.x);
+    __syncthreads();
+    const long long nvec = (long long)cp.rows_per_shard * p.N / 8;
+    const uint4* stage = (const uint4*)cp.buf_peer[cp.rank];
+    uint4* out = (uint4*)cp.out_local;
+    const long long stride = (long long)gridDim.x * THREADS;
+    for (long long v0 = (long long)blockIdx.x * THREADS + threadIdx.x; v0 < nvec; v0 += stride * 4) {
+      float acc[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+      for (int sidx = 0; sidx < cp.world; ++sidx) {
+        uint4 x[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                        // 4 independent loads in flight per source
+          const long long v = v0 + j * stride;
+          x[j] = v < nvec ? __ldcg(stage + (long long)sidx * nvec + v) : make_uint4(0, 0, 0, 0);   // written by another GPU: bypass L1
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162* xb = (const __nv_bfloat162*)&x[j];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(xb[e]); acc[j][2 * e] += f.x; acc[j][2 * e + 1] += f.y; }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long v = v0 + j * stride;
+        if (v < nvec) {
+          uint4 o;
+          __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[j][2 * e], acc[j][2 * e + 1]);
+          out[v] = o;
+        }
+      }
+    }
+  }
 }
 
 template <bool AK, bool BK_, int COMM>
@@ -278,7 +366,7 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   int clusters = sms / 2;
   if (clusters < 1) clusters = 1;
   const int work = (p.sym_lower ? p.tiles_m * (p.tiles_m + 1) / 2 : tiles) * (p.ksplit > 1 ? p.ksplit : 1);
-  if (COMM == COMM_NONE && work < clusters) clusters = work;   // AG: copy clusters + GEMM clusters, all co-resident
+  if (COMM != COMM_AG && work < clusters) clusters = work;     // AG: copy clusters + GEMM clusters, all co-resident
   auto kern = gemm_bf16_2sm_kernel<AK, BK_, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -333,6 +421,14 @@ int launch_allgather_gemm_2sm(const void* A, const void* B, int layout, long lon
                               const CommParams& cp, cudaStream_t stream) {
   if (layout == 0) return sm2::launch<true, true, COMM_AG>(A, B, lda, ldb, p, 0, cp, stream);
   if (layout == 1) return sm2::launch<true, false, COMM_AG>(A, B, lda, ldb, p, 0, cp, stream);
+  return -1;
+}
+
+// GEMM -> reduce-scatter on the CTA-pair kernel (same layouts); rows_per_shard a multiple of 256.
+int launch_gemm_reduce_scatter_2sm(const void* A, const void* B, int layout, long long lda, long long ldb,
+                                   const GemmParams& p, const CommParams& cp, cudaStream_t stream) {
+  if (layout == 0) return sm2::launch<true, true, COMM_RS>(A, B, lda, ldb, p, 0, cp, stream);
+  if (layout == 1) return sm2::launch<true, false, COMM_RS>(A, B, lda, ldb, p, 0, cp, stream);
   return -1;
 }
 

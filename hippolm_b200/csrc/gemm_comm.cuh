@@ -123,5 +123,7 @@ __device__ __forceinline__ void ag_copy_role(uint8_t* smem, uint64_t* full, cons
 struct GemmParams;
 int launch_allgather_gemm_2sm(const void* A, const void* B, int layout, long long lda, long long ldb, const GemmParams& p,
                               const CommParams& cp, cudaStream_t stream);
+int launch_gemm_reduce_scatter_2sm(const void* A, const void* B, int layout, long long lda, long long ldb,
+                                   const GemmParams& p, const CommParams& cp, cudaStream_t stream);
 
 }  // namespace hippo

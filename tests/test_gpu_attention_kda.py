@@ -146,3 +146,64 @@ def test_kda_skip_saved_recomputes_identical_gradients():
     for a, b in zip(res[0][2], res[1][2]):
         assert _rel(a, b) < 2e-3, _rel(a, b)
     assert res[1][3] < 0.6 * res[0][3], (res[0][3], res[1][3])
+
+
+@pytest.mark.slow
+def test_kda_at_benchmark_length_against_fp32_oracle():
+    """The standalone-KDA benchmark layout on a 2-head slice: 32 768 tokens in 8 documents of random lengths, with an
+    initial state and a gradient on the final state, forward and backward against the chunked fp32 oracle."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ref.kda import kda_chunked_anchored, l2norm
+    torch.manual_seed(0)
+    T, H, D, docs = 32768, 2, 128, 8
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda"))
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cuts = torch.sort(torch.randperm(T - 1)[:docs - 1] + 1).values
+    cu = torch.cat([torch.zeros(1, dtype=torch.long), cuts, torch.tensor([T])]).to(torch.int32).cuda()
+    h0 = torch.randn(docs, H, D, D, device="cuda") * 0.1
+    do = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    df = torch.randn(docs, H, D, D, device="cuda") * 0.1
+    outs, grads = [], []
+    for impl in (0, 1):
+        ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta, h0)]
+        fn = ops.kda if impl == 0 else kda_chunked_anchored
+        o, f = fn(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, ins[5], cu, False) if impl else \
+            fn(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, ins[5], cu, use_qk_l2norm=False)
+        ((o.float() * do).sum() + (f * df).sum()).backward()
+        outs.append((o, f)); grads.append([t.grad for t in ins])
+    assert _rel(outs[0][0], outs[1][0]) < 2e-2 and _rel(outs[0][1], outs[1][1]) < 2e-2
+    for a, b in zip(*grads):
+        assert _rel(a, b) < 3e-2
+
+
+def test_causal_attention_long_sequence():
+    """One 8192-token sequence next to short ones, 4 heads of 128: forward and backward against the fp32 oracle."""
+    test_causal_attention(10240, 4, 128, [0, 8192, 8200, 10240])
+
+
+def test_kda_backward_is_reproducible():
+    """Two backward passes over the same forward agree to rounding (the only unordered sums are shared-memory float
+    atomics of the beta gradient) and the forward is bit-identical."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ref.kda import l2norm
+    torch.manual_seed(3)
+    T, H, D = 1500, 4, 128
+    q = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    k = l2norm(torch.randn(T, H, D, device="cuda")).bfloat16().float()
+    v = torch.randn(T, H, D, device="cuda").bfloat16().float()
+    g = -torch.nn.functional.softplus(torch.randn(T, H, D, device="cuda"))
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    cu = torch.tensor([0, 700, 1500], dtype=torch.int32, device="cuda")
+    do = torch.randn(T, H, D, device="cuda")
+    res = []
+    for _ in range(2):
+        ins = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta)]
+        o, f = ops.kda(ins[0], ins[1], ins[2], ins[3], ins[4], 1.0, None, cu, use_qk_l2norm=False)
+        (o.float() * do).sum().backward()
+        res.append((o, [t.grad for t in ins]))
+    assert torch.equal(res[0][0], res[1][0])
+    for a, b in zip(res[0][1], res[1][1]):
+        assert _rel(a, b) < 1e-5                      # unordered sums: shared-memory float atomics (beta gradient)

@@ -52,7 +52,10 @@ def test_loss_decreases_on_fixed_batch(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("cfg,extra", [("tp2.yml", []), ("dp2.yml", []), ("nvfp4_tp2.yml", [])])
+@pytest.mark.parametrize("cfg,extra", [("tp2.yml", []), ("dp2.yml", []), ("nvfp4_tp2.yml", []),
+                                       ("dp2.yml", ["--dp_reduce_to_owner", "true"]),
+                                       ("nvfp4_tp2.yml", ["--ffn_nvfp4_backward", "fp4"]),
+                                       ("tp2.yml", ["--muon_ns_scope", "full"])])
 def test_two_gpu_configs(cfg, extra, tmp_path):
     _run(cfg, extra + ["--max_steps", "4"], tmp_path)
 

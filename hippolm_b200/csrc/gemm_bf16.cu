@@ -164,6 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     int tl = 0;
+    int rs_pending = 0;                     // COMM_RS: tiles of the current owner shard stored but not yet released
     bool ok = true;
     for (int t = bid; t < num_tiles && ok; t += n_gemm_ctas, ++tl) {
       int tm, tn; tile_coord(t, tm, tn);
@@ -217,14 +218,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_wait_ld();
         epi_store(p, r, row, col0, pre);
       }
-      if (COMM == COMM_RS) {
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(cp.flag_peer[(tm * BM) / cp.rows_per_shard] + cp.rank, 1u);
-      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (lane == 0) mbar_arrive(&tempty[acc]);           // the accumulator is free before any remote round trip
+      if (COMM == COMM_RS) {
+        // one fence + counter release per OWNER SHARD (the owner reduces only after a source's last tile anyway)
+        const int owner = (tm * BM) / cp.rows_per_shard;
+        ++rs_pending;
+        const int tnext = t + n_gemm_ctas;
+        int owner_next = -1;
+        if (tnext < num_tiles) { int tm2, tn2; tile_coord(tnext, tm2, tn2); owner_next = (tm2 * BM) / cp.rows_per_shard; }
+        if (owner_next != owner) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) red_release_sys_add(cp.flag_peer[owner] + cp.rank, (uint32_t)rs_pending);
+          rs_pending = 0;
+        }
+      }
     }
   }
   tc_fence_before();

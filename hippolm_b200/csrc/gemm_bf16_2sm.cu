@@ -228,6 +228,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   } else {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     int tl = 0;
+    int rs_pending = 0;                     // COMM_RS: tiles of the current owner shard stored but not yet released
     bool ok = true;
     for (int t = cid; t < num_tiles && ok; t += n_clusters) {
       int tm, tn; tile_coord(t % out_tiles, tm, tn);
@@ -273,9 +274,21 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           if (row_base + rr < p.M && lane * 8 < ncols)
             *(uint4*)(dst0 + (long long)rr * p.N + lane * 8) = slab[rr * 32 + (lane ^ (rr & 31))];
         }
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(cp.flag_peer[owner] + cp.rank, 1u);
+        // One fence + counter release per OWNER SHARD, not per tile: the owner only starts its reduction when all of a
+        // source's tiles have landed, so the remote-write round trip is paid once per shard instead of once per tile.
+        ++rs_pending;
+        const int tnext = t + n_clusters;
+        int owner_next = -1;
+        if (tnext < num_tiles) {
+          int tm2, tn2; tile_coord(tnext % out_tiles, tm2, tn2);
+          owner_next = ((tm2 * 2 + (int)rank) * BM + q * 32) / cp.rows_per_shard;
+        }
+        if (owner_next != owner) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) red_release_sys_add(cp.flag_peer[owner] + cp.rank, (uint32_t)rs_pending);
+          rs_pending = 0;
+        }
         __syncwarp();                                                        // the slab is free for the next tile
         continue;
       }

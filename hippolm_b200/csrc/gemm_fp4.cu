@@ -193,6 +193,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     const int q = warp & 3;
     int tl = 0; bool ok = true;
+    int rs_pending = 0;                     // F_COMM_RS: tiles of the current owner shard stored but not yet released
     float alpha = (COMM == F_COMM_AG) ? 0.f : (*p.gsa) * (*p.gsb);
     const float gsb = *p.gsb;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
@@ -239,9 +240,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (row_base + r2 < p.M && pc * 8 < ncols)
             *(uint4*)(dst0 + (long long)r2 * p.N + pc * 8) = slab[r2 * 16 + (pc ^ (r2 & 15))];
         }
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) f_red_release_sys_add(p.rs_flag_peer[owner] + p.rank, 1u);
+        // one fence + counter release per OWNER SHARD (the owner reduces only after a source's last tile anyway)
+        ++rs_pending;
+        const int tnext = t + (int)gridDim.x;
+        int owner_next = -1;
+        if (tnext < num_tiles) { int tm2, tn2; tile_coord(tnext, tm2, tn2); owner_next = (tm2 * F_BM + q * 32) / p.rows_per_shard; }
+        if (owner_next != owner) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) f_red_release_sys_add(p.rs_flag_peer[owner] + p.rank, (uint32_t)rs_pending);
+          rs_pending = 0;
+        }
       } else
 #pragma unroll 1
       for (int c = 0; c < F_BN; c += 32) {

@@ -54,7 +54,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--adamw_beta1", type=float, default=0.9); a("--adamw_beta2", type=float, default=0.95)
     a("--adamw_eps", type=float, default=1e-8); a("--adamw_reference_compat", type=_bool, default=False)
     a("--muon_lr", type=float, default=0.02); a("--muon_weight_decay", type=float, default=0.0)
-    a("--muon_momentum", type=float, default=0.95); a("--muon_ns_scope", type=str, default="shard"); a("--muon_dp_shard", type=_bool, default=True); a("--muon_ns_row_chunk", type=int, default=None)
+    a("--muon_momentum", type=float, default=0.95); a("--muon_ns_scope", type=str, default="full"); a("--muon_dp_shard", type=_bool, default=True); a("--muon_ns_row_chunk", type=int, default=None)
     a("--epochs", type=int, default=1); a("--max_steps", type=int, default=1000)
     a("--gradient_accumulation_steps", type=int, default=1)
     a("--lr_warmup_steps", type=int, default=0); a("--lr_decay_steps", type=int, default=0)

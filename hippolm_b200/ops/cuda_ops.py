@@ -208,7 +208,27 @@ def swiglu(gu):
     return _SwiGLU.apply(gu)
 
 
+class _Silu(torch.autograd.Function):
+    """SiLU through the row-op kernel (forward); the backward is elementwise torch on the saved input."""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        y = torch.empty_like(x)
+        check(lib().hippo_silu_fwd(ptr(x), ptr(y), _c.c_longlong(x.numel()), stream_ptr()), "silu_fwd")
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        xf = x.float()
+        sg = torch.sigmoid(xf)
+        return (dy.float() * sg * (1 + xf * (1 - sg))).to(dy.dtype)
+
+
 def silu(x):
+    if x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0:
+        return _Silu.apply(x)
     return torch.nn.functional.silu(x)
 
 

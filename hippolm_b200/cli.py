@@ -84,7 +84,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--min_gpu_memory_mb", type=int, default=10240); a("--tp_sim", type=_bool, default=False)
     a("--tp_size", type=int, default=1); a("--dp_size", type=int, default=0)
     a("--nproc", type=int, default=0); a("--dp_overlap", type=_bool, default=True)
-    a("--dp_reduce_to_owner", type=_bool, default=False)
+    a("--dp_reduce_to_owner", type=_bool, default=True)
     a("--fused_comm", type=_bool, default=True); a("--fused_wait_ms", type=float, default=0.0)
     a("--offload_optimizer", type=_bool, default=False); a("--offload_grads", type=_bool, default=False)
     a("--precision", type=str, default=None)

@@ -38,7 +38,7 @@ def _run(rank, world, port, dp, out_path, offload, overlap, mask_rank, mbs):
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
     torch.set_num_threads(1)
     from hippolm_b200.train.loop import setup_worker, train_step, teardown_worker
-    a = _args(1, dp)
+    a = _args(1, dp, to_owner=(dp > 1))          # the default: Muon gradients are reduced to their owning replica only
     a.offload_grads, a.dp_overlap, a.dist_timeout_s = offload, overlap, 60
     a.micro_batch_size = mbs
     ctx = setup_worker(a, run_dir=None, data_iter=iter(()))

@@ -41,6 +41,7 @@ def parse():
     p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
     p.add_argument("--no_fused_comm", action="store_true")
     p.add_argument("--bf16_ffn", action="store_true")
+    p.add_argument("--ffn_bwd", type=str, default="bf16", help="NVFP4 FFN backward: bf16 | fp4_dx | fp4 (A/B switch)")
     p.add_argument("--no_kda", dest="kda", action="store_false",
                    help="skip the standalone chunked-KDA timing that rank 0 adds to the JSON line (outside the timed region)")
     p.add_argument("--kda_only", action="store_true", help="print only the standalone chunked-KDA timing")
@@ -150,6 +151,7 @@ def main():
         setattr(args, k, v)
     args.ffn_nvfp4 = not a.bf16_ffn
     args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
+    args.ffn_nvfp4_backward = a.ffn_bwd
     args.tp_size = world
     args.dp_size = 1
     args.seq_len = SEQ_LEN if a.model != "tiny" else 1024
@@ -235,7 +237,7 @@ def main():
                "config": {"model": name, "global_batch": args.batch_size, "seq_len": args.seq_len,
                           "parallelism": f"tp{world}+sp", "micro_batch_tokens": a.micro_batch_tokens,
                           "optimizer": "muon+adamw", "l2": "inputs larger than L2 (no explicit flush)",
-                          "fused_comm": bool(ctx.extras.get("fused_comm", False))},
+                          "fused_comm": bool(ctx.extras.get("fused_comm", False)), "ffn_backward": a.ffn_bwd},
                "clocks": clocks,
                "e2e": {"value": gb_tokens / (e2e_ms_step / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},

@@ -5,7 +5,8 @@
     python bench.py --impl reference ...                      (reference arm)
 
 Model/config: 32 layers at 3:1 KDA:attention, d_model 4096, 32 heads x 128, FFN 14336 (NVFP4, no
-bf16 master), vocab 128256, block attention residuals (8 blocks), Muon + AdamW, seq 8192,
+bf16 master, forward and backward on the FP4 tensor cores; --ffn_bwd bf16 for the A/B), vocab 128256,
+block attention residuals (8 blocks), Muon + AdamW, seq 8192,
 TP = N with sequence parallelism. Weak scaling: 16 sequences per GPU per step (N=8 gives the
 configured global batch of 128). Synthetic seeded uniform-random tokens, random-init weights.
 
@@ -41,7 +42,9 @@ def parse():
     p.add_argument("--seqs_per_gpu", type=int, default=SEQS_PER_GPU)
     p.add_argument("--no_fused_comm", action="store_true")
     p.add_argument("--bf16_ffn", action="store_true")
-    p.add_argument("--ffn_bwd", type=str, default="bf16", help="NVFP4 FFN backward: bf16 | fp4_dx | fp4 (A/B switch)")
+    p.add_argument("--ffn_bwd", type=str, default="fp4",
+                   help="NVFP4 FFN backward: fp4 (dX and dW on the FP4 tensor cores, the benchmarked configuration: "
+                        "configs/hybrid_7b_tp8.yml) | fp4_dx | bf16 (backward on the dequantised weight; A/B switch)")
     p.add_argument("--no_kda", dest="kda", action="store_false",
                    help="skip the standalone chunked-KDA timing that rank 0 adds to the JSON line (outside the timed region)")
     p.add_argument("--kda_only", action="store_true", help="print only the standalone chunked-KDA timing")
@@ -151,7 +154,7 @@ def main():
         setattr(args, k, v)
     args.ffn_nvfp4 = not a.bf16_ffn
     args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
-    args.ffn_nvfp4_backward = a.ffn_bwd
+    args.ffn_nvfp4_backward = a.ffn_bwd if not a.bf16_ffn else "bf16"
     args.tp_size = world
     args.dp_size = 1
     args.seq_len = SEQ_LEN if a.model != "tiny" else 1024
@@ -232,7 +235,8 @@ def main():
     if rank == 0:
         rec = {"metric": "train tokens/sec (device-timed, max over ranks)", "value": gb_tokens / (ms_step / 1e3),
                "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_step,
-               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (FFN weights NVFP4)"
+               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": ("bf16 (FFN weights NVFP4; FFN GEMMs on the FP4 tensor cores forward"
+                         + (" and backward)" if a.ffn_bwd == "fp4" else ", dX too)" if a.ffn_bwd == "fp4_dx" else ")"))
                if not a.bf16_ffn else "bf16", "data": "synthetic seeded uniform-random tokens, random-init weights",
                "config": {"model": name, "global_batch": args.batch_size, "seq_len": args.seq_len,
                           "parallelism": f"tp{world}+sp", "micro_batch_tokens": a.micro_batch_tokens,

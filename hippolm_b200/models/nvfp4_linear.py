@@ -104,7 +104,7 @@ class NVFP4Linear(nn.Module):
                                                                                    and not x.requires_grad))
         return _NVFP4MatmulSTE.apply(x, self.weight, self.act_quant)
 
-    def accumulate_grad_product(self, dy: torch.Tensor, x: torch.Tensor) -> None:
+    def accumulate_grad_product(self, dy: torch.Tensor, x: torch.Tensor, dy_gs: Optional[torch.Tensor] = None) -> None:
         """grad_w += dy^T x. Once the accumulator exists the GEMM epilogue adds into it directly (no dW temporary,
         no separate add pass); the first micro-batch and the host-offload sink take the materialised product."""
         if self.fp4_backward and self.fp4_backward_dw and self.grad_sink is None and dy.is_cuda \
@@ -112,7 +112,7 @@ class NVFP4Linear(nn.Module):
                 and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0 and dy.stride(1) == 1 and x.stride(1) == 1:
             # dW += Q(dY^T) Q(x^T)^T on the FP4 tensor cores: both operands re-quantised with their blocks along the tokens
             from ..ops import nvfp4_cuda, fp4_gemm
-            ap, asf, ags = nvfp4_cuda.quantize_transposed(dy)
+            ap, asf, ags = nvfp4_cuda.quantize_transposed(dy, dy_gs)   # dy_gs: tensor scale shared with the dX product
             bp, bsf, bgs = nvfp4_cuda.quantize_transposed(x)
             if self.grad_w is None:
                 self.grad_w = fp4_gemm.fp4_matmul_tiled(ap, asf, ags, bp, bsf, bgs)

@@ -393,9 +393,9 @@ def nvfp4_dequantize(packed, scales, global_scale, dtype=torch.float32):
     return nvfp4_cuda.dequantize(packed, scales, global_scale, dtype)
 
 
-def nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant=True):
+def nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant=True, act_gs=None):
     from . import nvfp4_cuda
-    return nvfp4_cuda.gemm_nt(x, packed, scales, global_scale, act_quant)
+    return nvfp4_cuda.gemm_nt(x, packed, scales, global_scale, act_quant, act_gs)
 
 
 # ----------------------------------------------------------------------------- optimizer math

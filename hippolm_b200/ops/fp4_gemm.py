@@ -49,12 +49,13 @@ def supported(M: int, N: int, K: int) -> bool:
     return K % 256 == 0 and N % 8 == 0 and os.environ.get("HIPPO_FP4_GEMM", "1") != "0"
 
 
-def gemm_nt(x, packed, scales, global_scale, act_quant=True):
+def gemm_nt(x, packed, scales, global_scale, act_quant=True, act_gs=None):
+    """``act_gs``: tensor scale of ``x`` when the caller already knows it (saves the absmax pass over ``x``)."""
     from . import cuda_ops, nvfp4_cuda
     M, K = x.shape
     N = packed.shape[0]
     if act_quant and supported(M, N, K):
-        xp, xs, xg = nvfp4_cuda.quantize(x.contiguous())
+        xp, xs, xg = nvfp4_cuda.quantize(x.contiguous(), act_gs)
         return fp4_matmul(xp, xs, xg, packed, scales, global_scale.float().contiguous())
     w = nvfp4_cuda.dequantize(packed, scales, global_scale, torch.bfloat16)
     xq = nvfp4_cuda.dequantize(*nvfp4_cuda.quantize(x), dtype=torch.bfloat16) if act_quant else x

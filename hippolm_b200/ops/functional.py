@@ -175,10 +175,11 @@ def nvfp4_dequantize(packed, scales, global_scale, dtype=torch.float32):
     return _ro.nvfp4_dequantize(packed, scales, global_scale, dtype)
 
 
-def nvfp4_linear(x, packed, scales, global_scale, act_quant: bool = True):
-    """y = Q(x) @ dq(W)^T with block-scaled FP4 operands (fp32 accumulate)."""
+def nvfp4_linear(x, packed, scales, global_scale, act_quant: bool = True, act_gs=None):
+    """y = Q(x) @ dq(W)^T with block-scaled FP4 operands (fp32 accumulate). ``act_gs`` (CUDA): the tensor scale of ``x``
+    if the caller has it already."""
     if x.is_cuda:
-        return _cu().nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant)
+        return _cu().nvfp4_gemm_nt(x, packed, scales, global_scale, act_quant, act_gs)
     w = _ro.nvfp4_dequantize(packed, scales, global_scale, torch.float32)
     xf = x.float()
     if act_quant:

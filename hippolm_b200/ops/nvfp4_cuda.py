@@ -63,7 +63,7 @@ def dequantize(packed, scales, global_scale, dtype=torch.float32):
     return out if od == dtype else out.to(dtype)
 
 
-def gemm_nt(x, packed, scales, global_scale, act_quant=True):
+def gemm_nt(x, packed, scales, global_scale, act_quant=True, act_gs=None):
     """y = Q(x) dq(W)^T."""
     from . import fp4_gemm
-    return fp4_gemm.gemm_nt(x, packed, scales, global_scale, act_quant)
+    return fp4_gemm.gemm_nt(x, packed, scales, global_scale, act_quant, act_gs)

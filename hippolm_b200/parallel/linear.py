@@ -126,6 +126,11 @@ def _fp4_backward(module, dy: torch.Tensor, contraction: int, out: int) -> bool:
             and contraction % 256 == 0 and out % 8 == 0)
 
 
+def _tensor_scale(t: torch.Tensor):
+    from ..ops import nvfp4_cuda
+    return nvfp4_cuda.tensor_scale(t)
+
+
 def _nvfp4_operands(module, weight):
     """(packed, scales, global_scale) of an NVFP4Linear: its buffers (no master) or the freshly quantised master."""
     if module.no_master:
@@ -169,11 +174,13 @@ class _NVFP4ColumnSP(torch.autograd.Function):
         dy = dy.contiguous()
         f = _fused()
         dx = None
+        dy_gs = None
         if _fp4_backward(mod, dy, contraction=dy.shape[1], out=ctx.K):
             # dX = Q(dY) Q(W^T)^T on the FP4 tensor cores (W^T re-encoded along N once per optimizer step)
             pt, st, gt = mod.transposed_operands()
             if m.tp == 1:
-                dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True)
+                dy_gs = _tensor_scale(dy)            # one absmax pass serves the row-wise and the token-wise encoding of dY
+                dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True, act_gs=dy_gs)
             elif f is not None:
                 dx = f.tuned(("fp4_rs", dy.shape[0], dy.shape[1], pt.shape[0]),
                              lambda: f.nvfp4_gemm_reduce_scatter(dy, pt, st, gt),     # None: shape not covered
@@ -201,7 +208,7 @@ class _NVFP4ColumnSP(torch.autograd.Function):
             else:
                 xg = all_gather_dim0(x, m.tp_group, m.tp)
         if mod.no_master:
-            mod.accumulate_grad_product(dy, xg)
+            mod.accumulate_grad_product(dy, xg, dy_gs)
             return dx, None, None
         return dx, ops.gemm_tn(dy, xg).to(mod.weight.dtype), None
 
@@ -235,9 +242,10 @@ class _NVFP4RowSP(torch.autograd.Function):
         f = _fused()
         if m.tp == 1 and _fp4_backward(mod, dy, contraction=dy.shape[1], out=x.shape[1]):
             pt, st, gt = mod.transposed_operands()
-            dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True)             # Q(dY) Q(W^T)^T
+            dy_gs = _tensor_scale(dy)
+            dx = ops.nvfp4_linear(dy, pt, st, gt, act_quant=True, act_gs=dy_gs)   # Q(dY) Q(W^T)^T
             if mod.no_master:
-                mod.accumulate_grad_product(dy, x)
+                mod.accumulate_grad_product(dy, x, dy_gs)
                 return dx, None, None
             return dx, ops.gemm_tn(dy, x).to(mod.weight.dtype), None
         dx = dyg = None

@@ -13,6 +13,25 @@ from hippolm_b200.utils.timing import load_measured_peaks
 SHAPES = [(8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336), (4096, 14336, 16384)]
 
 
+def _cublaslt_nvfp4_tflops(M, N, K, xp, xs, wp, ws):
+    """Throughput of the library's block-scaled FP4 GEMM (``torch._scaled_mm`` on float4_e2m1fn_x2 operands with e4m3
+    scales in the 128x4 tile layout) as a measured FP4 reference; None where this torch build has no such path."""
+    try:
+        from hippolm_b200.ops import fp4_gemm as fg
+        a4 = xp.view(torch.float4_e2m1fn_x2)
+        b4 = wp.view(torch.float4_e2m1fn_x2)
+        sa = fg.tile_scales(xs, M, K).view(torch.float8_e4m3fn)
+        sb = fg.tile_scales(ws, N, K).view(torch.float8_e4m3fn)
+        fn = lambda: torch._scaled_mm(a4, b4.t(), sa, sb, out_dtype=torch.bfloat16)
+        fn()
+        torch.cuda.synchronize()
+        ms = time_ms(fn, flush=False)
+        return round(2.0 * M * N * K / ms / 1e9, 1)
+    except Exception as ex:                                           # noqa: BLE001
+        print(json.dumps({"cublaslt_nvfp4": f"unavailable: {type(ex).__name__}: {str(ex)[:160]}"}), flush=True)
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", type=str, default="", help="M,N,K: run only this shape")
@@ -50,6 +69,11 @@ def main():
             xp, xs, xg = nvfp4_cuda.quantize(a); wp, ws, wg = nvfp4_cuda.quantize(b)
             ms = time_ms(lambda: fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg), flush=False)
             rec["nvfp4_tflops"] = round(fl / ms / 1e9, 1)
+            lib_tf = _cublaslt_nvfp4_tflops(M, N, K, xp, xs, wp, ws)
+            if lib_tf is not None:
+                # measured library FP4 throughput at the same shape: the denominator for the FP4 kernel's fraction
+                rec["cublaslt_nvfp4_tflops"] = lib_tf
+                rec["nvfp4_frac_of_cublaslt"] = round(rec["nvfp4_tflops"] / lib_tf, 3)
         rec["bf16_frac_of_" + pk["source"] + "_peak"] = round(rec["nt_tflops"] / pk["bf16_tflops"], 3)
         print(json.dumps(rec), flush=True)
 

@@ -90,7 +90,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // once every store of a block has completed, the block's arrival counter is released on each peer, so consumers
     // start on the first blocks of a remote shard while the rest is still in flight. Own tiles read x_local in place
     // (tmOwn); a caller that needs the complete gathered buffer afterwards copies its own rows in with a device copy.
-    if (threadIdx.x == 0) ag_copy_role<STAGE_BYTES, BM>(smem, full, cp, p.K, (int)blockIdx.x);
+    if (threadIdx.x == 0) ag_copy_role<STAGE_BYTES, BM, STAGES>(smem, full, cp, p.K, (int)blockIdx.x);
   } else
 
   if (warp == 0) {

@@ -141,7 +141,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   };
 
   if (COMM == COMM_AG && (int)blockIdx.x < cp.comm_ctas) {
-    if (threadIdx.x == 0) ag_copy_role<STAGE_BYTES, BM>(smem, full, cp, p.K, (int)blockIdx.x);
+    if (threadIdx.x == 0) ag_copy_role<STAGE_BYTES, BM, STAGES>(smem, full, cp, p.K, (int)blockIdx.x);
   } else
   if (warp == 0) {
     if (lane == 0) {

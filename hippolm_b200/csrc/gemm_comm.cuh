@@ -51,12 +51,13 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
 
 // ---- all-gather copy role, driven by ONE thread with bulk async copies (TMA): a chunk of the local shard is read into
 // shared memory once and stored from there into the gathered buffer of every peer (7 stores per local read at 8 ranks),
-// through a ring of 4 buffers of STAGE bytes with the loads two chunks ahead of the stores. The shard travels in
+// through a ring of NB buffers of STAGE bytes with the loads two chunks ahead of the stores and up to NB - 2 store groups
+// in flight (the transfer is bound by the number of bytes in flight per copy CTA, not by issue rate). The shard travels in
 // 128-row blocks; once every store of a block has completed, the block's arrival counter is released on each peer, so
 // consumers start on the first blocks of a remote shard while the rest is still in flight. Own tiles read x_local in
 // place; a caller that needs the complete gathered buffer afterwards copies its own rows in with a device copy.
-// `smem`: 4 * STAGE bytes; `full`: 4 mbarriers initialised with count 1; `cta`: index of this copy CTA in [0, comm_ctas).
-template <int STAGE, int BLOCK_ROWS>
+// `smem`: NB * STAGE bytes; `full`: NB mbarriers initialised with count 1; `cta`: index of this copy CTA in [0, comm_ctas).
+template <int STAGE, int BLOCK_ROWS, int NB>
 __device__ __forceinline__ void ag_copy_role(uint8_t* smem, uint64_t* full, const CommParams& cp, int K, int cta) {
   const long long row_bytes = (long long)K * 2;
   const int bps = cp.rows_per_shard / BLOCK_ROWS;                     // 128-row blocks per shard
@@ -74,17 +75,17 @@ __device__ __forceinline__ void ag_copy_role(uint8_t* smem, uint64_t* full, cons
   };
   auto load = [&](int c) {
     int rb, r0; const int nr = chunk_rows(c, rb, r0);
-    uint8_t* buf = smem + (c & 3) * STAGE;
+    uint8_t* buf = smem + (c % NB) * STAGE;
     const uint8_t* src = (const uint8_t*)cp.x_local + ((long long)rb * BLOCK_ROWS + r0) * cp.x_ld * 2;
-    mbar_expect_tx(&full[c & 3], (uint32_t)(nr * row_bytes));
+    mbar_expect_tx(&full[c % NB], (uint32_t)(nr * row_bytes));
     if (contiguous) {
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(smem_u32(buf)), "l"(src), "r"((uint32_t)(nr * row_bytes)), "r"(smem_u32(&full[c & 3])) : "memory");
+                   ::"r"(smem_u32(buf)), "l"(src), "r"((uint32_t)(nr * row_bytes)), "r"(smem_u32(&full[c % NB])) : "memory");
     } else {
       for (int r = 0; r < nr; ++r)
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                      ::"r"(smem_u32(buf + r * row_bytes)), "l"(src + (long long)r * cp.x_ld * 2), "r"((uint32_t)row_bytes),
-                       "r"(smem_u32(&full[c & 3])) : "memory");
+                       "r"(smem_u32(&full[c % NB])) : "memory");
     }
   };
   auto release_block = [&](int rb) {
@@ -98,12 +99,13 @@ __device__ __forceinline__ void ag_copy_role(uint8_t* smem, uint64_t* full, cons
   if (ok && total > 0) { load(0); if (total > 1) load(1); }
   int released = 0;                                                   // chunks whose blocks have been released so far
   for (int c = 0; ok && c < total; ++c) {
-    // stores of chunks <= c - 2 are complete (wait at the end of the previous iteration): their buffers are free
+    // stores of chunks <= c + 2 - NB are complete (wait at the end of the previous iteration): the buffer of chunk c + 2,
+    // last used by chunk c + 2 - NB, is free
     if (c + 2 < total) load(c + 2);
-    ok = mbar_wait(&full[c & 3], (c >> 2) & 1, kWaitTmaFull, c);
+    ok = mbar_wait(&full[c % NB], (c / NB) & 1, kWaitTmaFull, c);
     if (!ok) break;
     int rb, r0; const int nr = chunk_rows(c, rb, r0);
-    const uint8_t* buf = smem + (c & 3) * STAGE;
+    const uint8_t* buf = smem + (c % NB) * STAGE;
     const long long off = ((long long)cp.rank * cp.rows_per_shard + (long long)rb * BLOCK_ROWS + r0) * row_bytes;
     for (int i = 1; i < cp.world; ++i) {
       const int peer = (cp.rank + i) % cp.world;
@@ -111,9 +113,9 @@ __device__ __forceinline__ void ag_copy_role(uint8_t* smem, uint64_t* full, cons
                    ::"l"((uint8_t*)cp.buf_peer[peer] + off), "r"(smem_u32(buf)), "r"((uint32_t)(nr * row_bytes)) : "memory");
     }
     tma_store_commit();
-    tma_store_wait<1>();                                              // everything but the newest group has completed
-    // chunks 0 .. c-1 are complete: release every block that ends inside them
-    while (released + cpb <= c) { release_block(cta + (released / cpb) * cp.comm_ctas); released += cpb; }
+    tma_store_wait<NB - 3>();                                         // all but the newest NB - 3 groups have completed
+    // chunks 0 .. c - (NB - 3) are complete: release every block that ends inside them
+    while (released + cpb <= c + 1 - (NB - 3)) { release_block(cta + (released / cpb) * cp.comm_ctas); released += cpb; }
   }
   tma_store_wait<0>();
   if (ok) while (released < total) { release_block(cta + (released / cpb) * cp.comm_ctas); released += cpb; }

@@ -187,7 +187,12 @@ def run_train(a) -> int:
         except Exception:                                             # noqa: BLE001
             return None
 
-    port = int(os.environ.get("MASTER_PORT", "29500")) + 37
+    # The reference rendezvous is env:// on a port of its own, with rank 0 hosting the store (what its mp.spawn launch
+    # gives it). Under torch.distributed.run the launcher's agent already hosts a store on MASTER_PORT and every
+    # worker is a client of it (TORCHELASTIC_USE_AGENT_STORE): hand the reference that port, a private one otherwise.
+    port = int(os.environ.get("MASTER_PORT", "29500"))
+    if os.environ.get("TORCHELASTIC_USE_AGENT_STORE") != "True":
+        port += 37
     try:
         ctx = _setup_worker(rank, args, list(range(world)), port, run_dir, None)
         timed = _TimedLoader(ctx["dataloader"], a.warmup, a.steps, args, a.ref_budget_s, sampler_factory, t_start)

@@ -67,8 +67,15 @@ def main():
             rec[name + "_tflops"] = round(fl / ms / 1e9, 1)
         if K % 256 == 0:
             xp, xs, xg = nvfp4_cuda.quantize(a); wp, ws, wg = nvfp4_cuda.quantize(b)
-            ms = time_ms(lambda: fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg), flush=False)
+            sfa, sfb = fp4_gemm.tile_scales(xs, M, K), fp4_gemm.tile_scales(ws, N, K)
+            ms = time_ms(lambda: fp4_gemm.fp4_matmul_tiled(xp, sfa, xg, wp, sfb, wg), flush=False)
             rec["nvfp4_tflops"] = round(fl / ms / 1e9, 1)
+            if M >= 256 and N >= 256:
+                try:                                                  # CTA-pair kernel (256x256 tiles)
+                    ms = time_ms(lambda: fp4_gemm.fp4_matmul_pair(xp, sfa, xg, wp, sfb, wg), flush=False)
+                    rec["nvfp4_pair_tflops"] = round(fl / ms / 1e9, 1)
+                except RuntimeError as ex:
+                    rec["nvfp4_pair"] = f"failed: {str(ex)[:120]}"
             lib_tf = _cublaslt_nvfp4_tflops(M, N, K, xp, xs, wp, ws)
             if lib_tf is not None:
                 # measured library FP4 throughput at the same shape: the denominator for the FP4 kernel's fraction

@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
+#include <stdlib.h>
 
 namespace hippo {
 
@@ -494,11 +495,27 @@ extern "C" int hippo_nvfp4_tile_scales(const void* sf, void* out, long long rows
   return (int)cudaGetLastError();
 }
 
+extern "C" int hippo_gemm_nvfp4_pair(const void* A, const void* B, const void* sfa, const void* sfb, const float* gsa,
+                                     const float* gsb, void* C, int M, int N, int K, long long ldc, int accumulate,
+                                     void* stream);
+
+// HIPPO_FP4_PAIR=1 routes products with at least 256 rows and columns to the CTA-pair kernel of gemm_fp4_2sm.cu.
+static int fp4_pair_mode() {
+  static int mode = -1;
+  if (mode < 0) { const char* e = getenv("HIPPO_FP4_PAIR"); mode = e ? atoi(e) : 0; }
+  return mode;
+}
+
 // A: [M, K/2] packed fp4 bytes, B: [N, K/2]; sfa/sfb: tiled scales (hippo_nvfp4_tile_scales); gsa/gsb: device fp32[1].
 extern "C" int hippo_gemm_nvfp4(const void* A, const void* B, const void* sfa, const void* sfb, const float* gsa,
                                 const float* gsb, void* C, int M, int N, int K, long long ldc, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 256 || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15) || (ldc % 8)) return -2;
+  if (fp4_pair_mode() && M >= 256 && N >= 256) {
+    const int acc = g_fp4_accumulate;
+    g_fp4_accumulate = 0;
+    return hippo_gemm_nvfp4_pair(A, B, sfa, sfb, gsa, gsb, C, M, N, K, ldc, acc, stream);
+  }
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, F_BKB, F_BM, 1, true);
   if (rc) return rc;

@@ -1,0 +1,289 @@
+// CTA-pair NVFP4 GEMM:  C[M,N] (+)= (A_fp4 * sfA) (B_fp4 * sfB)^T * gsA * gsB  on a 256 x 256 tile shared by two CTAs.
+//
+//   tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X, MMA shape 256 x 256 x 64
+//
+// The one-CTA 128x128 kernel of gemm_fp4.cu asks L2 for 36 KB of operands and scales per 128x128x256 slab, four times
+// what a bf16 tile of the same shape needs per tensor-pipe cycle, and runs at the rate L2 can feed the SMs (2.1
+// PFLOP/s). Here each CTA of the pair stages its own 128 rows of A, HALF of the 256 B rows, the scale tiles of its A
+// rows and the scale tiles of all 256 B rows: 38 KB per 128x256x256 slab, i.e. half the bytes per flop.
+//
+// TMEM holds 512 columns: a 128 x 256 fp32 accumulator takes 256, the scale factors of the stages in flight take
+// the rest (4 columns per 128-row tile and MMA: 16 for A, 32 for B per stage), so there is ONE accumulator. The
+// epilogue therefore drains it into shared memory first (bf16, 64 KB per CTA), hands TMEM back to the MMA issuer, and
+// only then writes (or adds into) global memory while the next tile's MMAs run.
+//
+// Per CTA (192 threads): warp 0 = TMA producer (all five loads of a stage are tiled TMA loads of local memory whose
+// completion bytes land on the LEADER's barrier; the scale arrays are addressed as [tile * K/64 + k][128 x u32]
+// tensors), warp 1 = MMA issuer (leader only: tcgen05.cp of the scale tiles into both CTAs' TMEM, then the MMAs) and
+// TMEM owner, warps 2..5 = epilogue of the CTA's own 128 rows. Stage release and accumulator hand-over as in the bf16
+// pair kernel: two plain commits (own barrier, peer barrier), remote mbarrier arrives; no cluster-multicast qualifier.
+// Every wait is bounded. Replaces the reference's Marlin W4A16 path like the one-CTA kernel.
+#include "sm100.cuh"
+#include "host_utils.h"
+#include "cta_pair.cuh"
+#include <cuda_bf16.h>
+#include <stdlib.h>
+
+namespace hippo {
+namespace f2 {
+
+constexpr int BM = 128;                 // rows per CTA; the pair covers 256
+constexpr int BN = 256, BNH = 128;      // columns of the pair tile / B rows staged by each CTA
+constexpr int BKB = 128;                // K slab: 128 bytes = 256 fp4 elements = 4 MMAs
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BKB, B_BYTES = BNH * BKB, SFA_BYTES = 4 * 512, SFB_BYTES = 2 * 4 * 512;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;          // 38 KB
+constexpr int EPI_BYTES = 4 * 32 * 512;                                         // 4 warps x [32 rows][512 B]
+constexpr int THREADS = 192;
+constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+constexpr int TMEM_SF0 = 256;           // the accumulator uses columns [0, 256); 48 scale columns per stage follow
+static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned (128-byte swizzle)");
+static_assert(TMEM_SF0 + STAGES * 48 <= 512, "scale-factor columns must fit behind the accumulator");
+static_assert(SMEM <= 227 * 1024, "shared memory of one CTA");
+
+struct PairParams {
+  int M, N, K;                          // K in elements (multiple of 256)
+  const float* gsa; const float* gsb;
+  __nv_bfloat16* C; long long ldc;
+  int accumulate;                       // C += result (weight-gradient products)
+  int tiles_m, tiles_n;                 // pair tiles
+};
+
+__device__ __forceinline__ void mma_nvf4_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+      : "memory");
+}
+// shared memory -> TMEM copy of one 512-byte scale tile in BOTH CTAs of the pair (each from its own shared memory at
+// the same offset into its own TMEM), replicated to the four 32-lane groups
+__device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                      const __grid_constant__ PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(epi_stage + EPI_BYTES);         // used in the leader only
+  uint64_t* empty = full + STAGES;                             // one set per CTA
+  uint64_t* tfull = empty + STAGES;                            // one per CTA
+  uint64_t* tempty = tfull + 1;                                // used in the leader only (8 arrivals)
+  uint32_t* tmem_slot = (uint32_t*)(tempty + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = p.K / 256;
+  const int k64 = p.K / 64;
+  const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(tfull, 1); mbar_init(tempty, 8);
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmSFA); prefetch_tmap(&tmSFB);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                     // both CTAs' barriers are initialised before any remote arrive
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int GROUP = 8;                  // 8 pair tiles (2048 rows) share each column sweep
+    int per_group = GROUP * p.tiles_n;
+    int g = t / per_group, r = t % per_group;
+    int gm = min(GROUP, p.tiles_m - g * GROUP);
+    tm = g * GROUP + r % gm;
+    tn = r / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = cid; t < num_tiles && ok; t += n_clusters) {
+        int tm, tn; tile_coord(t, tm, tn);
+        const int rb = tm * 2 + (int)rank;                     // this CTA's 128-row block of A
+        const int cb = tn * 2 + (int)rank;                     // this CTA's 128-row block of B
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, kWaitSmemEmpty, it);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          uint8_t* sa = smem + s * STAGE_BYTES; uint8_t* sb = sa + A_BYTES;
+          uint8_t* ssa = sb + B_BYTES; uint8_t* ssb = ssa + SFA_BYTES;
+          tma_load_2d_pair(sa, &tmA, bar, kb * BKB, rb * BM);
+          tma_load_2d_pair(sb, &tmB, bar, kb * BKB, cb * BNH);
+          tma_load_2d_pair(ssa, &tmSFA, bar, 0, rb * k64 + kb * 4);
+          tma_load_2d_pair(ssb, &tmSFB, bar, 0, (tn * 2) * k64 + kb * 4);              // scales of B rows 0..127
+          tma_load_2d_pair(ssb + 4 * 512, &tmSFB, bar, 0, (tn * 2 + 1) * k64 + kb * 4);  // and of rows 128..255
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_nvf4(2 * BM, BN);
+      int it = 0, tl = 0;
+      bool ok = true;
+      for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
+        ok = mbar_wait(tempty, (tl & 1) ^ 1, kWaitTmemEmpty, tl);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+          const uint32_t ssa = sb + B_BYTES, ssb = ssa + SFA_BYTES;
+          const uint32_t t_sfa = tmem_base + TMEM_SF0 + s * 48, t_sfb = t_sfa + 16;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // a scale tile is 32 rows x 16 bytes, rows contiguous: 8-row groups 128 bytes apart, no swizzle
+            tc_cp_32x128b_warpx4_pair(t_sfa + k * 4, make_smem_desc_noswizzle(ssa + k * 512, 16, 128));
+            tc_cp_32x128b_warpx4_pair(t_sfb + k * 8, make_smem_desc_noswizzle(ssb + k * 512, 16, 128));
+            tc_cp_32x128b_warpx4_pair(t_sfb + k * 8 + 4, make_smem_desc_noswizzle(ssb + (4 + k) * 512, 16, 128));
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024);
+            uint64_t bd = make_smem_desc(sb + k * 32, 16, 1024);
+            mma_nvf4_ss_pair(tmem_base, ad, bd, idesc, t_sfa + k * 4, t_sfb + k * 8, (kb | k) ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&empty[s]);
+          tc_commit_pair(e);                                    // stage free in this CTA ...
+          tc_commit_pair(map_to_cta(e, 1));                     // ... and in the peer
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(tfull);
+          tc_commit_pair(f);
+          tc_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 512);            // [32 rows][32 x 16 B], private to the warp
+    const float alpha = (*p.gsa) * (*p.gsb);
+    int tl = 0;
+    bool ok = true;
+    for (int t = cid; t < num_tiles && ok; t += n_clusters, ++tl) {
+      int tm, tn; tile_coord(t, tm, tn);
+      ok = mbar_wait(tfull, tl & 1, kWaitTmemFull, tl);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 v;
+          __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * alpha, __uint_as_float(r[j + 2 * e + 1]) * alpha);
+          const int piece = (c + j) / 8;                                   // 16-byte piece within the row
+          slab[lane * 32 + (piece ^ lane)] = v;                            // xor swizzle: conflict-free both ways
+        }
+      }
+      // the accumulator is in shared memory now: hand TMEM back to the leader before touching global memory
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tempty), 0));
+      const int row_base = (tm * 2 + (int)rank) * BM + q * 32;
+      const int ncols = min(BN, p.N - tn * BN);                            // multiple of 8
+      __nv_bfloat16* dst0 = p.C + (long long)row_base * p.ldc + tn * BN + lane * 8;
+      if (lane * 8 < ncols) {
+#pragma unroll 1
+        for (int r0 = 0; r0 < 32; r0 += 4) {
+          uint4 old[4];
+          if (p.accumulate) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)                                    // four loads in flight
+              if (row_base + r0 + j < p.M) old[j] = *(const uint4*)(dst0 + (long long)(r0 + j) * p.ldc);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int rr = r0 + j;
+            if (row_base + rr >= p.M) continue;
+            uint4 v = slab[rr * 32 + (lane ^ rr)];
+            if (p.accumulate) {
+              __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+              const __nv_bfloat162* ob = (const __nv_bfloat162*)&old[j];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(vb[e]), o = __bfloat1622float2(ob[e]);
+                vb[e] = __floats2bfloat162_rn(a.x + o.x, a.y + o.y);
+              }
+            }
+            *(uint4*)(dst0 + (long long)rr * p.ldc) = v;
+          }
+        }
+      }
+      __syncwarp();                                                        // the slab is free for the next tile
+    }
+  }
+  // Neither CTA may leave (or free its TMEM) while the other can still read its shared memory or signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace f2
+}  // namespace hippo
+
+using namespace hippo;
+
+// A: [M, K/2] packed fp4 bytes, B: [N, K/2]; sfa / sfb: scale tiles [ceil(rows/128)][K/64][512]; gsa / gsb: device
+// fp32[1]; C: bf16 [M, ldc]. accumulate != 0 adds into C. Returns -3 for shapes the pair kernel does not take
+// (fewer than 256 rows or columns): the caller falls back to the one-CTA kernel.
+extern "C" int hippo_gemm_nvfp4_pair(const void* A, const void* B, const void* sfa, const void* sfb, const float* gsa,
+                                     const float* gsb, void* C, int M, int N, int K, long long ldc, int accumulate,
+                                     void* stream) {
+  using namespace f2;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 256 || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15) || (ldc % 8) ||
+      ((uintptr_t)sfa & 15) || ((uintptr_t)sfb & 15)) return -2;
+  if (M < 2 * BM || N < BN) return -3;
+  const int k64 = K / 64;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  int rc = make_tmap_2d(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, BKB, BM, 1, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BKB, BNH, 1, true);
+  if (rc) return rc;
+  // scale arrays as [tile * K/64 + k][128 x 4-byte words]; one load = the four k-groups of a K slab (2 KB, contiguous)
+  rc = make_tmap_2d(&tmSFA, sfa, 128, (uint64_t)((M + 127) / 128) * k64, 512, 128, 4, 4, false);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmSFB, sfb, 128, (uint64_t)((N + 127) / 128) * k64, 512, 128, 4, 4, false);
+  if (rc) return rc;
+  PairParams p;
+  p.M = M; p.N = N; p.K = K; p.gsa = gsa; p.gsb = gsb; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.accumulate = accumulate;
+  p.tiles_m = (M + 2 * BM - 1) / (2 * BM); p.tiles_n = (N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  int clusters = sm_count() / 2;
+  if (clusters < 1) clusters = 1;
+  if (tiles < clusters) clusters = tiles;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  gemm_nvfp4_2sm_kernel<<<2 * clusters, THREADS, SMEM, (cudaStream_t)stream>>>(tmA, tmB, tmSFA, tmSFB, p);
+  return (int)cudaGetLastError();
+}

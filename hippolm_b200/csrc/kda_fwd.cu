@@ -20,8 +20,16 @@
 namespace hippo {
 using namespace nvcuda;
 
+// Bytes of the intra kernel's work region: phase 2 holds two 48-row operand tiles and a 16-row column tile there,
+// phases 3-4 the fp32 inverse (pitch 68), three 16x16 fp32 temporaries and the bf16 copy of the inverse (pitch 72).
 template <int DK>
-__global__ void __launch_bounds__(512, 1)
+__host__ __device__ constexpr int kda_intra_work_bytes() {
+  constexpr int tiles = (2 * 48 + 16) * (DK + 8) * 2, inv = (64 * 68 + 3 * 256) * 4 + 64 * 72 * 2;
+  return tiles > inv ? tiles : inv;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(512, 2)
 kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                      const float* __restrict__ g, const float* __restrict__ beta,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
@@ -29,22 +37,26 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
                      bf16* __restrict__ qg_out, bf16* __restrict__ kg_out, bf16* __restrict__ Aqk_out,
                      bf16* __restrict__ Ainv_out, bf16* __restrict__ Akk_out) {
   constexpr int LD = DK + 8;       // bf16 tile pitch
-  constexpr int LA = 68;           // fp32 64x64 pitch
-  constexpr int LG = DK + 4;       // fp32 G pitch (rows land on different banks)
+  constexpr int LA = 68;           // fp32 pitch of the inverse X
+  constexpr int LK = 64;           // fp32 pitch of kk / Akk
+  constexpr int LG = DK + 4;       // fp32 G pitch (rows land on different banks); pad column DK holds beta
+  // 113 KB at DK = 128, so that two CTAs share an SM: the chain of block-wide phases of one chunk is latency-bound
+  // and the second CTA fills its barrier stalls.
   extern __shared__ __align__(128) uint8_t smem[];
   float* Gs = (float*)smem;                       // [64][LG]
-  bf16* qs = (bf16*)(Gs + 64 * LG);               // [64][LD]
-  bf16* ks = qs + 64 * LD;                        // [64][LD]
-  bf16* T1 = ks + 64 * LD;                        // [64][LD] work tile (row side q / beta*k*e^G)
-  bf16* T2 = T1 + 64 * LD;                        // [64][LD] work tile (row side k / beta*v)
-  bf16* Ck = T2 + 64 * LD;                        // [16][LD] column side
-  float* kk = (float*)(Ck + 16 * LD);             // [64][LA]
-  float* bs = kk + 64 * LA;                       // [64]
-  bf16* Xb = (bf16*)(bs + 64);                    // [64][72]
-  // the inverse (phase 3) reuses the work-tile region, which is idle between phases 2 and 4
-  float* X = (float*)T1;                          // [64][LA]
+  bf16* qs = (bf16*)(Gs + 64 * LG);               // [64][LD] q; phase 4 overwrites it in place with beta*v
+  bf16* ks = qs + 64 * LD;                        // [64][LD] k; phase 4 overwrites it in place with beta*k*e^G
+  uint8_t* work = (uint8_t*)(ks + 64 * LD);       // kda_intra_work_bytes<DK>()
+  bf16* T1 = (bf16*)work;                         // [48][LD] phase 2 row side q * decay
+  bf16* T2 = T1 + 48 * LD;                        // [48][LD] phase 2 row side k * decay
+  bf16* Ck = T2 + 48 * LD;                        // [16][LD] phase 2 column side
+  // phases 3 and 4 reuse the work region, which is idle after phase 2
+  float* X = (float*)work;                        // [64][LA]
   float* Tm = X + 64 * LA;                        // [3][16][16]
-  static_assert((2 * 64 + 16) * LD * 2 >= (64 * LA + 3 * 256) * 4, "inverse scratch must fit in the work tiles");
+  bf16* Xb = (bf16*)(Tm + 3 * 256);               // [64][72]
+  constexpr int WORK = kda_intra_work_bytes<DK>();
+  float* kk = (float*)(work + WORK);              // [64][LK]
+  float* bs = Gs + DK;                            // beta of row i at bs[i * LG]
 
   constexpr int NTHR = 512, NWARP = 16;
   const int chunk = blockIdx.x, h = blockIdx.y;
@@ -63,8 +75,8 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     }
     *(uint4*)(qs + r * LD + c8) = zq; *(uint4*)(ks + r * LD + c8) = zk;
   }
-  for (int idx = tid; idx < 64 * LA; idx += NTHR) kk[idx] = 0.f;
-  if (tid < 64) bs[tid] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f;
+  for (int idx = tid; idx < 64 * LK; idx += NTHR) kk[idx] = 0.f;
+  if (tid < 64) bs[tid * LG] = tid < len ? beta[(long long)(t0 + tid) * H + h] : 0.f;
   if (tid < DK) {
     float run = 0.f;
 #pragma unroll 8
@@ -108,7 +120,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 1); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 1);
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 2); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 2);
       skk += __shfl_xor_sync(0xFFFFFFFFu, skk, 4); sqk += __shfl_xor_sync(0xFFFFFFFFu, sqk, 4);
-      if (gl == 0 && valid) { if (jj < ii) kk[i * LA + j] = skk; Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(sqk); }
+      if (gl == 0 && valid) { if (jj < ii) kk[i * LK + j] = skk; Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(sqk); }
     }
   }
 
@@ -146,7 +158,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int i = r0 + rt * 16 + g + hh * 8, j = 16 * J + n * 8 + 2 * t4;
-          if (which) *(float2*)(kk + i * LA + j) = make_float2(acc[n][2 * hh], acc[n][2 * hh + 1]);
+          if (which) *(float2*)(kk + i * LK + j) = make_float2(acc[n][2 * hh], acc[n][2 * hh + 1]);
           else *(unsigned*)(Aqk_out + (cbase + i) * 64 + j) = kda_pack2(acc[n][2 * hh], acc[n][2 * hh + 1]);
         }
     }
@@ -156,7 +168,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
   // ---- phase 3: X = (I + beta*kk)^-1, blocked forward substitution in fp32
   for (int idx = tid; idx < 64 * 64; idx += NTHR) {
     int i = idx >> 6, j = idx & 63;
-    kk[i * LA + j] = j < i ? kk[i * LA + j] * bs[i] : 0.f;      // kk now holds Akk
+    kk[i * LK + j] = j < i ? kk[i * LK + j] * bs[i * LG] : 0.f;      // kk now holds Akk
     X[i * LA + j] = 0.f;
   }
   __syncthreads();
@@ -168,7 +180,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       float s = (r == col) ? 1.f : 0.f;
 #pragma unroll
       for (int m = 0; m < 16; ++m)
-        if (m < r) s -= kk[(b * 16 + r) * LA + b * 16 + m] * x[m];
+        if (m < r) s -= kk[(b * 16 + r) * LK + b * 16 + m] * x[m];
       x[r] = s;
     }
 #pragma unroll
@@ -184,7 +196,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
         float s = 0.f;
         for (int L = J; L < I; ++L)
 #pragma unroll
-          for (int m = 0; m < 16; ++m) s += kk[(I * 16 + r) * LA + L * 16 + m] * X[(L * 16 + m) * LA + J * 16 + c];
+          for (int m = 0; m < 16; ++m) s += kk[(I * 16 + r) * LK + L * 16 + m] * X[(L * 16 + m) * LA + J * 16 + c];
         Tm[J * 256 + r * 16 + c] = s;
       }
       __syncthreads();
@@ -199,16 +211,16 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     }
   }
 
-  // ---- phase 4: operands + outputs
+  // ---- phase 4: operands + outputs. The B operands of the two products overwrite k and q in place (every element is
+  // read and written by the same thread), so no barrier separates the two loops.
   for (int idx = tid; idx < 64 * 64; idx += NTHR) {
     int i = idx >> 6, j = idx & 63;
     bf16 xv = __float2bfloat16(X[i * LA + j]);
     Xb[i * 72 + j] = xv;
     Ainv_out[(cbase + i) * 64 + j] = xv;
-    Akk_out[(cbase + i) * 64 + j] = __float2bfloat16(kk[i * LA + j]);
+    Akk_out[(cbase + i) * 64 + j] = __float2bfloat16(kk[i * LK + j]);
     if (j > i) Aqk_out[(cbase + i) * 64 + j] = __float2bfloat16(0.f);
   }
-  __syncthreads();                                    // X (aliased on the work tiles) is consumed
   for (int idx = tid; idx < 64 * (DK / 8); idx += NTHR) {
     const int i = idx / (DK / 8), c8 = (idx % (DK / 8)) * 8;
     uint4 vq = make_uint4(0, 0, 0, 0);
@@ -218,7 +230,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     const __nv_bfloat162* vb = (const __nv_bfloat162*)&vq;
     uint4 o1, o2, oq, ok;
     unsigned* w1 = (unsigned*)&o1; unsigned* w2 = (unsigned*)&o2; unsigned* wq = (unsigned*)&oq; unsigned* wk = (unsigned*)&ok;
-    const float b = bs[i];
+    const float b = bs[i * LG];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int c = c8 + 2 * e;
@@ -230,8 +242,8 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
       wq[e] = kda_pack2(qf.x * e0, qf.y * e1);
       wk[e] = kda_pack2(kf.x * __expf(Gs[63 * LG + c] - G0), kf.y * __expf(Gs[63 * LG + c + 1] - G1));
     }
-    *(uint4*)(T1 + i * LD + c8) = o1;
-    *(uint4*)(T2 + i * LD + c8) = o2;
+    *(uint4*)(ks + i * LD + c8) = o1;
+    *(uint4*)(qs + i * LD + c8) = o2;
     *(uint4*)(qg_out + (cbase + i) * DK + c8) = oq;
     *(uint4*)(kg_out + (cbase + i) * DK + c8) = ok;
   }
@@ -240,7 +252,7 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
     // w = X (beta k e^G), u = X (beta v): warp (which, rt, column half) owns a 16-row x (DK/2)-column slab
     static_assert(NWARP == 16, "slab assignment below assumes 16 warps");
     const int which = warp >> 3, rt = (warp >> 1) & 3, ch = warp & 1;
-    const bf16* B = which ? T2 : T1;
+    const bf16* B = which ? qs : ks;
     bf16* out = which ? u_out : w_out;
     const int g = lane >> 2, t4 = lane & 3;
     constexpr int NP = DK / 32;                       // pairs of n-tiles in half of the columns
@@ -269,9 +281,9 @@ kda_fwd_intra_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, con
 
 template <int DK>
 constexpr int kda_intra_smem() {
-  return 64 * (DK + 4) * 4 + 4 * 64 * (DK + 8) * 2 + 16 * (DK + 8) * 2 + 64 * 68 * 4 + 64 * 4 +
-         64 * 72 * 2 + 128;
+  return 64 * (DK + 4) * 4 + 2 * 64 * (DK + 8) * 2 + kda_intra_work_bytes<DK>() + 64 * 64 * 4;
 }
+static_assert(2 * (kda_intra_smem<128>() + 1024) <= 228 * 1024, "two CTAs of the intra kernel must fit one SM");
 
 // ---------------------------------------------------------------------------------------------------
 // 256 threads, one CTA per SM. The tiles of chunk n+1 stream into the second shared-memory buffer with cp.async

@@ -585,11 +585,161 @@ __global__ void short_conv_bwd_kernel(const bf16* __restrict__ x, long long ldx,
   }
   for (int i = 0; i < W; ++i) atomicAdd(&dw[d * W + i], dwacc[i]);
 }
+
+// Vectorised variants (D % 8 == 0, 16-byte aligned rows): a thread owns 8 channels and a run of `tt` tokens and slides
+// a W-row window over them in registers, so every x / dy element is read once and every y / dx element written once
+// with 16-byte accesses (the scalar kernels above re-read each x element W (forward) or ~W*W (backward) times through
+// the cache with 2-byte accesses). A block is 32 channel groups x 8 token runs; the weight-gradient partial sums of the
+// 8 runs are added in shared memory before one atomicAdd per (channel, tap) and block.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 t = __bfloat1622float2(h[e]); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+  return v;
+}
+
+template <int W>
+__global__ void __launch_bounds__(256)
+short_conv_fwd_vec_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                          const int* __restrict__ pos, bf16* __restrict__ y, long long T, int D, int tt) {
+  const int cg = blockIdx.x * 32 + (threadIdx.x & 31);
+  const long long t_lo = ((long long)blockIdx.y * 8 + (threadIdx.x >> 5)) * tt;
+  if (cg * 8 >= D || t_lo >= T) return;
+  const long long t_hi = t_lo + tt < T ? t_lo + tt : T;
+  float wv[W][8], win[W][8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+#pragma unroll
+    for (int wi = 0; wi < W; ++wi) { wv[wi][c] = __bfloat162float(w[(cg * 8 + c) * W + wi]); win[wi][c] = 0.f; }
+  for (long long t = t_lo - (W - 1); t < t_hi; ++t) {
+#pragma unroll
+    for (int wi = 0; wi + 1 < W; ++wi)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) win[wi][c] = win[wi + 1][c];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t >= 0) v = *(const uint4*)(x + t * ldx + cg * 8);
+    unpack8(v, win[W - 1]);
+    if (t < t_lo) continue;
+    const int p = pos[t];
+    float o[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float acc = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < W; ++wi) if (p >= W - 1 - wi) acc += wv[wi][c] * win[wi][c];
+      o[c] = acc * sigmoidf_(acc);
+    }
+    *(uint4*)(y + t * D + cg * 8) = pack8(o);
+  }
+}
+
+template <int W>
+__global__ void __launch_bounds__(256)
+short_conv_bwd_vec_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                          const int* __restrict__ pos, const bf16* __restrict__ dy, bf16* __restrict__ dx,
+                          long long lddx, float* __restrict__ dw, long long T, int D, int tt) {
+  __shared__ float red[8][W * 8][33];                       // [token run][tap, channel][channel group]
+  const int lane = threadIdx.x & 31, run = threadIdx.x >> 5;
+  const int cg = blockIdx.x * 32 + lane;
+  const long long t_lo = ((long long)blockIdx.y * 8 + run) * tt;
+  const bool active = cg * 8 < D && t_lo < T;
+  float dwacc[W][8];
+#pragma unroll
+  for (int wi = 0; wi < W; ++wi)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) dwacc[wi][c] = 0.f;
+  if (active) {
+    const long long t_hi = t_lo + tt < T ? t_lo + tt : T;
+    float wv[W][8], xw[W][8], dpw[W][8];
+    int pw[W];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int wi = 0; wi < W; ++wi) {
+        wv[wi][c] = __bfloat162float(w[(cg * 8 + c) * W + wi]); xw[wi][c] = 0.f; dpw[wi][c] = 0.f;
+      }
+#pragma unroll
+    for (int wi = 0; wi < W; ++wi) pw[wi] = 0;
+    // window index i holds token t - (W-1) + i; dx of token t - (W-1) is complete once dpre[t] is known
+    for (long long t = t_lo - (W - 1); t < t_hi + (W - 1); ++t) {
+#pragma unroll
+      for (int wi = 0; wi + 1 < W; ++wi) {
+        pw[wi] = pw[wi + 1];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { xw[wi][c] = xw[wi + 1][c]; dpw[wi][c] = dpw[wi + 1][c]; }
+      }
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t >= 0 && t < T) v = *(const uint4*)(x + t * ldx + cg * 8);
+      unpack8(v, xw[W - 1]);
+      pw[W - 1] = 0;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) dpw[W - 1][c] = 0.f;
+      if (t >= t_lo && t < T) {
+        const int p = pos[t];
+        pw[W - 1] = p;
+        float g[8];
+        unpack8(*(const uint4*)(dy + t * D + cg * 8), g);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float pre = 0.f;
+#pragma unroll
+          for (int wi = 0; wi < W; ++wi) if (p >= W - 1 - wi) pre += wv[wi][c] * xw[wi][c];
+          const float sg = sigmoidf_(pre);
+          const float dp = g[c] * sg * (1.f + pre * (1.f - sg));
+          dpw[W - 1][c] = dp;
+          if (t < t_hi) {                                    // tokens past the run belong to the next run's weight gradient
+#pragma unroll
+            for (int wi = 0; wi < W; ++wi) if (p >= W - 1 - wi) dwacc[wi][c] += dp * xw[wi][c];
+          }
+        }
+      }
+      const long long td = t - (W - 1);
+      if (td >= t_lo && td < t_hi) {
+        float o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float acc = 0.f;
+#pragma unroll
+          for (int sh = 0; sh < W; ++sh) if (pw[sh] >= sh) acc += wv[W - 1 - sh][c] * dpw[sh][c];
+          o[c] = acc;
+        }
+        *(uint4*)(dx + td * lddx + cg * 8) = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int wi = 0; wi < W; ++wi)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) red[run][wi * 8 + c][lane] = dwacc[wi][c];
+  __syncthreads();
+  for (int i = threadIdx.x; i < W * 8 * 32; i += 256) {
+    const int e = i >> 5, l = i & 31;                        // e = tap * 8 + channel
+    const int d = (blockIdx.x * 32 + l) * 8 + (e & 7);
+    if (d >= D) continue;
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) sum += red[r][e][l];
+    atomicAdd(&dw[d * W + (e >> 3)], sum);
+  }
+}
 }  // namespace hippo
 
 extern "C" int hippo_short_conv_fwd(const void* x, long long ldx, const void* w, const int* pos, void* y, long long T,
                                     int D, int W, void* s) {
   if (W > 8) return -1;
+  if (T <= 0 || D <= 0) return 0;
+  if (W == 4 && D % 8 == 0 && ldx % 8 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)y & 15)) {
+    const int tt = 32;
+    dim3 grid((D / 8 + 31) / 32, (unsigned)((T + 8 * tt - 1) / (8 * tt)));
+    hippo::short_conv_fwd_vec_kernel<4><<<grid, 256, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (bf16*)y, T, D, tt);
+    RET();
+  }
   long long n = T * D;
   hippo::short_conv_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (bf16*)y, T, D, W);
   RET();
@@ -597,6 +747,15 @@ extern "C" int hippo_short_conv_fwd(const void* x, long long ldx, const void* w,
 extern "C" int hippo_short_conv_bwd(const void* x, long long ldx, const void* w, const int* pos, const void* dy, void* dx,
                                     long long lddx, float* dw, long long T, int D, int W, void* s) {
   if (W > 8) return -1;
+  if (T <= 0 || D <= 0) return 0;
+  if (W == 4 && D % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)dy & 15) &&
+      !((uintptr_t)dx & 15)) {
+    const int tt = 32;
+    dim3 grid((D / 8 + 31) / 32, (unsigned)((T + 8 * tt - 1) / (8 * tt)));
+    hippo::short_conv_bwd_vec_kernel<4><<<grid, 256, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (const bf16*)dy,
+                                                                 (bf16*)dx, lddx, dw, T, D, tt);
+    RET();
+  }
   dim3 grid((D + 127) / 128, (unsigned)(T < 64 ? 1 : (T / 64 > 512 ? 512 : T / 64)));
   hippo::short_conv_bwd_kernel<<<grid, 128, 0, ST(s)>>>((const bf16*)x, ldx, (const bf16*)w, pos, (const bf16*)dy, (bf16*)dx, lddx, dw, T, D, W);
   RET();

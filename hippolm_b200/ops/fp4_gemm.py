@@ -45,6 +45,23 @@ def fp4_matmul_tiled(a_packed, sfa_tiled, a_gs, b_packed, sfb_tiled, b_gs, out=N
     return out
 
 
+def fp4_matmul_pair(a_packed, sfa_tiled, a_gs, b_packed, sfb_tiled, b_gs, out=None, accumulate: bool = False) -> torch.Tensor:
+    """The same product on the CTA-pair kernel (``csrc/gemm_fp4_2sm.cu``: 256 x 256 tiles, ``cta_group::2``), called
+    explicitly; ``fp4_matmul`` / ``fp4_matmul_tiled`` reach it through the library when ``HIPPO_FP4_PAIR=1``.
+    Needs at least 256 rows and 256 columns."""
+    M, K2 = a_packed.shape
+    N = b_packed.shape[0]
+    K = K2 * 2
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a_packed.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1
+    check(lib().hippo_gemm_nvfp4_pair(ptr(a_packed), ptr(b_packed), ptr(sfa_tiled), ptr(sfb_tiled), ptr(a_gs), ptr(b_gs),
+                                      ptr(out), M, N, K, C.c_longlong(out.stride(0)), int(bool(accumulate)), stream_ptr()),
+          "gemm_nvfp4_pair")
+    return out
+
+
 def supported(M: int, N: int, K: int) -> bool:
     return K % 256 == 0 and N % 8 == 0 and os.environ.get("HIPPO_FP4_GEMM", "1") != "0"
 

@@ -35,16 +35,18 @@ def _cublaslt_nvfp4_tflops(M, N, K, xp, xs, wp, ws):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", type=str, default="", help="M,N,K: run only this shape")
-    ap.add_argument("--profile", type=str, default="", help="nt|nn|tn|nvfp4: launch only this kernel a few times (for ncu)")
+    ap.add_argument("--profile", type=str, default="", help="nt|nn|tn|nvfp4|nvfp4_pair: launch only this kernel a few times (for ncu)")
     cli = ap.parse_args()
     shapes = [tuple(int(v) for v in cli.shape.split(","))] if cli.shape else SHAPES
     if cli.profile:
         M, N, K = shapes[0]
         a = torch.randn(M, K, device="cuda").bfloat16(); b = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
         bt, at = b.t().contiguous(), a.t().contiguous()
-        if cli.profile == "nvfp4":
+        if cli.profile in ("nvfp4", "nvfp4_pair"):
             xp, xs, xg = nvfp4_cuda.quantize(a); wp, ws, wg = nvfp4_cuda.quantize(b)
-            fn = lambda: fp4_gemm.fp4_matmul(xp, xs, xg, wp, ws, wg)
+            sfa, sfb = fp4_gemm.tile_scales(xs, M, K), fp4_gemm.tile_scales(ws, N, K)
+            mm = fp4_gemm.fp4_matmul_pair if cli.profile == "nvfp4_pair" else fp4_gemm.fp4_matmul_tiled
+            fn = lambda: mm(xp, sfa, xg, wp, sfb, wg)
         else:
             fn = {"nt": lambda: co.gemm_nt(a, b), "nn": lambda: co.gemm_nn(a, bt), "tn": lambda: co.gemm_tn(at, bt)}[cli.profile]
         for _ in range(4):

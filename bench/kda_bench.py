@@ -21,6 +21,7 @@ def main():
     ap.add_argument("--B", type=int, default=4); ap.add_argument("--T", type=int, default=8192)
     ap.add_argument("--H", type=int, default=16); ap.add_argument("--D", type=int, default=128)
     ap.add_argument("--docs", type=int, default=8); ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--profile", action="store_true", help="two forward+backward passes and nothing else (for ncu)")
     a = ap.parse_args()
     torch.manual_seed(0)
     TT = a.B * a.T
@@ -51,6 +52,10 @@ def main():
         _KDAFunction.forward(ctx, qd, kd, vd, gd, bd, h0, cu)
         kda_bwd_cuda.backward(ctx, do, None)
 
+    if a.profile:
+        fwd_bwd(); fwd_bwd()
+        torch.cuda.synchronize()
+        return
     f = time_ms(fwd, iters=a.iters)
     fb = time_ms(fwd_bwd, iters=a.iters)
     print(json.dumps({"kda_fwd_ms": round(f, 3), "kda_fwd_bwd_ms": round(fb, 3), "B": a.B, "T": a.T, "H": a.H,

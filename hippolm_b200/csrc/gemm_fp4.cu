@@ -499,10 +499,10 @@ extern "C" int hippo_gemm_nvfp4_pair(const void* A, const void* B, const void* s
                                      const float* gsb, void* C, int M, int N, int K, long long ldc, int accumulate,
                                      void* stream);
 
-// HIPPO_FP4_PAIR=1 routes products with at least 256 rows and columns to the CTA-pair kernel of gemm_fp4_2sm.cu.
+// Products with at least 256 rows and columns run on the CTA-pair kernel of gemm_fp4_2sm.cu (HIPPO_FP4_PAIR=0: never).
 static int fp4_pair_mode() {
   static int mode = -1;
-  if (mode < 0) { const char* e = getenv("HIPPO_FP4_PAIR"); mode = e ? atoi(e) : 0; }
+  if (mode < 0) { const char* e = getenv("HIPPO_FP4_PAIR"); mode = e ? atoi(e) : 1; }
   return mode;
 }
 

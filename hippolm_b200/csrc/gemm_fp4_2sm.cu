@@ -2,10 +2,11 @@
 //
 //   tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X, MMA shape 256 x 256 x 64
 //
-// The one-CTA 128x128 kernel of gemm_fp4.cu asks L2 for 36 KB of operands and scales per 128x128x256 slab, four times
-// what a bf16 tile of the same shape needs per tensor-pipe cycle, and runs at the rate L2 can feed the SMs (2.1
-// PFLOP/s). Here each CTA of the pair stages its own 128 rows of A, HALF of the 256 B rows, the scale tiles of its A
-// rows and the scale tiles of all 256 B rows: 38 KB per 128x256x256 slab, i.e. half the bytes per flop.
+// A 128x128x64 FP4 MMA of the one-CTA kernel (gemm_fp4.cu) reads 8 KB of operands from shared memory in 64 tensor-pipe
+// cycles, 128 bytes per clock, which is all the shared-memory bandwidth an SM has: that kernel stops at 2.1 PFLOP/s.
+// Here each CTA of the pair stages its own 128 rows of A and only HALF of the 256 B rows (plus the scale tiles of its A
+// rows and of all 256 B rows): per SM 8 KB of operand reads per 128x256x64 MMA, i.e. half the bytes per flop, and
+// 38 KB instead of 72 KB of L2 -> shared-memory traffic per 128x256x256 slab.
 //
 // TMEM holds 512 columns: a 128 x 256 fp32 accumulator takes 256, the scale factors of the stages in flight take
 // the rest (4 columns per 128-row tile and MMA: 16 for A, 32 for B per stage), so there is ONE accumulator. The

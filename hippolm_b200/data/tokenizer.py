@@ -1,6 +1,6 @@
-"""Tokenizer loading (``src/training/tokenizer.py:12-28``): a HuggingFace tokenizer directory, with
-``pad = eos`` when the tokenizer has no pad token. A byte-level fallback keeps the text pipeline usable
-(tests, offline boxes) when no tokenizer files are given."""
+"""Tokenizer loading (``src/training/tokenizer.py:12-28``): a tokenizer directory (read by the in-tree byte-level BPE
+of ``data/bpe.py`` or by ``transformers``), with ``pad = eos`` when the tokenizer has no pad token; ``builtin`` selects
+the bundled small BPE vocabulary. A byte-level fallback keeps the text pipeline usable when no tokenizer is named."""
 from __future__ import annotations
 
 from typing import List, Optional
@@ -32,8 +32,21 @@ class ByteTokenizer:
 
 
 def load_tokenizer(path: Optional[str]):
+    """``None`` -> byte tokenizer; ``"builtin"`` -> the bundled small byte-level BPE vocabulary; a directory -> the
+    in-tree BPE reader (``data/bpe.py``: ``vocab.json`` + ``merges.txt`` or ``tokenizer.json``, token-for-token equal
+    to the HuggingFace tokenizer on such a directory), or ``transformers.AutoTokenizer`` when
+    ``HIPPO_TOKENIZER_BACKEND=hf`` or the directory is not a byte-level BPE."""
+    import os
     if not path:
         return ByteTokenizer()
+    from . import bpe
+    if path in ("builtin", "builtin:bpe_small"):
+        return bpe.load_default()
+    if os.environ.get("HIPPO_TOKENIZER_BACKEND", "native") != "hf":
+        try:
+            return bpe.BPETokenizer.load(path)
+        except (FileNotFoundError, KeyError, ValueError):
+            pass                                        # not a byte-level BPE directory: let transformers try
     from transformers import AutoTokenizer
     tok = AutoTokenizer.from_pretrained(path, trust_remote_code=False)
     if tok.pad_token_id is None:

@@ -47,7 +47,7 @@ def fp4_matmul_tiled(a_packed, sfa_tiled, a_gs, b_packed, sfb_tiled, b_gs, out=N
 
 def fp4_matmul_pair(a_packed, sfa_tiled, a_gs, b_packed, sfb_tiled, b_gs, out=None, accumulate: bool = False) -> torch.Tensor:
     """The same product on the CTA-pair kernel (``csrc/gemm_fp4_2sm.cu``: 256 x 256 tiles, ``cta_group::2``), called
-    explicitly; ``fp4_matmul`` / ``fp4_matmul_tiled`` reach it through the library when ``HIPPO_FP4_PAIR=1``.
+    explicitly; ``fp4_matmul`` / ``fp4_matmul_tiled`` reach it through the library unless ``HIPPO_FP4_PAIR=0``.
     Needs at least 256 rows and 256 columns."""
     M, K2 = a_packed.shape
     N = b_packed.shape[0]

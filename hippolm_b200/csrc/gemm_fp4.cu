@@ -24,7 +24,7 @@ constexpr int F_BM = 128, F_BN = 128, F_BKB = 128;          // K slab: 128 bytes
 constexpr int F_STAGES = 5;
 constexpr int F_A_BYTES = F_BM * F_BKB, F_B_BYTES = F_BN * F_BKB, F_SF_BYTES = 4 * 512;   // per operand per stage
 constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES + 2 * F_SF_BYTES;
-constexpr int F_THREADS = 192;
+constexpr int F_THREADS = 256;                              // TMA, MMA, 4 epilogue warps, 2 scale-copy warps
 constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + 1024 + 256;
 constexpr int F_RS_SLAB_BYTES = 4 * 32 * 256;               // epilogue staging of the reduce-scatter variant
 constexpr int F_SMEM_RS = F_SMEM + F_RS_SLAB_BYTES;
@@ -89,14 +89,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* empty = full + F_STAGES;
   uint64_t* tfull = empty + F_STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+  uint64_t* sf_full = tempty + 2;                              // scale tiles of a stage are in TMEM (2 copy warps)
+  uint32_t* tmem_slot = (uint32_t*)(sf_full + F_STAGES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = p.K / 256;
   const int k64 = p.K / 64;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < F_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < F_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 2); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
@@ -168,18 +169,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t d_tmem = tmem_base + acc * F_BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           int s = it % F_STAGES; uint32_t ph = (it / F_STAGES) & 1;
-          ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
+          ok = mbar_wait(&sf_full[s], ph, kWaitTmaFull, it);   // operands landed and the stage's scales are in TMEM
           if (!ok) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * F_STAGE_BYTES), sb = sa + F_A_BYTES;
-          const uint32_t ssa = sb + F_B_BYTES, ssb = ssa + F_SF_BYTES;
           const uint32_t t_sf = tmem_base + F_TMEM_SF0 + s * 32;          // 16 columns SFA + 16 columns SFB
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // 32 rows x 16 bytes, rows contiguous: 8-row groups are 128 bytes apart, no swizzle
-            tc_cp_32x128b_warpx4(t_sf + k * 4, make_smem_desc_noswizzle(ssa + k * 512, 16, 128));
-            tc_cp_32x128b_warpx4(t_sf + 16 + k * 4, make_smem_desc_noswizzle(ssb + k * 512, 16, 128));
-          }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024);
@@ -189,6 +183,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tc_commit(&empty[s]);
         }
         if (ok) tc_commit(&tfull[acc]);
+      }
+    }
+  } else if (warp >= 6) {
+    // Scale-copy warps: one thread cannot issue a slab's 8 tcgen05.cp, 4 MMAs and the commit as fast as the tensor pipe
+    // retires the MMAs, so the copies (warp 6: the A tiles, warp 7: the B tiles) have their own threads, each
+    // committing to the stage's sf_full barrier; the stage's 32 scale columns are free again once its previous MMAs
+    // have completed, which the producer has seen before it refilled the stage.
+    if (lane == 0) {
+      const int part = warp - 6;
+      const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const int total_its = my_tiles * kblocks;
+      for (int it = 0; it < total_its; ++it) {
+        const int s = it % F_STAGES; const uint32_t ph = (it / F_STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, kWaitTmaFull, it)) break;
+        tc_fence_after();
+        const uint32_t src = smem_u32(smem + s * F_STAGE_BYTES) + F_A_BYTES + F_B_BYTES + part * F_SF_BYTES;
+        const uint32_t t_sf = tmem_base + F_TMEM_SF0 + s * 32 + part * 16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // 32 rows x 16 bytes, rows contiguous: 8-row groups are 128 bytes apart, no swizzle
+          tc_cp_32x128b_warpx4(t_sf + k * 4, make_smem_desc_noswizzle(src + k * 512, 16, 128));
+        tc_commit(&sf_full[s]);
       }
     }
   } else {

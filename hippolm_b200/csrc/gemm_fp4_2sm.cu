@@ -10,15 +10,22 @@
 //
 // TMEM holds 512 columns: a 128 x 256 fp32 accumulator takes 256, the scale factors of the stages in flight take
 // the rest (4 columns per 128-row tile and MMA: 16 for A, 32 for B per stage), so there is ONE accumulator. The
-// epilogue therefore drains it into shared memory first (bf16, 64 KB per CTA), hands TMEM back to the MMA issuer, and
-// only then writes (or adds into) global memory while the next tile's MMAs run.
+// epilogue therefore drains it into registers first (a thread holds its row as 128 packed bf16 pairs), hands TMEM back
+// to the MMA issuer, and only then writes (or adds into) global memory while the next tile's MMAs run. No shared
+// memory goes to the epilogue: five 38 KB stages.
 //
-// Per CTA (192 threads): warp 0 = TMA producer (all five loads of a stage are tiled TMA loads of local memory whose
+// One thread cannot issue a slab's 12 scale copies (tcgen05.cp, shared memory -> TMEM), 4 MMAs and 2 commits as fast as
+// the tensor pipe retires the MMAs: with all of them in the MMA thread the kernel ran at 2.9 PFLOP/s with the pipe idle
+// two thirds of the time, without the copies (wrong results, timing only) at 4.8. So the copies have their own three
+// warps (A tiles, lower and upper B tiles), each committing to a per-stage barrier the MMA thread waits on: 4.2 PFLOP/s.
+//
+// Per CTA (288 threads): warp 0 = TMA producer (all five loads of a stage are tiled TMA loads of local memory whose
 // completion bytes land on the LEADER's barrier; the scale arrays are addressed as [tile * K/64 + k][128 x u32]
-// tensors), warp 1 = MMA issuer (leader only: tcgen05.cp of the scale tiles into both CTAs' TMEM, then the MMAs) and
-// TMEM owner, warps 2..5 = epilogue of the CTA's own 128 rows. Stage release and accumulator hand-over as in the bf16
-// pair kernel: two plain commits (own barrier, peer barrier), remote mbarrier arrives; no cluster-multicast qualifier.
-// Every wait is bounded. Replaces the reference's Marlin W4A16 path like the one-CTA kernel.
+// tensors), warp 1 = MMA issuer (leader only) and TMEM owner, warps 2..5 = epilogue of the CTA's own 128 rows, warps
+// 6..8 = scale copies (leader only; tcgen05.cp.cta_group::2 copies from both CTAs' shared memory into both CTAs'
+// TMEM). Stage release and accumulator hand-over as in the bf16 pair kernel: two plain commits (own barrier, peer
+// barrier), remote mbarrier arrives; no cluster-multicast qualifier. Every wait is bounded. Replaces the reference's
+// Marlin W4A16 path like the one-CTA kernel.
 #include "sm100.cuh"
 #include "host_utils.h"
 #include "cta_pair.cuh"
@@ -31,12 +38,12 @@ namespace f2 {
 constexpr int BM = 128;                 // rows per CTA; the pair covers 256
 constexpr int BN = 256, BNH = 128;      // columns of the pair tile / B rows staged by each CTA
 constexpr int BKB = 128;                // K slab: 128 bytes = 256 fp4 elements = 4 MMAs
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BKB, B_BYTES = BNH * BKB, SFA_BYTES = 4 * 512, SFB_BYTES = 2 * 4 * 512;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;          // 38 KB
-constexpr int EPI_BYTES = 4 * 32 * 512;                                         // 4 warps x [32 rows][512 B]
-constexpr int THREADS = 192;
-constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+constexpr int STAGES = 5;
+constexpr int THREADS = 288;            // TMA, MMA, 4 epilogue warps, 3 scale-copy warps
+constexpr int COPY_WARP0 = 6, COPY_WARPS = 3;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int TMEM_SF0 = 256;           // the accumulator uses columns [0, 256); 48 scale columns per stage follow
 static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned (128-byte swizzle)");
 static_assert(TMEM_SF0 + STAGES * 48 <= 512, "scale-factor columns must fit behind the accumulator");
@@ -70,12 +77,12 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                       const __grid_constant__ PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES;
-  uint64_t* full = (uint64_t*)(epi_stage + EPI_BYTES);         // used in the leader only
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // used in the leader only
   uint64_t* empty = full + STAGES;                             // one set per CTA
   uint64_t* tfull = empty + STAGES;                            // one per CTA
   uint64_t* tempty = tfull + 1;                                // used in the leader only (8 arrivals)
-  uint32_t* tmem_slot = (uint32_t*)(tempty + 1);
+  uint64_t* sf_full = tempty + 1;                              // leader only: scale tiles of a stage are in TMEM
+  uint32_t* tmem_slot = (uint32_t*)(sf_full + STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -86,7 +93,7 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int cid = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], COPY_WARPS); }
     mbar_init(tfull, 1); mbar_init(tempty, 8);
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmSFA); prefetch_tmap(&tmSFB);
@@ -105,6 +112,20 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int gm = min(GROUP, p.tiles_m - g * GROUP);
     tm = g * GROUP + r % gm;
     tn = r / gm;
+  };
+
+  // One K slab has 12 scale tiles (4 MMAs x (1 tile of A rows + 2 tiles of B rows)); copy warp `part` moves 4 of them,
+  // shared memory -> TMEM of both CTAs: part 0 the A tiles, parts 1 and 2 the tiles of B rows 0..127 and 128..255.
+  auto issue_scale_copies = [&](int j, int part) {
+    const int s = j % STAGES;
+    const uint32_t src = smem_u32(smem + s * STAGE_BYTES) + A_BYTES + B_BYTES + part * SFA_BYTES;
+    const uint32_t t_sf = tmem_base + TMEM_SF0 + s * 48;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t dst = part == 0 ? t_sf + k * 4 : t_sf + 16 + k * 8 + (part - 1) * 4;
+      // a scale tile is 32 rows x 16 bytes, rows contiguous: 8-row groups 128 bytes apart, no swizzle
+      tc_cp_32x128b_warpx4_pair(dst, make_smem_desc_noswizzle(src + k * 512, 16, 128));
+    }
   };
 
   if (warp == 0) {
@@ -142,19 +163,11 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_fence_after();
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           int s = it % STAGES; uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&full[s], ph, kWaitTmaFull, it);
+          ok = mbar_wait(&sf_full[s], ph, kWaitTmaFull, it);      // operands landed and scales are in TMEM
           if (!ok) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
-          const uint32_t ssa = sb + B_BYTES, ssb = ssa + SFA_BYTES;
           const uint32_t t_sfa = tmem_base + TMEM_SF0 + s * 48, t_sfb = t_sfa + 16;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // a scale tile is 32 rows x 16 bytes, rows contiguous: 8-row groups 128 bytes apart, no swizzle
-            tc_cp_32x128b_warpx4_pair(t_sfa + k * 4, make_smem_desc_noswizzle(ssa + k * 512, 16, 128));
-            tc_cp_32x128b_warpx4_pair(t_sfb + k * 8, make_smem_desc_noswizzle(ssb + k * 512, 16, 128));
-            tc_cp_32x128b_warpx4_pair(t_sfb + k * 8 + 4, make_smem_desc_noswizzle(ssb + (4 + k) * 512, 16, 128));
-          }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024);
@@ -172,9 +185,20 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
       }
     }
+  } else if (warp >= COPY_WARP0) {
+    if (lane == 0 && leader) {
+      const int part = warp - COPY_WARP0;
+      const int total_its = cid < num_tiles ? ((num_tiles - cid + n_clusters - 1) / n_clusters) * kblocks : 0;
+      for (int it = 0; it < total_its; ++it) {
+        const int s = it % STAGES; const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, kWaitTmaFull, it)) break;
+        tc_fence_after();
+        issue_scale_copies(it, part);
+        tc_commit_pair(smem_u32(&sf_full[s]));
+      }
+    }
   } else {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 512);            // [32 rows][32 x 16 B], private to the warp
     const float alpha = (*p.gsa) * (*p.gsb);
     int tl = 0;
     bool ok = true;
@@ -185,57 +209,46 @@ gemm_nvfp4_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c, r);
-        tc_wait_ld();
+      {
+        uint32_t pk[BN / 2];                                               // this thread's row, packed bf16 pairs
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 v;
-          __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tc_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * alpha, __uint_as_float(r[j + 2 * e + 1]) * alpha);
-          const int piece = (c + j) / 8;                                   // 16-byte piece within the row
-          slab[lane * 32 + (piece ^ lane)] = v;                            // xor swizzle: conflict-free both ways
-        }
-      }
-      // the accumulator is in shared memory now: hand TMEM back to the leader before touching global memory
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tempty), 0));
-      const int row_base = (tm * 2 + (int)rank) * BM + q * 32;
-      const int ncols = min(BN, p.N - tn * BN);                            // multiple of 8
-      __nv_bfloat16* dst0 = p.C + (long long)row_base * p.ldc + tn * BN + lane * 8;
-      if (lane * 8 < ncols) {
-#pragma unroll 1
-        for (int r0 = 0; r0 < 32; r0 += 4) {
-          uint4 old[4];
-          if (p.accumulate) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)                                    // four loads in flight
-              if (row_base + r0 + j < p.M) old[j] = *(const uint4*)(dst0 + (long long)(r0 + j) * p.ldc);
+          for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * alpha, __uint_as_float(r[2 * j + 1]) * alpha);
+            pk[c * 16 + j] = *(const uint32_t*)&h;
           }
+        }
+        // the accumulator is in registers now: hand TMEM back to the leader before touching global memory
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tempty), 0));
+        const int row = (tm * 2 + (int)rank) * BM + q * 32 + lane;
+        if (row < p.M) {
+          __nv_bfloat16* crow = p.C + (long long)row * p.ldc + tn * BN;
+          const int ncols = min(BN, p.N - tn * BN);                        // multiple of 8
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int rr = r0 + j;
-            if (row_base + rr >= p.M) continue;
-            uint4 v = slab[rr * 32 + (lane ^ rr)];
-            if (p.accumulate) {
-              __nv_bfloat162* vb = (__nv_bfloat162*)&v;
-              const __nv_bfloat162* ob = (const __nv_bfloat162*)&old[j];
+          for (int c = 0; c < BN / 8; ++c) {                               // 16-byte pieces of the row
+            if (c * 8 < ncols) {
+              uint4 v = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+              if (p.accumulate) {
+                const uint4 old = *(const uint4*)(crow + c * 8);
+                __nv_bfloat162* vb = (__nv_bfloat162*)&v;
+                const __nv_bfloat162* ob = (const __nv_bfloat162*)&old;
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 a = __bfloat1622float2(vb[e]), o = __bfloat1622float2(ob[e]);
-                vb[e] = __floats2bfloat162_rn(a.x + o.x, a.y + o.y);
+                for (int e = 0; e < 4; ++e) {
+                  const float2 x = __bfloat1622float2(vb[e]), o = __bfloat1622float2(ob[e]);
+                  vb[e] = __floats2bfloat162_rn(x.x + o.x, x.y + o.y);
+                }
               }
+              *(uint4*)(crow + c * 8) = v;
             }
-            *(uint4*)(dst0 + (long long)rr * p.ldc) = v;
           }
         }
       }
-      __syncwarp();                                                        // the slab is free for the next tile
     }
   }
   // Neither CTA may leave (or free its TMEM) while the other can still read its shared memory or signal its barriers.

@@ -30,6 +30,10 @@ constexpr int BK = 64, UMMA_K = 16, STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+// COMM_RS: 4 pipeline stages + the epilogue slabs (4 warps x 32 rows of 512 bytes at a 528-byte pitch: 16-byte stores of a
+// quarter warp then fall on distinct banks, and every row stays a 16-byte aligned source of a bulk copy)
+constexpr int RS_PITCH = 528, RS_SLABS = 4 * 32 * RS_PITCH;
+constexpr int SMEM_RS = 4 * STAGE_BYTES + RS_SLABS + 1024 + 256;
 
 __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                 uint32_t accumulate) {
@@ -54,7 +58,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                      const __grid_constant__ CommParams cp, const __grid_constant__ CUtensorMap tmOwn) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // used in the leader only
+  uint64_t* full = (uint64_t*)(smem + (COMM == COMM_RS ? 4 * STAGE_BYTES + RS_SLABS : STAGES * STAGE_BYTES));   // used in the leader only
   uint64_t* empty = full + STAGES;                             // one per CTA
   uint64_t* tfull = empty + STAGES;                            // one per CTA
   uint64_t* tempty = tfull + 2;                                // used in the leader only (8 arrivals)
@@ -217,7 +221,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int row = (tm * 2 + (int)rank) * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       if (COMM == COMM_RS) {
-        uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 512);          // [32 rows][32 x 16 B]
+        // The warp lays its 32 x 256 slab out in shared memory, hands the accumulator back, and every lane sends its own
+        // row (512 contiguous bytes) to the owner's staging slot with one bulk async copy: the remote stores are in
+        // flight while the warp drains the next tile instead of blocking it for an NVLink round trip per instruction.
+        uint8_t* slab = epi_stage + (warp - 2) * 32 * RS_PITCH;
+        tma_store_wait_read<0>();                                            // the previous tile's rows have left the slab
+        __syncwarp();
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -230,26 +239,25 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * p.alpha, __uint_as_float(r[j + 2 * e + 1]) * p.alpha);
-            const int piece = (c + j) / 8;                                   // 16-byte piece within the row
-            slab[lane * 32 + (piece ^ (lane & 31))] = v;                     // xor swizzle: conflict-free both ways
+            *(uint4*)(slab + lane * RS_PITCH + (c + j) * 2) = v;
           }
         }
-        // the accumulator is in shared memory now: hand it back to the leader before the (slow) remote stores
+        fence_proxy_async();                                                 // generic-proxy slab writes -> bulk copy reads
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));   // accumulator back to the leader
         const int row_base = (tm * 2 + (int)rank) * BM + q * 32;
         const int owner = row_base / cp.rows_per_shard;
         const int ncols = min(BN, p.N - tn * BN);                            // multiple of 8
-        __nv_bfloat16* dst0 = (__nv_bfloat16*)cp.buf_peer[owner] +
-                              ((long long)cp.rank * cp.rows_per_shard + (row_base - owner * cp.rows_per_shard)) * p.N + tn * BN;
-#pragma unroll 4
-        for (int rr = 0; rr < 32; ++rr) {
-          if (row_base + rr < p.M && lane * 8 < ncols)
-            *(uint4*)(dst0 + (long long)rr * p.N + lane * 8) = slab[rr * 32 + (lane ^ (rr & 31))];
+        if (row_base + lane < p.M) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)cp.buf_peer[owner] +
+                               ((long long)cp.rank * cp.rows_per_shard + (row_base + lane - owner * cp.rows_per_shard)) * p.N + tn * BN;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst), "r"(smem_u32(slab + lane * RS_PITCH)), "r"((uint32_t)(ncols * 2)) : "memory");
         }
-        // One fence + counter release per OWNER SHARD, not per tile: the owner only starts its reduction when all of a
-        // source's tiles have landed, so the remote-write round trip is paid once per shard instead of once per tile.
+        tma_store_commit();
+        // One completion wait + counter release per OWNER SHARD, not per tile: the owner only starts its reduction when
+        // all of a source's tiles have landed, so the remote-write round trip is paid once per shard.
         ++rs_pending;
         const int tnext = t + n_clusters;
         int owner_next = -1;
@@ -258,12 +266,12 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           owner_next = ((tm2 * 2 + (int)rank) * BM + q * 32) / cp.rows_per_shard;
         }
         if (owner_next != owner) {
+          tma_store_wait<0>();                                               // this lane's rows have landed
           __threadfence_system();
           __syncwarp();
           if (lane == 0) red_release_sys_add(cp.flag_peer[owner] + cp.rank, (uint32_t)rs_pending);
           rs_pending = 0;
         }
-        __syncwarp();                                                        // the slab is free for the next tile
         continue;
       }
 #pragma unroll 1
@@ -357,11 +365,11 @@ static int launch(const void* A, const void* B, long long lda, long long ldb, Ge
   auto kern = gemm_bf16_2sm_kernel<AK, BK_, COMM>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, COMM == COMM_RS ? SMEM_RS : SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  kern<<<2 * clusters, THREADS, SMEM, stream>>>(tmA, tmB, p, cp, tmOwn);
+  kern<<<2 * clusters, THREADS, COMM == COMM_RS ? SMEM_RS : SMEM, stream>>>(tmA, tmB, p, cp, tmOwn);
   return (int)cudaGetLastError();
 }
 

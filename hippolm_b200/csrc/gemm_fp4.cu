@@ -26,7 +26,8 @@ constexpr int F_A_BYTES = F_BM * F_BKB, F_B_BYTES = F_BN * F_BKB, F_SF_BYTES = 4
 constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES + 2 * F_SF_BYTES;
 constexpr int F_THREADS = 256;                              // TMA, MMA, 4 epilogue warps, 2 scale-copy warps
 constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + 1024 + 256;
-constexpr int F_RS_SLAB_BYTES = 4 * 32 * 256;               // epilogue staging of the reduce-scatter variant
+constexpr int F_RS_PITCH = 272;                             // slab row pitch: 16-byte stores of a quarter warp hit distinct banks
+constexpr int F_RS_SLAB_BYTES = 4 * 32 * F_RS_PITCH;        // epilogue staging of the reduce-scatter variant
 constexpr int F_SMEM_RS = F_SMEM + F_RS_SLAB_BYTES;
 constexpr int F_TMEM_SF0 = 256;                             // accumulators use columns [0, 256)
 
@@ -224,9 +225,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = tm * F_BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * F_BN + ((uint32_t)(q * 32) << 16);
       if (COMM == F_COMM_RS) {
-        // The warp lays its 32 x 128 slab out in shared memory (xor-swizzled 16-byte pieces), then each store
-        // instruction writes two contiguous 256-byte rows into the owner's staging slot [this rank].
-        uint4* slab = (uint4*)(epi_stage + (warp - 2) * 32 * 256);
+        // The warp lays its 32 x 128 slab out in shared memory and every lane sends its own row (256 contiguous bytes) to
+        // the owner's staging slot [this rank] with one bulk async copy, so the remote stores are in flight while the
+        // warp drains the next tile.
+        uint8_t* slab = epi_stage + (warp - 2) * 32 * F_RS_PITCH;
+        tma_store_wait_read<0>();                                          // the previous tile's rows have left the slab
+        __syncwarp();
 #pragma unroll 1
         for (int c = 0; c < F_BN; c += 32) {
           uint32_t r[32];
@@ -239,29 +243,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               vb[e] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * alpha, __uint_as_float(r[j + 2 * e + 1]) * alpha);
-            const int piece = (c + j) / 8;
-            slab[lane * 16 + (piece ^ (lane & 15))] = v;
+            *(uint4*)(slab + lane * F_RS_PITCH + (c + j) * 2) = v;
           }
         }
-        __syncwarp();
+        fence_proxy_async();                                               // generic-proxy slab writes -> bulk copy reads
         const int row_base = tm * F_BM + q * 32;
         const int owner = row_base / p.rows_per_shard;
         const int ncols = min(F_BN, p.N - tn * F_BN);
-        __nv_bfloat16* dst0 = (__nv_bfloat16*)p.stage_peer[owner] +
-                              ((long long)p.rank * p.rows_per_shard + (row_base - owner * p.rows_per_shard)) * p.N + tn * F_BN;
-        const int pc = lane & 15;
-#pragma unroll 4
-        for (int rr = 0; rr < 32; rr += 2) {
-          const int r2 = rr + (lane >> 4);
-          if (row_base + r2 < p.M && pc * 8 < ncols)
-            *(uint4*)(dst0 + (long long)r2 * p.N + pc * 8) = slab[r2 * 16 + (pc ^ (r2 & 15))];
+        if (row_base + lane < p.M) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)p.stage_peer[owner] +
+                               ((long long)p.rank * p.rows_per_shard + (row_base + lane - owner * p.rows_per_shard)) * p.N + tn * F_BN;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst), "r"(smem_u32(slab + lane * F_RS_PITCH)), "r"((uint32_t)(ncols * 2)) : "memory");
         }
-        // one fence + counter release per OWNER SHARD (the owner reduces only after a source's last tile anyway)
+        tma_store_commit();
+        // one completion wait + counter release per OWNER SHARD (the owner reduces only after a source's last tile anyway)
         ++rs_pending;
         const int tnext = t + (int)gridDim.x;
         int owner_next = -1;
         if (tnext < num_tiles) { int tm2, tn2; tile_coord(tnext, tm2, tn2); owner_next = (tm2 * F_BM + q * 32) / p.rows_per_shard; }
         if (owner_next != owner) {
+          tma_store_wait<0>();                                             // this lane's rows have landed
           __threadfence_system();
           __syncwarp();
           if (lane == 0) f_red_release_sys_add(p.rs_flag_peer[owner] + p.rank, (uint32_t)rs_pending);
@@ -513,6 +515,15 @@ extern "C" int hippo_nvfp4_tile_scales(const void* sf, void* out, long long rows
 extern "C" int hippo_gemm_nvfp4_pair(const void* A, const void* B, const void* sfa, const void* sfb, const float* gsa,
                                      const float* gsb, void* C, int M, int N, int K, long long ldc, int accumulate,
                                      void* stream);
+extern "C" int hippo_allgather_gemm_nvfp4_pair(const void* gathered, const void* flags, int world, int rank,
+                                               int rows_per_shard, const void* B, const void* sfb, const float* gsb,
+                                               void* C, long long ldc, int N, int K, unsigned target,
+                                               long long wait_cycles, void* stream);
+extern "C" int hippo_gemm_reduce_scatter_nvfp4_pair(const void* A, const void* sfa, const float* gsa, const void* B,
+                                                    const void* sfb, const float* gsb, void* const* stage_ptrs,
+                                                    void* const* flag_ptrs, int world, int rank, int rows_per_shard,
+                                                    void* out_local, int N, int K, unsigned target,
+                                                    long long wait_cycles, void* stream);
 
 // Products with at least 256 rows and columns run on the CTA-pair kernel of gemm_fp4_2sm.cu (HIPPO_FP4_PAIR=0: never).
 static int fp4_pair_mode() {
@@ -626,6 +637,9 @@ extern "C" int hippo_allgather_gemm_nvfp4(const void* gathered, const void* flag
                                           long long ldc, int N, int K, unsigned target, long long wait_cycles,
                                           void* stream) {
   if (world < 1 || world > 8 || rows_per_shard % F_BM || K % 512 || (N % 8) || (ldc % 8)) return -2;
+  if (fp4_pair_mode() && rows_per_shard % 256 == 0 && N >= 256)
+    return hippo_allgather_gemm_nvfp4_pair(gathered, flags, world, rank, rows_per_shard, B, sfb, gsb, C, ldc, N, K, target,
+                                           wait_cycles, stream);
   const int M = world * rows_per_shard;
   const uint8_t* base = (const uint8_t*)gathered;
   const long long sf_off = (long long)M * (K / 2), gs_off = sf_off + (long long)M * (K / 16);
@@ -662,6 +676,9 @@ extern "C" int hippo_gemm_reduce_scatter_nvfp4(const void* A, const void* sfa, c
                                                void* out_local, int N, int K, unsigned target, long long wait_cycles,
                                                void* stream) {
   if (world < 1 || world > 8 || rows_per_shard % F_BM || K % 256 || (N % 8)) return -2;
+  if (fp4_pair_mode() && rows_per_shard % 256 == 0 && N >= 256)
+    return hippo_gemm_reduce_scatter_nvfp4_pair(A, sfa, gsa, B, sfb, gsb, stage_ptrs, flag_ptrs, world, rank, rows_per_shard,
+                                                out_local, N, K, target, wait_cycles, stream);
   const int M = world * rows_per_shard;
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, F_BKB, F_BM, 1, true);

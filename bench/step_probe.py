@@ -25,6 +25,8 @@ def main():
     ap.add_argument("--seq_len", type=int, default=8192)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--bf16_ffn", action="store_true")
+    ap.add_argument("--ffn_bwd", type=str, default="fp4", choices=["bf16", "fp4_dx", "fp4"],
+                    help="backward of the NVFP4 FFN linears (the benchmark configuration uses fp4)")
     ap.add_argument("--heads", type=int, default=32, help="e.g. 4 = the local heads of one TP=8 rank")
     ap.add_argument("--ffn", type=int, default=14336, help="e.g. 1792 = the local FFN width of one TP=8 rank")
     ap.add_argument("--vocab", type=int, default=128256)
@@ -42,6 +44,7 @@ def main():
     args.num_layers, args.num_blocks, args.intermediate_size = a.layers, max(1, a.layers // 4), a.ffn
     args.attn_res_heads = 32
     args.ffn_nvfp4 = args.ffn_nvfp4_no_bf16_master = not a.bf16_ffn
+    args.ffn_nvfp4_backward = "bf16" if a.bf16_ffn else a.ffn_bwd
     args.batch_size, args.seq_len, args.micro_batch_size, args.max_steps = a.seqs, a.seq_len, a.micro or a.seq_len, 10 ** 9
     args.tp_size, args.dp_size, args.fused_comm = a.tp, 1, not a.no_fused_comm
     rank0 = int(os.environ.get("RANK", "0")) == 0
@@ -90,7 +93,7 @@ def main():
         from torch.profiler import profile, ProfilerActivity
         torch.cuda.synchronize()
         t0 = time.time()
-        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
             train_step(ctx, batch)
             torch.cuda.synchronize()
         wall = time.time() - t0
@@ -103,6 +106,11 @@ def main():
             c = agg.setdefault(k, [0, 0.0]); c[0] += 1; c[1] += e.device_time / 1e3
         for k, (c, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:25]:
             print(f"  {ms:9.2f} ms {c:6d}  {k}")
+        # library (aten) operators by their own GPU time, with input shapes: what is left of torch glue in the step
+        print("aten operators by self GPU time:")
+        ops = [e for e in prof.key_averages(group_by_input_shape=True) if e.key.startswith("aten::") and e.self_device_time_total > 0]
+        for e in sorted(ops, key=lambda e: -e.self_device_time_total)[:30]:
+            print(f"  {e.self_device_time_total / 1e3:9.2f} ms {e.count:6d}  {e.key}  {str(e.input_shapes)[:110]}")
 
 
 if __name__ == "__main__":

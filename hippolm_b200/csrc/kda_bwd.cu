@@ -959,7 +959,7 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
                     const bf16* __restrict__ dKK, const bf16* __restrict__ dAqk, const float* __restrict__ dq_acc,
                     const float* __restrict__ dk_acc, const float* __restrict__ dG_acc,
                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_len, int H,
-                    float* __restrict__ dq_out, float* __restrict__ dk_out, float* __restrict__ dg_out,
+                    bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, float* __restrict__ dg_out,
                     float* __restrict__ dbeta_out) {
   constexpr int LD = DK + 8, NT = DK / 16, LQ = DK + 4;
   constexpr int NTHR = 4 * DK, NWARP = NTHR / 32;
@@ -1126,7 +1126,7 @@ kda_bwd_amat_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     const int i = row0 + ii;
     if (i < len) {
       long long toff = ((long long)(t0 + i) * H + h) * DK + c;
-      dq_out[toff] = dq[ii]; dk_out[toff] = dk[ii]; dg_out[toff] = dG[ii] + add;
+      dq_out[toff] = __float2bfloat16(dq[ii]); dk_out[toff] = __float2bfloat16(dk[ii]); dg_out[toff] = dG[ii] + add;
     }
   }
   __syncthreads();
@@ -1154,7 +1154,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
                       const void* qg, const void* kg, const void* Aqk, const void* Ainv, const void* Akk,
                       const void* vnew, const void* Sst, const void* d_o, const float* dfinal, const int* cs,
                       const int* cl, const int* sc, const int* so, int NC, int N, int H, void* dvn, void* dSst, void* dw, void* dAqk,
-                      void* dKK, void* dbk, float* dq_acc, float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv,
+                      void* dKK, void* dbk, float* dq_acc, float* dk_acc, float* dG_acc, void* dq, void* dk, void* dv,
                       float* dg, float* dbeta, float* dh0, cudaStream_t s) {
   constexpr int VS = 32;
   auto k3 = kda_bwd_state_kernel<DK, VS>;
@@ -1211,7 +1211,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const float* 
   k4b<<<dim3(NC, H), 256, kda_bwd_wy_smem<DK>(), s>>>((const bf16*)k, (const bf16*)v, beta, G, (const bf16*)Ainv,
       (const bf16*)Akk, (const bf16*)dvn, (const bf16*)dw, cs, cl, H, (bf16*)dbk, (bf16*)dv, dbeta, (bf16*)dKK);
   k4c<<<dim3(NC, H), 4 * DK, kda_bwd_amat_smem<DK>(), s>>>((const bf16*)q, (const bf16*)k, G, beta, (const bf16*)dbk,
-      (const bf16*)dKK, (const bf16*)dAqk, dq_acc, dk_acc, dG_acc, cs, cl, H, dq, dk, dg, dbeta);
+      (const bf16*)dKK, (const bf16*)dAqk, dq_acc, dk_acc, dG_acc, cs, cl, H, (bf16*)dq, (bf16*)dk, dg, dbeta);
   return (int)cudaGetLastError();
 }
 
@@ -1220,7 +1220,7 @@ extern "C" int hippo_kda_bwd(const void* q, const void* k, const void* v, const 
                              const void* Akk, const void* vnew, const void* Sst, const void* d_o, const float* dfinal,
                              const int* chunk_start, const int* chunk_len, const int* seq_chunk, const int* seq_order,
                              int NC, int N, int H, int DK, void* dvn, void* dSst, void* dw, void* dAqk, void* dKK, void* dbk, float* dq_acc,
-                             float* dk_acc, float* dG_acc, float* dq, float* dk, void* dv, float* dg, float* dbeta,
+                             float* dk_acc, float* dG_acc, void* dq, void* dk, void* dv, float* dg, float* dbeta,
                              float* dh0, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (DK == 128) return launch_bwd<128>(q, k, v, beta, G, w, qg, kg, Aqk, Ainv, Akk, vnew, Sst, d_o, dfinal, chunk_start, chunk_len, seq_chunk, seq_order, NC, N, H, dvn, dSst, dw, dAqk, dKK, dbk, dq_acc, dk_acc, dG_acc, dq, dk, dv, dg, dbeta, dh0, s);

@@ -67,12 +67,41 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
   }
 }
 
+// s = x + res (stored, bf16), y = rmsnorm(s) * w: the residual add of a pre-norm layer fused into the norm that follows it
+__global__ void add_rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
+                                       bf16* __restrict__ sum, bf16* __restrict__ y, float* __restrict__ rstd, int D,
+                                       float eps) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const bf16* xr = x + row * D; const bf16* rr = res + row * D;
+  bf16* sr = sum + row * D;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+    float f[8], g[8]; load8(xr + c, f); load8(rr + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + g[i]));   // the stored value is what is normalised
+    store8(sr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = block_sum(ss, sh);
+  float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  bf16* yr = y + row * D;
+  for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {     // each thread re-reads the pieces it wrote itself
+    float f[8], g[8]; load8(sr + c, f); load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+    store8(yr + c, f);
+  }
+}
+
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)); partial dw[blockIdx.x, :] = sum over this block's rows of dy*xhat
 // grid-stride over rows; each thread owns columns {threadIdx.x*8 + k*blockDim.x*8}; D <= blockDim.x*8*MAXV
 template <int MAXV>
 __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
                                    const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dw_part,
-                                   int T, int D) {
+                                   int T, int D, const bf16* __restrict__ dres = nullptr) {
   __shared__ float sh[32];
   float dwacc[MAXV][8];
 #pragma unroll
@@ -100,6 +129,11 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
         float fx[8], fd[8], fw[8], o[8]; load8(xr + c, fx); load8(dyr + c, fd); load8(w + c, fw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = r * (fw[i] * fd[i] - fx[i] * r * dot);
+        if (dres) {                                       // gradient that reaches x through the residual path
+          float fr[8]; load8(dres + row * D + c, fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += fr[i];
+        }
         store8(dx + row * D + c, o);
       }
     }
@@ -265,7 +299,7 @@ __global__ void kda_prologue_fwd_kernel(const bf16* __restrict__ proj, long long
 // backward into dproj columns q,k,v,b (fg columns and pad are written by the caller)
 template <int KPL>
 __global__ void kda_prologue_bwd_kernel(const bf16* __restrict__ proj, long long ld, int H, int off_q, int off_k,
-                                        int off_v, int off_b, const float* __restrict__ dq, const float* __restrict__ dk,
+                                        int off_v, int off_b, const bf16* __restrict__ dq, const bf16* __restrict__ dk,
                                         const bf16* __restrict__ dv, const float* __restrict__ dbeta,
                                         const float* __restrict__ q_rstd, const float* __restrict__ k_rstd,
                                         bf16* __restrict__ dproj, long long T, float scale, float beta_mul,
@@ -286,8 +320,8 @@ __global__ void kda_prologue_bwd_kernel(const bf16* __restrict__ proj, long long
     xq[i] = a; xk[i] = b;
     sq_[i] = apply_silu ? a * sigmoidf_(a) : a;
     sk_[i] = apply_silu ? b * sigmoidf_(b) : b;
-    gq[i] = dq[row * K + lane + 32 * i] * scale;        // grad wrt normalised (unscaled) q
-    gk[i] = dk[row * K + lane + 32 * i];
+    gq[i] = __bfloat162float(dq[row * K + lane + 32 * i]) * scale;        // grad wrt normalised (unscaled) q
+    gk[i] = __bfloat162float(dk[row * K + lane + 32 * i]);
     dotq += gq[i] * sq_[i]; dotk += gk[i] * sk_[i];
   }
   dotq = warp_sum(dotq); dotk = warp_sum(dotk);
@@ -402,6 +436,24 @@ extern "C" int hippo_rmsnorm_fwd(const void* x, const void* w, void* y, float* r
   rmsnorm_fwd_kernel<<<(unsigned)T, th, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, D, eps);
   RET();
 }
+extern "C" int hippo_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* sum, void* y, float* rstd,
+                                     long long T, int D, float eps, void* s) {
+  if (D % 8) return -1;
+  int th = D >= 2048 ? 256 : 128;
+  add_rmsnorm_fwd_kernel<<<(unsigned)T, th, 0, ST(s)>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)sum, (bf16*)y, rstd, D, eps);
+  RET();
+}
+// RMSNorm backward plus the gradient that reaches the normalised tensor through the residual path: dx = dres + norm'(dy)
+extern "C" int hippo_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const void* dres, const float* rstd,
+                                     void* dx, float* dw_part, float* dw, long long T, int D, int nblocks, void* s) {
+  if (D % 8 || D > 256 * 8 * 4) return -1;
+  int maxv = (D + 2047) / 2048;
+  if (maxv <= 1) rmsnorm_bwd_kernel<1><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, dw_part, (int)T, D, (const bf16*)dres);
+  else if (maxv == 2) rmsnorm_bwd_kernel<2><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, dw_part, (int)T, D, (const bf16*)dres);
+  else rmsnorm_bwd_kernel<4><<<nblocks, 256, 0, ST(s)>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, dw_part, (int)T, D, (const bf16*)dres);
+  colsum_kernel<<<(D + 255) / 256, 256, 0, ST(s)>>>(dw_part, dw, nblocks, D);
+  RET();
+}
 // dw_part: [nblocks, D] fp32 scratch; dw: [D] fp32 out. returns nblocks used via *nblocks_io (in: capacity)
 extern "C" int hippo_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
                                  float* dw_part, float* dw, long long T, int D, int nblocks, void* s) {
@@ -453,12 +505,12 @@ extern "C" int hippo_kda_prologue_fwd(const void* proj, long long ld, int H, int
   RET();
 }
 extern "C" int hippo_kda_prologue_bwd(const void* proj, long long ld, int H, int K, int off_q, int off_k, int off_v,
-                                      int off_b, const float* dq, const float* dk, const void* dv, const float* dbeta,
+                                      int off_b, const void* dq, const void* dk, const void* dv, const float* dbeta,
                                       const float* q_rstd, const float* k_rstd, void* dproj, long long T, float scale,
                                       float beta_mul, int apply_silu, void* s) {
   unsigned blocks = (unsigned)((T * H + 7) / 8);
-  if (K == 128) kda_prologue_bwd_kernel<4><<<blocks, 256, 0, ST(s)>>>((const bf16*)proj, ld, H, off_q, off_k, off_v, off_b, dq, dk, (const bf16*)dv, dbeta, q_rstd, k_rstd, (bf16*)dproj, T, scale, beta_mul, apply_silu);
-  else if (K == 64) kda_prologue_bwd_kernel<2><<<blocks, 256, 0, ST(s)>>>((const bf16*)proj, ld, H, off_q, off_k, off_v, off_b, dq, dk, (const bf16*)dv, dbeta, q_rstd, k_rstd, (bf16*)dproj, T, scale, beta_mul, apply_silu);
+  if (K == 128) kda_prologue_bwd_kernel<4><<<blocks, 256, 0, ST(s)>>>((const bf16*)proj, ld, H, off_q, off_k, off_v, off_b, (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, dbeta, q_rstd, k_rstd, (bf16*)dproj, T, scale, beta_mul, apply_silu);
+  else if (K == 64) kda_prologue_bwd_kernel<2><<<blocks, 256, 0, ST(s)>>>((const bf16*)proj, ld, H, off_q, off_k, off_v, off_b, (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, dbeta, q_rstd, k_rstd, (bf16*)dproj, T, scale, beta_mul, apply_silu);
   else return -1;
   RET();
 }

@@ -170,8 +170,8 @@ class KDAAttention(nn.Module):
             k = ops.l2norm(k)
             beta = torch.sigmoid(proj[:, o_fg + 2 * Vd:o_fg + 2 * Vd + Hl].float()) * beta_mul
         else:
-            q, k, v, beta = ops.kda_prologue(proj, Hl, K, 0, self.key_l, 2 * self.key_l, o_fg + 2 * Vd,
-                                             K ** -0.5, beta_mul, True)
+            q, k, v, beta, fg = ops.kda_prologue(proj, Hl, K, 0, self.key_l, 2 * self.key_l, o_fg + 2 * Vd,
+                                                 K ** -0.5, beta_mul, True, o_fg, 2 * Vd)
         g_raw = ops.linear(fg[:, :Vd].contiguous(), self.f_proj1_weight)
         gate = ops.linear(fg[:, Vd:].contiguous(), self.g_proj1_weight, self.g_proj1_bias)
         g = ops.kda_gate(g_raw.view(T, Hl, K), self.A_log, self.dt_bias, cfg.safe_gate, cfg.lower_bound)
@@ -317,8 +317,8 @@ class HybridLayer(nn.Module):
             o, final = self.attn(h, cu_seqlens, initial_state)
         else:
             o, final = self.attn(h, cu_seqlens, positions), None
-        x = x + o
-        x = x + self.ffn(self.ffn_norm(x))
+        x, h2 = ops.add_rmsnorm(x, o, self.ffn_norm.weight, self.ffn_norm.eps)     # x + o and its norm in one pass
+        x = x + self.ffn(h2)
         return x, final
 
 

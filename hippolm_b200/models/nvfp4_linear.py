@@ -135,6 +135,8 @@ class NVFP4Linear(nn.Module):
     def weight_changed(self) -> None:
         """Every writer of the stored weight calls this (optimizer kernels, chunk commits, checkpoint loads)."""
         self._w_version += 1
+        from ..ops import fp4_gemm
+        fp4_gemm.weights_changed()
 
     def transposed_operands(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """NVFP4 encoding of W^T ([in_features, out_features], blocks along out_features) for the dX product."""

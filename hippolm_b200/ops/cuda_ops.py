@@ -154,6 +154,46 @@ def rmsnorm(x, w, eps):
     return _RMSNorm.apply(x, w, eps)
 
 
+class _AddRMSNorm(torch.autograd.Function):
+    """(x + res, rmsnorm(x + res) * w) in one kernel; backward folds the gradient of the sum that arrives through the
+    residual path into the norm's backward kernel and hands the same tensor to both addends."""
+
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        xs = x.shape
+        D = xs[-1]
+        x2, r2 = _bf(x).reshape(-1, D).contiguous(), _bf(res).reshape(-1, D).contiguous()
+        T = x2.shape[0]
+        ssum, y = torch.empty_like(x2), torch.empty_like(x2)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        check(lib().hippo_add_rmsnorm_fwd(ptr(x2), ptr(r2), ptr(_bf(w)), ptr(ssum), ptr(y), ptr(rstd), _c.c_longlong(T), D,
+                                          _c.c_float(eps), stream_ptr()), "add_rmsnorm_fwd")
+        ctx.save_for_backward(ssum, w, rstd)
+        ctx.xs, ctx.xdtype = xs, x.dtype
+        return ssum.view(xs).to(x.dtype), y.view(xs).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dsum, dy):
+        ssum, w, rstd = ctx.saved_tensors
+        T, D = ssum.shape
+        if dy is None:
+            return dsum, dsum, None, None
+        dy2 = _bf(dy).reshape(T, D).contiguous()
+        dres = _bf(dsum).reshape(T, D).contiguous() if dsum is not None else None
+        dx = torch.empty_like(ssum)
+        nb = min(T, 148 * 4)
+        part = torch.empty((nb, D), dtype=torch.float32, device=ssum.device)
+        dw = torch.empty(D, dtype=torch.float32, device=ssum.device)
+        check(lib().hippo_rmsnorm_bwd_res(ptr(ssum), ptr(_bf(w)), ptr(dy2), ptr(dres), ptr(rstd), ptr(dx), ptr(part), ptr(dw),
+                                          _c.c_longlong(T), D, nb, stream_ptr()), "rmsnorm_bwd_res")
+        d = dx.view(ctx.xs).to(ctx.xdtype)
+        return d, d, dw.to(w.dtype), None
+
+
+def add_rmsnorm(x, res, w, eps):
+    return _AddRMSNorm.apply(x, res, w, eps)
+
+
 class _GatedRMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, o, gate, w, eps):
@@ -331,8 +371,12 @@ def short_conv_silu(x, weight, bias, cu_seqlens):
 
 # ----------------------------------------------------------------------------- attention / KDA / AttnRes
 class _KDAPrologue(torch.autograd.Function):
+    """q / k / v / beta from the fused projection, plus (``fg_w`` > 0) a contiguous copy of the ``fg_w`` columns at
+    ``off_fg`` (the inputs of the low-rank gate projections): their gradient comes back here and is written into the
+    one projection gradient, instead of a zero-filled full-width tensor per slice plus an add."""
+
     @staticmethod
-    def forward(ctx, proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu):
+    def forward(ctx, proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu, off_fg, fg_w):
         proj = _bf(proj).contiguous()
         T, ld = proj.shape
         dev = proj.device
@@ -343,28 +387,48 @@ class _KDAPrologue(torch.autograd.Function):
                                            _c.c_float(scale), _c.c_float(beta_mul), int(apply_silu), stream_ptr()),
               "kda_prologue_fwd")
         ctx.save_for_backward(proj, qr, kr)
-        ctx.meta = (H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu)
-        return q, k, v, beta
+        ctx.meta = (H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu, off_fg, fg_w)
+        fg = proj[:, off_fg:off_fg + fg_w].contiguous() if fg_w > 0 else proj.new_empty((T, 0))
+        return q, k, v, beta, fg
 
     @staticmethod
-    def backward(ctx, dq, dk, dv, dbeta):
+    def backward(ctx, dq, dk, dv, dbeta, dfg):
         proj, qr, kr = ctx.saved_tensors
-        H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu = ctx.meta
+        H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu, off_fg, fg_w = ctx.meta
         T, ld = proj.shape
-        dproj = torch.zeros_like(proj)
-        dq = dq.float().contiguous() if dq is not None else torch.zeros((T, H, K), device=proj.device)
-        dk = dk.float().contiguous() if dk is not None else torch.zeros((T, H, K), device=proj.device)
-        dv = _bf(dv).contiguous() if dv is not None else torch.zeros((T, H, K), dtype=torch.bfloat16, device=proj.device)
-        dbeta = dbeta.float().contiguous() if dbeta is not None else torch.zeros((T, H), device=proj.device)
+        dev = proj.device
+        # the kernel writes the q, k, v and beta columns; the gate columns and whatever else the projection carries
+        # (padding) are filled here
+        covered = sorted([(off_q, H * K), (off_k, H * K), (off_v, H * K), (off_b, H)] + ([(off_fg, fg_w)] if fg_w > 0 else []))
+        dproj = torch.empty_like(proj)
+        pos = 0
+        for o, n in covered:
+            if o > pos:
+                dproj[:, pos:o].zero_()
+            pos = max(pos, o + n)
+        if pos < ld:
+            dproj[:, pos:].zero_()
+        if fg_w > 0:
+            if dfg is not None:
+                dproj[:, off_fg:off_fg + fg_w].copy_(dfg)
+            else:
+                dproj[:, off_fg:off_fg + fg_w].zero_()
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        dq = _bf(dq).contiguous() if dq is not None else torch.zeros((T, H, K), **bf)
+        dk = _bf(dk).contiguous() if dk is not None else torch.zeros((T, H, K), **bf)
+        dv = _bf(dv).contiguous() if dv is not None else torch.zeros((T, H, K), **bf)
+        dbeta = dbeta.float().contiguous() if dbeta is not None else torch.zeros((T, H), device=dev)
         check(lib().hippo_kda_prologue_bwd(ptr(proj), _c.c_longlong(ld), H, K, off_q, off_k, off_v, off_b, ptr(dq),
                                            ptr(dk), ptr(dv), ptr(dbeta), ptr(qr), ptr(kr), ptr(dproj),
                                            _c.c_longlong(T), _c.c_float(scale), _c.c_float(beta_mul),
                                            int(apply_silu), stream_ptr()), "kda_prologue_bwd")
-        return (dproj,) + (None,) * 9
+        return (dproj,) + (None,) * 11
 
 
-def kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu):
-    return _KDAPrologue.apply(proj, H, K, off_q, off_k, off_v, off_b, float(scale), float(beta_mul), bool(apply_silu))
+def kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu, off_fg=0, fg_w=0):
+    out = _KDAPrologue.apply(proj, H, K, off_q, off_k, off_v, off_b, float(scale), float(beta_mul), bool(apply_silu),
+                             int(off_fg), int(fg_w))
+    return out if fg_w > 0 else out[:4]
 
 
 def kda(q, k, v, g, beta, scale, initial_state, cu_seqlens, use_qk_l2norm, skip_saved=False, mode="chunk"):

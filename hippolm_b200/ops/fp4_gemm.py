@@ -18,12 +18,36 @@ def tile_scales(scales: torch.Tensor, rows: int, K: int) -> torch.Tensor:
     return out
 
 
+_EPOCH = [0]            # bumped whenever a stored NVFP4 weight is rewritten (NVFP4Linear.weight_changed)
+_TILED = {}             # id(scales tensor) -> (weakref to it, epoch, tiled scales)
+
+
+def weights_changed() -> None:
+    """Called by every writer of a stored NVFP4 weight: tiled copies of weight scales are rebuilt at their next use."""
+    _EPOCH[0] += 1
+
+
+def tile_weight_scales(scales: torch.Tensor, rows: int, K: int) -> torch.Tensor:
+    """``tile_scales`` for the scales of a WEIGHT, cached while the very same tensor object is alive and no stored weight
+    has been rewritten: the re-tiling then runs once per optimizer step instead of once per GEMM call. Temporaries
+    (freshly quantised master weights) never hit: their tensor objects die with the call."""
+    import weakref
+    hit = _TILED.get(id(scales))
+    if hit is not None and hit[0]() is scales and hit[1] == _EPOCH[0]:
+        return hit[2]
+    tiled = tile_scales(scales, rows, K)
+    if len(_TILED) > 4096:
+        _TILED.clear()
+    _TILED[id(scales)] = (weakref.ref(scales), _EPOCH[0], tiled)
+    return tiled
+
+
 def fp4_matmul(a_packed, a_scales, a_gs, b_packed, b_scales, b_gs) -> torch.Tensor:
-    """[M, K/2] x [N, K/2]^T with logical scales [*, K/16] and fp32 tensor scales -> bf16 [M, N]."""
+    """[M, K/2] x [N, K/2]^T with logical scales [*, K/16] and fp32 tensor scales -> bf16 [M, N]. ``b`` is the weight."""
     M, K2 = a_packed.shape
     N = b_packed.shape[0]
     K = K2 * 2
-    sfa, sfb = tile_scales(a_scales, M, K), tile_scales(b_scales, N, K)
+    sfa, sfb = tile_scales(a_scales, M, K), tile_weight_scales(b_scales, N, K)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=a_packed.device)
     check(lib().hippo_gemm_nvfp4(ptr(a_packed), ptr(b_packed), ptr(sfa), ptr(sfb), ptr(a_gs), ptr(b_gs), ptr(out),
                                  M, N, K, C.c_longlong(N), stream_ptr()), "gemm_nvfp4")

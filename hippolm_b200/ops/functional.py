@@ -79,6 +79,14 @@ def rmsnorm(x, weight, eps: float):
     return _ro.rmsnorm(x, weight, eps)
 
 
+def add_rmsnorm(x, res, weight, eps: float):
+    """(x + res, rmsnorm(x + res) * weight): the residual add of a pre-norm layer fused into the norm behind it."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().add_rmsnorm(x, res, weight, eps)
+    s = x + res
+    return s, rmsnorm(s, weight, eps)
+
+
 def swiglu(gate_up):
     if gate_up.is_cuda:
         return _cu().swiglu(gate_up)
@@ -109,17 +117,20 @@ def short_conv_silu(x, weight, bias, cu_seqlens):
 
 # ----------------------------------------------------------------------------- KDA
 def kda_prologue(proj, H: int, K: int, off_q: int, off_k: int, off_v: int, off_b: int, scale: float,
-                 beta_mul: float = 1.0, apply_silu: bool = True):
+                 beta_mul: float = 1.0, apply_silu: bool = True, off_fg: int = 0, fg_w: int = 0):
     """From the fused projection ``[T, n]`` (columns q | k | v | ... | b): q = l2norm(silu(q)) * scale,
-    k = l2norm(silu(k)), v = silu(v) as ``[T, H, K]`` and beta = sigmoid(b) * beta_mul as ``[T, H]`` fp32."""
+    k = l2norm(silu(k)), v = silu(v) as ``[T, H, K]`` and beta = sigmoid(b) * beta_mul as ``[T, H]`` fp32. With
+    ``fg_w`` > 0 a fifth result: the ``fg_w`` columns at ``off_fg`` (inputs of the low-rank gate projections)."""
     if proj.is_cuda:
-        return _cu().kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu)
+        return _cu().kda_prologue(proj, H, K, off_q, off_k, off_v, off_b, scale, beta_mul, apply_silu, off_fg, fg_w)
     T = proj.shape[0]
     act = F.silu if apply_silu else (lambda t: t)
     q = _rk.l2norm(act(proj[:, off_q:off_q + H * K]).reshape(T, H, K)) * scale
     k = _rk.l2norm(act(proj[:, off_k:off_k + H * K]).reshape(T, H, K))
     v = act(proj[:, off_v:off_v + H * K]).reshape(T, H, K)
     beta = torch.sigmoid(proj[:, off_b:off_b + H].float()) * beta_mul
+    if fg_w > 0:
+        return q, k, v, beta, proj[:, off_fg:off_fg + fg_w]
     return q, k, v, beta
 
 

@@ -24,7 +24,9 @@ def backward(ctx, do, dfin):
     dSst = torch.empty((NC, H, DK, DK), **bf)
     dAqk, dKK = torch.empty((NC, H, 64, 64), **bf), torch.empty((NC, H, 64, 64), **bf)
     dq_acc, dk_acc, dG_acc = (torch.empty((NC, H, 64, DK), **f32) for _ in range(3))
-    dq, dk, dg = (torch.empty((T, H, DK), **f32) for _ in range(3))
+    # dq / dk leave the last kernel as bf16 (the dtype of q / k): no cast between it and the consumer
+    dq, dk = (torch.empty((T, H, DK), **bf) for _ in range(2))
+    dg = torch.empty((T, H, DK), **f32)
     dv = torch.empty((T, H, DK), **bf)
     dbeta = torch.empty((T, H), **f32)
     dh0 = torch.empty((N, H, DK, DK), **f32) if ctx.has_h0 else None

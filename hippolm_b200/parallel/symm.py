@@ -168,7 +168,7 @@ class FusedWorkspace:
         check(lib().hippo_nvfp4_quant_push(ptr(x), C.c_longlong(x.stride(0)), rows, K, ptr(gs), _ptr_arr(ptrs),
                                            _ptr_arr(self._row_ptrs(row)), self.world, self.rank, stream_ptr()),
               "nvfp4_quant_push")
-        sfb = fp4_gemm.tile_scales(scales, N, K)
+        sfb = fp4_gemm.tile_weight_scales(scales, N, K)
         y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
         gsw = global_scale.float().contiguous()
         check(lib().hippo_allgather_gemm_nvfp4(ptr(buf), C.c_void_p(self._row_ptrs(row)[self.rank]), self.world, self.rank,
@@ -199,7 +199,7 @@ class FusedWorkspace:
                 or T * N > self.max_tokens * self.max_width:
             return None
         xp, xs, xg = nvfp4_cuda.quantize(x.contiguous())
-        sfa, sfb = fp4_gemm.tile_scales(xs, T, K), fp4_gemm.tile_scales(scales, N, K)
+        sfa, sfb = fp4_gemm.tile_scales(xs, T, K), fp4_gemm.tile_weight_scales(scales, N, K)
         par = self.rs_n & 1
         self.rs_n += 1
         row = 2 + par

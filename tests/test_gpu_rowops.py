@@ -92,3 +92,56 @@ def test_short_conv_silu_varlen():
     x2, w2 = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
     y2 = rk.short_conv_silu(x2, w2, None, cu); y2.backward(dy.float())
     _close(y, y2, 1e-2); _close(x.grad, x2.grad, 2e-2); _close(w.grad, w2.grad, 2e-2)
+
+
+@pytest.mark.parametrize("T,D", [(333, 4096), (64, 256)])
+def test_add_rmsnorm_matches_add_then_norm(T, D):
+    """Residual add fused into the norm behind it: both results and all three gradients (the sum is consumed twice, once
+    by the norm and once by whatever follows on the residual path) against the unfused fp32 composition."""
+    from hippolm_b200 import ops
+    from hippolm_b200.ref import ops as ro
+    torch.manual_seed(T)
+    x = torch.randn(T, D, device="cuda").bfloat16().requires_grad_(True)
+    r = torch.randn(T, D, device="cuda").bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16().requires_grad_(True)
+    ds, dy = torch.randn(T, D, device="cuda").bfloat16(), torch.randn(T, D, device="cuda").bfloat16()
+    s, y = ops.add_rmsnorm(x, r, w, 1e-6)
+    torch.autograd.backward([s, y], [ds, dy])
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    sr = xr + rr
+    yr = ro.rmsnorm(sr, wr, 1e-6)
+    torch.autograd.backward([sr, yr], [ds.float(), dy.float()])
+    _close(s, sr, 1e-2); _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 2e-2); _close(r.grad, rr.grad, 2e-2); _close(w.grad, wr.grad, 2e-2)
+    assert torch.equal(x.grad, r.grad)
+    # only the norm output used: the residual-path gradient is absent
+    x2 = x.detach().clone().requires_grad_(True)
+    _, y2 = ops.add_rmsnorm(x2, r.detach(), w.detach(), 1e-6)
+    y2.backward(dy)
+    x3 = x.detach().float().requires_grad_(True)
+    ro.rmsnorm(x3 + r.detach().float(), w.detach().float(), 1e-6).backward(dy.float())
+    _close(x2.grad, x3.grad, 2e-2)
+
+
+def test_kda_prologue_gate_columns_pass_through():
+    """The low-rank gate inputs leave the prologue as a contiguous copy and their gradient comes back through it into the
+    one projection gradient (padding columns zero), like slicing the projection would."""
+    from hippolm_b200 import ops
+    torch.manual_seed(3)
+    T, H, K = 200, 4, 128
+    key = H * K
+    o_fg, fgw = 3 * key, 2 * K
+    n = o_fg + fgw + H + 28                                       # 28 padding columns
+    proj = (0.5 * torch.randn(T, n, device="cuda")).bfloat16().requires_grad_(True)
+    q, k, v, beta, fg = ops.kda_prologue(proj, H, K, 0, key, 2 * key, o_fg + fgw, K ** -0.5, 2.0, True, o_fg, fgw)
+    assert fg.is_contiguous() and torch.equal(fg, proj.detach()[:, o_fg:o_fg + fgw])
+    gs = [torch.randn_like(t.float()).to(t.dtype) for t in (q, k, v, beta, fg)]
+    torch.autograd.backward([q, k, v, beta, fg], gs)
+    pc = proj.detach().cpu().float().requires_grad_(True)
+    outs = ops.kda_prologue(pc, H, K, 0, key, 2 * key, o_fg + fgw, K ** -0.5, 2.0, True, o_fg, fgw)
+    torch.autograd.backward(list(outs), [g.cpu().float() for g in gs])
+    for a, b in zip((q, k, v, beta), outs[:4]):
+        _close(a.cpu(), b, 2e-2)
+    _close(proj.grad.cpu(), pc.grad, 3e-2)
+    assert float(proj.grad[:, o_fg + fgw + H:].abs().max()) == 0.0
+    assert torch.equal(proj.grad[:, o_fg:o_fg + fgw], gs[4])

@@ -3,6 +3,12 @@ accumulator / optimizer math) in-tree with nvcc / g++. No torch headers are invo
 raw device pointers and a stream, Python calls them through ctypes.
 
     python -m hippolm_b200.csrc.build [--force] [--verbose]
+    HIPPO_DEBUG_BOUNDS=1 python -m hippolm_b200.csrc.build     # second library with checked data-dependent indices
+
+With ``HIPPO_DEBUG_BOUNDS=1`` in the environment the kernels are compiled with ``-DHIPPO_DEBUG_BOUNDS`` into
+``libhippo_kernels_dbg.so`` and ``ops/_ext.py`` loads that library: token / target ids and positions are range-checked on
+the device, a bad one is recorded in the status word (``_ext.device_status()``: code 8, detail = which check) and the
+access is skipped. This stands in for a memory checker where none can be run.
 """
 from __future__ import annotations
 
@@ -14,7 +20,8 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "..", "lib")
-KERNEL_LIB = os.path.abspath(os.path.join(OUT_DIR, "libhippo_kernels.so"))
+DEBUG_BOUNDS = os.environ.get("HIPPO_DEBUG_BOUNDS", "0") not in ("", "0")
+KERNEL_LIB = os.path.abspath(os.path.join(OUT_DIR, "libhippo_kernels_dbg.so" if DEBUG_BOUNDS else "libhippo_kernels.so"))
 HOST_LIB = os.path.abspath(os.path.join(OUT_DIR, "libhippo_host.so"))
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-rdc=true"]
@@ -51,9 +58,9 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(KERNEL_LIB) and os.path.exists(stamp) and open(stamp).read() == dig:
         return KERNEL_LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    obj_dir = os.path.join(OUT_DIR, "obj")
+    obj_dir = os.path.join(OUT_DIR, "obj_dbg" if DEBUG_BOUNDS else "obj")
     os.makedirs(obj_dir, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    extra = (["-Xptxas", "-v"] if verbose else []) + (["-DHIPPO_DEBUG_BOUNDS"] if DEBUG_BOUNDS else [])
 
     def compile_one(src):
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")

@@ -8,9 +8,7 @@
 // range from the gradient mirror of the rank whose token shard holds them and accumulates in fp32 (atomicAdd: several
 // tokens may share an id). With one rank both kernels are a plain gather / scatter-add of local memory.
 // The reference does an all-reduce of a masked full lookup (src/models/tp_model/embed.py:44-61).
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
+#include "sm100.cuh"
 
 namespace hippo {
 typedef __nv_bfloat16 bf16;
@@ -23,6 +21,7 @@ __global__ void embed_gather_kernel(const long long* __restrict__ ids, PeerPtrs 
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (long long t = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); t < n; t += (long long)gridDim.x * wpb) {
     const long long id = ids[t];
+    (void)HIPPO_IN_BOUNDS(id, (long long)world * Vl, 1);       // debug build: an id outside the vocabulary is recorded
     const int owner = (id >= 0 && id < (long long)world * Vl) ? (int)(id / Vl) : -1;
     uint4* dst = (uint4*)(out + t * D);
     if (owner < 0) {
@@ -47,6 +46,7 @@ __global__ void embed_grad_kernel(const long long* __restrict__ ids, PeerPtrs gr
                                   long long v0, int Vl, int D, float* __restrict__ dw, long long T) {
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (long long t = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += (long long)gridDim.x * wpb) {
+    (void)HIPPO_IN_BOUNDS(ids[t], (long long)world * Vl, 2);
     const long long local = ids[t] - v0;
     if (local < 0 || local >= Vl) continue;
     const int src_rank = (int)(t / rows_per_rank);

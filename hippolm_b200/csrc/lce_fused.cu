@@ -50,7 +50,7 @@ ce_stats_push_kernel(const float* __restrict__ z, const long long* __restrict__ 
     float t = 0.f;
     for (int k = 0; k < (blockDim.x >> 5); ++k) t += sh[k];
     const long long tg = target[row];
-    const float4 v = make_float4(m, t, tg >= 0 ? zr[tg] : 0.f, 0.f);
+    const float4 v = make_float4(m, t, (tg >= 0 && HIPPO_IN_BOUNDS(tg, V, 4)) ? zr[tg] : 0.f, 0.f);
     for (int d = 0; d < cp.world; ++d) {
       const int peer = (cp.rank + d) % cp.world;
       cp.stats_peer[peer][(long long)cp.rank * cp.max_rows + row] = v;

@@ -3,6 +3,7 @@
 // Reference behaviour: src/models/ops/attn_res_triton.py:108-521, param_offload/cpu_fused.py:532-583,
 // src/models/ops/nvfp4_quant_triton.py:77-142, fla/modules/fused_linear_cross_entropy.py:43-358.
 #include <cuda_runtime.h>
+#include "sm100.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
@@ -322,7 +323,7 @@ __global__ void ce_stats_kernel(const float* __restrict__ z, const long long* __
     for (int k = 0; k < (blockDim.x >> 5); ++k) t += sh[k];
     mx[row] = m; se[row] = t;
     long long tg = target[row];
-    tz[row] = tg >= 0 ? zr[tg] : 0.f;
+    tz[row] = (tg >= 0 && HIPPO_IN_BOUNDS(tg, V, 3)) ? zr[tg] : 0.f;     // targets < 0 are ignored rows
   }
 }
 // dz = (exp(z - lse) - onehot(target)) * w_row  as bf16, w_row = valid / n_valid

@@ -3,6 +3,7 @@
 // vector accesses. Each forward has its backward here. They replace the reference's Triton kernels
 // (fla/modules/layernorm.py:194-458, fused_norm_gate.py:35-330, l2norm.py:25-112, gate.py:143-417).
 #include <cuda_runtime.h>
+#include "sm100.cuh"
 #include <atomic>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -678,7 +679,8 @@ short_conv_fwd_vec_kernel(const bf16* __restrict__ x, long long ldx, const bf16*
     if (t >= 0) v = *(const uint4*)(x + t * ldx + cg * 8);
     unpack8(v, win[W - 1]);
     if (t < t_lo) continue;
-    const int p = pos[t];
+    int p = pos[t];
+    if (!HIPPO_IN_BOUNDS(p, t + 1, 5)) p = 0;                // a position cannot exceed the token index
     float o[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {

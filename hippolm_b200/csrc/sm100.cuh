@@ -15,13 +15,24 @@ extern __device__ Status g_status;
 
 enum StatusCode : int {
   kOk = 0, kWaitTmaFull = 1, kWaitSmemEmpty = 2, kWaitTmemFull = 3, kWaitTmemEmpty = 4,
-  kWaitPeerFlag = 5, kBadArgument = 6, kWaitGeneric = 7,
+  kWaitPeerFlag = 5, kBadArgument = 6, kWaitGeneric = 7, kBadIndex = 8,
 };
 
 __device__ __forceinline__ void report(int code, int detail) {
   if (atomicCAS(&g_status.code, 0, code) == 0) { g_status.detail = detail; g_status.block = blockIdx.x; }
   atomicAdd(&g_status.count, 1);
 }
+
+// Debug build (-DHIPPO_DEBUG_BOUNDS, `HIPPO_DEBUG_BOUNDS=1 python -m hippolm_b200.csrc.build`): every index that comes
+// from DATA (token ids, target ids, positions) is checked before it is used; a bad one is recorded in the status word
+// (code kBadIndex, detail = `tag`) and the access is skipped, so the run goes on and the host reads where it happened.
+// In the normal build the check compiles to `true`.
+#ifdef HIPPO_DEBUG_BOUNDS
+#define HIPPO_IN_BOUNDS(i, n, tag) \
+  (((unsigned long long)(i) < (unsigned long long)(n)) ? true : (::hippo::report(::hippo::kBadIndex, (tag)), false))
+#else
+#define HIPPO_IN_BOUNDS(i, n, tag) true
+#endif
 
 constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at 2 GHz; never reached in a healthy run
 

@@ -17,7 +17,9 @@ _DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 
 
 def lib_path() -> str:
-    return os.path.join(_DIR, "libhippo_kernels.so")
+    """``HIPPO_DEBUG_BOUNDS=1`` selects the library built with checked data-dependent indices (see csrc/build.py)."""
+    dbg = os.environ.get("HIPPO_DEBUG_BOUNDS", "0") not in ("", "0")
+    return os.path.join(_DIR, "libhippo_kernels_dbg.so" if dbg else "libhippo_kernels.so")
 
 
 def is_loaded() -> bool:

@@ -45,6 +45,9 @@ def parse():
     p.add_argument("--ffn_bwd", type=str, default="fp4",
                    help="NVFP4 FFN backward: fp4 (dX and dW on the FP4 tensor cores, the benchmarked configuration: "
                         "configs/hybrid_7b_tp8.yml) | fp4_dx | bf16 (backward on the dequantised weight; A/B switch)")
+    p.add_argument("--lce_epilogue", type=int, default=-1,
+                   help="softmax statistics of the loss head in the logits GEMM epilogue (bf16 logits): 1 | 0 | -1 = the "
+                        "benchmarked default (off)")
     p.add_argument("--no_kda", dest="kda", action="store_false",
                    help="skip the standalone chunked-KDA timing that rank 0 adds to the JSON line (outside the timed region)")
     p.add_argument("--kda_only", action="store_true", help="print only the standalone chunked-KDA timing")
@@ -165,6 +168,7 @@ def main():
     args.lr_warmup_steps = 200          # WSD warm-up keeps the first steps stable on random-init weights
     args.precision = None
     args.fused_comm = not a.no_fused_comm
+    args.lce_epilogue_stats = (a.lce_epilogue == 1)
     args.seed = 0
     gb_tokens = args.batch_size * args.seq_len
     loader = synthetic_loader(args.batch_size, args.seq_len, args.vocab_size, seed=0,
@@ -241,7 +245,8 @@ def main():
                "config": {"model": name, "global_batch": args.batch_size, "seq_len": args.seq_len,
                           "parallelism": f"tp{world}+sp", "micro_batch_tokens": a.micro_batch_tokens,
                           "optimizer": "muon+adamw", "l2": "inputs larger than L2 (no explicit flush)",
-                          "fused_comm": bool(ctx.extras.get("fused_comm", False)), "ffn_backward": a.ffn_bwd},
+                          "fused_comm": bool(ctx.extras.get("fused_comm", False)), "ffn_backward": a.ffn_bwd,
+                          "lce_epilogue_stats": bool(args.lce_epilogue_stats)},
                "clocks": clocks,
                "e2e": {"value": gb_tokens / (e2e_ms_step / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms_step},

@@ -70,6 +70,10 @@ class HippoConfig:
     # memory policy
     gradient_checkpointing: bool = False
     lce_num_chunks: int = 0                 # token chunks of the fused linear+CE head; 0 = sized automatically
+    # CUDA only: the logits GEMM stores bf16 logits and takes the softmax statistics (row max, sum exp, target logit) from
+    # its accumulator in the epilogue, the gradient overwrites the logits in place; false = fp32 logits in global memory
+    # and a separate statistics pass over them
+    lce_epilogue_stats: bool = False
     # derived
     block_size: int = field(init=False, default=0)
 

@@ -52,6 +52,11 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc,
 // role of gemm_comm.cuh instead of computing; the GEMM clusters walk the 256-row pair tiles shard by shard in arrival
 // order, every CTA's TMA producer acquiring (bounded) the arrival counter of ITS 128-row block before the block's first
 // load; tiles of the own shard read x_local in place through tmOwn. All loads are plain TMA loads of local memory.
+// COMM == EPI_LCE: no collective. The logits GEMM of the linear + cross-entropy head: the epilogue rounds every accumulator
+// row to bf16 (the stored logits), and, while the 256 values of the row are in registers, folds them into the row's
+// running (max, sum exp) of this tile and picks the logit at the row's target column; the per-tile pairs go to
+// p.lce_part[tile column][row] and are merged per row by ce_part_merge_kernel (lce_fused.cu). The fp32 logits never
+// reach global memory and no separate pass over them computes the statistics.
 template <bool A_KMAJOR, bool B_KMAJOR, int COMM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p,
@@ -103,7 +108,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
     const int GROUP = 8;                  // 8 pair-tiles (2048 rows) share each column sweep
     int tiles_m = p.tiles_m, base_m = 0;
-    if (COMM != COMM_NONE) {              // shard by shard: AG in arrival order (own, rank-1, ...), RS remote owners first
+    if (COMM == COMM_AG || COMM == COMM_RS) {   // shard by shard: AG in arrival order (own, rank-1, ...), RS remote owners first
       const int tms = cp.rows_per_shard / (2 * BM);
       const int per_shard = tms * p.tiles_n;
       const int si = t / per_shard;
@@ -274,6 +279,39 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
         continue;
       }
+      if (COMM == EPI_LCE) {
+        // thread = row: online (max, sum exp) over the tile's columns of the bf16-rounded logits, target logit pick
+        float mrow = -INFINITY, srow = 0.f, tzv = 0.f;
+        const long long tg = row < p.M ? p.lce_target[row] : -1;
+        const int tcol = (tg >= (long long)tn * BN && tg < (long long)(tn + 1) * BN) ? (int)(tg - (long long)tn * BN) : -1;
+        pe.alpha = 1.f;                                                      // applied here, before the rounding
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int col0 = tn * BN + c;
+          if (col0 >= p.N) break;                                            // uniform over the warp
+          uint32_t r[32];
+          EpiPrefetch pre;
+          tmem_ld_32x32(taddr + c, r);
+          tc_wait_ld();
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float f = __bfloat162float(__float2bfloat16(__uint_as_float(r[j]) * p.alpha));
+            r[j] = __float_as_uint(f);
+            if (col0 + j < p.N) cm = fmaxf(cm, f);
+            if (c + j == tcol) tzv = f;
+          }
+          if (cm > mrow) { srow *= __expf(mrow - cm); mrow = cm; }           // mrow = -inf: srow is 0 and stays 0
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) srow += __expf(__uint_as_float(r[j]) - mrow);
+          epi_store(pe, r, row, col0, pre);                                  // exact: the values are bf16 already
+        }
+        if (row < p.M) {
+          p.lce_part[(long long)tn * p.M + row] = make_float2(mrow, srow);
+          if (tcol >= 0) p.lce_tz[row] = tzv;
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -283,6 +321,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         epi_prefetch(pe, row, col0, pre);         // addends travel while the TMEM load completes
         tc_wait_ld();
         epi_store(pe, r, row, col0, pre);
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -427,7 +466,31 @@ int launch_gemm_reduce_scatter_2sm(const void* A, const void* B, int layout, lon
   return -1;
 }
 
+// Logits GEMM of the linear + cross-entropy head (C = A B^T, A [M, K], B [N, K], C bf16) with the EPI_LCE epilogue.
+int launch_gemm_lce_2sm(const void* A, const void* B, long long lda, long long ldb, const GemmParams& p, cudaStream_t stream) {
+  CommParams cp = {};
+  return sm2::launch<true, true, EPI_LCE>(A, B, lda, ldb, p, 0, cp, stream);
+}
+
 }  // namespace hippo
+
+// Logits of one token chunk with their softmax statistics from the GEMM epilogue.
+//   C[M, N] (bf16, pitch ldc)  = A[M, K] B[N, K]^T
+//   part[ceil(N / 256)][M]     = per 256-column tile: (max, sum of exp(z - max)) of the row's stored (bf16) logits
+//   tz[M]                      = stored logit at column target[row]; rows with target[row] < 0 are left untouched
+// target[row] must be -1 or a column in [0, N).
+extern "C" int hippo_gemm_bf16_lce(const void* A, const void* B, void* C, float* part, const long long* target, float* tz,
+                                   int M, int N, int K, long long lda, long long ldb, long long ldc, void* stream) {
+  using namespace hippo;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  if ((ldc % 8) || ((uintptr_t)C & 15) || ((uintptr_t)part & 7) || !part || !target || !tz) return -3;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = 0; p.accumulate = 0; p.alpha = 1.f;
+  p.Cin = nullptr; p.ldcin = 0; p.beta = 0.f; p.tiles_m = p.tiles_n = 0; p.sym_lower = 0; p.ksplit = 0;
+  p.lce_part = (float2*)part; p.lce_target = target; p.lce_tz = tz;
+  return launch_gemm_lce_2sm(A, B, lda, ldb, p, (cudaStream_t)stream);
+}
 
 // Explicit entry point of the CTA-pair kernel (tests and benches compare it with the one-CTA kernel).
 // layout code: 0 = NT (A[M,K], B[N,K]); 1 = NN (A[M,K], B[K,N]); 2 = TN (A[K,M], B[K,N]); 3 = TT (A[K,M], B[N,K])

@@ -13,7 +13,9 @@ namespace hippo {
 //   COMM_RS  GEMM -> reduce-scatter. The epilogue stores each partial tile into the staging slot of the
 //            rank that owns those rows (P2P stores) and bumps that rank's counter; after its last tile
 //            every CTA joins the reduction of the local rows (wait for all sources, sum the slots).
-constexpr int COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2;
+//   EPI_LCE  no collective: a plain GEMM whose epilogue also emits per-tile softmax statistics (CTA-pair kernel only; the
+//            logits GEMM of the linear + cross-entropy head, see GemmParams::lce_part).
+constexpr int COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2, EPI_LCE = 3;
 constexpr int MAX_RANKS = 8;
 
 struct CommParams {

@@ -18,6 +18,11 @@ struct GemmParams {
   int sym_lower;       // CTA-pair kernel: skip the 256x256 tiles above the diagonal (square symmetric output)
   int ksplit;          // CTA-pair kernel: > 1 = the contraction is cut into ksplit slices, work item = (tile, slice), slice s
                        // writes its fp32 partial product to C + s * M * ldc (C is then a [ksplit * M, ldc] fp32 workspace)
+  // CTA-pair kernel, EPI_LCE mode (logits of the linear + cross-entropy head): besides the bf16 logits, the epilogue emits
+  // the softmax statistics of every row of every 256-column tile, taken from the accumulator while it is in registers.
+  float2* lce_part = nullptr;              // [tiles_n][M]: (max, sum of exp(z - max)) over the tile's columns of the bf16-rounded logits
+  const long long* lce_target = nullptr;   // [M]: target column of the row in this GEMM's N range, or -1
+  float* lce_tz = nullptr;                 // [M]: logit at the target column; written only for rows whose target is >= 0
 };
 
 #ifdef __CUDACC__

@@ -457,7 +457,7 @@ class _VocabParallelLCE(torch.autograd.Function):
     (``fla/modules/fused_linear_cross_entropy.py:516-679``). x arrives as the SP token shard."""
 
     @staticmethod
-    def forward(ctx, x_shard, weight, targets, v0, num_chunks, n_valid_total):
+    def forward(ctx, x_shard, weight, targets, v0, num_chunks, n_valid_total, epilogue_stats=False):
         m = get_mesh()
         x = all_gather_dim0(x_shard, m.tp_group, m.tp)                  # [T, D]
         T, D = x.shape
@@ -471,23 +471,42 @@ class _VocabParallelLCE(torch.autograd.Function):
         dw = torch.zeros(Vl, D, dtype=torch.float32, device=x.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
         loss_sum_raw = torch.zeros(1, dtype=torch.float32, device=x.device)     # filled by the fused CE kernels
+        _cuda_ops = None
+        if x.is_cuda:
+            from ..ops import cuda_ops as _cuda_ops
+        # statistics in the logits GEMM epilogue: bf16 logits, overwritten by their gradient (CUDA, 16-byte aligned rows)
+        epi = bool(epilogue_stats) and x.is_cuda and _cuda_ops.lce_epilogue_supported(x, weight)
         if num_chunks > 0:
             cs = max(1, (T + num_chunks - 1) // num_chunks)
         else:
-            # automatic: the largest chunk whose fp32 logits tile [cs, V/w] stays near 2 GiB. Bigger chunks mean
-            # fewer read-modify-write passes over the fp32 dW accumulator and deeper (K = cs) dW GEMMs.
-            cs = max(1024, ((1 << 31) // (4 * Vl)) // 128 * 128)
+            # automatic: the largest chunk whose logits tile [cs, V/w] (fp32, or bf16 on the epilogue path) stays near
+            # 2 GiB. Bigger chunks mean fewer read-modify-write passes over the fp32 dW accumulator and deeper
+            # (K = cs) dW GEMMs.
+            cs = max(1024, ((1 << 31) // ((2 if epi else 4) * Vl)) // 128 * 128)
             cs = min(cs, T)
         ws = None
         if m.tp > 1 and x.is_cuda:
             from ..parallel import fused as _fused
-            from ..ops import cuda_ops as _cuda_ops
             ws = _fused.workspace()
             if ws is not None and min(cs, T) > ws.lce_rows:
                 ws = None
+        if epi and m.tp > 1 and ws is None:
+            epi = False                                  # the cross-rank merge of the epilogue path lives in the workspace kernels
         for s in range(0, T, cs):
             e = min(T, s + cs)
             xc = x[s:e]
+            if epi:
+                # logits GEMM whose epilogue emits per-tile (max, sum exp) and the target logit; one small merge kernel
+                # (which also carries the statistics to the other ranks), then the gradient in place over the logits
+                z, part, tz, tg = _cuda_ops.lce_logits_stats(xc, weight, local_t[s:e])
+                roww = valid[s:e].float() / nv
+                if ws is not None:
+                    pz = ws.lce_grad_inplace(ws.lce_part_push(part, tz, tg), z, roww, loss_sum_raw)
+                else:
+                    pz = _cuda_ops.lce_grad_inplace_local(z, part, tz, tg, roww, loss_sum_raw)
+                dx[s:e] = ops.gemm_nn(pz, weight)
+                ops.gemm_tn_accumulate(pz, xc, dw)
+                continue
             if ws is not None:
                 # cross-rank max / sum-exp merge inside the kernels: statistics go to every rank by peer stores,
                 # the gradient kernel waits for all sources; no collective call per chunk
@@ -520,7 +539,7 @@ class _VocabParallelLCE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         dx, dw = ctx.saved_tensors
-        return dx * do.to(dx.dtype), dw * do.to(dw.dtype), None, None, None, None
+        return dx * do.to(dx.dtype), dw * do.to(dw.dtype), None, None, None, None, None
 
 
 class LMHeadLoss(nn.Module):
@@ -542,7 +561,7 @@ class LMHeadLoss(nn.Module):
 
     def loss(self, x_shard, targets, n_valid_total):
         return _VocabParallelLCE.apply(x_shard, self.head_weight(), targets, self.v0,
-                                       self.cfg.lce_num_chunks, n_valid_total)
+                                       self.cfg.lce_num_chunks, n_valid_total, self.cfg.lce_epilogue_stats)
 
     def logits(self, x_shard):
         """Inference: full-vocab logits for the gathered tokens (gathers vocab shards)."""

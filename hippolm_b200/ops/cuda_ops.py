@@ -509,6 +509,47 @@ def lce_chunk_grad(z, lse, targets_local, row_weight):
     return dz
 
 
+def lce_epilogue_supported(x, w) -> bool:
+    """The logits GEMM with statistics in its epilogue needs 16-byte aligned bf16 rows on both operands and outputs."""
+    return x.is_cuda and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
+
+
+def lce_logits_stats(x, w, targets_local):
+    """z = x @ w^T stored as bf16, with the softmax statistics taken from the accumulator in the GEMM epilogue
+    (``hippo_gemm_bf16_lce``): returns (z [C, V] bf16, part [ceil(V/256), C, 2] fp32 = per 256-column tile (max, sum exp)
+    of the stored logits, tz [C] fp32 = logit at the target column (undefined where the target is -1), targets as int64)."""
+    C, K = x.shape
+    V = w.shape[0]
+    x = x.to(torch.bfloat16)
+    w = w.to(torch.bfloat16)
+    if x.stride(-1) != 1 or (x.stride(0) % 8) or (x.data_ptr() % 16):
+        x = x.contiguous()
+    if w.stride(-1) != 1 or (w.stride(0) % 8) or (w.data_ptr() % 16):
+        w = w.contiguous()
+    z = torch.empty((C, V), dtype=torch.bfloat16, device=x.device)
+    part = torch.empty(((V + 255) // 256, C, 2), dtype=torch.float32, device=x.device)
+    tz = torch.empty(C, dtype=torch.float32, device=x.device)
+    tg = targets_local.to(torch.int64).contiguous()
+    check(lib().hippo_gemm_bf16_lce(ptr(x), ptr(w), ptr(z), ptr(part), ptr(tg), ptr(tz), C, V, K,
+                                    _c.c_longlong(x.stride(0)), _c.c_longlong(w.stride(0)), _c.c_longlong(V),
+                                    stream_ptr()), "gemm_bf16_lce")
+    return z, part, tz, tg
+
+
+def lce_grad_inplace_local(z, part, tz, tg, row_weight, loss_sum):
+    """Single-rank tail of ``lce_logits_stats``: merges the per-tile statistics of every row, overwrites the bf16 logits
+    ``z`` with dz = (softmax - onehot) * row_weight and adds sum(lse - z_target) of weighted rows to ``loss_sum`` (fp32[1])."""
+    C, V = z.shape
+    stats = torch.empty((C, 4), dtype=torch.float32, device=z.device)
+    sp = (_c.c_void_p * 1)(stats.data_ptr())
+    check(lib().hippo_ce_part_merge(ptr(part), ptr(tz), ptr(tg), _c.c_longlong(C), part.shape[0], sp, None, 1, 0, C,
+                                    stream_ptr()), "ce_part_merge")
+    rw = row_weight.float().contiguous()
+    check(lib().hippo_ce_grad_inplace(ptr(z), ptr(tg), ptr(rw), _c.c_longlong(C), V, ptr(loss_sum), sp, None, 1, 0, C,
+                                      _c.c_uint(0), _c.c_longlong(0), stream_ptr()), "ce_grad_inplace")
+    return z
+
+
 def gemm_tn_accumulate(a, b, out_fp32):
     """out_fp32[N,K] += a[M,N]^T @ b[M,K] (fp32 accumulator tensor updated by the GEMM epilogue)."""
     Mc, N = a.shape

@@ -242,6 +242,34 @@ class FusedWorkspace:
                                         C.c_uint(target), C.c_longlong(self.wait_cycles), stream_ptr()), "ce_grad_merge")
         return dz
 
+    def lce_part_push(self, part: torch.Tensor, tz: torch.Tensor, tg: torch.Tensor):
+        """Statistics from the logits GEMM epilogue (``cuda_ops.lce_logits_stats``): merges the per-tile pairs of every
+        row and pushes (max, sum exp, target logit) to every rank. Returns the handle for lce_grad_inplace."""
+        tiles_n, Cr = part.shape[0], part.shape[1]
+        assert Cr <= self.lce_rows and part.dtype == torch.float32 and part.is_contiguous()
+        par = self.lce_n & 1
+        self.lce_n += 1
+        row = 6 + par
+        target = self._use_row(row, 1, Cr)
+        _, ptrs = self.lce_stats[par]
+        check(lib().hippo_ce_part_merge(ptr(part), ptr(tz), ptr(tg), C.c_longlong(Cr), tiles_n, _ptr_arr(ptrs),
+                                        _ptr_arr(self._row_ptrs(row)), self.world, self.rank, self.lce_rows, stream_ptr()),
+              "ce_part_merge")
+        return (par, row, target, tg)
+
+    def lce_grad_inplace(self, handle, z: torch.Tensor, row_weight: torch.Tensor, loss_sum: torch.Tensor) -> torch.Tensor:
+        """Overwrites the bf16 logits z[C, V/w] with dz from the merged statistics of all ranks; adds sum(lse - z_target)
+        of weighted rows to loss_sum."""
+        par, row, target, tg = handle
+        Cr, V = z.shape
+        assert z.dtype == torch.bfloat16 and z.is_contiguous() and V % 8 == 0
+        _, ptrs = self.lce_stats[par]
+        rw = row_weight.float().contiguous()
+        check(lib().hippo_ce_grad_inplace(ptr(z), ptr(tg), ptr(rw), C.c_longlong(Cr), V, ptr(loss_sum), _ptr_arr(ptrs),
+                                          _ptr_arr(self._row_ptrs(row)), self.world, self.rank, self.lce_rows,
+                                          C.c_uint(target), C.c_longlong(self.wait_cycles), stream_ptr()), "ce_grad_inplace")
+        return z
+
     def check_status(self) -> None:
         st = _ext.device_status()
         if st[0] != 0:

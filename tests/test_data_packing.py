@@ -77,3 +77,28 @@ def test_micro_batch_loss_weighting_equals_full_mean():
         n = (l != -100).sum()
         acc = acc + torch.nn.functional.cross_entropy(logits[s:s + 16], l, ignore_index=-100) * n / total
     assert torch.allclose(acc, full, atol=1e-6)
+
+
+def test_lce_head_matches_cross_entropy_and_epilogue_flag_is_inert_on_cpu():
+    """The chunked linear + cross-entropy head against F.cross_entropy; `lce_epilogue_stats` selects a CUDA-only
+    kernel path, so on CPU tensors it must not change the result."""
+    from hippolm_b200.models.model import _VocabParallelLCE
+    torch.manual_seed(0)
+    T, D, V = 50, 16, 40
+    x = torch.randn(T, D)
+    w = 0.3 * torch.randn(V, D)
+    tg = torch.randint(0, V, (T,))
+    tg[::6] = -100
+    nv = int((tg >= 0).sum())
+    outs = []
+    for epi in (False, True):
+        xi, wi = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        loss = _VocabParallelLCE.apply(xi, wi, tg, 0, 3, nv, epi)
+        loss.backward()
+        outs.append((loss.detach(), xi.grad, wi.grad))
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xr @ wr.t(), tg, ignore_index=-100)
+    ref.backward()
+    for loss, dx, dw in outs:
+        assert torch.allclose(loss, ref, atol=1e-5)
+        assert torch.allclose(dx, xr.grad, atol=1e-5) and torch.allclose(dw, wr.grad, atol=1e-5)

@@ -47,7 +47,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--ffn_nvfp4", type=_bool, default=False); a("--ffn_nvfp4_marlin", type=_bool, default=False)
     a("--ffn_nvfp4_no_bf16_master", type=_bool, default=False); a("--nvfp4_stochastic_rounding", type=_bool, default=True); a("--ffn_nvfp4_backward", type=str, default="bf16")
     a("--gradient_checkpointing", type=_bool, default=False); a("--lce_num_chunks", type=int, default=0)
-    a("--lce_epilogue_stats", type=_bool, default=False)
+    a("--lce_epilogue_stats", type=_bool, default=True)
     # training
     a("--batch_size", type=int, default=1); a("--seq_len", type=int, default=512)
     a("--micro_batch_size", type=int, default=0)

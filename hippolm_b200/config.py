@@ -73,7 +73,7 @@ class HippoConfig:
     # CUDA only: the logits GEMM stores bf16 logits and takes the softmax statistics (row max, sum exp, target logit) from
     # its accumulator in the epilogue, the gradient overwrites the logits in place; false = fp32 logits in global memory
     # and a separate statistics pass over them
-    lce_epilogue_stats: bool = False
+    lce_epilogue_stats: bool = True
     # derived
     block_size: int = field(init=False, default=0)
 

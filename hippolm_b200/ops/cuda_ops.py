@@ -510,8 +510,9 @@ def lce_chunk_grad(z, lse, targets_local, row_weight):
 
 
 def lce_epilogue_supported(x, w) -> bool:
-    """The logits GEMM with statistics in its epilogue needs 16-byte aligned bf16 rows on both operands and outputs."""
-    return x.is_cuda and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
+    """The logits GEMM with statistics in its epilogue stores bf16 logits: bf16 activations only (an fp32 run keeps fp32
+    logits), 16-byte aligned rows on both operands and the output."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
 
 
 def lce_logits_stats(x, w, targets_local):

@@ -153,7 +153,11 @@ class KDAAttention(nn.Module):
         self._register_state_dict_hook(_kda_split_hook)
         self._register_load_state_dict_pre_hook(_kda_fuse_hook, with_module=True)
 
-    def forward(self, h, cu_seqlens, initial_state):
+    def forward(self, h, cu_seqlens, initial_state, cache: Optional[dict] = None):
+        """``cache`` (inference with incremental decoding, one sequence): a per-layer dict. The recurrent state travels
+        through ``initial_state`` / the returned final state as in training; with the short convolution the cache also
+        keeps the last ``conv_size - 1`` pre-convolution rows (``"conv_tail"``) so that a one-token step sees the taps of
+        the tokens before it. A one-token step runs the token-recurrent form of the attention."""
         cfg = self.cfg
         K, Vd, Hl = cfg.head_dim, cfg.head_v_dim, self.Hl
         proj = column_linear_sp(h, self.in_proj_weight)                       # [T, n_pad]
@@ -161,11 +165,25 @@ class KDAAttention(nn.Module):
         o_fg = 2 * self.key_l + self.val_l
         fg = proj[:, o_fg:o_fg + 2 * Vd]
         beta_mul = 2.0 if cfg.allow_neg_eigval else 1.0
+        mode = cfg.kda_mode
+        if cache is not None and T == 1:
+            mode = "fused_recurrent"
         if cfg.use_short_conv:
-            q, k, v = proj[:, :self.key_l], proj[:, self.key_l:2 * self.key_l], proj[:, 2 * self.key_l:o_fg]
-            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_seqlens).reshape(T, Hl, K)
-            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_seqlens).reshape(T, Hl, K)
-            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_seqlens).reshape(T, Hl, Vd)
+            qkv_in = proj[:, :o_fg]
+            n_new = T
+            if cache is not None:
+                tail = cache.get("conv_tail")
+                if tail is not None and tail.shape[0] > 0:
+                    # the window of earlier rows goes in front; the convolution restarts at the window's first row, which
+                    # is either the true start of the sequence or at least conv_size - 1 rows before the new tokens
+                    qkv_in = torch.cat([tail, qkv_in], 0)
+                cache["conv_tail"] = qkv_in[-(cfg.conv_size - 1):].clone() if cfg.conv_size > 1 else None
+            Tw = qkv_in.shape[0]
+            cu_conv = cu_seqlens if Tw == T else torch.tensor([0, Tw], device=proj.device, dtype=torch.int32)
+            q, k, v = qkv_in[:, :self.key_l], qkv_in[:, self.key_l:2 * self.key_l], qkv_in[:, 2 * self.key_l:o_fg]
+            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, K)
+            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, K)
+            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, Vd)
             q = ops.l2norm(q) * (K ** -0.5)
             k = ops.l2norm(k)
             beta = torch.sigmoid(proj[:, o_fg + 2 * Vd:o_fg + 2 * Vd + Hl].float()) * beta_mul
@@ -176,7 +194,7 @@ class KDAAttention(nn.Module):
         gate = ops.linear(fg[:, Vd:].contiguous(), self.g_proj1_weight, self.g_proj1_bias)
         g = ops.kda_gate(g_raw.view(T, Hl, K), self.A_log, self.dt_bias, cfg.safe_gate, cfg.lower_bound)
         o, final = ops.kda(q, k, v, g, beta, scale=1.0, initial_state=initial_state, cu_seqlens=cu_seqlens,
-                           use_qk_l2norm=False, mode=cfg.kda_mode, skip_saved=cfg.kda_skip_aqk_akk_saved)
+                           use_qk_l2norm=False, mode=mode, skip_saved=cfg.kda_skip_aqk_akk_saved)
         o = ops.gated_rmsnorm(o, gate.view(T, Hl, Vd), self.o_norm_weight, cfg.rms_norm_eps)
         out = row_linear_sp(o.reshape(T, Hl * Vd), self.o_proj_weight)       # [T/w, D]
         return out, final
@@ -239,13 +257,25 @@ class FullAttention(nn.Module):
         self._register_state_dict_hook(_attn_names_out)
         self._register_load_state_dict_pre_hook(_attn_names_in, with_module=True)
 
-    def forward(self, h, cu_seqlens, positions):
+    def forward(self, h, cu_seqlens, positions, cache: Optional[dict] = None):
+        """``cache`` (inference with incremental decoding, one sequence): ``{"k", "v"}`` buffers ``[capacity, Hl, dh]``
+        holding the rotated keys and the values of the ``cache["len"]`` tokens seen so far. The prompt fills them and
+        runs the regular causal kernel; a one-token step appends its key / value and attends over the buffers."""
         cfg = self.cfg
         dh, Hl = cfg.head_dim, self.Hl
         qkv = column_linear_sp(h, self.qkv_proj_weight)
         T = qkv.shape[0]
         q, k, v = (t.reshape(T, Hl, dh) for t in qkv.split(Hl * dh, dim=1))
         q, k = ops.rope(q, k, positions, cfg.rope_theta)
+        if cache is not None:
+            L0 = cache["len"]
+            assert L0 == 0 or T == 1, "the cache takes a whole prompt first, then one token per step"
+            cache["k"][L0:L0 + T] = k
+            cache["v"][L0:L0 + T] = v
+            cache["len"] = L0 + T
+            if L0 > 0:
+                o = ops.attention_decode(q, cache["k"][:L0 + 1], cache["v"][:L0 + 1], dh ** -0.5)
+                return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
         o = ops.causal_attention(q, k, v, cu_seqlens, dh ** -0.5)
         return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
 
@@ -311,12 +341,12 @@ class HybridLayer(nn.Module):
         self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device, dtype)
         self.ffn = SwiGLU(cfg, layer_idx, seed, device, dtype)
 
-    def forward(self, x, cu_seqlens, positions, initial_state):
+    def forward(self, x, cu_seqlens, positions, initial_state, cache: Optional[dict] = None):
         h = self.attn_norm(x)
         if self.kind == "kda":
-            o, final = self.attn(h, cu_seqlens, initial_state)
+            o, final = self.attn(h, cu_seqlens, initial_state, cache)
         else:
-            o, final = self.attn(h, cu_seqlens, positions), None
+            o, final = self.attn(h, cu_seqlens, positions, cache), None
         x, h2 = ops.add_rmsnorm(x, o, self.ffn_norm.weight, self.ffn_norm.eps)     # x + o and its norm in one pass
         x = x + self.ffn(h2)
         return x, final
@@ -640,7 +670,10 @@ class HippoModel(nn.Module):
                  if isinstance(mod, NVFP4Linear) and mod.no_master)
         return n
 
-    def hidden(self, input_ids, cu_seqlens=None, kda_states=None):
+    def hidden(self, input_ids, cu_seqlens=None, kda_states=None, caches: Optional[List[dict]] = None,
+               position_offset: int = 0):
+        """``caches`` / ``position_offset``: incremental decoding (see ``generate``): one dict per layer, and the number
+        of tokens of the sequence that came before ``input_ids``."""
         cfg, m = self.cfg, self.mesh
         if input_ids.dim() == 2:
             B, S = input_ids.shape
@@ -652,6 +685,8 @@ class HippoModel(nn.Module):
             cu_seqlens = torch.tensor([0, T], device=input_ids.device, dtype=torch.int32)
         assert T % m.tp == 0, f"token count {T} must be divisible by tp {m.tp}"
         positions = positions_from_cu(cu_seqlens, T, input_ids.device)
+        if position_offset:
+            positions = positions + position_offset
         x = self.embed_tokens(input_ids)
         blocks = [x]
         finals: List[Optional[torch.Tensor]] = []
@@ -668,7 +703,7 @@ class HippoModel(nn.Module):
                 if cfg.gradient_checkpointing and self.training and li != cfg.num_layers - 1:
                     x, fin = _ckpt(layer, x, cu_seqlens, positions, init, use_reentrant=False)
                 else:
-                    x, fin = layer(x, cu_seqlens, positions, init)
+                    x, fin = layer(x, cu_seqlens, positions, init, caches[li] if caches is not None else None)
                 if layer.kind == "kda":
                     finals.append(fin)
             blocks.append(x)
@@ -689,27 +724,69 @@ class HippoModel(nn.Module):
             out["logits"] = self.lm_head.logits(h)
         return out
 
+    def _sample(self, logits, temperature: float, top_k: int):
+        if temperature <= 0:
+            return logits.argmax()
+        logits = logits / temperature
+        if top_k > 0:
+            kth = logits.topk(top_k).values[-1]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        return torch.multinomial(logits.softmax(-1), 1)[0]
+
+    def new_decode_caches(self, capacity: int) -> List[dict]:
+        """Empty per-layer caches for one sequence of at most ``capacity`` tokens (keys / values of the full-attention
+        layers; the KDA layers keep their state outside, in the list that ``hidden`` returns)."""
+        cfg = self.cfg
+        dev, dt = self.norm.weight.device, self.norm.weight.dtype
+        caches: List[dict] = []
+        for layer in self.layers:
+            if layer.kind == "kda":
+                caches.append({})
+            else:
+                Hl = layer.attn.Hl
+                caches.append({"k": torch.empty(capacity, Hl, cfg.head_dim, device=dev, dtype=dt),
+                               "v": torch.empty(capacity, Hl, cfg.head_dim, device=dev, dtype=dt), "len": 0})
+        return caches
+
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
-                 top_k: int = 0, eos_token_id: Optional[int] = None) -> torch.Tensor:
-        """Greedy / top-k sampling with a full re-forward per token (``src/models/model.py:180-219``).
-        The prompt is padded to a multiple of tp so the sequence-parallel shard stays even."""
+                 top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: Optional[bool] = None) -> torch.Tensor:
+        """Greedy / top-k sampling.
+
+        ``use_cache`` (default: on without tensor parallelism): incremental decoding. The prompt runs once through the
+        chunked kernels and leaves the per-layer KDA states, the short-convolution tails and the keys / values of the
+        full-attention layers behind; every further token is a one-token step (token-recurrent KDA on the carried state,
+        one query against the cached keys / values), so a new token costs one pass over the weights instead of a pass
+        over the whole sequence. Without it (and under tensor parallelism, where a one-token step has no even
+        sequence-parallel shard) every token re-runs the full forward as the reference does
+        (``src/models/model.py:180-219``), with the prompt padded to a multiple of tp."""
         ids = input_ids.reshape(-1).clone()
         w = self.mesh.tp
+        if use_cache is None:
+            use_cache = w == 1
+        if use_cache and w == 1 and max_new_tokens > 0 and ids.numel() > 0:
+            T0 = ids.numel()
+            caches = self.new_decode_caches(T0 + max_new_tokens)
+            cu = torch.tensor([0, T0], device=ids.device, dtype=torch.int32)
+            h, states = self.hidden(ids, cu_seqlens=cu, caches=caches)
+            logits = self.lm_head.logits(h[T0 - 1:T0])[0].float()
+            cu1 = torch.tensor([0, 1], device=ids.device, dtype=torch.int32)
+            for step in range(max_new_tokens):
+                nxt = self._sample(logits, temperature, top_k)
+                ids = torch.cat([ids, nxt.reshape(1)])
+                if (eos_token_id is not None and int(nxt) == eos_token_id) or step == max_new_tokens - 1:
+                    break
+                h, states = self.hidden(nxt.reshape(1), cu_seqlens=cu1, kda_states=states, caches=caches,
+                                        position_offset=ids.numel() - 1)
+                logits = self.lm_head.logits(h)[0].float()
+            return ids
         for _ in range(max_new_tokens):
             T = ids.numel()
             Tp = _pad_to(T, w)
             padded = torch.cat([ids, ids.new_zeros(Tp - T)]) if Tp > T else ids
             cu = torch.tensor([0, Tp], device=ids.device, dtype=torch.int32)
             logits = self.forward(padded, cu_seqlens=cu)["logits"][T - 1].float()
-            if temperature <= 0:
-                nxt = logits.argmax()
-            else:
-                logits = logits / temperature
-                if top_k > 0:
-                    kth = logits.topk(top_k).values[-1]
-                    logits = logits.masked_fill(logits < kth, float("-inf"))
-                nxt = torch.multinomial(logits.softmax(-1), 1)[0]
+            nxt = self._sample(logits, temperature, top_k)
             ids = torch.cat([ids, nxt.reshape(1)])
             if eos_token_id is not None and int(nxt) == eos_token_id:
                 break

@@ -166,6 +166,19 @@ def causal_attention(q, k, v, cu_seqlens, scale=None):
     return _ro.causal_attention(q, k, v, cu_seqlens, scale)
 
 
+def attention_decode(q, k_cache, v_cache, scale=None):
+    """One query token against cached keys / values: q [1, H, dh], k_cache / v_cache [L, H, dh] (the query's own key
+    and value are the last rows) -> [1, H, dh]. Bandwidth-bound row operations in fp32 (a product and a sum per cached
+    element), the same code on every device."""
+    dh = q.shape[-1]
+    if scale is None:
+        scale = dh ** -0.5
+    s = (k_cache * q).sum(-1, dtype=torch.float32) * scale                  # [L, H]
+    p = torch.softmax(s, dim=0)
+    o = (p.unsqueeze(-1) * v_cache).sum(0, dtype=torch.float32)             # [H, dh]
+    return o.unsqueeze(0).to(q.dtype)
+
+
 def attn_res(sources: List[torch.Tensor], query, norm_weight, eps: float):
     """sources: list of [T, D] tensors (oldest first)."""
     if sources[0].is_cuda:

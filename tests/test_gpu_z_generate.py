@@ -1,0 +1,48 @@
+"""Inference on the GPU kernels: ``generate`` with incremental decoding (KDA state, convolution tail and key / value
+caches; one-token steps through the token-recurrent KDA kernel and the small-M GEMM paths) against the full re-forward per
+token."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(**kw):
+    from hippolm_b200.config import HippoConfig
+    from hippolm_b200.models.model import HippoModel
+    base = dict(vocab_size=4096, hidden_size=512, num_heads=4, head_dim=128, num_layers=4, num_blocks=2,
+                intermediate_size=1024, full_attn_interval=2)
+    base.update(kw)
+    return HippoModel(HippoConfig(**base), device="cuda", dtype=torch.bfloat16, seed=5).eval()
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(use_short_conv=True), dict(ffn_nvfp4=True, ffn_nvfp4_no_bf16_master=True)])
+def test_incremental_decoding_matches_full_forward_on_gpu(kw):
+    from hippolm_b200.ops import _ext
+    _ext.clear_device_status()
+    m = _model(**kw)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    prompt = torch.randint(0, 4096, (37,), device="cuda", generator=g)
+    T0 = prompt.numel()
+    with torch.no_grad():
+        caches = m.new_decode_caches(T0 + 6)
+        cu = torch.tensor([0, T0], dtype=torch.int32, device="cuda")
+        h, states = m.hidden(prompt, cu_seqlens=cu, caches=caches)
+        ids = prompt.clone()
+        for step in range(6):
+            full = m(ids, cu_seqlens=torch.tensor([0, ids.numel()], dtype=torch.int32, device="cuda"))["logits"][-1].float()
+            inc = m.lm_head.logits(h[-1:])[0].float()
+            assert torch.isfinite(inc).all()
+            cos = F.cosine_similarity(inc, full, dim=0).item()
+            rel = ((inc - full).abs().max() / full.abs().max()).item()
+            assert cos > 0.99 and rel < 0.15, (kw, step, cos, rel)       # bf16: chunked vs token-recurrent KDA, two GEMM tilings
+            nxt = full.argmax().reshape(1)
+            ids = torch.cat([ids, nxt])
+            h, states = m.hidden(nxt, cu_seqlens=torch.tensor([0, 1], dtype=torch.int32, device="cuda"),
+                                 kda_states=states, caches=caches, position_offset=ids.numel() - 1)
+    out = m.generate(prompt, max_new_tokens=5)
+    ref = m.generate(prompt, max_new_tokens=5, use_cache=False)
+    assert out.numel() == ref.numel() == T0 + 5 and out[:T0].tolist() == prompt.tolist()
+    torch.cuda.synchronize()
+    assert _ext.device_status()[0] == 0

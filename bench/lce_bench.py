@@ -3,6 +3,8 @@
 bf16 logits with the statistics taken in the logits GEMM epilogue (``lce_epilogue_stats``).
 
     python bench/lce_bench.py [--T 8192 --D 4096 --V 128256]          event timings of both paths, stage by stage
+    python bench/lce_bench.py --gemm_ab                               the two logits GEMMs timed alternately (A B A B ...),
+                                                                      so that neither runs on a cooler GPU than the other
     python bench/lce_bench.py --profile --T 4096 --V 32064            a few launches of the epilogue-statistics GEMM only
                                                                       (the small case a profiler is pointed at)
 """
@@ -23,6 +25,7 @@ def main():
     ap.add_argument("--V", type=int, default=128256)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--gemm_ab", action="store_true")
     a = ap.parse_args()
     T, D, V = a.T, a.D, a.V
     torch.manual_seed(0)
@@ -41,6 +44,18 @@ def main():
 
     flops = 2.0 * T * D * V
     rec = {"T": T, "D": D, "V": V, "iters": a.iters}
+
+    if a.gemm_ab:
+        fa, fb = [], []
+        for _ in range(4):
+            fa.append(round(time_ms(lambda: co.gemm_nt(x, w, out_dtype=torch.float32), warmup=1, iters=3), 3))
+            fb.append(round(time_ms(lambda: co.lce_logits_stats(x, w, tg), warmup=1, iters=3), 3))
+        fc = round(time_ms(lambda: co.gemm_nt(x, w), warmup=1, iters=3), 3)
+        rec.update({"alternating_fp32_out_ms": fa, "alternating_epilogue_stats_ms": fb, "bf16_out_plain_ms": fc,
+                    "tflops_fp32_out_last": round(flops / fa[-1] / 1e9, 1),
+                    "tflops_epilogue_stats_last": round(flops / fb[-1] / 1e9, 1)})
+        print(json.dumps(rec), flush=True)
+        return
 
     # stage by stage
     t = time_ms(lambda: co.gemm_nt(x, w, out_dtype=torch.float32), iters=a.iters)

@@ -36,7 +36,11 @@ def test_incremental_decoding_matches_full_forward_on_gpu(kw):
             assert torch.isfinite(inc).all()
             cos = F.cosine_similarity(inc, full, dim=0).item()
             rel = ((inc - full).abs().max() / full.abs().max()).item()
-            assert cos > 0.99 and rel < 0.15, (kw, step, cos, rel)       # bf16: chunked vs token-recurrent KDA, two GEMM tilings
+            # bf16: chunked vs token-recurrent KDA and two GEMM tilings. NVFP4 FFN: the activations of a one-token step
+            # are quantised with that token's own tensor scale, those of the full forward with the scale of the whole
+            # sequence, so the two paths differ by FP4 rounding noise (measured: cosine 0.989, max difference 0.18).
+            lim = (0.95, 0.5) if kw.get("ffn_nvfp4") else (0.99, 0.15)
+            assert cos > lim[0] and rel < lim[1], (kw, step, cos, rel)
             nxt = full.argmax().reshape(1)
             ids = torch.cat([ids, nxt])
             h, states = m.hidden(nxt, cu_seqlens=torch.tensor([0, 1], dtype=torch.int32, device="cuda"),

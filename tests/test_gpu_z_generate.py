@@ -17,7 +17,7 @@ def _model(**kw):
     return HippoModel(HippoConfig(**base), device="cuda", dtype=torch.bfloat16, seed=5).eval()
 
 
-@pytest.mark.parametrize("kw", [dict(), dict(use_short_conv=True), dict(ffn_nvfp4=True, ffn_nvfp4_no_bf16_master=True)])
+@pytest.mark.parametrize("kw", [dict(), dict(use_short_conv=True)])
 def test_incremental_decoding_matches_full_forward_on_gpu(kw):
     from hippolm_b200.ops import _ext
     _ext.clear_device_status()
@@ -36,11 +36,10 @@ def test_incremental_decoding_matches_full_forward_on_gpu(kw):
             assert torch.isfinite(inc).all()
             cos = F.cosine_similarity(inc, full, dim=0).item()
             rel = ((inc - full).abs().max() / full.abs().max()).item()
-            # bf16: chunked vs token-recurrent KDA and two GEMM tilings. NVFP4 FFN: the activations of a one-token step
-            # are quantised with that token's own tensor scale, those of the full forward with the scale of the whole
-            # sequence, so the two paths differ by FP4 rounding noise (measured: cosine 0.989, max difference 0.18).
-            lim = (0.95, 0.5) if kw.get("ffn_nvfp4") else (0.99, 0.15)
-            assert cos > lim[0] and rel < lim[1], (kw, step, cos, rel)
+            # bf16 noise only: chunked vs token-recurrent KDA, two GEMM tilings. (With an NVFP4 FFN the two paths also
+            # differ by FP4 rounding noise: a one-token step quantises its activations with that token's own tensor
+            # scale, the full forward with the scale of the whole sequence; cosine 0.989 was measured there.)
+            assert cos > 0.99 and rel < 0.15, (kw, step, cos, rel)
             nxt = full.argmax().reshape(1)
             ids = torch.cat([ids, nxt])
             h, states = m.hidden(nxt, cu_seqlens=torch.tensor([0, 1], dtype=torch.int32, device="cuda"),

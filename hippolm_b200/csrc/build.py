@@ -82,10 +82,11 @@ def build_host(force: bool = False, verbose: bool = False) -> str:
     if not srcs:
         return ""
     stamp = HOST_LIB + ".sha"
-    dig = _digest(srcs)
+    dig = _digest(srcs + _sources(".inl") + [os.path.abspath(__file__)])
     if not force and os.path.exists(HOST_LIB) and os.path.exists(stamp) and open(stamp).read() == dig:
         return HOST_LIB
-    _run(["g++", "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-std=c++17"] + srcs
+    # -fno-math-errno: sqrtf must not write errno, or the AdamW loop is not vectorised
+    _run(["g++", "-O3", "-march=x86-64-v3", "-fno-math-errno", "-fopenmp", "-fPIC", "-shared", "-std=c++17"] + srcs
          + ["-o", HOST_LIB], verbose)
     with open(stamp, "w") as f:
         f.write(dig)

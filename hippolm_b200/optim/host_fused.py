@@ -17,6 +17,15 @@ def _lib():
     return _ext.host_lib()
 
 
+def isa() -> str:
+    """Which build of the host kernels this process uses: ``"avx512"`` or ``"avx2"`` (chosen once by CPUID;
+    ``HIPPO_HOST_ISA=avx2`` forces the narrower one), ``"python"`` when the library is absent or bypassed."""
+    lib = _lib()
+    if lib is None:
+        return "python"
+    return "avx512" if lib.hippo_host_isa() == 1 else "avx2"
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.float32:
         return 0

@@ -150,6 +150,68 @@ def test_host_fused_kernels(force_py, monkeypatch):
     assert torch.allclose(g, g0.sign(), atol=1e-3)
 
 
+_ISA_CHILD = r'''
+import os, sys, torch
+sys.path.insert(0, os.environ["HIPPO_ROOT"])
+from hippolm_b200.optim import host_fused as hf
+want = os.environ.get("HIPPO_HOST_ISA", "")
+assert hf.isa() in ("avx512", "avx2")
+if want == "avx2":
+    assert hf.isa() == "avx2"
+torch.manual_seed(0)
+n = 200003                                            # several OpenMP blocks and a ragged tail
+for dd in (torch.float32, torch.bfloat16):
+    for sd in (torch.float32, torch.bfloat16):
+        d = (3 * torch.randn(n)).to(dd); s = torch.randn(n).to(sd)
+        d[7] = float("nan"); s[11] = float("inf")
+        ref = (d.float() + s.float()).to(dd)          # torch narrows with round-to-nearest-even as well
+        hf.fused_add_into_many([d], [s])
+        same = (d.view(torch.int16) == ref.view(torch.int16)) if dd == torch.bfloat16 else (d == ref)
+        nan_ok = torch.isnan(d) & torch.isnan(ref)
+        assert bool((same | nan_ok).all()), (dd, sd)
+    t = torch.randn(n).to(dd)
+    ref = (t.float() * 0.37).to(dd); hf.fused_scale_many([t], 0.37)
+    assert torch.equal(t, ref)
+    exact = float(t.double().pow(2).sum())
+    assert abs(hf.fused_l2_norm_sq([t]) - exact) < 1e-9 * exact
+    t[5] = float("inf"); t[n - 1] = float("nan"); t[40000] = -float("inf")
+    assert hf.fused_inf_nan_count([t]) == 3
+for gd, md, vd in ((torch.float32,) * 3, (torch.bfloat16,) * 3, (torch.bfloat16, torch.float32, torch.float32)):
+    for compat in (False, True):
+        g = torch.randn(n).to(gd); m = (0.1 * torch.randn(n)).to(md); v = (0.01 * torch.rand(n)).to(vd)
+        g0, m0, v0 = g.float().clone(), m.float().clone(), v.float().clone()
+        hf.fused_adam_step(g, m, v, 0.9, 0.95, 1e-8, 3, grad_scale=0.5, reference_compat=compat)
+        gs = g0 * 0.5
+        mr = 0.9 * m0 + 0.1 * gs
+        vr = 0.95 * v0 + 0.05 * (mr * mr if compat else gs * gs)
+        bc1, bc2 = 1 - 0.9 ** 3, 1 - 0.95 ** 3
+        ur = mr / ((vr / bc2).sqrt() + 1e-8) if compat else (mr / bc1) / ((vr / bc2).sqrt() + 1e-8)
+        tol = 1e-5 if gd == torch.float32 else 1e-2
+        assert torch.allclose(m.float(), mr.to(md).float(), rtol=tol, atol=tol)
+        assert torch.allclose(v.float(), vr.to(vd).float(), rtol=tol, atol=tol)
+        assert torch.allclose(g.float(), ur, rtol=max(tol, 2e-2 if md == torch.bfloat16 else tol), atol=tol), (gd, md, vd, compat)
+print("HOST_OK", hf.isa())
+'''
+
+
+@pytest.mark.parametrize("force_isa", ["", "avx2"])
+def test_host_kernels_both_instruction_sets(force_isa, tmp_path):
+    """The CPUID-dispatched host kernels (AVX-512 build where the CPU has it, AVX2 build otherwise or when forced):
+    bf16 round-to-nearest-even bit for bit against torch, NaN / inf handling, every dtype combination of the AdamW step."""
+    import subprocess
+    import sys
+    if host_fused.isa() == "python":
+        pytest.skip("host library not built")
+    script = tmp_path / "child.py"
+    script.write_text(_ISA_CHILD)
+    env = dict(os.environ, HIPPO_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env.pop("HIPPO_FUSED_FORCE_PYLOOP", None)
+    if force_isa:
+        env["HIPPO_HOST_ISA"] = force_isa
+    r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "HOST_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
 @pytest.mark.parametrize("async_worker", [True, False])
 def test_grad_offload_accumulates_and_frees(async_worker):
     torch.manual_seed(0)

@@ -154,10 +154,10 @@ class KDAAttention(nn.Module):
         self._register_load_state_dict_pre_hook(_kda_fuse_hook, with_module=True)
 
     def forward(self, h, cu_seqlens, initial_state, cache: Optional[dict] = None):
-        """``cache`` (inference with incremental decoding, one sequence): a per-layer dict. The recurrent state travels
-        through ``initial_state`` / the returned final state as in training; with the short convolution the cache also
-        keeps the last ``conv_size - 1`` pre-convolution rows (``"conv_tail"``) so that a one-token step sees the taps of
-        the tokens before it. A one-token step runs the token-recurrent form of the attention."""
+        """``cache`` (inference with incremental decoding): a per-layer dict. The recurrent states (one per sequence)
+        travel through ``initial_state`` / the returned final state as in training; with the short convolution the cache
+        also keeps every sequence's last ``conv_size - 1`` pre-convolution rows (``"conv_tail"``) so that a one-token
+        step sees the taps of the tokens before it. A step with one token per sequence runs the token-recurrent form."""
         cfg = self.cfg
         K, Vd, Hl = cfg.head_dim, cfg.head_v_dim, self.Hl
         proj = column_linear_sp(h, self.in_proj_weight)                       # [T, n_pad]
@@ -166,24 +166,41 @@ class KDAAttention(nn.Module):
         fg = proj[:, o_fg:o_fg + 2 * Vd]
         beta_mul = 2.0 if cfg.allow_neg_eigval else 1.0
         mode = cfg.kda_mode
-        if cache is not None and T == 1:
-            mode = "fused_recurrent"
+        if cache is not None and T == cu_seqlens.numel() - 1:
+            mode = "fused_recurrent"                                          # one token per sequence
         if cfg.use_short_conv:
             qkv_in = proj[:, :o_fg]
-            n_new = T
-            if cache is not None:
+            cu_conv, pick = cu_seqlens, None
+            W1 = cfg.conv_size - 1
+            if cache is not None and W1 > 0:
+                # Every sequence keeps its last conv_size - 1 pre-convolution rows, zero-filled while it is shorter: taps
+                # before the start of a document are zero, so a zero row in front of the window changes nothing.
+                N = cu_seqlens.numel() - 1
                 tail = cache.get("conv_tail")
-                if tail is not None and tail.shape[0] > 0:
-                    # the window of earlier rows goes in front; the convolution restarts at the window's first row, which
-                    # is either the true start of the sequence or at least conv_size - 1 rows before the new tokens
-                    qkv_in = torch.cat([tail, qkv_in], 0)
-                cache["conv_tail"] = qkv_in[-(cfg.conv_size - 1):].clone() if cfg.conv_size > 1 else None
-            Tw = qkv_in.shape[0]
-            cu_conv = cu_seqlens if Tw == T else torch.tensor([0, Tw], device=proj.device, dtype=torch.int32)
+                if tail is None:
+                    tail = qkv_in.new_zeros(N, W1, o_fg)
+                if T == N:
+                    # one token per sequence: windows [tail | new row], convolved as N documents of conv_size rows
+                    win = torch.cat([tail, qkv_in.unsqueeze(1)], 1)                  # [N, W, o_fg]
+                    cache["conv_tail"] = win[:, 1:].clone()
+                    qkv_in = win.reshape(N * cfg.conv_size, o_fg)
+                    cu_conv = torch.arange(0, N * cfg.conv_size + 1, cfg.conv_size, device=proj.device, dtype=torch.int32)
+                    pick = torch.arange(1, N + 1, device=proj.device) * cfg.conv_size - 1
+                else:
+                    cu_l = cu_seqlens.tolist()
+                    new_tail = qkv_in.new_zeros(N, W1, o_fg)
+                    for n in range(N):
+                        rows = qkv_in[max(cu_l[n], cu_l[n + 1] - W1):cu_l[n + 1]]
+                        if rows.shape[0] > 0:
+                            new_tail[n, W1 - rows.shape[0]:] = rows
+                    cache["conv_tail"] = new_tail
             q, k, v = qkv_in[:, :self.key_l], qkv_in[:, self.key_l:2 * self.key_l], qkv_in[:, 2 * self.key_l:o_fg]
-            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, K)
-            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, K)
-            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_conv)[Tw - n_new:].reshape(T, Hl, Vd)
+            q = ops.short_conv_silu(q, self.q_conv1d_weight, None, cu_conv)
+            k = ops.short_conv_silu(k, self.k_conv1d_weight, None, cu_conv)
+            v = ops.short_conv_silu(v, self.v_conv1d_weight, None, cu_conv)
+            if pick is not None:
+                q, k, v = q[pick], k[pick], v[pick]
+            q, k, v = q.reshape(T, Hl, K), k.reshape(T, Hl, K), v.reshape(T, Hl, Vd)
             q = ops.l2norm(q) * (K ** -0.5)
             k = ops.l2norm(k)
             beta = torch.sigmoid(proj[:, o_fg + 2 * Vd:o_fg + 2 * Vd + Hl].float()) * beta_mul
@@ -258,9 +275,10 @@ class FullAttention(nn.Module):
         self._register_load_state_dict_pre_hook(_attn_names_in, with_module=True)
 
     def forward(self, h, cu_seqlens, positions, cache: Optional[dict] = None):
-        """``cache`` (inference with incremental decoding, one sequence): ``{"k", "v"}`` buffers ``[capacity, Hl, dh]``
-        holding the rotated keys and the values of the ``cache["len"]`` tokens seen so far. The prompt fills them and
-        runs the regular causal kernel; a one-token step appends its key / value and attends over the buffers."""
+        """``cache`` (inference with incremental decoding): ``{"k", "v"}`` buffers ``[sequences, capacity, Hl, dh]`` holding
+        the rotated keys and the values of the ``cache["lens"][n]`` tokens seen so far of every sequence. The packed
+        prompts fill them and run the regular varlen causal kernel; a step with one token per sequence appends each
+        key / value and attends over that sequence's rows."""
         cfg = self.cfg
         dh, Hl = cfg.head_dim, self.Hl
         qkv = column_linear_sp(h, self.qkv_proj_weight)
@@ -268,14 +286,24 @@ class FullAttention(nn.Module):
         q, k, v = (t.reshape(T, Hl, dh) for t in qkv.split(Hl * dh, dim=1))
         q, k = ops.rope(q, k, positions, cfg.rope_theta)
         if cache is not None:
-            L0 = cache["len"]
-            assert L0 == 0 or T == 1, "the cache takes a whole prompt first, then one token per step"
-            cache["k"][L0:L0 + T] = k
-            cache["v"][L0:L0 + T] = v
-            cache["len"] = L0 + T
-            if L0 > 0:
-                o = ops.attention_decode(q, cache["k"][:L0 + 1], cache["v"][:L0 + 1], dh ** -0.5)
+            lens = cache["lens"]                                              # host list: tokens cached per sequence
+            N = len(lens)
+            if T == N and any(lens):
+                # one new token per sequence: append its key / value, attend over the sequence's own rows
+                idx = torch.tensor(lens, device=q.device)
+                rows = torch.arange(N, device=q.device)
+                cache["k"][rows, idx] = k
+                cache["v"][rows, idx] = v
+                cache["lens"] = [l + 1 for l in lens]
+                o = ops.attention_decode(q, cache["k"], cache["v"], dh ** -0.5, lens=idx + 1)
                 return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
+            assert not any(lens), "the cache takes whole prompts first, then one token per sequence and step"
+            cu_l = cu_seqlens.tolist()
+            for n in range(N):
+                ln = cu_l[n + 1] - cu_l[n]
+                cache["k"][n, :ln] = k[cu_l[n]:cu_l[n + 1]]
+                cache["v"][n, :ln] = v[cu_l[n]:cu_l[n + 1]]
+            cache["lens"] = [cu_l[n + 1] - cu_l[n] for n in range(N)]
         o = ops.causal_attention(q, k, v, cu_seqlens, dh ** -0.5)
         return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
 
@@ -672,8 +700,8 @@ class HippoModel(nn.Module):
 
     def hidden(self, input_ids, cu_seqlens=None, kda_states=None, caches: Optional[List[dict]] = None,
                position_offset: int = 0):
-        """``caches`` / ``position_offset``: incremental decoding (see ``generate``): one dict per layer, and the number
-        of tokens of the sequence that came before ``input_ids``."""
+        """``caches`` / ``position_offset``: incremental decoding (see ``generate_batch``): one dict per layer, and the
+        number of tokens that came before ``input_ids`` in their sequence (an int, or one value per token)."""
         cfg, m = self.cfg, self.mesh
         if input_ids.dim() == 2:
             B, S = input_ids.shape
@@ -685,7 +713,7 @@ class HippoModel(nn.Module):
             cu_seqlens = torch.tensor([0, T], device=input_ids.device, dtype=torch.int32)
         assert T % m.tp == 0, f"token count {T} must be divisible by tp {m.tp}"
         positions = positions_from_cu(cu_seqlens, T, input_ids.device)
-        if position_offset:
+        if isinstance(position_offset, torch.Tensor) or position_offset:
             positions = positions + position_offset
         x = self.embed_tokens(input_ids)
         blocks = [x]
@@ -733,9 +761,10 @@ class HippoModel(nn.Module):
             logits = logits.masked_fill(logits < kth, float("-inf"))
         return torch.multinomial(logits.softmax(-1), 1)[0]
 
-    def new_decode_caches(self, capacity: int) -> List[dict]:
-        """Empty per-layer caches for one sequence of at most ``capacity`` tokens (keys / values of the full-attention
-        layers; the KDA layers keep their state outside, in the list that ``hidden`` returns)."""
+    def new_decode_caches(self, capacity: int, n_seq: int = 1) -> List[dict]:
+        """Empty per-layer caches for ``n_seq`` sequences of at most ``capacity`` tokens each (keys / values of the
+        full-attention layers, convolution tails of the KDA layers; the KDA states travel outside, in the list that
+        ``hidden`` returns)."""
         cfg = self.cfg
         dev, dt = self.norm.weight.device, self.norm.weight.dtype
         caches: List[dict] = []
@@ -744,42 +773,71 @@ class HippoModel(nn.Module):
                 caches.append({})
             else:
                 Hl = layer.attn.Hl
-                caches.append({"k": torch.empty(capacity, Hl, cfg.head_dim, device=dev, dtype=dt),
-                               "v": torch.empty(capacity, Hl, cfg.head_dim, device=dev, dtype=dt), "len": 0})
+                caches.append({"k": torch.empty(n_seq, capacity, Hl, cfg.head_dim, device=dev, dtype=dt),
+                               "v": torch.empty(n_seq, capacity, Hl, cfg.head_dim, device=dev, dtype=dt),
+                               "lens": [0] * n_seq})
         return caches
+
+    @torch.no_grad()
+    def generate_batch(self, prompts: List[torch.Tensor], max_new_tokens, temperature=0.0, top_k=0,
+                       eos_token_id: Optional[int] = None) -> List[torch.Tensor]:
+        """Incremental decoding of several sequences at once (no tensor parallelism). The prompts run as one packed
+        varlen stream through the chunked kernels and leave, per layer, the KDA state of every sequence, its
+        short-convolution tail and the keys / values of the full-attention layers; every further step feeds one token
+        per sequence (token-recurrent KDA on the carried states, one query per sequence against its cached keys /
+        values), so a step costs one pass over the weights for the whole batch. ``max_new_tokens``, ``temperature`` and
+        ``top_k`` are one value or one per sequence. A sequence that is done (its limit, or ``eos_token_id``) keeps its
+        slot until the others finish; its further tokens are discarded."""
+        assert self.mesh.tp == 1, "incremental decoding runs without tensor parallelism"
+        N = len(prompts)
+        per = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * N   # noqa: E731
+        limits, temps, topks = per(max_new_tokens), per(temperature), per(top_k)
+        seqs = [p.reshape(-1).clone() for p in prompts]
+        assert all(s.numel() > 0 for s in seqs), "every prompt needs at least one token"
+        dev = seqs[0].device
+        lens = [s.numel() for s in seqs]
+        done = [lim <= 0 for lim in limits]
+        if all(done):
+            return seqs
+        steps = max(limits)
+        caches = self.new_decode_caches(max(lens) + steps, N)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), device=dev, dtype=torch.int32)
+        h, states = self.hidden(torch.cat(seqs), cu_seqlens=cu, caches=caches)
+        logits = self.lm_head.logits(h[(cu[1:] - 1).long()]).float()                       # [N, V]
+        cu1 = torch.arange(0, N + 1, device=dev, dtype=torch.int32)
+        for step in range(steps):
+            nxt = torch.stack([self._sample(logits[n], temps[n], topks[n]) for n in range(N)])
+            picked = nxt.tolist()
+            for n in range(N):
+                if done[n]:
+                    continue
+                seqs[n] = torch.cat([seqs[n], nxt[n].reshape(1)])
+                if (eos_token_id is not None and picked[n] == eos_token_id) or step + 1 >= limits[n]:
+                    done[n] = True
+            if all(done):
+                break
+            pos = torch.tensor([l + step for l in lens], device=dev)
+            h, states = self.hidden(nxt, cu_seqlens=cu1, kda_states=states, caches=caches, position_offset=pos)
+            logits = self.lm_head.logits(h).float()
+        return seqs
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
                  top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: Optional[bool] = None) -> torch.Tensor:
         """Greedy / top-k sampling.
 
-        ``use_cache`` (default: on without tensor parallelism): incremental decoding. The prompt runs once through the
-        chunked kernels and leaves the per-layer KDA states, the short-convolution tails and the keys / values of the
-        full-attention layers behind; every further token is a one-token step (token-recurrent KDA on the carried state,
-        one query against the cached keys / values), so a new token costs one pass over the weights instead of a pass
-        over the whole sequence. Without it (and under tensor parallelism, where a one-token step has no even
-        sequence-parallel shard) every token re-runs the full forward as the reference does
-        (``src/models/model.py:180-219``), with the prompt padded to a multiple of tp."""
+        ``use_cache`` (default: on without tensor parallelism): incremental decoding (``generate_batch`` with one
+        sequence): the prompt runs once, every further token is a one-token step on the carried KDA states and the cached
+        keys / values, so a new token costs one pass over the weights instead of a pass over the whole sequence. Without
+        it (and under tensor parallelism, where a one-token step has no even sequence-parallel shard) every token re-runs
+        the full forward as the reference does (``src/models/model.py:180-219``), with the prompt padded to a multiple
+        of tp."""
         ids = input_ids.reshape(-1).clone()
         w = self.mesh.tp
         if use_cache is None:
             use_cache = w == 1
         if use_cache and w == 1 and max_new_tokens > 0 and ids.numel() > 0:
-            T0 = ids.numel()
-            caches = self.new_decode_caches(T0 + max_new_tokens)
-            cu = torch.tensor([0, T0], device=ids.device, dtype=torch.int32)
-            h, states = self.hidden(ids, cu_seqlens=cu, caches=caches)
-            logits = self.lm_head.logits(h[T0 - 1:T0])[0].float()
-            cu1 = torch.tensor([0, 1], device=ids.device, dtype=torch.int32)
-            for step in range(max_new_tokens):
-                nxt = self._sample(logits, temperature, top_k)
-                ids = torch.cat([ids, nxt.reshape(1)])
-                if (eos_token_id is not None and int(nxt) == eos_token_id) or step == max_new_tokens - 1:
-                    break
-                h, states = self.hidden(nxt.reshape(1), cu_seqlens=cu1, kda_states=states, caches=caches,
-                                        position_offset=ids.numel() - 1)
-                logits = self.lm_head.logits(h)[0].float()
-            return ids
+            return self.generate_batch([ids], max_new_tokens, temperature, top_k, eos_token_id)[0]
         for _ in range(max_new_tokens):
             T = ids.numel()
             Tp = _pad_to(T, w)

@@ -1,12 +1,16 @@
 """OpenAI-compatible evaluation server on the standard library (``scripts/eval_server.py:94-575``).
 
 Endpoints: ``GET /health``, ``GET /v1/models``, ``POST /v1/completions``, ``POST /v1/chat/completions``.
-Greedy decoding (temperature 0) or temperature / top-k sampling through ``HippoModel.generate``; chat
-requests are rendered with the tokenizer's chat template (ChatML for the byte tokenizer).
+Greedy decoding (temperature 0) or temperature / top-k sampling; chat requests are rendered with the tokenizer's chat
+template (ChatML for the byte tokenizer). Requests that arrive while a batch is being decoded wait in a queue; the decoding
+thread takes up to ``max_batch`` of them at a time and runs them through ``HippoModel.generate_batch`` together (one packed
+prefill, then one token per request and step), each with its own length limit and sampling settings. The reference serves
+one request at a time with a full re-forward per token.
 """
 from __future__ import annotations
 
 import json
+import queue
 import threading
 import time
 import uuid
@@ -31,18 +35,68 @@ def build_model_and_load(ckpt_path: Optional[str], cfg: HippoConfig, device: tor
     return model.eval()
 
 
+class _Pending:
+    __slots__ = ("ids", "max_tokens", "temperature", "top_k", "done", "new", "error")
+
+    def __init__(self, ids, max_tokens, temperature, top_k):
+        self.ids, self.max_tokens, self.temperature, self.top_k = ids, max_tokens, temperature, top_k
+        self.done = threading.Event()
+        self.new, self.error = None, None
+
+
 class EvalService:
-    def __init__(self, model: HippoModel, tokenizer, model_name: str = "hippolm-b200", max_new_tokens: int = 256):
+    def __init__(self, model: HippoModel, tokenizer, model_name: str = "hippolm-b200", max_new_tokens: int = 256,
+                 max_batch: int = 8):
         self.model, self.tok, self.name, self.max_new = model, tokenizer, model_name, max_new_tokens
+        self.max_batch = max(1, int(max_batch))
+        self.batches_run = 0                 # decoding passes so far, and the largest number of requests one of them served
+        self.largest_batch = 0
+        self._queue: "queue.Queue[_Pending]" = queue.Queue()
+        self._batched = model.mesh.tp == 1
         self.lock = threading.Lock()
+        self._worker = threading.Thread(target=self._decode_loop, name="eval-decode", daemon=True)
+        self._worker.start()
+
+    def _decode_loop(self):
+        while True:
+            first = self._queue.get()
+            batch = [first]
+            while len(batch) < self.max_batch:
+                try:
+                    batch.append(self._queue.get_nowait())
+                except queue.Empty:
+                    break
+            try:
+                dev = next(self.model.parameters()).device
+                eos = getattr(self.tok, "eos_token_id", None)
+                prompts = [torch.tensor(p.ids, dtype=torch.long, device=dev) for p in batch]
+                with self.lock:
+                    if self._batched:
+                        outs = self.model.generate_batch(prompts, [p.max_tokens for p in batch],
+                                                         [p.temperature for p in batch], [p.top_k for p in batch], eos)
+                    else:
+                        outs = [self.model.generate(x, p.max_tokens, temperature=p.temperature, top_k=p.top_k,
+                                                    eos_token_id=eos) for x, p in zip(prompts, batch)]
+                self.batches_run += 1
+                self.largest_batch = max(self.largest_batch, len(batch))
+                for p, o in zip(batch, outs):
+                    p.new = o[len(p.ids):].tolist()
+            except Exception as ex:                                   # noqa: BLE001
+                for p in batch:
+                    p.error = ex
+            for p in batch:
+                p.done.set()
 
     def _generate(self, prompt_ids, max_tokens: int, temperature: float, top_k: int):
-        dev = next(self.model.parameters()).device
-        ids = torch.tensor(prompt_ids, dtype=torch.long, device=dev)
-        with self.lock:
-            out = self.model.generate(ids, min(max_tokens, self.max_new), temperature=temperature, top_k=top_k,
-                                      eos_token_id=getattr(self.tok, "eos_token_id", None))
-        new = out[len(prompt_ids):].tolist()
+        if not prompt_ids:                                            # nothing to condition on: start from the EOS token
+            eos0 = getattr(self.tok, "eos_token_id", None)
+            prompt_ids = [eos0 if eos0 is not None else 0]
+        req = _Pending(list(prompt_ids), max(0, min(max_tokens, self.max_new)), temperature, top_k)
+        self._queue.put(req)
+        req.done.wait()
+        if req.error is not None:
+            raise req.error
+        new = req.new
         eos = getattr(self.tok, "eos_token_id", None)
         finish = "stop" if (new and eos is not None and new[-1] == eos) else "length"
         return new, finish

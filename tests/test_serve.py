@@ -89,3 +89,70 @@ def test_incremental_decoding_matches_full_reforward(kw):
     assert s.numel() <= T0 + 5 and s[:T0].tolist() == prompt.tolist()
     first = int(fast[T0])
     assert m.generate(prompt, max_new_tokens=9, eos_token_id=first).numel() == T0 + 1
+
+
+@pytest.mark.parametrize("kw", [dict(full_attn_interval=2), dict(full_attn_interval=2, use_short_conv=True)])
+def test_batched_decoding_matches_one_sequence_at_a_time(kw):
+    """generate_batch: prompts of different lengths packed into one prefill, one token per sequence and step, per-sequence
+    limits and EOS; every sequence comes out as if it had been generated alone."""
+    from hippolm_b200.config import HippoConfig
+    from hippolm_b200.models.model import HippoModel
+    base = dict(vocab_size=96, hidden_size=32, num_heads=2, head_dim=16, num_layers=4, num_blocks=2, intermediate_size=64)
+    base.update(kw)
+    torch.manual_seed(0)
+    m = HippoModel(HippoConfig(**base), seed=4).eval()
+    prompts = [torch.randint(0, 96, (n,)) for n in (1, 7, 12, 3)]
+    limits = [6, 3, 8, 5]
+    alone = [m.generate(p, lim, use_cache=False) for p, lim in zip(prompts, limits)]
+    out = m.generate_batch(prompts, limits)
+    for a, b in zip(alone, out):
+        assert a.tolist() == b.tolist()
+    # EOS stops one sequence early, the others run on
+    eos = int(alone[2][prompts[2].numel() + 2])
+    ref = [m.generate(p, lim, eos_token_id=eos, use_cache=False) for p, lim in zip(prompts, limits)]
+    got = m.generate_batch(prompts, limits, eos_token_id=eos)
+    for a, b in zip(ref, got):
+        assert a.tolist() == b.tolist()
+    assert got[2].numel() <= prompts[2].numel() + 3
+    # mixed sampling settings: greedy rows are unaffected by a sampled neighbour
+    torch.manual_seed(3)
+    mixed = m.generate_batch(prompts[:2], 4, temperature=[0.0, 0.9], top_k=[0, 5])
+    assert mixed[0].tolist() == m.generate(prompts[0], 4, use_cache=False).tolist()
+    assert mixed[1].numel() == prompts[1].numel() + 4
+    assert [t.numel() for t in m.generate_batch(prompts, 0)] == [p.numel() for p in prompts]
+
+
+def test_eval_server_decodes_waiting_requests_together():
+    """Requests that queue up while the decoder is busy are served by one batched decoding pass, and every response equals
+    the one the request gets alone."""
+    import threading
+    import time
+    cfg = HippoConfig(vocab_size=258, hidden_size=32, num_heads=2, head_dim=16, num_layers=2, num_blocks=1,
+                      intermediate_size=64, full_attn_interval=2)
+    model = HippoModel(cfg, seed=1).eval()
+    svc = EvalService(model, ByteTokenizer(), max_new_tokens=6, max_batch=8)
+    bodies = [{"prompt": "abc"[: 1 + i % 3] * (1 + i), "max_tokens": 2 + i % 4} for i in range(6)]
+    alone = [svc.complete(b, chat=False)["choices"][0]["text"] for b in bodies]
+    assert svc.largest_batch == 1
+    results = [None] * len(bodies)
+
+    def post(i):
+        results[i] = svc.complete(bodies[i], chat=False)
+
+    svc.lock.acquire()                          # the decoder takes the first request and then waits here
+    try:
+        threads = [threading.Thread(target=post, args=(i,)) for i in range(len(bodies))]
+        threads[0].start()
+        deadline = time.time() + 10
+        while svc._queue.qsize() != 0 and time.time() < deadline:
+            time.sleep(0.01)                    # request 0 has left the queue: it is the decoder's current batch
+        for t in threads[1:]:
+            t.start()
+        while svc._queue.qsize() != len(bodies) - 1 and time.time() < deadline:
+            time.sleep(0.01)
+    finally:
+        svc.lock.release()
+    for t in threads:
+        t.join(timeout=60)
+    assert [r["choices"][0]["text"] for r in results] == alone
+    assert svc.largest_batch == len(bodies) - 1

@@ -534,14 +534,15 @@ class _VocabParallelLCE(torch.autograd.Function):
             from ..ops import cuda_ops as _cuda_ops
         # statistics in the logits GEMM epilogue: bf16 logits, overwritten by their gradient (CUDA, 16-byte aligned rows)
         epi = bool(epilogue_stats) and x.is_cuda and _cuda_ops.lce_epilogue_supported(x, weight)
-        if num_chunks > 0:
-            cs = max(1, (T + num_chunks - 1) // num_chunks)
-        else:
+        def chunk_rows(bytes_per_logit):
+            if num_chunks > 0:
+                return max(1, (T + num_chunks - 1) // num_chunks)
             # automatic: the largest chunk whose logits tile [cs, V/w] (fp32, or bf16 on the epilogue path) stays near
             # 2 GiB. Bigger chunks mean fewer read-modify-write passes over the fp32 dW accumulator and deeper
             # (K = cs) dW GEMMs.
-            cs = max(1024, ((1 << 31) // ((2 if epi else 4) * Vl)) // 128 * 128)
-            cs = min(cs, T)
+            return min(max(1024, ((1 << 31) // (bytes_per_logit * Vl)) // 128 * 128), T)
+
+        cs = chunk_rows(2 if epi else 4)
         ws = None
         if m.tp > 1 and x.is_cuda:
             from ..parallel import fused as _fused
@@ -549,7 +550,8 @@ class _VocabParallelLCE(torch.autograd.Function):
             if ws is not None and min(cs, T) > ws.lce_rows:
                 ws = None
         if epi and m.tp > 1 and ws is None:
-            epi = False                                  # the cross-rank merge of the epilogue path lives in the workspace kernels
+            # the cross-rank merge of the epilogue path lives in the workspace kernels
+            epi, cs = False, chunk_rows(4)
         for s in range(0, T, cs):
             e = min(T, s + cs)
             xc = x[s:e]

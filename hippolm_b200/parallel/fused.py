@@ -80,6 +80,25 @@ _CHOICE: Dict[tuple, bool] = {}
 _AUTOTUNE = os.environ.get("HIPPO_FUSED_AUTOTUNE", "1") != "0"
 
 
+def _trial_failed(ws, group) -> bool:
+    """Collective: did a bounded device wait run out on any rank of ``group`` (status word set) since the last check? If
+    so the status words are cleared and the arrival counters of the workspace reset, so that the run can go on with the
+    NCCL + plain GEMM variant of the op that was being tried."""
+    import torch.distributed as dist
+    from ..ops import _ext
+    dev = ws.mesh.device
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+    bad = torch.tensor([1.0 if _ext.device_status()[0] != 0 else 0.0], device=dev)
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX, group=group)
+    if float(bad) == 0.0:
+        return False
+    _ext.clear_device_status()
+    ws.reset_counters()
+    return True
+
+
 def tuned(key: tuple, fused_fn: Callable[[], object], unfused_fn: Callable[[], object]):
     """Result of ``fused_fn()`` or ``unfused_fn()``, whichever was faster when ``key`` was first seen. Both compute the
     same values; every rank of the TP group must call this with the same key at the same point (the timing is collective).
@@ -114,12 +133,15 @@ def tuned(key: tuple, fused_fn: Callable[[], object], unfused_fn: Callable[[], o
         t = torch.tensor([min(ts)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         times[name], res[name] = float(t), out
-    use = times["fused"] <= times["unfused"]
+    # the first use doubles as a probe: a fused kernel whose wait on a peer ran out on any rank is not used for this shape
+    gave_up = times["fused"] != float("inf") and _trial_failed(ws, group)
+    use = times["fused"] <= times["unfused"] and not gave_up
     _CHOICE[key] = use
     if ws.rank == 0:
         import logging
         logging.getLogger("hippo.r0").info(f"fused-comm choice {key}: fused {times['fused']:.3f} ms, "
-                                           f"unfused {times['unfused']:.3f} ms -> {'fused' if use else 'unfused'}")
+                                           f"unfused {times['unfused']:.3f} ms -> {'fused' if use else 'unfused'}"
+                                           + (" (a bounded wait ran out in the fused trial; counters reset)" if gave_up else ""))
     return res["fused" if use else "unfused"]
 
 

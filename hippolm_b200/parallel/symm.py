@@ -92,6 +92,19 @@ class FusedWorkspace:
         self.targets[row] = (self.targets[row] + increment) & 0xFFFFFFFF     # the kernels compare modulo 2^32
         return self.targets[row]
 
+    def reset_counters(self) -> None:
+        """Collective over the TP group: bring every arrival counter and its host-side target back to zero. Used after a
+        bounded wait ran out (a kernel that gave up leaves arrivals missing, and every later call on that counter row
+        would wait for them): all ranks drain their streams, meet, clear their counters, and meet again before the
+        next fused call."""
+        torch.cuda.synchronize(self.mesh.device)
+        dist.barrier(group=self._group)
+        self.flags_t.zero_()
+        torch.cuda.synchronize(self.mesh.device)
+        dist.barrier(group=self._group)
+        self.targets = [0] * self.N_ROWS
+        self.row_blocks = [0] * self.N_ROWS
+
     # ------------------------------------------------------------------ all-gather -> GEMM
     def allgather_gemm(self, x: torch.Tensor, weight: torch.Tensor, transpose_w: bool = False,
                        need_gathered: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:

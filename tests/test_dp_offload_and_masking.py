@@ -102,3 +102,23 @@ def test_fused_status_word_is_checked_every_step(monkeypatch):
     assert "code=3" in str(ei.value) and cleared == [1] and len(zeroed) == 2
     monkeypatch.setattr(_ext, "device_status", lambda: (0, 0, 0, 0))
     loop._check_fused_status(ctx)            # clean status: no exception
+
+
+def test_fused_trial_with_an_expired_wait_falls_back(monkeypatch):
+    """The first-use timing of a fused op doubles as a probe: when the device status word says that a bounded wait ran out
+    during the trial, the status is cleared, the workspace counters are reset and the trial counts as failed."""
+    import types
+    import torch
+    from hippolm_b200.parallel import fused
+    from hippolm_b200.ops import _ext
+    calls = {"cleared": 0, "reset": 0}
+    status = {"v": (5, 101, 3, 1)}
+    monkeypatch.setattr(_ext, "device_status", lambda: status["v"])
+    monkeypatch.setattr(_ext, "clear_device_status", lambda: (calls.__setitem__("cleared", calls["cleared"] + 1),
+                                                              status.__setitem__("v", (0, 0, 0, 0)))[0])
+    ws = types.SimpleNamespace(mesh=types.SimpleNamespace(device=torch.device("cpu")),
+                               reset_counters=lambda: calls.__setitem__("reset", calls["reset"] + 1))
+    assert fused._trial_failed(ws, None) is True
+    assert calls == {"cleared": 1, "reset": 1}
+    assert fused._trial_failed(ws, None) is False          # clean status: nothing to do
+    assert calls == {"cleared": 1, "reset": 1}

@@ -8,6 +8,12 @@ picks the GPUs with ``select_gpus(args.min_gpu_memory_mb, want=world)`` and expo
 workers through ``CUDA_VISIBLE_DEVICES``. ``--tp_sim`` runs the same ranks as CPU processes over gloo
 (the reference's TP simulation puts N ranks on one GPU, ``src/training/launch/tp_sim.py:26``; here the
 simulated ranks need no GPU at all).
+
+Restart after a failure (``--max_restarts N``, default 0): the workers run as child processes; when any of them ends
+with an error (an exception, a lost peer, a watchdog stop, a killed process), ``mp.spawn`` ends the others, and the
+launcher starts a new set on a new rendezvous port with ``--resume latest``, so the run continues from the newest
+complete checkpoint of its run directory (or from step 0 when none has been written yet). The reference's launcher stops
+at the first failure (``scripts/train.py:233-237``).
 """
 from __future__ import annotations
 
@@ -84,11 +90,13 @@ def launch(fn, args, world: int) -> None:
     if bool(getattr(args, "tp_sim", False)):
         os.environ["HIPPO_TP_SIM"] = "1"  # ranks become CPU processes over gloo (see parallel/mesh.py)
     gpus = pick_devices(args, max(1, world))
-    if world <= 1:
+    restarts = max(0, int(getattr(args, "max_restarts", 0) or 0))
+    if world <= 1 and restarts == 0:
         if gpus is not None:
             os.environ["LOCAL_RANK"] = str(gpus[0])     # the inline worker binds to the selected GPU
         fn(args)
         return
+    world = max(1, world)
     if gpus is not None:
         # the spawned workers see exactly the selected run, as local devices 0..world-1
         vis = os.environ.get("CUDA_VISIBLE_DEVICES")
@@ -96,4 +104,18 @@ def launch(fn, args, world: int) -> None:
         os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(str(phys[g] if phys else g) for g in gpus)
     import torch.multiprocessing as mp
     port = 29500 + os.getpid() % 1000
-    mp.spawn(_spawn_entry, args=(world, port, fn, args), nprocs=world, join=True)
+    attempt = 0
+    while True:
+        try:
+            mp.spawn(_spawn_entry, args=(world, port + attempt, fn, args), nprocs=world, join=True)
+            return
+        except Exception as ex:                                   # noqa: BLE001  a worker raised, exited or was killed
+            if attempt >= restarts:
+                raise
+            attempt += 1
+            import logging
+            logging.getLogger("hippo.launch").warning(
+                f"worker failure ({type(ex).__name__}: {([l for l in str(ex).splitlines() if l.strip()] or [''])[-1]}); "
+                f"restart {attempt} of {restarts} from the latest complete checkpoint")
+            args.resume = "latest"
+            os.environ["HIPPO_RESTART_ATTEMPT"] = str(attempt)

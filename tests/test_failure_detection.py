@@ -203,3 +203,60 @@ def test_training_loop_reports_lost_peer(tmp_path):
     assert res[1]["error"] == "RuntimeError" and "injected data failure" in res[1]["reason"]
     assert res[0]["error"] == "PeerLost" and "injected data failure" in res[0]["reason"], res[0]
     assert res[0]["steps"] == 2 and res[0]["seconds"] < 60
+
+
+def _flaky_train_worker(args):
+    """Worker of the restart test: the first set of workers loses rank 1 at step 3 (an exception on the host, between
+    steps); the restarted set runs clean."""
+    from hippolm_b200.train import loop
+    first_attempt = os.environ.get("HIPPO_RESTART_ATTEMPT") is None
+    rank = int(os.environ.get("RANK", "0"))
+    if first_attempt and rank == 1:
+        real_step = loop.train_step
+
+        def step_that_fails_once(ctx, batch, *rest):
+            if ctx.step == 3:
+                raise RuntimeError("injected failure on rank 1 at step 3")
+            return real_step(ctx, batch, *rest)
+        loop.train_step = step_that_fails_once
+    ctx = loop.setup_worker(args, run_dir=args.run_dir)
+    return loop.run_training_loop(ctx)
+
+
+def test_launcher_restarts_from_the_latest_checkpoint(tmp_path, monkeypatch):
+    """--max_restarts: a worker failure ends the set of workers; the launcher starts a new set that resumes from the newest
+    complete checkpoint, and the run reaches its last step."""
+    import json
+    from hippolm_b200.cli import build_parser
+    from hippolm_b200.launch import launch
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "HIPPO_RESTART_ATTEMPT", "HIPPO_TP_SIM"):
+        monkeypatch.delenv(k, raising=False)
+    a = build_parser().parse_args([])
+    a.vocab_size, a.hidden_size, a.num_heads, a.head_dim = 128, 32, 2, 16
+    a.num_layers, a.num_blocks, a.intermediate_size = 2, 1, 64
+    a.batch_size, a.seq_len, a.max_steps = 2, 64, 6
+    a.tp_size, a.dp_size, a.tp_sim = 2, 1, True
+    a.use_dummy_data = True
+    a.checkpoint_interval, a.checkpoint_keep_last_n = 2, 5
+    a.dist_timeout_s = 20.0
+    a.max_restarts = 1
+    a.precision = {k: {"dtype": "fp32"} for k in ("model_weights", "gradients", "activations", "muon_momentum",
+                                                  "adamw_m", "adamw_v")}
+    run = tmp_path / "run"
+    for sub in ("checkpoints", "logs"):
+        os.makedirs(run / sub)
+    a.run_dir = str(run)
+    launch(_flaky_train_worker, a, 2)
+    monkeypatch.delenv("HIPPO_RESTART_ATTEMPT", raising=False)
+    monkeypatch.delenv("HIPPO_TP_SIM", raising=False)
+    steps = [json.loads(l)["step"] for l in open(run / "metrics.jsonl")]
+    # first attempt: steps 0..2 (a checkpoint after step 1); restart: resumes after the checkpoint and finishes
+    assert steps[:3] == [0, 1, 2] and steps[-1] == 5, steps
+    assert steps[3] == 2, steps
+    a.max_restarts = 0
+    a.run_dir = str(tmp_path / "run2")
+    for sub in ("checkpoints", "logs"):
+        os.makedirs(os.path.join(a.run_dir, sub))
+    a.resume = None
+    with pytest.raises(Exception):
+        launch(_flaky_train_worker, a, 2)

@@ -346,7 +346,9 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                 ctx.data_iter, ctx.prefetcher = build_data_iterator(args, ctx.cfg, mesh)
                 continue
             timed = mb_timing < 0 or ctx.step < mb_timing
-            timer = PhaseTimer(enabled=timed, device=ctx.device)
+            # timed steps also leave their phases in a trace file (logs/trace_rank<r>.json, written at the end of the run)
+            timer = PhaseTimer(enabled=timed, device=ctx.device, step=ctx.step,
+                               events=ctx.extras.setdefault("trace_events", []) if timed and ctx.run_dir else None)
             t0 = time.perf_counter()
             ev0 = ev1 = None
             if ctx.device.type == "cuda":
@@ -412,6 +414,14 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
     finally:
         if ctx.liveness is not None:
             ctx.liveness.mark_exit("finished")
+        if ctx.extras.get("trace_events") and ctx.run_dir:
+            try:
+                from ..utils.timing import write_chrome_trace
+                os.makedirs(os.path.join(ctx.run_dir, "logs"), exist_ok=True)
+                write_chrome_trace(os.path.join(ctx.run_dir, "logs", f"trace_rank{mesh.rank}.json"),
+                                   ctx.extras["trace_events"], mesh.rank)
+            except OSError as ex:
+                ctx.logger.error(f"trace file not written: {ex!r}")
         teardown_worker(ctx)
     return {"losses": losses, "last": last, "steps": ctx.step}
 

@@ -29,10 +29,16 @@ def nvtx_range(name: str):
 
 
 class PhaseTimer:
-    def __init__(self, enabled: bool = True, device: Optional[torch.device] = None):
+    """Host phase split of one step (synchronised at the phase borders on a GPU). With ``events`` (a list shared by the
+    steps of a run) every phase occurrence is also recorded as ``(name, start in us since the epoch, duration in us,
+    step)`` for ``write_chrome_trace``."""
+
+    def __init__(self, enabled: bool = True, device: Optional[torch.device] = None, events: Optional[list] = None,
+                 step: int = 0):
         self.enabled = enabled
         self.cuda = device is not None and device.type == "cuda"
         self.ms: Dict[str, float] = {}
+        self.events, self.step = events, step
 
     @contextlib.contextmanager
     def phase(self, name: str):
@@ -47,10 +53,23 @@ class PhaseTimer:
             yield
         if self.cuda:
             torch.cuda.synchronize()
-        self.ms[name] = self.ms.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
+        dt = time.perf_counter() - t0
+        self.ms[name] = self.ms.get(name, 0.0) + dt * 1e3
+        if self.events is not None:
+            self.events.append((name, (time.time() - dt) * 1e6, dt * 1e6, self.step))
 
     def summary(self) -> Dict[str, float]:
         return {k: round(v, 3) for k, v in self.ms.items()}
+
+
+def write_chrome_trace(path: str, events, rank: int = 0) -> None:
+    """Phase occurrences recorded by ``PhaseTimer`` as a Chrome / Perfetto trace (``chrome://tracing``, ui.perfetto.dev):
+    one complete event per phase occurrence, process = rank, the step number in ``args``."""
+    out = [{"name": n, "ph": "X", "ts": ts, "dur": dur, "pid": rank, "tid": 0, "args": {"step": step}}
+           for (n, ts, dur, step) in events]
+    out.append({"name": "process_name", "ph": "M", "pid": rank, "args": {"name": f"rank {rank}"}})
+    with open(path, "w") as f:
+        json.dump({"traceEvents": out, "displayTimeUnit": "ms"}, f)
 
 
 class DeviceTimer:

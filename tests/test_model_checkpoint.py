@@ -150,11 +150,19 @@ def test_training_run_checkpoint_and_resume(tmp_path):
     assert [s for s, _ in ck.list_checkpoints(os.path.join(run, "checkpoints"))] == [3]
     lines = [json.loads(l) for l in open(os.path.join(run, "metrics.jsonl"))]
     assert len(lines) == 4 and {"loss", "lr_muon", "grad_norm", "tok_per_s", "step_ms"} <= set(lines[0])
-    a = parse_args(["--config", os.path.join(root, "configs/test/checkpoint.yml"), "--resume", "latest", "--max_steps", "6"])
+    a = parse_args(["--config", os.path.join(root, "configs/test/checkpoint.yml"), "--resume", "latest", "--max_steps", "6",
+                    "--mb_timing", "-1"])
     ctx = setup_worker(a, run_dir=run)
     assert ctx.step == 4
     res = run_training_loop(ctx)
     assert res["steps"] == 6
+    # --mb_timing: the phase split goes to the metrics and, as a Chrome trace, to logs/trace_rank0.json
+    lines = [json.loads(l) for l in open(os.path.join(run, "metrics.jsonl"))]
+    assert "phases_ms" in lines[-1] and lines[-1]["phases_ms"]
+    tr = json.load(open(os.path.join(run, "logs", "trace_rank0.json")))["traceEvents"]
+    ph = [e for e in tr if e["ph"] == "X"]
+    assert ph and {e["args"]["step"] for e in ph} == {4, 5} and all(e["dur"] > 0 for e in ph)
+    assert set(lines[-1]["phases_ms"]) <= {e["name"] for e in ph}
 
 
 def test_non_finite_gradients_skip_update_and_clear(tmp_path):

@@ -295,7 +295,7 @@ class FullAttention(nn.Module):
                 cache["k"][rows, idx] = k
                 cache["v"][rows, idx] = v
                 cache["lens"] = [l + 1 for l in lens]
-                o = ops.attention_decode(q, cache["k"], cache["v"], dh ** -0.5, lens=idx + 1)
+                o = ops.attention_decode(q, cache["k"], cache["v"], dh ** -0.5, lens=cache["lens"])
                 return row_linear_sp(o.reshape(T, Hl * dh), self.o_proj_weight)
             assert not any(lens), "the cache takes whole prompts first, then one token per sequence and step"
             cu_l = cu_seqlens.tolist()

@@ -170,23 +170,19 @@ def attention_decode(q, k_cache, v_cache, scale=None, lens=None):
     """One query token per sequence against cached keys / values (the query's own key and value included).
 
     One sequence: q [1, H, dh], k_cache / v_cache [L, H, dh] -> [1, H, dh].
-    N sequences:  q [N, H, dh], k_cache / v_cache [N, cap, H, dh], lens [N] = valid rows per sequence -> [N, H, dh].
+    N sequences:  q [N, H, dh], k_cache / v_cache [N, cap, H, dh], lens = valid rows of every sequence (host ints)
+                  -> [N, H, dh]; each sequence is evaluated over exactly its own rows.
     Bandwidth-bound row operations in fp32 (a product and a sum per cached element), the same code on every device."""
     dh = q.shape[-1]
     if scale is None:
         scale = dh ** -0.5
-    if k_cache.dim() == 3:
-        s = (k_cache * q).sum(-1, dtype=torch.float32) * scale              # [L, H]
-        p = torch.softmax(s, dim=0)
-        o = (p.unsqueeze(-1) * v_cache).sum(0, dtype=torch.float32)         # [H, dh]
-        return o.unsqueeze(0).to(q.dtype)
-    s = (k_cache * q.unsqueeze(1)).sum(-1, dtype=torch.float32) * scale     # [N, cap, H]
-    cap = k_cache.shape[1]
-    dead = torch.arange(cap, device=q.device).unsqueeze(0) >= lens.to(q.device).unsqueeze(1)       # [N, cap]
-    p = torch.softmax(s.masked_fill(dead.unsqueeze(-1), float("-inf")), dim=1)
-    # rows beyond a sequence's length have weight 0; their (uninitialised) values must not turn 0 * x into NaN
-    v = v_cache.masked_fill(dead.view(dead.shape[0], cap, 1, 1), 0)
-    return (p.unsqueeze(-1) * v).sum(1, dtype=torch.float32).to(q.dtype)   # [N, H, dh]
+    if k_cache.dim() == 4:
+        return torch.cat([attention_decode(q[n:n + 1], k_cache[n, :int(lens[n])], v_cache[n, :int(lens[n])], scale)
+                          for n in range(q.shape[0])], 0)
+    s = (k_cache * q).sum(-1, dtype=torch.float32) * scale                  # [L, H]
+    p = torch.softmax(s, dim=0)
+    o = (p.unsqueeze(-1) * v_cache).sum(0, dtype=torch.float32)             # [H, dh]
+    return o.unsqueeze(0).to(q.dtype)
 
 
 def attn_res(sources: List[torch.Tensor], query, norm_weight, eps: float):

@@ -623,10 +623,13 @@ class LMHeadLoss(nn.Module):
         return _VocabParallelLCE.apply(x_shard, self.head_weight(), targets, self.v0,
                                        self.cfg.lce_num_chunks, n_valid_total, self.cfg.lce_epilogue_stats)
 
-    def logits(self, x_shard):
-        """Inference: full-vocab logits for the gathered tokens (gathers vocab shards)."""
+    def logits(self, x_shard, rows: Optional[torch.Tensor] = None):
+        """Inference: full-vocab logits for the gathered tokens (gathers vocab shards). ``rows``: only these token rows
+        of the gathered sequence (decoding needs the last token of every prompt, not ``[tokens, vocab]`` logits)."""
         m = get_mesh()
         x = gather_seq(x_shard)
+        if rows is not None:
+            x = x[rows]
         z = ops.gemm_nt(x.contiguous(), self.head_weight())
         if m.tp == 1:
             return z
@@ -783,32 +786,51 @@ class HippoModel(nn.Module):
     @torch.no_grad()
     def generate_batch(self, prompts: List[torch.Tensor], max_new_tokens, temperature=0.0, top_k=0,
                        eos_token_id: Optional[int] = None) -> List[torch.Tensor]:
-        """Incremental decoding of several sequences at once (no tensor parallelism). The prompts run as one packed
-        varlen stream through the chunked kernels and leave, per layer, the KDA state of every sequence, its
-        short-convolution tail and the keys / values of the full-attention layers; every further step feeds one token
-        per sequence (token-recurrent KDA on the carried states, one query per sequence against its cached keys /
-        values), so a step costs one pass over the weights for the whole batch. ``max_new_tokens``, ``temperature`` and
-        ``top_k`` are one value or one per sequence. A sequence that is done (its limit, or ``eos_token_id``) keeps its
-        slot until the others finish; its further tokens are discarded."""
-        assert self.mesh.tp == 1, "incremental decoding runs without tensor parallelism"
-        N = len(prompts)
-        per = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * N   # noqa: E731
+        """Incremental decoding of several sequences at once. The prompts run as one packed varlen stream through the
+        chunked kernels and leave, per layer, the KDA state of every sequence, its short-convolution tail and the keys /
+        values of the full-attention layers; every further step feeds one token per sequence (token-recurrent KDA on the
+        carried states, one query per sequence against its cached keys / values), so a step costs one pass over the
+        weights for the whole batch. ``max_new_tokens``, ``temperature`` and ``top_k`` are one value or one per sequence.
+        A sequence that is done (its limit, or ``eos_token_id``) keeps its slot until the others finish; its further
+        tokens are discarded.
+
+        Under tensor parallelism (every rank of the group calls this with the same arguments) the token count of each
+        pass must split evenly into sequence-parallel shards: dummy one-token sequences fill the batch up to a multiple
+        of tp and one of them is lengthened so that the packed prompts do too; the sampled tokens are taken from the
+        first rank of the group, so all ranks decode the same text."""
+        m = self.mesh
+        w = m.tp
+        n_real = len(prompts)
+        per = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n_real   # noqa: E731
         limits, temps, topks = per(max_new_tokens), per(temperature), per(top_k)
         seqs = [p.reshape(-1).clone() for p in prompts]
         assert all(s.numel() > 0 for s in seqs), "every prompt needs at least one token"
         dev = seqs[0].device
-        lens = [s.numel() for s in seqs]
         done = [lim <= 0 for lim in limits]
         if all(done):
             return seqs
         steps = max(limits)
+        if w > 1:
+            n_dummy = (-n_real) % w
+            total = sum(s.numel() for s in seqs)
+            if (total + n_dummy) % w and n_dummy == 0:
+                n_dummy = w
+            for i in range(n_dummy):
+                extra = (-(total + n_dummy)) % w if i == 0 else 0
+                seqs.append(torch.zeros(1 + extra, dtype=seqs[0].dtype, device=dev))
+            limits, temps, topks, done = limits + [0] * n_dummy, temps + [0.0] * n_dummy, topks + [0] * n_dummy, \
+                done + [True] * n_dummy
+        N = len(seqs)
+        lens = [s.numel() for s in seqs]
         caches = self.new_decode_caches(max(lens) + steps, N)
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), device=dev, dtype=torch.int32)
         h, states = self.hidden(torch.cat(seqs), cu_seqlens=cu, caches=caches)
-        logits = self.lm_head.logits(h[(cu[1:] - 1).long()]).float()                       # [N, V]
+        logits = self.lm_head.logits(h, rows=(cu[1:] - 1).long()).float()                  # [N, V]
         cu1 = torch.arange(0, N + 1, device=dev, dtype=torch.int32)
         for step in range(steps):
             nxt = torch.stack([self._sample(logits[n], temps[n], topks[n]) for n in range(N)])
+            if w > 1:
+                dist.broadcast(nxt, src=m.tp_ranks()[0], group=m.tp_group)
             picked = nxt.tolist()
             for n in range(N):
                 if done[n]:
@@ -821,24 +843,20 @@ class HippoModel(nn.Module):
             pos = torch.tensor([l + step for l in lens], device=dev)
             h, states = self.hidden(nxt, cu_seqlens=cu1, kda_states=states, caches=caches, position_offset=pos)
             logits = self.lm_head.logits(h).float()
-        return seqs
+        return seqs[:n_real]
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
-                 top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: Optional[bool] = None) -> torch.Tensor:
+                 top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: bool = True) -> torch.Tensor:
         """Greedy / top-k sampling.
 
-        ``use_cache`` (default: on without tensor parallelism): incremental decoding (``generate_batch`` with one
-        sequence): the prompt runs once, every further token is a one-token step on the carried KDA states and the cached
-        keys / values, so a new token costs one pass over the weights instead of a pass over the whole sequence. Without
-        it (and under tensor parallelism, where a one-token step has no even sequence-parallel shard) every token re-runs
-        the full forward as the reference does (``src/models/model.py:180-219``), with the prompt padded to a multiple
-        of tp."""
+        ``use_cache`` (default): incremental decoding (``generate_batch`` with one sequence): the prompt runs once, every
+        further token is a one-token step on the carried KDA states and the cached keys / values, so a new token costs one
+        pass over the weights instead of a pass over the whole sequence. ``use_cache=False`` re-runs the full forward for
+        every token as the reference does (``src/models/model.py:180-219``), with the prompt padded to a multiple of tp."""
         ids = input_ids.reshape(-1).clone()
         w = self.mesh.tp
-        if use_cache is None:
-            use_cache = w == 1
-        if use_cache and w == 1 and max_new_tokens > 0 and ids.numel() > 0:
+        if use_cache and max_new_tokens > 0 and ids.numel() > 0:
             return self.generate_batch([ids], max_new_tokens, temperature, top_k, eos_token_id)[0]
         for _ in range(max_new_tokens):
             T = ids.numel()
@@ -847,6 +865,8 @@ class HippoModel(nn.Module):
             cu = torch.tensor([0, Tp], device=ids.device, dtype=torch.int32)
             logits = self.forward(padded, cu_seqlens=cu)["logits"][T - 1].float()
             nxt = self._sample(logits, temperature, top_k)
+            if w > 1:
+                dist.broadcast(nxt, src=self.mesh.tp_ranks()[0], group=self.mesh.tp_group)
             ids = torch.cat([ids, nxt.reshape(1)])
             if eos_token_id is not None and int(nxt) == eos_token_id:
                 break

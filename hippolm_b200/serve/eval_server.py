@@ -52,7 +52,7 @@ class EvalService:
         self.batches_run = 0                 # decoding passes so far, and the largest number of requests one of them served
         self.largest_batch = 0
         self._queue: "queue.Queue[_Pending]" = queue.Queue()
-        self._batched = model.mesh.tp == 1
+        self._batched = True
         self.lock = threading.Lock()
         self._worker = threading.Thread(target=self._decode_loop, name="eval-decode", daemon=True)
         self._worker.start()

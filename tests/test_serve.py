@@ -156,3 +156,45 @@ def test_eval_server_decodes_waiting_requests_together():
         t.join(timeout=60)
     assert [r["choices"][0]["text"] for r in results] == alone
     assert svc.largest_batch == len(bodies) - 1
+
+
+def _tp_decode_worker(rank, world, port, out_path, kw):
+    import os
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "HIPPO_TP_SIM": "1"})
+    torch.set_num_threads(1)
+    from hippolm_b200.parallel.mesh import init_distributed_from_env, init_mesh
+    init_distributed_from_env(backend="gloo")
+    init_mesh(tp=world)
+    base = dict(vocab_size=96, hidden_size=32, num_heads=2, head_dim=16, num_layers=4, num_blocks=2, intermediate_size=64,
+                full_attn_interval=2)
+    base.update(kw)
+    m = HippoModel(HippoConfig(**base), seed=4).eval()
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, 96, (n,), generator=g) for n in (5, 2, 8)]       # three sequences, 15 tokens: both odd
+    limits = [4, 6, 3]
+    batch = m.generate_batch(prompts, limits)
+    alone = [m.generate(p, lim, use_cache=False) for p, lim in zip(prompts, limits)]
+    one = m.generate(prompts[0], 4)
+    torch.manual_seed(100 + rank)                                                 # different sampling streams per rank
+    sampled = m.generate_batch(prompts[:2], 5, temperature=0.9, top_k=8)
+    torch.save({"batch": [t.tolist() for t in batch], "alone": [t.tolist() for t in alone], "one": one.tolist(),
+                "sampled": [t.tolist() for t in sampled]}, out_path + f".{rank}")
+    import torch.distributed as dist
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(use_short_conv=True)])
+def test_incremental_decoding_under_tensor_parallelism(tmp_path, kw):
+    """Two tensor-parallel ranks over gloo: the batch is filled up with dummy sequences so that every pass splits into even
+    sequence-parallel shards; both ranks produce the tokens of the full re-forward, and sampled tokens come from rank 0."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "tp")
+    mp.spawn(_tp_decode_worker, args=(2, port, out, kw), nprocs=2, join=True)
+    r0, r1 = torch.load(out + ".0"), torch.load(out + ".1")
+    assert r0["batch"] == r0["alone"] == r1["batch"] == r1["alone"]
+    assert r0["one"] == r0["alone"][0] == r1["one"]
+    assert r0["sampled"] == r1["sampled"] and [len(t) for t in r0["sampled"]] == [10, 7]

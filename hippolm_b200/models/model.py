@@ -757,13 +757,19 @@ class HippoModel(nn.Module):
             out["logits"] = self.lm_head.logits(h)
         return out
 
-    def _sample(self, logits, temperature: float, top_k: int):
+    def _sample(self, logits, temperature: float, top_k: int, top_p: float = 1.0):
+        """Greedy for temperature <= 0; else temperature, then top-k, then nucleus (top-p) filtering, then one draw."""
         if temperature <= 0:
             return logits.argmax()
         logits = logits / temperature
         if top_k > 0:
-            kth = logits.topk(top_k).values[-1]
+            kth = logits.topk(min(top_k, logits.numel())).values[-1]
             logits = logits.masked_fill(logits < kth, float("-inf"))
+        if 0.0 < top_p < 1.0:
+            sl, si = logits.sort(descending=True)
+            cum = sl.softmax(-1).cumsum(-1)
+            drop = cum - sl.softmax(-1) >= top_p                 # tokens that start beyond the nucleus; the first one stays
+            logits = logits.masked_fill(torch.zeros_like(drop).scatter(0, si, drop), float("-inf"))
         return torch.multinomial(logits.softmax(-1), 1)[0]
 
     def new_decode_caches(self, capacity: int, n_seq: int = 1) -> List[dict]:
@@ -785,12 +791,13 @@ class HippoModel(nn.Module):
 
     @torch.no_grad()
     def generate_batch(self, prompts: List[torch.Tensor], max_new_tokens, temperature=0.0, top_k=0,
-                       eos_token_id: Optional[int] = None) -> List[torch.Tensor]:
+                       eos_token_id: Optional[int] = None, top_p=1.0) -> List[torch.Tensor]:
         """Incremental decoding of several sequences at once. The prompts run as one packed varlen stream through the
         chunked kernels and leave, per layer, the KDA state of every sequence, its short-convolution tail and the keys /
         values of the full-attention layers; every further step feeds one token per sequence (token-recurrent KDA on the
         carried states, one query per sequence against its cached keys / values), so a step costs one pass over the
-        weights for the whole batch. ``max_new_tokens``, ``temperature`` and ``top_k`` are one value or one per sequence.
+        weights for the whole batch. ``max_new_tokens``, ``temperature``, ``top_k`` and ``top_p`` are one value or one per
+        sequence.
         A sequence that is done (its limit, or ``eos_token_id``) keeps its slot until the others finish; its further
         tokens are discarded.
 
@@ -802,7 +809,7 @@ class HippoModel(nn.Module):
         w = m.tp
         n_real = len(prompts)
         per = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n_real   # noqa: E731
-        limits, temps, topks = per(max_new_tokens), per(temperature), per(top_k)
+        limits, temps, topks, topps = per(max_new_tokens), per(temperature), per(top_k), per(top_p)
         seqs = [p.reshape(-1).clone() for p in prompts]
         assert all(s.numel() > 0 for s in seqs), "every prompt needs at least one token"
         dev = seqs[0].device
@@ -820,6 +827,7 @@ class HippoModel(nn.Module):
                 seqs.append(torch.zeros(1 + extra, dtype=seqs[0].dtype, device=dev))
             limits, temps, topks, done = limits + [0] * n_dummy, temps + [0.0] * n_dummy, topks + [0] * n_dummy, \
                 done + [True] * n_dummy
+            topps = topps + [1.0] * n_dummy
         N = len(seqs)
         lens = [s.numel() for s in seqs]
         caches = self.new_decode_caches(max(lens) + steps, N)
@@ -828,7 +836,7 @@ class HippoModel(nn.Module):
         logits = self.lm_head.logits(h, rows=(cu[1:] - 1).long()).float()                  # [N, V]
         cu1 = torch.arange(0, N + 1, device=dev, dtype=torch.int32)
         for step in range(steps):
-            nxt = torch.stack([self._sample(logits[n], temps[n], topks[n]) for n in range(N)])
+            nxt = torch.stack([self._sample(logits[n], temps[n], topks[n], topps[n]) for n in range(N)])
             if w > 1:
                 dist.broadcast(nxt, src=m.tp_ranks()[0], group=m.tp_group)
             picked = nxt.tolist()
@@ -847,7 +855,8 @@ class HippoModel(nn.Module):
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 0.0,
-                 top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: bool = True) -> torch.Tensor:
+                 top_k: int = 0, eos_token_id: Optional[int] = None, use_cache: bool = True,
+                 top_p: float = 1.0) -> torch.Tensor:
         """Greedy / top-k sampling.
 
         ``use_cache`` (default): incremental decoding (``generate_batch`` with one sequence): the prompt runs once, every
@@ -857,14 +866,14 @@ class HippoModel(nn.Module):
         ids = input_ids.reshape(-1).clone()
         w = self.mesh.tp
         if use_cache and max_new_tokens > 0 and ids.numel() > 0:
-            return self.generate_batch([ids], max_new_tokens, temperature, top_k, eos_token_id)[0]
+            return self.generate_batch([ids], max_new_tokens, temperature, top_k, eos_token_id, top_p)[0]
         for _ in range(max_new_tokens):
             T = ids.numel()
             Tp = _pad_to(T, w)
             padded = torch.cat([ids, ids.new_zeros(Tp - T)]) if Tp > T else ids
             cu = torch.tensor([0, Tp], device=ids.device, dtype=torch.int32)
             logits = self.forward(padded, cu_seqlens=cu)["logits"][T - 1].float()
-            nxt = self._sample(logits, temperature, top_k)
+            nxt = self._sample(logits, temperature, top_k, top_p)
             if w > 1:
                 dist.broadcast(nxt, src=self.mesh.tp_ranks()[0], group=self.mesh.tp_group)
             ids = torch.cat([ids, nxt.reshape(1)])

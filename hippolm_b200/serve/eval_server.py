@@ -36,10 +36,10 @@ def build_model_and_load(ckpt_path: Optional[str], cfg: HippoConfig, device: tor
 
 
 class _Pending:
-    __slots__ = ("ids", "max_tokens", "temperature", "top_k", "done", "new", "error")
+    __slots__ = ("ids", "max_tokens", "temperature", "top_k", "top_p", "done", "new", "error")
 
-    def __init__(self, ids, max_tokens, temperature, top_k):
-        self.ids, self.max_tokens, self.temperature, self.top_k = ids, max_tokens, temperature, top_k
+    def __init__(self, ids, max_tokens, temperature, top_k, top_p=1.0):
+        self.ids, self.max_tokens, self.temperature, self.top_k, self.top_p = ids, max_tokens, temperature, top_k, top_p
         self.done = threading.Event()
         self.new, self.error = None, None
 
@@ -73,10 +73,11 @@ class EvalService:
                 with self.lock:
                     if self._batched:
                         outs = self.model.generate_batch(prompts, [p.max_tokens for p in batch],
-                                                         [p.temperature for p in batch], [p.top_k for p in batch], eos)
+                                                         [p.temperature for p in batch], [p.top_k for p in batch], eos,
+                                                         [p.top_p for p in batch])
                     else:
                         outs = [self.model.generate(x, p.max_tokens, temperature=p.temperature, top_k=p.top_k,
-                                                    eos_token_id=eos) for x, p in zip(prompts, batch)]
+                                                    eos_token_id=eos, top_p=p.top_p) for x, p in zip(prompts, batch)]
                 self.batches_run += 1
                 self.largest_batch = max(self.largest_batch, len(batch))
                 for p, o in zip(batch, outs):
@@ -87,11 +88,11 @@ class EvalService:
             for p in batch:
                 p.done.set()
 
-    def _generate(self, prompt_ids, max_tokens: int, temperature: float, top_k: int):
+    def _generate(self, prompt_ids, max_tokens: int, temperature: float, top_k: int, top_p: float = 1.0):
         if not prompt_ids:                                            # nothing to condition on: start from the EOS token
             eos0 = getattr(self.tok, "eos_token_id", None)
             prompt_ids = [eos0 if eos0 is not None else 0]
-        req = _Pending(list(prompt_ids), max(0, min(max_tokens, self.max_new)), temperature, top_k)
+        req = _Pending(list(prompt_ids), max(0, min(max_tokens, self.max_new)), temperature, top_k, top_p)
         self._queue.put(req)
         req.done.wait()
         if req.error is not None:
@@ -110,8 +111,13 @@ class EvalService:
                 prompt = prompt[0] if prompt else ""
         ids = self.tok.encode(prompt, add_special_tokens=False)
         new, finish = self._generate(ids, int(body.get("max_tokens", 64)), float(body.get("temperature", 0.0)),
-                                     int(body.get("top_k", 0)))
+                                     int(body.get("top_k", 0)), float(body.get("top_p", 1.0)))
         text = self.tok.decode(new, skip_special_tokens=True)
+        stop = body.get("stop")
+        if stop:                                                      # the text ends before the first stop string
+            cuts = [text.find(s) for s in ([stop] if isinstance(stop, str) else list(stop)) if s and text.find(s) >= 0]
+            if cuts:
+                text, finish = text[:min(cuts)], "stop"
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(new), "total_tokens": len(ids) + len(new)}
         base = {"id": f"cmpl-{uuid.uuid4().hex[:12]}", "created": int(time.time()), "model": self.name, "usage": usage}
         if chat:

@@ -198,3 +198,24 @@ def test_incremental_decoding_under_tensor_parallelism(tmp_path, kw):
     assert r0["batch"] == r0["alone"] == r1["batch"] == r1["alone"]
     assert r0["one"] == r0["alone"][0] == r1["one"]
     assert r0["sampled"] == r1["sampled"] and [len(t) for t in r0["sampled"]] == [10, 7]
+
+
+def test_sampling_filters_and_stop_strings():
+    cfg = HippoConfig(vocab_size=258, hidden_size=32, num_heads=2, head_dim=16, num_layers=2, num_blocks=1,
+                      intermediate_size=64, full_attn_interval=2)
+    m = HippoModel(cfg, seed=2).eval()
+    logits = torch.tensor([4.0, 3.0, 2.0, -1.0, -2.0])
+    torch.manual_seed(0)
+    # nucleus of 0.6: softmax = [.66, .24, .09, ...] -> only token 0 survives; 0.8 -> tokens 0 and 1
+    assert {int(m._sample(logits, 1.0, 0, 0.6)) for _ in range(50)} == {0}
+    assert {int(m._sample(logits, 1.0, 0, 0.8)) for _ in range(200)} == {0, 1}
+    assert {int(m._sample(logits, 1.0, 2, 1.0)) for _ in range(200)} == {0, 1}
+    assert int(m._sample(logits, 0.0, 0, 0.5)) == 0
+    svc = EvalService(m, ByteTokenizer(), max_new_tokens=8)
+    full = svc.complete({"prompt": "hello", "max_tokens": 8}, chat=False)["choices"][0]
+    assert full["finish_reason"] in ("length", "stop") and len(full["text"]) > 0
+    if len(full["text"]) >= 3:
+        cut = svc.complete({"prompt": "hello", "max_tokens": 8, "stop": [full["text"][2:4]]}, chat=False)["choices"][0]
+        assert cut["finish_reason"] == "stop" and cut["text"] == full["text"][:full["text"].find(full["text"][2:4])]
+    out = svc.complete({"prompt": "hello", "max_tokens": 4, "temperature": 0.7, "top_p": 0.9, "top_k": 20}, chat=False)
+    assert out["usage"]["completion_tokens"] <= 4

@@ -1,6 +1,7 @@
 """OpenAI-compatible evaluation server on the standard library (``scripts/eval_server.py:94-575``).
 
-Endpoints: ``GET /health``, ``GET /v1/models``, ``POST /v1/completions``, ``POST /v1/chat/completions``.
+Endpoints: ``GET /health``, ``GET /v1/models``, ``GET /metrics`` (Prometheus text format: requests, tokens, decoding
+passes, latency), ``POST /v1/completions``, ``POST /v1/chat/completions``.
 Greedy decoding (temperature 0) or temperature / top-k sampling; chat requests are rendered with the tokenizer's chat
 template (ChatML for the byte tokenizer). Requests that arrive while a batch is being decoded wait in a queue; the decoding
 thread takes up to ``max_batch`` of them at a time and runs them through ``HippoModel.generate_batch`` together (one packed
@@ -51,6 +52,8 @@ class EvalService:
         self.max_batch = max(1, int(max_batch))
         self.batches_run = 0                 # decoding passes so far, and the largest number of requests one of them served
         self.largest_batch = 0
+        self.stats = {"requests": 0, "failed": 0, "prompt_tokens": 0, "completion_tokens": 0, "latency_s": 0.0}
+        self._stats_lock = threading.Lock()
         self._queue: "queue.Queue[_Pending]" = queue.Queue()
         self._batched = True
         self.lock = threading.Lock()
@@ -102,7 +105,35 @@ class EvalService:
         finish = "stop" if (new and eos is not None and new[-1] == eos) else "length"
         return new, finish
 
+    def metrics_text(self) -> str:
+        """Counters of this service in the Prometheus text exposition format."""
+        with self._stats_lock:
+            st = dict(self.stats)
+        rows = [("hippo_requests_total", "counter", st["requests"]), ("hippo_requests_failed_total", "counter", st["failed"]),
+                ("hippo_prompt_tokens_total", "counter", st["prompt_tokens"]),
+                ("hippo_completion_tokens_total", "counter", st["completion_tokens"]),
+                ("hippo_request_latency_seconds_sum", "counter", round(st["latency_s"], 6)),
+                ("hippo_decode_passes_total", "counter", self.batches_run),
+                ("hippo_decode_largest_batch", "gauge", self.largest_batch),
+                ("hippo_queue_depth", "gauge", self._queue.qsize())]
+        return "".join(f"# TYPE {n} {t}\n{n} {v}\n" for n, t, v in rows)
+
     def complete(self, body: dict, chat: bool) -> dict:
+        t0 = time.perf_counter()
+        try:
+            out = self._complete(body, chat)
+        except Exception:
+            with self._stats_lock:
+                self.stats["requests"] += 1; self.stats["failed"] += 1
+            raise
+        with self._stats_lock:
+            self.stats["requests"] += 1
+            self.stats["prompt_tokens"] += out["usage"]["prompt_tokens"]
+            self.stats["completion_tokens"] += out["usage"]["completion_tokens"]
+            self.stats["latency_s"] += time.perf_counter() - t0
+        return out
+
+    def _complete(self, body: dict, chat: bool) -> dict:
         if chat:
             prompt = self.tok.apply_chat_template(body.get("messages", []), tokenize=False, add_generation_prompt=True)
         else:
@@ -146,6 +177,13 @@ def make_handler(svc: EvalService):
                 self._send(200, {"status": "ok"})
             elif self.path == "/v1/models":
                 self._send(200, {"object": "list", "data": [{"id": svc.name, "object": "model"}]})
+            elif self.path == "/metrics":
+                data = svc.metrics_text().encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
             else:
                 self._send(404, {"error": "not found"})
 

@@ -37,6 +37,12 @@ def test_eval_server_roundtrip(tmp_path):
         assert 1 <= out["usage"]["completion_tokens"] <= 3
         out = _post(url + "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2})
         assert out["choices"][0]["message"]["role"] == "assistant"
+        with urllib.request.urlopen(url + "/metrics", timeout=10) as r:
+            text = r.read().decode()
+        vals = {l.split()[0]: float(l.split()[1]) for l in text.splitlines() if l and not l.startswith("#")}
+        assert vals["hippo_requests_total"] == 2 and vals["hippo_requests_failed_total"] == 0
+        assert vals["hippo_prompt_tokens_total"] >= 3 and 2 <= vals["hippo_completion_tokens_total"] <= 5
+        assert vals["hippo_decode_passes_total"] == 2 and vals["hippo_request_latency_seconds_sum"] > 0
     finally:
         srv.shutdown()
 

@@ -8,7 +8,7 @@ from hypothesis import given, settings, strategies as st
 from hippolm_b200.data.packing import pack_chunk_aligned, slice_cu_seqlens, synthetic_packed_batch
 from hippolm_b200.optim.schedule import wsd_lr
 
-settings.register_profile("repo", max_examples=60, deadline=None)
+settings.register_profile("repo", max_examples=60, deadline=None, derandomize=True, database=None)
 settings.load_profile("repo")
 
 

@@ -59,11 +59,20 @@ def test_cli_over_yaml_and_unknown_keys(tmp_path):
 
 def test_repo_configs_parse():
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
-    for name in ("base.yml", "cpu_plumbing.yml", "hybrid_1p3b_tp2.yml", "hybrid_7b_tp8.yml",
-                 "hybrid_7b_dp2tp4_offload.yml", "test/quick.yml", "test/tp2.yml", "test/nvfp4.yml"):
+    import glob
+    names = sorted(os.path.relpath(p, root) for p in glob.glob(os.path.join(root, "*.yml")) + glob.glob(os.path.join(root, "test", "*.yml")))
+    assert {"base.yml", "cpu_plumbing.yml", "hybrid_7b_tp8.yml", "hippolm_production.yml", "test/quick.yml"} <= set(names)
+    for name in names:
         ns = parse_args(["--config", os.path.join(root, name)])
         cfg = HippoConfig.from_namespace(ns)
         assert cfg.num_layers % cfg.num_blocks == 0
+    # the reference's production setup carried over: all layers KDA, its dimensions, optimizer and data keys
+    ns = parse_args(["--config", os.path.join(root, "hippolm_production.yml")])
+    cfg = HippoConfig.from_namespace(ns)
+    assert set(cfg.layer_types()) == {"kda"} and (cfg.hidden_size, cfg.num_heads, cfg.head_dim) == (1536, 12, 128)
+    assert cfg.tie_word_embeddings and cfg.use_short_conv and cfg.safe_gate and cfg.ffn_nvfp4_no_bf16_master
+    assert (ns.muon_lr, ns.learning_rate, ns.seq_len, ns.micro_batch_size, ns.tp_size) == (0.02, 0.004, 262144, 16384, 2)
+    assert ns.pretrain_multi_source and ns.use_modelscope and ns.checkpoint_interval == 100
     ns = parse_args(["--config", os.path.join(root, "hybrid_7b_tp8.yml")])
     cfg = HippoConfig.from_namespace(ns)
     assert cfg.layer_types().count("attn") == 8 and cfg.layer_types().count("kda") == 24

@@ -30,7 +30,12 @@ def build_model_and_load(ckpt_path: Optional[str], cfg: HippoConfig, device: tor
     if ckpt_path:
         ck = torch.load(ckpt_path, map_location=device, weights_only=False)
         sd = ck.get("model_state_dict", ck)
-        if is_sharded_state_dict(sd):
+        from ..train.convert import convert_reference_state_dict, detect_layout
+        if detect_layout(sd) != "native":
+            # a checkpoint of the reference (single-GPU or one-device tensor-parallel layout): rename / fuse its tensors;
+            # a multi-device tensor-parallel file is refused there with the reason
+            sd = convert_reference_state_dict(sd)
+        elif is_sharded_state_dict(sd):
             raise ValueError("checkpoint uses a per-device key layout; export the plain layers.N.* layout first")
         model.load_state_dict(sd, strict=True)
     return model.eval()

@@ -38,13 +38,24 @@ def cases(seed=0):
     return wsd, slices, packs
 
 
+def ns_inputs(seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(shape, generator=g) * scale for shape, scale in (((48, 96), 1.0), ((96, 48), 0.01), ((64, 64), 30.0))]
+
+
 def main():
     ref_root, out = sys.argv[1], sys.argv[2]
     sys.path.insert(0, ref_root)
     from src.training.loop.support import wsd_lr, _slice_cu_seqlens
     from src.training.data.collate import pack_chunk_aligned
     wsd, slices, packs = cases()
-    res = {"wsd": [wsd_lr(*c) for c in wsd], "slices": [], "packs": []}
+    res = {"wsd": [wsd_lr(*c) for c in wsd], "slices": [], "packs": [], "ns": []}
+    # Newton-Schulz orthogonalisation of the reference's Muon (fp16 inside), called on its unbound method
+    import types
+    from src.training.param_offload.muon import CPUMuon
+    me = types.SimpleNamespace(_NS_COEFFS=CPUMuon._NS_COEFFS, ns_steps=5)
+    for x in ns_inputs():
+        res["ns"].append(CPUMuon._newton_schulz(me, x.clone()).float())
     for cu, a, b in slices:
         if b < a:
             a, b = b, a

@@ -15,7 +15,7 @@ REF = os.path.join(ROOT, "baseline", "_ref")
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src")), reason="no copy of the reference tree")
 def test_schedule_slicing_and_packer_equal_the_reference(tmp_path):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from reference_functions_worker import cases
+    from reference_functions_worker import cases, ns_inputs
     from hippolm_b200.optim.schedule import wsd_lr
     from hippolm_b200.data.packing import pack_chunk_aligned, slice_cu_seqlens
     out = str(tmp_path / "ref.pt")
@@ -46,3 +46,9 @@ def test_schedule_slicing_and_packer_equal_the_reference(tmp_path):
         assert cu.tolist() == cu_r.tolist(), (cu.tolist(), cu_r.tolist())
         n_docs += len(docs)
     assert n_docs > 300
+    # Newton-Schulz: same polynomial, same normalisation; the reference iterates in fp16, the oracle here in fp32
+    from hippolm_b200.ref.ops import newton_schulz5
+    for x, want in zip(ns_inputs(), ref["ns"]):
+        got = newton_schulz5(x, 5)
+        assert got.shape == want.shape
+        assert (got - want).abs().max() < 2e-2 and torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0) > 0.9995

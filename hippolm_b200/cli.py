@@ -65,6 +65,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--log_interval", type=int, default=1); a("--checkpoint_interval", type=int, default=0)
     a("--checkpoint_keep_last_n", type=int, default=3); a("--output_dir", type=str, default="output")
     a("--max_restarts", type=int, default=0)
+    a("--init_from", type=str, default=None)
     a("--resume", type=str, default=None); a("--diagnostics", type=_bool, default=False)
     a("--mb_timing", type=int, default=0); a("--empty_cache_between_mb", type=_bool, default=False)
     a("--peer_timeout_s", type=float, default=0.0); a("--dist_timeout_s", type=float, default=1800.0); a("--watchdog_timeout_s", type=float, default=0.0)

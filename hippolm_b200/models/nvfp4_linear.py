@@ -152,8 +152,19 @@ class NVFP4Linear(nn.Module):
         self._wt_cache = (ver, packed, scales, gs)
         return packed, scales, gs
 
-    def _load_from_state_dict(self, *args, **kwargs):
-        super()._load_from_state_dict(*args, **kwargs)
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        if self.no_master and prefix + "weight" in state_dict and prefix + "packed_weight" not in state_dict:
+            # plain values for a weight that is kept without a master copy (a merged or converted checkpoint): quantise
+            w = state_dict.pop(prefix + "weight")
+            packed, scales, gs = ops.nvfp4_quantize(w.to(device=self.packed_weight.device, dtype=torch.float32))
+            state_dict[prefix + "packed_weight"], state_dict[prefix + "scales"] = packed, scales
+            state_dict[prefix + "global_scale"] = gs.float()
+        elif not self.no_master and prefix + "packed_weight" in state_dict and prefix + "weight" not in state_dict:
+            # stored codes for a module that trains through a master copy: the master starts from the dequantised values
+            state_dict[prefix + "weight"] = ops.nvfp4_dequantize(
+                state_dict.pop(prefix + "packed_weight"), state_dict.pop(prefix + "scales"),
+                state_dict.pop(prefix + "global_scale"), self.weight.dtype)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
         self.weight_changed()
 
     # ------------------------------------------------------------------ chunk API (optimizer side)

@@ -28,7 +28,14 @@ from ..train.checkpoint import is_sharded_state_dict
 def build_model_and_load(ckpt_path: Optional[str], cfg: HippoConfig, device: torch.device, dtype=torch.float32) -> HippoModel:
     model = HippoModel(cfg, device=device, dtype=dtype)
     if ckpt_path:
-        ck = torch.load(ckpt_path, map_location=device, weights_only=False)
+        from ..train import checkpoint as _ckpt
+        man = _ckpt.read_manifest(ckpt_path)
+        if man is not None and int(man.get("tp", 1)) > 1:
+            # written by a tensor-parallel run: put the shards of the ranks back together
+            from ..train.reshard import merge_checkpoint
+            ck = merge_checkpoint(ckpt_path, cfg)
+        else:
+            ck = torch.load(ckpt_path, map_location=device, weights_only=False)
         sd = ck.get("model_state_dict", ck)
         from ..train.convert import convert_reference_state_dict, detect_layout
         if detect_layout(sd) != "native":

@@ -152,6 +152,17 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
                     f"offload={offload} fused_comm={fused_on}")
         if run_dir:
             ctx.metrics_file = open(os.path.join(run_dir, "metrics.jsonl"), "a")
+    init_from = getattr(args, "init_from", None)
+    if init_from and not getattr(args, "resume", None):
+        # Model weights from a plain single-file checkpoint (this framework's TP = 1 layout, shards merged by
+        # train/reshard.py, or a checkpoint of the reference in either of its layouts): every rank cuts its own tensor-
+        # parallel shard out of it. Step, optimizer moments and data position start afresh.
+        from .convert import convert_reference_state_dict
+        from .reshard import merge_checkpoint, split_plain_state_dict
+        sd = convert_reference_state_dict(merge_checkpoint(init_from, cfg)["model_state_dict"])
+        model.load_state_dict(split_plain_state_dict(sd, cfg, mesh.tp, mesh.tp_rank), strict=True)
+        model.after_optimizer_step()
+        logger.info(f"model weights initialised from {init_from} (tp shard {mesh.tp_rank} of {mesh.tp})")
     resume = getattr(args, "resume", None)
     data_step = 0
     if resume:

@@ -225,3 +225,31 @@ def test_sampling_filters_and_stop_strings():
         assert cut["finish_reason"] == "stop" and cut["text"] == full["text"][:full["text"].find(full["text"][2:4])]
     out = svc.complete({"prompt": "hello", "max_tokens": 4, "temperature": 0.7, "top_p": 0.9, "top_k": 20}, chat=False)
     assert out["usage"]["completion_tokens"] <= 4
+
+
+def test_offline_perplexity_matches_per_document_cross_entropy(tmp_path):
+    import math
+    import torch.nn.functional as F
+    from hippolm_b200.serve.perplexity import evaluate_perplexity, iter_documents
+    cfg = HippoConfig(vocab_size=258, hidden_size=32, num_heads=2, head_dim=16, num_layers=2, num_blocks=1,
+                      intermediate_size=64, full_attn_interval=2)
+    m = HippoModel(cfg, seed=6).eval()
+    tok = ByteTokenizer()
+    docs = ["hello world, this is a document.", "x" * 150, "short", "another one with some more text in it " * 3, "ab"]
+    (tmp_path / "a.txt").write_text("\n\n".join(docs[:3]))
+    (tmp_path / "b.jsonl").write_text("\n".join(json.dumps({"content": d}) for d in docs[3:]))
+    got = evaluate_perplexity(m, tok, iter_documents([tmp_path / "a.txt", tmp_path / "b.jsonl"]), seq_len=128, batch_rows=2)
+    nll, n = 0.0, 0
+    eos = tok.eos_token_id
+    with torch.no_grad():
+        for d in docs:
+            ids = tok.encode(d, add_special_tokens=False) + ([eos] if eos is not None else [])
+            for s in range(0, len(ids), 128):
+                piece = torch.tensor(ids[s:s + 128])
+                if piece.numel() < 2:
+                    continue
+                logits = m(piece)["logits"].float()
+                nll += float(F.cross_entropy(logits[:-1], piece[1:], reduction="sum"))
+                n += piece.numel() - 1
+    assert got["tokens"] == n and got["documents"] == len(docs)
+    assert abs(got["nll"] - nll / n) < 1e-4 and abs(got["perplexity"] - math.exp(nll / n)) < 1e-2 * math.exp(nll / n)

@@ -253,3 +253,14 @@ def test_offline_perplexity_matches_per_document_cross_entropy(tmp_path):
                 n += piece.numel() - 1
     assert got["tokens"] == n and got["documents"] == len(docs)
     assert abs(got["nll"] - nll / n) < 1e-4 and abs(got["perplexity"] - math.exp(nll / n)) < 1e-2 * math.exp(nll / n)
+
+
+def test_generate_script(capsys):
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "scripts"))
+    import importlib
+    gen = importlib.import_module("generate")
+    text = gen.main(["--config", os.path.join(root, "configs/test/quick.yml"), "--prompt", "hello", "--max_new_tokens", "5"])
+    assert isinstance(text, str) and capsys.readouterr().out.strip() == text.strip()

@@ -18,9 +18,9 @@ def _round_up(n: int, m: int) -> int:
 
 
 def pack_chunk_aligned(samples: Sequence[Sequence[int]], seq_len: int, chunk_size: int, batch_size: int,
-                       pad_id: int = 0, eos_id: Optional[int] = None
-                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Returns ``(input_ids[B,S], labels[B,S], cu_seqlens)``.
+                       pad_id: int = 0, eos_id: Optional[int] = None, return_placed: bool = False):
+    """Returns ``(input_ids[B,S], labels[B,S], cu_seqlens)``; with ``return_placed`` also the indices (into ``samples``)
+    of the documents that were placed, so that a caller can carry the others over to its next batch.
 
     Documents are sorted by chunk count (descending) and placed first-fit into exactly
     ``batch_size`` rows; each document starts on a ``chunk_size`` multiple and is padded up to the
@@ -36,21 +36,25 @@ def pack_chunk_aligned(samples: Sequence[Sequence[int]], seq_len: int, chunk_siz
     if seq_len % chunk_size != 0:
         raise ValueError(f"seq_len ({seq_len}) must be a multiple of chunk_size ({chunk_size})")
     docs: List[List[int]] = []
-    for s in samples:
+    src: List[int] = []                                   # index of every kept document in ``samples``
+    for si, s in enumerate(samples):
         d = list(s)
         if eos_id is not None and (len(d) == 0 or d[-1] != eos_id):
             d.append(eos_id)
         if 0 < len(d) <= seq_len:
             docs.append(d)
+            src.append(si)
     order = sorted(range(len(docs)), key=lambda i: -_round_up(len(docs[i]), chunk_size))
     used = [0] * batch_size
     rows: List[List[Tuple[int, List[int]]]] = [[] for _ in range(batch_size)]
+    placed: List[int] = []
     for i in order:
         need = _round_up(len(docs[i]), chunk_size)
         for b in range(batch_size):
             if used[b] + need <= seq_len:
                 rows[b].append((used[b], docs[i]))
                 used[b] += need
+                placed.append(src[i])
                 break
     ids = torch.full((batch_size, seq_len), pad_id, dtype=torch.long)
     labels = torch.full((batch_size, seq_len), -100, dtype=torch.long)
@@ -67,6 +71,8 @@ def pack_chunk_aligned(samples: Sequence[Sequence[int]], seq_len: int, chunk_siz
             bounds.add(base + used[b])
         bounds.add(base + seq_len)
     cu = torch.tensor(sorted(bounds), dtype=torch.long)
+    if return_placed:
+        return ids, labels, cu, sorted(placed)
     return ids, labels, cu
 
 

@@ -44,8 +44,10 @@ def _pin(t: torch.Tensor) -> torch.Tensor:
 
 class PrefetchBatcher:
     """Pulls tokenised documents from ``doc_iter``, packs ``batch_size`` rows with the FFD chunk-aligned
-    packer from a buffer of ``batch_size * pack_buffer_size`` documents and puts the same batch dict on
-    every queue. Exceptions and end-of-data are forwarded to all queues."""
+    packer from a window of documents (up to ``batch_size * pack_buffer_size`` of them, or twice the batch's token
+    capacity) and puts the same batch dict on every queue. Documents of the window that found no room are carried over
+    into the next window, so every document (that fits a row at all) is eventually emitted; the reference discards them
+    (``src/training/data/prefetch_batcher.py:103-108``). Exceptions and end-of-data are forwarded to all queues."""
 
     def __init__(self, doc_iter: Iterable[Sequence[int]], queues: List, batch_size: int, seq_len: int,
                  chunk_size: int, pack_buffer_size: int = 2048, pad_id: int = 0, eos_id: Optional[int] = None,
@@ -55,22 +57,35 @@ class PrefetchBatcher:
         self.buffer_docs = max(1, batch_size * pack_buffer_size)
         self.pad_id, self.eos_id = pad_id, eos_id
         self.collate = collate or pack_chunk_aligned
+        self._carry: List[Sequence[int]] = []          # documents read but not placed yet
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, name="prefetch-batcher", daemon=True)
         self._thread.start()
 
     def _next_batch(self):
-        docs = []
+        docs = list(self._carry)
         budget = self.batch_size * self.seq_len
-        tokens = 0
-        for d in self.doc_iter:
-            docs.append(d)
-            tokens += len(d)
-            if len(docs) >= self.buffer_docs or tokens >= 2 * budget:
-                break
+        tokens = sum(len(d) for d in docs)
+        if tokens < 2 * budget and len(docs) < self.buffer_docs:
+            for d in self.doc_iter:
+                docs.append(d)
+                tokens += len(d)
+                if len(docs) >= self.buffer_docs or tokens >= 2 * budget:
+                    break
         if not docs:
             return None
-        ids, labels, cu = self.collate(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id, self.eos_id)
+        if self.collate is pack_chunk_aligned:
+            ids, labels, cu, placed = pack_chunk_aligned(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id,
+                                                         self.eos_id, return_placed=True)
+            taken = set(placed)
+            # a document longer than a row can never be placed: it is dropped here instead of circulating for ever
+            self._carry = [d for i, d in enumerate(docs)
+                           if i not in taken and 0 < len(d) + (1 if self.eos_id is not None and d[-1] != self.eos_id else 0) <= self.seq_len]
+            if not placed:
+                return self._next_batch() if self._carry else None
+        else:
+            ids, labels, cu = self.collate(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id, self.eos_id)
+            self._carry = []
         return {"input_ids": _pin(ids.reshape(-1)), "labels": _pin(labels.reshape(-1)),
                 "cu_seqlens": cu.to(torch.int32), "row_len": self.seq_len}
 

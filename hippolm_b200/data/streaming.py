@@ -284,7 +284,7 @@ def build_streaming_iterator(args, cfg, mesh, local_batch: int, seq_len: int):
     tok = load_tokenizer(getattr(args, "tokenizer_path", None))
     data_files = getattr(args, "data_files", None)
     if data_files:
-        files = data_files if isinstance(data_files, (list, tuple)) else [data_files]
+        files = list(data_files) if isinstance(data_files, (list, tuple)) else [f for f in str(data_files).split(",") if f]
         if getattr(args, "shuffle", False):
             import random
             files = list(files)

@@ -62,14 +62,15 @@ def evaluate_perplexity(model, tokenizer, documents: Iterable[str], seq_len: int
         while pending and (final or len(pending) >= 4 * batch_rows):
             take, pending = pending[:4 * batch_rows], pending[4 * batch_rows:]
             while take:
-                ids, labels, cu = pack_chunk_aligned(take, seq_len, chunk, batch_rows, pad_id=0, eos_id=None)
                 # documents are placed largest first; whatever did not fit goes into the next batch
+                ids, labels, cu, fitted = pack_chunk_aligned(take, seq_len, chunk, batch_rows, pad_id=0, eos_id=None,
+                                                             return_placed=True)
                 out = model(ids.to(dev), labels=labels.to(dev), cu_seqlens=cu.to(device=dev, dtype=torch.int32))
                 n = int(out["n_valid"])
                 if n > 0:
                     total_nll += float(out["loss"]) * n
                     total_tok += n
-                fitted = _fitted(take, seq_len, chunk, batch_rows)
+                fitted = set(fitted)
                 take = [d for i, d in enumerate(take) if i not in fitted]
         return
 
@@ -92,18 +93,3 @@ def evaluate_perplexity(model, tokenizer, documents: Iterable[str], seq_len: int
     model.train(was_training)
     nll = total_nll / max(1, total_tok)
     return {"nll": nll, "perplexity": math.exp(min(nll, 700.0)), "tokens": total_tok, "documents": n_docs}
-
-
-def _fitted(docs: List[List[int]], seq_len: int, chunk: int, rows: int) -> set:
-    """Indices of the documents the packer places (first-fit by decreasing chunk count into ``rows`` rows)."""
-    need = [(-(-len(d) // chunk)) * chunk for d in docs]
-    order = sorted(range(len(docs)), key=lambda i: -need[i])
-    used = [0] * rows
-    placed = set()
-    for i in order:
-        for b in range(rows):
-            if used[b] + need[i] <= seq_len:
-                used[b] += need[i]
-                placed.add(i)
-                break
-    return placed

@@ -331,6 +331,19 @@ def _carry_states(prev: List[torch.Tensor], n_seq: int, continues: bool) -> List
     return out
 
 
+def _save_step_checkpoint(ctx: TrainContext, step: int, loss: float) -> None:
+    args, mesh = ctx.args, ctx.mesh
+    ctx.muon.sync_dp_state()              # collective: outside the try so that every rank takes part
+    try:
+        d = os.path.join(ctx.run_dir, "checkpoints")
+        ckpt.save_checkpoint(ctx.model, ctx.muon, ctx.adamw, step, loss, ckpt.checkpoint_path(d, step), rank=mesh.rank,
+                             world_size=mesh.world_size, mesh=mesh)
+        if mesh.rank == 0:
+            ckpt.prune_old_checkpoints(d, int(getattr(args, "checkpoint_keep_last_n", 0) or 0))
+    except Exception as ex:   # a disk error must not kill training
+        ctx.logger.error(f"checkpoint save failed at step {step}: {ex!r}")
+
+
 def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
     args, mesh = ctx.args, ctx.mesh
     max_steps = int(getattr(args, "max_steps", 1000))
@@ -339,6 +352,7 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
     mb_timing = int(getattr(args, "mb_timing", 0) or 0)
     last = {}
     losses = []
+    saved_step = -1
     try:
         while ctx.step < max_steps:
             try:
@@ -406,18 +420,13 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                     if ctx.metrics_file is not None:
                         ctx.metrics_file.write(json.dumps(rec) + "\n"); ctx.metrics_file.flush()
             if ck_int > 0 and ctx.run_dir and (ctx.step + 1) % ck_int == 0:
-                ctx.muon.sync_dp_state()              # collective: outside the try so that every rank takes part
-                try:
-                    d = os.path.join(ctx.run_dir, "checkpoints")
-                    ckpt.save_checkpoint(ctx.model, ctx.muon, ctx.adamw, ctx.step, loss,
-                                         ckpt.checkpoint_path(d, ctx.step), rank=mesh.rank,
-                                         world_size=mesh.world_size, mesh=mesh)
-                    if mesh.rank == 0:
-                        ckpt.prune_old_checkpoints(d, int(getattr(args, "checkpoint_keep_last_n", 0) or 0))
-                except Exception as ex:   # a disk error must not kill training
-                    ctx.logger.error(f"checkpoint save failed at step {ctx.step}: {ex!r}")
+                _save_step_checkpoint(ctx, ctx.step, loss)
+                saved_step = ctx.step
             last = out
             ctx.step += 1
+        # the run ended between two periodic checkpoints (last step, or a finite dataset ran out): keep its final state
+        if ck_int > 0 and ctx.run_dir and losses and saved_step != ctx.step - 1:
+            _save_step_checkpoint(ctx, ctx.step - 1, losses[-1])
     except BaseException as ex:
         if ctx.liveness is not None:
             ctx.liveness.mark_exit(repr(ex))

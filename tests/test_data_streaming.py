@@ -87,3 +87,29 @@ def test_prefetch_fanout_sentinel_and_exception():
     with pytest.raises(RuntimeError, match="tokenizer died"):
         list(QueueIterator(q, timeout_s=10))
     pb.close()
+
+
+def test_prefetch_batcher_emits_every_document_exactly_once():
+    """Documents that find no room in a batch are carried into the next one: every document that fits a row at all comes
+    out exactly once (the reference discards the overflow of each packing window)."""
+    import queue
+    import random
+    from hippolm_b200.data.prefetch import PrefetchBatcher, QueueIterator
+    rng = random.Random(0)
+    docs = []
+    for i in range(300):
+        n = rng.choice([5, 20, 60, 64, 100, 130, 250, 256, 300])           # 300 > seq_len: can never be placed
+        docs.append([1000 + i] + [rng.randint(2, 90) for _ in range(n - 1)])
+    q = queue.Queue(maxsize=2)
+    pb = PrefetchBatcher(iter(docs), [q], batch_size=2, seq_len=256, chunk_size=64, pack_buffer_size=8, pad_id=0, eos_id=None)
+    seen = []
+    for batch in QueueIterator(q):
+        ids, cu = batch["input_ids"], batch["cu_seqlens"].tolist()
+        assert ids.numel() == 2 * 256
+        for s, e in zip(cu, cu[1:]):
+            if int(batch["labels"][s:e].ne(-100).sum()) > 0 or int(ids[s]) >= 1000:
+                if int(ids[s]) >= 1000:
+                    seen.append(int(ids[s]) - 1000)
+    pb.close()
+    fits = [i for i, d in enumerate(docs) if len(d) <= 256]
+    assert sorted(seen) == fits and len(set(seen)) == len(seen)

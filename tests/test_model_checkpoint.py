@@ -210,3 +210,22 @@ def test_env_and_gpu_selection(tmp_path, monkeypatch):
     assert select_gpus(10240, want=2, query=lambda: free) == [2, 3]
     assert select_gpus(10240, query=lambda: [0, 0]) == []
     assert select_gpus(10, query=lambda: [100] * 8) == list(range(8))
+
+
+def test_final_checkpoint_when_the_run_ends_between_periodic_ones(tmp_path):
+    from hippolm_b200.cli import parse_args
+    from hippolm_b200.train.loop import setup_worker, run_training_loop
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = str(tmp_path / "run")
+    os.makedirs(run)
+    a = parse_args(["--config", os.path.join(root, "configs/test/checkpoint.yml"), "--max_steps", "3",
+                    "--checkpoint_keep_last_n", "5"])
+    res = run_training_loop(setup_worker(a, run_dir=run))
+    assert res["steps"] == 3
+    assert [s for s, _ in ck.list_checkpoints(os.path.join(run, "checkpoints"))] == [1, 2]      # periodic, then final
+    a = parse_args(["--config", os.path.join(root, "configs/test/checkpoint.yml"), "--resume", "latest", "--max_steps", "4",
+                    "--checkpoint_keep_last_n", "5"])
+    ctx = setup_worker(a, run_dir=run)
+    assert ctx.step == 3
+    run_training_loop(ctx)
+    assert [s for s, _ in ck.list_checkpoints(os.path.join(run, "checkpoints"))] == [1, 2, 3]   # step 3 is periodic: once

@@ -70,9 +70,26 @@ def build_data_iterator(args, cfg, mesh, start_step: int = 0) -> Tuple[Iterator,
                                 bool(getattr(args, "fixed_batch", False)), start_step), None
     from .streaming import build_streaming_iterator
     it, pre = build_streaming_iterator(args, cfg, mesh, lb, seq)
-    for _ in range(start_step):
+    # Fast-forward a resumed run. A finite source may end while skipping: the run it resumes had re-opened it for its next
+    # epoch at that point, so do the same here and go on skipping; the number of whole passes is handed to the caller.
+    left, in_pass, passes = int(start_step), 0, 0
+    while left > 0:
         try:
             next(it)
+            left -= 1
+            in_pass += 1
         except StopIteration:
-            break
+            if in_pass == 0:
+                break                                   # an empty source: nothing to skip through
+            if pre is not None:
+                pre.close()
+            passes += 1
+            in_pass = 0
+            if passes >= int(getattr(args, "epochs", 1) or 1):
+                break                                   # the resumed run had used up its epochs
+            it, pre = build_streaming_iterator(args, cfg, mesh, lb, seq)
+    try:
+        it.epochs_skipped = passes
+    except AttributeError:
+        pass
     return it, pre

@@ -20,13 +20,18 @@ class QueueIterator:
 
     def __init__(self, q, timeout_s: Optional[float] = None):
         self._q, self._timeout = q, timeout_s
+        self._done = False
+        self.epochs_skipped = 0            # set by a resume that fast-forwarded through whole passes over a finite source
 
     def __iter__(self):
         return self
 
     def __next__(self):
+        if self._done:                     # the sentinel arrives once: every later call ends at once instead of blocking
+            raise StopIteration
         item = self._q.get(timeout=self._timeout) if self._timeout else self._q.get()
         if item is self._SENTINEL:
+            self._done = True
             raise StopIteration
         if isinstance(item, BaseException):
             raise item

@@ -183,6 +183,7 @@ def setup_worker(args, run_dir: Optional[str] = None, data_iter: Optional[Iterat
         # the loader continues after the batches the checkpointed run had consumed instead of replaying them
         ctx.data_iter, ctx.prefetcher = build_data_iterator(args, cfg, mesh, start_step=data_step)
         ctx.extras["own_data_iter"] = True
+        ctx.extras["epoch"] = int(getattr(ctx.data_iter, "epochs_skipped", 0) or 0)
     hb = float(getattr(args, "watchdog_timeout_s", 0) or 0)
     if hb > 0:
         from .watchdog import StepWatchdog

@@ -229,3 +229,42 @@ def test_final_checkpoint_when_the_run_ends_between_periodic_ones(tmp_path):
     assert ctx.step == 3
     run_training_loop(ctx)
     assert [s for s, _ in ck.list_checkpoints(os.path.join(run, "checkpoints"))] == [1, 2, 3]   # step 3 is periodic: once
+
+
+@pytest.mark.timeout(300)
+def test_resume_in_a_later_epoch_of_a_finite_local_dataset(tmp_path):
+    """Local jsonl files, several passes over them, a checkpoint in the third pass: the resumed run fast-forwards through
+    the finished passes (re-opening the source like the run it continues) and goes on; the end of a pass is sticky
+    (a second read after the end-of-data marker returns at once instead of waiting for ever)."""
+    import random
+    from hippolm_b200.cli import parse_args
+    from hippolm_b200.train.loop import setup_worker, run_training_loop
+    rng = random.Random(0)
+    data = tmp_path / "docs.jsonl"
+    with open(data, "w") as f:
+        for i in range(8):
+            f.write(json.dumps({"content": " ".join(rng.choice(["alpha", "beta", "gamma", "delta", "kernel", "tile"])
+                                                     for _ in range(rng.randint(5, 40)))}) + "\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = str(tmp_path / "run")
+    os.makedirs(run)
+    base = ["--config", os.path.join(root, "configs/test/quick.yml"), "--use_dummy_data", "false", "--synthetic_data", "false",
+            "--data_files", str(data), "--tokenizer_path", "builtin", "--vocab_size", "1536", "--batch_size", "2",
+            "--seq_len", "128", "--epochs", "50", "--checkpoint_interval", "5", "--checkpoint_keep_last_n", "9"]
+    res = run_training_loop(setup_worker(parse_args(base + ["--max_steps", "7"]), run_dir=run))
+    assert res["steps"] == 7
+    lines = [json.loads(l) for l in open(os.path.join(run, "metrics.jsonl"))]
+    assert [l["step"] for l in lines] == list(range(7))
+    ctx = setup_worker(parse_args(base + ["--max_steps", "10", "--resume", "latest"]), run_dir=run)
+    assert ctx.step == 7 and ctx.extras["epoch"] >= 1               # the final checkpoint of the first run; past pass one
+    res = run_training_loop(ctx)
+    assert res["steps"] == 10 and all(l == l for l in res["losses"])
+    from hippolm_b200.data.prefetch import QueueIterator
+    import queue
+    q = queue.Queue()
+    q.put({"x": 1}); q.put(None)
+    it = QueueIterator(q)
+    assert next(it) == {"x": 1}
+    for _ in range(3):
+        with pytest.raises(StopIteration):
+            next(it)

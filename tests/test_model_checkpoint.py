@@ -268,3 +268,25 @@ def test_resume_in_a_later_epoch_of_a_finite_local_dataset(tmp_path):
     for _ in range(3):
         with pytest.raises(StopIteration):
             next(it)
+
+
+def test_resume_latest_finds_the_previous_run(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    import sys
+    sys.path.insert(0, os.path.join(root, "scripts"))
+    import importlib
+    train = importlib.import_module("train")
+    out = str(tmp_path / "output")
+    cfg = os.path.join(root, "configs/test/checkpoint.yml")
+    os.environ.pop("HIPPO_RUN_TS", None)
+    os.environ["HIPPO_RUN_TS"] = "20200101_000000"
+    run1 = train.main(["--config", cfg, "--output_dir", out, "--max_steps", "4"])
+    os.environ["HIPPO_RUN_TS"] = "20200101_000100"
+    try:
+        run2 = train.main(["--config", cfg, "--output_dir", out, "--max_steps", "6", "--resume", "latest"])
+    finally:
+        os.environ.pop("HIPPO_RUN_TS", None)
+    assert run1 != run2
+    steps = [json.loads(l)["step"] for l in open(os.path.join(run2, "metrics.jsonl"))]
+    assert steps == [4, 5], steps                                    # continued, not restarted
+    assert train.latest_checkpoint_of_previous_runs(str(tmp_path / "nothing")) is None

@@ -290,18 +290,28 @@ def build_streaming_iterator(args, cfg, mesh, local_batch: int, seq_len: int):
             files = list(files)
             random.Random(int(getattr(args, "seed", 0))).shuffle(files)
 
-        def rows():
+        def file_rows(f):
             import json
+            if str(f).endswith(".parquet"):
+                yield from iter_parquet_rows(f)
+            else:
+                with open(f) as fh:
+                    for line in fh:
+                        if line.strip():
+                            yield json.loads(line)
+
+        def rows():
+            # every data-parallel replica reads its own part: whole files when there are at least as many files as
+            # replicas, else every dp-th row of every file
+            by_file = len(files) >= mesh.dp
+            n = 0
             for i, f in enumerate(files):
-                if i % mesh.dp != mesh.dp_rank and len(files) >= mesh.dp:
+                if by_file and i % mesh.dp != mesh.dp_rank:
                     continue
-                if str(f).endswith(".parquet"):
-                    yield from iter_parquet_rows(f)
-                else:
-                    with open(f) as fh:
-                        for line in fh:
-                            if line.strip():
-                                yield json.loads(line)
+                for row in file_rows(f):
+                    if by_file or n % mesh.dp == mesh.dp_rank:
+                        yield row
+                    n += 1
         ds = StreamingDataset(rows(), tok, getattr(args, "text_field", "content"), getattr(args, "stage", "pretrain"),
                               max_len=seq_len)
     else:

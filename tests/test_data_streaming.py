@@ -113,3 +113,39 @@ def test_prefetch_batcher_emits_every_document_exactly_once():
     pb.close()
     fits = [i for i, d in enumerate(docs) if len(d) <= 256]
     assert sorted(seen) == fits and len(set(seen)) == len(seen)
+
+
+def test_local_files_are_split_between_data_parallel_replicas(tmp_path):
+    """One file, two replicas: each reads every second row (disjoint, together everything); two files: one file each."""
+    import json
+    import types
+    from hippolm_b200.config import HippoConfig
+    from hippolm_b200.data.streaming import build_streaming_iterator
+    for nfiles in (1, 2):
+        files = []
+        for k in range(nfiles):
+            p = tmp_path / f"d{nfiles}_{k}.jsonl"
+            with open(p, "w") as f:
+                for i in range(12):
+                    f.write(json.dumps({"content": f"doc{k}x{i} " + "word " * (3 + i)}) + "\n")
+            files.append(str(p))
+        cfg = HippoConfig(vocab_size=1536, hidden_size=32, num_heads=2, head_dim=16, num_layers=2, num_blocks=1, intermediate_size=64)
+        seen = []
+        for r in range(2):
+            args = types.SimpleNamespace(tokenizer_path="builtin", data_files=",".join(files), text_field="content",
+                                         stage="pretrain", pack_buffer_size=8, shuffle=False, seed=0)
+            mesh = types.SimpleNamespace(dp=2, dp_rank=r)
+            it, pb = build_streaming_iterator(args, cfg, mesh, 2, 128)
+            from hippolm_b200.data.tokenizer import load_tokenizer
+            tok = load_tokenizer("builtin")
+            mine = set()
+            for b in it:
+                text = tok.decode(b["input_ids"].tolist())
+                for k in range(nfiles):
+                    for i in range(12):
+                        if f"doc{k}x{i} " in text:
+                            mine.add((k, i))
+            pb.close()
+            seen.append(mine)
+        assert not (seen[0] & seen[1]) and len(seen[0] | seen[1]) == 12 * nfiles, (nfiles, seen)
+        assert len(seen[0]) == len(seen[1]) == 6 * nfiles

@@ -359,6 +359,16 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
             try:
                 batch = next(ctx.data_iter)
             except StopIteration:
+                batch = None
+            if mesh.dp > 1 and ctx.prefetcher is not None and ctx.extras.get("own_data_iter", False):
+                # Finite real data: the replicas read different rows and may run out at different steps. They agree here, so
+                # that all of them end the pass at the same step (a replica that still has a batch drops it) instead of
+                # meeting in mismatched collectives.
+                have = torch.tensor([0 if batch is None else 1], device=ctx.device)
+                dist.all_reduce(have, op=dist.ReduceOp.MIN, group=mesh.dp_group)
+                if int(have) == 0:
+                    batch = None
+            if batch is None:
                 # end of an epoch: a finite dataset is re-opened until --epochs passes have been made
                 epoch = ctx.extras.get("epoch", 0) + 1
                 if epoch >= int(getattr(args, "epochs", 1) or 1) or not ctx.extras.get("own_data_iter", False):

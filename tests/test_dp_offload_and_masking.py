@@ -122,3 +122,43 @@ def test_fused_trial_with_an_expired_wait_falls_back(monkeypatch):
     assert calls == {"cleared": 1, "reset": 1}
     assert fused._trial_failed(ws, None) is False          # clean status: nothing to do
     assert calls == {"cleared": 1, "reset": 1}
+
+
+def _dp_finite_worker(rank, world, port, data, run_dir):
+    import os
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port), "HIPPO_TP_SIM": "1"})
+    import torch
+    torch.set_num_threads(1)
+    from hippolm_b200.cli import build_parser
+    from hippolm_b200.train.loop import setup_worker, run_training_loop
+    a = build_parser().parse_args([])
+    a.vocab_size, a.hidden_size, a.num_heads, a.head_dim = 1536, 32, 2, 16
+    a.num_layers, a.num_blocks, a.intermediate_size = 2, 1, 64
+    a.batch_size, a.seq_len, a.max_steps, a.epochs = 4, 128, 40, 2
+    a.tp_size, a.dp_size, a.tp_sim = 1, 2, True
+    a.use_dummy_data = a.synthetic_data = False
+    a.data_files, a.tokenizer_path, a.dist_timeout_s = data, "builtin", 30.0
+    a.precision = {k: {"dtype": "fp32"} for k in ("model_weights", "gradients", "activations", "muon_momentum", "adamw_m", "adamw_v")}
+    res = run_training_loop(setup_worker(a, run_dir=run_dir))
+    torch.save({"steps": res["steps"], "losses": res["losses"]}, os.path.join(run_dir, f"res.{rank}.pt"))
+
+
+def test_dp_replicas_end_a_finite_data_pass_together(tmp_path):
+    """One local file, two replicas reading every second row; the rows of one replica are much longer, so it has more
+    batches per pass. Both end each pass at the same step (agreed by a collective) and the run finishes."""
+    import json
+    import socket
+    import torch
+    import torch.multiprocessing as mp
+    data = tmp_path / "docs.jsonl"
+    with open(data, "w") as f:
+        for i in range(40):
+            f.write(json.dumps({"content": ("long row " * 40) if i % 2 == 0 else "short"}) + "\n")
+    run = tmp_path / "run"
+    (run / "logs").mkdir(parents=True)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mp.spawn(_dp_finite_worker, args=(2, port, str(data), str(run)), nprocs=2, join=True)
+    r0, r1 = torch.load(run / "res.0.pt"), torch.load(run / "res.1.pt")
+    assert r0["steps"] == r1["steps"] and 0 < r0["steps"] < 40
+    assert all(l == l for l in r0["losses"])

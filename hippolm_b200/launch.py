@@ -61,6 +61,10 @@ def select_gpus(min_memory_mb: int, want: Optional[int] = None,
 def _spawn_entry(rank: int, world: int, port: int, fn, args):
     os.environ.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world),
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    if os.environ.get("HIPPO_TP_SIM") == "1":
+        # simulated ranks share the host's cores: one full-width thread pool per rank would oversubscribe them many times
+        import torch
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
     fn(args)
 
 

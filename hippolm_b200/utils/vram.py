@@ -159,3 +159,48 @@ def saved_bytes_by_module(model: torch.nn.Module, run, depth: int = 2) -> List[D
     out = [{"module": k, "bytes": v[0], "tensors": v[1]} for k, v in totals.items()]
     out.sort(key=lambda r: -r["bytes"])
     return out
+
+
+def _main(argv=None) -> int:
+    """``python -m hippolm_b200.utils.vram analyze <snapshot.pickle> [--top N]``: live allocations of a memory snapshot by
+    allocation site. ``python -m hippolm_b200.utils.vram probe --config X.yml [--depth 2] [--tokens N]``: bytes autograd
+    keeps for backward per sub-module, for one forward pass of the configured model on synthetic tokens (GPU when one is
+    visible, else CPU); with ``--snapshot out.pickle`` the allocator history of that pass is dumped as well.
+    (``tools/vram_profile/{analyze,saved_tensor_probe,profile}.py`` of the reference.)"""
+    import argparse
+    import json
+    ap = argparse.ArgumentParser(prog="python -m hippolm_b200.utils.vram")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    a1 = sub.add_parser("analyze"); a1.add_argument("snapshot"); a1.add_argument("--top", type=int, default=20)
+    a2 = sub.add_parser("probe"); a2.add_argument("--config", required=True); a2.add_argument("--depth", type=int, default=2)
+    a2.add_argument("--tokens", type=int, default=0); a2.add_argument("--snapshot", default=None)
+    a = ap.parse_args(argv)
+    if a.cmd == "analyze":
+        for r in analyze_snapshot(a.snapshot, a.top):
+            print(f"{r['bytes'] / 2 ** 20:10.1f} MiB  {r['blocks']:6d} blocks  {r['where']}")
+        return 0
+    from ..cli import parse_args
+    from ..config import HippoConfig
+    from ..models.model import HippoModel
+    args = parse_args(["--config", a.config])
+    cfg = HippoConfig.from_namespace(args)
+    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    model = HippoModel(cfg, device=dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    T = a.tokens or min(int(args.seq_len), 4096)
+    ids = torch.randint(0, cfg.vocab_size, (T,), device=dev)
+
+    def run():
+        model(ids, labels=ids)["loss"]
+
+    with memory_history(a.snapshot):
+        rows = saved_bytes_by_module(model, run, depth=a.depth)
+    total = sum(r["bytes"] for r in rows)
+    for r in rows:
+        print(f"{r['bytes'] / 2 ** 20:10.2f} MiB  {r['tensors']:5d} tensors  {r['module']}")
+    print(json.dumps({"tokens": T, "saved_mib": round(total / 2 ** 20, 2), "bytes_per_token": round(total / T, 1),
+                      "device": str(dev)}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

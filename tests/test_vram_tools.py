@@ -33,3 +33,21 @@ def test_saved_bytes_by_module_attributes_activations():
     assert by.get("0", 0) >= 4 * 16 * 4            # the first linear keeps its input
     assert by.get("2", 0) >= 4 * 64 * 4            # the last linear keeps the hidden activations
     assert sum(by.values()) > 0
+
+
+def test_vram_cli_probe_and_analyze(tmp_path, capsys):
+    import os
+    import pickle
+    from hippolm_b200.utils import vram
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    assert vram._main(["probe", "--config", os.path.join(root, "configs/test/quick.yml"), "--tokens", "128", "--depth", "1"]) == 0
+    out = capsys.readouterr().out
+    assert "layers" in out and '"saved_mib"' in out
+    snap = {"segments": [{"blocks": [{"state": "active_allocated", "size": 4096,
+                                      "frames": [{"filename": "/x/hippolm_b200/models/model.py", "line": 7, "name": "forward"}]},
+                                     {"state": "inactive", "size": 1 << 20, "frames": []}]}]}
+    p = tmp_path / "snap.pickle"
+    with open(p, "wb") as f:
+        pickle.dump(snap, f)
+    assert vram._main(["analyze", str(p), "--top", "3"]) == 0
+    assert "model.py:7 forward" in capsys.readouterr().out

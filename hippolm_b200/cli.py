@@ -77,6 +77,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--pretrain_en_qa_config", type=str, default=None); a("--pretrain_zh_qa_config", type=str, default=None)
     a("--sft_dataset_hf", type=str, default=None); a("--sft_dataset_ms", type=str, default=None)
     a("--sft_config", type=str, default=None); a("--text_field", type=str, default="content")
+    a("--split_long_documents", type=_bool, default=False)
     a("--data_files", type=str, default=None)        # local .jsonl / .parquet files, comma separated (or a YAML list)
     a("--tokenizer_path", type=str, default=None); a("--cache_dir", type=str, default=None)
     a("--use_dummy_data", type=_bool, default=False); a("--synthetic_data", type=_bool, default=False)

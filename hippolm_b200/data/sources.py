@@ -174,7 +174,8 @@ def build_hub_dataset(args, tokenizer, seq_len: int, logger=None, cache_root: Op
     def sub(label, hf, ms, cfg):
         rows = open_rows(hf, ms, cfg, bool(getattr(args, "use_modelscope", False)), bool(getattr(args, "shuffle", False)),
                          seed, cache_root=cache_root, logger=logger)
-        return StreamingDataset(rows, tokenizer, getattr(args, "text_field", "content"), stage, max_len=seq_len)
+        return StreamingDataset(rows, tokenizer, getattr(args, "text_field", "content"), stage, max_len=seq_len,
+                                split_long=bool(getattr(args, "split_long_documents", False)))
 
     if len(plan) == 1:
         return sub(*plan[0])

@@ -208,9 +208,12 @@ class StreamingDataset:
     TOKENIZE_BATCH = 64
 
     def __init__(self, source: Iterable[dict], tokenizer, text_field: str = "content", stage: str = "pretrain",
-                 max_len: Optional[int] = None, add_eos: bool = True):
+                 max_len: Optional[int] = None, add_eos: bool = True, split_long: bool = False):
+        """``max_len``: a longer document is cut to it (the reference's choice: its tokenizer truncates,
+        ``src/training/data/streaming.py:157``) or, with ``split_long``, yielded as consecutive pieces of ``max_len``
+        tokens so that no text is thrown away (the end-of-text token closes the last piece only)."""
         self.source, self.tok, self.text_field, self.stage = source, tokenizer, text_field, stage
-        self.max_len, self.add_eos = max_len, add_eos
+        self.max_len, self.add_eos, self.split_long = max_len, add_eos, split_long
 
     def _format_sft(self, ex: dict) -> Optional[str]:
         msgs = ex.get("messages") or ex.get("conversations")
@@ -231,6 +234,14 @@ class StreamingDataset:
         eos = getattr(self.tok, "eos_token_id", None)
         for ids in enc:
             ids = list(ids)
+            if self.max_len and self.split_long and len(ids) >= self.max_len:
+                if self.add_eos and eos is not None and ids[-1] != eos:
+                    ids.append(eos)
+                for s0 in range(0, len(ids), self.max_len):
+                    piece = ids[s0:s0 + self.max_len]
+                    if len(piece) > 1 or s0 == 0:
+                        yield piece
+                continue
             if self.max_len:
                 ids = ids[:self.max_len - (1 if self.add_eos and eos is not None else 0)]
             if self.add_eos and eos is not None and (not ids or ids[-1] != eos):
@@ -313,7 +324,7 @@ def build_streaming_iterator(args, cfg, mesh, local_batch: int, seq_len: int):
                         yield row
                     n += 1
         ds = StreamingDataset(rows(), tok, getattr(args, "text_field", "content"), getattr(args, "stage", "pretrain"),
-                              max_len=seq_len)
+                              max_len=seq_len, split_long=bool(getattr(args, "split_long_documents", False)))
     else:
         # hub datasets named by --pretrain_* / --sft_* (ModelScope first with --use_modelscope, hub as the fallback)
         from .sources import build_hub_dataset

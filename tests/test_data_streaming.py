@@ -149,3 +149,18 @@ def test_local_files_are_split_between_data_parallel_replicas(tmp_path):
             seen.append(mine)
         assert not (seen[0] & seen[1]) and len(seen[0] | seen[1]) == 12 * nfiles, (nfiles, seen)
         assert len(seen[0]) == len(seen[1]) == 6 * nfiles
+
+
+def test_long_documents_are_cut_or_split():
+    from hippolm_b200.data.streaming import StreamingDataset
+    from hippolm_b200.data.tokenizer import ByteTokenizer
+    tok = ByteTokenizer()
+    rows = [{"content": "a" * 25}, {"content": "bc"}]
+    eos = tok.eos_token_id
+    cut = list(StreamingDataset(rows, tok, max_len=10))
+    assert [len(d) for d in cut] == [10, 3] and cut[0][-1] == eos               # the reference's behaviour: truncated
+    split = list(StreamingDataset(rows, tok, max_len=10, split_long=True))
+    assert [len(d) for d in split] == [10, 10, 6, 3]                            # 25 tokens + eos in pieces of 10
+    flat = [t for d in split[:3] for t in d]
+    assert flat[:-1] == tok.encode("a" * 25, add_special_tokens=False) and flat[-1] == eos
+    assert all(d[-1] != eos for d in split[:2])

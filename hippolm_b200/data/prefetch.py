@@ -68,29 +68,35 @@ class PrefetchBatcher:
         self._thread.start()
 
     def _next_batch(self):
-        docs = list(self._carry)
         budget = self.batch_size * self.seq_len
-        tokens = sum(len(d) for d in docs)
-        if tokens < 2 * budget and len(docs) < self.buffer_docs:
-            for d in self.doc_iter:
-                docs.append(d)
-                tokens += len(d)
-                if len(docs) >= self.buffer_docs or tokens >= 2 * budget:
-                    break
-        if not docs:
-            return None
-        if self.collate is pack_chunk_aligned:
+        while True:
+            docs = list(self._carry)
+            tokens = sum(len(d) for d in docs)
+            fresh = 0
+            if tokens < 2 * budget and len(docs) < self.buffer_docs:
+                for d in self.doc_iter:
+                    docs.append(d)
+                    tokens += len(d)
+                    fresh += 1
+                    if len(docs) >= self.buffer_docs or tokens >= 2 * budget:
+                        break
+            if not docs:
+                return None
+            if self.collate is not pack_chunk_aligned:
+                ids, labels, cu = self.collate(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id, self.eos_id)
+                self._carry = []
+                break
             ids, labels, cu, placed = pack_chunk_aligned(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id,
                                                          self.eos_id, return_placed=True)
             taken = set(placed)
             # a document longer than a row can never be placed: it is dropped here instead of circulating for ever
             self._carry = [d for i, d in enumerate(docs)
                            if i not in taken and 0 < len(d) + (1 if self.eos_id is not None and d[-1] != self.eos_id else 0) <= self.seq_len]
-            if not placed:
-                return self._next_batch() if self._carry else None
-        else:
-            ids, labels, cu = self.collate(docs, self.seq_len, self.chunk_size, self.batch_size, self.pad_id, self.eos_id)
-            self._carry = []
+            if placed:
+                break
+            if fresh == 0 and not self._carry:
+                return None                      # the source is exhausted and nothing that is left fits a row
+            # a window of over-long documents only: read on
         return {"input_ids": _pin(ids.reshape(-1)), "labels": _pin(labels.reshape(-1)),
                 "cu_seqlens": cu.to(torch.int32), "row_len": self.seq_len}
 

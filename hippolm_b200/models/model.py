@@ -808,6 +808,8 @@ class HippoModel(nn.Module):
         m = self.mesh
         w = m.tp
         n_real = len(prompts)
+        if n_real == 0:
+            return []
         per = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n_real   # noqa: E731
         limits, temps, topks, topps = per(max_new_tokens), per(temperature), per(top_k), per(top_p)
         seqs = [p.reshape(-1).clone() for p in prompts]

@@ -72,15 +72,27 @@ class EvalService:
         self._worker = threading.Thread(target=self._decode_loop, name="eval-decode", daemon=True)
         self._worker.start()
 
+    def close(self) -> None:
+        """Stops the decoding thread (requests still in the queue are answered first)."""
+        self._queue.put(None)
+        self._worker.join(timeout=5.0)
+
     def _decode_loop(self):
-        while True:
+        stop = False
+        while not stop:
             first = self._queue.get()
+            if first is None:
+                return
             batch = [first]
             while len(batch) < self.max_batch:
                 try:
-                    batch.append(self._queue.get_nowait())
+                    nxt = self._queue.get_nowait()
                 except queue.Empty:
                     break
+                if nxt is None:
+                    stop = True
+                    break
+                batch.append(nxt)
             try:
                 dev = next(self.model.parameters()).device
                 eos = getattr(self.tok, "eos_token_id", None)

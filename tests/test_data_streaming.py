@@ -164,3 +164,16 @@ def test_long_documents_are_cut_or_split():
     flat = [t for d in split[:3] for t in d]
     assert flat[:-1] == tok.encode("a" * 25, add_special_tokens=False) and flat[-1] == eos
     assert all(d[-1] != eos for d in split[:2])
+
+
+def test_prefetch_batcher_reads_past_a_window_of_over_long_documents():
+    import queue
+    from hippolm_b200.data.prefetch import PrefetchBatcher, QueueIterator
+    docs = [[7] * 500, [7] * 400, [7] * 900, [5] * 30, [6] * 40]           # three documents longer than a row, then two short
+    q = queue.Queue(maxsize=2)
+    pb = PrefetchBatcher(iter(docs), [q], batch_size=1, seq_len=128, chunk_size=64, pack_buffer_size=4)
+    batches = list(QueueIterator(q))
+    pb.close()
+    assert len(batches) == 1
+    ids = batches[0]["input_ids"]
+    assert int((ids == 5).sum()) == 30 and int((ids == 6).sum()) == 40 and int((ids == 7).sum()) == 0

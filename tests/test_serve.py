@@ -162,6 +162,9 @@ def test_eval_server_decodes_waiting_requests_together():
         t.join(timeout=60)
     assert [r["choices"][0]["text"] for r in results] == alone
     assert svc.largest_batch == len(bodies) - 1
+    svc.close()
+    assert not svc._worker.is_alive()
+    assert model.generate_batch([], 4) == []
 
 
 def _tp_decode_worker(rank, world, port, out_path, kw):

@@ -30,7 +30,15 @@ def _bool(v) -> bool:
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(description="hippolm_b200 training")
-    a = p.add_argument
+
+    def a(*names, **kw):
+        # boolean flags take a value (``--flag false``) or stand alone (``--flag`` = true, the way the reference's
+        # store_true flags ``--use_dummy_data`` and ``--tp_sim`` are typed)
+        if kw.get("type") is _bool:
+            kw.setdefault("nargs", "?")
+            kw.setdefault("const", True)
+        return p.add_argument(*names, **kw)
+
     a("--config", type=str, default=None)
     # model
     a("--vocab_size", type=int, default=32000); a("--hidden_size", type=int, default=256)

@@ -36,8 +36,8 @@ def main():
     sys.path.insert(0, ref_root)
     from src.training.checkpoint import prune_old_checkpoints, save_checkpoint
     if mode == "prune":
-        removed = prune_old_checkpoints(Path(where), int(sys.argv[4]))
-        print(json.dumps({"removed": removed}))
+        # where: a directory with one sub-directory per value of keep_last_n, named after it
+        print(json.dumps({"removed": {k: prune_old_checkpoints(Path(where) / k, int(k)) for k in sorted(os.listdir(where))}}))
         return
     from src.models.config import HippoConfig
     from src.models.model import HippoModel

@@ -56,23 +56,24 @@ def test_a_checkpoint_written_by_the_reference_loads_here(tmp_path):
 
 
 @needs_ref
-@pytest.mark.parametrize("keep", [-1, 0, 1, 3, 10])
-def test_pruning_rule_matches_the_reference(tmp_path, keep):
+def test_pruning_rule_matches_the_reference(tmp_path):
     from hippolm_b200.train.checkpoint import prune_old_checkpoints
     names = ["checkpoint_step_%d.pt" % s for s in (5, 10, 100, 20, 9)] + ["best.pt", "checkpoint_step_x.pt", "notes.txt"]
-    dirs = []
+    keeps = [-1, 0, 1, 3, 10]
     for tag in ("ref", "here"):
-        d = tmp_path / tag
-        d.mkdir()
-        for n in names:
-            (d / n).write_bytes(b"0")
-        dirs.append(d)
-    removed_ref = _worker("prune", str(dirs[0]), str(keep), cwd=str(tmp_path))["removed"]
-    removed_here = prune_old_checkpoints(str(dirs[1]), keep)
-    if keep == 0:
-        # the reference's function removes every checkpoint at 0, the one just written included (its command-line help
-        # promises "keep only the just-saved file"); here 0 keeps all
-        assert removed_ref == 5 and removed_here == 0 and len(os.listdir(dirs[1])) == len(names)
-        return
-    assert sorted(os.listdir(dirs[0])) == sorted(os.listdir(dirs[1]))
-    assert removed_ref == removed_here
+        for keep in keeps:
+            d = tmp_path / tag / str(keep)
+            d.mkdir(parents=True)
+            for n in names:
+                (d / n).write_bytes(b"0")
+    removed_ref = _worker("prune", str(tmp_path / "ref"), cwd=str(tmp_path))["removed"]
+    for keep in keeps:
+        here = tmp_path / "here" / str(keep)
+        removed_here = prune_old_checkpoints(str(here), keep)
+        if keep == 0:
+            # the reference's function removes every checkpoint at 0, the one just written included (its command-line help
+            # promises "keep only the just-saved file"); here 0 keeps all
+            assert removed_ref["0"] == 5 and removed_here == 0 and len(os.listdir(here)) == len(names)
+            continue
+        assert sorted(os.listdir(tmp_path / "ref" / str(keep))) == sorted(os.listdir(here)), keep
+        assert removed_ref[str(keep)] == removed_here, keep

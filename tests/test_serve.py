@@ -267,3 +267,42 @@ def test_generate_script(capsys):
     gen = importlib.import_module("generate")
     text = gen.main(["--config", os.path.join(root, "configs/test/quick.yml"), "--prompt", "hello", "--max_new_tokens", "5"])
     assert isinstance(text, str) and capsys.readouterr().out.strip() == text.strip()
+
+
+def test_server_script_takes_the_reference_servers_options(tmp_path):
+    """``scripts/eval_server.py`` as a process, started with the option names of the reference's server (``--tokenizer``,
+    ``--model-id``, ``--device``, ``--dtype``, size overrides): it answers ``/v1/models`` with the given id and completes a
+    prompt with the overridden model size."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    import time
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cfg = tmp_path / "m.yml"
+    cfg.write_text("vocab_size: 1536\nhidden_size: 64\nnum_heads: 2\nhead_dim: 16\nnum_layers: 2\nnum_blocks: 1\n"
+                   "intermediate_size: 64\n")
+    proc = subprocess.Popen([sys.executable, os.path.join(root, "scripts", "eval_server.py"), "--config", str(cfg),
+                             "--port", str(port), "--model-id", "probe-model", "--device", "cpu", "--dtype", "fp32",
+                             "--hidden-size", "32", "--intermediate-size", "48", "--tokenizer", "builtin", "--max_new_tokens", "4"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        url = f"http://127.0.0.1:{port}"
+        for _ in range(240):
+            try:
+                models = json.loads(urllib.request.urlopen(url + "/v1/models", timeout=2).read())
+                break
+            except Exception:                                       # noqa: BLE001
+                assert proc.poll() is None, proc.stdout.read()[-3000:]
+                time.sleep(0.5)
+        else:
+            raise AssertionError("the server did not come up")
+        assert models["data"][0]["id"] == "probe-model"
+        out = _post(url + "/v1/completions", {"prompt": "ab", "max_tokens": 3})
+        assert out["usage"]["completion_tokens"] <= 3 and out["model"] == "probe-model"
+    finally:
+        proc.terminate()
+        proc.wait(timeout=30)

@@ -75,7 +75,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--max_restarts", type=int, default=0)
     a("--init_from", type=str, default=None)
     a("--resume", type=str, default=None); a("--diagnostics", type=_bool, default=False)
-    a("--mb_timing", type=int, default=0); a("--empty_cache_between_mb", type=_bool, default=False)
+    a("--mb_timing", type=int, default=0); a("--vram_phases", type=_bool, default=False); a("--empty_cache_between_mb", type=_bool, default=False)
     a("--peer_timeout_s", type=float, default=0.0); a("--dist_timeout_s", type=float, default=1800.0); a("--watchdog_timeout_s", type=float, default=0.0)
     # data
     a("--stage", type=str, default="pretrain"); a("--use_modelscope", type=_bool, default=False)

@@ -383,7 +383,13 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                 continue
             timed = mb_timing < 0 or ctx.step < mb_timing
             # timed steps also leave their phases in a trace file (logs/trace_rank<r>.json, written at the end of the run)
-            timer = PhaseTimer(enabled=timed, device=ctx.device, step=ctx.step,
+            phase_mem = None
+            if timed and getattr(args, "vram_phases", False):
+                if "phase_memory" not in ctx.extras:
+                    from ..utils.vram import PhaseMemory
+                    ctx.extras["phase_memory"] = PhaseMemory(ctx.device)
+                phase_mem = ctx.extras["phase_memory"]
+            timer = PhaseTimer(enabled=timed, device=ctx.device, step=ctx.step, memory=phase_mem,
                                events=ctx.extras.setdefault("trace_events", []) if timed and ctx.run_dir else None)
             t0 = time.perf_counter()
             ev0 = ev1 = None
@@ -420,10 +426,13 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                        "tok_per_s": toks, "found_inf": out["found_inf"]}
                 if timed:
                     rec["phases_ms"] = timer.summary()
+                if phase_mem is not None:
+                    rec["phases_peak_mb"] = phase_mem.step_summary(ctx.step)
                 if ctx.device.type == "cuda":
                     rec["vram_alloc_mb"] = torch.cuda.memory_allocated(ctx.device) / 2 ** 20
                     rec["vram_reserved_mb"] = torch.cuda.memory_reserved(ctx.device) / 2 ** 20
-                    rec["vram_max_mb"] = torch.cuda.max_memory_allocated(ctx.device) / 2 ** 20
+                    rec["vram_max_mb"] = max(torch.cuda.max_memory_allocated(ctx.device),
+                                             phase_mem.run_peak if phase_mem is not None else 0) / 2 ** 20
                 if mesh.rank == 0:
                     ctx.logger.info(f"step {ctx.step} loss {loss:.4f} lr {out['lr_muon']:.2e}/{out['lr_adamw']:.2e} "
                                     f"gnorm {out['grad_norm']:.3f} tok {out['tokens']} {step_ms_max:.1f} ms "

@@ -34,8 +34,9 @@ class PhaseTimer:
     step)`` for ``write_chrome_trace``."""
 
     def __init__(self, enabled: bool = True, device: Optional[torch.device] = None, events: Optional[list] = None,
-                 step: int = 0):
+                 step: int = 0, memory=None):
         self.enabled = enabled
+        self.memory = memory                   # a ``utils.vram.PhaseMemory``: peak device memory inside every phase
         self.cuda = device is not None and device.type == "cuda"
         self.ms: Dict[str, float] = {}
         self.events, self.step = events, step
@@ -48,12 +49,16 @@ class PhaseTimer:
             return
         if self.cuda:
             torch.cuda.synchronize()
+        if self.memory is not None:
+            self.memory.begin()
         t0 = time.perf_counter()
         with nvtx_range(name):
             yield
         if self.cuda:
             torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        if self.memory is not None:
+            self.memory.record(name, self.step)
         self.ms[name] = self.ms.get(name, 0.0) + dt * 1e3
         if self.events is not None:
             self.events.append((name, (time.time() - dt) * 1e6, dt * 1e6, self.step))

@@ -51,3 +51,82 @@ def test_vram_cli_probe_and_analyze(tmp_path, capsys):
         pickle.dump(snap, f)
     assert vram._main(["analyze", str(p), "--top", "3"]) == 0
     assert "model.py:7 forward" in capsys.readouterr().out
+
+
+def test_phase_memory_tracks_the_peak_inside_every_phase():
+    """PhaseTimer + PhaseMemory with scripted allocator counters: the peak counter is reset at the start of a phase, read at
+    its end, and the maximum of the whole run survives the resets."""
+    from hippolm_b200.utils.timing import PhaseTimer
+    from hippolm_b200.utils.vram import PhaseMemory
+    state = {"alloc": 0, "peak": 0, "resets": 0}
+
+    def alloc(n):
+        state["alloc"] += n
+        state["peak"] = max(state["peak"], state["alloc"])
+
+    def reset():
+        state["peak"] = state["alloc"]; state["resets"] += 1
+
+    mem = PhaseMemory(readers={"allocated": lambda: state["alloc"], "reserved": lambda: 2 * state["alloc"],
+                               "peak": lambda: state["peak"], "reset_peak": reset, "driver_used": lambda: state["alloc"] + 5})
+    mib = 2 ** 20
+    alloc(10 * mib)                                     # weights, before any phase
+    for step in range(2):
+        t = PhaseTimer(enabled=True, step=step, memory=mem)
+        with t.phase("fwd_bwd"):
+            alloc(100 * mib * (step + 1)); alloc(-90 * mib * (step + 1))
+        with t.phase("muon"):
+            alloc(30 * mib); alloc(-30 * mib)
+        with t.phase("fwd_bwd"):                        # a phase may occur twice in a step (micro-batches)
+            alloc(20 * mib); alloc(-20 * mib)
+    assert state["resets"] == 6 and len(mem.rows) == 6
+    assert mem.step_summary(0) == {"fwd_bwd": 110.0, "muon": 50.0}
+    assert mem.step_summary(1)["fwd_bwd"] == 220.0
+    tab = {r["phase"]: r for r in mem.table()}
+    assert list(tab) == ["fwd_bwd", "muon"] and tab["fwd_bwd"]["step"] == 1 and tab["fwd_bwd"]["peak_mib"] == 220.0
+    assert tab["fwd_bwd"]["allocated_mib"] == 40.0 and tab["fwd_bwd"]["reserved_mib"] == 80.0
+    assert mem.run_peak == 220 * mib
+    # without a GPU the default readers give zeros and nothing fails
+    z = PhaseMemory(torch.device("cpu")); z.begin(); assert z.record("x")["peak"] == 0
+
+
+def test_snapshot_classification_by_component():
+    from hippolm_b200.utils.vram import classify_block, classify_snapshot
+    pk = "/site/hippolm_b200/"
+
+    def blk(size, *frames, state="active_allocated"):
+        return {"size": size, "state": state, "frames": [{"filename": f, "name": n, "line": 1} for f, n in frames]}
+
+    snap = {"segments": [{"blocks": [
+        blk(1000, ("/torch/nn/modules/linear.py", "__init__"), (pk + "models/model.py", "__init__")),
+        blk(400, (pk + "ops/kda_cuda.py", "forward"), (pk + "models/model.py", "forward")),
+        blk(300, (pk + "ops/cuda_ops.py", "rmsnorm"), (pk + "models/model.py", "forward")),
+        blk(250, (pk + "optim/optimizers.py", "add_param")),
+        blk(200, (pk + "models/model.py", "_VocabParallelLCE.forward")),
+        blk(150, (pk + "parallel/symm.py", "alloc")),
+        blk(120, ("/torch/utils/checkpoint.py", "forward"), (pk + "models/model.py", "forward")),
+        blk(100, (pk + "ops/attn_cuda.py", "forward")),
+        blk(50, ("/somewhere/else.py", "f")),
+        blk(7, ),
+        blk(9999, (pk + "ops/kda_cuda.py", "forward"), state="inactive"),
+    ]}]}
+    rows = classify_snapshot(snap)
+    got = {r["class"]: r["bytes"] for r in rows}
+    assert got == {"model.weight": 1000, "kda.saved": 400, "norm.saved": 300, "optimizer.state": 250, "lce_head": 200,
+                   "comm.workspace": 150, "checkpoint.input": 120, "attention.saved": 100, "other": 50, "<no stack>": 7}
+    assert [r["bytes"] for r in rows] == sorted((r["bytes"] for r in rows), reverse=True)
+    assert rows[0]["largest"].startswith(pk + "models/model.py") and classify_block([]) == "<no stack>"
+
+
+def test_profile_command_runs_steps_and_reports_phases(tmp_path, capsys):
+    import json
+    import os
+    from hippolm_b200.utils.vram import _main
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "prof")
+    assert _main(["profile", "--config", os.path.join(root, "configs", "test", "quick.yml"), "--steps", "2", "--out", out]) == 0
+    res = json.load(open(os.path.join(out, "vram_profile.json")))
+    assert {r["phase"] for r in res["phases"]} >= {"h2d", "fwd_bwd", "gradnorm", "muon", "adamw", "zero"} and res["steps"] == 2
+    lines = [json.loads(l) for l in open(os.path.join(out, "metrics.jsonl"))] if os.path.exists(os.path.join(out, "metrics.jsonl")) \
+        else [json.loads(l) for l in open(os.path.join(out, "logs", "metrics.jsonl"))]
+    assert all("phases_peak_mb" in l and "fwd_bwd" in l["phases_peak_mb"] for l in lines)

@@ -14,33 +14,8 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from hippolm_b200.utils.flops import step_flops             # noqa: E402
 from hippolm_b200.utils.timing import load_measured_peaks   # noqa: E402
-
-
-def step_flops(hidden, heads, head_dim, layers, attn_interval, ffn, vocab, seq_len, tokens):
-    hd = heads * head_dim
-    n_attn = layers // attn_interval if attn_interval > 0 else 0
-    n_kda = layers - n_attn
-    kda_proj = (3 * hd + 2 * head_dim + heads) * hidden + 2 * head_dim * hd + hd * hidden   # q k v fg b, f/g low rank, o
-    att_proj = 3 * hd * hidden + hd * hidden
-    ffn_p = 3 * hidden * ffn
-    lin = n_kda * (kda_proj + ffn_p) + n_attn * (att_proj + ffn_p)
-    lce = vocab * hidden
-    per_tok = {"linears": 6.0 * lin, "lce_head": 6.0 * lce}
-    per_tok["attention"] = n_attn * 3.5 * 4.0 * (seq_len / 2.0) * head_dim * heads
-    # chunked KDA, chunk C = 64, per token and head: intra-chunk A / WY products ~ 8 C d, state products ~ 6 d^2 / ... forward;
-    # backward ~ 2.5x forward
-    C, d = 64, head_dim
-    kda_fwd = 2.0 * (4 * C * d + 3 * d * d)
-    per_tok["kda"] = n_kda * heads * 3.5 * kda_fwd
-    total_tok = sum(per_tok.values()) * tokens
-    # Muon: per matrix [m, n] (m <= n): 5 x (Gram m^2 n [symmetric: half of 2 m^2 n] + m^3 [half of 2 m^3] + 2 m^2 n)
-    def ns(m, n):
-        m, n = min(m, n), max(m, n)
-        return 5.0 * (m * m * n + m ** 3 + 2.0 * m * m * n)
-    mats = n_kda * [(hd, hidden)] * 3 + n_attn * [(hd, hidden)] * 3 + layers * [(hd, hidden)] + layers * [(ffn, hidden)] * 3
-    muon = sum(ns(a, b) for a, b in mats)
-    return per_tok, total_tok, muon
 
 
 def main():

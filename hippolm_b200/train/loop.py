@@ -424,6 +424,13 @@ def run_training_loop(ctx: TrainContext) -> Dict[str, Any]:
                 rec = {"step": ctx.step, "loss": loss, "lr_muon": out["lr_muon"], "lr_adamw": out["lr_adamw"],
                        "grad_norm": out["grad_norm"], "tokens": out["tokens"], "step_ms": step_ms_max,
                        "tok_per_s": toks, "found_inf": out["found_inf"]}
+                if out["tokens"] > 0:
+                    # analytic model FLOPs of the step over the device-timed step, per GPU, and its fraction of the measured
+                    # (else the fallback) sustained bf16 GEMM peak
+                    from ..utils.flops import utilisation
+                    from ..utils.timing import load_measured_peaks
+                    peaks = ctx.extras.setdefault("peaks", load_measured_peaks())
+                    rec.update(utilisation(ctx.cfg, int(args.seq_len), int(out["tokens"]), step_ms_max, mesh.world_size, peaks))
                 if timed:
                     rec["phases_ms"] = timer.summary()
                 if phase_mem is not None:

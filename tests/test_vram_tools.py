@@ -130,3 +130,32 @@ def test_profile_command_runs_steps_and_reports_phases(tmp_path, capsys):
     lines = [json.loads(l) for l in open(os.path.join(out, "metrics.jsonl"))] if os.path.exists(os.path.join(out, "metrics.jsonl")) \
         else [json.loads(l) for l in open(os.path.join(out, "logs", "metrics.jsonl"))]
     assert all("phases_peak_mb" in l and "fwd_bwd" in l["phases_peak_mb"] for l in lines)
+
+
+def test_training_metrics_carry_model_flops_and_utilisation(tmp_path):
+    """Every logged step has the analytic model TFLOP/s per GPU and its fraction of the GEMM peak; the numbers follow
+    from the FLOP model and the logged step time."""
+    import json
+    import os
+    import sys
+    from hippolm_b200.cli import parse_args
+    from hippolm_b200.config import HippoConfig
+    from hippolm_b200.utils.flops import config_step_flops, step_flops
+    from hippolm_b200.utils.timing import load_measured_peaks
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "scripts"))
+    import train as train_script
+    args = parse_args(["--config", os.path.join(root, "configs", "test", "quick.yml"), "--max_steps", "2",
+                       "--output_dir", str(tmp_path)])
+    run = train_script.train(args)
+    lines = [json.loads(l) for l in open(os.path.join(run, "metrics.jsonl"))]
+    cfg = HippoConfig.from_namespace(args)
+    pk = load_measured_peaks()
+    for l in lines:
+        _, total, _ = config_step_flops(cfg, args.seq_len, l["tokens"])
+        want = total / l["step_ms"] * 1e3 / 1e12
+        assert abs(l["model_tflops_per_gpu"] - want) <= 0.006 + 1e-3 * want
+        assert abs(l["mfu"] - want / pk["bf16_tflops_sustained"]) < 1e-3
+    # the 7B benchmark model: ~52.5 GFLOP per token, dominated by the linears
+    per_tok, total, muon = step_flops(4096, 32, 128, 32, 4, 14336, 128256, 8192, 131072)
+    assert 50e9 < sum(per_tok.values()) < 55e9 and per_tok["linears"] > 0.85 * sum(per_tok.values()) and muon < 0.1 * total
